@@ -1,0 +1,11 @@
+"""B200-native force path for compact two-layer MACE models.
+
+Host-side mirror of the reference evaluator interface (pybind class ``MACEKokkos``,
+symmetrix/source/cpp/mace_kokkos.cpp:262+) over a C-ABI shared library of
+hand-written sm_100a CUDA kernels (``csrc/``).  The directory name carries a
+hyphen, so the package is loaded under the importable name ``symmetrix_xl_b200``
+(see ``__graft_entry__.load_package``).
+"""
+from . import structure, modelgen  # noqa: F401
+
+__all__ = ["structure", "modelgen"]
