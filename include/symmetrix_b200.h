@@ -1,0 +1,132 @@
+/* C ABI of the B200 (sm_100a) force-path library: energy, forces and stress of a compact
+ * two-layer MACE model.  Plain pointers and sizes only; every array is caller-owned and is
+ * copied in or out during the call.  Each entry point names the interface of the reference
+ * (bonan-group/symmetrix-xl) that it replaces, by the file's path inside that project.
+ *
+ * Status: every function returns 0 on success, a negative SXB_ERR_* code otherwise;
+ * sxb_last_error() returns the message of the calling thread's last failure.  An evaluator is
+ * used by one host thread at a time and owns one CUDA stream.  There is no CPU fallback: a
+ * missing or unusable CUDA device makes sxb_create fail.
+ */
+#ifndef SYMMETRIX_B200_H
+#define SYMMETRIX_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SXB_OK 0
+#define SXB_ERR_INVALID_ARGUMENT (-1) /* std::invalid_argument in the reference (ValueError in Python) */
+#define SXB_ERR_RUNTIME (-2)          /* std::runtime_error / CUDA failure (RuntimeError) */
+#define SXB_ERR_STALE_GRAPH (-3)      /* graph generation token does not name the prepared graph */
+#define SXB_ERR_CAPACITY (-4)         /* graph exceeds 32-bit edge indexing (std::length_error) */
+
+typedef struct sxb_evaluator sxb_evaluator;
+
+typedef struct sxb_model_info {
+    int32_t num_elements;
+    int32_t num_channels;
+    int32_t l_max;          /* edge harmonics */
+    int32_t hidden_l_max;   /* hidden irreps (L_max) */
+    int32_t num_paths;      /* layer-1 tensor-product paths */
+    int32_t num_lme;        /* layer-1 output components */
+    int32_t shape_id;       /* compiled coupling structure in use */
+    int32_t reserved;
+    double r_cut;
+} sxb_model_info;
+
+/* Replaces the evaluator constructor MACEKokkos<float>(filename)
+ * (libsymmetrix/source/mace_kokkos_model.cpp:146; loader twin mace.cpp:2660-2959; Python binding
+ * symmetrix/source/cpp/mace_kokkos.cpp:262).  Reads a format-v4 compact model JSON, builds the
+ * spline tables and uploads the weights to CUDA device `device_ordinal`. */
+int sxb_create(const char* model_json_path, int device_ordinal, sxb_evaluator** out);
+void sxb_destroy(sxb_evaluator* evaluator);
+const char* sxb_last_error(void);
+
+/* Attributes atomic_numbers, atomic_energies, r_cut, num_channels ... of the Python class
+ * (symmetrix/source/cpp/mace_kokkos.cpp:2040-2087). */
+int sxb_model_info_get(const sxb_evaluator* evaluator, sxb_model_info* out);
+int sxb_atomic_numbers(const sxb_evaluator* evaluator, int32_t* out, int32_t capacity);
+
+/* Replaces _prepare_periodic_factorized_graph(node_types, positions, cell, inverse_cell,
+ * neighbor_cutoff) -> {generation, num_edges} (symmetrix/source/cpp/mace_kokkos.cpp:1580-1603;
+ * MACEKokkos::prepare_periodic_factorized_graph, mace_kokkos_factorized_lifecycle.cpp:1934-2316;
+ * cell list libsymmetrix/source/neighbor_graph_kokkos.cpp:39-405).  Host arrays:
+ * node_types int32[num_nodes] (indices into the model's element list), positions f64[3*num_nodes],
+ * cell and inverse_cell f64[9] row-major. */
+int sxb_prepare_periodic_graph(sxb_evaluator* evaluator, int32_t num_nodes, const int32_t* node_types,
+                               const double* positions, const double* cell, const double* inverse_cell,
+                               double neighbor_cutoff, uint64_t* generation, int64_t* num_edges);
+
+/* Replaces _prepare_factorized_graph(num_nodes, node_types, num_neigh, neigh_indices, neigh_types)
+ * (symmetrix/source/cpp/mace_kokkos.cpp:1561-1579): a receiver-major CSR graph built by the caller.
+ * `shifts` (int32[3*num_edges], periodic image of each source) and `cell` may be NULL when the
+ * graph will only be evaluated from explicit edge vectors (sxb_compute_edge_vectors). */
+int sxb_prepare_graph(sxb_evaluator* evaluator, int32_t num_nodes, const int32_t* node_types,
+                      const int32_t* num_neigh, const int32_t* neigh_indices, const int32_t* shifts,
+                      const double* cell, uint64_t* generation);
+
+/* Copies the prepared graph out in the caller's node order and the reference's edge order
+ * (the arrays KokkosNeighborGraph holds: receiver_offsets, sources, shifts;
+ * libsymmetrix/source/neighbor_graph_kokkos.hpp:13-23).  first_neigh int32[num_nodes+1],
+ * sources int32[num_edges], shifts int32[3*num_edges] (may be NULL). */
+int sxb_get_graph(sxb_evaluator* evaluator, uint64_t generation, int32_t* first_neigh, int32_t* sources,
+                  int32_t* shifts);
+
+/* Replaces _compute_prepared_factorized_positions(generation, positions)
+ * (symmetrix/source/cpp/mace_kokkos.cpp:1828-1836; MACEKokkos::compute_prepared_factorized_positions,
+ * mace_kokkos_factorized_lifecycle.cpp:3089-3123 -> compute_node_energies_forces,
+ * mace_kokkos_evaluate.cpp:314-611).  positions: host f64[3*num_nodes].  Copies positions to the
+ * device, runs the whole forward + reverse pipeline and the force/stress reduction. */
+int sxb_compute_positions(sxb_evaluator* evaluator, uint64_t generation, const double* positions);
+
+/* Same evaluation with positions already resident in device memory (f64[3*num_nodes] on the
+ * evaluator's device); nothing is copied to the host.  Device-view counterpart of the call above
+ * (MACEKokkos::compute_prepared_factorized_positions takes device views inside LAMMPS,
+ * pair_symmetrix/pair_symmetrix_mace_kokkos.cpp:1532-1568). */
+int sxb_compute_positions_device(sxb_evaluator* evaluator, uint64_t generation, const double* device_positions);
+
+/* Replaces _compute_prepared_factorized(generation, xyz, r) and the one-shot
+ * compute_node_energies_forces(num_nodes, node_types, num_neigh, neigh_indices, neigh_types, xyz, r)
+ * (symmetrix/source/cpp/mace_kokkos.cpp:1817-1827, 2169-2204): edge vectors xyz f64[3*num_edges] in
+ * the caller's edge order. */
+int sxb_compute_edge_vectors(sxb_evaluator* evaluator, uint64_t generation, const double* xyz);
+
+int sxb_synchronize(sxb_evaluator* evaluator);
+
+/* Results of the last compute, caller node / edge order, all f64.
+ * node_energies: property node_energies (mace_kokkos.cpp:2088-2095), [num_nodes].
+ * edge_forces:   property node_forces, the directed forces dE/d(xyz_ij) (2096-2102), [3*num_edges];
+ *                only filled when enabled with sxb_set_keep_edge_forces.
+ * atom forces:   _reduce_atom_forces (2103-2133), [num_nodes][3].
+ * stress:        _reduce_stress(volume) (2134-2154), [3][3] = -(1/volume) sum f_ij (x) xyz_ij.
+ * energy:        sum of node energies (calculator.py:3821-3858 sums them in f64). */
+int sxb_get_node_energies(sxb_evaluator* evaluator, double* out, int64_t capacity);
+int sxb_set_keep_edge_forces(sxb_evaluator* evaluator, int32_t enabled);
+int sxb_get_edge_forces(sxb_evaluator* evaluator, double* out, int64_t capacity);
+int sxb_reduce_atom_forces(sxb_evaluator* evaluator, uint64_t generation, double* out, int64_t capacity);
+int sxb_reduce_stress(sxb_evaluator* evaluator, uint64_t generation, double volume, double* out9);
+int sxb_get_energy(sxb_evaluator* evaluator, double* out);
+
+/* Device addresses of the last results (valid until the next prepare/compute): energy f64[1],
+ * forces f64[3*num_nodes] in caller order, virial f64[9] = sum f_ij (x) xyz_ij. */
+int sxb_device_results(sxb_evaluator* evaluator, const double** energy, const double** forces,
+                       const double** virial);
+
+/* Stage tensors of the last compute for parity tests, caller node order, converted to f64:
+ * "A0","M0","H1","Phi1","A1","M1","H2","H2_adj","A1_adj","dPhi1","H1_adj","M0_adj","A0_adj"
+ * (the public member vectors of the reference's serial evaluator, libsymmetrix/source/mace.hpp).
+ * Returns the element count through `count`; out may be NULL to query it. */
+int sxb_get_stage(sxb_evaluator* evaluator, const char* name, double* out, int64_t capacity, int64_t* count);
+
+/* Number of kernels this library launched since creation, and device time of the last compute in
+ * milliseconds (CUDA events on the evaluator's stream). */
+int sxb_launch_count(const sxb_evaluator* evaluator, int64_t* out);
+int sxb_last_compute_ms(const sxb_evaluator* evaluator, float* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -4,8 +4,9 @@ Host-side mirror of the reference evaluator interface (pybind class ``MACEKokkos
 symmetrix/source/cpp/mace_kokkos.cpp:262+) over a C-ABI shared library of
 hand-written sm_100a CUDA kernels (``csrc/``).  The directory name carries a
 hyphen, so the package is loaded under the importable name ``symmetrix_xl_b200``
-(see ``__graft_entry__.load_package``).
+(``__graft_entry__.load_package``).
 """
 from . import structure, modelgen  # noqa: F401
+from .evaluator import MACEB200, Calculator, load_library, LIBRARY_PATH, SIGNATURES  # noqa: F401
 
-__all__ = ["structure", "modelgen"]
+__all__ = ["structure", "modelgen", "MACEB200", "Calculator", "load_library", "LIBRARY_PATH", "SIGNATURES"]

@@ -1,0 +1,234 @@
+// extern "C" boundary (include/symmetrix_b200.h): translates exceptions into status codes and a
+// thread-local message, the way the reference's Python binding turns C++ exceptions into
+// ValueError / RuntimeError (symmetrix/source/cpp/mace_kokkos.cpp).
+#include "../../include/symmetrix_b200.h"
+
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "evaluator.hpp"
+
+struct sxb_evaluator {
+    sxb::Evaluator impl;
+    sxb_evaluator(const char* path, int device) : impl(path, device) {}
+};
+
+namespace {
+thread_local std::string g_last_error;
+
+template <typename F>
+int guarded(F&& body)
+{
+    try {
+        body();
+        return SXB_OK;
+    } catch (const sxb::StaleGraph& e) {
+        g_last_error = e.what();
+        return SXB_ERR_STALE_GRAPH;
+    } catch (const std::length_error& e) {
+        g_last_error = e.what();
+        return SXB_ERR_CAPACITY;
+    } catch (const std::invalid_argument& e) {
+        g_last_error = e.what();
+        return SXB_ERR_INVALID_ARGUMENT;
+    } catch (const std::out_of_range& e) {
+        g_last_error = e.what();
+        return SXB_ERR_INVALID_ARGUMENT;
+    } catch (const std::exception& e) {
+        g_last_error = e.what();
+        return SXB_ERR_RUNTIME;
+    } catch (...) {
+        g_last_error = "unknown failure";
+        return SXB_ERR_RUNTIME;
+    }
+}
+
+void require(const void* p, const char* what)
+{
+    if (p == nullptr) throw std::invalid_argument(std::string(what) + " must not be NULL.");
+}
+}  // namespace
+
+extern "C" {
+
+const char* sxb_last_error(void) { return g_last_error.c_str(); }
+
+int sxb_create(const char* model_json_path, int device_ordinal, sxb_evaluator** out)
+{
+    return guarded([&] {
+        require(model_json_path, "model_json_path");
+        require(out, "out");
+        *out = new sxb_evaluator(model_json_path, device_ordinal);
+    });
+}
+
+void sxb_destroy(sxb_evaluator* evaluator) { delete evaluator; }
+
+int sxb_model_info_get(const sxb_evaluator* ev, sxb_model_info* out)
+{
+    return guarded([&] {
+        require(ev, "evaluator");
+        require(out, "out");
+        const auto& m = ev->impl.model();
+        out->num_elements = m.num_elements;
+        out->num_channels = m.channels;
+        out->l_max = m.l_max;
+        out->hidden_l_max = m.hidden_l_max;
+        out->num_paths = m.num_paths;
+        out->num_lme = m.num_lme;
+        out->shape_id = m.shape_id;
+        out->reserved = 0;
+        out->r_cut = m.r_cut;
+    });
+}
+
+int sxb_atomic_numbers(const sxb_evaluator* ev, int32_t* out, int32_t capacity)
+{
+    return guarded([&] {
+        require(ev, "evaluator");
+        require(out, "out");
+        const auto& z = ev->impl.model().atomic_numbers;
+        if (capacity < static_cast<int32_t>(z.size())) throw std::invalid_argument("atomic_numbers buffer is too small.");
+        for (std::size_t i = 0; i < z.size(); ++i) out[i] = z[i];
+    });
+}
+
+int sxb_prepare_periodic_graph(sxb_evaluator* ev, int32_t num_nodes, const int32_t* node_types, const double* positions,
+                               const double* cell, const double* inverse_cell, double neighbor_cutoff, uint64_t* generation,
+                               int64_t* num_edges)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(node_types, "node_types"); require(positions, "positions");
+        require(cell, "cell"); require(inverse_cell, "inverse_cell"); require(generation, "generation");
+        const auto result = ev->impl.prepare_periodic_graph(num_nodes, node_types, positions, cell, inverse_cell, neighbor_cutoff);
+        *generation = result.first;
+        if (num_edges != nullptr) *num_edges = result.second;
+    });
+}
+
+int sxb_prepare_graph(sxb_evaluator* ev, int32_t num_nodes, const int32_t* node_types, const int32_t* num_neigh,
+                      const int32_t* neigh_indices, const int32_t* shifts, const double* cell, uint64_t* generation)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(node_types, "node_types"); require(num_neigh, "num_neigh");
+        require(neigh_indices, "neigh_indices"); require(generation, "generation");
+        *generation = ev->impl.prepare_graph(num_nodes, node_types, num_neigh, neigh_indices, shifts, cell);
+    });
+}
+
+int sxb_get_graph(sxb_evaluator* ev, uint64_t generation, int32_t* first_neigh, int32_t* sources, int32_t* shifts)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(first_neigh, "first_neigh"); require(sources, "sources");
+        ev->impl.get_graph(generation, first_neigh, sources, shifts);
+    });
+}
+
+int sxb_compute_positions(sxb_evaluator* ev, uint64_t generation, const double* positions)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(positions, "positions");
+        ev->impl.compute_positions(generation, positions, false);
+    });
+}
+
+int sxb_compute_positions_device(sxb_evaluator* ev, uint64_t generation, const double* device_positions)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(device_positions, "device_positions");
+        ev->impl.compute_positions(generation, device_positions, true);
+    });
+}
+
+int sxb_compute_edge_vectors(sxb_evaluator* ev, uint64_t generation, const double* xyz)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(xyz, "xyz");
+        ev->impl.compute_edge_vectors(generation, xyz);
+    });
+}
+
+int sxb_synchronize(sxb_evaluator* ev)
+{
+    return guarded([&] { require(ev, "evaluator"); ev->impl.synchronize(); });
+}
+
+int sxb_get_node_energies(sxb_evaluator* ev, double* out, int64_t capacity)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(out, "out");
+        if (capacity < ev->impl.num_nodes()) throw std::invalid_argument("node_energies buffer is too small.");
+        ev->impl.get_node_energies(out);
+    });
+}
+
+int sxb_set_keep_edge_forces(sxb_evaluator* ev, int32_t enabled)
+{
+    return guarded([&] { require(ev, "evaluator"); ev->impl.set_keep_edge_forces(enabled != 0); });
+}
+
+int sxb_get_edge_forces(sxb_evaluator* ev, double* out, int64_t capacity)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(out, "out");
+        if (capacity < 3 * ev->impl.num_edges()) throw std::invalid_argument("edge_forces buffer is too small.");
+        ev->impl.get_edge_forces(out);
+    });
+}
+
+int sxb_reduce_atom_forces(sxb_evaluator* ev, uint64_t generation, double* out, int64_t capacity)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(out, "out");
+        ev->impl.check_generation(generation);
+        if (capacity < 3L * ev->impl.num_nodes()) throw std::invalid_argument("atom_forces buffer is too small.");
+        ev->impl.get_atom_forces(out);
+    });
+}
+
+int sxb_reduce_stress(sxb_evaluator* ev, uint64_t generation, double volume, double* out9)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(out9, "out9");
+        ev->impl.check_generation(generation);
+        ev->impl.get_stress(volume, out9);
+    });
+}
+
+int sxb_get_energy(sxb_evaluator* ev, double* out)
+{
+    return guarded([&] { require(ev, "evaluator"); require(out, "out"); *out = ev->impl.energy(); });
+}
+
+int sxb_device_results(sxb_evaluator* ev, const double** energy, const double** forces, const double** virial)
+{
+    return guarded([&] {
+        require(ev, "evaluator");
+        ev->impl.require_results();
+        if (energy) *energy = ev->impl.device_energy();
+        if (forces) *forces = ev->impl.device_forces();
+        if (virial) *virial = ev->impl.device_virial();
+    });
+}
+
+int sxb_get_stage(sxb_evaluator* ev, const char* name, double* out, int64_t capacity, int64_t* count)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(name, "name");
+        const long n = ev->impl.get_stage(name, out, capacity);
+        if (count) *count = n;
+    });
+}
+
+int sxb_launch_count(const sxb_evaluator* ev, int64_t* out)
+{
+    return guarded([&] { require(ev, "evaluator"); require(out, "out"); *out = ev->impl.launches(); });
+}
+
+int sxb_last_compute_ms(const sxb_evaluator* ev, float* out)
+{
+    return guarded([&] { require(ev, "evaluator"); require(out, "out"); *out = ev->impl.last_ms(); });
+}
+
+}  // extern "C"

@@ -1,0 +1,552 @@
+// Receiver-sorted, warp-cooperative edge kernels of the force path (sm_100a).
+//
+// One thread block owns one receiver atom and has one thread per channel.  For a
+// chunk of the receiver's edges the block first computes the channel-independent
+// edge state once (spline interval and offset, spherical harmonics and, for the
+// reverse kernels, their Cartesian gradients) into shared memory; then every thread
+// walks the chunk for its own channel, evaluating the radial splines from the
+// coefficient table (coalesced over channels) and accumulating in registers.  Edge
+// state is regenerated here from the 16-byte geometry record and never stored
+// graph-wide; the receiver's sums need no atomics.
+//
+// Reference statements of the same math: layer 0 forward/reverse
+// libsymmetrix/source/mace.cpp:1356-1403 and 1486-1559 (with the H0 / W_A0 folding of
+// mace_kokkos_factorized_lifecycle.cpp:3988-4047); layer 1 forward/reverse
+// mace.cpp:2023-2083 and 2199-2302; harmonics mace.cpp:1269-1299; spline evaluation
+// cubic_spline_set.cpp:33-80; force and virial reduction
+// mace_kokkos_evaluate.cpp:92-106 and 157-186.
+#pragma once
+
+#include "common.cuh"
+#include "generated/structures.h"
+
+namespace sxb {
+
+constexpr int kEdgeChunk = 64;
+
+// ---------------------------------------------------------------------------------------------
+// Real spherical harmonics up to l = 3 of a unit direction, model convention: the vector is
+// permuted to (z, x, y), orthonormal harmonics are scaled by 2 sqrt(pi).  Each Y_lm is a
+// homogeneous polynomial P of degree l, so dY/dX = (grad P - l P u) / r (Euler's theorem).
+template <bool kGradient>
+__device__ __forceinline__ void harmonics16(float dx, float dy, float dz, float inv_r, float* __restrict__ Y,
+                                            float* __restrict__ gX, float* __restrict__ gY, float* __restrict__ gZ)
+{
+    // permuted frame and a second normalisation, as the reference's device path does
+    const float n = rsqrtf(dx * dx + dy * dy + dz * dz);
+    const float x = dz * n, y = dx * n, z = dy * n;
+    const float x2 = x * x, y2 = y * y, z2 = z * z;
+    // constants already multiplied by 2 sqrt(pi)
+    constexpr float c1 = 1.7320508075688772f;     // sqrt(3)
+    constexpr float a2 = 3.8729833462074170f;     // sqrt(15)
+    constexpr float b2 = 1.1180339887498949f;     // sqrt(5)/2
+    constexpr float h2 = 1.9364916731037085f;     // sqrt(15)/2
+    constexpr float c3 = 2.0916500663351889f;     // sqrt(35/8)
+    constexpr float d3 = 10.246950765959598f;     // sqrt(105)
+    constexpr float e3 = 1.6201851746019651f;     // sqrt(21/8)
+    constexpr float f3 = 1.3228756555322954f;     // sqrt(7)/2
+    constexpr float k3 = 5.1234753829797990f;     // sqrt(105)/2
+    const float q = 4.0f * z2 - x2 - y2;
+    float P[16];
+    P[0] = 1.0f;
+    P[1] = c1 * y; P[2] = c1 * z; P[3] = c1 * x;
+    P[4] = a2 * x * y; P[5] = a2 * y * z; P[6] = b2 * (2.0f * z2 - x2 - y2); P[7] = a2 * x * z; P[8] = h2 * (x2 - y2);
+    P[9] = c3 * y * (3.0f * x2 - y2); P[10] = d3 * x * y * z; P[11] = e3 * y * q;
+    P[12] = f3 * z * (2.0f * z2 - 3.0f * x2 - 3.0f * y2); P[13] = e3 * x * q; P[14] = k3 * z * (x2 - y2);
+    P[15] = c3 * x * (x2 - 3.0f * y2);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) Y[i] = P[i];
+    if constexpr (kGradient) {
+        float gx[16], gy[16], gz[16];   // polynomial gradients in the permuted frame
+        gx[0] = gy[0] = gz[0] = 0.0f;
+        gx[1] = 0.0f; gy[1] = c1; gz[1] = 0.0f;
+        gx[2] = 0.0f; gy[2] = 0.0f; gz[2] = c1;
+        gx[3] = c1; gy[3] = 0.0f; gz[3] = 0.0f;
+        gx[4] = a2 * y; gy[4] = a2 * x; gz[4] = 0.0f;
+        gx[5] = 0.0f; gy[5] = a2 * z; gz[5] = a2 * y;
+        gx[6] = -2.0f * b2 * x; gy[6] = -2.0f * b2 * y; gz[6] = 4.0f * b2 * z;
+        gx[7] = a2 * z; gy[7] = 0.0f; gz[7] = a2 * x;
+        gx[8] = 2.0f * h2 * x; gy[8] = -2.0f * h2 * y; gz[8] = 0.0f;
+        gx[9] = 6.0f * c3 * x * y; gy[9] = 3.0f * c3 * (x2 - y2); gz[9] = 0.0f;
+        gx[10] = d3 * y * z; gy[10] = d3 * x * z; gz[10] = d3 * x * y;
+        gx[11] = -2.0f * e3 * x * y; gy[11] = e3 * (q - 2.0f * y2); gz[11] = 8.0f * e3 * y * z;
+        gx[12] = -6.0f * f3 * x * z; gy[12] = -6.0f * f3 * y * z; gz[12] = f3 * (6.0f * z2 - 3.0f * x2 - 3.0f * y2);
+        gx[13] = e3 * (q - 2.0f * x2); gy[13] = -2.0f * e3 * x * y; gz[13] = 8.0f * e3 * x * z;
+        gx[14] = 2.0f * k3 * x * z; gy[14] = -2.0f * k3 * y * z; gz[14] = k3 * (x2 - y2);
+        gx[15] = 3.0f * c3 * (x2 - y2); gy[15] = -6.0f * c3 * x * y; gz[15] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float l = i < 1 ? 0.0f : (i < 4 ? 1.0f : (i < 9 ? 2.0f : 3.0f));
+            const float radial = l * P[i];
+            // back to the original frame: X is the permuted y, Y the permuted z, Z the permuted x
+            gX[i] = (gy[i] - y * radial) * inv_r;
+            gY[i] = (gz[i] - z * radial) * inv_r;
+            gZ[i] = (gx[i] - x * radial) * inv_r;
+        }
+    }
+}
+
+// Spline evaluation point in float, as the reference forms it (cubic_spline_set.cpp:33-47).
+__device__ __forceinline__ void spline_point(const SplineGrid& g, float r, int& interval, float& x)
+{
+    interval = static_cast<int>(floorf((r - g.x0) / g.h));
+    x = r - g.x0 - g.h * static_cast<float>(interval);
+    if (interval < 0) {
+        interval = 0;
+        x = 0.0f;
+    } else if (interval >= g.intervals) {
+        interval = g.intervals - 1;
+        x = g.h;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Per-step geometry: xyz_ij = r_j - r_i + shift * cell in double, then the float record.
+// One warp per receiver, lanes over its edges.
+__global__ void geometry_from_positions_kernel(int num_nodes, const int* __restrict__ first,
+                                               const int* __restrict__ sources, const int* __restrict__ shifts,
+                                               const double* __restrict__ positions, const int* __restrict__ original,
+                                               const double* __restrict__ cell, EdgeGeom* __restrict__ geom,
+                                               int* __restrict__ error_flag)
+{
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= num_nodes) return;
+    const int oi = original[warp];
+    const double xi = positions[3 * oi], yi = positions[3 * oi + 1], zi = positions[3 * oi + 2];
+    const int begin = first[warp], end = first[warp + 1];
+    for (int e = begin + lane; e < end; e += 32) {
+        const int oj = original[sources[e]];
+        const double sx = shifts[3 * e], sy = shifts[3 * e + 1], sz = shifts[3 * e + 2];
+        const double dx = positions[3 * oj] - xi + sx * cell[0] + sy * cell[3] + sz * cell[6];
+        const double dy = positions[3 * oj + 1] - yi + sx * cell[1] + sy * cell[4] + sz * cell[7];
+        const double dz = positions[3 * oj + 2] - zi + sx * cell[2] + sy * cell[5] + sz * cell[8];
+        const double r = sqrt(dx * dx + dy * dy + dz * dz);
+        if (!(r > 0.0) || !isfinite(r)) atomicOr(error_flag, 1);
+        EdgeGeom g;
+        g.ux = static_cast<float>(dx / r);
+        g.uy = static_cast<float>(dy / r);
+        g.uz = static_cast<float>(dz / r);
+        g.r = static_cast<float>(r);
+        geom[e] = g;
+    }
+}
+
+// Geometry from caller-supplied edge vectors (original edge order == internal edge order of
+// each receiver; ``edge_map`` gives the caller's edge index of every internal edge).
+__global__ void geometry_from_vectors_kernel(long num_edges, const double* __restrict__ xyz,
+                                             const int* __restrict__ edge_map, EdgeGeom* __restrict__ geom,
+                                             int* __restrict__ error_flag)
+{
+    const long e = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= num_edges) return;
+    const long o = edge_map[e];
+    const double dx = xyz[3 * o], dy = xyz[3 * o + 1], dz = xyz[3 * o + 2];
+    const double r = sqrt(dx * dx + dy * dy + dz * dz);
+    if (!(r > 0.0) || !isfinite(r)) atomicOr(error_flag, 1);
+    EdgeGeom g;
+    g.ux = static_cast<float>(dx / r);
+    g.uy = static_cast<float>(dy / r);
+    g.uz = static_cast<float>(dz / r);
+    g.r = static_cast<float>(r);
+    geom[e] = g;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Shared-memory edge state of one chunk.
+template <bool kGradient>
+struct ChunkState {
+    float y[kEdgeChunk][16];
+    float gx[kGradient ? kEdgeChunk : 1][16];
+    float gy[kGradient ? kEdgeChunk : 1][16];
+    float gz[kGradient ? kEdgeChunk : 1][16];
+    float x[kEdgeChunk];          // offset inside the spline interval
+    float dir[kGradient ? kEdgeChunk : 1][3];
+    float len[kGradient ? kEdgeChunk : 1];
+    int base[kEdgeChunk];         // first coefficient of (pair, interval), or -1 for an inactive edge
+    int source[kEdgeChunk];
+};
+
+// Fills the chunk state for edges [begin, begin+count) of one receiver.
+// ``pair_stride`` = intervals*4*functions; pair index chosen by ``kOrderedPairs``.
+template <bool kGradient, bool kOrderedPairs>
+__device__ __forceinline__ void fill_chunk(ChunkState<kGradient>& s, int begin, int count, const int* __restrict__ sources,
+                                           const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype,
+                                           int type_i, int num_active, const SplineGrid& grid, int functions)
+{
+    for (int t = threadIdx.x; t < count; t += blockDim.x) {
+        const int e = begin + t;
+        const EdgeGeom g = geom[e];
+        const int j = sources[e];
+        s.source[t] = j;
+        if (!(g.r < grid.r_cut)) {
+            s.base[t] = -1;
+            continue;
+        }
+        int interval;
+        float x;
+        spline_point(grid, g.r, interval, x);
+        const int type_j = atype[j];
+        int pair;
+        if constexpr (kOrderedPairs) {
+            pair = type_i * num_active + type_j;
+        } else {
+            pair = 0;   // layer-1 tables do not depend on the species pair without a distance transform
+        }
+        s.base[t] = (pair * grid.intervals + interval) * 4 * functions;
+        s.x[t] = x;
+        const float inv_r = 1.0f / g.r;
+        if constexpr (kGradient) {
+            harmonics16<true>(g.ux, g.uy, g.uz, inv_r, s.y[t], s.gx[t], s.gy[t], s.gz[t]);
+            s.dir[t][0] = g.ux; s.dir[t][1] = g.uy; s.dir[t][2] = g.uz;
+            s.len[t] = g.r;
+        } else {
+            harmonics16<false>(g.ux, g.uy, g.uz, inv_r, s.y[t], nullptr, nullptr, nullptr);
+        }
+    }
+}
+
+__device__ __forceinline__ float cubic(float c0, float c1, float c2, float c3, float x, float xx, float xxx)
+{
+    return fmaf(c3, xxx, fmaf(c2, xx, fmaf(c1, x, c0)));
+}
+__device__ __forceinline__ float cubic_derivative(float c1, float c2, float c3, float x, float xx)
+{
+    return fmaf(3.0f * c3, xx, fmaf(2.0f * c2, x, c1));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Layer 0 forward: A0_i[lm,k] = sum_j S0[pair(i,j), r_ij][l,k] * Y_ij[lm].
+__global__ void __launch_bounds__(256)
+l0_forward_kernel(int num_nodes, int C, const int* __restrict__ first, const int* __restrict__ sources,
+                  const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype, int num_active,
+                  SplineGrid grid, const float* __restrict__ table, float* __restrict__ A0)
+{
+    __shared__ ChunkState<false> s;
+    const int i = blockIdx.x;
+    const int k = threadIdx.x;
+    const int F = 4 * C;
+    const int type_i = atype[i];
+    const int begin = first[i], end = first[i + 1];
+    float acc[16];
+#pragma unroll
+    for (int lm = 0; lm < 16; ++lm) acc[lm] = 0.0f;
+    for (int chunk = begin; chunk < end; chunk += kEdgeChunk) {
+        const int count = min(kEdgeChunk, end - chunk);
+        __syncthreads();
+        fill_chunk<false, true>(s, chunk, count, sources, geom, atype, type_i, num_active, grid, F);
+        __syncthreads();
+        for (int t = 0; t < count; ++t) {
+            const int base = s.base[t];
+            if (base < 0) continue;
+            const float x = s.x[t], xx = x * x, xxx = xx * x;
+            const float* c = table + base + k;
+            float R[4];
+#pragma unroll
+            for (int l = 0; l < 4; ++l)
+                R[l] = cubic(c[l * C], c[F + l * C], c[2 * F + l * C], c[3 * F + l * C], x, xx, xxx);
+            const float* y = s.y[t];
+            acc[0] = fmaf(R[0], y[0], acc[0]);
+#pragma unroll
+            for (int lm = 1; lm < 4; ++lm) acc[lm] = fmaf(R[1], y[lm], acc[lm]);
+#pragma unroll
+            for (int lm = 4; lm < 9; ++lm) acc[lm] = fmaf(R[2], y[lm], acc[lm]);
+#pragma unroll
+            for (int lm = 9; lm < 16; ++lm) acc[lm] = fmaf(R[3], y[lm], acc[lm]);
+        }
+    }
+    float* out = A0 + static_cast<size_t>(i) * 16 * C + k;
+#pragma unroll
+    for (int lm = 0; lm < 16; ++lm) out[lm * C] = acc[lm];
+}
+
+// Block-level force bookkeeping shared by the two reverse kernels.  Each warp leaves its
+// channel-partial edge force in ``partial``; after the chunk one thread per edge sums the warps,
+// pushes +f to the source atom, adds -f to the receiver total and f (x) xyz to the virial.
+struct ForceOutputs {
+    double* atom_forces;     // [N][3], internal node order
+    double* virial_slots;    // [kVirialSlots][9]
+    double* edge_forces;     // optional [E][3] directed forces dE/d(xyz_ij), may be nullptr
+    int accumulate_edge;     // 0: overwrite edge_forces, 1: add
+};
+
+__device__ __forceinline__ void warp_reduce3(float& a, float& b, float& c)
+{
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, offset);
+        b += __shfl_xor_sync(0xffffffffu, b, offset);
+        c += __shfl_xor_sync(0xffffffffu, c, offset);
+    }
+}
+
+template <int kMaxWarps>
+struct ForceScratch {
+    float partial[kEdgeChunk][kMaxWarps][3];
+    double receiver[3];
+    double virial[9];
+};
+
+template <int kMaxWarps>
+__device__ __forceinline__ void flush_chunk_forces(ForceScratch<kMaxWarps>& fs, const ChunkState<true>& s, int chunk_begin,
+                                                   int count, int num_warps, const ForceOutputs& out)
+{
+    // called by all threads after a __syncthreads(); threads t < count own one edge each
+    double fx = 0.0, fy = 0.0, fz = 0.0;
+    double v[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+    for (int t = threadIdx.x; t < count; t += blockDim.x) {
+        if (s.base[t] < 0) {
+            if (out.edge_forces != nullptr && !out.accumulate_edge) {
+                double* ef = out.edge_forces + 3 * static_cast<size_t>(chunk_begin + t);
+                ef[0] = ef[1] = ef[2] = 0.0;
+            }
+            continue;
+        }
+        float px = 0.0f, py = 0.0f, pz = 0.0f;
+        for (int w = 0; w < num_warps; ++w) {
+            px += fs.partial[t][w][0];
+            py += fs.partial[t][w][1];
+            pz += fs.partial[t][w][2];
+        }
+        // directed force dE/d(xyz_ij) with the reference's sign: force -= adjoint * (...)
+        const double ex = -static_cast<double>(px), ey = -static_cast<double>(py), ez = -static_cast<double>(pz);
+        const int j = s.source[t];
+        atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j), ex);
+        atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 1, ey);
+        atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 2, ez);
+        fx -= ex; fy -= ey; fz -= ez;
+        const double len = s.len[t];
+        const double rx = len * s.dir[t][0], ry = len * s.dir[t][1], rz = len * s.dir[t][2];
+        v[0] += ex * rx; v[1] += ex * ry; v[2] += ex * rz;
+        v[3] += ey * rx; v[4] += ey * ry; v[5] += ey * rz;
+        v[6] += ez * rx; v[7] += ez * ry; v[8] += ez * rz;
+        if (out.edge_forces != nullptr) {
+            double* ef = out.edge_forces + 3 * static_cast<size_t>(chunk_begin + t);
+            if (out.accumulate_edge) { ef[0] += ex; ef[1] += ey; ef[2] += ez; }
+            else { ef[0] = ex; ef[1] = ey; ef[2] = ez; }
+        }
+    }
+    // only the first two warps can hold non-zero sums (count <= 64)
+    if (threadIdx.x < kEdgeChunk) {
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            fx += __shfl_xor_sync(0xffffffffu, fx, offset);
+            fy += __shfl_xor_sync(0xffffffffu, fy, offset);
+            fz += __shfl_xor_sync(0xffffffffu, fz, offset);
+#pragma unroll
+            for (int q = 0; q < 9; ++q) v[q] += __shfl_xor_sync(0xffffffffu, v[q], offset);
+        }
+        if ((threadIdx.x & 31) == 0) {
+            atomicAdd(&fs.receiver[0], fx);
+            atomicAdd(&fs.receiver[1], fy);
+            atomicAdd(&fs.receiver[2], fz);
+#pragma unroll
+            for (int q = 0; q < 9; ++q) atomicAdd(&fs.virial[q], v[q]);
+        }
+    }
+}
+
+template <int kMaxWarps>
+__device__ __forceinline__ void finish_receiver_forces(ForceScratch<kMaxWarps>& fs, int receiver, const ForceOutputs& out)
+{
+    __syncthreads();
+    if (threadIdx.x < 3) atomicAdd(out.atom_forces + 3 * static_cast<size_t>(receiver) + threadIdx.x, fs.receiver[threadIdx.x]);
+    if (threadIdx.x < 9) {
+        const int slot = receiver % kVirialSlots;
+        atomicAdd(out.virial_slots + slot * 9 + threadIdx.x, fs.virial[threadIdx.x]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Layer 0 reverse: f_ij -= sum_{lm,k} A0_adj_i[lm,k] * (rhat S0' Y + S0 grad Y).
+__global__ void __launch_bounds__(256)
+l0_reverse_kernel(int num_nodes, int C, const int* __restrict__ first, const int* __restrict__ sources,
+                  const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype, int num_active,
+                  SplineGrid grid, const float* __restrict__ table, const float* __restrict__ A0_adj, ForceOutputs out)
+{
+    __shared__ ChunkState<true> s;
+    __shared__ ForceScratch<8> fs;
+    const int i = blockIdx.x;
+    const int k = threadIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, num_warps = blockDim.x >> 5;
+    const int F = 4 * C;
+    const int type_i = atype[i];
+    const int begin = first[i], end = first[i + 1];
+    if (threadIdx.x < 3) fs.receiver[threadIdx.x] = 0.0;
+    if (threadIdx.x < 9) fs.virial[threadIdx.x] = 0.0;
+    float adj[16];
+    const float* in = A0_adj + static_cast<size_t>(i) * 16 * C + k;
+#pragma unroll
+    for (int lm = 0; lm < 16; ++lm) adj[lm] = in[lm * C];
+    for (int chunk = begin; chunk < end; chunk += kEdgeChunk) {
+        const int count = min(kEdgeChunk, end - chunk);
+        __syncthreads();
+        fill_chunk<true, true>(s, chunk, count, sources, geom, atype, type_i, num_active, grid, F);
+        __syncthreads();
+        for (int t = 0; t < count; ++t) {
+            const int base = s.base[t];
+            if (base < 0) continue;
+            const float x = s.x[t], xx = x * x, xxx = xx * x;
+            const float* c = table + base + k;
+            const float* y = s.y[t];
+            const float* gx = s.gx[t];
+            const float* gy = s.gy[t];
+            const float* gz = s.gz[t];
+            float radial = 0.0f, fx = 0.0f, fy = 0.0f, fz = 0.0f;
+#pragma unroll
+            for (int l = 0; l < 4; ++l) {
+                const float c0 = c[l * C], c1 = c[F + l * C], c2 = c[2 * F + l * C], c3 = c[3 * F + l * C];
+                const float R = cubic(c0, c1, c2, c3, x, xx, xxx);
+                const float dR = cubic_derivative(c1, c2, c3, x, xx);
+                float ya = 0.0f;
+#pragma unroll
+                for (int lm = l * l; lm < (l + 1) * (l + 1); ++lm) {
+                    ya = fmaf(y[lm], adj[lm], ya);
+                    const float a = R * adj[lm];
+                    fx = fmaf(a, gx[lm], fx);
+                    fy = fmaf(a, gy[lm], fy);
+                    fz = fmaf(a, gz[lm], fz);
+                }
+                radial = fmaf(dR, ya, radial);
+            }
+            fx = fmaf(radial, s.dir[t][0], fx);
+            fy = fmaf(radial, s.dir[t][1], fy);
+            fz = fmaf(radial, s.dir[t][2], fz);
+            warp_reduce3(fx, fy, fz);
+            if (lane == 0) {
+                fs.partial[t][warp][0] = fx;
+                fs.partial[t][warp][1] = fy;
+                fs.partial[t][warp][2] = fz;
+            }
+        }
+        __syncthreads();
+        flush_chunk_forces<8>(fs, s, chunk, count, num_warps, out);
+    }
+    finish_receiver_forces<8>(fs, i, out);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Layer 1 kernels, one instantiation per compiled coupling structure.
+//   forward:  Phi1_i[lme,k] = sum_terms cg * sum_j R1_ij[path,k] Y_ij[lm1] H1_j[lm2,k]
+//   reverse:  row adjoints from dPhi1_i, then per edge the force and the source adjoint
+//             H1_adj_j[lm2,k] += sum R1 Y adj  (vector red.add into the source row)
+#define SXB_TERM_FORWARD(term, row, lme) out_lme[lme] = fmaf(cgc.cg[term], acc[row], out_lme[lme]);
+#define SXB_TERM_TRANSPOSE(term, row, lme) adj[row] = fmaf(cgc.cg[term], dphi[lme], adj[row]);
+
+#define SXB_DEFINE_L1_KERNELS(NAME)                                                                                  \
+    __global__ void __launch_bounds__(256)                                                                           \
+    l1_forward_kernel_##NAME(int num_nodes, int C, const int* __restrict__ first, const int* __restrict__ sources,   \
+                             const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype,             \
+                             SplineGrid grid, const float* __restrict__ table, const float* __restrict__ H1,         \
+                             const __grid_constant__ CouplingConstants cgc, float* __restrict__ Phi1)                \
+    {                                                                                                                \
+        constexpr int NP = SXB_##NAME##_NUM_PATHS, NR = SXB_##NAME##_NUM_ROWS, NH = SXB_##NAME##_NUM_HIDDEN;          \
+        constexpr int NE = SXB_##NAME##_NUM_LME;                                                                     \
+        __shared__ ChunkState<false> s;                                                                              \
+        const int i = blockIdx.x;                                                                                    \
+        const int k = threadIdx.x;                                                                                   \
+        const int F = NP * C;                                                                                        \
+        const int begin = first[i], end = first[i + 1];                                                              \
+        float acc[NR];                                                                                               \
+        _Pragma("unroll") for (int r_ = 0; r_ < NR; ++r_) acc[r_] = 0.0f;                                            \
+        for (int chunk = begin; chunk < end; chunk += kEdgeChunk) {                                                  \
+            const int count = min(kEdgeChunk, end - chunk);                                                          \
+            __syncthreads();                                                                                         \
+            fill_chunk<false, false>(s, chunk, count, sources, geom, atype, 0, 1, grid, F);                          \
+            __syncthreads();                                                                                         \
+            for (int t = 0; t < count; ++t) {                                                                        \
+                const int base = s.base[t];                                                                          \
+                if (base < 0) continue;                                                                              \
+                const float x = s.x[t], xx = x * x, xxx = xx * x;                                                    \
+                const float* c = table + base + k;                                                                   \
+                float R[NP];                                                                                         \
+                _Pragma("unroll") for (int p = 0; p < NP; ++p)                                                       \
+                    R[p] = cubic(c[p * C], c[F + p * C], c[2 * F + p * C], c[3 * F + p * C], x, xx, xxx);            \
+                const float* hsrc = H1 + static_cast<size_t>(s.source[t]) * NH * C + k;                              \
+                float h[NH];                                                                                         \
+                _Pragma("unroll") for (int q = 0; q < NH; ++q) h[q] = hsrc[q * C];                                   \
+                float y[16];                                                                                         \
+                _Pragma("unroll") for (int q = 0; q < 16; ++q) y[q] = s.y[t][q];                                     \
+                SXB_##NAME##_L1_FORWARD_BODY                                                                         \
+            }                                                                                                        \
+        }                                                                                                            \
+        float out_lme[NE];                                                                                           \
+        _Pragma("unroll") for (int q = 0; q < NE; ++q) out_lme[q] = 0.0f;                                            \
+        SXB_##NAME##_TERMS(SXB_TERM_FORWARD)                                                                         \
+        float* out = Phi1 + static_cast<size_t>(i) * NE * C + k;                                                     \
+        _Pragma("unroll") for (int q = 0; q < NE; ++q) out[q * C] = out_lme[q];                                      \
+    }                                                                                                                \
+                                                                                                                     \
+    __global__ void __launch_bounds__(256)                                                                           \
+    l1_reverse_kernel_##NAME(int num_nodes, int C, const int* __restrict__ first, const int* __restrict__ sources,   \
+                             const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype,             \
+                             SplineGrid grid, const float* __restrict__ table, const float* __restrict__ H1,         \
+                             const float* __restrict__ dPhi1, const __grid_constant__ CouplingConstants cgc,         \
+                             float* __restrict__ H1_adj, ForceOutputs out)                                           \
+    {                                                                                                                \
+        constexpr int NP = SXB_##NAME##_NUM_PATHS, NR = SXB_##NAME##_NUM_ROWS, NH = SXB_##NAME##_NUM_HIDDEN;          \
+        constexpr int NE = SXB_##NAME##_NUM_LME;                                                                     \
+        __shared__ ChunkState<true> s;                                                                               \
+        __shared__ ForceScratch<8> fs;                                                                               \
+        const int i = blockIdx.x;                                                                                    \
+        const int k = threadIdx.x;                                                                                   \
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, num_warps = blockDim.x >> 5;                     \
+        const int F = NP * C;                                                                                        \
+        const int begin = first[i], end = first[i + 1];                                                              \
+        if (threadIdx.x < 3) fs.receiver[threadIdx.x] = 0.0;                                                         \
+        if (threadIdx.x < 9) fs.virial[threadIdx.x] = 0.0;                                                           \
+        float adj[NR];                                                                                               \
+        {                                                                                                            \
+            float dphi[NE];                                                                                          \
+            const float* in = dPhi1 + static_cast<size_t>(i) * NE * C + k;                                           \
+            _Pragma("unroll") for (int q = 0; q < NE; ++q) dphi[q] = in[q * C];                                      \
+            _Pragma("unroll") for (int r_ = 0; r_ < NR; ++r_) adj[r_] = 0.0f;                                        \
+            SXB_##NAME##_TERMS(SXB_TERM_TRANSPOSE)                                                                   \
+        }                                                                                                            \
+        for (int chunk = begin; chunk < end; chunk += kEdgeChunk) {                                                  \
+            const int count = min(kEdgeChunk, end - chunk);                                                          \
+            __syncthreads();                                                                                         \
+            fill_chunk<true, false>(s, chunk, count, sources, geom, atype, 0, 1, grid, F);                           \
+            __syncthreads();                                                                                         \
+            for (int t = 0; t < count; ++t) {                                                                        \
+                const int base = s.base[t];                                                                          \
+                if (base < 0) continue;                                                                              \
+                const float x = s.x[t], xx = x * x, xxx = xx * x;                                                    \
+                const float* c = table + base + k;                                                                   \
+                float R[NP], dR[NP];                                                                                 \
+                _Pragma("unroll") for (int p = 0; p < NP; ++p) {                                                     \
+                    const float c0 = c[p * C], c1 = c[F + p * C], c2 = c[2 * F + p * C], c3 = c[3 * F + p * C];      \
+                    R[p] = cubic(c0, c1, c2, c3, x, xx, xxx);                                                        \
+                    dR[p] = cubic_derivative(c1, c2, c3, x, xx);                                                     \
+                }                                                                                                    \
+                const size_t source_row = static_cast<size_t>(s.source[t]) * NH * C + k;                             \
+                float h[NH], hadj[NH];                                                                               \
+                _Pragma("unroll") for (int q = 0; q < NH; ++q) { h[q] = H1[source_row + q * C]; hadj[q] = 0.0f; }    \
+                float y[16], ang[16];                                                                                \
+                _Pragma("unroll") for (int q = 0; q < 16; ++q) { y[q] = s.y[t][q]; ang[q] = 0.0f; }                  \
+                float radial = 0.0f;                                                                                 \
+                SXB_##NAME##_L1_REVERSE_BODY                                                                         \
+                _Pragma("unroll") for (int q = 0; q < NH; ++q) atomicAdd(H1_adj + source_row + q * C, hadj[q]);      \
+                float fx = radial * s.dir[t][0], fy = radial * s.dir[t][1], fz = radial * s.dir[t][2];               \
+                _Pragma("unroll") for (int q = 0; q < 16; ++q) {                                                     \
+                    fx = fmaf(ang[q], s.gx[t][q], fx);                                                               \
+                    fy = fmaf(ang[q], s.gy[t][q], fy);                                                               \
+                    fz = fmaf(ang[q], s.gz[t][q], fz);                                                               \
+                }                                                                                                    \
+                warp_reduce3(fx, fy, fz);                                                                            \
+                if (lane == 0) {                                                                                     \
+                    fs.partial[t][warp][0] = fx;                                                                     \
+                    fs.partial[t][warp][1] = fy;                                                                     \
+                    fs.partial[t][warp][2] = fz;                                                                     \
+                }                                                                                                    \
+            }                                                                                                        \
+            __syncthreads();                                                                                         \
+            flush_chunk_forces<8>(fs, s, chunk, count, num_warps, out);                                              \
+        }                                                                                                            \
+        finish_receiver_forces<8>(fs, i, out);                                                                       \
+    }
+
+SXB_DEFINE_L1_KERNELS(S0)
+SXB_DEFINE_L1_KERNELS(S1)
+
+}  // namespace sxb

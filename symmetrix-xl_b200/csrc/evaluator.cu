@@ -1,0 +1,620 @@
+// Evaluator: owns the model tables, the prepared graph and the work buffers on one B200, and
+// sequences the forward + reverse pipeline of the force path on one stream.  Stage order follows
+// the reference driver (libsymmetrix/source/mace_kokkos_evaluate.cpp:314-611 and the serial
+// statement libsymmetrix/source/mace.cpp:232-319).
+#include "evaluator.hpp"
+
+#include <cub/device/device_scan.cuh>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <limits>
+#include <numeric>
+
+#include "edge_kernels.cuh"
+#include "graph_kernels.cuh"
+#include "node_kernels.cuh"
+
+namespace sxb {
+
+namespace {
+
+template <typename T>
+void upload(DeviceBuffer<T>& buffer, const std::vector<T>& host, cudaStream_t stream)
+{
+    buffer.reserve(host.size());
+    if (!host.empty())
+        SXB_CUDA(cudaMemcpyAsync(buffer.ptr, host.data(), host.size() * sizeof(T), cudaMemcpyHostToDevice, stream));
+}
+
+__global__ void unpermute_doubles_kernel(int n, int width, const int* __restrict__ original, const double* __restrict__ in,
+                                         double* __restrict__ out)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int o = original[i];
+    for (int q = 0; q < width; ++q) out[static_cast<size_t>(o) * width + q] = in[static_cast<size_t>(i) * width + q];
+}
+
+__global__ void unpermute_stage_kernel(long n, long row, const int* __restrict__ original, const float* __restrict__ in,
+                                       double* __restrict__ out)
+{
+    const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= n * row) return;
+    const long node = idx / row, q = idx % row;
+    out[static_cast<long>(original[node]) * row + q] = static_cast<double>(in[idx]);
+}
+
+__global__ void unpermute_edges_kernel(long num_edges, const int* __restrict__ edge_map, const double* __restrict__ in,
+                                       double* __restrict__ out)
+{
+    const long e = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= num_edges) return;
+    const long o = edge_map[e];
+    out[3 * o] = in[3 * e];
+    out[3 * o + 1] = in[3 * e + 1];
+    out[3 * o + 2] = in[3 * e + 2];
+}
+
+__global__ void narrow_offsets_kernel(int n, const long long* __restrict__ wide, int* __restrict__ narrow)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i <= n) narrow[i] = static_cast<int>(wide[i]);
+}
+
+inline int blocks_for(long n, int threads) { return static_cast<int>((n + threads - 1) / threads); }
+
+}  // namespace
+
+Evaluator::Evaluator(const std::string& json_path, int device_ordinal) : device_(device_ordinal)
+{
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0)
+        throw std::runtime_error("No CUDA device is available; this library has no CPU fallback.");
+    if (device_ordinal < 0 || device_ordinal >= count) throw std::invalid_argument("CUDA device ordinal is out of range.");
+    SXB_CUDA(cudaSetDevice(device_));
+    model_ = load_model(json_path);
+    if (model_.shape_id > 1)
+        throw std::invalid_argument("This build carries kernels for hidden irreps 0e and 0e+1o only.");
+    if (model_.a0_scaled || model_.a1_scaled)
+        throw std::invalid_argument("Density-scaled (A0_scaled / A1_scaled) models are not supported yet.");
+    SXB_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+    SXB_CUDA(cudaEventCreate(&event_begin_));
+    SXB_CUDA(cudaEventCreate(&event_end_));
+
+    const int C = model_.channels;
+    // layer-1 table [interval][4][paths*C] in float
+    std::vector<float> r1(model_.r1_coeff.size());
+    for (std::size_t i = 0; i < r1.size(); ++i) r1[i] = static_cast<float>(model_.r1_coeff[i]);
+    upload(r1_table_, r1, stream_);
+    upload(m0_weights_, model_.m0_weights, stream_);
+    upload(m1_weights_, model_.m1_weights, stream_);
+    upload(w_h1_, model_.w_h1, stream_);
+    for (int l = 0; l <= model_.l_max; ++l) upload(w_a1_[l], model_.w_a1[l], stream_);
+    upload(h2_skip_, model_.h2_skip, stream_);
+    upload(h2_m1_, model_.h2_m1, stream_);
+    upload(readout1_, model_.readout1, stream_);
+    upload(readout2_w1_, model_.readout2_w1, stream_);
+    upload(readout2_w2_, model_.readout2_w2, stream_);
+    upload(atomic_energies_, model_.atomic_energies, stream_);
+    std::memset(&coupling_, 0, sizeof(coupling_));
+    if (model_.num_terms > 256) throw std::invalid_argument("Too many coupling terms.");
+    for (int t = 0; t < model_.num_terms; ++t) coupling_.cg[t] = model_.cg[t];
+    grid_.x0 = static_cast<float>(model_.spline_x0);
+    grid_.h = static_cast<float>(model_.spline_h);
+    grid_.r_cut = static_cast<float>(model_.r_cut);
+    grid_.intervals = model_.spline_points - 1;
+    totals_.reserve(10);
+    energy_slots_.reserve(kVirialSlots);
+    virial_slots_.reserve(kVirialSlots * 9);
+    error_flag_.reserve(1);
+    cell_.reserve(9);
+    inv_cell_.reserve(9);
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+    (void)C;
+}
+
+Evaluator::~Evaluator()
+{
+    cudaSetDevice(device_);
+    if (event_begin_) cudaEventDestroy(event_begin_);
+    if (event_end_) cudaEventDestroy(event_end_);
+    if (stream_) cudaStreamDestroy(stream_);
+}
+
+void Evaluator::prepare_active_types(const std::vector<int>& node_types)
+{
+    std::vector<int> requested(node_types);
+    std::sort(requested.begin(), requested.end());
+    requested.erase(std::unique(requested.begin(), requested.end()), requested.end());
+    if (requested.empty()) throw std::invalid_argument("MACE compact radial cache requires at least one active type.");
+    for (int t : requested)
+        if (t < 0 || t >= model_.num_elements) throw std::invalid_argument("MACE active type index is out of range.");
+    if (requested.size() > 255) throw std::invalid_argument("More than 255 active element types.");
+    if (requested == active_types_) return;
+    active_types_ = requested;
+    const auto table = fold_r0_table(model_, active_types_);
+    if (table.size() > static_cast<std::size_t>(std::numeric_limits<int>::max()))
+        throw std::length_error("Layer-0 spline table exceeds 32-bit indexing; too many active element types.");
+    upload(r0_table_, table, stream_);
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+}
+
+// Installs a caller-order CSR graph that already sits on the device, re-expressed in the internal
+// node order (stable sort by element type).
+void Evaluator::install_graph(int num_nodes, const std::vector<int>& node_types, long num_edges, bool has_shifts)
+{
+    num_nodes_ = num_nodes;
+    num_edges_ = num_edges;
+    has_shifts_ = has_shifts;
+    prepare_active_types(node_types);
+    std::vector<int> type_to_active(model_.num_elements, -1);
+    for (std::size_t a = 0; a < active_types_.size(); ++a) type_to_active[active_types_[a]] = static_cast<int>(a);
+    std::vector<int> original(num_nodes);
+    std::iota(original.begin(), original.end(), 0);
+    std::stable_sort(original.begin(), original.end(), [&](int a, int b) { return node_types[a] < node_types[b]; });
+    std::vector<int> internal_of(num_nodes);
+    std::vector<unsigned char> atype(num_nodes), element(num_nodes);
+    type_begin_.assign(active_types_.size() + 1, 0);
+    for (int i = 0; i < num_nodes; ++i) {
+        internal_of[original[i]] = i;
+        atype[i] = static_cast<unsigned char>(type_to_active[node_types[original[i]]]);
+        element[i] = static_cast<unsigned char>(node_types[original[i]]);
+        type_begin_[atype[i] + 1] += 1;
+    }
+    for (std::size_t a = 0; a < active_types_.size(); ++a) type_begin_[a + 1] += type_begin_[a];
+    if (model_.num_elements > 255) throw std::invalid_argument("More than 255 element types.");
+    upload(original_, original, stream_);
+    upload(internal_of_, internal_of, stream_);
+    upload(atype_, atype, stream_);
+    upload(element_, element, stream_);
+
+    // internal CSR
+    first_.reserve(num_nodes + 1);
+    sources_.reserve(num_edges);
+    if (has_shifts) shifts_.reserve(3 * num_edges);
+    edge_map_.reserve(num_edges);
+    DeviceBuffer<int> counts;
+    counts.reserve(num_nodes + 1);
+    SXB_CUDA(cudaMemsetAsync(counts.ptr, 0, (num_nodes + 1) * sizeof(int), stream_));
+    gather_counts_kernel<<<blocks_for(num_nodes, 256), 256, 0, stream_>>>(num_nodes, original_.ptr, first_caller_.ptr, counts.ptr);
+    launches_ += 1;
+    std::size_t temp_bytes = 0;
+    cub::DeviceScan::ExclusiveSum(nullptr, temp_bytes, counts.ptr, first_.ptr, num_nodes + 1, stream_);
+    DeviceBuffer<unsigned char> temp;
+    temp.reserve(temp_bytes);
+    cub::DeviceScan::ExclusiveSum(temp.ptr, temp_bytes, counts.ptr, first_.ptr, num_nodes + 1, stream_);
+    permute_graph_kernel<<<blocks_for(static_cast<long>(num_nodes) * 32, 256), 256, 0, stream_>>>(
+        num_nodes, original_.ptr, internal_of_.ptr, first_caller_.ptr, sources_caller_.ptr,
+        has_shifts ? shifts_caller_.ptr : nullptr, first_.ptr, sources_.ptr, has_shifts ? shifts_.ptr : nullptr, edge_map_.ptr);
+    launches_ += 1;
+    SXB_CUDA(cudaGetLastError());
+
+    // work buffers
+    const std::size_t N = num_nodes, C = model_.channels, NH = model_.num_hidden, NE = model_.num_lme;
+    geom_.reserve(num_edges);
+    A0_.reserve(N * 16 * C);
+    A0_adj_.reserve(N * 16 * C);
+    M0_.reserve(N * NH * C);
+    M0_adj_.reserve(N * NH * C);
+    H1_.reserve(N * NH * C);
+    H1_adj_.reserve(N * NH * C);
+    Phi1_.reserve(N * NE * C);
+    dPhi1_.reserve(N * NE * C);
+    A1_.reserve(N * 16 * C);
+    A1_adj_.reserve(N * 16 * C);
+    M1_.reserve(N * C);
+    M1_adj_.reserve(N * C);
+    H2_.reserve(N * C);
+    H2_adj_.reserve(N * C);
+    node_energies_.reserve(N);
+    node_energies_out_.reserve(N);
+    forces_.reserve(N * 3);
+    forces_out_.reserve(N * 3);
+    positions_.reserve(N * 3);
+    if (keep_edge_forces_) edge_forces_.reserve(3 * static_cast<std::size_t>(num_edges));
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+    generation_ += 1;
+    have_results_ = false;
+}
+
+std::pair<std::uint64_t, long> Evaluator::prepare_periodic_graph(int num_nodes, const int* node_types, const double* positions,
+                                                                 const double* cell, const double* inverse_cell, double cutoff)
+{
+    SXB_CUDA(cudaSetDevice(device_));
+    if (num_nodes <= 0) throw std::invalid_argument("Neighbor graph needs at least one node.");
+    if (!std::isfinite(cutoff) || !(cutoff > 0.0)) throw std::invalid_argument("Neighbor graph cutoff must be finite and positive.");
+    for (int i = 0; i < 3 * num_nodes; ++i)
+        if (!std::isfinite(positions[i])) throw std::invalid_argument("Neighbor graph positions must be finite.");
+    for (int i = 0; i < 9; ++i)
+        if (!std::isfinite(cell[i]) || !std::isfinite(inverse_cell[i]))
+            throw std::invalid_argument("Neighbor graph cell must be finite.");
+    for (int row = 0; row < 3; ++row)
+        for (int column = 0; column < 3; ++column) {
+            double product = 0.0;
+            for (int inner = 0; inner < 3; ++inner) product += cell[3 * row + inner] * inverse_cell[3 * inner + column];
+            if (std::abs(product - (row == column ? 1.0 : 0.0)) > 1e-9)
+                throw std::invalid_argument("Neighbor graph cell and inverse cell are inconsistent.");
+        }
+    CellList cl;
+    for (int axis = 0; axis < 3; ++axis) {
+        double inverse_norm_squared = 0.0;
+        for (int component = 0; component < 3; ++component) {
+            const double value = inverse_cell[3 * component + axis];
+            inverse_norm_squared += value * value;
+        }
+        if (!(inverse_norm_squared > 0.0)) throw std::invalid_argument("Neighbor graph cell must be invertible.");
+        const double face_height = 1.0 / std::sqrt(inverse_norm_squared);
+        const double bins = std::floor(face_height / cutoff);
+        if (bins >= static_cast<double>(std::numeric_limits<int>::max()))
+            throw std::length_error("Neighbor graph bin extent exceeds 32-bit indexing.");
+        cl.bins[axis] = std::max(1, static_cast<int>(bins));
+        const double reach = std::ceil(cutoff * std::sqrt(inverse_norm_squared) * cl.bins[axis]) + 1.0;
+        cl.reach[axis] = std::max(1, static_cast<int>(reach));
+    }
+    const std::size_t num_bins = static_cast<std::size_t>(cl.bins[0]) * cl.bins[1] * cl.bins[2];
+    if (num_bins >= static_cast<std::size_t>(std::numeric_limits<int>::max()))
+        throw std::length_error("Neighbor graph bin count exceeds 32-bit indexing.");
+    cl.num_bins = static_cast<int>(num_bins);
+    cl.cutoff_squared = cutoff * cutoff;
+
+    const int n = num_nodes;
+    positions_.reserve(3 * static_cast<std::size_t>(n));
+    SXB_CUDA(cudaMemcpyAsync(positions_.ptr, positions, 3 * sizeof(double) * n, cudaMemcpyHostToDevice, stream_));
+    SXB_CUDA(cudaMemcpyAsync(cell_.ptr, cell, 9 * sizeof(double), cudaMemcpyHostToDevice, stream_));
+    SXB_CUDA(cudaMemcpyAsync(inv_cell_.ptr, inverse_cell, 9 * sizeof(double), cudaMemcpyHostToDevice, stream_));
+    DeviceBuffer<double> wrapped_frac, wrapped_pos;
+    DeviceBuffer<int> wrap_shift, atom_bin, bin_sizes, bin_offsets, cursors, bin_atoms;
+    DeviceBuffer<long long> counts, offsets;
+    wrapped_frac.reserve(3 * static_cast<std::size_t>(n));
+    wrapped_pos.reserve(3 * static_cast<std::size_t>(n));
+    wrap_shift.reserve(3 * static_cast<std::size_t>(n));
+    atom_bin.reserve(n);
+    bin_sizes.reserve(num_bins + 1);
+    bin_offsets.reserve(num_bins + 1);
+    cursors.reserve(num_bins + 1);
+    bin_atoms.reserve(n);
+    counts.reserve(n + 1);
+    offsets.reserve(n + 1);
+    SXB_CUDA(cudaMemsetAsync(bin_sizes.ptr, 0, (num_bins + 1) * sizeof(int), stream_));
+    SXB_CUDA(cudaMemsetAsync(counts.ptr, 0, (n + 1) * sizeof(long long), stream_));
+    const int T = 128;
+    wrap_positions_kernel<<<blocks_for(n, T), T, 0, stream_>>>(n, positions_.ptr, inv_cell_.ptr, cell_.ptr, wrapped_frac.ptr,
+                                                                wrapped_pos.ptr, wrap_shift.ptr);
+    count_bins_kernel<<<blocks_for(n, T), T, 0, stream_>>>(n, cl, wrapped_frac.ptr, atom_bin.ptr, bin_sizes.ptr);
+    std::size_t temp_bytes = 0, temp_bytes2 = 0;
+    cub::DeviceScan::ExclusiveSum(nullptr, temp_bytes, bin_sizes.ptr, bin_offsets.ptr, cl.num_bins + 1, stream_);
+    cub::DeviceScan::ExclusiveSum(nullptr, temp_bytes2, counts.ptr, offsets.ptr, n + 1, stream_);
+    DeviceBuffer<unsigned char> temp;
+    temp.reserve(std::max(temp_bytes, temp_bytes2));
+    cub::DeviceScan::ExclusiveSum(temp.ptr, temp_bytes, bin_sizes.ptr, bin_offsets.ptr, cl.num_bins + 1, stream_);
+    SXB_CUDA(cudaMemcpyAsync(cursors.ptr, bin_offsets.ptr, (num_bins + 1) * sizeof(int), cudaMemcpyDeviceToDevice, stream_));
+    fill_bins_kernel<<<blocks_for(n, T), T, 0, stream_>>>(n, atom_bin.ptr, cursors.ptr, bin_atoms.ptr);
+    sort_bins_kernel<<<blocks_for(cl.num_bins, T), T, 0, stream_>>>(cl.num_bins, bin_offsets.ptr, bin_atoms.ptr);
+    neighbor_edges_kernel<false><<<blocks_for(n, T), T, 0, stream_>>>(n, cl, atom_bin.ptr, bin_offsets.ptr, bin_atoms.ptr,
+                                                                       wrapped_pos.ptr, wrap_shift.ptr, cell_.ptr, counts.ptr,
+                                                                       nullptr, nullptr, nullptr);
+    cub::DeviceScan::ExclusiveSum(temp.ptr, temp_bytes2, counts.ptr, offsets.ptr, n + 1, stream_);
+    long long total = 0;
+    SXB_CUDA(cudaMemcpyAsync(&total, offsets.ptr + n, sizeof(long long), cudaMemcpyDeviceToHost, stream_));
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+    if (total > static_cast<long long>(std::numeric_limits<int>::max()))
+        throw std::length_error("Neighbor graph exceeds 32-bit edge indexing.");
+    first_caller_.reserve(n + 1);
+    sources_caller_.reserve(static_cast<std::size_t>(total));
+    shifts_caller_.reserve(3 * static_cast<std::size_t>(total));
+    narrow_offsets_kernel<<<blocks_for(n + 1, T), T, 0, stream_>>>(n, offsets.ptr, first_caller_.ptr);
+    neighbor_edges_kernel<true><<<blocks_for(n, T), T, 0, stream_>>>(n, cl, atom_bin.ptr, bin_offsets.ptr, bin_atoms.ptr,
+                                                                      wrapped_pos.ptr, wrap_shift.ptr, cell_.ptr, nullptr,
+                                                                      first_caller_.ptr, sources_caller_.ptr, shifts_caller_.ptr);
+    launches_ += 8;
+    SXB_CUDA(cudaGetLastError());
+    std::vector<int> types(node_types, node_types + n);
+    install_graph(n, types, static_cast<long>(total), true);
+    return {generation_, static_cast<long>(total)};
+}
+
+std::uint64_t Evaluator::prepare_graph(int num_nodes, const int* node_types, const int* num_neigh, const int* neigh_indices,
+                                       const int* shifts, const double* cell)
+{
+    SXB_CUDA(cudaSetDevice(device_));
+    if (num_nodes <= 0) throw std::invalid_argument("Graph needs at least one node.");
+    std::vector<int> first(num_nodes + 1, 0);
+    for (int i = 0; i < num_nodes; ++i) {
+        if (num_neigh[i] < 0) throw std::invalid_argument("num_neigh must be non-negative.");
+        const long long next = static_cast<long long>(first[i]) + num_neigh[i];
+        if (next > std::numeric_limits<int>::max()) throw std::length_error("Graph exceeds 32-bit edge indexing.");
+        first[i + 1] = static_cast<int>(next);
+    }
+    const long E = first[num_nodes];
+    for (long e = 0; e < E; ++e)
+        if (neigh_indices[e] < 0 || neigh_indices[e] >= num_nodes) throw std::invalid_argument("neigh_indices entry is out of range.");
+    if ((shifts == nullptr) != (cell == nullptr)) throw std::invalid_argument("shifts and cell must be given together.");
+    upload(first_caller_, first, stream_);
+    sources_caller_.reserve(E);
+    SXB_CUDA(cudaMemcpyAsync(sources_caller_.ptr, neigh_indices, E * sizeof(int), cudaMemcpyHostToDevice, stream_));
+    if (shifts != nullptr) {
+        shifts_caller_.reserve(3 * E);
+        SXB_CUDA(cudaMemcpyAsync(shifts_caller_.ptr, shifts, 3 * E * sizeof(int), cudaMemcpyHostToDevice, stream_));
+        SXB_CUDA(cudaMemcpyAsync(cell_.ptr, cell, 9 * sizeof(double), cudaMemcpyHostToDevice, stream_));
+    }
+    std::vector<int> types(node_types, node_types + num_nodes);
+    install_graph(num_nodes, types, E, shifts != nullptr);
+    return generation_;
+}
+
+void Evaluator::check_generation(std::uint64_t generation) const
+{
+    if (generation == 0 || generation != generation_)
+        throw StaleGraph("Prepared graph generation is stale or invalid.");
+}
+
+void Evaluator::get_graph(std::uint64_t generation, int* first, int* sources, int* shifts)
+{
+    check_generation(generation);
+    SXB_CUDA(cudaSetDevice(device_));
+    SXB_CUDA(cudaMemcpyAsync(first, first_caller_.ptr, (num_nodes_ + 1) * sizeof(int), cudaMemcpyDeviceToHost, stream_));
+    SXB_CUDA(cudaMemcpyAsync(sources, sources_caller_.ptr, num_edges_ * sizeof(int), cudaMemcpyDeviceToHost, stream_));
+    if (shifts != nullptr) {
+        if (!has_shifts_) throw std::invalid_argument("The prepared graph carries no periodic shifts.");
+        SXB_CUDA(cudaMemcpyAsync(shifts, shifts_caller_.ptr, 3 * num_edges_ * sizeof(int), cudaMemcpyDeviceToHost, stream_));
+    }
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+}
+
+void Evaluator::launch_gemm(const float* A, const RowMap& a_rows, const float* B, int ldb, bool b_transposed, float* Cout,
+                            const RowMap& c_rows, int first_node, int num_nodes, int N, int K, bool accumulate, const float* bias)
+{
+    if (num_nodes <= 0) return;
+    GemmArgs args;
+    args.A = A; args.B = B; args.C = Cout; args.bias = bias;
+    args.a_rows = a_rows; args.c_rows = c_rows;
+    args.first_node = first_node;
+    args.M = num_nodes * a_rows.components;
+    args.N = N; args.K = K; args.ldb = ldb;
+    args.b_transposed = b_transposed ? 1 : 0;
+    args.accumulate = accumulate ? 1 : 0;
+    dim3 grid(blocks_for(args.M, kGemmBM), blocks_for(N, kGemmBN));
+    gemm_rows_kernel<<<grid, 256, 0, stream_>>>(args);
+    launches_ += 1;
+}
+
+void Evaluator::run_pipeline()
+{
+    const int N = num_nodes_, C = model_.channels, NH = model_.num_hidden, NE = model_.num_lme;
+    const int n_active = static_cast<int>(active_types_.size());
+    SXB_CUDA(cudaMemsetAsync(forces_.ptr, 0, sizeof(double) * 3 * N, stream_));
+    SXB_CUDA(cudaMemsetAsync(H1_adj_.ptr, 0, sizeof(float) * static_cast<std::size_t>(N) * NH * C, stream_));
+    SXB_CUDA(cudaMemsetAsync(energy_slots_.ptr, 0, sizeof(double) * kVirialSlots, stream_));
+    SXB_CUDA(cudaMemsetAsync(virial_slots_.ptr, 0, sizeof(double) * kVirialSlots * 9, stream_));
+
+    // layer 0 forward
+    l0_forward_kernel<<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
+    const dim3 poly_grid(blocks_for(N, kPolyWarps), C / 32);
+    if (model_.shape_id == 0)
+        m0_forward_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A0_.ptr, element_.ptr, m0_weights_.ptr, M0_.ptr);
+    else
+        m0_forward_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A0_.ptr, element_.ptr, m0_weights_.ptr, M0_.ptr);
+    launches_ += 2;
+    // H1_il = M0_il W_l
+    for (int l = 0; l <= model_.hidden_l_max; ++l) {
+        const RowMap rows{static_cast<long>(NH) * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
+        launch_gemm(M0_.ptr, rows, w_h1_.ptr + static_cast<std::size_t>(l) * C * C, C, false, H1_.ptr, rows, 0, N, C, C, false, nullptr);
+    }
+    // layer 1 forward
+    if (model_.shape_id == 0)
+        l1_forward_kernel_S0<<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, r1_table_.ptr, H1_.ptr, coupling_, Phi1_.ptr);
+    else
+        l1_forward_kernel_S1<<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, r1_table_.ptr, H1_.ptr, coupling_, Phi1_.ptr);
+    launches_ += 1;
+    // A1_il = Phi1_il W_l
+    for (int l = 0; l <= model_.l_max; ++l) {
+        const int eta = model_.eta[l];
+        const RowMap a_rows{static_cast<long>(NE) * C, static_cast<long>(eta) * C, static_cast<long>(model_.group_begin[l]) * C, 2 * l + 1};
+        const RowMap c_rows{16L * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
+        launch_gemm(Phi1_.ptr, a_rows, w_a1_[l].ptr, C, false, A1_.ptr, c_rows, 0, N, C, eta * C, false, nullptr);
+    }
+    if (model_.shape_id == 0)
+        m1_forward_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A1_.ptr, element_.ptr, m1_weights_.ptr, M1_.ptr);
+    else
+        m1_forward_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A1_.ptr, element_.ptr, m1_weights_.ptr, M1_.ptr);
+    launches_ += 1;
+    // H2 = xs T_element + M1 W
+    const RowMap scalar_rows{static_cast<long>(NH) * C, C, 0, 1};
+    const RowMap flat_rows{static_cast<long>(C), C, 0, 1};
+    for (int a = 0; a < n_active; ++a) {
+        const int begin = type_begin_[a], count = type_begin_[a + 1] - begin;
+        launch_gemm(M0_.ptr, scalar_rows, h2_skip_.ptr + static_cast<std::size_t>(active_types_[a]) * C * C, C, false, H2_.ptr,
+                    flat_rows, begin, count, C, C, false, nullptr);
+    }
+    launch_gemm(M1_.ptr, flat_rows, h2_m1_.ptr, C, false, H2_.ptr, flat_rows, 0, N, C, C, true, nullptr);
+    readout_kernel<<<blocks_for(static_cast<long>(N) * 32, 256), 256, 0, stream_>>>(
+        N, C, model_.readout2_hidden, model_.readout2_scale, M0_.ptr, NH, H2_.ptr, element_.ptr, atomic_energies_.ptr,
+        readout1_.ptr, readout2_w1_.ptr, readout2_w2_.ptr, node_energies_.ptr, H2_adj_.ptr, energy_slots_.ptr);
+    launches_ += 1;
+
+    // reverse
+    launch_gemm(H2_adj_.ptr, flat_rows, h2_m1_.ptr, C, true, M1_adj_.ptr, flat_rows, 0, N, C, C, false, nullptr);
+    if (model_.shape_id == 0)
+        m1_reverse_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A1_.ptr, element_.ptr, m1_weights_.ptr, M1_adj_.ptr, A1_adj_.ptr);
+    else
+        m1_reverse_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A1_.ptr, element_.ptr, m1_weights_.ptr, M1_adj_.ptr, A1_adj_.ptr);
+    launches_ += 1;
+    for (int l = 0; l <= model_.l_max; ++l) {
+        const int eta = model_.eta[l];
+        const RowMap a_rows{16L * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
+        const RowMap c_rows{static_cast<long>(NE) * C, static_cast<long>(eta) * C, static_cast<long>(model_.group_begin[l]) * C, 2 * l + 1};
+        launch_gemm(A1_adj_.ptr, a_rows, w_a1_[l].ptr, C, true, dPhi1_.ptr, c_rows, 0, N, eta * C, C, false, nullptr);
+    }
+    ForceOutputs fo;
+    fo.atom_forces = forces_.ptr;
+    fo.virial_slots = virial_slots_.ptr;
+    fo.edge_forces = keep_edge_forces_ ? edge_forces_.ptr : nullptr;
+    fo.accumulate_edge = 0;
+    if (model_.shape_id == 0)
+        l1_reverse_kernel_S0<<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, r1_table_.ptr, H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
+    else
+        l1_reverse_kernel_S1<<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, r1_table_.ptr, H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
+    launches_ += 1;
+    // M0_adj_il = H1_adj_il W_l^T, then the direct adjoint q + T_element H2_adj on the scalar block
+    for (int l = 0; l <= model_.hidden_l_max; ++l) {
+        const RowMap rows{static_cast<long>(NH) * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
+        launch_gemm(H1_adj_.ptr, rows, w_h1_.ptr + static_cast<std::size_t>(l) * C * C, C, true, M0_adj_.ptr, rows, 0, N, C, C, false,
+                    l == 0 ? readout1_.ptr : nullptr);
+    }
+    for (int a = 0; a < n_active; ++a) {
+        const int begin = type_begin_[a], count = type_begin_[a + 1] - begin;
+        launch_gemm(H2_adj_.ptr, flat_rows, h2_skip_.ptr + static_cast<std::size_t>(active_types_[a]) * C * C, C, true, M0_adj_.ptr,
+                    scalar_rows, begin, count, C, C, true, nullptr);
+    }
+    if (model_.shape_id == 0)
+        m0_reverse_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A0_.ptr, element_.ptr, m0_weights_.ptr, M0_adj_.ptr, A0_adj_.ptr);
+    else
+        m0_reverse_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A0_.ptr, element_.ptr, m0_weights_.ptr, M0_adj_.ptr, A0_adj_.ptr);
+    fo.accumulate_edge = 1;
+    l0_reverse_kernel<<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
+    finalize_kernel<<<1, 32, 0, stream_>>>(energy_slots_.ptr, virial_slots_.ptr, totals_.ptr);
+    unpermute_doubles_kernel<<<blocks_for(N, 256), 256, 0, stream_>>>(N, 3, original_.ptr, forces_.ptr, forces_out_.ptr);
+    unpermute_doubles_kernel<<<blocks_for(N, 256), 256, 0, stream_>>>(N, 1, original_.ptr, node_energies_.ptr, node_energies_out_.ptr);
+    launches_ += 5;
+    SXB_CUDA(cudaGetLastError());
+}
+
+void Evaluator::finish_compute()
+{
+    SXB_CUDA(cudaEventRecord(event_end_, stream_));
+    int flag = 0;
+    SXB_CUDA(cudaMemcpyAsync(&flag, error_flag_.ptr, sizeof(int), cudaMemcpyDeviceToHost, stream_));
+    SXB_CUDA(cudaMemcpyAsync(host_totals_, totals_.ptr, 10 * sizeof(double), cudaMemcpyDeviceToHost, stream_));
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+    SXB_CUDA(cudaEventElapsedTime(&last_ms_, event_begin_, event_end_));
+    if (flag != 0) throw std::invalid_argument("Edge geometry contains a zero-length or non-finite edge vector.");
+    have_results_ = true;
+}
+
+void Evaluator::compute_positions(std::uint64_t generation, const double* positions, bool on_device)
+{
+    check_generation(generation);
+    if (!has_shifts_) throw std::invalid_argument("The prepared graph has no periodic shifts; use edge vectors.");
+    SXB_CUDA(cudaSetDevice(device_));
+    have_results_ = false;
+    SXB_CUDA(cudaEventRecord(event_begin_, stream_));
+    const double* dpos = positions;
+    if (!on_device) {
+        SXB_CUDA(cudaMemcpyAsync(positions_.ptr, positions, sizeof(double) * 3 * num_nodes_, cudaMemcpyHostToDevice, stream_));
+        dpos = positions_.ptr;
+    }
+    SXB_CUDA(cudaMemsetAsync(error_flag_.ptr, 0, sizeof(int), stream_));
+    geometry_from_positions_kernel<<<blocks_for(static_cast<long>(num_nodes_) * 32, 256), 256, 0, stream_>>>(
+        num_nodes_, first_.ptr, sources_.ptr, shifts_.ptr, dpos, original_.ptr, cell_.ptr, geom_.ptr, error_flag_.ptr);
+    launches_ += 1;
+    run_pipeline();
+    finish_compute();
+}
+
+void Evaluator::compute_edge_vectors(std::uint64_t generation, const double* xyz)
+{
+    check_generation(generation);
+    SXB_CUDA(cudaSetDevice(device_));
+    have_results_ = false;
+    DeviceBuffer<double> dxyz;
+    dxyz.reserve(3 * static_cast<std::size_t>(num_edges_));
+    SXB_CUDA(cudaEventRecord(event_begin_, stream_));
+    SXB_CUDA(cudaMemcpyAsync(dxyz.ptr, xyz, sizeof(double) * 3 * num_edges_, cudaMemcpyHostToDevice, stream_));
+    SXB_CUDA(cudaMemsetAsync(error_flag_.ptr, 0, sizeof(int), stream_));
+    geometry_from_vectors_kernel<<<blocks_for(num_edges_, 256), 256, 0, stream_>>>(num_edges_, dxyz.ptr, edge_map_.ptr, geom_.ptr, error_flag_.ptr);
+    launches_ += 1;
+    run_pipeline();
+    finish_compute();
+}
+
+void Evaluator::synchronize()
+{
+    SXB_CUDA(cudaSetDevice(device_));
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+}
+
+void Evaluator::require_results() const
+{
+    if (!have_results_) throw std::runtime_error("No evaluation results are available; call a compute function first.");
+}
+
+void Evaluator::get_node_energies(double* out)
+{
+    require_results();
+    SXB_CUDA(cudaMemcpyAsync(out, node_energies_out_.ptr, sizeof(double) * num_nodes_, cudaMemcpyDeviceToHost, stream_));
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+}
+
+void Evaluator::get_atom_forces(double* out)
+{
+    require_results();
+    SXB_CUDA(cudaMemcpyAsync(out, forces_out_.ptr, sizeof(double) * 3 * num_nodes_, cudaMemcpyDeviceToHost, stream_));
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+}
+
+void Evaluator::get_edge_forces(double* out)
+{
+    require_results();
+    if (!keep_edge_forces_) throw std::invalid_argument("Directed edge forces were not retained; enable them before compute.");
+    DeviceBuffer<double> tmp;
+    tmp.reserve(3 * static_cast<std::size_t>(num_edges_));
+    unpermute_edges_kernel<<<blocks_for(num_edges_, 256), 256, 0, stream_>>>(num_edges_, edge_map_.ptr, edge_forces_.ptr, tmp.ptr);
+    launches_ += 1;
+    SXB_CUDA(cudaMemcpyAsync(out, tmp.ptr, sizeof(double) * 3 * num_edges_, cudaMemcpyDeviceToHost, stream_));
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+}
+
+void Evaluator::set_keep_edge_forces(bool enabled)
+{
+    keep_edge_forces_ = enabled;
+    if (enabled && num_edges_ > 0) edge_forces_.reserve(3 * static_cast<std::size_t>(num_edges_));
+}
+
+void Evaluator::get_stress(double volume, double* out9)
+{
+    require_results();
+    if (!(volume > 0.0)) throw std::invalid_argument("Stress reduction needs a positive volume.");
+    for (int q = 0; q < 9; ++q) out9[q] = -host_totals_[1 + q] / volume;
+}
+
+double Evaluator::energy() const
+{
+    require_results();
+    return host_totals_[0];
+}
+
+long Evaluator::get_stage(const std::string& name, double* out, long capacity)
+{
+    require_results();
+    const long N = num_nodes_, C = model_.channels, NH = model_.num_hidden, NE = model_.num_lme;
+    const float* src = nullptr;
+    long row = 0;
+    if (name == "A0") { src = A0_.ptr; row = 16 * C; }
+    else if (name == "A0_adj") { src = A0_adj_.ptr; row = 16 * C; }
+    else if (name == "M0") { src = M0_.ptr; row = NH * C; }
+    else if (name == "M0_adj") { src = M0_adj_.ptr; row = NH * C; }
+    else if (name == "H1") { src = H1_.ptr; row = NH * C; }
+    else if (name == "H1_adj") { src = H1_adj_.ptr; row = NH * C; }
+    else if (name == "Phi1") { src = Phi1_.ptr; row = NE * C; }
+    else if (name == "dPhi1") { src = dPhi1_.ptr; row = NE * C; }
+    else if (name == "A1") { src = A1_.ptr; row = 16 * C; }
+    else if (name == "A1_adj") { src = A1_adj_.ptr; row = 16 * C; }
+    else if (name == "M1") { src = M1_.ptr; row = C; }
+    else if (name == "H2") { src = H2_.ptr; row = C; }
+    else if (name == "H2_adj") { src = H2_adj_.ptr; row = C; }
+    else throw std::invalid_argument("Unknown stage tensor name: " + name);
+    const long count = N * row;
+    if (out == nullptr) return count;
+    if (capacity < count) throw std::invalid_argument("Stage output buffer is too small.");
+    DeviceBuffer<double> tmp;
+    tmp.reserve(count);
+    unpermute_stage_kernel<<<blocks_for(count, 256), 256, 0, stream_>>>(N, row, original_.ptr, src, tmp.ptr);
+    launches_ += 1;
+    SXB_CUDA(cudaMemcpyAsync(out, tmp.ptr, sizeof(double) * count, cudaMemcpyDeviceToHost, stream_));
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+    return count;
+}
+
+}  // namespace sxb

@@ -1,0 +1,102 @@
+// Evaluator class behind the C ABI (include/symmetrix_b200.h).
+#pragma once
+
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "common.cuh"
+#include "model.hpp"
+
+namespace sxb {
+
+
+struct StaleGraph : std::invalid_argument {
+    using std::invalid_argument::invalid_argument;
+};
+
+class Evaluator {
+public:
+    Evaluator(const std::string& json_path, int device_ordinal);
+    ~Evaluator();
+    Evaluator(const Evaluator&) = delete;
+    Evaluator& operator=(const Evaluator&) = delete;
+
+    const HostModel& model() const { return model_; }
+    int num_nodes() const { return num_nodes_; }
+    long num_edges() const { return num_edges_; }
+    std::uint64_t generation() const { return generation_; }
+
+    std::pair<std::uint64_t, long> prepare_periodic_graph(int num_nodes, const int* node_types, const double* positions,
+                                                          const double* cell, const double* inverse_cell, double cutoff);
+    std::uint64_t prepare_graph(int num_nodes, const int* node_types, const int* num_neigh, const int* neigh_indices,
+                                const int* shifts, const double* cell);
+    void get_graph(std::uint64_t generation, int* first, int* sources, int* shifts);
+    void check_generation(std::uint64_t generation) const;
+
+    void compute_positions(std::uint64_t generation, const double* positions, bool on_device);
+    void compute_edge_vectors(std::uint64_t generation, const double* xyz);
+    void synchronize();
+
+    void get_node_energies(double* out);
+    void get_atom_forces(double* out);
+    void get_edge_forces(double* out);
+    void set_keep_edge_forces(bool enabled);
+    void get_stress(double volume, double* out9);
+    double energy() const;
+    long get_stage(const std::string& name, double* out, long capacity);
+    const double* device_energy() const { return totals_.ptr; }
+    const double* device_forces() const { return forces_out_.ptr; }
+    const double* device_virial() const { return totals_.ptr + 1; }
+    long launches() const { return launches_; }
+    float last_ms() const { return last_ms_; }
+    void require_results() const;
+
+private:
+    void prepare_active_types(const std::vector<int>& node_types);
+    void install_graph(int num_nodes, const std::vector<int>& node_types, long num_edges, bool has_shifts);
+    void run_pipeline();
+    void finish_compute();
+    void launch_gemm(const float* A, const RowMap& a_rows, const float* B, int ldb, bool b_transposed, float* C,
+                     const RowMap& c_rows, int first_node, int num_nodes, int N, int K, bool accumulate, const float* bias);
+
+    int device_ = 0;
+    cudaStream_t stream_ = nullptr;
+    cudaEvent_t event_begin_ = nullptr, event_end_ = nullptr;
+    HostModel model_;
+    std::vector<int> active_types_;
+    std::vector<int> type_begin_;
+
+    // model tables on the device
+    DeviceBuffer<float> r0_table_, r1_table_, m0_weights_, m1_weights_, w_h1_, w_a1_[4], h2_skip_, h2_m1_;
+    DeviceBuffer<float> readout1_, readout2_w1_, readout2_w2_;
+    DeviceBuffer<double> atomic_energies_;
+    CouplingConstants coupling_;
+    SplineGrid grid_;
+
+    // prepared graph
+    std::uint64_t generation_ = 0;
+    int num_nodes_ = 0;
+    long num_edges_ = 0;
+    bool has_shifts_ = false;
+    DeviceBuffer<int> first_caller_, sources_caller_, shifts_caller_;
+    DeviceBuffer<int> first_, sources_, shifts_, edge_map_, original_, internal_of_;
+    DeviceBuffer<unsigned char> atype_, element_;
+    DeviceBuffer<double> cell_, inv_cell_, positions_;
+
+    // work buffers
+    DeviceBuffer<EdgeGeom> geom_;
+    DeviceBuffer<float> A0_, A0_adj_, M0_, M0_adj_, H1_, H1_adj_, Phi1_, dPhi1_, A1_, A1_adj_, M1_, M1_adj_, H2_, H2_adj_;
+    DeviceBuffer<double> node_energies_, node_energies_out_, forces_, forces_out_, edge_forces_;
+    DeviceBuffer<double> totals_, energy_slots_, virial_slots_;
+    DeviceBuffer<int> error_flag_;
+    double host_totals_[10] = {0};
+    bool keep_edge_forces_ = false;
+    bool have_results_ = false;
+    long launches_ = 0;
+    float last_ms_ = 0.0f;
+};
+
+}  // namespace sxb

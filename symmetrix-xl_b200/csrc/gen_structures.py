@@ -1,0 +1,147 @@
+"""Emits csrc/generated/structures.h: the coupling structure of each supported model
+shape as X-macro lists, so that the CUDA kernels expand into straight-line code with
+every row, coupling term and monomial index a compile-time constant.
+
+Run from the repository root:  python symmetrix-xl_b200/csrc/gen_structures.py
+The tables come from symmetrix-xl_b200/structure.py (first-principles derivation) plus
+the extra zero-weight monomials modelgen.model_tables adds for the (3,1) shape.
+"""
+from __future__ import annotations
+
+import importlib.util
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[2]
+PKG = ROOT / "symmetrix-xl_b200"
+
+
+def _load_pkg():
+    spec = importlib.util.spec_from_file_location(
+        "symmetrix_xl_b200", PKG / "__init__.py", submodule_search_locations=[str(PKG)])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["symmetrix_xl_b200"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+SHAPES = [("S0", 3, 0), ("S1", 3, 1), ("S2", 3, 2)]
+
+
+def emit_shape(name, l_max, L_max, tables):
+    out = []
+    paths = list(zip(tables["Phi1_l"], tables["Phi1_l1"], tables["Phi1_l2"]))
+    num_lm, num_LM = (l_max + 1) ** 2, (L_max + 1) ** 2
+    rows = []
+    row_begin = []
+    for p, (l, l1, l2) in enumerate(paths):
+        row_begin.append(len(rows))
+        for lm1 in range(l1 * l1, (l1 + 1) ** 2):
+            for lm2 in range(l2 * l2, (l2 + 1) ** 2):
+                rows.append((p, lm1, lm2))
+    out.append(f"// ---- shape {name}: edge l_max={l_max}, hidden L_max={L_max}")
+    out.append(f"#define SXB_{name}_LMAX {l_max}")
+    out.append(f"#define SXB_{name}_HIDDEN_LMAX {L_max}")
+    out.append(f"#define SXB_{name}_NUM_LM {num_lm}")
+    out.append(f"#define SXB_{name}_NUM_HIDDEN {num_LM}")
+    out.append(f"#define SXB_{name}_NUM_PATHS {len(paths)}")
+    out.append(f"#define SXB_{name}_NUM_ROWS {len(rows)}")
+    out.append(f"#define SXB_{name}_NUM_LME {tables['num_lme']}")
+    out.append(f"#define SXB_{name}_NUM_TERMS {len(tables['Phi1_lme'])}")
+    out.append(f"// X(path, l_out, l_edge, l_source, first_row)")
+    out.append(f"#define SXB_{name}_PATHS(X) \\")
+    out.append(" \\\n".join(f"    X({p}, {l}, {l1}, {l2}, {row_begin[p]})" for p, (l, l1, l2) in enumerate(paths)))
+    out.append(f"// X(row, path, lm_edge, lm_source)")
+    out.append(f"#define SXB_{name}_ROWS(X) \\")
+    out.append(" \\\n".join(f"    X({r}, {p}, {lm1}, {lm2})" for r, (p, lm1, lm2) in enumerate(rows)))
+    out.append(f"// X(term, row, lme): coefficient values live in constant memory, indexed by term")
+    out.append(f"#define SXB_{name}_TERMS(X) \\")
+    out.append(" \\\n".join(f"    X({t}, {row}, {lme})" for t, (row, lme) in
+                            enumerate(zip(tables["Phi1_lelm1lm2"], tables["Phi1_lme"]))))
+    # symmetric contraction: weights laid out [type][term][channel], term = offset(LM) + index
+    offset = 0
+    lines1, lines2, lines3 = [], [], []
+    offs = []
+    for LM in range(num_LM):
+        mons = tables["M0_monomials"][str(LM)]
+        offs.append(offset)
+        for t, mono in enumerate(mons):
+            if len(mono) == 1:
+                lines1.append(f"    X1({LM}, {offset + t}, {mono[0]})")
+            elif len(mono) == 2:
+                lines2.append(f"    X2({LM}, {offset + t}, {mono[0]}, {mono[1]})")
+            else:
+                lines3.append(f"    X3({LM}, {offset + t}, {mono[0]}, {mono[1]}, {mono[2]})")
+        offset += len(mons)
+    out.append(f"#define SXB_{name}_M0_NUM_TERMS {offset}")
+    out.append(f"#define SXB_{name}_M0_OFFSETS {{{', '.join(map(str, offs + [offset]))}}}")
+    out.append(f"// X1(out, term, a)  X2(out, term, a, b)  X3(out, term, a, b, c)")
+    out.append(f"#define SXB_{name}_M0_TERMS(X1, X2, X3) \\")
+    out.append(" \\\n".join(lines1 + lines2 + lines3))
+    m1 = tables["M1_monomials"]
+    out.append(f"#define SXB_{name}_M1_NUM_TERMS {len(m1)}")
+    l1_, l2_, l3_ = [], [], []
+    for t, mono in enumerate(m1):
+        if len(mono) == 1:
+            l1_.append(f"    X1(0, {t}, {mono[0]})")
+        elif len(mono) == 2:
+            l2_.append(f"    X2(0, {t}, {mono[0]}, {mono[1]})")
+        else:
+            l3_.append(f"    X3(0, {t}, {mono[0]}, {mono[1]}, {mono[2]})")
+    out.append(f"#define SXB_{name}_M1_TERMS(X1, X2, X3) \\")
+    out.append(" \\\n".join(l1_ + l2_ + l3_))
+    # straight-line bodies of the layer-1 edge kernels (one channel per thread):
+    #   R[p], dR[p]: radial value / derivative of path p;  y[lm]: edge harmonics;
+    #   h[lm2]: source features;  acc[row] / adj[row]: receiver row sums / row adjoints
+    fwd, rev = [], []
+    for p, (l, l1, l2) in enumerate(paths):
+        n1, n2 = 2 * l1 + 1, 2 * l2 + 1
+        fwd.append(f"    {{ /* path {p}: edge l={l1}, source l={l2} -> l={l} */")
+        for b in range(n2):
+            fwd.append(f"      const float t{b} = R[{p}] * h[{l2 * l2 + b}];")
+        for a in range(n1):
+            for b in range(n2):
+                row = row_begin[p] + a * n2 + b
+                fwd.append(f"      acc[{row}] = fmaf(t{b}, y[{l1 * l1 + a}], acc[{row}]);")
+        fwd.append("    }")
+        rev.append(f"    {{ /* path {p}: edge l={l1}, source l={l2} -> l={l} */")
+        rev.append("      float yw = 0.0f;")
+        for a in range(n1):
+            terms_ = [f"h[{l2 * l2 + b}] * adj[{row_begin[p] + a * n2 + b}]" for b in range(n2)]
+            expr = terms_[0]
+            for t_ in terms_[1:]:
+                hh, aa = t_.split(" * ")
+                expr = f"fmaf({hh}, {aa}, {expr})"
+            rev.append(f"      {{ const float w = {expr};")
+            rev.append(f"        ang[{l1 * l1 + a}] = fmaf(R[{p}], w, ang[{l1 * l1 + a}]); yw = fmaf(y[{l1 * l1 + a}], w, yw); }}")
+        rev.append(f"      radial = fmaf(dR[{p}], yw, radial);")
+        for b in range(n2):
+            terms_ = [(f"y[{l1 * l1 + a}]", f"adj[{row_begin[p] + a * n2 + b}]") for a in range(n1)]
+            expr = f"{terms_[0][0]} * {terms_[0][1]}"
+            for yy, aa in terms_[1:]:
+                expr = f"fmaf({yy}, {aa}, {expr})"
+            rev.append(f"      hadj[{l2 * l2 + b}] = fmaf(R[{p}], {expr}, hadj[{l2 * l2 + b}]);")
+        rev.append("    }")
+    out.append(f"#define SXB_{name}_L1_FORWARD_BODY \\")
+    out.append(" \\\n".join(fwd))
+    out.append(f"#define SXB_{name}_L1_REVERSE_BODY \\")
+    out.append(" \\\n".join(rev))
+    out.append("")
+    return "\n".join(out)
+
+
+def main():
+    pkg = _load_pkg()
+    text = ["// Generated by symmetrix-xl_b200/csrc/gen_structures.py -- do not edit.",
+            "// Coupling structure of the supported model shapes as X-macro lists.",
+            "#pragma once", ""]
+    for name, l_max, L_max in SHAPES:
+        tables = pkg.modelgen.model_tables(l_max, L_max)
+        text.append(emit_shape(name, l_max, L_max, tables))
+    target = PKG / "csrc" / "generated" / "structures.h"
+    target.write_text("\n".join(text))
+    print("wrote", target)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,422 @@
+#include "model.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <fstream>
+#include <map>
+#include <stdexcept>
+
+#include "nlohmann/json.hpp"
+
+#include "generated/structures.h"
+
+namespace sxb {
+namespace {
+
+using json = nlohmann::json;
+
+// ---------------------------------------------------------------- compiled shapes
+#define SXB_PATH_PUSH(p, l, l1, l2, first_row) t.path_l.push_back(l); t.path_l1.push_back(l1); t.path_l2.push_back(l2);
+#define SXB_TERM_PUSH(term, row, lme) t.term_row.push_back(row); t.term_lme.push_back(lme);
+#define SXB_M_SET1(out, term, a) terms[term] = {a}; outs[term] = out;
+#define SXB_M_SET2(out, term, a, b) terms[term] = {a, b}; outs[term] = out;
+#define SXB_M_SET3(out, term, a, b, c) terms[term] = {a, b, c}; outs[term] = out;
+
+#define SXB_DEFINE_SHAPE(NAME, ID)                                                      \
+    ShapeTables make_##NAME()                                                            \
+    {                                                                                    \
+        ShapeTables t;                                                                   \
+        t.name = #NAME; t.shape_id = ID;                                                 \
+        t.l_max = SXB_##NAME##_LMAX; t.hidden_l_max = SXB_##NAME##_HIDDEN_LMAX;          \
+        t.num_paths = SXB_##NAME##_NUM_PATHS; t.num_rows = SXB_##NAME##_NUM_ROWS;        \
+        t.num_lme = SXB_##NAME##_NUM_LME; t.num_terms = SXB_##NAME##_NUM_TERMS;          \
+        SXB_##NAME##_PATHS(SXB_PATH_PUSH)                                                \
+        SXB_##NAME##_TERMS(SXB_TERM_PUSH)                                                \
+        {                                                                                \
+            std::vector<std::vector<int>> terms(SXB_##NAME##_M0_NUM_TERMS);              \
+            std::vector<int> outs(SXB_##NAME##_M0_NUM_TERMS);                            \
+            SXB_##NAME##_M0_TERMS(SXB_M_SET1, SXB_M_SET2, SXB_M_SET3)                    \
+            t.m0_terms = terms; t.m0_out = outs;                                         \
+        }                                                                                \
+        {                                                                                \
+            std::vector<std::vector<int>> terms(SXB_##NAME##_M1_NUM_TERMS);              \
+            std::vector<int> outs(SXB_##NAME##_M1_NUM_TERMS);                            \
+            SXB_##NAME##_M1_TERMS(SXB_M_SET1, SXB_M_SET2, SXB_M_SET3)                    \
+            t.m1_terms = terms;                                                          \
+        }                                                                                \
+        return t;                                                                        \
+    }
+
+SXB_DEFINE_SHAPE(S0, 0)
+SXB_DEFINE_SHAPE(S1, 1)
+SXB_DEFINE_SHAPE(S2, 2)
+
+const std::vector<ShapeTables>& all_shapes()
+{
+    static const std::vector<ShapeTables> shapes = {make_S0(), make_S1(), make_S2()};
+    return shapes;
+}
+
+// ---------------------------------------------------------------- radial tables
+struct Network {
+    std::vector<int> shape;
+    std::vector<std::vector<double>> weights;
+    double activation_scale = 1.0;
+    bool tanh_square = false;
+};
+
+Network parse_network(const json& def, const std::string& name)
+{
+    Network n;
+    n.shape = def.at("shape").get<std::vector<int>>();
+    n.weights = def.at("weights").get<std::vector<std::vector<double>>>();
+    n.activation_scale = def.at("activation_scale").get<double>();
+    const auto post = def.value("postprocess", std::string());
+    if (!post.empty() && post != "tanh-square")
+        throw std::invalid_argument("Compact radial network " + name + " has unsupported postprocessing.");
+    n.tanh_square = post == "tanh-square";
+    if (def.at("activation").get<std::string>() != "silu")
+        throw std::invalid_argument("Compact radial network " + name + " must use SiLU.");
+    if (n.shape.size() < 2 || n.weights.size() != n.shape.size() - 1)
+        throw std::invalid_argument("Compact radial network " + name + " has an invalid shape.");
+    for (std::size_t layer = 0; layer < n.weights.size(); ++layer)
+        if (n.weights[layer].size() != static_cast<std::size_t>(n.shape[layer]) * n.shape[layer + 1])
+            throw std::invalid_argument("Compact radial network " + name + " has invalid weights.");
+    return n;
+}
+
+// values[node][out] for a batch of feature rows (weights are [out][in] row-major)
+std::vector<double> run_network(const Network& n, const std::vector<double>& features, int batch)
+{
+    std::vector<double> x = features;
+    for (std::size_t layer = 0; layer + 1 < n.shape.size(); ++layer) {
+        const int in = n.shape[layer], out = n.shape[layer + 1];
+        const bool last = layer + 2 == n.shape.size();
+        std::vector<double> y(static_cast<std::size_t>(batch) * out);
+        const auto& w = n.weights[layer];
+        for (int b = 0; b < batch; ++b)
+            for (int o = 0; o < out; ++o) {
+                double s = 0.0;
+                for (int i = 0; i < in; ++i)
+                    s += x[static_cast<std::size_t>(b) * in + i] * w[static_cast<std::size_t>(o) * in + i];
+                if (!last)
+                    s = n.activation_scale * s / (1.0 + std::exp(-s));
+                else if (n.tanh_square)
+                    s = std::tanh(s * s);
+                y[static_cast<std::size_t>(b) * out + o] = s;
+            }
+        x.swap(y);
+    }
+    return x;
+}
+
+// Cubic coefficients [interval][4][F] from nodal values [node][F]: nodal derivatives by
+// the reference's tridiagonal system (left not-a-knot-like closure, zero right
+// derivative), then the Hermite-to-monomial conversion.
+std::vector<double> spline_coefficients(const std::vector<double>& values, int points, int F, double h)
+{
+    const int n = points - 2;
+    std::vector<double> lower(n, 0.0), diag(n, 4.0), upper(n, 0.0);
+    upper[0] = 2.0;
+    for (int node = 2; node < points - 1; ++node) {
+        const int row = node - 1;
+        lower[row] = 1.0;
+        if (node + 1 <= points - 2) upper[row] = 1.0;
+    }
+    std::vector<double> factor(n, 0.0);
+    for (int row = 1; row < n; ++row) {
+        factor[row] = lower[row] / diag[row - 1];
+        diag[row] -= factor[row] * upper[row - 1];
+    }
+    std::vector<double> coeff(static_cast<std::size_t>(points - 1) * 4 * F);
+    std::vector<double> rhs(n), d(points);
+    for (int f = 0; f < F; ++f) {
+        auto v = [&](int node) { return values[static_cast<std::size_t>(node) * F + f]; };
+        const double left = 2.0 * (-v(0) + 2.0 * v(1) - v(2)) / h;
+        rhs[0] = 3.0 * (v(2) - v(0)) / h - left;
+        for (int node = 2; node < points - 1; ++node)
+            rhs[node - 1] = 3.0 * (v(node + 1) - v(node - 1)) / h;
+        for (int row = 1; row < n; ++row) rhs[row] -= factor[row] * rhs[row - 1];
+        d[points - 2] = rhs[n - 1] / diag[n - 1];
+        for (int row = n - 2; row >= 0; --row) d[row + 1] = (rhs[row] - upper[row] * d[row + 2]) / diag[row];
+        d[0] = d[2] + left;
+        d[points - 1] = 0.0;
+        for (int i = 0; i < points - 1; ++i) {
+            double* c = coeff.data() + static_cast<std::size_t>(i) * 4 * F + f;
+            c[0] = v(i);
+            c[F] = d[i];
+            c[2 * F] = (-3 * v(i) - 2 * h * d[i] + 3 * v(i + 1) - h * d[i + 1]) / (h * h);
+            c[3 * F] = (2 * v(i) + h * d[i] - 2 * v(i + 1) + h * d[i + 1]) / (h * h * h);
+        }
+    }
+    return coeff;
+}
+
+template <typename T>
+std::vector<T> to_vec(const std::vector<double>& v)
+{
+    std::vector<T> out(v.size());
+    for (std::size_t i = 0; i < v.size(); ++i) {
+        if (!std::isfinite(v[i])) throw std::invalid_argument("MACE model contains a non-finite value.");
+        out[i] = static_cast<T>(v[i]);
+    }
+    return out;
+}
+
+}  // namespace
+
+const ShapeTables& shape_tables(int shape_id) { return all_shapes().at(shape_id); }
+int num_compiled_shapes() { return static_cast<int>(all_shapes().size()); }
+
+HostModel load_model(const std::string& json_path)
+{
+    std::ifstream stream(json_path);
+    if (!stream) throw std::runtime_error("Could not open Symmetrix model file: " + json_path);
+    const json file = json::parse(stream);
+    HostModel m;
+
+    if (file.value("model_type", std::string("MACE")) != "MACE")
+        throw std::invalid_argument("Only the standard two-layer MACE model family is supported.");
+    if (file.value("symmetrix_format_version", 1) != 4 || file.value("h1_affine_mode", std::string()) != "m0_composite")
+        throw std::invalid_argument("Model must be format version 4 with h1_affine_mode m0_composite.");
+    if (file.value("radial_representation", std::string()) != "compact")
+        throw std::invalid_argument("Model must use the compact radial representation.");
+    if (file.value("num_interactions", 2) != 2 || file.value("single_layer_readout", false))
+        throw std::invalid_argument("Only two-interaction models are supported.");
+    if (file.value("has_zbl", false)) throw std::invalid_argument("ZBL pair repulsion is not supported.");
+    if (file.value("has_field_coupling", false)) throw std::invalid_argument("MACEField models are not supported.");
+    if (file.value("first_interaction_residual", false))
+        throw std::invalid_argument("Residual-first models are not supported.");
+
+    m.num_elements = file.at("num_elements").get<int>();
+    m.channels = file.at("num_channels").get<int>();
+    m.r_cut = file.at("r_cut").get<double>();
+    m.l_max = file.at("l_max").get<int>();
+    m.hidden_l_max = file.at("L_max").get<int>();
+    m.num_lm = (m.l_max + 1) * (m.l_max + 1);
+    m.num_hidden = (m.hidden_l_max + 1) * (m.hidden_l_max + 1);
+    m.atomic_numbers = file.at("atomic_numbers").get<std::vector<int>>();
+    m.atomic_energies = file.at("atomic_energies").get<std::vector<double>>();
+    const int A = m.num_elements, C = m.channels;
+    if (static_cast<int>(m.atomic_numbers.size()) != A || static_cast<int>(m.atomic_energies.size()) != A)
+        throw std::invalid_argument("atomic_numbers / atomic_energies do not match num_elements.");
+    if (C % 32 != 0 || C > 256) throw std::invalid_argument("num_channels must be a multiple of 32, at most 256.");
+
+    // ---- structure: match against a compiled shape
+    const auto phi_l = file.at("Phi1_l").get<std::vector<int>>();
+    const auto phi_l1 = file.at("Phi1_l1").get<std::vector<int>>();
+    const auto phi_l2 = file.at("Phi1_l2").get<std::vector<int>>();
+    const auto phi_lme = file.at("Phi1_lme").get<std::vector<int>>();
+    const auto phi_row = file.at("Phi1_lelm1lm2").get<std::vector<int>>();
+    const auto phi_cg = file.at("Phi1_clebsch_gordan").get<std::vector<double>>();
+    const auto m0_monomials = file.at("M0_monomials").get<std::map<std::string, std::vector<std::vector<int>>>>();
+    const auto m1_monomials = file.at("M1_monomials").get<std::vector<std::vector<int>>>();
+    const ShapeTables* shape = nullptr;
+    for (const auto& s : all_shapes())
+        if (s.l_max == m.l_max && s.hidden_l_max == m.hidden_l_max && s.path_l == phi_l && s.path_l1 == phi_l1
+            && s.path_l2 == phi_l2)
+            shape = &s;
+    if (shape == nullptr)
+        throw std::invalid_argument("Model coupling structure (l_max, L_max, paths) matches no compiled shape.");
+    m.shape_id = shape->shape_id;
+    m.num_paths = shape->num_paths;
+    m.num_rows = shape->num_rows;
+    m.num_lme = shape->num_lme;
+    m.num_terms = shape->num_terms;
+    if (phi_lme.size() != phi_row.size() || phi_lme.size() != phi_cg.size())
+        throw std::invalid_argument("Phi1 sparse coupling arrays must have equal lengths.");
+    m.cg.assign(shape->num_terms, 0.0f);
+    {
+        std::map<std::pair<int, int>, int> compiled;
+        for (int t = 0; t < shape->num_terms; ++t) compiled[{shape->term_row[t], shape->term_lme[t]}] = t;
+        for (std::size_t t = 0; t < phi_cg.size(); ++t) {
+            auto it = compiled.find({phi_row[t], phi_lme[t]});
+            if (it == compiled.end()) {
+                if (phi_cg[t] == 0.0) continue;
+                throw std::invalid_argument("Model has a Phi1 coupling term outside the compiled structure.");
+            }
+            m.cg[it->second] += static_cast<float>(phi_cg[t]);
+        }
+    }
+    m.eta.assign(m.l_max + 1, 0);
+    for (int l : phi_l) m.eta[l] += 1;
+    m.group_begin.assign(m.l_max + 2, 0);
+    for (int l = 0; l <= m.l_max; ++l) m.group_begin[l + 1] = m.group_begin[l] + (2 * l + 1) * m.eta[l];
+
+    // ---- symmetric contraction weights in compiled term order
+    auto map_terms = [](const std::vector<std::vector<int>>& compiled, const std::vector<int>* outs, int out,
+                        const std::vector<std::vector<int>>& given, const char* what) {
+        std::map<std::vector<int>, int> where;
+        for (std::size_t t = 0; t < compiled.size(); ++t)
+            if (outs == nullptr || (*outs)[t] == out) where[compiled[t]] = static_cast<int>(t);
+        std::vector<int> position(given.size());
+        for (std::size_t t = 0; t < given.size(); ++t) {
+            auto sorted = given[t];
+            std::sort(sorted.begin(), sorted.end());
+            auto it = where.find(sorted);
+            if (it == where.end())
+                throw std::invalid_argument(std::string(what) + " contains a monomial outside the compiled structure.");
+            position[t] = it->second;
+        }
+        return position;
+    };
+    m.m0_num_terms = static_cast<int>(shape->m0_terms.size());
+    m.m1_num_terms = static_cast<int>(shape->m1_terms.size());
+    m.m0_weights.assign(static_cast<std::size_t>(A) * m.m0_num_terms * C, 0.0f);
+    m.m1_weights.assign(static_cast<std::size_t>(A) * m.m1_num_terms * C, 0.0f);
+    {
+        const auto& weights = file.at("M0_weights");
+        for (int lm = 0; lm < m.num_hidden; ++lm) {
+            const auto position = map_terms(shape->m0_terms, &shape->m0_out, lm, m0_monomials.at(std::to_string(lm)),
+                                            "M0_monomials");
+            for (int a = 0; a < A; ++a)
+                for (int k = 0; k < C; ++k) {
+                    const auto w = weights.at(std::to_string(a)).at(std::to_string(lm)).at(std::to_string(k))
+                                       .get<std::vector<double>>();
+                    if (w.size() != position.size()) throw std::invalid_argument("M0_weights extent mismatch.");
+                    for (std::size_t t = 0; t < w.size(); ++t)
+                        m.m0_weights[(static_cast<std::size_t>(a) * m.m0_num_terms + position[t]) * C + k] +=
+                            static_cast<float>(w[t]);
+                }
+        }
+        const auto position = map_terms(shape->m1_terms, nullptr, 0, m1_monomials, "M1_monomials");
+        const auto& w1 = file.at("M1_weights");
+        for (int a = 0; a < A; ++a)
+            for (int k = 0; k < C; ++k) {
+                const auto w = w1.at(std::to_string(a)).at(std::to_string(k)).get<std::vector<double>>();
+                if (w.size() != position.size()) throw std::invalid_argument("M1_weights extent mismatch.");
+                for (std::size_t t = 0; t < w.size(); ++t)
+                    m.m1_weights[(static_cast<std::size_t>(a) * m.m1_num_terms + position[t]) * C + k] +=
+                        static_cast<float>(w[t]);
+            }
+    }
+
+    // ---- radial tables
+    const auto& radial = file.at("compact_radial");
+    m.spline_x0 = radial.at("spline_grid_min").get<double>();
+    m.spline_points = radial.at("num_spline_points").get<int>();
+    if (!(m.spline_x0 > 0.0) || m.spline_points < 4)
+        throw std::invalid_argument("Compact radial model has an invalid spline grid.");
+    m.spline_h = (m.r_cut - m.spline_x0) / (m.spline_points - 1);
+    const auto& basis = radial.at("basis");
+    if (basis.at("type").get<std::string>() != "bessel")
+        throw std::invalid_argument("Compact radial model only supports a Bessel basis.");
+    const auto bessel = basis.at("weights").get<std::vector<double>>();
+    const double prefactor = basis.at("prefactor").get<double>();
+    const auto& cutoff = radial.at("cutoff");
+    if (cutoff.at("type").get<std::string>() != "polynomial")
+        throw std::invalid_argument("Compact radial model only supports a polynomial cutoff.");
+    const double r_max = cutoff.at("r_max").get<double>();
+    const int p = cutoff.at("p").get<int>();
+    if (std::abs(r_max - m.r_cut) > 1e-12) throw std::invalid_argument("Compact radial cutoff does not match model r_cut.");
+    if (radial.at("distance_transform").at("type").get<std::string>() != "none")
+        throw std::invalid_argument("Only the untransformed radial distance is supported.");
+    const int nb = static_cast<int>(bessel.size());
+    std::vector<double> features(static_cast<std::size_t>(m.spline_points) * nb);
+    for (int node = 0; node < m.spline_points; ++node) {
+        const double r = m.spline_x0 + node * m.spline_h;
+        double cut = 0.0;
+        if (r < r_max) {
+            const double u = r / r_max;
+            cut = 1.0 - ((p + 1.0) * (p + 2.0) / 2.0) * std::pow(u, p) + p * (p + 2.0) * std::pow(u, p + 1)
+                  - (p * (p + 1.0) / 2.0) * std::pow(u, p + 2);
+        }
+        for (int b = 0; b < nb; ++b)
+            features[static_cast<std::size_t>(node) * nb + b] = prefactor * std::sin(bessel[b] * r) / r * cut;
+    }
+    const auto& networks = radial.at("networks");
+    auto table = [&](const char* name, int expected) {
+        const Network net = parse_network(networks.at(name), name);
+        if (net.shape.front() != nb || net.shape.back() != expected)
+            throw std::invalid_argument(std::string("Compact radial network ") + name + " has an invalid extent.");
+        const auto values = run_network(net, features, m.spline_points);
+        return spline_coefficients(values, m.spline_points, expected, m.spline_h);
+    };
+    m.r0_coeff = table("R0", (m.l_max + 1) * C);
+    m.r1_coeff = table("R1", m.num_paths * C);
+    m.a0_scaled = file.at("A0_scaled").get<bool>();
+    m.a1_scaled = file.value("A1_scaled", false);
+    if (m.a0_scaled != networks.contains("A0") || m.a1_scaled != networks.contains("A1"))
+        throw std::invalid_argument("Compact radial density networks do not match A0_scaled / A1_scaled.");
+    if (m.a0_scaled) m.a0_density_coeff = table("A0", 1);
+    if (m.a1_scaled) m.a1_density_coeff = table("A1", 1);
+
+    // ---- dense weights
+    m.h0 = file.at("H0_weights").get<std::vector<double>>();
+    if (m.h0.size() != static_cast<std::size_t>(A) * C) throw std::invalid_argument("H0_weights extent mismatch.");
+    {
+        const auto w = file.at("A0_weights").get<std::vector<std::vector<std::vector<double>>>>();
+        if (static_cast<int>(w.size()) != A) throw std::invalid_argument("A0_weights extent mismatch.");
+        m.w_a0.reserve(static_cast<std::size_t>(A) * (m.l_max + 1) * C * C);
+        for (const auto& per_element : w) {
+            if (static_cast<int>(per_element.size()) != m.l_max + 1) throw std::invalid_argument("A0_weights extent mismatch.");
+            for (const auto& block : per_element) {
+                if (block.size() != static_cast<std::size_t>(C) * C) throw std::invalid_argument("A0_weights extent mismatch.");
+                m.w_a0.insert(m.w_a0.end(), block.begin(), block.end());
+            }
+        }
+    }
+    m.w_h1 = to_vec<float>(file.at("H1_weights").get<std::vector<double>>());
+    if (m.w_h1.size() != static_cast<std::size_t>(m.hidden_l_max + 1) * C * C)
+        throw std::invalid_argument("H1_weights extent mismatch.");
+    {
+        const auto w = file.at("A1_weights").get<std::vector<std::vector<double>>>();
+        if (static_cast<int>(w.size()) != m.l_max + 1) throw std::invalid_argument("A1_weights extent mismatch.");
+        for (int l = 0; l <= m.l_max; ++l) {
+            if (w[l].size() != static_cast<std::size_t>(m.eta[l]) * C * C) throw std::invalid_argument("A1_weights extent mismatch.");
+            m.w_a1.push_back(to_vec<float>(w[l]));
+        }
+    }
+    {
+        const auto w = file.at("H2_weights_for_M0").get<std::vector<std::vector<double>>>();
+        if (static_cast<int>(w.size()) != A) throw std::invalid_argument("H2_weights_for_M0 extent mismatch.");
+        for (const auto& block : w) {
+            if (block.size() != static_cast<std::size_t>(C) * C) throw std::invalid_argument("H2_weights_for_M0 extent mismatch.");
+            const auto f = to_vec<float>(block);
+            m.h2_skip.insert(m.h2_skip.end(), f.begin(), f.end());
+        }
+    }
+    m.h2_m1 = to_vec<float>(file.at("H2_weights_for_M1").get<std::vector<double>>());
+    m.readout1 = to_vec<float>(file.at("readout_1_weights_for_M0").get<std::vector<double>>());
+    m.readout2_w1 = to_vec<float>(file.at("readout_2_weights_1").get<std::vector<double>>());
+    m.readout2_w2 = to_vec<float>(file.at("readout_2_weights_2").get<std::vector<double>>());
+    m.readout2_hidden = file.value("readout_2_hidden_size", 16);
+    m.readout2_scale = static_cast<float>(file.at("readout_2_scale_factor").get<double>());
+    if (m.h2_m1.size() != static_cast<std::size_t>(C) * C || m.readout1.size() != static_cast<std::size_t>(C)
+        || m.readout2_hidden <= 0 || m.readout2_hidden > 64
+        || m.readout2_w1.size() != static_cast<std::size_t>(C) * m.readout2_hidden
+        || m.readout2_w2.size() != static_cast<std::size_t>(m.readout2_hidden))
+        throw std::invalid_argument("MACE readout weights do not match the declared sizes.");
+    return m;
+}
+
+std::vector<float> fold_r0_table(const HostModel& m, const std::vector<int>& active_types)
+{
+    const int n = static_cast<int>(active_types.size());
+    const int C = m.channels, L = m.l_max + 1, F = L * C;
+    const int rows = (m.spline_points - 1) * 4;
+    std::vector<float> out(static_cast<std::size_t>(n) * n * rows * F);
+    std::vector<double> scaled(C), acc(C);
+    for (int ai = 0; ai < n; ++ai)
+        for (int aj = 0; aj < n; ++aj) {
+            const double* h0 = m.h0.data() + static_cast<std::size_t>(active_types[aj]) * C;
+            float* table = out.data() + static_cast<std::size_t>(ai * n + aj) * rows * F;
+            for (int row = 0; row < rows; ++row)
+                for (int l = 0; l < L; ++l) {
+                    const double* c = m.r0_coeff.data() + static_cast<std::size_t>(row) * F + l * C;
+                    const double* w = m.w_a0.data() + (static_cast<std::size_t>(active_types[ai]) * L + l) * C * C;
+                    for (int k = 0; k < C; ++k) scaled[k] = c[k] * h0[k];
+                    std::fill(acc.begin(), acc.end(), 0.0);
+                    for (int k = 0; k < C; ++k) {
+                        const double s = scaled[k];
+                        const double* wk = w + static_cast<std::size_t>(k) * C;
+                        for (int j = 0; j < C; ++j) acc[j] += s * wk[j];
+                    }
+                    float* o = table + static_cast<std::size_t>(row) * F + l * C;
+                    for (int j = 0; j < C; ++j) o[j] = static_cast<float>(acc[j]);
+                }
+        }
+    return out;
+}
+
+}  // namespace sxb

@@ -1,0 +1,75 @@
+// Host-side model container: reads a format-v4 compact MACE JSON file and turns it
+// into the flat tables the device kernels consume.  Mirrors what the reference's
+// loader and radial-table builder produce (libsymmetrix/source/mace.cpp:2660-2959,
+// compact_radial.cpp:227-366, cubic_spline_set.cpp:8-31), with the weights laid
+// out for the kernels of this library.
+#pragma once
+
+#include <cstdint>
+#include <string>
+#include <vector>
+
+namespace sxb {
+
+// Coupling structure of one compiled model shape, expanded from the generated
+// X-macro lists so that a model file can be matched against it at load time.
+struct ShapeTables {
+    const char* name;
+    int shape_id;                 // 0: hidden 0e, 1: 0e+1o, 2: 0e+1o+2e
+    int l_max, hidden_l_max;
+    int num_paths, num_rows, num_lme, num_terms;
+    std::vector<int> path_l, path_l1, path_l2;
+    std::vector<int> term_row, term_lme;
+    std::vector<std::vector<int>> m0_terms;   // compiled order, term index = position
+    std::vector<int> m0_out;                  // output component of each compiled term
+    std::vector<std::vector<int>> m1_terms;
+};
+
+const ShapeTables& shape_tables(int shape_id);
+int num_compiled_shapes();
+
+struct HostModel {
+    int shape_id = -1;
+    int num_elements = 0, channels = 0, l_max = 0, hidden_l_max = 0;
+    int num_lm = 0, num_hidden = 0, num_paths = 0, num_rows = 0, num_lme = 0, num_terms = 0;
+    double r_cut = 0.0;
+    std::vector<int> atomic_numbers;
+    std::vector<double> atomic_energies;
+    std::vector<int> eta;                    // paths per output l
+    std::vector<int> group_begin;            // first lme of each output l
+
+    // radial spline grid
+    double spline_x0 = 0.0, spline_h = 0.0;
+    int spline_points = 0;
+    // cubic coefficients [interval][4][functions], functions = (l_max+1)*C and paths*C
+    std::vector<double> r0_coeff, r1_coeff;
+    bool a0_scaled = false, a1_scaled = false;
+    std::vector<double> a0_density_coeff, a1_density_coeff;   // [interval][4]
+
+    std::vector<double> h0;                  // [A][C]
+    std::vector<double> w_a0;                // [A][l][C_in][C_out]
+    std::vector<float> m0_weights;           // [A][compiled term][C]
+    std::vector<float> m1_weights;           // [A][compiled term][C]
+    int m0_num_terms = 0, m1_num_terms = 0;
+    std::vector<float> w_h1;                 // [L+1][C_in][C_out]
+    std::vector<std::vector<float>> w_a1;    // per l: [eta_l*C][C]
+    std::vector<float> h2_skip;              // T[A][C_in][C_out]
+    std::vector<float> h2_m1;                // [C_in][C_out]
+    std::vector<float> readout1;             // q[C]
+    std::vector<float> readout2_w1;          // [hidden][C]
+    std::vector<float> readout2_w2;          // [hidden]
+    int readout2_hidden = 16;
+    float readout2_scale = 1.0f;
+    std::vector<float> cg;                   // [compiled term]
+};
+
+// Throws std::runtime_error / std::invalid_argument with a message naming the key.
+HostModel load_model(const std::string& json_path);
+
+// Folds H0[type_j] and W_A0[type_i][l] into the layer-0 spline coefficients for the
+// given active types (the reference does the same per ordered species pair,
+// mace_kokkos_factorized_lifecycle.cpp:3988-4047), in double, rounded once to float.
+// Output layout [pair = ai*n+aj][interval][4][(l_max+1)*C].
+std::vector<float> fold_r0_table(const HostModel& model, const std::vector<int>& active_types);
+
+}  // namespace sxb

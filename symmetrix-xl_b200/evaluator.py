@@ -1,0 +1,299 @@
+"""Host-side mirror of the reference evaluator class over the C-ABI library.
+
+``MACEB200`` keeps the method names, argument meaning and error behaviour of the
+pybind class ``MACEKokkosFloat`` that the reference's ASE calculator drives
+(symmetrix/source/cpp/mace_kokkos.cpp:262+; call order in
+symmetrix/source/symmetrix/calculator.py:2953-2971, 3253-3273, 3821-3894), so the
+parity tests read like the reference's own.  Arrays are copied in; results are
+fresh float64 NumPy arrays.  There is no CPU fallback: if the CUDA library is
+missing or no device is usable, construction raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+import numpy as np
+
+_PKG_DIR = Path(__file__).resolve().parent
+LIBRARY_PATH = _PKG_DIR / "libsymmetrix_b200.so"
+
+SXB_ERR_INVALID_ARGUMENT = -1
+SXB_ERR_RUNTIME = -2
+SXB_ERR_STALE_GRAPH = -3
+SXB_ERR_CAPACITY = -4
+
+_lib = None
+
+
+class ModelInfo(ctypes.Structure):
+    _fields_ = [("num_elements", ctypes.c_int32), ("num_channels", ctypes.c_int32), ("l_max", ctypes.c_int32),
+                ("hidden_l_max", ctypes.c_int32), ("num_paths", ctypes.c_int32), ("num_lme", ctypes.c_int32),
+                ("shape_id", ctypes.c_int32), ("reserved", ctypes.c_int32), ("r_cut", ctypes.c_double)]
+
+
+# name -> (restype, argtypes); every symbol include/symmetrix_b200.h declares
+_P = ctypes.c_void_p
+SIGNATURES = {
+    "sxb_create": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(_P)]),
+    "sxb_destroy": (None, [_P]),
+    "sxb_last_error": (ctypes.c_char_p, []),
+    "sxb_model_info_get": (ctypes.c_int, [_P, ctypes.POINTER(ModelInfo)]),
+    "sxb_atomic_numbers": (ctypes.c_int, [_P, _P, ctypes.c_int32]),
+    "sxb_prepare_periodic_graph": (ctypes.c_int, [_P, ctypes.c_int32, _P, _P, _P, _P, ctypes.c_double,
+                                                  ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_int64)]),
+    "sxb_prepare_graph": (ctypes.c_int, [_P, ctypes.c_int32, _P, _P, _P, _P, _P, ctypes.POINTER(ctypes.c_uint64)]),
+    "sxb_get_graph": (ctypes.c_int, [_P, ctypes.c_uint64, _P, _P, _P]),
+    "sxb_compute_positions": (ctypes.c_int, [_P, ctypes.c_uint64, _P]),
+    "sxb_compute_positions_device": (ctypes.c_int, [_P, ctypes.c_uint64, _P]),
+    "sxb_compute_edge_vectors": (ctypes.c_int, [_P, ctypes.c_uint64, _P]),
+    "sxb_synchronize": (ctypes.c_int, [_P]),
+    "sxb_get_node_energies": (ctypes.c_int, [_P, _P, ctypes.c_int64]),
+    "sxb_set_keep_edge_forces": (ctypes.c_int, [_P, ctypes.c_int32]),
+    "sxb_get_edge_forces": (ctypes.c_int, [_P, _P, ctypes.c_int64]),
+    "sxb_reduce_atom_forces": (ctypes.c_int, [_P, ctypes.c_uint64, _P, ctypes.c_int64]),
+    "sxb_reduce_stress": (ctypes.c_int, [_P, ctypes.c_uint64, ctypes.c_double, _P]),
+    "sxb_get_energy": (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_double)]),
+    "sxb_device_results": (ctypes.c_int, [_P, ctypes.POINTER(_P), ctypes.POINTER(_P), ctypes.POINTER(_P)]),
+    "sxb_get_stage": (ctypes.c_int, [_P, ctypes.c_char_p, _P, ctypes.c_int64, ctypes.POINTER(ctypes.c_int64)]),
+    "sxb_launch_count": (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_int64)]),
+    "sxb_last_compute_ms": (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_float)]),
+}
+
+
+def load_library():
+    """Loads the in-tree CUDA library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not LIBRARY_PATH.exists():
+            raise RuntimeError(f"{LIBRARY_PATH} is missing: build it with __graft_entry__.build(); "
+                               "this package has no CPU fallback")
+        lib = ctypes.CDLL(str(LIBRARY_PATH))
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = lib
+    return _lib
+
+
+def _check(status):
+    if status == 0:
+        return
+    message = load_library().sxb_last_error().decode()
+    if status in (SXB_ERR_INVALID_ARGUMENT, SXB_ERR_STALE_GRAPH, SXB_ERR_CAPACITY):
+        raise ValueError(message)
+    raise RuntimeError(message)
+
+
+def _i32(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def _f64(a):
+    return np.ascontiguousarray(a, dtype=np.float64)
+
+
+class MACEB200:
+    """FP32 evaluator of a compact two-layer MACE model on one B200."""
+
+    def __init__(self, filename, device: int = 0):
+        lib = load_library()
+        handle = _P()
+        _check(lib.sxb_create(str(filename).encode(), int(device), ctypes.byref(handle)))
+        self._h = handle
+        self._lib = lib
+        info = ModelInfo()
+        _check(lib.sxb_model_info_get(self._h, ctypes.byref(info)))
+        self.num_elements = info.num_elements
+        self.num_channels = info.num_channels
+        self.l_max = info.l_max
+        self.L_max = info.hidden_l_max
+        self.num_lme = info.num_lme
+        self.r_cut = info.r_cut
+        z = np.zeros(info.num_elements, dtype=np.int32)
+        _check(lib.sxb_atomic_numbers(self._h, z.ctypes.data, len(z)))
+        self.atomic_numbers = z.tolist()
+        self._num_nodes = 0
+        self._num_edges = 0
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.sxb_destroy(self._h)
+            self._h = None
+
+    # -- graph -----------------------------------------------------------------------------
+    def _prepare_periodic_factorized_graph(self, node_types, positions, cell, inverse_cell, neighbor_cutoff):
+        node_types, positions = _i32(node_types), _f64(positions).reshape(-1)
+        cell, inverse_cell = _f64(cell).reshape(-1), _f64(inverse_cell).reshape(-1)
+        if positions.size != 3 * node_types.size or cell.size != 9 or inverse_cell.size != 9:
+            raise ValueError("Neighbor graph input extents are inconsistent.")
+        gen, edges = ctypes.c_uint64(), ctypes.c_int64()
+        _check(self._lib.sxb_prepare_periodic_graph(self._h, node_types.size, node_types.ctypes.data, positions.ctypes.data,
+                                                    cell.ctypes.data, inverse_cell.ctypes.data, float(neighbor_cutoff),
+                                                    ctypes.byref(gen), ctypes.byref(edges)))
+        self._num_nodes, self._num_edges = int(node_types.size), int(edges.value)
+        return {"generation": int(gen.value), "num_edges": int(edges.value)}
+
+    def _prepare_factorized_graph(self, num_nodes, node_types, num_neigh, neigh_indices, neigh_types=None,
+                                  shifts=None, cell=None):
+        node_types, num_neigh, neigh_indices = _i32(node_types), _i32(num_neigh), _i32(neigh_indices)
+        if node_types.size != num_nodes or num_neigh.size != num_nodes or neigh_indices.size != int(num_neigh.sum()):
+            raise ValueError("Graph input extents are inconsistent.")
+        if neigh_types is not None and not np.array_equal(_i32(neigh_types), node_types[neigh_indices]):
+            raise ValueError("neigh_types disagree with node_types[neigh_indices].")
+        sp = cp = None
+        if shifts is not None:
+            shifts = _i32(shifts).reshape(-1)
+            cell = _f64(cell).reshape(-1)
+            if shifts.size != 3 * neigh_indices.size or cell.size != 9:
+                raise ValueError("Graph shift extents are inconsistent.")
+            sp, cp = shifts.ctypes.data, cell.ctypes.data
+        gen = ctypes.c_uint64()
+        _check(self._lib.sxb_prepare_graph(self._h, int(num_nodes), node_types.ctypes.data, num_neigh.ctypes.data,
+                                           neigh_indices.ctypes.data, sp, cp, ctypes.byref(gen)))
+        self._num_nodes, self._num_edges = int(num_nodes), int(neigh_indices.size)
+        return int(gen.value)
+
+    def graph(self, generation, with_shifts=True):
+        """(first_neigh, sources, shifts) of the prepared graph in caller node order."""
+        first = np.zeros(self._num_nodes + 1, dtype=np.int32)
+        sources = np.zeros(self._num_edges, dtype=np.int32)
+        shifts = np.zeros((self._num_edges, 3), dtype=np.int32) if with_shifts else None
+        _check(self._lib.sxb_get_graph(self._h, int(generation), first.ctypes.data, sources.ctypes.data,
+                                       shifts.ctypes.data if with_shifts else None))
+        return first, sources, shifts
+
+    # -- evaluation ------------------------------------------------------------------------
+    def _compute_prepared_factorized_positions(self, graph_generation, positions):
+        positions = _f64(positions).reshape(-1)
+        if positions.size != 3 * self._num_nodes:
+            raise ValueError("positions extent does not match the prepared graph.")
+        _check(self._lib.sxb_compute_positions(self._h, int(graph_generation), positions.ctypes.data))
+
+    def compute_positions_device(self, graph_generation, device_pointer: int):
+        """Evaluation from float64 positions already resident on the evaluator's device."""
+        _check(self._lib.sxb_compute_positions_device(self._h, int(graph_generation), ctypes.c_void_p(device_pointer)))
+
+    def _compute_prepared_factorized(self, execution_graph_generation, xyz, r=None):
+        xyz = _f64(xyz).reshape(-1)
+        if xyz.size != 3 * self._num_edges:
+            raise ValueError("xyz extent does not match the prepared graph.")
+        _check(self._lib.sxb_compute_edge_vectors(self._h, int(execution_graph_generation), xyz.ctypes.data))
+
+    def compute_node_energies_forces(self, num_nodes, node_types, num_neigh, neigh_indices, neigh_types, xyz, r=None,
+                                     execution_graph_generation=0):
+        """One-shot evaluation from a CSR graph and edge vectors; keeps the directed forces."""
+        if execution_graph_generation == 0:
+            execution_graph_generation = self._prepare_factorized_graph(num_nodes, node_types, num_neigh,
+                                                                       neigh_indices, neigh_types)
+        self.set_keep_edge_forces(True)
+        self._compute_prepared_factorized(execution_graph_generation, xyz, r)
+        return execution_graph_generation
+
+    def set_keep_edge_forces(self, enabled: bool):
+        _check(self._lib.sxb_set_keep_edge_forces(self._h, int(bool(enabled))))
+
+    @property
+    def node_energies(self):
+        out = np.zeros(self._num_nodes, dtype=np.float64)
+        _check(self._lib.sxb_get_node_energies(self._h, out.ctypes.data, out.size))
+        return out
+
+    @property
+    def node_forces(self):
+        """Directed forces dE/d(xyz_ij), [3*num_edges], caller edge order."""
+        out = np.zeros(3 * self._num_edges, dtype=np.float64)
+        _check(self._lib.sxb_get_edge_forces(self._h, out.ctypes.data, out.size))
+        return out
+
+    def _reduce_atom_forces(self, num_nodes, edge_receivers=None, edge_sources=None, execution_graph_generation=0):
+        if execution_graph_generation == 0:
+            raise ValueError("Atom-force reduction needs the generation of the prepared graph.")
+        out = np.zeros((int(num_nodes), 3), dtype=np.float64)
+        _check(self._lib.sxb_reduce_atom_forces(self._h, int(execution_graph_generation), out.ctypes.data, out.size))
+        return out
+
+    def _reduce_stress(self, volume, xyz=None, execution_graph_generation=0):
+        if execution_graph_generation == 0:
+            raise ValueError("Stress reduction needs the generation of the prepared graph.")
+        out = np.zeros((3, 3), dtype=np.float64)
+        _check(self._lib.sxb_reduce_stress(self._h, int(execution_graph_generation), float(volume), out.ctypes.data))
+        return out
+
+    @property
+    def energy(self):
+        value = ctypes.c_double()
+        _check(self._lib.sxb_get_energy(self._h, ctypes.byref(value)))
+        return value.value
+
+    def stage(self, name):
+        """A stage tensor of the last evaluation as float64, caller node order (parity tests)."""
+        count = ctypes.c_int64()
+        _check(self._lib.sxb_get_stage(self._h, name.encode(), None, 0, ctypes.byref(count)))
+        out = np.zeros(count.value, dtype=np.float64)
+        _check(self._lib.sxb_get_stage(self._h, name.encode(), out.ctypes.data, out.size, ctypes.byref(count)))
+        return out
+
+    def device_results(self):
+        e, f, v = _P(), _P(), _P()
+        _check(self._lib.sxb_device_results(self._h, ctypes.byref(e), ctypes.byref(f), ctypes.byref(v)))
+        return e.value, f.value, v.value
+
+    def synchronize(self):
+        _check(self._lib.sxb_synchronize(self._h))
+
+    @property
+    def launch_count(self):
+        value = ctypes.c_int64()
+        _check(self._lib.sxb_launch_count(self._h, ctypes.byref(value)))
+        return value.value
+
+    @property
+    def last_compute_ms(self):
+        value = ctypes.c_float()
+        _check(self._lib.sxb_last_compute_ms(self._h, ctypes.byref(value)))
+        return value.value
+
+
+class Calculator:
+    """Minimal stand-in for the reference's ASE calculator hot path (``Symmetrix.calculate``,
+    symmetrix/source/symmetrix/calculator.py:3934-4021): Verlet-skin neighbor cache (rebuild when
+    the largest displacement exceeds skin/2, :2894-2899), device graph builder, evaluation from
+    positions, and result assembly (:3821-3894)."""
+
+    def __init__(self, model_path, skin: float = 0.5, device: int = 0):
+        self.evaluator = MACEB200(model_path, device)
+        self.skin = float(skin)
+        self._generation = 0
+        self._reference_positions = None
+        self._reference_cell = None
+        self._types = None
+        self.rebuilds = 0
+
+    def calculate(self, positions, cell, node_types):
+        positions = _f64(positions).reshape(-1, 3)
+        cell = _f64(cell).reshape(3, 3)
+        node_types = _i32(node_types)
+        reuse = (self._generation != 0 and self._reference_positions.shape == positions.shape
+                 and np.array_equal(self._reference_cell, cell) and np.array_equal(self._types, node_types)
+                 and np.sqrt(((positions - self._reference_positions) ** 2).sum(axis=1).max()) <= 0.5 * self.skin)
+        if not reuse:
+            result = self.evaluator._prepare_periodic_factorized_graph(
+                node_types, positions, cell, np.linalg.inv(cell), self.evaluator.r_cut + self.skin)
+            self._generation = result["generation"]
+            self._reference_positions = positions.copy()
+            self._reference_cell = cell.copy()
+            self._types = node_types.copy()
+            self.rebuilds += 1
+        ev = self.evaluator
+        ev._compute_prepared_factorized_positions(self._generation, positions)
+        n = len(node_types)
+        volume = abs(np.linalg.det(cell))
+        energies = ev.node_energies
+        return {
+            "energy": float(energies.sum()),
+            "energies": energies,
+            "forces": ev._reduce_atom_forces(n, execution_graph_generation=self._generation),
+            "stress": ev._reduce_stress(volume, execution_graph_generation=self._generation),
+        }

@@ -1,0 +1,174 @@
+"""GPU parity tests: the CUDA path through the C ABI against the oracles on identical inputs.
+
+Tolerances are BASELINE's: |dE| <= 1e-5 eV/atom, |dF| <= 1e-4 eV/A per component,
+|dsigma| <= 1e-6 eV/A^3; the neighbor list must be bit-exact.
+"""
+import numpy as np
+import pytest
+
+from conftest import csr_from_positions
+from oracle import mace_numpy, neighbor, ref
+
+pytestmark = pytest.mark.gpu
+
+TOL_E, TOL_F, TOL_S = 1e-5, 1e-4, 1e-6
+
+STAGES = ["A0", "M0", "H1", "Phi1", "A1", "M1", "H2", "H2_adj", "A1_adj", "dPhi1", "H1_adj", "M0_adj", "A0_adj"]
+
+
+def _edge_set(first, src, shifts):
+    recv = np.repeat(np.arange(len(first) - 1), np.diff(first))
+    return np.stack([recv, src, shifts[:, 0], shifts[:, 1], shifts[:, 2]], axis=1)
+
+
+@pytest.mark.parametrize("n,sigma,cutoff,seed", [(3, 0.05, 5.5, 0), (4, 0.05, 5.5, 1), (4, 0.3, 6.5, 2), (2, 0.05, 6.5, 3)])
+def test_neighbor_graph_bit_exact(pkg, model_path, n, sigma, cutoff, seed):
+    pos, cell, types = pkg.modelgen.srtio3(n, sigma, seed)
+    ev = pkg.MACEB200(model_path("small"))
+    res = ev._prepare_periodic_factorized_graph(types, pos, cell, np.linalg.inv(cell), cutoff)
+    first, src, shifts = ev.graph(res["generation"])
+    ofirst, osrc, oshifts = neighbor.build_neighbor_graph(pos, cell, cutoff)
+    assert res["num_edges"] == len(osrc)
+    # identical order, not only identical sets
+    assert np.array_equal(first, ofirst)
+    assert np.array_equal(src, osrc)
+    assert np.array_equal(shifts, oshifts)
+
+
+def test_neighbor_graph_triclinic_and_wrapped(pkg, model_path):
+    rng = np.random.default_rng(7)
+    cell = np.array([[9.0, 0.0, 0.0], [2.5, 8.0, 0.0], [-1.0, 1.5, 10.0]])
+    pos = rng.random((60, 3)) @ cell + rng.integers(-2, 3, size=(60, 3)) @ cell  # atoms outside the home cell
+    types = rng.integers(0, 3, size=60).astype(np.int32)
+    ev = pkg.MACEB200(model_path("small"))
+    res = ev._prepare_periodic_factorized_graph(types, pos, cell, np.linalg.inv(cell), 4.0)
+    first, src, shifts = ev.graph(res["generation"])
+    ofirst, osrc, oshifts = neighbor.build_neighbor_graph(pos, cell, 4.0)
+    assert np.array_equal(first, ofirst) and np.array_equal(src, osrc) and np.array_equal(shifts, oshifts)
+    brute = neighbor.brute_force_edges(pos, cell, 4.0, max_image=6)
+    mine = set(map(tuple, _edge_set(first, src, shifts).tolist()))
+    assert mine == brute
+
+
+@pytest.mark.parametrize("arch,n", [("small", 3), ("medium", 2)])
+def test_stage_tensors_match_oracle(pkg, model_path, arch, n):
+    path = model_path(arch)
+    pos, cell, types = pkg.modelgen.srtio3(n, 0.05, 11)
+    cutoff = pkg.modelgen.ARCHITECTURES[arch]["r_cut"]
+    first, src, shifts, xyz = csr_from_positions(pos, cell, cutoff)
+    ev = pkg.MACEB200(path)
+    ev.compute_node_energies_forces(len(pos), types, np.diff(first), src, types[src], xyz)
+    oracle = mace_numpy.NumpyMACE(str(path))
+    oracle.compute(types, first, src, xyz)
+    for name in STAGES:
+        got = ev.stage(name)
+        want = oracle.stage[name].reshape(-1)
+        scale = max(1.0, np.abs(want).max())
+        assert np.abs(got - want).max() <= 2e-5 * scale, name
+    de = np.abs(ev.node_energies - oracle.stage["node_energies"]).max()
+    df = np.abs(ev.node_forces.reshape(-1, 3) - oracle.stage["node_forces"]).max()
+    assert de <= TOL_E and df <= TOL_F
+
+
+@pytest.mark.parametrize("arch,n,seed", [("small", 4, 0), ("medium", 3, 1)])
+def test_energy_forces_stress_vs_reference_evaluator(pkg, model_path, arch, n, seed):
+    """Against the reference's own serial evaluator (MACECPU<double> and <float>)."""
+    if not ref.available():
+        pytest.skip("oracle/_ref was not built")
+    path = model_path(arch)
+    pos, cell, types = pkg.modelgen.srtio3(n, 0.05, seed)
+    calc = pkg.Calculator(path, skin=0.5)
+    out = calc.calculate(pos, cell, types)
+    r_cut = calc.evaluator.r_cut
+    # exact-cutoff graph for the reference (skin edges contribute exactly zero on the device path)
+    first, src, shifts, xyz = csr_from_positions(pos, cell, r_cut)
+    volume = abs(np.linalg.det(cell))
+    for double in (True, False):
+        m = ref.ReferenceMACE(str(path), double=double)
+        m.compute(types, np.diff(first), src, xyz)
+        F, S = ref.reduce_forces_stress(len(pos), np.diff(first), src, m.get("node_forces"), xyz, volume)
+        e = m.get("node_energies")
+        assert abs(out["energy"] - e.sum()) / len(pos) <= TOL_E
+        assert np.abs(out["energies"] - e).max() <= TOL_E
+        assert np.abs(out["forces"] - F).max() <= TOL_F
+        assert np.abs(out["stress"] - S).max() <= TOL_S
+
+
+def test_tiny_systems_and_isolated_atoms(pkg, model_path):
+    """3..9 atoms (tile-boundary sizes of the reference's tests) and an atom with no neighbors."""
+    path = model_path("small")
+    oracle = mace_numpy.NumpyMACE(str(path))
+    rng = np.random.default_rng(3)
+    for natoms in (3, 4, 5, 8, 9):
+        cell = np.eye(3) * 14.0
+        pos = rng.random((natoms, 3)) * 5.0 + 1.0
+        pos[0] = [12.0, 12.0, 12.0] if natoms > 3 else pos[0]   # far from the others: empty neighbor list
+        # keep a sane minimum distance
+        for i in range(1, natoms):
+            while i > 0 and np.min(np.linalg.norm(pos[:i] - pos[i], axis=1)) < 1.5:
+                pos[i] = rng.random(3) * 5.0 + 1.0
+        types = rng.integers(0, 3, size=natoms).astype(np.int32)
+        calc = pkg.Calculator(path, skin=0.5)
+        out = calc.calculate(pos, cell, types)
+        first, src, shifts = neighbor.build_neighbor_graph(pos, cell, calc.evaluator.r_cut + 0.5)
+        e, energies, F, S = oracle.energy_forces_stress(types, pos, cell, first, src, shifts)
+        assert abs(out["energy"] - e) / natoms <= TOL_E
+        assert np.abs(out["forces"] - F).max() <= TOL_F
+        assert np.abs(out["stress"] - S).max() <= TOL_S
+
+
+def test_skin_graph_matches_exact_graph_and_is_reused(pkg, model_path):
+    """Skin 0.5 vs exact graph, and no rebuild after a 0.1 A move
+    (reference: symmetrix/test/test_mace_streamed_edges.py:4592-4676)."""
+    path = model_path("small")
+    pos, cell, types = pkg.modelgen.srtio3(3, 0.05, 2)
+    skin = pkg.Calculator(path, skin=0.5)
+    exact = pkg.Calculator(path, skin=0.0)
+    a, b = skin.calculate(pos, cell, types), exact.calculate(pos, cell, types)
+    assert abs(a["energy"] - b["energy"]) / len(pos) <= 1e-6
+    assert np.abs(a["forces"] - b["forces"]).max() <= 1e-5
+    moved = pos + np.random.default_rng(0).normal(scale=0.03, size=pos.shape)
+    a2 = skin.calculate(moved, cell, types)
+    assert skin.rebuilds == 1
+    b2 = pkg.Calculator(path, skin=0.0).calculate(moved, cell, types)
+    assert abs(a2["energy"] - b2["energy"]) / len(pos) <= 1e-6
+    assert np.abs(a2["forces"] - b2["forces"]).max() <= 1e-5
+
+
+def test_stale_generation_and_bad_inputs_raise(pkg, model_path):
+    ev = pkg.MACEB200(model_path("small"))
+    pos, cell, types = pkg.modelgen.srtio3(2, 0.05, 0)
+    with pytest.raises(ValueError):
+        ev._compute_prepared_factorized_positions(1, pos)            # nothing prepared
+    res = ev._prepare_periodic_factorized_graph(types, pos, cell, np.linalg.inv(cell), 5.5)
+    ev._compute_prepared_factorized_positions(res["generation"], pos)
+    res2 = ev._prepare_periodic_factorized_graph(types, pos, cell, np.linalg.inv(cell), 5.5)
+    assert res2["generation"] > res["generation"]
+    with pytest.raises(ValueError):
+        ev._compute_prepared_factorized_positions(res["generation"], pos)   # stale token
+    with pytest.raises(ValueError):
+        ev._prepare_periodic_factorized_graph(types, pos, cell, np.linalg.inv(cell) * 2.0, 5.5)  # inconsistent inverse
+    with pytest.raises(ValueError):
+        ev._prepare_periodic_factorized_graph(types + 7, pos, cell, np.linalg.inv(cell), 5.5)     # type out of range
+    bad = pos.copy()
+    bad[1] = bad[0]                                                     # zero-length edge
+    res3 = ev._prepare_periodic_factorized_graph(types, pos, cell, np.linalg.inv(cell), 5.5)
+    with pytest.raises(ValueError):
+        ev._compute_prepared_factorized_positions(res3["generation"], bad)
+
+
+def test_forces_are_energy_gradient(pkg, model_path):
+    """Finite-difference check (reference: symmetrix/test/test_mace.py:74-85)."""
+    path = model_path("small")
+    pos, cell, types = pkg.modelgen.srtio3(2, 0.05, 4)
+    calc = pkg.Calculator(path, skin=0.5)
+    base = calc.calculate(pos, cell, types)
+    h = 2e-3
+    for atom, axis in ((0, 0), (7, 1), (13, 2)):
+        p, m = pos.copy(), pos.copy()
+        p[atom, axis] += h
+        m[atom, axis] -= h
+        ep = calc.calculate(p, cell, types)["energy"]
+        em = calc.calculate(m, cell, types)["energy"]
+        fd = -(ep - em) / (2 * h)
+        assert abs(fd - base["forces"][atom, axis]) <= 5e-3 * max(1.0, abs(fd))
