@@ -1,0 +1,328 @@
+"""Benchmark of the force path: us/atom/step for one complete energy + forces + stress evaluation.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Workload at every N: the MACE-OMAT-0-medium architecture (random-init weights from a seed) on a
+10x10x10 cubic SrTiO3 supercell (5,000 atoms, a = 3.905 A, sigma = 0.05 A perturbation, 0.5 A
+neighbor skin), FP32 -- per GPU.  For N > 1 each rank evaluates its own replica (weak scaling).
+`value` is timed with the positions already resident in HBM; `e2e` goes through the host-facing
+call with pinned host buffers (positions H2D, energies / forces / stress D2H inside the timed
+region).  The reference arm (`--impl reference`) times the reference's own serial CPU evaluator
+(oracle/_ref) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "us/atom/step (E+F+stress, FP32)"
+UNIT = "us/atom"
+SUPERCELL = 10
+SIGMA = 0.05
+SKIN = 0.5
+SEED = 17
+# algorithmic work of the reference's formulation per (edge, channel), see DESIGN.md
+FLOP_PER_EDGE_CHANNEL = {"l0_forward": 56, "l0_reverse": 284, "l1_forward": 408, "l1_reverse": 850}
+
+
+def _peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return float(data["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, sm_max, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                sm_max.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[5:9]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(sm_max) if sm_max else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_workload(tmpdir):
+    import __graft_entry__ as graft
+
+    pkg = graft.load_package()
+    model = Path(tmpdir) / "medium.json"
+    pkg.modelgen.write_model(model, "medium", seed=SEED)
+    pos, cell, types = pkg.modelgen.srtio3(SUPERCELL, SIGMA, SEED)
+    return pkg, model, pos, cell, types
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    torch.cuda.set_device(local_rank)
+    with tempfile.TemporaryDirectory() as tmp:
+        pkg, model, pos, cell, types = build_workload(tmp)
+        ev = pkg.MACEB200(model, device=local_rank)
+        n = len(pos)
+        volume = abs(np.linalg.det(cell))
+        res = ev._prepare_periodic_factorized_graph(types, pos, cell, np.linalg.inv(cell), ev.r_cut + SKIN)
+        gen, num_edges = res["generation"], res["num_edges"]
+        first, sources, shifts = ev.graph(gen)
+        recv = np.repeat(np.arange(n), np.diff(first))
+        xyz = pos[sources] - pos[recv] + shifts @ cell
+        active_edges = int((np.sqrt((xyz * xyz).sum(1)) < ev.r_cut).sum())
+
+        d_pos = torch.from_numpy(pos.reshape(-1).copy()).cuda()
+        flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+        pinned_pos = torch.from_numpy(pos.reshape(-1).copy()).pin_memory()
+        host_pos = pinned_pos.numpy()
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        def step_device():
+            ev.compute_positions_device(gen, d_pos.data_ptr())
+            return ev.last_compute_ms
+
+        def step_e2e():
+            t0 = time.perf_counter()
+            ev._compute_prepared_factorized_positions(gen, host_pos)
+            energies = ev.node_energies
+            forces = ev._reduce_atom_forces(n, execution_graph_generation=gen)
+            stress = ev._reduce_stress(volume, execution_graph_generation=gen)
+            return (time.perf_counter() - t0) * 1e3, float(energies.sum()), forces, stress
+
+        for _ in range(max(args.warmup, 3)):
+            flush.fill_(1)
+            step_device()
+        barrier()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        launches_before = ev.launch_count
+        wall0 = time.perf_counter()
+        device_ms = []
+        for _ in range(args.steps):
+            flush.fill_(1)
+            torch.cuda.synchronize()
+            device_ms.append(step_device())
+        barrier()
+        wall_ms = (time.perf_counter() - wall0) * 1e3
+        launches = ev.launch_count - launches_before
+        # end to end through the host-facing call
+        for _ in range(3):
+            step_e2e()
+        e2e_ms = []
+        for _ in range(args.steps):
+            flush.fill_(1)
+            torch.cuda.synchronize()
+            e2e_ms.append(step_e2e()[0])
+        clocks = sampler.stop()
+        # per-kernel device times (separate pass with event pairs around each stage)
+        ev.set_profiling(True)
+        stage_ms = {}
+        reps = 5
+        for _ in range(reps):
+            flush.fill_(1)
+            torch.cuda.synchronize()
+            step_device()
+            for name, ms, _l in ev.profile():
+                stage_ms[name] = stage_ms.get(name, 0.0) + ms / reps
+        ev.set_profiling(False)
+
+        step_ms = float(np.mean(device_ms))
+        e2e_step_ms = float(np.mean(e2e_ms))
+        if world > 1:
+            t = torch.tensor([step_ms, e2e_step_ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            step_ms, e2e_step_ms = float(t[0]), float(t[1])
+        total_atoms = n * world
+        value = step_ms * 1e3 / n          # us/atom/step on each GPU's own replica; atoms/s scales with N
+        e2e_value = e2e_step_ms * 1e3 / n
+
+        C = ev.num_channels
+        dominant = max((k for k in stage_ms if k in FLOP_PER_EDGE_CHANNEL), key=lambda k: stage_ms[k])
+        hbm_peak, peak_kind = _peaks()
+        num_lme, num_hidden = ev.num_lme, (ev.L_max + 1) ** 2
+        # compulsory HBM bytes of one launch of each edge kernel: geometry record + source
+        # index per edge, plus the node rows the kernel must read / write once
+        node_rows = {"l0_forward": 16, "l0_reverse": 16, "l1_forward": num_lme + num_hidden,
+                     "l1_reverse": num_lme + 3 * num_hidden}
+        alg_bytes = num_edges * 20 + n * node_rows[dominant] * C * 4
+        dom_s = stage_ms[dominant] * 1e-3
+        achieved = alg_bytes / dom_s / 1e9
+        alg_flops = FLOP_PER_EDGE_CHANNEL[dominant] * active_edges * C
+        roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                    "frac": achieved / hbm_peak, "peak_source": f"{peak_kind} copy bandwidth", "traffic": None,
+                    "kernel_ms": stage_ms[dominant], "algorithmic_bytes": alg_bytes,
+                    "algorithmic_gflop": alg_flops / 1e9, "achieved_fp32_tflops": alg_flops / dom_s / 1e12,
+                    "note": "edge kernels are FP32-issue / L2 bound, not HBM bound; both figures are reported"}
+
+        cpu = None
+        if rank == 0 and world == 1:
+            cpu = cpu_baseline(pkg, model, sample_cells=3, calls=2)
+
+        if world > 1:
+            dist.barrier()
+        if rank == 0:
+            line = {
+                "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": False, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "medium-5000-SrTiO3", "atoms_per_gpu": n, "total_atoms": total_atoms,
+                           "edges_per_gpu": num_edges, "active_edges_per_gpu": active_edges, "skin": SKIN,
+                           "parallelism": "replicas" if world > 1 else "single", "elements": 3,
+                           "l2": "flushed between timed steps (256 MiB write)"},
+                "atoms_per_s": total_atoms / (step_ms * 1e-3),
+                "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 24 * n,
+                        "d2h_bytes_per_step": 8 * n + 24 * n + 72 + 80, "ms_per_step": e2e_step_ms},
+                "gpu_launches": int(launches),
+                "clocks": clocks,
+                "roofline": roofline,
+                "stage_ms": {k: round(v, 4) for k, v in stage_ms.items()},
+                "wall_ms_timed_region": wall_ms,
+            }
+            if cpu is not None:
+                line["cpu_baseline"] = cpu
+            print(json.dumps(line))
+        if world > 1:
+            dist.destroy_process_group()
+
+
+def cpu_baseline(pkg, model, sample_cells=3, calls=2):
+    """Times the reference's serial evaluator (oracle/_ref, MACECPU<float>) on a bounded sample."""
+    from oracle import neighbor, ref
+
+    if not ref.available():
+        return {"value": None, "unit": UNIT, "cores": 0, "kind": "reference", "sample": "oracle/_ref not built"}
+    pos, cell, types = pkg.modelgen.srtio3(sample_cells, SIGMA, SEED)
+    m = ref.ReferenceMACE(str(model), double=False)
+    first, src, shifts = neighbor.build_neighbor_graph(pos, cell, m.r_cut)
+    xyz = neighbor.edge_vectors(pos, cell, first, src, shifts)
+    m.compute(types, np.diff(first), src, xyz)   # warm-up (builds the radial cache)
+    times = []
+    for _ in range(calls):
+        t0 = time.perf_counter()
+        m.compute(types, np.diff(first), src, xyz)
+        times.append(time.perf_counter() - t0)
+    value = statistics.median(times) * 1e6 / len(pos)
+    return {"value": value, "unit": UNIT, "cores": 1, "kind": "reference",
+            "sample": f"{len(pos)}-atom SrTiO3 ({sample_cells}x{sample_cells}x{sample_cells}), same model, "
+                      f"{len(src)} edges at the model cutoff, median of {calls} calls of MACECPU<float> (serial)"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    with tempfile.TemporaryDirectory() as tmp:
+        pkg, model, pos, cell, types = build_workload(tmp)
+        from oracle import neighbor, ref
+
+        if not ref.available():
+            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref was not built in this snapshot"}))
+            return
+        cells = 3
+        spos, scell, stypes = pkg.modelgen.srtio3(cells, SIGMA, SEED)
+        m = ref.ReferenceMACE(str(model), double=False)
+        first, src, shifts = neighbor.build_neighbor_graph(spos, scell, m.r_cut)
+        xyz = neighbor.edge_vectors(spos, scell, first, src, shifts)
+        warm = max(1, min(args.warmup, 2))
+        steps = max(1, min(args.steps, 5))
+        for _ in range(warm):
+            m.compute(stypes, np.diff(first), src, xyz)
+        times = []
+        for _ in range(steps):
+            t0 = time.perf_counter()
+            m.compute(stypes, np.diff(first), src, xyz)
+            times.append(time.perf_counter() - t0)
+        ms = float(np.mean(times)) * 1e3
+        value = ms * 1e3 / len(spos)
+        sample = (f"{len(spos)}-atom SrTiO3 ({cells}x{cells}x{cells}) with the workload's model and perturbation, "
+                  f"{len(src)} edges; reference serial evaluator MACECPU<float> (no OpenMP in its source), "
+                  f"{steps} timed calls")
+        print(json.dumps({
+            "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps,
+            "warmup": warm, "ms_per_step": ms, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "medium-5000-SrTiO3", "sample_atoms": len(spos)},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": 1, "kind": "reference", "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }))
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=10)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

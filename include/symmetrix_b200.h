@@ -126,6 +126,15 @@ int sxb_get_stage(sxb_evaluator* evaluator, const char* name, double* out, int64
 int sxb_launch_count(const sxb_evaluator* evaluator, int64_t* out);
 int sxb_last_compute_ms(const sxb_evaluator* evaluator, float* out);
 
+/* Per-stage device times of the last compute (CUDA events on the evaluator's stream around each
+ * kernel group), collected only while profiling is enabled; counterpart of the reference's per-stage
+ * counters (factorized_last_evaluation_ms ..., libsymmetrix/source/mace_kokkos.hpp:1431-1454).
+ * sxb_profile_entry returns the number of entries through `count`; index outside [0,count) only
+ * reports the count. */
+int sxb_set_profiling(sxb_evaluator* evaluator, int32_t enabled);
+int sxb_profile_entry(const sxb_evaluator* evaluator, int32_t index, char* name, int32_t name_capacity, float* ms,
+                      int32_t* launches, int32_t* count);
+
 #ifdef __cplusplus
 }
 #endif

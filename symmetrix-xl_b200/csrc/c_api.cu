@@ -231,4 +231,27 @@ int sxb_last_compute_ms(const sxb_evaluator* ev, float* out)
     return guarded([&] { require(ev, "evaluator"); require(out, "out"); *out = ev->impl.last_ms(); });
 }
 
+int sxb_set_profiling(sxb_evaluator* ev, int32_t enabled)
+{
+    return guarded([&] { require(ev, "evaluator"); ev->impl.set_profiling(enabled != 0); });
+}
+
+int sxb_profile_entry(const sxb_evaluator* ev, int32_t index, char* name, int32_t name_capacity, float* ms, int32_t* launches,
+                      int32_t* count)
+{
+    return guarded([&] {
+        require(ev, "evaluator");
+        const auto& profile = ev->impl.profile();
+        if (count) *count = static_cast<int32_t>(profile.size());
+        if (index < 0 || index >= static_cast<int32_t>(profile.size())) return;
+        const auto& entry = profile[index];
+        if (name != nullptr && name_capacity > 0) {
+            std::strncpy(name, entry.name.c_str(), name_capacity - 1);
+            name[name_capacity - 1] = 0;
+        }
+        if (ms) *ms = entry.ms;
+        if (launches) *launches = entry.launches;
+    });
+}
+
 }  // extern "C"

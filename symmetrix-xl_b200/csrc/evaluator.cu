@@ -120,6 +120,7 @@ Evaluator::~Evaluator()
     cudaSetDevice(device_);
     if (event_begin_) cudaEventDestroy(event_begin_);
     if (event_end_) cudaEventDestroy(event_end_);
+    for (auto e : event_pool_) cudaEventDestroy(e);
     if (stream_) cudaStreamDestroy(stream_);
 }
 
@@ -380,8 +381,40 @@ void Evaluator::launch_gemm(const float* A, const RowMap& a_rows, const float* B
     launches_ += 1;
 }
 
+cudaEvent_t Evaluator::pooled_event()
+{
+    if (events_used_ == event_pool_.size()) {
+        cudaEvent_t e;
+        SXB_CUDA(cudaEventCreate(&e));
+        event_pool_.push_back(e);
+    }
+    return event_pool_[events_used_++];
+}
+
+void Evaluator::span_begin(const char* name)
+{
+    if (!profiling_) return;
+    Span s;
+    s.name = name;
+    s.begin = pooled_event();
+    s.end = pooled_event();
+    s.launches = 0;
+    span_launch_mark_ = launches_;
+    SXB_CUDA(cudaEventRecord(s.begin, stream_));
+    spans_.push_back(s);
+}
+
+void Evaluator::span_end()
+{
+    if (!profiling_) return;
+    spans_.back().launches = static_cast<int>(launches_ - span_launch_mark_);
+    SXB_CUDA(cudaEventRecord(spans_.back().end, stream_));
+}
+
 void Evaluator::run_pipeline()
 {
+    spans_.clear();
+    events_used_ = 0;
     const int N = num_nodes_, C = model_.channels, NH = model_.num_hidden, NE = model_.num_lme;
     const int n_active = static_cast<int>(active_types_.size());
     SXB_CUDA(cudaMemsetAsync(forces_.ptr, 0, sizeof(double) * 3 * N, stream_));
@@ -390,37 +423,51 @@ void Evaluator::run_pipeline()
     SXB_CUDA(cudaMemsetAsync(virial_slots_.ptr, 0, sizeof(double) * kVirialSlots * 9, stream_));
 
     // layer 0 forward
+    span_begin("l0_forward");
     l0_forward_kernel<<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
+    launches_ += 1;
+    span_end();
+    span_begin("m0_forward");
     const dim3 poly_grid(blocks_for(N, kPolyWarps), C / 32);
     if (model_.shape_id == 0)
         m0_forward_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A0_.ptr, element_.ptr, m0_weights_.ptr, M0_.ptr);
     else
         m0_forward_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A0_.ptr, element_.ptr, m0_weights_.ptr, M0_.ptr);
-    launches_ += 2;
+    launches_ += 1;
+    span_end();
     // H1_il = M0_il W_l
+    span_begin("gemm_h1");
     for (int l = 0; l <= model_.hidden_l_max; ++l) {
         const RowMap rows{static_cast<long>(NH) * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
         launch_gemm(M0_.ptr, rows, w_h1_.ptr + static_cast<std::size_t>(l) * C * C, C, false, H1_.ptr, rows, 0, N, C, C, false, nullptr);
     }
+    span_end();
     // layer 1 forward
+    span_begin("l1_forward");
     if (model_.shape_id == 0)
         l1_forward_kernel_S0<<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, r1_table_.ptr, H1_.ptr, coupling_, Phi1_.ptr);
     else
         l1_forward_kernel_S1<<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, r1_table_.ptr, H1_.ptr, coupling_, Phi1_.ptr);
     launches_ += 1;
+    span_end();
     // A1_il = Phi1_il W_l
+    span_begin("gemm_a1");
     for (int l = 0; l <= model_.l_max; ++l) {
         const int eta = model_.eta[l];
         const RowMap a_rows{static_cast<long>(NE) * C, static_cast<long>(eta) * C, static_cast<long>(model_.group_begin[l]) * C, 2 * l + 1};
         const RowMap c_rows{16L * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
         launch_gemm(Phi1_.ptr, a_rows, w_a1_[l].ptr, C, false, A1_.ptr, c_rows, 0, N, C, eta * C, false, nullptr);
     }
+    span_end();
+    span_begin("m1_forward");
     if (model_.shape_id == 0)
         m1_forward_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A1_.ptr, element_.ptr, m1_weights_.ptr, M1_.ptr);
     else
         m1_forward_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A1_.ptr, element_.ptr, m1_weights_.ptr, M1_.ptr);
     launches_ += 1;
+    span_end();
     // H2 = xs T_element + M1 W
+    span_begin("gemm_h2");
     const RowMap scalar_rows{static_cast<long>(NH) * C, C, 0, 1};
     const RowMap flat_rows{static_cast<long>(C), C, 0, 1};
     for (int a = 0; a < n_active; ++a) {
@@ -429,24 +476,34 @@ void Evaluator::run_pipeline()
                     flat_rows, begin, count, C, C, false, nullptr);
     }
     launch_gemm(M1_.ptr, flat_rows, h2_m1_.ptr, C, false, H2_.ptr, flat_rows, 0, N, C, C, true, nullptr);
+    span_end();
+    span_begin("readout");
     readout_kernel<<<blocks_for(static_cast<long>(N) * 32, 256), 256, 0, stream_>>>(
         N, C, model_.readout2_hidden, model_.readout2_scale, M0_.ptr, NH, H2_.ptr, element_.ptr, atomic_energies_.ptr,
         readout1_.ptr, readout2_w1_.ptr, readout2_w2_.ptr, node_energies_.ptr, H2_adj_.ptr, energy_slots_.ptr);
     launches_ += 1;
+    span_end();
 
     // reverse
+    span_begin("gemm_h2_reverse");
     launch_gemm(H2_adj_.ptr, flat_rows, h2_m1_.ptr, C, true, M1_adj_.ptr, flat_rows, 0, N, C, C, false, nullptr);
+    span_end();
+    span_begin("m1_reverse");
     if (model_.shape_id == 0)
         m1_reverse_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A1_.ptr, element_.ptr, m1_weights_.ptr, M1_adj_.ptr, A1_adj_.ptr);
     else
         m1_reverse_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A1_.ptr, element_.ptr, m1_weights_.ptr, M1_adj_.ptr, A1_adj_.ptr);
     launches_ += 1;
+    span_end();
+    span_begin("gemm_a1_reverse");
     for (int l = 0; l <= model_.l_max; ++l) {
         const int eta = model_.eta[l];
         const RowMap a_rows{16L * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
         const RowMap c_rows{static_cast<long>(NE) * C, static_cast<long>(eta) * C, static_cast<long>(model_.group_begin[l]) * C, 2 * l + 1};
         launch_gemm(A1_adj_.ptr, a_rows, w_a1_[l].ptr, C, true, dPhi1_.ptr, c_rows, 0, N, eta * C, C, false, nullptr);
     }
+    span_end();
+    span_begin("l1_reverse");
     ForceOutputs fo;
     fo.atom_forces = forces_.ptr;
     fo.virial_slots = virial_slots_.ptr;
@@ -457,6 +514,8 @@ void Evaluator::run_pipeline()
     else
         l1_reverse_kernel_S1<<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, r1_table_.ptr, H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
     launches_ += 1;
+    span_end();
+    span_begin("gemm_h1_reverse");
     // M0_adj_il = H1_adj_il W_l^T, then the direct adjoint q + T_element H2_adj on the scalar block
     for (int l = 0; l <= model_.hidden_l_max; ++l) {
         const RowMap rows{static_cast<long>(NH) * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
@@ -468,16 +527,25 @@ void Evaluator::run_pipeline()
         launch_gemm(H2_adj_.ptr, flat_rows, h2_skip_.ptr + static_cast<std::size_t>(active_types_[a]) * C * C, C, true, M0_adj_.ptr,
                     scalar_rows, begin, count, C, C, true, nullptr);
     }
+    span_end();
+    span_begin("m0_reverse");
     if (model_.shape_id == 0)
         m0_reverse_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A0_.ptr, element_.ptr, m0_weights_.ptr, M0_adj_.ptr, A0_adj_.ptr);
     else
         m0_reverse_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A0_.ptr, element_.ptr, m0_weights_.ptr, M0_adj_.ptr, A0_adj_.ptr);
+    launches_ += 1;
+    span_end();
+    span_begin("l0_reverse");
     fo.accumulate_edge = 1;
     l0_reverse_kernel<<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
+    launches_ += 1;
+    span_end();
+    span_begin("finalize");
     finalize_kernel<<<1, 32, 0, stream_>>>(energy_slots_.ptr, virial_slots_.ptr, totals_.ptr);
     unpermute_doubles_kernel<<<blocks_for(N, 256), 256, 0, stream_>>>(N, 3, original_.ptr, forces_.ptr, forces_out_.ptr);
     unpermute_doubles_kernel<<<blocks_for(N, 256), 256, 0, stream_>>>(N, 1, original_.ptr, node_energies_.ptr, node_energies_out_.ptr);
-    launches_ += 5;
+    launches_ += 3;
+    span_end();
     SXB_CUDA(cudaGetLastError());
 }
 
@@ -489,6 +557,12 @@ void Evaluator::finish_compute()
     SXB_CUDA(cudaMemcpyAsync(host_totals_, totals_.ptr, 10 * sizeof(double), cudaMemcpyDeviceToHost, stream_));
     SXB_CUDA(cudaStreamSynchronize(stream_));
     SXB_CUDA(cudaEventElapsedTime(&last_ms_, event_begin_, event_end_));
+    profile_.clear();
+    for (const auto& span : spans_) {
+        float ms = 0.0f;
+        SXB_CUDA(cudaEventElapsedTime(&ms, span.begin, span.end));
+        profile_.push_back({span.name, ms, span.launches});
+    }
     if (flag != 0) throw std::invalid_argument("Edge geometry contains a zero-length or non-finite edge vector.");
     have_results_ = true;
 }

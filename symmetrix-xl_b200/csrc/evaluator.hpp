@@ -51,6 +51,11 @@ public:
     const double* device_forces() const { return forces_out_.ptr; }
     const double* device_virial() const { return totals_.ptr + 1; }
     long launches() const { return launches_; }
+    // Per-kernel device times of the last compute (CUDA events on the evaluator's stream), only
+    // collected while profiling is switched on.
+    void set_profiling(bool enabled) { profiling_ = enabled; }
+    struct ProfileEntry { std::string name; float ms; int launches; };
+    const std::vector<ProfileEntry>& profile() const { return profile_; }
     float last_ms() const { return last_ms_; }
     void require_results() const;
 
@@ -97,6 +102,16 @@ private:
     bool have_results_ = false;
     long launches_ = 0;
     float last_ms_ = 0.0f;
+    bool profiling_ = false;
+    struct Span { std::string name; cudaEvent_t begin, end; int launches; };
+    std::vector<Span> spans_;
+    std::vector<cudaEvent_t> event_pool_;
+    std::size_t events_used_ = 0;
+    std::vector<ProfileEntry> profile_;
+    cudaEvent_t pooled_event();
+    void span_begin(const char* name);
+    void span_end();
+    long span_launch_mark_ = 0;
 };
 
 }  // namespace sxb

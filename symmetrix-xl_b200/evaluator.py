@@ -58,6 +58,9 @@ SIGNATURES = {
     "sxb_get_stage": (ctypes.c_int, [_P, ctypes.c_char_p, _P, ctypes.c_int64, ctypes.POINTER(ctypes.c_int64)]),
     "sxb_launch_count": (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_int64)]),
     "sxb_last_compute_ms": (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_float)]),
+    "sxb_set_profiling": (ctypes.c_int, [_P, ctypes.c_int32]),
+    "sxb_profile_entry": (ctypes.c_int, [_P, ctypes.c_int32, ctypes.c_char_p, ctypes.c_int32, ctypes.POINTER(ctypes.c_float),
+                                         ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]),
 }
 
 
@@ -242,6 +245,21 @@ class MACEB200:
 
     def synchronize(self):
         _check(self._lib.sxb_synchronize(self._h))
+
+    def set_profiling(self, enabled: bool):
+        _check(self._lib.sxb_set_profiling(self._h, int(bool(enabled))))
+
+    def profile(self):
+        """[(stage name, device ms, kernel launches)] of the last evaluation (profiling must be on)."""
+        count = ctypes.c_int32()
+        _check(self._lib.sxb_profile_entry(self._h, -1, None, 0, None, None, ctypes.byref(count)))
+        out = []
+        for i in range(count.value):
+            name = ctypes.create_string_buffer(64)
+            ms, launches = ctypes.c_float(), ctypes.c_int32()
+            _check(self._lib.sxb_profile_entry(self._h, i, name, 64, ctypes.byref(ms), ctypes.byref(launches), None))
+            out.append((name.value.decode(), ms.value, launches.value))
+        return out
 
     @property
     def launch_count(self):
