@@ -1,0 +1,114 @@
+"""Generates the golden fixtures of tests/golden/ from the reference's own code.
+
+Run in a container that holds the reference checkout (default /root/reference):
+
+    python tests/golden/make_golden.py
+
+1. reference_evaluator_<arch>.npz -- energies, directed edge forces and stage-tensor checksums of
+   the reference's serial evaluator MACECPU<double> (built into oracle/_ref from the checkout's
+   sources) on a small seeded SrTiO3 cell with a seeded synthetic model of each architecture.
+2. harmonics_reference.npz -- Y_lm and their Cartesian gradients from the reference's first-party
+   closed forms for l <= 3: the C text its generator emits for the device force kernels
+   (symmetrix/source/symmetrix/jit_codegen.py, _render_direct_harmonic_gradient_helper, and the
+   value table in the same file) is rendered, compiled with g++ and evaluated on seeded directions.
+3. structure_reference.json -- path list, sparse coupling (row, lme, |coefficient|) and monomial tables
+   read from the reference's execution-contract fixtures, to pin the first-principles derivation in
+   symmetrix-xl_b200/structure.py.
+The fixtures are outputs (numbers), not reference source.
+"""
+from __future__ import annotations
+
+import ctypes
+import importlib
+import json
+import subprocess
+import sys
+import tempfile
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+REFERENCE = Path("/root/reference")
+OUT = Path(__file__).resolve().parent
+
+import __graft_entry__ as graft  # noqa: E402
+
+
+def evaluator_goldens():
+    from oracle import neighbor, ref
+
+    pkg = graft.load_package()
+    for arch, cells, cutoff in (("small", 2, 5.0), ("medium", 2, 6.0)):
+        with tempfile.TemporaryDirectory() as tmp:
+            path = Path(tmp) / "model.json"
+            pkg.modelgen.write_model(path, arch, seed=101)
+            pos, cell, types = pkg.modelgen.srtio3(cells, 0.05, 202)
+            first, src, shifts = neighbor.build_neighbor_graph(pos, cell, cutoff)
+            xyz = neighbor.edge_vectors(pos, cell, first, src, shifts)
+            m = ref.ReferenceMACE(str(path), double=True)
+            m.compute(types, np.diff(first), src, xyz)
+            data = {"positions": pos, "cell": cell, "types": types, "first": first, "sources": src, "shifts": shifts,
+                    "node_energies": m.get("node_energies"), "edge_forces": m.get("node_forces")}
+            for name in ("A0", "M0", "H1", "Phi1", "A1", "M1", "H2", "H1_adj", "A0_adj"):
+                v = m.get(name)
+                data["sum_" + name] = np.array([v.sum(), np.abs(v).sum(), (v * v).sum()])
+            np.savez_compressed(OUT / f"reference_evaluator_{arch}.npz", **data)
+            print("wrote", arch, len(pos), "atoms", len(src), "edges")
+
+
+def harmonics_goldens():
+    sys.path.insert(0, str(REFERENCE / "symmetrix" / "source"))
+    codegen = importlib.import_module("symmetrix.jit_codegen")
+    helper = codegen._render_direct_harmonic_gradient_helper("static", 16)
+    source = f"""
+#include <cmath>
+#include <cstddef>
+#include <cstdint>
+using Scalar = double;
+{helper}
+extern "C" void golden_gradients(const double* xyz, double radius, double* out) {{
+    direct_harmonic_gradients(xyz, sizeof(double), 0u, 0, radius, out);
+}}
+"""
+    rng = np.random.default_rng(77)
+    vectors = rng.normal(size=(40, 3)) * rng.uniform(0.8, 5.5, size=(40, 1))
+    with tempfile.TemporaryDirectory() as tmp:
+        src = Path(tmp) / "h.cpp"
+        lib = Path(tmp) / "h.so"
+        src.write_text(source)
+        subprocess.run(["g++", "-O2", "-shared", "-fPIC", "-o", str(lib), str(src)], check=True)
+        dll = ctypes.CDLL(str(lib))
+        grads = np.zeros((len(vectors), 3, 16))
+        for i, v in enumerate(vectors):
+            v = np.ascontiguousarray(v)
+            out = np.zeros(48)
+            dll.golden_gradients(v.ctypes.data_as(ctypes.c_void_p), ctypes.c_double(float(np.linalg.norm(v))),
+                                 out.ctypes.data_as(ctypes.c_void_p))
+            grads[i] = out.reshape(3, 16)
+    np.savez_compressed(OUT / "harmonics_reference.npz", vectors=vectors, gradients=grads)
+    print("wrote harmonics goldens")
+
+
+def structure_goldens():
+    base = REFERENCE / "symmetrix" / "test" / "data" / "execution_contracts"
+    out = {}
+    for key, name in (("S0", "jit_r1_mace_omat0_small_contract.json"), ("S1", "jit_r1_mace_mpa0_medium_contract.json"),
+                      ("S2", "jit_r1_mace_mp0b2_large_contract.json")):
+        c = json.loads((base / name).read_text())
+        terms = c["sparse_coupling"]["terms"]
+        out[key] = {"paths": [[p["output_l"], p["edge_l"], p["source_l"]] for p in c["paths"]],
+                    "rows": [t["row"] for t in terms], "lme": [t["lme"] for t in terms],
+                    "abs_cg": [round(abs(t["coefficient"]), 12) for t in terms]}
+    m0 = json.loads((base / "standard_m0_contract.json").read_text())
+    out["M0_medium"] = {str(g["output_component"]): g["terms"] for g in m0["monomial_groups"]}
+    (OUT / "structure_reference.json").write_text(json.dumps(out, separators=(",", ":")))
+    print("wrote structure goldens")
+
+
+if __name__ == "__main__":
+    graft.build()
+    evaluator_goldens()
+    harmonics_goldens()
+    structure_goldens()
