@@ -153,22 +153,20 @@ __global__ void geometry_from_vectors_kernel(long num_edges, const double* __res
 }
 
 // ---------------------------------------------------------------------------------------------
-// Shared-memory edge state of one chunk.
+// Shared-memory edge state of one chunk; every row is 16-byte aligned so that a thread reads
+// it with 128-bit shared loads (all threads read the same address: a broadcast).
 template <bool kGradient>
-struct ChunkState {
-    float y[kEdgeChunk][16];
-    float gx[kGradient ? kEdgeChunk : 1][16];
-    float gy[kGradient ? kEdgeChunk : 1][16];
-    float gz[kGradient ? kEdgeChunk : 1][16];
-    float x[kEdgeChunk];          // offset inside the spline interval
-    float dir[kGradient ? kEdgeChunk : 1][3];
+struct alignas(16) ChunkState {
+    float4 y[kEdgeChunk][4];
+    float4 gx[kGradient ? kEdgeChunk : 1][4];
+    float4 gy[kGradient ? kEdgeChunk : 1][4];
+    float4 gz[kGradient ? kEdgeChunk : 1][4];
+    float4 misc[kEdgeChunk];      // x = offset inside the spline interval, yzw = unit direction
+    int2 index[kEdgeChunk];       // x = first coefficient of (pair, interval) or -1 (inactive), y = source
     float len[kGradient ? kEdgeChunk : 1];
-    int base[kEdgeChunk];         // first coefficient of (pair, interval), or -1 for an inactive edge
-    int source[kEdgeChunk];
 };
 
 // Fills the chunk state for edges [begin, begin+count) of one receiver.
-// ``pair_stride`` = intervals*4*functions; pair index chosen by ``kOrderedPairs``.
 template <bool kGradient, bool kOrderedPairs>
 __device__ __forceinline__ void fill_chunk(ChunkState<kGradient>& s, int begin, int count, const int* __restrict__ sources,
                                            const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype,
@@ -178,51 +176,59 @@ __device__ __forceinline__ void fill_chunk(ChunkState<kGradient>& s, int begin, 
         const int e = begin + t;
         const EdgeGeom g = geom[e];
         const int j = sources[e];
-        s.source[t] = j;
         if (!(g.r < grid.r_cut)) {
-            s.base[t] = -1;
+            s.index[t] = make_int2(-1, j);
             continue;
         }
         int interval;
         float x;
         spline_point(grid, g.r, interval, x);
-        const int type_j = atype[j];
-        int pair;
-        if constexpr (kOrderedPairs) {
-            pair = type_i * num_active + type_j;
-        } else {
-            pair = 0;   // layer-1 tables do not depend on the species pair without a distance transform
-        }
-        s.base[t] = (pair * grid.intervals + interval) * 4 * functions;
-        s.x[t] = x;
+        int pair = 0;   // layer-1 tables do not depend on the species pair without a distance transform
+        if constexpr (kOrderedPairs) pair = type_i * num_active + atype[j];
+        s.index[t] = make_int2((pair * grid.intervals + interval) * 4 * functions, j);
+        s.misc[t] = make_float4(x, g.ux, g.uy, g.uz);
         const float inv_r = 1.0f / g.r;
         if constexpr (kGradient) {
-            harmonics16<true>(g.ux, g.uy, g.uz, inv_r, s.y[t], s.gx[t], s.gy[t], s.gz[t]);
-            s.dir[t][0] = g.ux; s.dir[t][1] = g.uy; s.dir[t][2] = g.uz;
+            harmonics16<true>(g.ux, g.uy, g.uz, inv_r, reinterpret_cast<float*>(s.y[t]), reinterpret_cast<float*>(s.gx[t]),
+                              reinterpret_cast<float*>(s.gy[t]), reinterpret_cast<float*>(s.gz[t]));
             s.len[t] = g.r;
         } else {
-            harmonics16<false>(g.ux, g.uy, g.uz, inv_r, s.y[t], nullptr, nullptr, nullptr);
+            harmonics16<false>(g.ux, g.uy, g.uz, inv_r, reinterpret_cast<float*>(s.y[t]), nullptr, nullptr, nullptr);
         }
     }
 }
 
+__device__ __forceinline__ void load16(const float4* __restrict__ row, float* __restrict__ out)
+{
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float4 v = row[q];
+        out[4 * q] = v.x; out[4 * q + 1] = v.y; out[4 * q + 2] = v.z; out[4 * q + 3] = v.w;
+    }
+}
+
+// value c0 + c1 x + c2 x^2 + c3 x^3 and derivative c1 + 2 c2 x + 3 c3 x^2 with shared powers
+// (x2 = 2x and xx3 = 3x^2 are formed once per edge)
 __device__ __forceinline__ float cubic(float c0, float c1, float c2, float c3, float x, float xx, float xxx)
 {
     return fmaf(c3, xxx, fmaf(c2, xx, fmaf(c1, x, c0)));
 }
-__device__ __forceinline__ float cubic_derivative(float c1, float c2, float c3, float x, float xx)
+__device__ __forceinline__ float cubic_derivative(float c1, float c2, float c3, float x2, float xx3)
 {
-    return fmaf(3.0f * c3, xx, fmaf(2.0f * c2, x, c1));
+    return fmaf(c3, xx3, fmaf(c2, x2, c1));
 }
 
 // ---------------------------------------------------------------------------------------------
 // Layer 0 forward: A0_i[lm,k] = sum_j S0[pair(i,j), r_ij][l,k] * Y_ij[lm].
-__global__ void __launch_bounds__(256)
-l0_forward_kernel(int num_nodes, int C, const int* __restrict__ first, const int* __restrict__ sources,
+// kC > 0 fixes the channel count at compile time (all strides become immediates).
+template <int kC>
+__global__ void __launch_bounds__(kC > 0 ? kC : 256)
+l0_forward_kernel(int num_nodes, int C_runtime, const int* __restrict__ first, const int* __restrict__ sources,
                   const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype, int num_active,
                   SplineGrid grid, const float* __restrict__ table, float* __restrict__ A0)
 {
     __shared__ ChunkState<false> s;
+    const int C = kC > 0 ? kC : C_runtime;
     const int i = blockIdx.x;
     const int k = threadIdx.x;
     const int F = 4 * C;
@@ -237,15 +243,16 @@ l0_forward_kernel(int num_nodes, int C, const int* __restrict__ first, const int
         fill_chunk<false, true>(s, chunk, count, sources, geom, atype, type_i, num_active, grid, F);
         __syncthreads();
         for (int t = 0; t < count; ++t) {
-            const int base = s.base[t];
+            const int base = s.index[t].x;
             if (base < 0) continue;
-            const float x = s.x[t], xx = x * x, xxx = xx * x;
+            const float x = s.misc[t].x, xx = x * x, xxx = xx * x;
             const float* c = table + base + k;
             float R[4];
 #pragma unroll
             for (int l = 0; l < 4; ++l)
                 R[l] = cubic(c[l * C], c[F + l * C], c[2 * F + l * C], c[3 * F + l * C], x, xx, xxx);
-            const float* y = s.y[t];
+            float y[16];
+            load16(s.y[t], y);
             acc[0] = fmaf(R[0], y[0], acc[0]);
 #pragma unroll
             for (int lm = 1; lm < 4; ++lm) acc[lm] = fmaf(R[1], y[lm], acc[lm]);
@@ -295,7 +302,7 @@ __device__ __forceinline__ void flush_chunk_forces(ForceScratch<kMaxWarps>& fs, 
     double fx = 0.0, fy = 0.0, fz = 0.0;
     double v[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
     for (int t = threadIdx.x; t < count; t += blockDim.x) {
-        if (s.base[t] < 0) {
+        if (s.index[t].x < 0) {
             if (out.edge_forces != nullptr && !out.accumulate_edge) {
                 double* ef = out.edge_forces + 3 * static_cast<size_t>(chunk_begin + t);
                 ef[0] = ef[1] = ef[2] = 0.0;
@@ -310,13 +317,14 @@ __device__ __forceinline__ void flush_chunk_forces(ForceScratch<kMaxWarps>& fs, 
         }
         // directed force dE/d(xyz_ij) with the reference's sign: force -= adjoint * (...)
         const double ex = -static_cast<double>(px), ey = -static_cast<double>(py), ez = -static_cast<double>(pz);
-        const int j = s.source[t];
+        const int j = s.index[t].y;
         atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j), ex);
         atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 1, ey);
         atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 2, ez);
         fx -= ex; fy -= ey; fz -= ez;
         const double len = s.len[t];
-        const double rx = len * s.dir[t][0], ry = len * s.dir[t][1], rz = len * s.dir[t][2];
+        const float4 m = s.misc[t];
+        const double rx = len * m.y, ry = len * m.z, rz = len * m.w;
         v[0] += ex * rx; v[1] += ex * ry; v[2] += ex * rz;
         v[3] += ey * rx; v[4] += ey * ry; v[5] += ey * rz;
         v[6] += ez * rx; v[7] += ez * ry; v[8] += ez * rz;
@@ -359,13 +367,15 @@ __device__ __forceinline__ void finish_receiver_forces(ForceScratch<kMaxWarps>& 
 
 // ---------------------------------------------------------------------------------------------
 // Layer 0 reverse: f_ij -= sum_{lm,k} A0_adj_i[lm,k] * (rhat S0' Y + S0 grad Y).
-__global__ void __launch_bounds__(256)
-l0_reverse_kernel(int num_nodes, int C, const int* __restrict__ first, const int* __restrict__ sources,
+template <int kC>
+__global__ void __launch_bounds__(kC > 0 ? kC : 256)
+l0_reverse_kernel(int num_nodes, int C_runtime, const int* __restrict__ first, const int* __restrict__ sources,
                   const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype, int num_active,
                   SplineGrid grid, const float* __restrict__ table, const float* __restrict__ A0_adj, ForceOutputs out)
 {
     __shared__ ChunkState<true> s;
     __shared__ ForceScratch<8> fs;
+    const int C = kC > 0 ? kC : C_runtime;
     const int i = blockIdx.x;
     const int k = threadIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, num_warps = blockDim.x >> 5;
@@ -384,34 +394,40 @@ l0_reverse_kernel(int num_nodes, int C, const int* __restrict__ first, const int
         fill_chunk<true, true>(s, chunk, count, sources, geom, atype, type_i, num_active, grid, F);
         __syncthreads();
         for (int t = 0; t < count; ++t) {
-            const int base = s.base[t];
+            const int base = s.index[t].x;
             if (base < 0) continue;
-            const float x = s.x[t], xx = x * x, xxx = xx * x;
+            const float4 m = s.misc[t];
+            const float x = m.x, xx = x * x, xxx = xx * x, x2 = 2.0f * x, xx3 = 3.0f * xx;
             const float* c = table + base + k;
-            const float* y = s.y[t];
-            const float* gx = s.gx[t];
-            const float* gy = s.gy[t];
-            const float* gz = s.gz[t];
-            float radial = 0.0f, fx = 0.0f, fy = 0.0f, fz = 0.0f;
+            float y[16], ang[16];
+            load16(s.y[t], y);
+            float radial = 0.0f;
 #pragma unroll
             for (int l = 0; l < 4; ++l) {
                 const float c0 = c[l * C], c1 = c[F + l * C], c2 = c[2 * F + l * C], c3 = c[3 * F + l * C];
                 const float R = cubic(c0, c1, c2, c3, x, xx, xxx);
-                const float dR = cubic_derivative(c1, c2, c3, x, xx);
+                const float dR = cubic_derivative(c1, c2, c3, x2, xx3);
                 float ya = 0.0f;
 #pragma unroll
                 for (int lm = l * l; lm < (l + 1) * (l + 1); ++lm) {
                     ya = fmaf(y[lm], adj[lm], ya);
-                    const float a = R * adj[lm];
-                    fx = fmaf(a, gx[lm], fx);
-                    fy = fmaf(a, gy[lm], fy);
-                    fz = fmaf(a, gz[lm], fz);
+                    ang[lm] = R * adj[lm];
                 }
                 radial = fmaf(dR, ya, radial);
             }
-            fx = fmaf(radial, s.dir[t][0], fx);
-            fy = fmaf(radial, s.dir[t][1], fy);
-            fz = fmaf(radial, s.dir[t][2], fz);
+            float fx = radial * m.y, fy = radial * m.z, fz = radial * m.w;
+            {
+                float g[16];
+                load16(s.gx[t], g);
+#pragma unroll
+                for (int q = 0; q < 16; ++q) fx = fmaf(ang[q], g[q], fx);
+                load16(s.gy[t], g);
+#pragma unroll
+                for (int q = 0; q < 16; ++q) fy = fmaf(ang[q], g[q], fy);
+                load16(s.gz[t], g);
+#pragma unroll
+                for (int q = 0; q < 16; ++q) fz = fmaf(ang[q], g[q], fz);
+            }
             warp_reduce3(fx, fy, fz);
             if (lane == 0) {
                 fs.partial[t][warp][0] = fx;
@@ -429,20 +445,23 @@ l0_reverse_kernel(int num_nodes, int C, const int* __restrict__ first, const int
 // Layer 1 kernels, one instantiation per compiled coupling structure.
 //   forward:  Phi1_i[lme,k] = sum_terms cg * sum_j R1_ij[path,k] Y_ij[lm1] H1_j[lm2,k]
 //   reverse:  row adjoints from dPhi1_i, then per edge the force and the source adjoint
-//             H1_adj_j[lm2,k] += sum R1 Y adj  (vector red.add into the source row)
+//             H1_adj_j[lm2,k] += sum R1 Y adj  (coalesced red.add into the source row)
 #define SXB_TERM_FORWARD(term, row, lme) out_lme[lme] = fmaf(cgc.cg[term], acc[row], out_lme[lme]);
 #define SXB_TERM_TRANSPOSE(term, row, lme) adj[row] = fmaf(cgc.cg[term], dphi[lme], adj[row]);
 
 #define SXB_DEFINE_L1_KERNELS(NAME)                                                                                  \
-    __global__ void __launch_bounds__(256)                                                                           \
-    l1_forward_kernel_##NAME(int num_nodes, int C, const int* __restrict__ first, const int* __restrict__ sources,   \
-                             const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype,             \
-                             SplineGrid grid, const float* __restrict__ table, const float* __restrict__ H1,         \
+    template <int kC>                                                                                                \
+    __global__ void __launch_bounds__(kC > 0 ? kC : 256)                                                             \
+    l1_forward_kernel_##NAME(int num_nodes, int C_runtime, const int* __restrict__ first,                            \
+                             const int* __restrict__ sources, const EdgeGeom* __restrict__ geom,                     \
+                             const unsigned char* __restrict__ atype, SplineGrid grid,                               \
+                             const float* __restrict__ table, const float* __restrict__ H1,                          \
                              const __grid_constant__ CouplingConstants cgc, float* __restrict__ Phi1)                \
     {                                                                                                                \
         constexpr int NP = SXB_##NAME##_NUM_PATHS, NR = SXB_##NAME##_NUM_ROWS, NH = SXB_##NAME##_NUM_HIDDEN;          \
         constexpr int NE = SXB_##NAME##_NUM_LME;                                                                     \
         __shared__ ChunkState<false> s;                                                                              \
+        const int C = kC > 0 ? kC : C_runtime;                                                                       \
         const int i = blockIdx.x;                                                                                    \
         const int k = threadIdx.x;                                                                                   \
         const int F = NP * C;                                                                                        \
@@ -455,18 +474,18 @@ l0_reverse_kernel(int num_nodes, int C, const int* __restrict__ first, const int
             fill_chunk<false, false>(s, chunk, count, sources, geom, atype, 0, 1, grid, F);                          \
             __syncthreads();                                                                                         \
             for (int t = 0; t < count; ++t) {                                                                        \
-                const int base = s.base[t];                                                                          \
-                if (base < 0) continue;                                                                              \
-                const float x = s.x[t], xx = x * x, xxx = xx * x;                                                    \
-                const float* c = table + base + k;                                                                   \
+                const int2 id = s.index[t];                                                                          \
+                if (id.x < 0) continue;                                                                              \
+                const float x = s.misc[t].x, xx = x * x, xxx = xx * x;                                               \
+                const float* c = table + id.x + k;                                                                   \
                 float R[NP];                                                                                         \
                 _Pragma("unroll") for (int p = 0; p < NP; ++p)                                                       \
                     R[p] = cubic(c[p * C], c[F + p * C], c[2 * F + p * C], c[3 * F + p * C], x, xx, xxx);            \
-                const float* hsrc = H1 + static_cast<size_t>(s.source[t]) * NH * C + k;                              \
+                const float* hsrc = H1 + static_cast<size_t>(id.y) * NH * C + k;                                     \
                 float h[NH];                                                                                         \
                 _Pragma("unroll") for (int q = 0; q < NH; ++q) h[q] = hsrc[q * C];                                   \
                 float y[16];                                                                                         \
-                _Pragma("unroll") for (int q = 0; q < 16; ++q) y[q] = s.y[t][q];                                     \
+                load16(s.y[t], y);                                                                                   \
                 SXB_##NAME##_L1_FORWARD_BODY                                                                         \
             }                                                                                                        \
         }                                                                                                            \
@@ -477,10 +496,12 @@ l0_reverse_kernel(int num_nodes, int C, const int* __restrict__ first, const int
         _Pragma("unroll") for (int q = 0; q < NE; ++q) out[q * C] = out_lme[q];                                      \
     }                                                                                                                \
                                                                                                                      \
-    __global__ void __launch_bounds__(256)                                                                           \
-    l1_reverse_kernel_##NAME(int num_nodes, int C, const int* __restrict__ first, const int* __restrict__ sources,   \
-                             const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype,             \
-                             SplineGrid grid, const float* __restrict__ table, const float* __restrict__ H1,         \
+    template <int kC>                                                                                                \
+    __global__ void __launch_bounds__(kC > 0 ? kC : 256)                                                             \
+    l1_reverse_kernel_##NAME(int num_nodes, int C_runtime, const int* __restrict__ first,                            \
+                             const int* __restrict__ sources, const EdgeGeom* __restrict__ geom,                     \
+                             const unsigned char* __restrict__ atype, SplineGrid grid,                               \
+                             const float* __restrict__ table, const float* __restrict__ H1,                          \
                              const float* __restrict__ dPhi1, const __grid_constant__ CouplingConstants cgc,         \
                              float* __restrict__ H1_adj, ForceOutputs out)                                           \
     {                                                                                                                \
@@ -488,6 +509,7 @@ l0_reverse_kernel(int num_nodes, int C, const int* __restrict__ first, const int
         constexpr int NE = SXB_##NAME##_NUM_LME;                                                                     \
         __shared__ ChunkState<true> s;                                                                               \
         __shared__ ForceScratch<8> fs;                                                                               \
+        const int C = kC > 0 ? kC : C_runtime;                                                                       \
         const int i = blockIdx.x;                                                                                    \
         const int k = threadIdx.x;                                                                                   \
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, num_warps = blockDim.x >> 5;                     \
@@ -509,29 +531,35 @@ l0_reverse_kernel(int num_nodes, int C, const int* __restrict__ first, const int
             fill_chunk<true, false>(s, chunk, count, sources, geom, atype, 0, 1, grid, F);                           \
             __syncthreads();                                                                                         \
             for (int t = 0; t < count; ++t) {                                                                        \
-                const int base = s.base[t];                                                                          \
-                if (base < 0) continue;                                                                              \
-                const float x = s.x[t], xx = x * x, xxx = xx * x;                                                    \
-                const float* c = table + base + k;                                                                   \
+                const int2 id = s.index[t];                                                                          \
+                if (id.x < 0) continue;                                                                              \
+                const float4 m = s.misc[t];                                                                          \
+                const float x = m.x, xx = x * x, xxx = xx * x, x2 = 2.0f * x, xx3 = 3.0f * xx;                       \
+                const float* c = table + id.x + k;                                                                   \
                 float R[NP], dR[NP];                                                                                 \
                 _Pragma("unroll") for (int p = 0; p < NP; ++p) {                                                     \
                     const float c0 = c[p * C], c1 = c[F + p * C], c2 = c[2 * F + p * C], c3 = c[3 * F + p * C];      \
                     R[p] = cubic(c0, c1, c2, c3, x, xx, xxx);                                                        \
-                    dR[p] = cubic_derivative(c1, c2, c3, x, xx);                                                     \
+                    dR[p] = cubic_derivative(c1, c2, c3, x2, xx3);                                                   \
                 }                                                                                                    \
-                const size_t source_row = static_cast<size_t>(s.source[t]) * NH * C + k;                             \
+                const size_t source_row = static_cast<size_t>(id.y) * NH * C + k;                                    \
                 float h[NH], hadj[NH];                                                                               \
                 _Pragma("unroll") for (int q = 0; q < NH; ++q) { h[q] = H1[source_row + q * C]; hadj[q] = 0.0f; }    \
                 float y[16], ang[16];                                                                                \
-                _Pragma("unroll") for (int q = 0; q < 16; ++q) { y[q] = s.y[t][q]; ang[q] = 0.0f; }                  \
+                load16(s.y[t], y);                                                                                   \
+                _Pragma("unroll") for (int q = 0; q < 16; ++q) ang[q] = 0.0f;                                        \
                 float radial = 0.0f;                                                                                 \
                 SXB_##NAME##_L1_REVERSE_BODY                                                                         \
                 _Pragma("unroll") for (int q = 0; q < NH; ++q) atomicAdd(H1_adj + source_row + q * C, hadj[q]);      \
-                float fx = radial * s.dir[t][0], fy = radial * s.dir[t][1], fz = radial * s.dir[t][2];               \
-                _Pragma("unroll") for (int q = 0; q < 16; ++q) {                                                     \
-                    fx = fmaf(ang[q], s.gx[t][q], fx);                                                               \
-                    fy = fmaf(ang[q], s.gy[t][q], fy);                                                               \
-                    fz = fmaf(ang[q], s.gz[t][q], fz);                                                               \
+                float fx = radial * m.y, fy = radial * m.z, fz = radial * m.w;                                       \
+                {                                                                                                    \
+                    float g[16];                                                                                     \
+                    load16(s.gx[t], g);                                                                              \
+                    _Pragma("unroll") for (int q = 0; q < 16; ++q) fx = fmaf(ang[q], g[q], fx);                      \
+                    load16(s.gy[t], g);                                                                              \
+                    _Pragma("unroll") for (int q = 0; q < 16; ++q) fy = fmaf(ang[q], g[q], fy);                      \
+                    load16(s.gz[t], g);                                                                              \
+                    _Pragma("unroll") for (int q = 0; q < 16; ++q) fz = fmaf(ang[q], g[q], fz);                      \
                 }                                                                                                    \
                 warp_reduce3(fx, fy, fz);                                                                            \
                 if (lane == 0) {                                                                                     \

@@ -65,6 +65,14 @@ __global__ void narrow_offsets_kernel(int n, const long long* __restrict__ wide,
 
 inline int blocks_for(long n, int threads) { return static_cast<int>((n + threads - 1) / threads); }
 
+// Launches KERNEL<kC> with the channel count fixed at compile time for the common widths.
+#define SXB_LAUNCH_BY_CHANNELS(KERNEL, C, GRID, STREAM, ...)                         \
+    do {                                                                              \
+        if ((C) == 128) KERNEL<128><<<(GRID), 128, 0, (STREAM)>>>(__VA_ARGS__);       \
+        else if ((C) == 32) KERNEL<32><<<(GRID), 32, 0, (STREAM)>>>(__VA_ARGS__);     \
+        else KERNEL<0><<<(GRID), (C), 0, (STREAM)>>>(__VA_ARGS__);                    \
+    } while (0)
+
 }  // namespace
 
 Evaluator::Evaluator(const std::string& json_path, int device_ordinal) : device_(device_ordinal)
@@ -424,7 +432,8 @@ void Evaluator::run_pipeline()
 
     // layer 0 forward
     span_begin("l0_forward");
-    l0_forward_kernel<<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
+    SXB_LAUNCH_BY_CHANNELS(l0_forward_kernel, C, N, stream_, N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_,
+                           r0_table_.ptr, A0_.ptr);
     launches_ += 1;
     span_end();
     span_begin("m0_forward");
@@ -445,9 +454,11 @@ void Evaluator::run_pipeline()
     // layer 1 forward
     span_begin("l1_forward");
     if (model_.shape_id == 0)
-        l1_forward_kernel_S0<<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, r1_table_.ptr, H1_.ptr, coupling_, Phi1_.ptr);
+        SXB_LAUNCH_BY_CHANNELS(l1_forward_kernel_S0, C, N, stream_, N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
+                               r1_table_.ptr, H1_.ptr, coupling_, Phi1_.ptr);
     else
-        l1_forward_kernel_S1<<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, r1_table_.ptr, H1_.ptr, coupling_, Phi1_.ptr);
+        SXB_LAUNCH_BY_CHANNELS(l1_forward_kernel_S1, C, N, stream_, N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
+                               r1_table_.ptr, H1_.ptr, coupling_, Phi1_.ptr);
     launches_ += 1;
     span_end();
     // A1_il = Phi1_il W_l
@@ -510,9 +521,11 @@ void Evaluator::run_pipeline()
     fo.edge_forces = keep_edge_forces_ ? edge_forces_.ptr : nullptr;
     fo.accumulate_edge = 0;
     if (model_.shape_id == 0)
-        l1_reverse_kernel_S0<<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, r1_table_.ptr, H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
+        SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S0, C, N, stream_, N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
+                               r1_table_.ptr, H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
     else
-        l1_reverse_kernel_S1<<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, r1_table_.ptr, H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
+        SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S1, C, N, stream_, N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
+                               r1_table_.ptr, H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
     launches_ += 1;
     span_end();
     span_begin("gemm_h1_reverse");
@@ -537,7 +550,8 @@ void Evaluator::run_pipeline()
     span_end();
     span_begin("l0_reverse");
     fo.accumulate_edge = 1;
-    l0_reverse_kernel<<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
+    SXB_LAUNCH_BY_CHANNELS(l0_reverse_kernel, C, N, stream_, N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_,
+                           r0_table_.ptr, A0_adj_.ptr, fo);
     launches_ += 1;
     span_end();
     span_begin("finalize");
