@@ -34,6 +34,11 @@ struct DeviceBuffer {
     DeviceBuffer() = default;
     DeviceBuffer(const DeviceBuffer&) = delete;
     DeviceBuffer& operator=(const DeviceBuffer&) = delete;
+    DeviceBuffer(DeviceBuffer&& other) noexcept : ptr(other.ptr), capacity(other.capacity)
+    {
+        other.ptr = nullptr;
+        other.capacity = 0;
+    }
     ~DeviceBuffer() { release(); }
 
     void release()
@@ -69,8 +74,6 @@ struct SplineGrid {
 struct CouplingConstants {
     float cg[256];
 };
-
-struct RowMap;
 
 constexpr int kVirialSlots = 64;   // spread the 9-component virial atomics over this many slots
 

@@ -8,6 +8,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <limits>
 #include <numeric>
@@ -15,6 +16,7 @@
 #include "edge_kernels.cuh"
 #include "graph_kernels.cuh"
 #include "node_kernels.cuh"
+#include "tc_gemm.cuh"
 
 namespace sxb {
 
@@ -106,6 +108,15 @@ Evaluator::Evaluator(const std::string& json_path, int device_ordinal) : device_
     upload(readout2_w1_, model_.readout2_w1, stream_);
     upload(readout2_w2_, model_.readout2_w2, stream_);
     upload(atomic_energies_, model_.atomic_energies, stream_);
+    if (const char* env = std::getenv("SXB_SIMT_LINEARS")) use_tensor_cores_ = !(env[0] == '1');
+    for (int l = 0; l <= model_.hidden_l_max; ++l)
+        upload_split(s_h1_[l], model_.w_h1.data() + static_cast<std::size_t>(l) * C * C, C, C);
+    for (int l = 0; l <= model_.l_max; ++l) upload_split(s_a1_[l], model_.w_a1[l].data(), model_.eta[l] * C, C);
+    s_h2_skip_.resize(model_.num_elements);
+    for (int a = 0; a < model_.num_elements; ++a)
+        upload_split(s_h2_skip_[a], model_.h2_skip.data() + static_cast<std::size_t>(a) * C * C, C, C);
+    upload_split(s_h2_m1_, model_.h2_m1.data(), C, C);
+    SXB_CUDA(cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes));
     std::memset(&coupling_, 0, sizeof(coupling_));
     if (model_.num_terms > 256) throw std::invalid_argument("Too many coupling terms.");
     for (int t = 0; t < model_.num_terms; ++t) coupling_.cg[t] = model_.cg[t];
@@ -419,6 +430,127 @@ void Evaluator::span_end()
     SXB_CUDA(cudaEventRecord(spans_.back().end, stream_));
 }
 
+namespace {
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled_entry()
+{
+    static EncodeTiled fn = [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        SXB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result));
+        if (ptr == nullptr || result != cudaDriverEntryPointSuccess)
+            throw std::runtime_error("cuTensorMapEncodeTiled is not available from the CUDA driver.");
+        return reinterpret_cast<EncodeTiled>(ptr);
+    }();
+    return fn;
+}
+
+// Tensor map of a row-major FP32 matrix [n][k] (k contiguous): box [n_tile rows][32 floats], 128-byte swizzle.
+CUtensorMap make_weight_map(const float* device_ptr, int n, int k, int n_tile)
+{
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(n)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * sizeof(float)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kTcChunk), static_cast<cuuint32_t>(n_tile)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = encode_tiled_entry()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(device_ptr), dims, strides,
+                                             box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed for a weight matrix.");
+    return map;
+}
+}  // namespace
+
+// Splits W [rows][cols] into a TF32-exact high part (low 13 mantissa bits cleared) and the
+// residual, in both orientations the tensor-core kernel needs ([N][K], K contiguous).
+void Evaluator::upload_split(SplitWeight& out, const float* w, int rows, int cols)
+{
+    out.rows = rows;
+    out.cols = cols;
+    const std::size_t n = static_cast<std::size_t>(rows) * cols;
+    std::vector<float> hi(n), lo(n), thi(n), tlo(n);
+    for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < cols; ++c) {
+            const float v = w[static_cast<std::size_t>(r) * cols + c];
+            std::uint32_t bits;
+            std::memcpy(&bits, &v, 4);
+            bits &= 0xffffe000u;
+            float h;
+            std::memcpy(&h, &bits, 4);
+            const float l = v - h;
+            hi[static_cast<std::size_t>(r) * cols + c] = h;      // rev: Bt[n = r][k = c] = W[r][c]
+            lo[static_cast<std::size_t>(r) * cols + c] = l;
+            thi[static_cast<std::size_t>(c) * rows + r] = h;     // fwd: Bt[n = c][k = r] = W[r][c]
+            tlo[static_cast<std::size_t>(c) * rows + r] = l;
+        }
+    upload(out.full, std::vector<float>(w, w + n), stream_);
+    upload(out.rev_hi, hi, stream_);
+    upload(out.rev_lo, lo, stream_);
+    upload(out.fwd_hi, thi, stream_);
+    upload(out.fwd_lo, tlo, stream_);
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+    // forward product: N = cols, K = rows; reverse product: N = rows, K = cols
+    if (rows % kTcChunk != 0 || cols % kTcChunk != 0)
+        throw std::invalid_argument("Linear extents must be multiples of 32 for the tensor-core kernel.");
+    out.map_fwd_hi = make_weight_map(out.fwd_hi.ptr, cols, rows, std::min(cols, kTcNTile));
+    out.map_fwd_lo = make_weight_map(out.fwd_lo.ptr, cols, rows, std::min(cols, kTcNTile));
+    out.map_rev_hi = make_weight_map(out.rev_hi.ptr, rows, cols, std::min(rows, kTcNTile));
+    out.map_rev_lo = make_weight_map(out.rev_lo.ptr, rows, cols, std::min(rows, kTcNTile));
+}
+
+// Runs a group of independent linears as one tensor-core launch (or as FP32 SIMT launches when the
+// tensor-core path is switched off for comparison).
+void Evaluator::launch_tc(const std::vector<TcCall>& calls)
+{
+    if (!use_tensor_cores_) {
+        for (const auto& c : calls) {
+            const int N = c.reverse ? c.w->rows : c.w->cols, K = c.reverse ? c.w->cols : c.w->rows;
+            launch_gemm(c.A, c.a_rows, c.w->full.ptr, c.w->cols, c.reverse, c.C, c.c_rows, c.first_node, c.num_nodes, N, K,
+                        c.accumulate, c.bias);
+        }
+        return;
+    }
+    std::size_t begin = 0;
+    while (begin < calls.size()) {
+        TcBatch batch;
+        std::memset(static_cast<void*>(&batch), 0, sizeof(batch));
+        int tiles = 0, count = 0;
+        for (; begin < calls.size() && count < kTcMaxProblems; ++begin) {
+            const auto& c = calls[begin];
+            if (c.num_nodes <= 0) continue;
+            TcProblem& p = batch.problem[count];
+            p.A = c.A;
+            p.map_hi = c.reverse ? c.w->map_rev_hi : c.w->map_fwd_hi;
+            p.map_lo = c.reverse ? c.w->map_rev_lo : c.w->map_fwd_lo;
+            p.C = c.C;
+            p.bias = c.bias;
+            p.a_rows = c.a_rows;
+            p.c_rows = c.c_rows;
+            p.first_node = c.first_node;
+            p.M = c.num_nodes * c.a_rows.components;
+            p.N = c.reverse ? c.w->rows : c.w->cols;
+            p.K = c.reverse ? c.w->cols : c.w->rows;
+            p.accumulate = c.accumulate ? 1 : 0;
+            p.n_tile = std::min(p.N, kTcNTile);
+            if (p.K % kTcChunk != 0 || p.N % p.n_tile != 0 || p.n_tile % 32 != 0)
+                throw std::invalid_argument("Linear extents are not supported by the tensor-core kernel.");
+            p.m_tiles = (p.M + kTcRows - 1) / kTcRows;
+            p.n_tiles = p.N / p.n_tile;
+            p.tile_begin = tiles;
+            tiles += p.m_tiles * p.n_tiles;
+            ++count;
+        }
+        if (count == 0) continue;
+        batch.count = count;
+        batch.total_tiles = tiles;
+        tc_gemm_kernel<<<tiles, kTcThreads, kTcSmemBytes, stream_>>>(batch, error_flag_.ptr);
+        launches_ += 1;
+    }
+}
+
 void Evaluator::run_pipeline()
 {
     spans_.clear();
@@ -446,9 +578,13 @@ void Evaluator::run_pipeline()
     span_end();
     // H1_il = M0_il W_l
     span_begin("gemm_h1");
-    for (int l = 0; l <= model_.hidden_l_max; ++l) {
-        const RowMap rows{static_cast<long>(NH) * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
-        launch_gemm(M0_.ptr, rows, w_h1_.ptr + static_cast<std::size_t>(l) * C * C, C, false, H1_.ptr, rows, 0, N, C, C, false, nullptr);
+    {
+        std::vector<TcCall> calls;
+        for (int l = 0; l <= model_.hidden_l_max; ++l) {
+            const RowMap rows{static_cast<long>(NH) * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
+            calls.push_back({M0_.ptr, rows, &s_h1_[l], false, H1_.ptr, rows, 0, N, false, nullptr});
+        }
+        launch_tc(calls);
     }
     span_end();
     // layer 1 forward
@@ -463,11 +599,15 @@ void Evaluator::run_pipeline()
     span_end();
     // A1_il = Phi1_il W_l
     span_begin("gemm_a1");
-    for (int l = 0; l <= model_.l_max; ++l) {
-        const int eta = model_.eta[l];
-        const RowMap a_rows{static_cast<long>(NE) * C, static_cast<long>(eta) * C, static_cast<long>(model_.group_begin[l]) * C, 2 * l + 1};
-        const RowMap c_rows{16L * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
-        launch_gemm(Phi1_.ptr, a_rows, w_a1_[l].ptr, C, false, A1_.ptr, c_rows, 0, N, C, eta * C, false, nullptr);
+    {
+        std::vector<TcCall> calls;
+        for (int l = 0; l <= model_.l_max; ++l) {
+            const int eta = model_.eta[l];
+            const RowMap a_rows{static_cast<long>(NE) * C, static_cast<long>(eta) * C, static_cast<long>(model_.group_begin[l]) * C, 2 * l + 1};
+            const RowMap c_rows{16L * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
+            calls.push_back({Phi1_.ptr, a_rows, &s_a1_[l], false, A1_.ptr, c_rows, 0, N, false, nullptr});
+        }
+        launch_tc(calls);
     }
     span_end();
     span_begin("m1_forward");
@@ -481,12 +621,15 @@ void Evaluator::run_pipeline()
     span_begin("gemm_h2");
     const RowMap scalar_rows{static_cast<long>(NH) * C, C, 0, 1};
     const RowMap flat_rows{static_cast<long>(C), C, 0, 1};
-    for (int a = 0; a < n_active; ++a) {
-        const int begin = type_begin_[a], count = type_begin_[a + 1] - begin;
-        launch_gemm(M0_.ptr, scalar_rows, h2_skip_.ptr + static_cast<std::size_t>(active_types_[a]) * C * C, C, false, H2_.ptr,
-                    flat_rows, begin, count, C, C, false, nullptr);
+    {
+        std::vector<TcCall> calls;
+        for (int a = 0; a < n_active; ++a) {
+            const int begin = type_begin_[a], count = type_begin_[a + 1] - begin;
+            calls.push_back({M0_.ptr, scalar_rows, &s_h2_skip_[active_types_[a]], false, H2_.ptr, flat_rows, begin, count, false, nullptr});
+        }
+        launch_tc(calls);
+        launch_tc({{M1_.ptr, flat_rows, &s_h2_m1_, false, H2_.ptr, flat_rows, 0, N, true, nullptr}});
     }
-    launch_gemm(M1_.ptr, flat_rows, h2_m1_.ptr, C, false, H2_.ptr, flat_rows, 0, N, C, C, true, nullptr);
     span_end();
     span_begin("readout");
     readout_kernel<<<blocks_for(static_cast<long>(N) * 32, 256), 256, 0, stream_>>>(
@@ -497,7 +640,7 @@ void Evaluator::run_pipeline()
 
     // reverse
     span_begin("gemm_h2_reverse");
-    launch_gemm(H2_adj_.ptr, flat_rows, h2_m1_.ptr, C, true, M1_adj_.ptr, flat_rows, 0, N, C, C, false, nullptr);
+    launch_tc({{H2_adj_.ptr, flat_rows, &s_h2_m1_, true, M1_adj_.ptr, flat_rows, 0, N, false, nullptr}});
     span_end();
     span_begin("m1_reverse");
     if (model_.shape_id == 0)
@@ -507,11 +650,15 @@ void Evaluator::run_pipeline()
     launches_ += 1;
     span_end();
     span_begin("gemm_a1_reverse");
-    for (int l = 0; l <= model_.l_max; ++l) {
-        const int eta = model_.eta[l];
-        const RowMap a_rows{16L * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
-        const RowMap c_rows{static_cast<long>(NE) * C, static_cast<long>(eta) * C, static_cast<long>(model_.group_begin[l]) * C, 2 * l + 1};
-        launch_gemm(A1_adj_.ptr, a_rows, w_a1_[l].ptr, C, true, dPhi1_.ptr, c_rows, 0, N, eta * C, C, false, nullptr);
+    {
+        std::vector<TcCall> calls;
+        for (int l = 0; l <= model_.l_max; ++l) {
+            const int eta = model_.eta[l];
+            const RowMap a_rows{16L * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
+            const RowMap c_rows{static_cast<long>(NE) * C, static_cast<long>(eta) * C, static_cast<long>(model_.group_begin[l]) * C, 2 * l + 1};
+            calls.push_back({A1_adj_.ptr, a_rows, &s_a1_[l], true, dPhi1_.ptr, c_rows, 0, N, false, nullptr});
+        }
+        launch_tc(calls);
     }
     span_end();
     span_begin("l1_reverse");
@@ -530,15 +677,19 @@ void Evaluator::run_pipeline()
     span_end();
     span_begin("gemm_h1_reverse");
     // M0_adj_il = H1_adj_il W_l^T, then the direct adjoint q + T_element H2_adj on the scalar block
-    for (int l = 0; l <= model_.hidden_l_max; ++l) {
-        const RowMap rows{static_cast<long>(NH) * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
-        launch_gemm(H1_adj_.ptr, rows, w_h1_.ptr + static_cast<std::size_t>(l) * C * C, C, true, M0_adj_.ptr, rows, 0, N, C, C, false,
-                    l == 0 ? readout1_.ptr : nullptr);
-    }
-    for (int a = 0; a < n_active; ++a) {
-        const int begin = type_begin_[a], count = type_begin_[a + 1] - begin;
-        launch_gemm(H2_adj_.ptr, flat_rows, h2_skip_.ptr + static_cast<std::size_t>(active_types_[a]) * C * C, C, true, M0_adj_.ptr,
-                    scalar_rows, begin, count, C, C, true, nullptr);
+    {
+        std::vector<TcCall> calls;
+        for (int l = 0; l <= model_.hidden_l_max; ++l) {
+            const RowMap rows{static_cast<long>(NH) * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
+            calls.push_back({H1_adj_.ptr, rows, &s_h1_[l], true, M0_adj_.ptr, rows, 0, N, false, l == 0 ? readout1_.ptr : nullptr});
+        }
+        launch_tc(calls);
+        calls.clear();
+        for (int a = 0; a < n_active; ++a) {
+            const int begin = type_begin_[a], count = type_begin_[a + 1] - begin;
+            calls.push_back({H2_adj_.ptr, flat_rows, &s_h2_skip_[active_types_[a]], true, M0_adj_.ptr, scalar_rows, begin, count, true, nullptr});
+        }
+        launch_tc(calls);
     }
     span_end();
     span_begin("m0_reverse");
@@ -577,6 +728,7 @@ void Evaluator::finish_compute()
         SXB_CUDA(cudaEventElapsedTime(&ms, span.begin, span.end));
         profile_.push_back({span.name, ms, span.launches});
     }
+    if (flag & 2) throw std::runtime_error("Tensor-core linear: a bounded wait expired; results are invalid.");
     if (flag != 0) throw std::invalid_argument("Edge geometry contains a zero-length or non-finite edge vector.");
     have_results_ = true;
 }

@@ -8,7 +8,10 @@
 #include <vector>
 
 #include "common.cuh"
+#include <cuda.h>
+
 #include "model.hpp"
+#include "row_map.hpp"
 
 namespace sxb {
 
@@ -77,6 +80,22 @@ private:
     // model tables on the device
     DeviceBuffer<float> r0_table_, r1_table_, m0_weights_, m1_weights_, w_h1_, w_a1_[4], h2_skip_, h2_m1_;
     DeviceBuffer<float> readout1_, readout2_w1_, readout2_w2_;
+    // the same weights split into TF32-exact high part and residual, stored [N][K] (K contiguous)
+    // for the product with W ("fwd", C = A W) and with W^T ("rev", C = A W^T)
+    struct SplitWeight {
+        DeviceBuffer<float> fwd_hi, fwd_lo, rev_hi, rev_lo, full;
+        int rows = 0, cols = 0;   // W is [rows = K of fwd][cols = N of fwd]
+        CUtensorMap map_fwd_hi, map_fwd_lo, map_rev_hi, map_rev_lo;   // [N][K] tensors, box [n_tile][32]
+    };
+    SplitWeight s_h1_[4], s_a1_[4], s_h2_m1_;
+    std::vector<SplitWeight> s_h2_skip_;
+    bool use_tensor_cores_ = true;
+    void upload_split(SplitWeight& out, const float* w, int rows, int cols);
+    struct TcCall {
+        const float* A; RowMap a_rows; const SplitWeight* w; bool reverse; float* C; RowMap c_rows;
+        int first_node, num_nodes; bool accumulate; const float* bias;
+    };
+    void launch_tc(const std::vector<TcCall>& calls);
     DeviceBuffer<double> atomic_energies_;
     CouplingConstants coupling_;
     SplineGrid grid_;

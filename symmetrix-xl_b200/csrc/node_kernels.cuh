@@ -6,6 +6,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "row_map.hpp"
 #include "generated/structures.h"
 
 namespace sxb {
@@ -120,13 +121,6 @@ SXB_DEFINE_POLY_KERNELS(S1)
 //   C[row(g)][n] (+)= sum_k A[row(g)][k] * B[k][n]      (B stored [K][N], or [N][K] when transposed)
 // Logical row g of a node tensor (node, component, channel): node = first_node + g / components,
 // m = g % components, address = node*node_stride + offset + m*component_stride.
-struct RowMap {
-    long node_stride;
-    long component_stride;
-    long offset;
-    int components;
-};
-
 struct GemmArgs {
     const float* A;
     const float* B;
