@@ -14,6 +14,7 @@
 #include <numeric>
 
 #include "edge_kernels.cuh"
+#include "edge_kernels_warp.cuh"
 #include "graph_kernels.cuh"
 #include "node_kernels.cuh"
 #include "tc_gemm.cuh"
@@ -564,8 +565,17 @@ void Evaluator::run_pipeline()
 
     // layer 0 forward
     span_begin("l0_forward");
-    SXB_LAUNCH_BY_CHANNELS(l0_forward_kernel, C, N, stream_, N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_,
-                           r0_table_.ptr, A0_.ptr);
+    {
+        const int warp_grid = blocks_for(N, kWarpsPerBlock), warp_threads = 32 * kWarpsPerBlock;
+        if (C == 128)
+            l0_forward_warp_kernel<4><<<warp_grid, warp_threads, 0, stream_>>>(N, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
+        else if (C == 64)
+            l0_forward_warp_kernel<2><<<warp_grid, warp_threads, 0, stream_>>>(N, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
+        else if (C == 32)
+            l0_forward_warp_kernel<1><<<warp_grid, warp_threads, 0, stream_>>>(N, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
+        else
+            l0_forward_kernel<0><<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
+    }
     launches_ += 1;
     span_end();
     span_begin("m0_forward");
@@ -701,8 +711,17 @@ void Evaluator::run_pipeline()
     span_end();
     span_begin("l0_reverse");
     fo.accumulate_edge = 1;
-    SXB_LAUNCH_BY_CHANNELS(l0_reverse_kernel, C, N, stream_, N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_,
-                           r0_table_.ptr, A0_adj_.ptr, fo);
+    {
+        const int warp_grid = blocks_for(N, kWarpsPerBlock), warp_threads = 32 * kWarpsPerBlock;
+        if (C == 128)
+            l0_reverse_warp_kernel<4><<<warp_grid, warp_threads, 0, stream_>>>(N, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
+        else if (C == 64)
+            l0_reverse_warp_kernel<2><<<warp_grid, warp_threads, 0, stream_>>>(N, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
+        else if (C == 32)
+            l0_reverse_warp_kernel<1><<<warp_grid, warp_threads, 0, stream_>>>(N, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
+        else
+            l0_reverse_kernel<0><<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
+    }
     launches_ += 1;
     span_end();
     span_begin("finalize");
