@@ -110,6 +110,17 @@ int sxb_reduce_atom_forces(sxb_evaluator* evaluator, uint64_t generation, double
 int sxb_reduce_stress(sxb_evaluator* evaluator, uint64_t generation, double volume, double* out9);
 int sxb_get_energy(sxb_evaluator* evaluator, double* out);
 
+/* Graph-less reduction of caller-held directed edge forces: F_j += f_ij, F_i -= f_ij and
+ * stress = -(1/volume) sum f_ij (x) xyz_ij.  Replaces _reduce_atom_forces(num_nodes, edge_receivers,
+ * edge_sources) and _reduce_stress(volume, xyz) with execution_graph_generation = 0
+ * (symmetrix/source/cpp/mace_kokkos.cpp:2103-2154; MACEKokkos::reduce_node_forces / reduce_stress,
+ * libsymmetrix/source/mace_kokkos_evaluate.cpp:92-106, 157-186).  Host arrays: edge_receivers,
+ * edge_sources int32[num_edges]; edge_forces, xyz f64[3*num_edges]; atom_forces f64[3*num_nodes];
+ * stress9 f64[9].  Runs on the current CUDA device and allocates its device buffers per call. */
+int sxb_reduce_edge_forces(int32_t num_nodes, int64_t num_edges, const int32_t* edge_receivers,
+                           const int32_t* edge_sources, const double* edge_forces, const double* xyz, double volume,
+                           double* atom_forces, double* stress9);
+
 /* Device addresses of the last results (valid until the next prepare/compute): energy f64[1],
  * forces f64[3*num_nodes] in caller order, virial f64[9] = sum f_ij (x) xyz_ij. */
 int sxb_device_results(sxb_evaluator* evaluator, const double** energy, const double** forces,

@@ -7,6 +7,6 @@ hyphen, so the package is loaded under the importable name ``symmetrix_xl_b200``
 (``__graft_entry__.load_package``).
 """
 from . import structure, modelgen  # noqa: F401
-from .evaluator import MACEB200, Calculator, load_library, LIBRARY_PATH, SIGNATURES  # noqa: F401
+from .evaluator import MACEB200, Calculator, load_library, reduce_edge_forces, LIBRARY_PATH, SIGNATURES  # noqa: F401
 
-__all__ = ["structure", "modelgen", "MACEB200", "Calculator", "load_library", "LIBRARY_PATH", "SIGNATURES"]
+__all__ = ["structure", "modelgen", "MACEB200", "Calculator", "load_library", "reduce_edge_forces", "LIBRARY_PATH", "SIGNATURES"]

@@ -16,6 +16,13 @@ struct sxb_evaluator {
 
 namespace {
 thread_local std::string g_last_error;
+}  // namespace
+
+namespace sxb {
+void set_last_error(const std::string& message) { g_last_error = message; }
+}  // namespace sxb
+
+namespace {
 
 template <typename F>
 int guarded(F&& body)

@@ -54,6 +54,7 @@ SIGNATURES = {
     "sxb_reduce_atom_forces": (ctypes.c_int, [_P, ctypes.c_uint64, _P, ctypes.c_int64]),
     "sxb_reduce_stress": (ctypes.c_int, [_P, ctypes.c_uint64, ctypes.c_double, _P]),
     "sxb_get_energy": (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_double)]),
+    "sxb_reduce_edge_forces": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int64, _P, _P, _P, _P, ctypes.c_double, _P, _P]),
     "sxb_device_results": (ctypes.c_int, [_P, ctypes.POINTER(_P), ctypes.POINTER(_P), ctypes.POINTER(_P)]),
     "sxb_get_stage": (ctypes.c_int, [_P, ctypes.c_char_p, _P, ctypes.c_int64, ctypes.POINTER(ctypes.c_int64)]),
     "sxb_launch_count": (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_int64)]),
@@ -272,6 +273,21 @@ class MACEB200:
         value = ctypes.c_float()
         _check(self._lib.sxb_last_compute_ms(self._h, ctypes.byref(value)))
         return value.value
+
+
+def reduce_edge_forces(num_nodes, edge_receivers, edge_sources, edge_forces, xyz, volume):
+    """Atom forces [N,3] and stress [3,3] from directed edge forces and explicit edge lists (the
+    graph-less mode of the reference's _reduce_atom_forces / _reduce_stress)."""
+    lib = load_library()
+    recv, src = _i32(edge_receivers), _i32(edge_sources)
+    f, r = _f64(edge_forces).reshape(-1), _f64(xyz).reshape(-1)
+    if recv.size != src.size or f.size != 3 * recv.size or r.size != 3 * recv.size:
+        raise ValueError("Atom-force reduction edge extents are inconsistent.")
+    forces = np.zeros((int(num_nodes), 3), dtype=np.float64)
+    stress = np.zeros((3, 3), dtype=np.float64)
+    _check(lib.sxb_reduce_edge_forces(int(num_nodes), recv.size, recv.ctypes.data, src.ctypes.data, f.ctypes.data,
+                                      r.ctypes.data, float(volume), forces.ctypes.data, stress.ctypes.data))
+    return forces, stress
 
 
 class Calculator:

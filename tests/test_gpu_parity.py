@@ -172,3 +172,23 @@ def test_forces_are_energy_gradient(pkg, model_path):
         em = calc.calculate(m, cell, types)["energy"]
         fd = -(ep - em) / (2 * h)
         assert abs(fd - base["forces"][atom, axis]) <= 5e-3 * max(1.0, abs(fd))
+
+
+def test_graphless_force_and_stress_reduction(pkg, model_path):
+    """Directed forces reduced from explicit edge lists (reference: _reduce_atom_forces /
+    _reduce_stress with execution_graph_generation = 0) agree with the fused reduction."""
+    path = model_path("small")
+    pos, cell, types = pkg.modelgen.srtio3(3, 0.05, 6)
+    first, src, shifts, xyz = csr_from_positions(pos, cell, 5.0)
+    ev = pkg.MACEB200(path)
+    gen = ev.compute_node_energies_forces(len(pos), types, np.diff(first), src, types[src], xyz)
+    volume = abs(np.linalg.det(cell))
+    fused_f = ev._reduce_atom_forces(len(pos), execution_graph_generation=gen)
+    fused_s = ev._reduce_stress(volume, execution_graph_generation=gen)
+    recv = np.repeat(np.arange(len(pos)), np.diff(first))
+    f, s = pkg.reduce_edge_forces(len(pos), recv, src, ev.node_forces, xyz, volume)
+    want_f, want_s = ref.reduce_forces_stress(len(pos), np.diff(first), src, ev.node_forces, xyz, volume)
+    assert np.abs(f - want_f).max() < 1e-12 and np.abs(s - want_s).max() < 1e-14
+    assert np.abs(f - fused_f).max() < 1e-6 and np.abs(s - fused_s).max() < 1e-8
+    with pytest.raises(ValueError):
+        pkg.reduce_edge_forces(len(pos), recv, src + 1000, ev.node_forces, xyz, volume)
