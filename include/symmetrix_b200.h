@@ -121,6 +121,26 @@ int sxb_reduce_edge_forces(int32_t num_nodes, int64_t num_edges, const int32_t* 
                            const int32_t* edge_sources, const double* edge_forces, const double* xyz, double volume,
                            double* atom_forces, double* stress9);
 
+/* The same reduction for callers that cannot allocate device memory.  It has no counterpart in
+ * the reference.  It exists for hosts that have given all device memory to a pool of their own
+ * (a raw cudaMalloc may then fail although the pool has room) and for force callbacks inside a
+ * time step, where cudaMalloc / cudaFree would stall the whole device because they synchronise it.
+ * Every pointer is a DEVICE pointer on the current CUDA device and the work is only enqueued on
+ * `stream` (results are ready once the stream reaches them).  Scratch (per-block virial partials)
+ * lives in a static device array inside the library: 1.18 MB per GPU, held until the process
+ * exits, enough for at most 4,194,304 edges per call -- larger edge counts are rejected with
+ * SXB_ERR_INVALID_ARGUMENT.  The call itself performs no cudaMalloc / cudaFree.  The first call on
+ * each device looks up the array's device address; make that first call before any stream capture
+ * is open on the device.  All calls share the one array, which keeps the previous call's contents
+ * (nothing in it needs clearing: each call rewrites every entry it later reads), so two calls whose
+ * kernels can overlap on the GPU -- different streams, or the same stream from two host threads
+ * without ordering -- race on it; serialise them.  device_status (may be NULL) receives 1 when an
+ * edge names a node outside [0, num_nodes), 0 otherwise; such edges are skipped. */
+int sxb_reduce_edge_forces_static(int32_t num_nodes, int64_t num_edges, const int32_t* device_receivers,
+                                  const int32_t* device_sources, const double* device_edge_forces,
+                                  const double* device_xyz, double volume, double* device_atom_forces,
+                                  double* device_stress9, int32_t* device_status, void* stream);
+
 /* Device addresses of the last results (valid until the next prepare/compute): energy f64[1],
  * forces f64[3*num_nodes] in caller order, virial f64[9] = sum f_ij (x) xyz_ij. */
 int sxb_device_results(sxb_evaluator* evaluator, const double** energy, const double** forces,

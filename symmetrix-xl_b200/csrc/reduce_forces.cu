@@ -148,3 +148,81 @@ extern "C" int sxb_reduce_edge_forces(int32_t num_nodes, int64_t num_edges, cons
         return SXB_ERR_RUNTIME;
     }
 }
+
+// ---------------------------------------------------------------------------------------------
+// Variant for callers that must not allocate device memory.  Two kinds of callers of this library
+// are in that position: a molecular-dynamics engine that has handed the whole device to its own
+// memory pool (LAMMPS/Kokkos, or a Python driver under a caching allocator), where a raw
+// cudaMalloc can fail although the pool still has room; and a force callback in the middle of a
+// time step, where cudaMalloc / cudaFree would stall every stream of the device because they
+// synchronise it.  For them the per-block virial partials (and a status word) live in a file-scope
+// device array that every GPU loading this library holds until the process exits.
+namespace sxb {
+
+constexpr long kStaticMaxEdges = 4194304;                                   // 2^22 directed edges per call
+constexpr int kStaticMaxBlocks = static_cast<int>(kStaticMaxEdges / kReduceThreads);
+// 16,384 blocks x 9 doubles = 1.18 MB per GPU
+static __device__ __align__(256) double g_static_partials[static_cast<long>(kStaticMaxBlocks) * 9];
+static __device__ __align__(256) int g_static_status[64];
+
+// In host code the array names above are host-side stand-ins, not device addresses: the device
+// address is looked up once per device (with that device current) and kept here.
+struct StaticScratch {
+    double* partials = nullptr;
+    int* status = nullptr;
+    bool ready = false;
+};
+constexpr int kMaxDevices = 64;
+static StaticScratch g_static_scratch[kMaxDevices];
+static std::mutex g_static_mutex;
+
+static const StaticScratch& static_scratch_for_current_device()
+{
+    int device = -1;
+    SXB_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) throw std::invalid_argument("CUDA device ordinal is outside the supported range.");
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    StaticScratch& entry = g_static_scratch[device];
+    if (!entry.ready) {
+        void* partials = nullptr;
+        void* status = nullptr;
+        SXB_CUDA(cudaGetSymbolAddress(&partials, g_static_partials));
+        SXB_CUDA(cudaGetSymbolAddress(&status, g_static_status));
+        entry.partials = static_cast<double*>(partials);
+        entry.status = static_cast<int*>(status);
+        entry.ready = true;
+    }
+    return entry;
+}
+
+}  // namespace sxb
+
+extern "C" int sxb_reduce_edge_forces_static(int32_t num_nodes, int64_t num_edges, const int32_t* device_receivers,
+                                             const int32_t* device_sources, const double* device_edge_forces,
+                                             const double* device_xyz, double volume, double* device_atom_forces,
+                                             double* device_stress9, int32_t* device_status, void* stream)
+{
+    using namespace sxb;
+    try {
+        if (num_nodes <= 0 || num_edges < 0) throw std::invalid_argument("Force reduction extents must be positive.");
+        if (num_edges > kStaticMaxEdges)
+            throw std::invalid_argument("sxb_reduce_edge_forces_static handles at most 4,194,304 edges per call (" +
+                                        std::to_string(num_edges) + " given); split the edge list or use sxb_reduce_edge_forces.");
+        if (!(volume > 0.0)) throw std::invalid_argument("Stress reduction needs a positive volume.");
+        if (!device_receivers || !device_sources || !device_edge_forces || !device_xyz || !device_atom_forces || !device_stress9)
+            throw std::invalid_argument("Force reduction arguments must not be NULL.");
+        const StaticScratch& scratch = static_scratch_for_current_device();
+        // every partial the second kernel reads is rewritten by the first one, so nothing in the
+        // scratch has to be cleared; the status word and the output forces are zeroed on the stream
+        launch_reduce_edge_forces(num_edges, num_nodes, device_receivers, device_sources, device_edge_forces, device_xyz, volume,
+                                  device_atom_forces, device_stress9, scratch.partials,
+                                  device_status != nullptr ? device_status : scratch.status, static_cast<cudaStream_t>(stream));
+        return SXB_OK;
+    } catch (const std::invalid_argument& e) {
+        set_last_error(e.what());
+        return SXB_ERR_INVALID_ARGUMENT;
+    } catch (const std::exception& e) {
+        set_last_error(e.what());
+        return SXB_ERR_RUNTIME;
+    }
+}

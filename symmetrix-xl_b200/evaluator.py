@@ -55,6 +55,8 @@ SIGNATURES = {
     "sxb_reduce_stress": (ctypes.c_int, [_P, ctypes.c_uint64, ctypes.c_double, _P]),
     "sxb_get_energy": (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_double)]),
     "sxb_reduce_edge_forces": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int64, _P, _P, _P, _P, ctypes.c_double, _P, _P]),
+    "sxb_reduce_edge_forces_static": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int64, _P, _P, _P, _P, ctypes.c_double, _P, _P,
+                                                     _P, _P]),
     "sxb_device_results": (ctypes.c_int, [_P, ctypes.POINTER(_P), ctypes.POINTER(_P), ctypes.POINTER(_P)]),
     "sxb_get_stage": (ctypes.c_int, [_P, ctypes.c_char_p, _P, ctypes.c_int64, ctypes.POINTER(ctypes.c_int64)]),
     "sxb_launch_count": (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_int64)]),
