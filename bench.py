@@ -61,7 +61,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -152,12 +152,16 @@ def run_ours(args):
             stress = ev._reduce_stress(volume, execution_graph_generation=gen)
             return (time.perf_counter() - t0) * 1e3, float(energies.sum()), forces, stress
 
+        sampler = ClockSampler(local_rank)
+        sampler.start()
         for _ in range(max(args.warmup, 3)):
             flush.fill_(1)
             step_device()
+        # keep the GPU under the same load for ~0.4 s so that the 50 ms clock samples see it busy
+        t_busy = time.perf_counter()
+        while time.perf_counter() - t_busy < 0.4:
+            step_device()
         barrier()
-        sampler = ClockSampler(local_rank)
-        sampler.start()
         launches_before = ev.launch_count
         wall0 = time.perf_counter()
         device_ms = []

@@ -157,6 +157,44 @@ int sxb_get_stage(sxb_evaluator* evaluator, const char* name, double* out, int64
 int sxb_launch_count(const sxb_evaluator* evaluator, int64_t* out);
 int sxb_last_compute_ms(const sxb_evaluator* evaluator, float* out);
 
+/* ---- Domain-decomposed evaluation (one process per GPU) ------------------------------------------
+ * A rank holds `num_receivers` owned atoms followed by its ghost atoms (copies of atoms owned by
+ * other ranks, or periodic images of its own, within the halo), num_nodes in total.  Only owned atoms
+ * are receivers; ghosts carry H1, H1_adj, a type, a position and a force row.
+ *
+ * sxb_prepare_local_graph replaces MACEKokkos::prepare_factorized_graph_device(num_receivers,
+ * num_feature_nodes, ...) as the LAMMPS pair style calls it
+ * (pair_symmetrix/pair_symmetrix_mace_kokkos.cpp:1464-1476; libsymmetrix/source/mace_kokkos.hpp:672-697),
+ * building the receiver-major graph of the open (non-periodic) local node set on the device.
+ * positions: host f64[3*num_nodes] with ghosts already displaced to their image positions.
+ *
+ * sxb_distributed_begin / _continue / _finish replace begin_ / continue_ /
+ * finish_factorized_distributed_evaluation (libsymmetrix/source/mace_kokkos_evaluate.cpp:1658-1833,
+ * 1836-1983, 1986-2101; call sites pair_symmetrix_mace_kokkos.cpp:1568, 1690, 1705):
+ *   begin:    geometry, layer 0, M0, H1 of the owned atoms          -> exchange H1 rows of ghosts
+ *   continue: layer 1 forward ... fused layer-1 gradient            -> return H1_adj rows of ghosts
+ *   finish:   rest of the reverse pass, forces on owned and ghost nodes, energy, virial.
+ * Calling them out of order fails with SXB_ERR_INVALID_ARGUMENT and resets the phase (the reference
+ * throws std::logic_error).  device_positions: f64[3*num_nodes] on the evaluator's device.
+ *
+ * sxb_halo_pack / sxb_halo_unpack replace the pair style's pack/unpack_forward_comm_kokkos and
+ * pack/unpack_reverse_comm_kokkos kernels (pair_symmetrix_mace_kokkos.cpp:737-1005): rows of H1
+ * (which = 0) or H1_adj (which = 1), FP32, [count][num_hidden*num_channels], for the caller-order
+ * node indices in device_indices; unpack with accumulate != 0 adds (owners summing ghost adjoints).
+ * sxb_add_force_rows adds returned ghost forces f64[count][3] into the owners' force rows after
+ * finish (the pair style's force reverse communication, pair_symmetrix_mace_kokkos.cpp:1853-1876).
+ * sxb_set_stream makes the evaluator enqueue on the caller's stream (e.g. the one NCCL uses). */
+int sxb_prepare_local_graph(sxb_evaluator* evaluator, int32_t num_receivers, int32_t num_nodes, const int32_t* node_types,
+                            const double* positions, double neighbor_cutoff, uint64_t* generation, int64_t* num_edges);
+int sxb_distributed_begin(sxb_evaluator* evaluator, uint64_t generation, const double* device_positions);
+int sxb_distributed_continue(sxb_evaluator* evaluator);
+int sxb_distributed_finish(sxb_evaluator* evaluator);
+int sxb_halo_pack(sxb_evaluator* evaluator, int32_t which, const int32_t* device_indices, int64_t count, float* device_out);
+int sxb_halo_unpack(sxb_evaluator* evaluator, int32_t which, const int32_t* device_indices, int64_t count,
+                    const float* device_in, int32_t accumulate);
+int sxb_add_force_rows(sxb_evaluator* evaluator, const int32_t* device_indices, int64_t count, const double* device_in);
+int sxb_set_stream(sxb_evaluator* evaluator, void* stream);
+
 /* Per-stage device times of the last compute (CUDA events on the evaluator's stream around each
  * kernel group), collected only while profiling is enabled; counterpart of the reference's per-stage
  * counters (factorized_last_evaluation_ms ..., libsymmetrix/source/mace_kokkos.hpp:1431-1454).

@@ -3,7 +3,9 @@
 // ValueError / RuntimeError (symmetrix/source/cpp/mace_kokkos.cpp).
 #include "../../include/symmetrix_b200.h"
 
+#include <algorithm>
 #include <cstring>
+#include <vector>
 #include <new>
 #include <string>
 
@@ -39,7 +41,7 @@ int guarded(F&& body)
     } catch (const std::invalid_argument& e) {
         g_last_error = e.what();
         return SXB_ERR_INVALID_ARGUMENT;
-    } catch (const std::out_of_range& e) {
+    } catch (const std::logic_error& e) {
         g_last_error = e.what();
         return SXB_ERR_INVALID_ARGUMENT;
     } catch (const std::exception& e) {
@@ -236,6 +238,87 @@ int sxb_launch_count(const sxb_evaluator* ev, int64_t* out)
 int sxb_last_compute_ms(const sxb_evaluator* ev, float* out)
 {
     return guarded([&] { require(ev, "evaluator"); require(out, "out"); *out = ev->impl.last_ms(); });
+}
+
+int sxb_prepare_local_graph(sxb_evaluator* ev, int32_t num_receivers, int32_t num_nodes, const int32_t* node_types,
+                            const double* positions, double neighbor_cutoff, uint64_t* generation, int64_t* num_edges)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(node_types, "node_types"); require(positions, "positions"); require(generation, "generation");
+        if (num_nodes <= 0) throw std::invalid_argument("Neighbor graph needs at least one node.");
+        // open (non-periodic) set of nodes: a box around them with a margin wider than the cutoff, so
+        // that no periodic image of the box can come within reach and every shift is zero
+        double lo[3] = {positions[0], positions[1], positions[2]}, hi[3] = {positions[0], positions[1], positions[2]};
+        for (int i = 0; i < num_nodes; ++i)
+            for (int d = 0; d < 3; ++d) {
+                lo[d] = std::min(lo[d], positions[3 * i + d]);
+                hi[d] = std::max(hi[d], positions[3 * i + d]);
+            }
+        double cell[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0}, inverse[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+        const double margin = neighbor_cutoff + 1.0;
+        for (int d = 0; d < 3; ++d) {
+            cell[4 * d] = (hi[d] - lo[d]) + 2.0 * margin;
+            inverse[4 * d] = 1.0 / cell[4 * d];
+        }
+        std::vector<double> shifted(3 * static_cast<std::size_t>(num_nodes));
+        for (int i = 0; i < num_nodes; ++i)
+            for (int d = 0; d < 3; ++d) shifted[3 * i + d] = positions[3 * i + d] - lo[d] + margin;
+        const auto result = ev->impl.prepare_periodic_graph(num_nodes, node_types, shifted.data(), cell, inverse, neighbor_cutoff,
+                                                            num_receivers);
+        *generation = result.first;
+        if (num_edges != nullptr) *num_edges = result.second;
+    });
+}
+
+int sxb_distributed_begin(sxb_evaluator* ev, uint64_t generation, const double* device_positions)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(device_positions, "device_positions");
+        ev->impl.distributed_begin(generation, device_positions);
+    });
+}
+
+int sxb_distributed_continue(sxb_evaluator* ev)
+{
+    return guarded([&] { require(ev, "evaluator"); ev->impl.distributed_continue(); });
+}
+
+int sxb_distributed_finish(sxb_evaluator* ev)
+{
+    return guarded([&] { require(ev, "evaluator"); ev->impl.distributed_finish(); });
+}
+
+int sxb_halo_pack(sxb_evaluator* ev, int32_t which, const int32_t* device_indices, int64_t count, float* device_out)
+{
+    return guarded([&] {
+        require(ev, "evaluator");
+        if (count > 0) { require(device_indices, "device_indices"); require(device_out, "device_out"); }
+        ev->impl.pack_rows(which, device_indices, count, device_out);
+    });
+}
+
+int sxb_halo_unpack(sxb_evaluator* ev, int32_t which, const int32_t* device_indices, int64_t count, const float* device_in,
+                    int32_t accumulate)
+{
+    return guarded([&] {
+        require(ev, "evaluator");
+        if (count > 0) { require(device_indices, "device_indices"); require(device_in, "device_in"); }
+        ev->impl.unpack_rows(which, device_indices, count, device_in, accumulate != 0);
+    });
+}
+
+int sxb_add_force_rows(sxb_evaluator* ev, const int32_t* device_indices, int64_t count, const double* device_in)
+{
+    return guarded([&] {
+        require(ev, "evaluator");
+        if (count > 0) { require(device_indices, "device_indices"); require(device_in, "device_in"); }
+        ev->impl.add_force_rows(device_indices, count, device_in);
+    });
+}
+
+int sxb_set_stream(sxb_evaluator* ev, void* stream)
+{
+    return guarded([&] { require(ev, "evaluator"); ev->impl.set_stream(static_cast<cudaStream_t>(stream)); });
 }
 
 int sxb_set_profiling(sxb_evaluator* ev, int32_t enabled)

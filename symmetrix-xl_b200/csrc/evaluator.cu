@@ -141,7 +141,7 @@ Evaluator::~Evaluator()
     if (event_begin_) cudaEventDestroy(event_begin_);
     if (event_end_) cudaEventDestroy(event_end_);
     for (auto e : event_pool_) cudaEventDestroy(e);
-    if (stream_) cudaStreamDestroy(stream_);
+    if (stream_ && owns_stream_) cudaStreamDestroy(stream_);
 }
 
 void Evaluator::prepare_active_types(const std::vector<int>& node_types)
@@ -164,8 +164,12 @@ void Evaluator::prepare_active_types(const std::vector<int>& node_types)
 
 // Installs a caller-order CSR graph that already sits on the device, re-expressed in the internal
 // node order (stable sort by element type).
-void Evaluator::install_graph(int num_nodes, const std::vector<int>& node_types, long num_edges, bool has_shifts)
+void Evaluator::install_graph(int num_receivers, int num_nodes, const std::vector<int>& node_types, long num_edges, bool has_shifts)
 {
+    // Receivers (nodes that own edges and readouts) come first in the caller's order; the nodes
+    // after them are feature-only nodes (ghost atoms of a domain decomposition): they carry H1,
+    // H1_adj, a type, a position and a force row, nothing else.
+    num_receivers_ = num_receivers;
     num_nodes_ = num_nodes;
     num_edges_ = num_edges;
     has_shifts_ = has_shifts;
@@ -174,7 +178,7 @@ void Evaluator::install_graph(int num_nodes, const std::vector<int>& node_types,
     for (std::size_t a = 0; a < active_types_.size(); ++a) type_to_active[active_types_[a]] = static_cast<int>(a);
     std::vector<int> original(num_nodes);
     std::iota(original.begin(), original.end(), 0);
-    std::stable_sort(original.begin(), original.end(), [&](int a, int b) { return node_types[a] < node_types[b]; });
+    std::stable_sort(original.begin(), original.begin() + num_receivers, [&](int a, int b) { return node_types[a] < node_types[b]; });
     std::vector<int> internal_of(num_nodes);
     std::vector<unsigned char> atype(num_nodes), element(num_nodes);
     type_begin_.assign(active_types_.size() + 1, 0);
@@ -182,7 +186,7 @@ void Evaluator::install_graph(int num_nodes, const std::vector<int>& node_types,
         internal_of[original[i]] = i;
         atype[i] = static_cast<unsigned char>(type_to_active[node_types[original[i]]]);
         element[i] = static_cast<unsigned char>(node_types[original[i]]);
-        type_begin_[atype[i] + 1] += 1;
+        if (i < num_receivers) type_begin_[atype[i] + 1] += 1;
     }
     for (std::size_t a = 0; a < active_types_.size(); ++a) type_begin_[a + 1] += type_begin_[a];
     if (model_.num_elements > 255) throw std::invalid_argument("More than 255 element types.");
@@ -192,35 +196,36 @@ void Evaluator::install_graph(int num_nodes, const std::vector<int>& node_types,
     upload(element_, element, stream_);
 
     // internal CSR
-    first_.reserve(num_nodes + 1);
+    const int R = num_receivers;
+    first_.reserve(R + 1);
     sources_.reserve(num_edges);
     if (has_shifts) shifts_.reserve(3 * num_edges);
     edge_map_.reserve(num_edges);
     DeviceBuffer<int> counts;
-    counts.reserve(num_nodes + 1);
-    SXB_CUDA(cudaMemsetAsync(counts.ptr, 0, (num_nodes + 1) * sizeof(int), stream_));
-    gather_counts_kernel<<<blocks_for(num_nodes, 256), 256, 0, stream_>>>(num_nodes, original_.ptr, first_caller_.ptr, counts.ptr);
+    counts.reserve(R + 1);
+    SXB_CUDA(cudaMemsetAsync(counts.ptr, 0, (R + 1) * sizeof(int), stream_));
+    gather_counts_kernel<<<blocks_for(R, 256), 256, 0, stream_>>>(R, original_.ptr, first_caller_.ptr, counts.ptr);
     launches_ += 1;
     std::size_t temp_bytes = 0;
-    cub::DeviceScan::ExclusiveSum(nullptr, temp_bytes, counts.ptr, first_.ptr, num_nodes + 1, stream_);
+    cub::DeviceScan::ExclusiveSum(nullptr, temp_bytes, counts.ptr, first_.ptr, R + 1, stream_);
     DeviceBuffer<unsigned char> temp;
     temp.reserve(temp_bytes);
-    cub::DeviceScan::ExclusiveSum(temp.ptr, temp_bytes, counts.ptr, first_.ptr, num_nodes + 1, stream_);
-    permute_graph_kernel<<<blocks_for(static_cast<long>(num_nodes) * 32, 256), 256, 0, stream_>>>(
-        num_nodes, original_.ptr, internal_of_.ptr, first_caller_.ptr, sources_caller_.ptr,
+    cub::DeviceScan::ExclusiveSum(temp.ptr, temp_bytes, counts.ptr, first_.ptr, R + 1, stream_);
+    permute_graph_kernel<<<blocks_for(static_cast<long>(R) * 32, 256), 256, 0, stream_>>>(
+        R, original_.ptr, internal_of_.ptr, first_caller_.ptr, sources_caller_.ptr,
         has_shifts ? shifts_caller_.ptr : nullptr, first_.ptr, sources_.ptr, has_shifts ? shifts_.ptr : nullptr, edge_map_.ptr);
     launches_ += 1;
     SXB_CUDA(cudaGetLastError());
 
     // work buffers
-    const std::size_t N = num_nodes, C = model_.channels, NH = model_.num_hidden, NE = model_.num_lme;
+    const std::size_t N = num_receivers, ALL = num_nodes, C = model_.channels, NH = model_.num_hidden, NE = model_.num_lme;
     geom_.reserve(num_edges);
     A0_.reserve(N * 16 * C);
     A0_adj_.reserve(N * 16 * C);
     M0_.reserve(N * NH * C);
     M0_adj_.reserve(N * NH * C);
-    H1_.reserve(N * NH * C);
-    H1_adj_.reserve(N * NH * C);
+    H1_.reserve(ALL * NH * C);
+    H1_adj_.reserve(ALL * NH * C);
     Phi1_.reserve(N * NE * C);
     dPhi1_.reserve(N * NE * C);
     A1_.reserve(N * 16 * C);
@@ -231,20 +236,24 @@ void Evaluator::install_graph(int num_nodes, const std::vector<int>& node_types,
     H2_adj_.reserve(N * C);
     node_energies_.reserve(N);
     node_energies_out_.reserve(N);
-    forces_.reserve(N * 3);
-    forces_out_.reserve(N * 3);
-    positions_.reserve(N * 3);
+    forces_.reserve(ALL * 3);
+    forces_out_.reserve(ALL * 3);
+    positions_.reserve(ALL * 3);
     if (keep_edge_forces_) edge_forces_.reserve(3 * static_cast<std::size_t>(num_edges));
     SXB_CUDA(cudaStreamSynchronize(stream_));
     generation_ += 1;
     have_results_ = false;
+    phase_ = 0;
 }
 
 std::pair<std::uint64_t, long> Evaluator::prepare_periodic_graph(int num_nodes, const int* node_types, const double* positions,
-                                                                 const double* cell, const double* inverse_cell, double cutoff)
+                                                                 const double* cell, const double* inverse_cell, double cutoff,
+                                                                 int num_receivers)
 {
     SXB_CUDA(cudaSetDevice(device_));
     if (num_nodes <= 0) throw std::invalid_argument("Neighbor graph needs at least one node.");
+    if (num_receivers < 0) num_receivers = num_nodes;
+    if (num_receivers == 0 || num_receivers > num_nodes) throw std::invalid_argument("Receiver count must lie in [1, num_nodes].");
     if (!std::isfinite(cutoff) || !(cutoff > 0.0)) throw std::invalid_argument("Neighbor graph cutoff must be finite and positive.");
     for (int i = 0; i < 3 * num_nodes; ++i)
         if (!std::isfinite(positions[i])) throw std::invalid_argument("Neighbor graph positions must be finite.");
@@ -306,33 +315,34 @@ std::pair<std::uint64_t, long> Evaluator::prepare_periodic_graph(int num_nodes, 
     count_bins_kernel<<<blocks_for(n, T), T, 0, stream_>>>(n, cl, wrapped_frac.ptr, atom_bin.ptr, bin_sizes.ptr);
     std::size_t temp_bytes = 0, temp_bytes2 = 0;
     cub::DeviceScan::ExclusiveSum(nullptr, temp_bytes, bin_sizes.ptr, bin_offsets.ptr, cl.num_bins + 1, stream_);
-    cub::DeviceScan::ExclusiveSum(nullptr, temp_bytes2, counts.ptr, offsets.ptr, n + 1, stream_);
+    cub::DeviceScan::ExclusiveSum(nullptr, temp_bytes2, counts.ptr, offsets.ptr, num_receivers + 1, stream_);
     DeviceBuffer<unsigned char> temp;
     temp.reserve(std::max(temp_bytes, temp_bytes2));
     cub::DeviceScan::ExclusiveSum(temp.ptr, temp_bytes, bin_sizes.ptr, bin_offsets.ptr, cl.num_bins + 1, stream_);
     SXB_CUDA(cudaMemcpyAsync(cursors.ptr, bin_offsets.ptr, (num_bins + 1) * sizeof(int), cudaMemcpyDeviceToDevice, stream_));
     fill_bins_kernel<<<blocks_for(n, T), T, 0, stream_>>>(n, atom_bin.ptr, cursors.ptr, bin_atoms.ptr);
     sort_bins_kernel<<<blocks_for(cl.num_bins, T), T, 0, stream_>>>(cl.num_bins, bin_offsets.ptr, bin_atoms.ptr);
-    neighbor_edges_kernel<false><<<blocks_for(n, T), T, 0, stream_>>>(n, cl, atom_bin.ptr, bin_offsets.ptr, bin_atoms.ptr,
+    const int nr = num_receivers;
+    neighbor_edges_kernel<false><<<blocks_for(nr, T), T, 0, stream_>>>(nr, cl, atom_bin.ptr, bin_offsets.ptr, bin_atoms.ptr,
                                                                        wrapped_pos.ptr, wrap_shift.ptr, cell_.ptr, counts.ptr,
                                                                        nullptr, nullptr, nullptr);
-    cub::DeviceScan::ExclusiveSum(temp.ptr, temp_bytes2, counts.ptr, offsets.ptr, n + 1, stream_);
+    cub::DeviceScan::ExclusiveSum(temp.ptr, temp_bytes2, counts.ptr, offsets.ptr, nr + 1, stream_);
     long long total = 0;
-    SXB_CUDA(cudaMemcpyAsync(&total, offsets.ptr + n, sizeof(long long), cudaMemcpyDeviceToHost, stream_));
+    SXB_CUDA(cudaMemcpyAsync(&total, offsets.ptr + nr, sizeof(long long), cudaMemcpyDeviceToHost, stream_));
     SXB_CUDA(cudaStreamSynchronize(stream_));
     if (total > static_cast<long long>(std::numeric_limits<int>::max()))
         throw std::length_error("Neighbor graph exceeds 32-bit edge indexing.");
-    first_caller_.reserve(n + 1);
+    first_caller_.reserve(nr + 1);
     sources_caller_.reserve(static_cast<std::size_t>(total));
     shifts_caller_.reserve(3 * static_cast<std::size_t>(total));
-    narrow_offsets_kernel<<<blocks_for(n + 1, T), T, 0, stream_>>>(n, offsets.ptr, first_caller_.ptr);
-    neighbor_edges_kernel<true><<<blocks_for(n, T), T, 0, stream_>>>(n, cl, atom_bin.ptr, bin_offsets.ptr, bin_atoms.ptr,
+    narrow_offsets_kernel<<<blocks_for(nr + 1, T), T, 0, stream_>>>(nr, offsets.ptr, first_caller_.ptr);
+    neighbor_edges_kernel<true><<<blocks_for(nr, T), T, 0, stream_>>>(nr, cl, atom_bin.ptr, bin_offsets.ptr, bin_atoms.ptr,
                                                                       wrapped_pos.ptr, wrap_shift.ptr, cell_.ptr, nullptr,
                                                                       first_caller_.ptr, sources_caller_.ptr, shifts_caller_.ptr);
     launches_ += 8;
     SXB_CUDA(cudaGetLastError());
     std::vector<int> types(node_types, node_types + n);
-    install_graph(n, types, static_cast<long>(total), true);
+    install_graph(nr, n, types, static_cast<long>(total), true);
     return {generation_, static_cast<long>(total)};
 }
 
@@ -361,7 +371,7 @@ std::uint64_t Evaluator::prepare_graph(int num_nodes, const int* node_types, con
         SXB_CUDA(cudaMemcpyAsync(cell_.ptr, cell, 9 * sizeof(double), cudaMemcpyHostToDevice, stream_));
     }
     std::vector<int> types(node_types, node_types + num_nodes);
-    install_graph(num_nodes, types, E, shifts != nullptr);
+    install_graph(num_nodes, num_nodes, types, E, shifts != nullptr);
     return generation_;
 }
 
@@ -375,7 +385,7 @@ void Evaluator::get_graph(std::uint64_t generation, int* first, int* sources, in
 {
     check_generation(generation);
     SXB_CUDA(cudaSetDevice(device_));
-    SXB_CUDA(cudaMemcpyAsync(first, first_caller_.ptr, (num_nodes_ + 1) * sizeof(int), cudaMemcpyDeviceToHost, stream_));
+    SXB_CUDA(cudaMemcpyAsync(first, first_caller_.ptr, (num_receivers_ + 1) * sizeof(int), cudaMemcpyDeviceToHost, stream_));
     SXB_CUDA(cudaMemcpyAsync(sources, sources_caller_.ptr, num_edges_ * sizeof(int), cudaMemcpyDeviceToHost, stream_));
     if (shifts != nullptr) {
         if (!has_shifts_) throw std::invalid_argument("The prepared graph carries no periodic shifts.");
@@ -552,14 +562,27 @@ void Evaluator::launch_tc(const std::vector<TcCall>& calls)
     }
 }
 
-void Evaluator::run_pipeline()
+// phases: bit 0 = up to H1 of the receivers, bit 1 = layer 1 forward .. fused layer-1 gradient,
+// bit 2 = the rest of the reverse pass.  Between the phases a domain-decomposed run exchanges the
+// H1 rows and then the H1_adj rows of its ghost nodes (reference: begin / continue /
+// finish_factorized_distributed_evaluation, libsymmetrix/source/mace_kokkos_evaluate.cpp:1658-2101).
+void Evaluator::run_pipeline(int phases)
 {
+    const int N = num_receivers_, ALL = num_nodes_, C = model_.channels, NH = model_.num_hidden, NE = model_.num_lme;
+    const int n_active = static_cast<int>(active_types_.size());
+    const dim3 poly_grid(blocks_for(N, kPolyWarps), C / 32);
+    const RowMap scalar_rows{static_cast<long>(NH) * C, C, 0, 1};
+    const RowMap flat_rows{static_cast<long>(C), C, 0, 1};
+    ForceOutputs fo;
+    fo.atom_forces = forces_.ptr;
+    fo.virial_slots = virial_slots_.ptr;
+    fo.edge_forces = keep_edge_forces_ ? edge_forces_.ptr : nullptr;
+    fo.accumulate_edge = 0;
+    if (phases & 1) {
     spans_.clear();
     events_used_ = 0;
-    const int N = num_nodes_, C = model_.channels, NH = model_.num_hidden, NE = model_.num_lme;
-    const int n_active = static_cast<int>(active_types_.size());
-    SXB_CUDA(cudaMemsetAsync(forces_.ptr, 0, sizeof(double) * 3 * N, stream_));
-    SXB_CUDA(cudaMemsetAsync(H1_adj_.ptr, 0, sizeof(float) * static_cast<std::size_t>(N) * NH * C, stream_));
+    SXB_CUDA(cudaMemsetAsync(forces_.ptr, 0, sizeof(double) * 3 * ALL, stream_));
+    SXB_CUDA(cudaMemsetAsync(H1_adj_.ptr, 0, sizeof(float) * static_cast<std::size_t>(ALL) * NH * C, stream_));
     SXB_CUDA(cudaMemsetAsync(energy_slots_.ptr, 0, sizeof(double) * kVirialSlots, stream_));
     SXB_CUDA(cudaMemsetAsync(virial_slots_.ptr, 0, sizeof(double) * kVirialSlots * 9, stream_));
 
@@ -579,7 +602,6 @@ void Evaluator::run_pipeline()
     launches_ += 1;
     span_end();
     span_begin("m0_forward");
-    const dim3 poly_grid(blocks_for(N, kPolyWarps), C / 32);
     if (model_.shape_id == 0)
         m0_forward_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A0_.ptr, element_.ptr, m0_weights_.ptr, M0_.ptr);
     else
@@ -597,6 +619,8 @@ void Evaluator::run_pipeline()
         launch_tc(calls);
     }
     span_end();
+    }
+    if (phases & 2) {
     // layer 1 forward
     span_begin("l1_forward");
     if (model_.shape_id == 0)
@@ -629,8 +653,6 @@ void Evaluator::run_pipeline()
     span_end();
     // H2 = xs T_element + M1 W
     span_begin("gemm_h2");
-    const RowMap scalar_rows{static_cast<long>(NH) * C, C, 0, 1};
-    const RowMap flat_rows{static_cast<long>(C), C, 0, 1};
     {
         std::vector<TcCall> calls;
         for (int a = 0; a < n_active; ++a) {
@@ -672,11 +694,6 @@ void Evaluator::run_pipeline()
     }
     span_end();
     span_begin("l1_reverse");
-    ForceOutputs fo;
-    fo.atom_forces = forces_.ptr;
-    fo.virial_slots = virial_slots_.ptr;
-    fo.edge_forces = keep_edge_forces_ ? edge_forces_.ptr : nullptr;
-    fo.accumulate_edge = 0;
     if (model_.shape_id == 0)
         SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S0, C, N, stream_, N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
                                r1_table_.ptr, H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
@@ -685,6 +702,8 @@ void Evaluator::run_pipeline()
                                r1_table_.ptr, H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
     launches_ += 1;
     span_end();
+    }
+    if (phases & 4) {
     span_begin("gemm_h1_reverse");
     // M0_adj_il = H1_adj_il W_l^T, then the direct adjoint q + T_element H2_adj on the scalar block
     {
@@ -726,10 +745,11 @@ void Evaluator::run_pipeline()
     span_end();
     span_begin("finalize");
     finalize_kernel<<<1, 32, 0, stream_>>>(energy_slots_.ptr, virial_slots_.ptr, totals_.ptr);
-    unpermute_doubles_kernel<<<blocks_for(N, 256), 256, 0, stream_>>>(N, 3, original_.ptr, forces_.ptr, forces_out_.ptr);
+    unpermute_doubles_kernel<<<blocks_for(ALL, 256), 256, 0, stream_>>>(ALL, 3, original_.ptr, forces_.ptr, forces_out_.ptr);
     unpermute_doubles_kernel<<<blocks_for(N, 256), 256, 0, stream_>>>(N, 1, original_.ptr, node_energies_.ptr, node_energies_out_.ptr);
     launches_ += 3;
     span_end();
+    }
     SXB_CUDA(cudaGetLastError());
 }
 
@@ -765,10 +785,10 @@ void Evaluator::compute_positions(std::uint64_t generation, const double* positi
         dpos = positions_.ptr;
     }
     SXB_CUDA(cudaMemsetAsync(error_flag_.ptr, 0, sizeof(int), stream_));
-    geometry_from_positions_kernel<<<blocks_for(static_cast<long>(num_nodes_) * 32, 256), 256, 0, stream_>>>(
-        num_nodes_, first_.ptr, sources_.ptr, shifts_.ptr, dpos, original_.ptr, cell_.ptr, geom_.ptr, error_flag_.ptr);
+    geometry_from_positions_kernel<<<blocks_for(static_cast<long>(num_receivers_) * 32, 256), 256, 0, stream_>>>(
+        num_receivers_, first_.ptr, sources_.ptr, shifts_.ptr, dpos, original_.ptr, cell_.ptr, geom_.ptr, error_flag_.ptr);
     launches_ += 1;
-    run_pipeline();
+    run_pipeline(7);
     finish_compute();
 }
 
@@ -784,8 +804,139 @@ void Evaluator::compute_edge_vectors(std::uint64_t generation, const double* xyz
     SXB_CUDA(cudaMemsetAsync(error_flag_.ptr, 0, sizeof(int), stream_));
     geometry_from_vectors_kernel<<<blocks_for(num_edges_, 256), 256, 0, stream_>>>(num_edges_, dxyz.ptr, edge_map_.ptr, geom_.ptr, error_flag_.ptr);
     launches_ += 1;
-    run_pipeline();
+    run_pipeline(7);
     finish_compute();
+}
+
+// ---- three-phase evaluation for a domain-decomposed run (positions: device f64[3*num_nodes],
+// receivers first, ghosts after them)
+void Evaluator::distributed_begin(std::uint64_t generation, const double* device_positions)
+{
+    check_generation(generation);
+    if (!has_shifts_) throw std::invalid_argument("The prepared graph has no periodic shifts; use edge vectors.");
+    if (phase_ != 0) {
+        phase_ = 0;
+        throw std::logic_error("distributed evaluation: begin called while another evaluation is open.");
+    }
+    SXB_CUDA(cudaSetDevice(device_));
+    have_results_ = false;
+    SXB_CUDA(cudaEventRecord(event_begin_, stream_));
+    SXB_CUDA(cudaMemsetAsync(error_flag_.ptr, 0, sizeof(int), stream_));
+    geometry_from_positions_kernel<<<blocks_for(static_cast<long>(num_receivers_) * 32, 256), 256, 0, stream_>>>(
+        num_receivers_, first_.ptr, sources_.ptr, shifts_.ptr, device_positions, original_.ptr, cell_.ptr, geom_.ptr, error_flag_.ptr);
+    launches_ += 1;
+    run_pipeline(1);
+    phase_ = 1;
+}
+
+void Evaluator::distributed_continue()
+{
+    if (phase_ != 1) {
+        phase_ = 0;
+        throw std::logic_error("distributed evaluation: continue must follow begin.");
+    }
+    SXB_CUDA(cudaSetDevice(device_));
+    run_pipeline(2);
+    phase_ = 2;
+}
+
+void Evaluator::distributed_finish()
+{
+    if (phase_ != 2) {
+        phase_ = 0;
+        throw std::logic_error("distributed evaluation: finish must follow continue.");
+    }
+    SXB_CUDA(cudaSetDevice(device_));
+    phase_ = 0;
+    run_pipeline(4);
+    finish_compute();
+}
+
+namespace {
+// rows of a node tensor (row_floats per node) gathered into / scattered from a dense buffer;
+// indices are caller-order node numbers
+__global__ void pack_rows_kernel(long count, int row_floats, const int* __restrict__ indices, const int* __restrict__ internal_of,
+                                 const float* __restrict__ tensor, float* __restrict__ out)
+{
+    const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int vec = row_floats >> 2;
+    if (idx >= count * vec) return;
+    const long r = idx / vec, q = idx % vec;
+    const long node = internal_of[indices[r]];
+    reinterpret_cast<float4*>(out)[idx] = reinterpret_cast<const float4*>(tensor + node * row_floats)[q];
+}
+
+__global__ void unpack_rows_kernel(long count, int row_floats, const int* __restrict__ indices, const int* __restrict__ internal_of,
+                                   const float* __restrict__ in, float* __restrict__ tensor, int accumulate)
+{
+    const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int vec = row_floats >> 2;
+    if (idx >= count * vec) return;
+    const long r = idx / vec, q = idx % vec;
+    const long node = internal_of[indices[r]];
+    const float4 v = reinterpret_cast<const float4*>(in)[idx];
+    float* dst = tensor + node * row_floats + 4 * q;
+    if (accumulate) {
+        // several images of one owned atom may be ghosts elsewhere: rows can repeat
+        atomicAdd(dst, v.x); atomicAdd(dst + 1, v.y); atomicAdd(dst + 2, v.z); atomicAdd(dst + 3, v.w);
+    } else {
+        *reinterpret_cast<float4*>(dst) = v;
+    }
+}
+
+__global__ void add_force_rows_kernel(long count, const int* __restrict__ indices, const double* __restrict__ in,
+                                      double* __restrict__ forces_caller_order)
+{
+    const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= count * 3) return;
+    const long r = idx / 3, q = idx % 3;
+    atomicAdd(forces_caller_order + 3 * static_cast<long>(indices[r]) + q, in[idx]);
+}
+}  // namespace
+
+float* Evaluator::halo_tensor(int which)
+{
+    if (which == 0) return H1_.ptr;
+    if (which == 1) return H1_adj_.ptr;
+    throw std::invalid_argument("Halo tensor selector must be 0 (H1) or 1 (H1_adj).");
+}
+
+void Evaluator::pack_rows(int which, const int* device_indices, long count, float* device_out)
+{
+    const int row = model_.num_hidden * model_.channels;
+    if (count <= 0) return;
+    pack_rows_kernel<<<blocks_for(count * (row / 4), 256), 256, 0, stream_>>>(count, row, device_indices, internal_of_.ptr,
+                                                                              halo_tensor(which), device_out);
+    launches_ += 1;
+    SXB_CUDA(cudaGetLastError());
+}
+
+void Evaluator::unpack_rows(int which, const int* device_indices, long count, const float* device_in, bool accumulate)
+{
+    const int row = model_.num_hidden * model_.channels;
+    if (count <= 0) return;
+    unpack_rows_kernel<<<blocks_for(count * (row / 4), 256), 256, 0, stream_>>>(count, row, device_indices, internal_of_.ptr, device_in,
+                                                                                halo_tensor(which), accumulate ? 1 : 0);
+    launches_ += 1;
+    SXB_CUDA(cudaGetLastError());
+}
+
+void Evaluator::add_force_rows(const int* device_indices, long count, const double* device_in)
+{
+    require_results();
+    if (count <= 0) return;
+    add_force_rows_kernel<<<blocks_for(count * 3, 256), 256, 0, stream_>>>(count, device_indices, device_in, forces_out_.ptr);
+    launches_ += 1;
+    SXB_CUDA(cudaGetLastError());
+}
+
+void Evaluator::set_stream(cudaStream_t stream)
+{
+    SXB_CUDA(cudaSetDevice(device_));
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+    if (owns_stream_ && stream_ != nullptr) SXB_CUDA(cudaStreamDestroy(stream_));
+    stream_ = stream;
+    owns_stream_ = false;
 }
 
 void Evaluator::synchronize()
@@ -802,7 +953,7 @@ void Evaluator::require_results() const
 void Evaluator::get_node_energies(double* out)
 {
     require_results();
-    SXB_CUDA(cudaMemcpyAsync(out, node_energies_out_.ptr, sizeof(double) * num_nodes_, cudaMemcpyDeviceToHost, stream_));
+    SXB_CUDA(cudaMemcpyAsync(out, node_energies_out_.ptr, sizeof(double) * num_receivers_, cudaMemcpyDeviceToHost, stream_));
     SXB_CUDA(cudaStreamSynchronize(stream_));
 }
 
@@ -847,15 +998,16 @@ double Evaluator::energy() const
 long Evaluator::get_stage(const std::string& name, double* out, long capacity)
 {
     require_results();
-    const long N = num_nodes_, C = model_.channels, NH = model_.num_hidden, NE = model_.num_lme;
+    const long C = model_.channels, NH = model_.num_hidden, NE = model_.num_lme;
+    long N = num_receivers_;
     const float* src = nullptr;
     long row = 0;
     if (name == "A0") { src = A0_.ptr; row = 16 * C; }
     else if (name == "A0_adj") { src = A0_adj_.ptr; row = 16 * C; }
     else if (name == "M0") { src = M0_.ptr; row = NH * C; }
     else if (name == "M0_adj") { src = M0_adj_.ptr; row = NH * C; }
-    else if (name == "H1") { src = H1_.ptr; row = NH * C; }
-    else if (name == "H1_adj") { src = H1_adj_.ptr; row = NH * C; }
+    else if (name == "H1") { src = H1_.ptr; row = NH * C; N = num_nodes_; }
+    else if (name == "H1_adj") { src = H1_adj_.ptr; row = NH * C; N = num_nodes_; }
     else if (name == "Phi1") { src = Phi1_.ptr; row = NE * C; }
     else if (name == "dPhi1") { src = dPhi1_.ptr; row = NE * C; }
     else if (name == "A1") { src = A1_.ptr; row = 16 * C; }

@@ -29,11 +29,14 @@ public:
 
     const HostModel& model() const { return model_; }
     int num_nodes() const { return num_nodes_; }
+    int num_receivers() const { return num_receivers_; }
     long num_edges() const { return num_edges_; }
     std::uint64_t generation() const { return generation_; }
 
+    // num_receivers < num_nodes: only the first num_receivers nodes own edges (the others are ghosts)
     std::pair<std::uint64_t, long> prepare_periodic_graph(int num_nodes, const int* node_types, const double* positions,
-                                                          const double* cell, const double* inverse_cell, double cutoff);
+                                                          const double* cell, const double* inverse_cell, double cutoff,
+                                                          int num_receivers = -1);
     std::uint64_t prepare_graph(int num_nodes, const int* node_types, const int* num_neigh, const int* neigh_indices,
                                 const int* shifts, const double* cell);
     void get_graph(std::uint64_t generation, int* first, int* sources, int* shifts);
@@ -42,6 +45,13 @@ public:
     void compute_positions(std::uint64_t generation, const double* positions, bool on_device);
     void compute_edge_vectors(std::uint64_t generation, const double* xyz);
     void synchronize();
+    void distributed_begin(std::uint64_t generation, const double* device_positions);
+    void distributed_continue();
+    void distributed_finish();
+    void pack_rows(int which, const int* device_indices, long count, float* device_out);
+    void unpack_rows(int which, const int* device_indices, long count, const float* device_in, bool accumulate);
+    void add_force_rows(const int* device_indices, long count, const double* device_in);
+    void set_stream(cudaStream_t stream);
 
     void get_node_energies(double* out);
     void get_atom_forces(double* out);
@@ -64,8 +74,9 @@ public:
 
 private:
     void prepare_active_types(const std::vector<int>& node_types);
-    void install_graph(int num_nodes, const std::vector<int>& node_types, long num_edges, bool has_shifts);
-    void run_pipeline();
+    void install_graph(int num_receivers, int num_nodes, const std::vector<int>& node_types, long num_edges, bool has_shifts);
+    void run_pipeline(int phases);
+    float* halo_tensor(int which);
     void finish_compute();
     void launch_gemm(const float* A, const RowMap& a_rows, const float* B, int ldb, bool b_transposed, float* C,
                      const RowMap& c_rows, int first_node, int num_nodes, int N, int K, bool accumulate, const float* bias);
@@ -102,7 +113,9 @@ private:
 
     // prepared graph
     std::uint64_t generation_ = 0;
-    int num_nodes_ = 0;
+    int num_nodes_ = 0, num_receivers_ = 0;
+    int phase_ = 0;
+    bool owns_stream_ = true;
     long num_edges_ = 0;
     bool has_shifts_ = false;
     DeviceBuffer<int> first_caller_, sources_caller_, shifts_caller_;

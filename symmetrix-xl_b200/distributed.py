@@ -1,0 +1,253 @@
+"""Spatial domain decomposition of one evaluation over the GPUs of a node, one process per GPU.
+
+The periodic cell is cut into a px x py x pz grid of bricks in fractional coordinates.  A rank owns
+the atoms inside its brick and keeps ghost copies of every atom image within the halo (model cutoff
++ skin) of the brick.  Owned atoms are the receivers of the rank's graph; ghosts only supply
+``H1`` rows and collect ``H1_adj`` rows and forces.  A two-layer model therefore needs exactly one
+forward exchange of ghost features and one reverse exchange of ghost adjoints per evaluation, plus
+ghost positions in and ghost forces out -- the protocol of the reference's LAMMPS pair style
+(pair_symmetrix/pair_symmetrix_mace_kokkos.cpp:1285-1938; phases
+libsymmetrix/source/mace_kokkos_evaluate.cpp:1658-2101), carried here by ``torch.distributed``
+all-to-all exchanges (NCCL over NVLink between GPUs, gloo in the CPU tests of the exchange plan)
+instead of LAMMPS' MPI brick swaps.  Remote rows always land in a local receive buffer first; no
+kernel of this package reads another GPU's memory.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+GRIDS = {1: (1, 1, 1), 2: (2, 1, 1), 4: (2, 2, 1), 8: (2, 2, 2)}
+
+
+class BrickDecomposition:
+    """Ownership and ghost selection for a brick grid over a periodic cell."""
+
+    def __init__(self, cell, grid, halo):
+        self.cell = np.asarray(cell, dtype=np.float64).reshape(3, 3)
+        self.inv = np.linalg.inv(self.cell)
+        self.grid = tuple(int(g) for g in grid)
+        self.halo = float(halo)
+        # distance between the lattice planes of axis a is 1/|column a of the inverse cell|
+        self.halo_frac = self.halo * np.sqrt((self.inv ** 2).sum(axis=0))
+
+    @property
+    def world(self):
+        return self.grid[0] * self.grid[1] * self.grid[2]
+
+    def brick_of_rank(self, rank):
+        px, py, pz = self.grid
+        return rank // (py * pz), (rank // pz) % py, rank % pz
+
+    def wrapped_fractional(self, positions):
+        frac = np.asarray(positions, dtype=np.float64).reshape(-1, 3) @ self.inv
+        return frac - np.floor(frac), np.floor(frac).astype(np.int64)
+
+    def owner(self, positions):
+        """Rank owning each atom: the brick its wrapped fractional position falls in."""
+        wf, _ = self.wrapped_fractional(positions)
+        idx = [np.minimum(self.grid[a] - 1, (wf[:, a] * self.grid[a]).astype(np.int64)) for a in range(3)]
+        return (idx[0] * self.grid[1] + idx[1]) * self.grid[2] + idx[2]
+
+    def select(self, positions, rank):
+        """Owned atoms and ghost images of ``rank``.
+
+        Returns (owned global indices ascending, ghost global indices, ghost image shifts int[G,3]
+        relative to the atoms' given (unwrapped) positions), ghosts ordered by (owner rank, atom, image).
+        A ghost is any atom image whose fractional coordinates lie in the brick widened by the halo on
+        every side, except the home image of an owned atom."""
+        positions = np.asarray(positions, dtype=np.float64).reshape(-1, 3)
+        wf, wrap = self.wrapped_fractional(positions)
+        owner = self.owner(positions)
+        owned = np.flatnonzero(owner == rank)
+        b = self.brick_of_rank(rank)
+        lo = np.array([b[a] / self.grid[a] for a in range(3)]) - self.halo_frac
+        hi = np.array([(b[a] + 1) / self.grid[a] for a in range(3)]) + self.halo_frac
+        reach = [int(np.ceil(self.halo_frac[a])) for a in range(3)]
+        ghost_idx, ghost_shift = [], []
+        for sx in range(-reach[0], reach[0] + 1):
+            for sy in range(-reach[1], reach[1] + 1):
+                for sz in range(-reach[2], reach[2] + 1):
+                    s = np.array([sx, sy, sz])
+                    f = wf + s
+                    inside = ((f >= lo) & (f < hi)).all(axis=1)
+                    if sx == 0 and sy == 0 and sz == 0:
+                        inside &= owner != rank
+                    hit = np.flatnonzero(inside)
+                    ghost_idx.append(hit)
+                    # shift relative to the unwrapped input position: image minus the wrap of the atom
+                    ghost_shift.append(s[None, :] - wrap[hit])
+        ghost_idx = np.concatenate(ghost_idx)
+        ghost_shift = np.concatenate(ghost_shift)
+        # owned atoms are wrapped into the home cell too: their shift is minus their wrap
+        order = np.lexsort((ghost_shift[:, 2], ghost_shift[:, 1], ghost_shift[:, 0], ghost_idx, owner[ghost_idx]))
+        return owned, ghost_idx[order], ghost_shift[order], -wrap[owned], owner
+
+
+class _SoloComm:
+    """Stand-in for a one-process world: the all-to-all of a single rank is a copy."""
+
+    rank, world = 0, 1
+
+    def all_to_all(self, send, send_counts, recv_counts):
+        return send.clone()
+
+    def all_reduce_sum(self, tensor):
+        return tensor
+
+
+class _TorchComm:
+    def __init__(self):
+        import torch.distributed as dist
+
+        self.dist = dist
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+
+    def all_to_all(self, send, send_counts, recv_counts):
+        import torch
+
+        row = send.shape[1:] if send.dim() > 1 else ()
+        recv = torch.empty((int(sum(recv_counts)), *row), dtype=send.dtype, device=send.device)
+        self.dist.all_to_all_single(recv, send.contiguous(), output_split_sizes=[int(c) for c in recv_counts],
+                                    input_split_sizes=[int(c) for c in send_counts])
+        return recv
+
+    def all_reduce_sum(self, tensor):
+        self.dist.all_reduce(tensor, op=self.dist.ReduceOp.SUM)
+        return tensor
+
+
+def make_comm():
+    try:
+        import torch.distributed as dist
+
+        if dist.is_available() and dist.is_initialized():
+            return _TorchComm()
+    except ImportError:
+        pass
+    return _SoloComm()
+
+
+class ExchangePlan:
+    """Who sends which owned rows to whom.  Built once per neighbor-list rebuild."""
+
+    def __init__(self, decomposition, positions, comm, device="cpu"):
+        import torch
+
+        self.comm = comm
+        self.device = device
+        rank, world = comm.rank, comm.world
+        owned, ghost_idx, ghost_shift, owned_shift, owner = decomposition.select(positions, rank)
+        self.owned = owned
+        self.owned_shift = owned_shift
+        self.ghost_idx, self.ghost_shift = ghost_idx, ghost_shift
+        ghost_owner = owner[ghost_idx]
+        self.recv_counts = np.bincount(ghost_owner, minlength=world).astype(np.int64)     # ghosts I receive, per owner
+        # tell every owner which of its atoms I need
+        counts = torch.from_numpy(self.recv_counts).to(device)
+        self.send_counts = comm.all_to_all(counts, [1] * world, [1] * world).cpu().numpy().astype(np.int64)
+        wanted = comm.all_to_all(torch.from_numpy(ghost_idx.astype(np.int64)).to(device), self.recv_counts, self.send_counts)
+        wanted = wanted.cpu().numpy()
+        local = np.searchsorted(owned, wanted)
+        if len(wanted) and (local >= len(owned)).any() or (len(wanted) and (owned[np.minimum(local, len(owned) - 1)] != wanted).any()):
+            raise RuntimeError("exchange plan: a rank asked for an atom its owner does not hold")
+        self.send_local = local.astype(np.int32)          # my owned rows to send, ordered by destination rank
+        self.num_owned, self.num_ghost = len(owned), len(ghost_idx)
+
+
+class DistributedCalculator:
+    """Energy, forces and stress of a periodic system decomposed over the ranks of the process group."""
+
+    def __init__(self, model_path, evaluator_cls, skin=0.5, device=0):
+        import torch
+
+        self.torch = torch
+        self.device = torch.device("cuda", device)
+        torch.cuda.set_device(self.device)
+        self.ev = evaluator_cls(model_path, device=device)
+        self.ev.set_stream(torch.cuda.current_stream().cuda_stream)
+        self.skin = float(skin)
+        self.comm = make_comm()
+        self.generation = 0
+
+    def prepare(self, positions, cell, types, grid=None):
+        """Decomposes the global system (every rank passes the same arrays) and builds the local graph."""
+        torch = self.torch
+        positions = np.asarray(positions, dtype=np.float64).reshape(-1, 3)
+        types = np.asarray(types, dtype=np.int32)
+        self.cell = np.asarray(cell, dtype=np.float64).reshape(3, 3)
+        self.volume = abs(np.linalg.det(self.cell))
+        grid = grid or GRIDS[self.comm.world]
+        halo = self.ev.r_cut + self.skin
+        self.decomposition = BrickDecomposition(self.cell, grid, halo)
+        if self.decomposition.world != self.comm.world:
+            raise ValueError("brick grid does not match the number of ranks")
+        plan = ExchangePlan(self.decomposition, positions, self.comm, self.device)
+        self.plan = plan
+        n_own, n_ghost = plan.num_owned, plan.num_ghost
+        owned_pos = positions[plan.owned] + plan.owned_shift @ self.cell
+        ghost_pos = positions[plan.ghost_idx] + plan.ghost_shift @ self.cell
+        local_pos = np.concatenate([owned_pos, ghost_pos], axis=0)
+        local_types = np.concatenate([types[plan.owned], types[plan.ghost_idx]])
+        result = self.ev.prepare_local_graph(n_own, local_types, local_pos, halo)
+        self.generation = result["generation"]
+        self.num_edges = result["num_edges"]
+        dev = self.device
+        self.send_local = torch.from_numpy(plan.send_local).to(dev)
+        self.ghost_nodes = torch.arange(n_own, n_own + n_ghost, dtype=torch.int32, device=dev)
+        # ghost position = owner's current (wrapped-at-prepare) position + image offset relative to it
+        owner_shift_of_ghost = -self.decomposition.wrapped_fractional(positions)[1][plan.ghost_idx]
+        self.ghost_offset = torch.from_numpy((plan.ghost_shift - owner_shift_of_ghost) @ self.cell).to(dev)
+        self.owned_positions = torch.from_numpy(owned_pos).to(dev)
+        self.row = (self.ev.L_max + 1) ** 2 * self.ev.num_channels
+        return plan
+
+    def calculate(self, owned_positions=None):
+        """One evaluation.  ``owned_positions``: device tensor f64 [num_owned, 3] (defaults to the
+        positions given to ``prepare``).  Returns energy and stress of the whole system and the forces
+        on this rank's owned atoms (device tensor)."""
+        torch, ev, plan, comm = self.torch, self.ev, self.plan, self.comm
+        if owned_positions is None:
+            owned_positions = self.owned_positions
+        n_own, n_ghost = plan.num_owned, plan.num_ghost
+        sc, rc = plan.send_counts, plan.recv_counts
+        # ghost positions
+        ghost_pos = comm.all_to_all(owned_positions.index_select(0, self.send_local.long()), sc, rc) + self.ghost_offset
+        local_pos = torch.cat([owned_positions, ghost_pos], dim=0).contiguous()
+        ev.distributed_begin(self.generation, local_pos.data_ptr())
+        # forward halo: H1 rows of my owned atoms to the ranks that hold them as ghosts
+        send = torch.empty((len(self.send_local), self.row), dtype=torch.float32, device=self.device)
+        ev.halo_pack(0, self.send_local.data_ptr(), len(self.send_local), send.data_ptr())
+        recv = comm.all_to_all(send, sc, rc)
+        ev.halo_unpack(0, self.ghost_nodes.data_ptr(), n_ghost, recv.data_ptr(), False)
+        ev.distributed_continue()
+        # reverse halo: H1_adj rows of my ghosts back to their owners, summed there
+        back = torch.empty((n_ghost, self.row), dtype=torch.float32, device=self.device)
+        ev.halo_pack(1, self.ghost_nodes.data_ptr(), n_ghost, back.data_ptr())
+        got = comm.all_to_all(back, rc, sc)
+        ev.halo_unpack(1, self.send_local.data_ptr(), len(self.send_local), got.data_ptr(), True)
+        ev.distributed_finish()
+        # ghost forces back to the owners
+        _e, f_ptr, _v = ev.device_results()
+        n_local = n_own + n_ghost
+        forces = _as_tensor(torch, f_ptr, (n_local, 3), torch.float64, self.device)
+        got_f = comm.all_to_all(forces[n_own:].contiguous(), rc, sc)
+        ev.add_force_rows(self.send_local.data_ptr(), len(self.send_local), got_f.data_ptr())
+        totals = torch.empty(10, dtype=torch.float64, device=self.device)
+        totals[0] = ev.energy
+        e_ptr, _f, v_ptr = ev.device_results()
+        totals[1:] = _as_tensor(torch, v_ptr, (9,), torch.float64, self.device)
+        totals = comm.all_reduce_sum(totals)
+        host = totals.cpu().numpy()
+        return {"energy": float(host[0]), "stress": -host[1:].reshape(3, 3) / self.volume,
+                "forces": forces[:n_own], "owned": plan.owned}
+
+
+def _as_tensor(torch, ptr, shape, dtype, device):
+    """Zero-copy torch view of device memory owned by the evaluator."""
+    count = int(np.prod(shape))
+
+    class _Array:
+        __cuda_array_interface__ = {"shape": (count,), "typestr": "<f8" if dtype == torch.float64 else "<f4",
+                                    "data": (int(ptr), False), "version": 2}
+
+    return torch.as_tensor(_Array(), device=device).view(*shape)

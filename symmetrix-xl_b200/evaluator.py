@@ -61,6 +61,15 @@ SIGNATURES = {
     "sxb_get_stage": (ctypes.c_int, [_P, ctypes.c_char_p, _P, ctypes.c_int64, ctypes.POINTER(ctypes.c_int64)]),
     "sxb_launch_count": (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_int64)]),
     "sxb_last_compute_ms": (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_float)]),
+    "sxb_prepare_local_graph": (ctypes.c_int, [_P, ctypes.c_int32, ctypes.c_int32, _P, _P, ctypes.c_double,
+                                               ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_int64)]),
+    "sxb_distributed_begin": (ctypes.c_int, [_P, ctypes.c_uint64, _P]),
+    "sxb_distributed_continue": (ctypes.c_int, [_P]),
+    "sxb_distributed_finish": (ctypes.c_int, [_P]),
+    "sxb_halo_pack": (ctypes.c_int, [_P, ctypes.c_int32, _P, ctypes.c_int64, _P]),
+    "sxb_halo_unpack": (ctypes.c_int, [_P, ctypes.c_int32, _P, ctypes.c_int64, _P, ctypes.c_int32]),
+    "sxb_add_force_rows": (ctypes.c_int, [_P, _P, ctypes.c_int64, _P]),
+    "sxb_set_stream": (ctypes.c_int, [_P, _P]),
     "sxb_set_profiling": (ctypes.c_int, [_P, ctypes.c_int32]),
     "sxb_profile_entry": (ctypes.c_int, [_P, ctypes.c_int32, ctypes.c_char_p, ctypes.c_int32, ctypes.POINTER(ctypes.c_float),
                                          ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]),
@@ -138,7 +147,7 @@ class MACEB200:
         _check(self._lib.sxb_prepare_periodic_graph(self._h, node_types.size, node_types.ctypes.data, positions.ctypes.data,
                                                     cell.ctypes.data, inverse_cell.ctypes.data, float(neighbor_cutoff),
                                                     ctypes.byref(gen), ctypes.byref(edges)))
-        self._num_nodes, self._num_edges = int(node_types.size), int(edges.value)
+        self._num_nodes, self._num_edges, self._num_receivers = int(node_types.size), int(edges.value), int(node_types.size)
         return {"generation": int(gen.value), "num_edges": int(edges.value)}
 
     def _prepare_factorized_graph(self, num_nodes, node_types, num_neigh, neigh_indices, neigh_types=None,
@@ -158,12 +167,50 @@ class MACEB200:
         gen = ctypes.c_uint64()
         _check(self._lib.sxb_prepare_graph(self._h, int(num_nodes), node_types.ctypes.data, num_neigh.ctypes.data,
                                            neigh_indices.ctypes.data, sp, cp, ctypes.byref(gen)))
-        self._num_nodes, self._num_edges = int(num_nodes), int(neigh_indices.size)
+        self._num_nodes, self._num_edges, self._num_receivers = int(num_nodes), int(neigh_indices.size), int(num_nodes)
         return int(gen.value)
+
+    def prepare_local_graph(self, num_receivers, node_types, positions, neighbor_cutoff):
+        """Graph of an open node set whose first ``num_receivers`` nodes are receivers (owned atoms) and
+        whose other nodes are ghosts (reference: prepare_factorized_graph_device with num_receivers <
+        num_feature_nodes, libsymmetrix/source/mace_kokkos.hpp:672-697)."""
+        node_types, positions = _i32(node_types), _f64(positions).reshape(-1)
+        if positions.size != 3 * node_types.size:
+            raise ValueError("Neighbor graph input extents are inconsistent.")
+        gen, edges = ctypes.c_uint64(), ctypes.c_int64()
+        _check(self._lib.sxb_prepare_local_graph(self._h, int(num_receivers), node_types.size, node_types.ctypes.data,
+                                                 positions.ctypes.data, float(neighbor_cutoff), ctypes.byref(gen),
+                                                 ctypes.byref(edges)))
+        self._num_nodes, self._num_edges, self._num_receivers = int(node_types.size), int(edges.value), int(num_receivers)
+        return {"generation": int(gen.value), "num_edges": int(edges.value)}
+
+    # three-phase evaluation and halo rows (device pointers as integers)
+    def distributed_begin(self, generation, device_positions_ptr):
+        _check(self._lib.sxb_distributed_begin(self._h, int(generation), ctypes.c_void_p(device_positions_ptr)))
+
+    def distributed_continue(self):
+        _check(self._lib.sxb_distributed_continue(self._h))
+
+    def distributed_finish(self):
+        _check(self._lib.sxb_distributed_finish(self._h))
+
+    def halo_pack(self, which, indices_ptr, count, out_ptr):
+        _check(self._lib.sxb_halo_pack(self._h, int(which), ctypes.c_void_p(indices_ptr), int(count), ctypes.c_void_p(out_ptr)))
+
+    def halo_unpack(self, which, indices_ptr, count, in_ptr, accumulate):
+        _check(self._lib.sxb_halo_unpack(self._h, int(which), ctypes.c_void_p(indices_ptr), int(count), ctypes.c_void_p(in_ptr),
+                                         int(bool(accumulate))))
+
+    def add_force_rows(self, indices_ptr, count, in_ptr):
+        _check(self._lib.sxb_add_force_rows(self._h, ctypes.c_void_p(indices_ptr), int(count), ctypes.c_void_p(in_ptr)))
+
+    def set_stream(self, stream_ptr):
+        _check(self._lib.sxb_set_stream(self._h, ctypes.c_void_p(stream_ptr)))
 
     def graph(self, generation, with_shifts=True):
         """(first_neigh, sources, shifts) of the prepared graph in caller node order."""
-        first = np.zeros(self._num_nodes + 1, dtype=np.int32)
+        first = np.zeros(getattr(self, "_num_receivers", None) or self._num_nodes, dtype=np.int32)
+        first = np.zeros(len(first) + 1, dtype=np.int32)
         sources = np.zeros(self._num_edges, dtype=np.int32)
         shifts = np.zeros((self._num_edges, 3), dtype=np.int32) if with_shifts else None
         _check(self._lib.sxb_get_graph(self._h, int(generation), first.ctypes.data, sources.ctypes.data,
@@ -202,7 +249,7 @@ class MACEB200:
 
     @property
     def node_energies(self):
-        out = np.zeros(self._num_nodes, dtype=np.float64)
+        out = np.zeros(getattr(self, "_num_receivers", self._num_nodes), dtype=np.float64)
         _check(self._lib.sxb_get_node_energies(self._h, out.ctypes.data, out.size))
         return out
 

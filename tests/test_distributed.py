@@ -1,0 +1,149 @@
+"""Domain decomposition: exchange plan on CPU (gloo, 2 ranks), decomposed evaluation on the GPU."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _brute_ghosts(dec, positions, rank):
+    wf, wrap = dec.wrapped_fractional(positions)
+    owner = dec.owner(positions)
+    b = dec.brick_of_rank(rank)
+    lo = np.array([b[a] / dec.grid[a] for a in range(3)]) - dec.halo_frac
+    hi = np.array([(b[a] + 1) / dec.grid[a] for a in range(3)]) + dec.halo_frac
+    out = set()
+    for i in range(len(positions)):
+        for sx in range(-2, 3):
+            for sy in range(-2, 3):
+                for sz in range(-2, 3):
+                    f = wf[i] + np.array([sx, sy, sz])
+                    if ((f >= lo) & (f < hi)).all() and not (owner[i] == rank and (sx, sy, sz) == (0, 0, 0)):
+                        out.add((i, sx - wrap[i, 0], sy - wrap[i, 1], sz - wrap[i, 2]))
+    return out
+
+
+@pytest.mark.parametrize("grid", [(1, 1, 1), (2, 1, 1), (2, 2, 1), (2, 2, 2)])
+def test_brick_selection_covers_every_atom_and_image(pkg, grid):
+    pos, cell, types = pkg.modelgen.srtio3((4, 3, 3), 0.05, 3)
+    pos = pos + np.array([0.3, -0.2, 40.0])          # atoms outside the home cell
+    dec = pkg.distributed.BrickDecomposition(cell, grid, 6.5)
+    owned_all = []
+    for rank in range(dec.world):
+        owned, gidx, gshift, oshift, owner = dec.select(pos, rank)
+        owned_all.append(owned)
+        got = set(zip(gidx.tolist(), *gshift.T.tolist()))
+        assert len(got) == len(gidx)
+        assert got == _brute_ghosts(dec, pos, rank)
+        assert (np.diff(owner[gidx]) >= 0).all()      # ordered by owner rank
+        # every neighbor within the halo of an owned atom is owned or a ghost
+        local = np.concatenate([pos[owned] + oshift @ cell, pos[gidx] + gshift @ cell])
+        from oracle import neighbor
+
+        first, src, shifts = neighbor.build_neighbor_graph(pos, cell, 6.5)
+        for i in owned[:5]:
+            li = np.flatnonzero(owned == i)[0]
+            d = np.linalg.norm(local - local[li], axis=1)
+            assert (d <= 6.5).sum() - 1 == first[i + 1] - first[i]
+    allowned = np.concatenate(owned_all)
+    assert sorted(allowned.tolist()) == list(range(len(pos)))
+
+
+def _plan_worker(rank, world, port, out_dir):
+    import torch
+    import torch.distributed as dist
+
+    sys.path.insert(0, str(ROOT))
+    import __graft_entry__ as graft
+
+    pkg = graft.load_package()
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    pos, cell, types = pkg.modelgen.srtio3((4, 2, 2), 0.05, 5)
+    dec = pkg.distributed.BrickDecomposition(cell, pkg.distributed.GRIDS[world], 6.5)
+    comm = pkg.distributed.make_comm()
+    plan = pkg.distributed.ExchangePlan(dec, pos, comm, "cpu")
+    # forward exchange of positions reproduces the ghost positions
+    owned_pos = torch.from_numpy(pos[plan.owned] + plan.owned_shift @ cell)
+    got = comm.all_to_all(owned_pos[torch.from_numpy(plan.send_local).long()], plan.send_counts, plan.recv_counts).numpy()
+    wrap = dec.wrapped_fractional(pos)[1]
+    want = pos[plan.ghost_idx] - wrap[plan.ghost_idx] @ cell
+    ok_forward = np.abs(got - want).max() < 1e-12
+    # reverse exchange: every ghost returns 1.0 to its owner; owners sum how often they are ghosts elsewhere
+    back = comm.all_to_all(torch.ones(plan.num_ghost, 1, dtype=torch.float64), plan.recv_counts, plan.send_counts).numpy()
+    tally = np.zeros(len(pos))
+    np.add.at(tally, plan.owned[plan.send_local], back[:, 0])
+    total = torch.from_numpy(tally)
+    comm.all_reduce_sum(total)
+    ghosts = torch.tensor([float(plan.num_ghost)], dtype=torch.float64)
+    comm.all_reduce_sum(ghosts)
+    ok_reverse = abs(total.sum().item() - ghosts.item()) < 1e-9
+    np.save(Path(out_dir) / f"r{rank}.npy", np.array([ok_forward, ok_reverse, plan.num_owned, plan.num_ghost]))
+    dist.destroy_process_group()
+
+
+def test_exchange_plan_two_ranks_gloo(tmp_path):
+    import torch.multiprocessing as mp
+
+    port = 29500 + os.getpid() % 2000
+    mp.spawn(_plan_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = np.load(tmp_path / "r0.npy"), np.load(tmp_path / "r1.npy")
+    assert r0[0] and r0[1] and r1[0] and r1[1]
+    assert r0[2] + r1[2] == 4 * 2 * 2 * 5
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("arch,cells", [("small", (3, 3, 3)), ("medium", (3, 2, 2))])
+def test_single_rank_decomposition_matches_periodic_evaluation(pkg, model_path, arch, cells):
+    """One rank whose ghosts are the periodic images of its own atoms: the three-phase path with
+    halo pack/unpack must reproduce the periodic single-GPU result."""
+    path = model_path(arch)
+    pos, cell, types = pkg.modelgen.srtio3(cells, 0.05, 8)
+    ref_out = pkg.Calculator(path, skin=0.5).calculate(pos, cell, types)
+    calc = pkg.distributed.DistributedCalculator(path, pkg.MACEB200, skin=0.5, device=0)
+    plan = calc.prepare(pos, cell, types)
+    assert plan.num_owned == len(pos) and plan.num_ghost > 0
+    for _ in range(2):                                    # twice: state must reset between evaluations
+        out = calc.calculate()
+        forces = out["forces"].cpu().numpy()
+        assert abs(out["energy"] - ref_out["energy"]) / len(pos) <= 1e-6
+        assert np.abs(forces - ref_out["forces"][out["owned"]]).max() <= 1e-5
+        assert np.abs(out["stress"] - ref_out["stress"]).max() <= 1e-7
+
+
+@pytest.mark.gpu
+def test_distributed_phase_order_is_enforced(pkg, model_path):
+    import torch
+
+    ev = pkg.MACEB200(model_path("small"))
+    pos, cell, types = pkg.modelgen.srtio3(2, 0.05, 1)
+    res = ev.prepare_local_graph(len(pos), types, pos, 5.5)
+    with pytest.raises(ValueError):
+        ev.distributed_continue()
+    d = torch.from_numpy(pos.reshape(-1).copy()).cuda()
+    ev.distributed_begin(res["generation"], d.data_ptr())
+    with pytest.raises(ValueError):
+        ev.distributed_finish()                        # continue was skipped: phase resets
+    with pytest.raises(ValueError):
+        ev.distributed_continue()
+
+
+@pytest.mark.gpu
+def test_two_rank_decomposition_matches_single_gpu(pkg, tmp_path):
+    """Two processes on two GPUs (NCCL) against the periodic single-GPU evaluation."""
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = tmp_path / "dd.json"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29611", str(ROOT / "tests" / "dd_worker.py"), str(out)]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    subprocess.run(cmd, check=True, cwd=str(ROOT), env=env, timeout=600)
+    import json
+
+    r = json.loads(out.read_text())
+    assert r["dE_per_atom"] <= 1e-6 and r["dF"] <= 1e-5 and r["dS"] <= 1e-7
