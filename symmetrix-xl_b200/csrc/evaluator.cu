@@ -849,7 +849,11 @@ void Evaluator::distributed_finish()
     SXB_CUDA(cudaSetDevice(device_));
     phase_ = 0;
     run_pipeline(4);
-    finish_compute();
+    // no host synchronisation here: the caller still has ghost forces to exchange on this stream;
+    // synchronize() fetches the totals and checks the device status word
+    SXB_CUDA(cudaEventRecord(event_end_, stream_));
+    pending_finish_ = true;
+    have_results_ = true;
 }
 
 namespace {
@@ -942,6 +946,12 @@ void Evaluator::set_stream(cudaStream_t stream)
 void Evaluator::synchronize()
 {
     SXB_CUDA(cudaSetDevice(device_));
+    if (pending_finish_) {
+        pending_finish_ = false;
+        have_results_ = false;
+        finish_compute();
+        return;
+    }
     SXB_CUDA(cudaStreamSynchronize(stream_));
 }
 
@@ -992,6 +1002,7 @@ void Evaluator::get_stress(double volume, double* out9)
 double Evaluator::energy() const
 {
     require_results();
+    if (pending_finish_) throw std::logic_error("Call synchronize() after distributed_finish before reading host results.");
     return host_totals_[0];
 }
 

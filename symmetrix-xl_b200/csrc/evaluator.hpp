@@ -116,6 +116,7 @@ private:
     int num_nodes_ = 0, num_receivers_ = 0;
     int phase_ = 0;
     bool owns_stream_ = true;
+    bool pending_finish_ = false;
     long num_edges_ = 0;
     bool has_shifts_ = false;
     DeviceBuffer<int> first_caller_, sources_caller_, shifts_caller_;

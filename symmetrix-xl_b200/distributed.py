@@ -232,12 +232,11 @@ class DistributedCalculator:
         forces = _as_tensor(torch, f_ptr, (n_local, 3), torch.float64, self.device)
         got_f = comm.all_to_all(forces[n_own:].contiguous(), rc, sc)
         ev.add_force_rows(self.send_local.data_ptr(), len(self.send_local), got_f.data_ptr())
-        totals = torch.empty(10, dtype=torch.float64, device=self.device)
-        totals[0] = ev.energy
-        e_ptr, _f, v_ptr = ev.device_results()
-        totals[1:] = _as_tensor(torch, v_ptr, (9,), torch.float64, self.device)
-        totals = comm.all_reduce_sum(totals)
+        # energy and virial of this rank sit next to each other on the device: [E, 9 virial components]
+        e_ptr, _f, _v = ev.device_results()
+        totals = comm.all_reduce_sum(_as_tensor(torch, e_ptr, (10,), torch.float64, self.device).clone())
         host = totals.cpu().numpy()
+        ev.synchronize()        # fetches the status word of the evaluation (raises on a device-side error)
         return {"energy": float(host[0]), "stress": -host[1:].reshape(3, 3) / self.volume,
                 "forces": forces[:n_own], "owned": plan.owned}
 
