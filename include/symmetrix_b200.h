@@ -195,6 +195,15 @@ int sxb_halo_unpack(sxb_evaluator* evaluator, int32_t which, const int32_t* devi
 int sxb_add_force_rows(sxb_evaluator* evaluator, const int32_t* device_indices, int64_t count, const double* device_in);
 int sxb_set_stream(sxb_evaluator* evaluator, void* stream);
 
+/* Tiled streaming (the reference's fixed-workspace dual-layer plan, allow_fixed_workspace:
+ * libsymmetrix/source/mace_kokkos_evaluate.cpp:755-1148, workspace
+ * mace_kokkos_factorized_lifecycle.cpp:1353-1569): receivers are processed in tiles of
+ * `receivers_per_tile` with one reusable workspace in three sweeps (layer 0 -> H1; layer 1 forward
+ * and its fused gradient; layer-0 forward recomputed, then the layer-0 gradient).  Graph-wide state
+ * is H1, H1_adj, M0, the readout adjoint and the outputs only.  0 switches tiling off.  The setting
+ * invalidates the prepared graph; prepare again afterwards. */
+int sxb_set_tile_size(sxb_evaluator* evaluator, int32_t receivers_per_tile);
+
 /* Per-stage device times of the last compute (CUDA events on the evaluator's stream around each
  * kernel group), collected only while profiling is enabled; counterpart of the reference's per-stage
  * counters (factorized_last_evaluation_ms ..., libsymmetrix/source/mace_kokkos.hpp:1431-1454).

@@ -316,6 +316,11 @@ int sxb_add_force_rows(sxb_evaluator* ev, const int32_t* device_indices, int64_t
     });
 }
 
+int sxb_set_tile_size(sxb_evaluator* ev, int32_t receivers_per_tile)
+{
+    return guarded([&] { require(ev, "evaluator"); ev->impl.set_tile_size(receivers_per_tile); });
+}
+
 int sxb_set_stream(sxb_evaluator* ev, void* stream)
 {
     return guarded([&] { require(ev, "evaluator"); ev->impl.set_stream(static_cast<cudaStream_t>(stream)); });

@@ -223,13 +223,13 @@ __device__ __forceinline__ float cubic_derivative(float c1, float c2, float c3, 
 // kC > 0 fixes the channel count at compile time (all strides become immediates).
 template <int kC>
 __global__ void __launch_bounds__(kC > 0 ? kC : 256)
-l0_forward_kernel(int num_nodes, int C_runtime, const int* __restrict__ first, const int* __restrict__ sources,
+l0_forward_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict__ first, const int* __restrict__ sources,
                   const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype, int num_active,
                   SplineGrid grid, const float* __restrict__ table, float* __restrict__ A0)
 {
     __shared__ ChunkState<false> s;
     const int C = kC > 0 ? kC : C_runtime;
-    const int i = blockIdx.x;
+    const int local = blockIdx.x, i = node0 + local;   // tile-local and graph-wide receiver index
     const int k = threadIdx.x;
     const int F = 4 * C;
     const int type_i = atype[i];
@@ -262,7 +262,7 @@ l0_forward_kernel(int num_nodes, int C_runtime, const int* __restrict__ first, c
             for (int lm = 9; lm < 16; ++lm) acc[lm] = fmaf(R[3], y[lm], acc[lm]);
         }
     }
-    float* out = A0 + static_cast<size_t>(i) * 16 * C + k;
+    float* out = A0 + static_cast<size_t>(local) * 16 * C + k;
 #pragma unroll
     for (int lm = 0; lm < 16; ++lm) out[lm * C] = acc[lm];
 }
@@ -369,14 +369,14 @@ __device__ __forceinline__ void finish_receiver_forces(ForceScratch<kMaxWarps>& 
 // Layer 0 reverse: f_ij -= sum_{lm,k} A0_adj_i[lm,k] * (rhat S0' Y + S0 grad Y).
 template <int kC>
 __global__ void __launch_bounds__(kC > 0 ? kC : 256)
-l0_reverse_kernel(int num_nodes, int C_runtime, const int* __restrict__ first, const int* __restrict__ sources,
+l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict__ first, const int* __restrict__ sources,
                   const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype, int num_active,
                   SplineGrid grid, const float* __restrict__ table, const float* __restrict__ A0_adj, ForceOutputs out)
 {
     __shared__ ChunkState<true> s;
     __shared__ ForceScratch<8> fs;
     const int C = kC > 0 ? kC : C_runtime;
-    const int i = blockIdx.x;
+    const int local = blockIdx.x, i = node0 + local;   // tile-local and graph-wide receiver index
     const int k = threadIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, num_warps = blockDim.x >> 5;
     const int F = 4 * C;
@@ -385,7 +385,7 @@ l0_reverse_kernel(int num_nodes, int C_runtime, const int* __restrict__ first, c
     if (threadIdx.x < 3) fs.receiver[threadIdx.x] = 0.0;
     if (threadIdx.x < 9) fs.virial[threadIdx.x] = 0.0;
     float adj[16];
-    const float* in = A0_adj + static_cast<size_t>(i) * 16 * C + k;
+    const float* in = A0_adj + static_cast<size_t>(local) * 16 * C + k;
 #pragma unroll
     for (int lm = 0; lm < 16; ++lm) adj[lm] = in[lm * C];
     for (int chunk = begin; chunk < end; chunk += kEdgeChunk) {
@@ -452,7 +452,7 @@ l0_reverse_kernel(int num_nodes, int C_runtime, const int* __restrict__ first, c
 #define SXB_DEFINE_L1_KERNELS(NAME)                                                                                  \
     template <int kC>                                                                                                \
     __global__ void __launch_bounds__(kC > 0 ? kC : 256)                                                             \
-    l1_forward_kernel_##NAME(int num_nodes, int C_runtime, const int* __restrict__ first,                            \
+    l1_forward_kernel_##NAME(int num_nodes, int node0, int C_runtime, const int* __restrict__ first,                            \
                              const int* __restrict__ sources, const EdgeGeom* __restrict__ geom,                     \
                              const unsigned char* __restrict__ atype, SplineGrid grid,                               \
                              const float* __restrict__ table, const float* __restrict__ H1,                          \
@@ -462,7 +462,7 @@ l0_reverse_kernel(int num_nodes, int C_runtime, const int* __restrict__ first, c
         constexpr int NE = SXB_##NAME##_NUM_LME;                                                                     \
         __shared__ ChunkState<false> s;                                                                              \
         const int C = kC > 0 ? kC : C_runtime;                                                                       \
-        const int i = blockIdx.x;                                                                                    \
+        const int local = blockIdx.x, i = node0 + local;                                                             \
         const int k = threadIdx.x;                                                                                   \
         const int F = NP * C;                                                                                        \
         const int begin = first[i], end = first[i + 1];                                                              \
@@ -492,13 +492,13 @@ l0_reverse_kernel(int num_nodes, int C_runtime, const int* __restrict__ first, c
         float out_lme[NE];                                                                                           \
         _Pragma("unroll") for (int q = 0; q < NE; ++q) out_lme[q] = 0.0f;                                            \
         SXB_##NAME##_TERMS(SXB_TERM_FORWARD)                                                                         \
-        float* out = Phi1 + static_cast<size_t>(i) * NE * C + k;                                                     \
+        float* out = Phi1 + static_cast<size_t>(local) * NE * C + k;                                                     \
         _Pragma("unroll") for (int q = 0; q < NE; ++q) out[q * C] = out_lme[q];                                      \
     }                                                                                                                \
                                                                                                                      \
     template <int kC>                                                                                                \
     __global__ void __launch_bounds__(kC > 0 ? kC : 256)                                                             \
-    l1_reverse_kernel_##NAME(int num_nodes, int C_runtime, const int* __restrict__ first,                            \
+    l1_reverse_kernel_##NAME(int num_nodes, int node0, int C_runtime, const int* __restrict__ first,                            \
                              const int* __restrict__ sources, const EdgeGeom* __restrict__ geom,                     \
                              const unsigned char* __restrict__ atype, SplineGrid grid,                               \
                              const float* __restrict__ table, const float* __restrict__ H1,                          \
@@ -510,7 +510,7 @@ l0_reverse_kernel(int num_nodes, int C_runtime, const int* __restrict__ first, c
         __shared__ ChunkState<true> s;                                                                               \
         __shared__ ForceScratch<8> fs;                                                                               \
         const int C = kC > 0 ? kC : C_runtime;                                                                       \
-        const int i = blockIdx.x;                                                                                    \
+        const int local = blockIdx.x, i = node0 + local;                                                             \
         const int k = threadIdx.x;                                                                                   \
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, num_warps = blockDim.x >> 5;                     \
         const int F = NP * C;                                                                                        \
@@ -520,7 +520,7 @@ l0_reverse_kernel(int num_nodes, int C_runtime, const int* __restrict__ first, c
         float adj[NR];                                                                                               \
         {                                                                                                            \
             float dphi[NE];                                                                                          \
-            const float* in = dPhi1 + static_cast<size_t>(i) * NE * C + k;                                           \
+            const float* in = dPhi1 + static_cast<size_t>(local) * NE * C + k;                                           \
             _Pragma("unroll") for (int q = 0; q < NE; ++q) dphi[q] = in[q * C];                                      \
             _Pragma("unroll") for (int r_ = 0; r_ < NR; ++r_) adj[r_] = 0.0f;                                        \
             SXB_##NAME##_TERMS(SXB_TERM_TRANSPOSE)                                                                   \

@@ -112,15 +112,16 @@ __device__ __forceinline__ float warp_reduce3_transposed(float a, float b, float
 // ---------------------------------------------------------------------------------------------
 template <int kVec>
 __global__ void __launch_bounds__(32 * kWarpsPerBlock)
-l0_forward_warp_kernel(int num_nodes, const int* __restrict__ first, const int* __restrict__ sources,
+l0_forward_warp_kernel(int num_nodes, int node0, const int* __restrict__ first, const int* __restrict__ sources,
                        const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype, int num_active,
                        SplineGrid grid, const float* __restrict__ table, float* __restrict__ A0)
 {
     constexpr int C = 32 * kVec, F = 4 * C;
     __shared__ WarpChunk<false> chunks[kWarpsPerBlock];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int i = blockIdx.x * kWarpsPerBlock + warp;
-    if (i >= num_nodes) return;
+    const int local = blockIdx.x * kWarpsPerBlock + warp;   // receiver inside the tile
+    if (local >= num_nodes) return;
+    const int i = node0 + local;                            // graph-wide receiver index
     WarpChunk<false>& s = chunks[warp];
     const int k = lane * kVec;
     const int type_i = atype[i];
@@ -158,7 +159,7 @@ l0_forward_warp_kernel(int num_nodes, const int* __restrict__ first, const int* 
             }
         }
     }
-    float* out = A0 + static_cast<size_t>(i) * 16 * C + k;
+    float* out = A0 + static_cast<size_t>(local) * 16 * C + k;
 #pragma unroll
     for (int lm = 0; lm < 16; ++lm) VecLoad<kVec>::store(out + lm * C, acc[lm]);
 }
@@ -166,22 +167,23 @@ l0_forward_warp_kernel(int num_nodes, const int* __restrict__ first, const int* 
 // ---------------------------------------------------------------------------------------------
 template <int kVec>
 __global__ void __launch_bounds__(32 * kWarpsPerBlock)
-l0_reverse_warp_kernel(int num_nodes, const int* __restrict__ first, const int* __restrict__ sources,
+l0_reverse_warp_kernel(int num_nodes, int node0, const int* __restrict__ first, const int* __restrict__ sources,
                        const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype, int num_active,
                        SplineGrid grid, const float* __restrict__ table, const float* __restrict__ A0_adj, ForceOutputs out)
 {
     constexpr int C = 32 * kVec, F = 4 * C;
     __shared__ WarpChunk<true> chunks[kWarpsPerBlock];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int i = blockIdx.x * kWarpsPerBlock + warp;
-    if (i >= num_nodes) return;
+    const int local = blockIdx.x * kWarpsPerBlock + warp;   // receiver inside the tile
+    if (local >= num_nodes) return;
+    const int i = node0 + local;                            // graph-wide receiver index
     WarpChunk<true>& s = chunks[warp];
     const int k = lane * kVec;
     const int type_i = atype[i];
     const int begin = first[i], end = first[i + 1];
     float adj[16][kVec];
     {
-        const float* in = A0_adj + static_cast<size_t>(i) * 16 * C + k;
+        const float* in = A0_adj + static_cast<size_t>(local) * 16 * C + k;
 #pragma unroll
         for (int lm = 0; lm < 16; ++lm) VecLoad<kVec>::load(in + lm * C, adj[lm]);
     }

@@ -218,21 +218,24 @@ void Evaluator::install_graph(int num_receivers, int num_nodes, const std::vecto
     SXB_CUDA(cudaGetLastError());
 
     // work buffers
+    // graph-wide state: H1, H1_adj (all nodes), M0, H2_adj, energies (receivers), forces (all nodes);
+    // everything else lives in a workspace sized for one tile of receivers and is reused tile by tile
     const std::size_t N = num_receivers, ALL = num_nodes, C = model_.channels, NH = model_.num_hidden, NE = model_.num_lme;
+    const std::size_t T = static_cast<std::size_t>(tile_capacity());
     geom_.reserve(num_edges);
-    A0_.reserve(N * 16 * C);
-    A0_adj_.reserve(N * 16 * C);
+    A0_.reserve(T * 16 * C);
+    A0_adj_.reserve(T * 16 * C);
     M0_.reserve(N * NH * C);
-    M0_adj_.reserve(N * NH * C);
+    M0_adj_.reserve(T * NH * C);
     H1_.reserve(ALL * NH * C);
     H1_adj_.reserve(ALL * NH * C);
-    Phi1_.reserve(N * NE * C);
-    dPhi1_.reserve(N * NE * C);
-    A1_.reserve(N * 16 * C);
-    A1_adj_.reserve(N * 16 * C);
-    M1_.reserve(N * C);
-    M1_adj_.reserve(N * C);
-    H2_.reserve(N * C);
+    Phi1_.reserve(T * NE * C);
+    dPhi1_.reserve(T * NE * C);
+    A1_.reserve(T * 16 * C);
+    A1_adj_.reserve(T * 16 * C);
+    M1_.reserve(T * C);
+    M1_adj_.reserve(T * C);
+    H2_.reserve(T * C);
     H2_adj_.reserve(N * C);
     node_energies_.reserve(N);
     node_energies_out_.reserve(N);
@@ -568,9 +571,11 @@ void Evaluator::launch_tc(const std::vector<TcCall>& calls)
 // finish_factorized_distributed_evaluation, libsymmetrix/source/mace_kokkos_evaluate.cpp:1658-2101).
 void Evaluator::run_pipeline(int phases)
 {
-    const int N = num_receivers_, ALL = num_nodes_, C = model_.channels, NH = model_.num_hidden, NE = model_.num_lme;
+    const int R = num_receivers_, ALL = num_nodes_, C = model_.channels, NH = model_.num_hidden, NE = model_.num_lme;
     const int n_active = static_cast<int>(active_types_.size());
-    const dim3 poly_grid(blocks_for(N, kPolyWarps), C / 32);
+    const int tile_cap = tile_capacity();
+    const bool tiled = tile_cap < R;
+    const std::size_t rowH = static_cast<std::size_t>(NH) * C;
     const RowMap scalar_rows{static_cast<long>(NH) * C, C, 0, 1};
     const RowMap flat_rows{static_cast<long>(C), C, 0, 1};
     ForceOutputs fo;
@@ -578,177 +583,204 @@ void Evaluator::run_pipeline(int phases)
     fo.virial_slots = virial_slots_.ptr;
     fo.edge_forces = keep_edge_forces_ ? edge_forces_.ptr : nullptr;
     fo.accumulate_edge = 0;
-    if (phases & 1) {
-    spans_.clear();
-    events_used_ = 0;
-    SXB_CUDA(cudaMemsetAsync(forces_.ptr, 0, sizeof(double) * 3 * ALL, stream_));
-    SXB_CUDA(cudaMemsetAsync(H1_adj_.ptr, 0, sizeof(float) * static_cast<std::size_t>(ALL) * NH * C, stream_));
-    SXB_CUDA(cudaMemsetAsync(energy_slots_.ptr, 0, sizeof(double) * kVirialSlots, stream_));
-    SXB_CUDA(cudaMemsetAsync(virial_slots_.ptr, 0, sizeof(double) * kVirialSlots * 9, stream_));
+    const int warp_threads = 32 * kWarpsPerBlock;
 
-    // layer 0 forward
-    span_begin("l0_forward");
-    {
-        const int warp_grid = blocks_for(N, kWarpsPerBlock), warp_threads = 32 * kWarpsPerBlock;
+    // launch helpers for one tile of T receivers starting at t0 (tile tensors are indexed from 0)
+    auto l0_forward = [&](int t0, int T) {
+        const int warp_grid = blocks_for(T, kWarpsPerBlock);
         if (C == 128)
-            l0_forward_warp_kernel<4><<<warp_grid, warp_threads, 0, stream_>>>(N, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
+            l0_forward_warp_kernel<4><<<warp_grid, warp_threads, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
         else if (C == 64)
-            l0_forward_warp_kernel<2><<<warp_grid, warp_threads, 0, stream_>>>(N, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
+            l0_forward_warp_kernel<2><<<warp_grid, warp_threads, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
         else if (C == 32)
-            l0_forward_warp_kernel<1><<<warp_grid, warp_threads, 0, stream_>>>(N, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
+            l0_forward_warp_kernel<1><<<warp_grid, warp_threads, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
         else
-            l0_forward_kernel<0><<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
-    }
-    launches_ += 1;
-    span_end();
-    span_begin("m0_forward");
-    if (model_.shape_id == 0)
-        m0_forward_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A0_.ptr, element_.ptr, m0_weights_.ptr, M0_.ptr);
-    else
-        m0_forward_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A0_.ptr, element_.ptr, m0_weights_.ptr, M0_.ptr);
-    launches_ += 1;
-    span_end();
-    // H1_il = M0_il W_l
-    span_begin("gemm_h1");
-    {
-        std::vector<TcCall> calls;
-        for (int l = 0; l <= model_.hidden_l_max; ++l) {
-            const RowMap rows{static_cast<long>(NH) * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
-            calls.push_back({M0_.ptr, rows, &s_h1_[l], false, H1_.ptr, rows, 0, N, false, nullptr});
+            l0_forward_kernel<0><<<T, C, 0, stream_>>>(T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
+        launches_ += 1;
+    };
+    // per-element node ranges intersected with the tile
+    auto for_type_ranges = [&](int t0, int T, auto&& body) {
+        for (int a = 0; a < n_active; ++a) {
+            const int begin = std::max(type_begin_[a], t0), end = std::min(type_begin_[a + 1], t0 + T);
+            if (end > begin) body(a, begin, end - begin);
         }
-        launch_tc(calls);
-    }
-    span_end();
+    };
+
+    if (phases & 1) {
+        spans_.clear();
+        events_used_ = 0;
+        SXB_CUDA(cudaMemsetAsync(forces_.ptr, 0, sizeof(double) * 3 * ALL, stream_));
+        SXB_CUDA(cudaMemsetAsync(H1_adj_.ptr, 0, sizeof(float) * static_cast<std::size_t>(ALL) * rowH, stream_));
+        SXB_CUDA(cudaMemsetAsync(energy_slots_.ptr, 0, sizeof(double) * kVirialSlots, stream_));
+        SXB_CUDA(cudaMemsetAsync(virial_slots_.ptr, 0, sizeof(double) * kVirialSlots * 9, stream_));
+        for (int t0 = 0; t0 < R; t0 += tile_cap) {
+            const int T = std::min(tile_cap, R - t0);
+            span_begin("l0_forward");
+            l0_forward(t0, T);
+            span_end();
+            span_begin("m0_forward");
+            const dim3 poly_grid(blocks_for(T, kPolyWarps), C / 32);
+            float* m0 = M0_.ptr + t0 * rowH;
+            if (model_.shape_id == 0)
+                m0_forward_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(T, C, A0_.ptr, element_.ptr + t0, m0_weights_.ptr, m0);
+            else
+                m0_forward_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(T, C, A0_.ptr, element_.ptr + t0, m0_weights_.ptr, m0);
+            launches_ += 1;
+            span_end();
+            // H1_il = M0_il W_l
+            span_begin("gemm_h1");
+            std::vector<TcCall> calls;
+            for (int l = 0; l <= model_.hidden_l_max; ++l) {
+                const RowMap rows{static_cast<long>(NH) * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
+                calls.push_back({m0, rows, &s_h1_[l], false, H1_.ptr + t0 * rowH, rows, 0, T, false, nullptr});
+            }
+            launch_tc(calls);
+            span_end();
+        }
     }
     if (phases & 2) {
-    // layer 1 forward
-    span_begin("l1_forward");
-    if (model_.shape_id == 0)
-        SXB_LAUNCH_BY_CHANNELS(l1_forward_kernel_S0, C, N, stream_, N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
-                               r1_table_.ptr, H1_.ptr, coupling_, Phi1_.ptr);
-    else
-        SXB_LAUNCH_BY_CHANNELS(l1_forward_kernel_S1, C, N, stream_, N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
-                               r1_table_.ptr, H1_.ptr, coupling_, Phi1_.ptr);
-    launches_ += 1;
-    span_end();
-    // A1_il = Phi1_il W_l
-    span_begin("gemm_a1");
-    {
-        std::vector<TcCall> calls;
-        for (int l = 0; l <= model_.l_max; ++l) {
-            const int eta = model_.eta[l];
-            const RowMap a_rows{static_cast<long>(NE) * C, static_cast<long>(eta) * C, static_cast<long>(model_.group_begin[l]) * C, 2 * l + 1};
-            const RowMap c_rows{16L * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
-            calls.push_back({Phi1_.ptr, a_rows, &s_a1_[l], false, A1_.ptr, c_rows, 0, N, false, nullptr});
+        for (int t0 = 0; t0 < R; t0 += tile_cap) {
+            const int T = std::min(tile_cap, R - t0);
+            const dim3 poly_grid(blocks_for(T, kPolyWarps), C / 32);
+            span_begin("l1_forward");
+            if (model_.shape_id == 0)
+                SXB_LAUNCH_BY_CHANNELS(l1_forward_kernel_S0, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
+                                       r1_table_.ptr, H1_.ptr, coupling_, Phi1_.ptr);
+            else
+                SXB_LAUNCH_BY_CHANNELS(l1_forward_kernel_S1, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
+                                       r1_table_.ptr, H1_.ptr, coupling_, Phi1_.ptr);
+            launches_ += 1;
+            span_end();
+            // A1_il = Phi1_il W_l
+            span_begin("gemm_a1");
+            {
+                std::vector<TcCall> calls;
+                for (int l = 0; l <= model_.l_max; ++l) {
+                    const int eta = model_.eta[l];
+                    const RowMap a_rows{static_cast<long>(NE) * C, static_cast<long>(eta) * C, static_cast<long>(model_.group_begin[l]) * C, 2 * l + 1};
+                    const RowMap c_rows{16L * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
+                    calls.push_back({Phi1_.ptr, a_rows, &s_a1_[l], false, A1_.ptr, c_rows, 0, T, false, nullptr});
+                }
+                launch_tc(calls);
+            }
+            span_end();
+            span_begin("m1_forward");
+            if (model_.shape_id == 0)
+                m1_forward_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_.ptr);
+            else
+                m1_forward_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_.ptr);
+            launches_ += 1;
+            span_end();
+            // H2 = xs T_element + M1 W
+            span_begin("gemm_h2");
+            {
+                std::vector<TcCall> calls;
+                for_type_ranges(t0, T, [&](int a, int begin, int count) {
+                    calls.push_back({M0_.ptr + begin * rowH, scalar_rows, &s_h2_skip_[active_types_[a]], false,
+                                     H2_.ptr + static_cast<std::size_t>(begin - t0) * C, flat_rows, 0, count, false, nullptr});
+                });
+                launch_tc(calls);
+                launch_tc({{M1_.ptr, flat_rows, &s_h2_m1_, false, H2_.ptr, flat_rows, 0, T, true, nullptr}});
+            }
+            span_end();
+            span_begin("readout");
+            readout_kernel<<<blocks_for(static_cast<long>(T) * 32, 256), 256, 0, stream_>>>(
+                T, C, model_.readout2_hidden, model_.readout2_scale, M0_.ptr + t0 * rowH, NH, H2_.ptr, element_.ptr + t0,
+                atomic_energies_.ptr, readout1_.ptr, readout2_w1_.ptr, readout2_w2_.ptr, node_energies_.ptr + t0,
+                H2_adj_.ptr + static_cast<std::size_t>(t0) * C, energy_slots_.ptr);
+            launches_ += 1;
+            span_end();
+            // reverse
+            span_begin("gemm_h2_reverse");
+            launch_tc({{H2_adj_.ptr + static_cast<std::size_t>(t0) * C, flat_rows, &s_h2_m1_, true, M1_adj_.ptr, flat_rows, 0, T, false, nullptr}});
+            span_end();
+            span_begin("m1_reverse");
+            if (model_.shape_id == 0)
+                m1_reverse_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_adj_.ptr, A1_adj_.ptr);
+            else
+                m1_reverse_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_adj_.ptr, A1_adj_.ptr);
+            launches_ += 1;
+            span_end();
+            span_begin("gemm_a1_reverse");
+            {
+                std::vector<TcCall> calls;
+                for (int l = 0; l <= model_.l_max; ++l) {
+                    const int eta = model_.eta[l];
+                    const RowMap a_rows{16L * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
+                    const RowMap c_rows{static_cast<long>(NE) * C, static_cast<long>(eta) * C, static_cast<long>(model_.group_begin[l]) * C, 2 * l + 1};
+                    calls.push_back({A1_adj_.ptr, a_rows, &s_a1_[l], true, dPhi1_.ptr, c_rows, 0, T, false, nullptr});
+                }
+                launch_tc(calls);
+            }
+            span_end();
+            span_begin("l1_reverse");
+            if (model_.shape_id == 0)
+                SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S0, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
+                                       r1_table_.ptr, H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
+            else
+                SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S1, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
+                                       r1_table_.ptr, H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
+            launches_ += 1;
+            span_end();
         }
-        launch_tc(calls);
-    }
-    span_end();
-    span_begin("m1_forward");
-    if (model_.shape_id == 0)
-        m1_forward_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A1_.ptr, element_.ptr, m1_weights_.ptr, M1_.ptr);
-    else
-        m1_forward_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A1_.ptr, element_.ptr, m1_weights_.ptr, M1_.ptr);
-    launches_ += 1;
-    span_end();
-    // H2 = xs T_element + M1 W
-    span_begin("gemm_h2");
-    {
-        std::vector<TcCall> calls;
-        for (int a = 0; a < n_active; ++a) {
-            const int begin = type_begin_[a], count = type_begin_[a + 1] - begin;
-            calls.push_back({M0_.ptr, scalar_rows, &s_h2_skip_[active_types_[a]], false, H2_.ptr, flat_rows, begin, count, false, nullptr});
-        }
-        launch_tc(calls);
-        launch_tc({{M1_.ptr, flat_rows, &s_h2_m1_, false, H2_.ptr, flat_rows, 0, N, true, nullptr}});
-    }
-    span_end();
-    span_begin("readout");
-    readout_kernel<<<blocks_for(static_cast<long>(N) * 32, 256), 256, 0, stream_>>>(
-        N, C, model_.readout2_hidden, model_.readout2_scale, M0_.ptr, NH, H2_.ptr, element_.ptr, atomic_energies_.ptr,
-        readout1_.ptr, readout2_w1_.ptr, readout2_w2_.ptr, node_energies_.ptr, H2_adj_.ptr, energy_slots_.ptr);
-    launches_ += 1;
-    span_end();
-
-    // reverse
-    span_begin("gemm_h2_reverse");
-    launch_tc({{H2_adj_.ptr, flat_rows, &s_h2_m1_, true, M1_adj_.ptr, flat_rows, 0, N, false, nullptr}});
-    span_end();
-    span_begin("m1_reverse");
-    if (model_.shape_id == 0)
-        m1_reverse_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A1_.ptr, element_.ptr, m1_weights_.ptr, M1_adj_.ptr, A1_adj_.ptr);
-    else
-        m1_reverse_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A1_.ptr, element_.ptr, m1_weights_.ptr, M1_adj_.ptr, A1_adj_.ptr);
-    launches_ += 1;
-    span_end();
-    span_begin("gemm_a1_reverse");
-    {
-        std::vector<TcCall> calls;
-        for (int l = 0; l <= model_.l_max; ++l) {
-            const int eta = model_.eta[l];
-            const RowMap a_rows{16L * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
-            const RowMap c_rows{static_cast<long>(NE) * C, static_cast<long>(eta) * C, static_cast<long>(model_.group_begin[l]) * C, 2 * l + 1};
-            calls.push_back({A1_adj_.ptr, a_rows, &s_a1_[l], true, dPhi1_.ptr, c_rows, 0, N, false, nullptr});
-        }
-        launch_tc(calls);
-    }
-    span_end();
-    span_begin("l1_reverse");
-    if (model_.shape_id == 0)
-        SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S0, C, N, stream_, N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
-                               r1_table_.ptr, H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
-    else
-        SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S1, C, N, stream_, N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
-                               r1_table_.ptr, H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
-    launches_ += 1;
-    span_end();
     }
     if (phases & 4) {
-    span_begin("gemm_h1_reverse");
-    // M0_adj_il = H1_adj_il W_l^T, then the direct adjoint q + T_element H2_adj on the scalar block
-    {
-        std::vector<TcCall> calls;
-        for (int l = 0; l <= model_.hidden_l_max; ++l) {
-            const RowMap rows{static_cast<long>(NH) * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
-            calls.push_back({H1_adj_.ptr, rows, &s_h1_[l], true, M0_adj_.ptr, rows, 0, N, false, l == 0 ? readout1_.ptr : nullptr});
+        fo.accumulate_edge = 1;
+        for (int t0 = 0; t0 < R; t0 += tile_cap) {
+            const int T = std::min(tile_cap, R - t0);
+            const dim3 poly_grid(blocks_for(T, kPolyWarps), C / 32);
+            if (tiled) {
+                // the tile workspace no longer holds this tile's A0: regenerate it
+                span_begin("l0_forward_recompute");
+                l0_forward(t0, T);
+                span_end();
+            }
+            span_begin("gemm_h1_reverse");
+            // M0_adj_il = H1_adj_il W_l^T, then the direct adjoint q + T_element H2_adj on the scalar block
+            {
+                std::vector<TcCall> calls;
+                for (int l = 0; l <= model_.hidden_l_max; ++l) {
+                    const RowMap rows{static_cast<long>(NH) * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
+                    calls.push_back({H1_adj_.ptr + t0 * rowH, rows, &s_h1_[l], true, M0_adj_.ptr, rows, 0, T, false,
+                                     l == 0 ? readout1_.ptr : nullptr});
+                }
+                launch_tc(calls);
+                calls.clear();
+                for_type_ranges(t0, T, [&](int a, int begin, int count) {
+                    calls.push_back({H2_adj_.ptr + static_cast<std::size_t>(begin) * C, flat_rows, &s_h2_skip_[active_types_[a]], true,
+                                     M0_adj_.ptr + (begin - t0) * rowH, scalar_rows, 0, count, true, nullptr});
+                });
+                launch_tc(calls);
+            }
+            span_end();
+            span_begin("m0_reverse");
+            if (model_.shape_id == 0)
+                m0_reverse_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(T, C, A0_.ptr, element_.ptr + t0, m0_weights_.ptr, M0_adj_.ptr, A0_adj_.ptr);
+            else
+                m0_reverse_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(T, C, A0_.ptr, element_.ptr + t0, m0_weights_.ptr, M0_adj_.ptr, A0_adj_.ptr);
+            launches_ += 1;
+            span_end();
+            span_begin("l0_reverse");
+            {
+                const int warp_grid = blocks_for(T, kWarpsPerBlock);
+                if (C == 128)
+                    l0_reverse_warp_kernel<4><<<warp_grid, warp_threads, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
+                else if (C == 64)
+                    l0_reverse_warp_kernel<2><<<warp_grid, warp_threads, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
+                else if (C == 32)
+                    l0_reverse_warp_kernel<1><<<warp_grid, warp_threads, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
+                else
+                    l0_reverse_kernel<0><<<T, C, 0, stream_>>>(T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
+            }
+            launches_ += 1;
+            span_end();
         }
-        launch_tc(calls);
-        calls.clear();
-        for (int a = 0; a < n_active; ++a) {
-            const int begin = type_begin_[a], count = type_begin_[a + 1] - begin;
-            calls.push_back({H2_adj_.ptr, flat_rows, &s_h2_skip_[active_types_[a]], true, M0_adj_.ptr, scalar_rows, begin, count, true, nullptr});
-        }
-        launch_tc(calls);
-    }
-    span_end();
-    span_begin("m0_reverse");
-    if (model_.shape_id == 0)
-        m0_reverse_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A0_.ptr, element_.ptr, m0_weights_.ptr, M0_adj_.ptr, A0_adj_.ptr);
-    else
-        m0_reverse_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(N, C, A0_.ptr, element_.ptr, m0_weights_.ptr, M0_adj_.ptr, A0_adj_.ptr);
-    launches_ += 1;
-    span_end();
-    span_begin("l0_reverse");
-    fo.accumulate_edge = 1;
-    {
-        const int warp_grid = blocks_for(N, kWarpsPerBlock), warp_threads = 32 * kWarpsPerBlock;
-        if (C == 128)
-            l0_reverse_warp_kernel<4><<<warp_grid, warp_threads, 0, stream_>>>(N, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
-        else if (C == 64)
-            l0_reverse_warp_kernel<2><<<warp_grid, warp_threads, 0, stream_>>>(N, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
-        else if (C == 32)
-            l0_reverse_warp_kernel<1><<<warp_grid, warp_threads, 0, stream_>>>(N, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
-        else
-            l0_reverse_kernel<0><<<N, C, 0, stream_>>>(N, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
-    }
-    launches_ += 1;
-    span_end();
-    span_begin("finalize");
-    finalize_kernel<<<1, 32, 0, stream_>>>(energy_slots_.ptr, virial_slots_.ptr, totals_.ptr);
-    unpermute_doubles_kernel<<<blocks_for(ALL, 256), 256, 0, stream_>>>(ALL, 3, original_.ptr, forces_.ptr, forces_out_.ptr);
-    unpermute_doubles_kernel<<<blocks_for(N, 256), 256, 0, stream_>>>(N, 1, original_.ptr, node_energies_.ptr, node_energies_out_.ptr);
-    launches_ += 3;
-    span_end();
+        span_begin("finalize");
+        finalize_kernel<<<1, 32, 0, stream_>>>(energy_slots_.ptr, virial_slots_.ptr, totals_.ptr);
+        unpermute_doubles_kernel<<<blocks_for(ALL, 256), 256, 0, stream_>>>(ALL, 3, original_.ptr, forces_.ptr, forces_out_.ptr);
+        unpermute_doubles_kernel<<<blocks_for(R, 256), 256, 0, stream_>>>(R, 1, original_.ptr, node_energies_.ptr, node_energies_out_.ptr);
+        launches_ += 3;
+        span_end();
     }
     SXB_CUDA(cudaGetLastError());
 }
@@ -1006,9 +1038,25 @@ double Evaluator::energy() const
     return host_totals_[0];
 }
 
+int Evaluator::tile_capacity() const
+{
+    if (tile_size_ > 0 && tile_size_ < num_receivers_) return tile_size_;
+    return std::max(num_receivers_, 1);
+}
+
+void Evaluator::set_tile_size(int receivers_per_tile)
+{
+    if (receivers_per_tile < 0) throw std::invalid_argument("Tile size must be non-negative (0 switches tiling off).");
+    tile_size_ = receivers_per_tile;
+    generation_ += 1;      // buffers are sized at graph installation: the prepared graph becomes stale
+    have_results_ = false;
+}
+
 long Evaluator::get_stage(const std::string& name, double* out, long capacity)
 {
     require_results();
+    if (tile_capacity() < num_receivers_ && name != "H1" && name != "H1_adj" && name != "M0")
+        throw std::invalid_argument("Stage tensors other than H1, H1_adj and M0 are not retained in tiled-streaming mode.");
     const long C = model_.channels, NH = model_.num_hidden, NE = model_.num_lme;
     long N = num_receivers_;
     const float* src = nullptr;

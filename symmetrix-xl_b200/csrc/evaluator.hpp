@@ -52,6 +52,10 @@ public:
     void unpack_rows(int which, const int* device_indices, long count, const float* device_in, bool accumulate);
     void add_force_rows(const int* device_indices, long count, const double* device_in);
     void set_stream(cudaStream_t stream);
+    // Tiled streaming: receivers are processed in tiles of this many with one reusable workspace
+    // (0 = one tile holding every receiver).  Takes effect at the next graph preparation.
+    void set_tile_size(int receivers_per_tile);
+    int tile_capacity() const;
 
     void get_node_energies(double* out);
     void get_atom_forces(double* out);
@@ -115,6 +119,7 @@ private:
     std::uint64_t generation_ = 0;
     int num_nodes_ = 0, num_receivers_ = 0;
     int phase_ = 0;
+    int tile_size_ = 0;
     bool owns_stream_ = true;
     bool pending_finish_ = false;
     long num_edges_ = 0;

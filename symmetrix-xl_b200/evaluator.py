@@ -70,6 +70,7 @@ SIGNATURES = {
     "sxb_halo_unpack": (ctypes.c_int, [_P, ctypes.c_int32, _P, ctypes.c_int64, _P, ctypes.c_int32]),
     "sxb_add_force_rows": (ctypes.c_int, [_P, _P, ctypes.c_int64, _P]),
     "sxb_set_stream": (ctypes.c_int, [_P, _P]),
+    "sxb_set_tile_size": (ctypes.c_int, [_P, ctypes.c_int32]),
     "sxb_set_profiling": (ctypes.c_int, [_P, ctypes.c_int32]),
     "sxb_profile_entry": (ctypes.c_int, [_P, ctypes.c_int32, ctypes.c_char_p, ctypes.c_int32, ctypes.POINTER(ctypes.c_float),
                                          ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]),
@@ -203,6 +204,10 @@ class MACEB200:
 
     def add_force_rows(self, indices_ptr, count, in_ptr):
         _check(self._lib.sxb_add_force_rows(self._h, ctypes.c_void_p(indices_ptr), int(count), ctypes.c_void_p(in_ptr)))
+
+    def set_tile_size(self, receivers_per_tile: int):
+        """Tiled streaming with a reusable workspace (0 = off); prepare the graph again afterwards."""
+        _check(self._lib.sxb_set_tile_size(self._h, int(receivers_per_tile)))
 
     def set_stream(self, stream_ptr):
         _check(self._lib.sxb_set_stream(self._h, ctypes.c_void_p(stream_ptr)))

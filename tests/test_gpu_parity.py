@@ -192,3 +192,61 @@ def test_graphless_force_and_stress_reduction(pkg, model_path):
     assert np.abs(f - fused_f).max() < 1e-6 and np.abs(s - fused_s).max() < 1e-8
     with pytest.raises(ValueError):
         pkg.reduce_edge_forces(len(pos), recv, src + 1000, ev.node_forces, xyz, volume)
+
+
+@pytest.mark.parametrize("arch,cells,tile", [("small", (2, 2, 2), 4), ("small", (3, 2, 2), 7), ("medium", (2, 2, 2), 16),
+                                             ("medium", (3, 2, 2), 32)])
+def test_tiled_streaming_matches_untiled(pkg, model_path, arch, cells, tile):
+    """Tiled streaming with a reusable workspace against the one-tile evaluation
+    (reference: symmetrix/test/test_dual_layer_fixed_workspace.py:104-146, rtol 2e-4 / atol 2e-5)."""
+    path = model_path(arch)
+    pos, cell, types = pkg.modelgen.srtio3(cells, 0.05, 12)
+    plain = pkg.Calculator(path, skin=0.5)
+    a = plain.calculate(pos, cell, types)
+    h1_adj = plain.evaluator.stage("H1_adj")
+    tiled = pkg.Calculator(path, skin=0.5)
+    tiled.evaluator.set_tile_size(tile)
+    b = tiled.calculate(pos, cell, types)
+    b = tiled.calculate(pos, cell, types)         # the workspace is reused across evaluations
+    assert abs(a["energy"] - b["energy"]) / len(pos) <= 1e-7
+    assert np.abs(a["energies"] - b["energies"]).max() <= 1e-6
+    assert np.abs(a["forces"] - b["forces"]).max() <= 1e-5
+    assert np.abs(a["stress"] - b["stress"]).max() <= 1e-8
+    got = tiled.evaluator.stage("H1_adj")
+    assert np.abs(got - h1_adj).max() <= 2e-5 * max(1.0, np.abs(h1_adj).max())
+    with pytest.raises(ValueError):
+        tiled.evaluator.stage("Phi1")
+
+
+def test_tile_boundary_sizes(pkg, model_path):
+    """3, 4, 5, 8 and 9 atoms with a tile capacity of 4 (the reference's tile-boundary cases)."""
+    path = model_path("small")
+    rng = np.random.default_rng(5)
+    for natoms in (3, 4, 5, 8, 9):
+        cell = np.eye(3) * 9.0
+        pos = rng.random((natoms, 3)) * 9.0
+        for i in range(1, natoms):
+            while np.min(np.linalg.norm(pos[:i] - pos[i], axis=1)) < 1.6:
+                pos[i] = rng.random(3) * 9.0
+        types = rng.integers(0, 3, size=natoms).astype(np.int32)
+        a = pkg.Calculator(path, skin=0.5).calculate(pos, cell, types)
+        calc = pkg.Calculator(path, skin=0.5)
+        calc.evaluator.set_tile_size(4)
+        b = calc.calculate(pos, cell, types)
+        assert abs(a["energy"] - b["energy"]) <= 1e-6
+        assert np.abs(a["forces"] - b["forces"]).max() <= 1e-5
+
+
+def test_nve_energy_conservation(pkg, model_path):
+    """20 velocity-Verlet steps of 1 fs at 300 K: total energy is conserved to integrator accuracy."""
+    path = model_path("small")
+    pos, cell, types = pkg.modelgen.srtio3(3, 0.05, 3)
+    z = np.array([8, 22, 38])[types]
+    masses = np.array([pkg.md.MASSES[int(v)] for v in z])
+    vel = pkg.md.maxwell_boltzmann(masses, 300.0, 3)
+    ev = pkg.MACEB200(path)
+    md = pkg.md.NVEIntegrator(ev, pos, cell, types, masses, vel, dt_fs=1.0, skin=0.5)
+    e = md.run(20)
+    drift = np.abs(e - e[0]).max() / len(pos)
+    assert drift < 2e-4, drift          # eV/atom over 20 fs
+    assert md.kinetic() > 0
