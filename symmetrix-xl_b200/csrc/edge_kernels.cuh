@@ -442,7 +442,9 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
 }
 
 // ---------------------------------------------------------------------------------------------
-// Layer 1 kernels, one instantiation per compiled coupling structure.
+// Layer 1 kernels, one instantiation per compiled coupling structure.  The coefficient table is
+// laid out [interval][function][4] (function = path*C + channel): a thread fetches the cubic of one
+// function with a single 128-bit load, a warp 512 contiguous bytes.
 //   forward:  Phi1_i[lme,k] = sum_terms cg * sum_j R1_ij[path,k] Y_ij[lm1] H1_j[lm2,k]
 //   reverse:  row adjoints from dPhi1_i, then per edge the force and the source adjoint
 //             H1_adj_j[lm2,k] += sum R1 Y adj  (coalesced red.add into the source row)
@@ -455,7 +457,7 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
     l1_forward_kernel_##NAME(int num_nodes, int node0, int C_runtime, const int* __restrict__ first,                            \
                              const int* __restrict__ sources, const EdgeGeom* __restrict__ geom,                     \
                              const unsigned char* __restrict__ atype, SplineGrid grid,                               \
-                             const float* __restrict__ table, const float* __restrict__ H1,                          \
+                             const float4* __restrict__ table4, const float* __restrict__ H1,                        \
                              const __grid_constant__ CouplingConstants cgc, float* __restrict__ Phi1)                \
     {                                                                                                                \
         constexpr int NP = SXB_##NAME##_NUM_PATHS, NR = SXB_##NAME##_NUM_ROWS, NH = SXB_##NAME##_NUM_HIDDEN;          \
@@ -477,10 +479,12 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
                 const int2 id = s.index[t];                                                                          \
                 if (id.x < 0) continue;                                                                              \
                 const float x = s.misc[t].x, xx = x * x, xxx = xx * x;                                               \
-                const float* c = table + id.x + k;                                                                   \
+                const float4* c4 = table4 + (id.x >> 2) + k;   /* the four coefficients of a function are adjacent */ \
                 float R[NP];                                                                                         \
-                _Pragma("unroll") for (int p = 0; p < NP; ++p)                                                       \
-                    R[p] = cubic(c[p * C], c[F + p * C], c[2 * F + p * C], c[3 * F + p * C], x, xx, xxx);            \
+                _Pragma("unroll") for (int p = 0; p < NP; ++p) {                                                     \
+                    const float4 c = c4[p * C];                                                                      \
+                    R[p] = cubic(c.x, c.y, c.z, c.w, x, xx, xxx);                                                    \
+                }                                                                                                    \
                 const float* hsrc = H1 + static_cast<size_t>(id.y) * NH * C + k;                                     \
                 float h[NH];                                                                                         \
                 _Pragma("unroll") for (int q = 0; q < NH; ++q) h[q] = hsrc[q * C];                                   \
@@ -501,7 +505,7 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
     l1_reverse_kernel_##NAME(int num_nodes, int node0, int C_runtime, const int* __restrict__ first,                            \
                              const int* __restrict__ sources, const EdgeGeom* __restrict__ geom,                     \
                              const unsigned char* __restrict__ atype, SplineGrid grid,                               \
-                             const float* __restrict__ table, const float* __restrict__ H1,                          \
+                             const float4* __restrict__ table4, const float* __restrict__ H1,                        \
                              const float* __restrict__ dPhi1, const __grid_constant__ CouplingConstants cgc,         \
                              float* __restrict__ H1_adj, ForceOutputs out)                                           \
     {                                                                                                                \
@@ -535,12 +539,12 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
                 if (id.x < 0) continue;                                                                              \
                 const float4 m = s.misc[t];                                                                          \
                 const float x = m.x, xx = x * x, xxx = xx * x, x2 = 2.0f * x, xx3 = 3.0f * xx;                       \
-                const float* c = table + id.x + k;                                                                   \
+                const float4* c4 = table4 + (id.x >> 2) + k;                                                         \
                 float R[NP], dR[NP];                                                                                 \
                 _Pragma("unroll") for (int p = 0; p < NP; ++p) {                                                     \
-                    const float c0 = c[p * C], c1 = c[F + p * C], c2 = c[2 * F + p * C], c3 = c[3 * F + p * C];      \
-                    R[p] = cubic(c0, c1, c2, c3, x, xx, xxx);                                                        \
-                    dR[p] = cubic_derivative(c1, c2, c3, x2, xx3);                                                   \
+                    const float4 c = c4[p * C];                                                                      \
+                    R[p] = cubic(c.x, c.y, c.z, c.w, x, xx, xxx);                                                    \
+                    dR[p] = cubic_derivative(c.y, c.z, c.w, x2, xx3);                                                \
                 }                                                                                                    \
                 const size_t source_row = static_cast<size_t>(id.y) * NH * C + k;                                    \
                 float h[NH], hadj[NH];                                                                               \

@@ -95,10 +95,17 @@ Evaluator::Evaluator(const std::string& json_path, int device_ordinal) : device_
     SXB_CUDA(cudaEventCreate(&event_end_));
 
     const int C = model_.channels;
-    // layer-1 table [interval][4][paths*C] in float
-    std::vector<float> r1(model_.r1_coeff.size());
-    for (std::size_t i = 0; i < r1.size(); ++i) r1[i] = static_cast<float>(model_.r1_coeff[i]);
-    upload(r1_table_, r1, stream_);
+    // layer-1 table in float, repacked from [interval][4][paths*C] to [interval][paths*C][4]
+    {
+        const std::size_t F = static_cast<std::size_t>(model_.num_paths) * C;
+        const std::size_t intervals = static_cast<std::size_t>(model_.spline_points - 1);
+        std::vector<float> r1(model_.r1_coeff.size());
+        for (std::size_t i = 0; i < intervals; ++i)
+            for (std::size_t f = 0; f < F; ++f)
+                for (std::size_t c = 0; c < 4; ++c)
+                    r1[(i * F + f) * 4 + c] = static_cast<float>(model_.r1_coeff[(i * 4 + c) * F + f]);
+        upload(r1_table_, r1, stream_);
+    }
     upload(m0_weights_, model_.m0_weights, stream_);
     upload(m1_weights_, model_.m1_weights, stream_);
     upload(w_h1_, model_.w_h1, stream_);
@@ -645,10 +652,10 @@ void Evaluator::run_pipeline(int phases)
             span_begin("l1_forward");
             if (model_.shape_id == 0)
                 SXB_LAUNCH_BY_CHANNELS(l1_forward_kernel_S0, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
-                                       r1_table_.ptr, H1_.ptr, coupling_, Phi1_.ptr);
+                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, coupling_, Phi1_.ptr);
             else
                 SXB_LAUNCH_BY_CHANNELS(l1_forward_kernel_S1, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
-                                       r1_table_.ptr, H1_.ptr, coupling_, Phi1_.ptr);
+                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, coupling_, Phi1_.ptr);
             launches_ += 1;
             span_end();
             // A1_il = Phi1_il W_l
@@ -716,10 +723,10 @@ void Evaluator::run_pipeline(int phases)
             span_begin("l1_reverse");
             if (model_.shape_id == 0)
                 SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S0, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
-                                       r1_table_.ptr, H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
+                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
             else
                 SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S1, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
-                                       r1_table_.ptr, H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
+                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
             launches_ += 1;
             span_end();
         }
