@@ -164,13 +164,65 @@ struct alignas(16) ChunkState {
     float4 misc[kEdgeChunk];      // x = offset inside the spline interval, yzw = unit direction
     int2 index[kEdgeChunk];       // x = first coefficient of (pair, interval) or -1 (inactive), y = source
     float len[kGradient ? kEdgeChunk : 1];
+    float dens[kGradient ? kEdgeChunk : 1];   // d/dr of the density spline at the edge (0 without density scaling)
 };
+
+// Optional per-receiver density scaling of a layer's A tensor, A_i /= 1 + sum_j s(r_ij)
+// (reference: libsymmetrix/source/mace.cpp:1562-1584 and 2381-2403; gradient 1587-1636, 2406-2458).
+struct DensityScale {
+    const float* table;       // cubic coefficients [interval][4] of s, nullptr when the model has none
+    const float* inv_scale;   // [receiver] 1 / (1 + sum_j s(r_ij))
+    const float* dot;         // [receiver] sum over (lm, k) of A_adj * A, both taken for the scaled A
+};
+
+// Derivative of a scalar spline stored [interval][4].
+__device__ __forceinline__ float scalar_spline_derivative(const float* __restrict__ table, int interval, float x)
+{
+    const float4 c = reinterpret_cast<const float4*>(table)[interval];
+    return fmaf(3.0f * c.w, x * x, fmaf(2.0f * c.z, x, c.y));
+}
+__device__ __forceinline__ float scalar_spline_value(const float* __restrict__ table, int interval, float x)
+{
+    const float4 c = reinterpret_cast<const float4*>(table)[interval];
+    return fmaf(c.w, x * x * x, fmaf(c.z, x * x, fmaf(c.y, x, c.x)));
+}
+
+// inv_scale[i] = 1 / (1 + sum_j s(r_ij)) for the layer-0 and the layer-1 density spline (either table
+// may be nullptr).  One warp per receiver; edge values in float as every radial function, summed in
+// double.  Reference: libsymmetrix/source/mace.cpp:1562-1584 (layer 0), 2381-2403 (layer 1).
+__global__ void density_scale_kernel(int num_receivers, const int* __restrict__ first, const EdgeGeom* __restrict__ geom,
+                                     SplineGrid grid, const float* __restrict__ table0, const float* __restrict__ table1,
+                                     float* __restrict__ inv_scale0, float* __restrict__ inv_scale1)
+{
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (i >= num_receivers) return;
+    double rho0 = 0.0, rho1 = 0.0;
+    for (int e = first[i] + lane; e < first[i + 1]; e += 32) {
+        const float r = geom[e].r;
+        if (!(r < grid.r_cut)) continue;
+        int interval;
+        float x;
+        spline_point(grid, r, interval, x);
+        if (table0 != nullptr) rho0 += scalar_spline_value(table0, interval, x);
+        if (table1 != nullptr) rho1 += scalar_spline_value(table1, interval, x);
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        rho0 += __shfl_xor_sync(0xffffffffu, rho0, offset);
+        rho1 += __shfl_xor_sync(0xffffffffu, rho1, offset);
+    }
+    if (lane == 0) {
+        if (table0 != nullptr) inv_scale0[i] = static_cast<float>(1.0 / (1.0 + rho0));
+        if (table1 != nullptr) inv_scale1[i] = static_cast<float>(1.0 / (1.0 + rho1));
+    }
+}
 
 // Fills the chunk state for edges [begin, begin+count) of one receiver.
 template <bool kGradient, bool kOrderedPairs>
 __device__ __forceinline__ void fill_chunk(ChunkState<kGradient>& s, int begin, int count, const int* __restrict__ sources,
                                            const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype,
-                                           int type_i, int num_active, const SplineGrid& grid, int functions)
+                                           int type_i, int num_active, const SplineGrid& grid, int functions,
+                                           const float* __restrict__ density_table = nullptr)
 {
     for (int t = threadIdx.x; t < count; t += blockDim.x) {
         const int e = begin + t;
@@ -192,6 +244,7 @@ __device__ __forceinline__ void fill_chunk(ChunkState<kGradient>& s, int begin, 
             harmonics16<true>(g.ux, g.uy, g.uz, inv_r, reinterpret_cast<float*>(s.y[t]), reinterpret_cast<float*>(s.gx[t]),
                               reinterpret_cast<float*>(s.gy[t]), reinterpret_cast<float*>(s.gz[t]));
             s.len[t] = g.r;
+            s.dens[t] = density_table != nullptr ? scalar_spline_derivative(density_table, interval, x) : 0.0f;
         } else {
             harmonics16<false>(g.ux, g.uy, g.uz, inv_r, reinterpret_cast<float*>(s.y[t]), nullptr, nullptr, nullptr);
         }
@@ -225,7 +278,8 @@ template <int kC>
 __global__ void __launch_bounds__(kC > 0 ? kC : 256)
 l0_forward_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict__ first, const int* __restrict__ sources,
                   const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype, int num_active,
-                  SplineGrid grid, const float* __restrict__ table, float* __restrict__ A0)
+                  SplineGrid grid, const float* __restrict__ table, float* __restrict__ A0,
+                  const float* __restrict__ inv_scale)
 {
     __shared__ ChunkState<false> s;
     const int C = kC > 0 ? kC : C_runtime;
@@ -262,9 +316,10 @@ l0_forward_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
             for (int lm = 9; lm < 16; ++lm) acc[lm] = fmaf(R[3], y[lm], acc[lm]);
         }
     }
+    const float scale = inv_scale != nullptr ? inv_scale[i] : 1.0f;   // density scaling, mace.cpp:1562-1584
     float* out = A0 + static_cast<size_t>(local) * 16 * C + k;
 #pragma unroll
-    for (int lm = 0; lm < 16; ++lm) out[lm * C] = acc[lm];
+    for (int lm = 0; lm < 16; ++lm) out[lm * C] = acc[lm] * scale;
 }
 
 // Block-level force bookkeeping shared by the two reverse kernels.  Each warp leaves its
@@ -287,6 +342,28 @@ __device__ __forceinline__ void warp_reduce3(float& a, float& b, float& c)
     }
 }
 
+// Sums three values over the warp with 6 shuffles: the exchange at distance 16 halves the data
+// (each half-warp keeps two of the four slots), the one at distance 8 halves it again, three more
+// finish the sum.  On return lanes 0, 8 and 16 hold the totals of a, b and c respectively.
+__device__ __forceinline__ float warp_reduce3_transposed(float a, float b, float c, int lane)
+{
+    const bool upper = lane & 16;
+    // lower half keeps (a, b) and receives the partner's (a, b); upper half keeps (c, 0)
+    const float send0 = upper ? a : c, send1 = upper ? b : 0.0f;
+    const float recv0 = __shfl_xor_sync(0xffffffffu, send0, 16);
+    const float recv1 = __shfl_xor_sync(0xffffffffu, send1, 16);
+    float k0 = (upper ? c : a) + recv0;      // lower: a total of pair, upper: c total of pair
+    float k1 = (upper ? 0.0f : b) + recv1;   // lower: b, upper: 0
+    const bool second = lane & 8;
+    const float send = second ? k0 : k1;
+    const float recv = __shfl_xor_sync(0xffffffffu, send, 8);
+    float v = (second ? k1 : k0) + recv;     // lanes 0-7: a, 8-15: b, 16-23: c, 24-31: 0
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v;
+}
+
 template <int kMaxWarps>
 struct ForceScratch {
     float partial[kEdgeChunk][kMaxWarps][3];
@@ -296,7 +373,8 @@ struct ForceScratch {
 
 template <int kMaxWarps>
 __device__ __forceinline__ void flush_chunk_forces(ForceScratch<kMaxWarps>& fs, const ChunkState<true>& s, int chunk_begin,
-                                                   int count, int num_warps, const ForceOutputs& out)
+                                                   int count, int num_warps, const ForceOutputs& out,
+                                                   float density_coef = 0.0f)
 {
     // called by all threads after a __syncthreads(); threads t < count own one edge each
     double fx = 0.0, fy = 0.0, fz = 0.0;
@@ -314,6 +392,11 @@ __device__ __forceinline__ void flush_chunk_forces(ForceScratch<kMaxWarps>& fs, 
             px += fs.partial[t][w][0];
             py += fs.partial[t][w][1];
             pz += fs.partial[t][w][2];
+        }
+        {   // density scaling: dE/d(xyz_ij) += (A_adj . A) / (1 + rho_i) * s'(r) * rhat
+            const float4 u = s.misc[t];
+            const float d = density_coef * s.dens[t];
+            px -= d * u.y; py -= d * u.z; pz -= d * u.w;
         }
         // directed force dE/d(xyz_ij) with the reference's sign: force -= adjoint * (...)
         const double ex = -static_cast<double>(px), ey = -static_cast<double>(py), ez = -static_cast<double>(pz);
@@ -371,7 +454,8 @@ template <int kC>
 __global__ void __launch_bounds__(kC > 0 ? kC : 256)
 l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict__ first, const int* __restrict__ sources,
                   const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype, int num_active,
-                  SplineGrid grid, const float* __restrict__ table, const float* __restrict__ A0_adj, ForceOutputs out)
+                  SplineGrid grid, const float* __restrict__ table, const float* __restrict__ A0_adj, ForceOutputs out,
+                  DensityScale density)
 {
     __shared__ ChunkState<true> s;
     __shared__ ForceScratch<8> fs;
@@ -384,14 +468,17 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
     const int begin = first[i], end = first[i + 1];
     if (threadIdx.x < 3) fs.receiver[threadIdx.x] = 0.0;
     if (threadIdx.x < 9) fs.virial[threadIdx.x] = 0.0;
+    // with density scaling the stored adjoint refers to the scaled A0: dE/dA0_unscaled = adj / (1 + rho_i)
+    const float scale = density.table != nullptr ? density.inv_scale[i] : 1.0f;
+    const float density_coef = density.table != nullptr ? density.dot[i] * scale : 0.0f;
     float adj[16];
     const float* in = A0_adj + static_cast<size_t>(local) * 16 * C + k;
 #pragma unroll
-    for (int lm = 0; lm < 16; ++lm) adj[lm] = in[lm * C];
+    for (int lm = 0; lm < 16; ++lm) adj[lm] = in[lm * C] * scale;
     for (int chunk = begin; chunk < end; chunk += kEdgeChunk) {
         const int count = min(kEdgeChunk, end - chunk);
         __syncthreads();
-        fill_chunk<true, true>(s, chunk, count, sources, geom, atype, type_i, num_active, grid, F);
+        fill_chunk<true, true>(s, chunk, count, sources, geom, atype, type_i, num_active, grid, F, density.table);
         __syncthreads();
         for (int t = 0; t < count; ++t) {
             const int base = s.index[t].x;
@@ -436,7 +523,7 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
             }
         }
         __syncthreads();
-        flush_chunk_forces<8>(fs, s, chunk, count, num_warps, out);
+        flush_chunk_forces<8>(fs, s, chunk, count, num_warps, out, density_coef);
     }
     finish_receiver_forces<8>(fs, i, out);
 }
@@ -458,7 +545,8 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
                              const int* __restrict__ sources, const EdgeGeom* __restrict__ geom,                     \
                              const unsigned char* __restrict__ atype, SplineGrid grid,                               \
                              const float4* __restrict__ table4, const float* __restrict__ H1,                        \
-                             const __grid_constant__ CouplingConstants cgc, float* __restrict__ Phi1)                \
+                             const __grid_constant__ CouplingConstants cgc, float* __restrict__ Phi1,                \
+                             const float* __restrict__ inv_scale)                                                    \
     {                                                                                                                \
         constexpr int NP = SXB_##NAME##_NUM_PATHS, NR = SXB_##NAME##_NUM_ROWS, NH = SXB_##NAME##_NUM_HIDDEN;          \
         constexpr int NE = SXB_##NAME##_NUM_LME;                                                                     \
@@ -496,8 +584,10 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
         float out_lme[NE];                                                                                           \
         _Pragma("unroll") for (int q = 0; q < NE; ++q) out_lme[q] = 0.0f;                                            \
         SXB_##NAME##_TERMS(SXB_TERM_FORWARD)                                                                         \
-        float* out = Phi1 + static_cast<size_t>(local) * NE * C + k;                                                     \
-        _Pragma("unroll") for (int q = 0; q < NE; ++q) out[q * C] = out_lme[q];                                      \
+        /* density scaling of A1 = Phi1 W (mace.cpp:2381-2403) commutes with the linear: scale Phi1 */              \
+        const float scale = inv_scale != nullptr ? inv_scale[i] : 1.0f;                                              \
+        float* out = Phi1 + static_cast<size_t>(local) * NE * C + k;                                                 \
+        _Pragma("unroll") for (int q = 0; q < NE; ++q) out[q * C] = out_lme[q] * scale;                              \
     }                                                                                                                \
                                                                                                                      \
     template <int kC>                                                                                                \
@@ -507,7 +597,7 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
                              const unsigned char* __restrict__ atype, SplineGrid grid,                               \
                              const float4* __restrict__ table4, const float* __restrict__ H1,                        \
                              const float* __restrict__ dPhi1, const __grid_constant__ CouplingConstants cgc,         \
-                             float* __restrict__ H1_adj, ForceOutputs out)                                           \
+                             float* __restrict__ H1_adj, ForceOutputs out, DensityScale density)                     \
     {                                                                                                                \
         constexpr int NP = SXB_##NAME##_NUM_PATHS, NR = SXB_##NAME##_NUM_ROWS, NH = SXB_##NAME##_NUM_HIDDEN;          \
         constexpr int NE = SXB_##NAME##_NUM_LME;                                                                     \
@@ -521,18 +611,21 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
         const int begin = first[i], end = first[i + 1];                                                              \
         if (threadIdx.x < 3) fs.receiver[threadIdx.x] = 0.0;                                                         \
         if (threadIdx.x < 9) fs.virial[threadIdx.x] = 0.0;                                                           \
+        /* with density scaling dPhi1 holds the adjoint of the scaled Phi1: divide by 1 + rho_i once more */       \
+        const float scale = density.table != nullptr ? density.inv_scale[i] : 1.0f;                                  \
+        const float density_coef = density.table != nullptr ? density.dot[i] * scale : 0.0f;                         \
         float adj[NR];                                                                                               \
         {                                                                                                            \
             float dphi[NE];                                                                                          \
-            const float* in = dPhi1 + static_cast<size_t>(local) * NE * C + k;                                           \
-            _Pragma("unroll") for (int q = 0; q < NE; ++q) dphi[q] = in[q * C];                                      \
+            const float* in = dPhi1 + static_cast<size_t>(local) * NE * C + k;                                       \
+            _Pragma("unroll") for (int q = 0; q < NE; ++q) dphi[q] = in[q * C] * scale;                              \
             _Pragma("unroll") for (int r_ = 0; r_ < NR; ++r_) adj[r_] = 0.0f;                                        \
             SXB_##NAME##_TERMS(SXB_TERM_TRANSPOSE)                                                                   \
         }                                                                                                            \
         for (int chunk = begin; chunk < end; chunk += kEdgeChunk) {                                                  \
             const int count = min(kEdgeChunk, end - chunk);                                                          \
             __syncthreads();                                                                                         \
-            fill_chunk<true, false>(s, chunk, count, sources, geom, atype, 0, 1, grid, F);                           \
+            fill_chunk<true, false>(s, chunk, count, sources, geom, atype, 0, 1, grid, F, density.table);            \
             __syncthreads();                                                                                         \
             for (int t = 0; t < count; ++t) {                                                                        \
                 const int2 id = s.index[t];                                                                          \
@@ -565,15 +658,11 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
                     load16(s.gz[t], g);                                                                              \
                     _Pragma("unroll") for (int q = 0; q < 16; ++q) fz = fmaf(ang[q], g[q], fz);                      \
                 }                                                                                                    \
-                warp_reduce3(fx, fy, fz);                                                                            \
-                if (lane == 0) {                                                                                     \
-                    fs.partial[t][warp][0] = fx;                                                                     \
-                    fs.partial[t][warp][1] = fy;                                                                     \
-                    fs.partial[t][warp][2] = fz;                                                                     \
-                }                                                                                                    \
+                const float total = warp_reduce3_transposed(fx, fy, fz, lane);   /* lanes 0, 8, 16: x, y, z */       \
+                if ((lane & 7) == 0 && lane < 24) fs.partial[t][warp][lane >> 3] = total;                            \
             }                                                                                                        \
             __syncthreads();                                                                                         \
-            flush_chunk_forces<8>(fs, s, chunk, count, num_warps, out);                                              \
+            flush_chunk_forces<8>(fs, s, chunk, count, num_warps, out, density_coef);                                \
         }                                                                                                            \
         finish_receiver_forces<8>(fs, i, out);                                                                       \
     }

@@ -24,6 +24,7 @@ struct alignas(16) WarpChunk {
     float4 misc[kWarpChunk];      // x = spline offset, yzw = unit direction
     int2 index[kWarpChunk];       // x = coefficient base or -1, y = source
     float len[kGradient ? kWarpChunk : 1];
+    float dens[kGradient ? kWarpChunk : 1];   // d/dr of the density spline (0 without density scaling)
     float force[kGradient ? kWarpChunk : 1][3];
 };
 
@@ -31,7 +32,8 @@ template <bool kGradient>
 __device__ __forceinline__ void fill_warp_chunk(WarpChunk<kGradient>& s, int lane, int begin, int count,
                                                 const int* __restrict__ sources, const EdgeGeom* __restrict__ geom,
                                                 const unsigned char* __restrict__ atype, int type_i, int num_active,
-                                                const SplineGrid& grid, int functions)
+                                                const SplineGrid& grid, int functions,
+                                                const float* __restrict__ density_table = nullptr)
 {
     if (lane < count) {
         const int e = begin + lane;
@@ -51,6 +53,7 @@ __device__ __forceinline__ void fill_warp_chunk(WarpChunk<kGradient>& s, int lan
                 harmonics16<true>(g.ux, g.uy, g.uz, inv_r, reinterpret_cast<float*>(s.y[lane]), reinterpret_cast<float*>(s.gx[lane]),
                                   reinterpret_cast<float*>(s.gy[lane]), reinterpret_cast<float*>(s.gz[lane]));
                 s.len[lane] = g.r;
+                s.dens[lane] = density_table != nullptr ? scalar_spline_derivative(density_table, interval, x) : 0.0f;
             } else {
                 harmonics16<false>(g.ux, g.uy, g.uz, inv_r, reinterpret_cast<float*>(s.y[lane]), nullptr, nullptr, nullptr);
             }
@@ -87,34 +90,13 @@ struct VecLoad<4> {
     }
 };
 
-// Sums three values over the warp with 6 shuffles: the exchange at distance 16 halves the data
-// (each half-warp keeps two of the four slots), the one at distance 8 halves it again, three more
-// finish the sum.  On return lanes 0, 8 and 16 hold the totals of a, b and c respectively.
-__device__ __forceinline__ float warp_reduce3_transposed(float a, float b, float c, int lane)
-{
-    const bool upper = lane & 16;
-    // lower half keeps (a, b) and receives the partner's (a, b); upper half keeps (c, 0)
-    const float send0 = upper ? a : c, send1 = upper ? b : 0.0f;
-    const float recv0 = __shfl_xor_sync(0xffffffffu, send0, 16);
-    const float recv1 = __shfl_xor_sync(0xffffffffu, send1, 16);
-    float k0 = (upper ? c : a) + recv0;      // lower: a total of pair, upper: c total of pair
-    float k1 = (upper ? 0.0f : b) + recv1;   // lower: b, upper: 0
-    const bool second = lane & 8;
-    const float send = second ? k0 : k1;
-    const float recv = __shfl_xor_sync(0xffffffffu, send, 8);
-    float v = (second ? k1 : k0) + recv;     // lanes 0-7: a, 8-15: b, 16-23: c, 24-31: 0
-    v += __shfl_xor_sync(0xffffffffu, v, 4);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    return v;
-}
-
 // ---------------------------------------------------------------------------------------------
 template <int kVec>
 __global__ void __launch_bounds__(32 * kWarpsPerBlock)
 l0_forward_warp_kernel(int num_nodes, int node0, const int* __restrict__ first, const int* __restrict__ sources,
                        const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype, int num_active,
-                       SplineGrid grid, const float* __restrict__ table, float* __restrict__ A0)
+                       SplineGrid grid, const float* __restrict__ table, float* __restrict__ A0,
+                       const float* __restrict__ inv_scale)
 {
     constexpr int C = 32 * kVec, F = 4 * C;
     __shared__ WarpChunk<false> chunks[kWarpsPerBlock];
@@ -159,6 +141,13 @@ l0_forward_warp_kernel(int num_nodes, int node0, const int* __restrict__ first, 
             }
         }
     }
+    if (inv_scale != nullptr) {   // density scaling, mace.cpp:1562-1584
+        const float scale = inv_scale[i];
+#pragma unroll
+        for (int lm = 0; lm < 16; ++lm)
+#pragma unroll
+            for (int v = 0; v < kVec; ++v) acc[lm][v] *= scale;
+    }
     float* out = A0 + static_cast<size_t>(local) * 16 * C + k;
 #pragma unroll
     for (int lm = 0; lm < 16; ++lm) VecLoad<kVec>::store(out + lm * C, acc[lm]);
@@ -169,7 +158,8 @@ template <int kVec>
 __global__ void __launch_bounds__(32 * kWarpsPerBlock)
 l0_reverse_warp_kernel(int num_nodes, int node0, const int* __restrict__ first, const int* __restrict__ sources,
                        const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype, int num_active,
-                       SplineGrid grid, const float* __restrict__ table, const float* __restrict__ A0_adj, ForceOutputs out)
+                       SplineGrid grid, const float* __restrict__ table, const float* __restrict__ A0_adj, ForceOutputs out,
+                       DensityScale density)
 {
     constexpr int C = 32 * kVec, F = 4 * C;
     __shared__ WarpChunk<true> chunks[kWarpsPerBlock];
@@ -187,13 +177,23 @@ l0_reverse_warp_kernel(int num_nodes, int node0, const int* __restrict__ first, 
 #pragma unroll
         for (int lm = 0; lm < 16; ++lm) VecLoad<kVec>::load(in + lm * C, adj[lm]);
     }
+    // with density scaling the stored adjoint refers to the scaled A0: dE/dA0_unscaled = adj / (1 + rho_i)
+    float density_coef = 0.0f;
+    if (density.table != nullptr) {
+        const float scale = density.inv_scale[i];
+        density_coef = density.dot[i] * scale;
+#pragma unroll
+        for (int lm = 0; lm < 16; ++lm)
+#pragma unroll
+            for (int v = 0; v < kVec; ++v) adj[lm][v] *= scale;
+    }
     // per-lane partial sums over the edges this lane finishes (lane t owns edge t of every chunk)
     double rfx = 0.0, rfy = 0.0, rfz = 0.0;
     double vir[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
     for (int chunk = begin; chunk < end; chunk += kWarpChunk) {
         const int count = min(kWarpChunk, end - chunk);
         __syncwarp();
-        fill_warp_chunk<true>(s, lane, chunk, count, sources, geom, atype, type_i, num_active, grid, F);
+        fill_warp_chunk<true>(s, lane, chunk, count, sources, geom, atype, type_i, num_active, grid, F, density.table);
         __syncwarp();
         for (int t = 0; t < count; ++t) {
             const int base = s.index[t].x;
@@ -245,9 +245,11 @@ l0_reverse_warp_kernel(int num_nodes, int node0, const int* __restrict__ first, 
         __syncwarp();
         // lane t finishes edge t: directed force dE/d(xyz_ij) = -(sum), scatter and virial
         if (lane < count && s.index[lane].x >= 0) {
-            const double ex = -static_cast<double>(s.force[lane][0]);
-            const double ey = -static_cast<double>(s.force[lane][1]);
-            const double ez = -static_cast<double>(s.force[lane][2]);
+            const float4 u = s.misc[lane];
+            const float dens = density_coef * s.dens[lane];   // dE/d(xyz) += (A_adj . A) / (1 + rho) * s'(r) * rhat
+            const double ex = -static_cast<double>(s.force[lane][0] - dens * u.y);
+            const double ey = -static_cast<double>(s.force[lane][1] - dens * u.z);
+            const double ez = -static_cast<double>(s.force[lane][2] - dens * u.w);
             const int j = s.index[lane].y;
             atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j), ex);
             atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 1, ey);

@@ -76,6 +76,21 @@ inline int blocks_for(long n, int threads) { return static_cast<int>((n + thread
         else KERNEL<0><<<(GRID), (C), 0, (STREAM)>>>(__VA_ARGS__);                    \
     } while (0)
 
+// Launches a symmetric-contraction kernel with G nodes per thread (G in {1, 2}); the dynamic
+// shared memory holds the [terms][32] weight slice of the block's element.
+#define SXB_LAUNCH_POLY(KERNEL, G, TERMS, T, C, STREAM, ...)                                                 \
+    do {                                                                                                     \
+        const dim3 grid_(blocks_for((T), kPolyNodesPerBlock), (C) / 32);                                     \
+        const std::size_t smem_ = static_cast<std::size_t>(TERMS) * 32 * sizeof(float);                      \
+        if ((G) == 2) {                                                                                      \
+            SXB_CUDA(cudaFuncSetAttribute(KERNEL<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_))); \
+            KERNEL<2><<<grid_, 32 * kPolyWarps, smem_, (STREAM)>>>(__VA_ARGS__);                             \
+        } else {                                                                                             \
+            SXB_CUDA(cudaFuncSetAttribute(KERNEL<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_))); \
+            KERNEL<1><<<grid_, 32 * kPolyWarps, smem_, (STREAM)>>>(__VA_ARGS__);                             \
+        }                                                                                                    \
+    } while (0)
+
 }  // namespace
 
 Evaluator::Evaluator(const std::string& json_path, int device_ordinal) : device_(device_ordinal)
@@ -88,8 +103,6 @@ Evaluator::Evaluator(const std::string& json_path, int device_ordinal) : device_
     model_ = load_model(json_path);
     if (model_.shape_id > 1)
         throw std::invalid_argument("This build carries kernels for hidden irreps 0e and 0e+1o only.");
-    if (model_.a0_scaled || model_.a1_scaled)
-        throw std::invalid_argument("Density-scaled (A0_scaled / A1_scaled) models are not supported yet.");
     SXB_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
     SXB_CUDA(cudaEventCreate(&event_begin_));
     SXB_CUDA(cudaEventCreate(&event_end_));
@@ -106,6 +119,9 @@ Evaluator::Evaluator(const std::string& json_path, int device_ordinal) : device_
                     r1[(i * F + f) * 4 + c] = static_cast<float>(model_.r1_coeff[(i * 4 + c) * F + f]);
         upload(r1_table_, r1, stream_);
     }
+    // density splines of A0_scaled / A1_scaled models, [interval][4] in float
+    if (model_.a0_scaled) upload(density0_table_, std::vector<float>(model_.a0_density_coeff.begin(), model_.a0_density_coeff.end()), stream_);
+    if (model_.a1_scaled) upload(density1_table_, std::vector<float>(model_.a1_density_coeff.begin(), model_.a1_density_coeff.end()), stream_);
     upload(m0_weights_, model_.m0_weights, stream_);
     upload(m1_weights_, model_.m1_weights, stream_);
     upload(w_h1_, model_.w_h1, stream_);
@@ -117,6 +133,10 @@ Evaluator::Evaluator(const std::string& json_path, int device_ordinal) : device_
     upload(readout2_w2_, model_.readout2_w2, stream_);
     upload(atomic_energies_, model_.atomic_energies, stream_);
     if (const char* env = std::getenv("SXB_SIMT_LINEARS")) use_tensor_cores_ = !(env[0] == '1');
+    if (const char* env = std::getenv("SXB_POLY_GROUP")) {   // nodes per thread in the contraction kernels: "<forward><reverse>"
+        if (env[0] == '1' || env[0] == '2') poly_g_forward_ = env[0] - '0';
+        if (env[0] != 0 && (env[1] == '1' || env[1] == '2')) poly_g_reverse_ = env[1] - '0';
+    }
     for (int l = 0; l <= model_.hidden_l_max; ++l)
         upload_split(s_h1_[l], model_.w_h1.data() + static_cast<std::size_t>(l) * C * C, C, C);
     for (int l = 0; l <= model_.l_max; ++l) upload_split(s_a1_[l], model_.w_a1[l].data(), model_.eta[l] * C, C);
@@ -245,6 +265,8 @@ void Evaluator::install_graph(int num_receivers, int num_nodes, const std::vecto
     H2_.reserve(T * C);
     H2_adj_.reserve(N * C);
     node_energies_.reserve(N);
+    if (model_.a0_scaled) { inv_scale0_.reserve(N); dot0_.reserve(N); }
+    if (model_.a1_scaled) { inv_scale1_.reserve(N); dot1_.reserve(N); }
     node_energies_out_.reserve(N);
     forces_.reserve(ALL * 3);
     forces_out_.reserve(ALL * 3);
@@ -593,16 +615,20 @@ void Evaluator::run_pipeline(int phases)
     const int warp_threads = 32 * kWarpsPerBlock;
 
     // launch helpers for one tile of T receivers starting at t0 (tile tensors are indexed from 0)
+    const float* inv0 = model_.a0_scaled ? inv_scale0_.ptr : nullptr;
+    const float* inv1 = model_.a1_scaled ? inv_scale1_.ptr : nullptr;
+    const DensityScale density0{model_.a0_scaled ? density0_table_.ptr : nullptr, inv_scale0_.ptr, dot0_.ptr};
+    const DensityScale density1{model_.a1_scaled ? density1_table_.ptr : nullptr, inv_scale1_.ptr, dot1_.ptr};
     auto l0_forward = [&](int t0, int T) {
         const int warp_grid = blocks_for(T, kWarpsPerBlock);
         if (C == 128)
-            l0_forward_warp_kernel<4><<<warp_grid, warp_threads, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
+            l0_forward_warp_kernel<4><<<warp_grid, warp_threads, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr, inv0);
         else if (C == 64)
-            l0_forward_warp_kernel<2><<<warp_grid, warp_threads, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
+            l0_forward_warp_kernel<2><<<warp_grid, warp_threads, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr, inv0);
         else if (C == 32)
-            l0_forward_warp_kernel<1><<<warp_grid, warp_threads, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
+            l0_forward_warp_kernel<1><<<warp_grid, warp_threads, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr, inv0);
         else
-            l0_forward_kernel<0><<<T, C, 0, stream_>>>(T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr);
+            l0_forward_kernel<0><<<T, C, 0, stream_>>>(T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_.ptr, inv0);
         launches_ += 1;
     };
     // per-element node ranges intersected with the tile
@@ -620,18 +646,26 @@ void Evaluator::run_pipeline(int phases)
         SXB_CUDA(cudaMemsetAsync(H1_adj_.ptr, 0, sizeof(float) * static_cast<std::size_t>(ALL) * rowH, stream_));
         SXB_CUDA(cudaMemsetAsync(energy_slots_.ptr, 0, sizeof(double) * kVirialSlots, stream_));
         SXB_CUDA(cudaMemsetAsync(virial_slots_.ptr, 0, sizeof(double) * kVirialSlots * 9, stream_));
+        if (model_.a0_scaled || model_.a1_scaled) {
+            if (model_.a0_scaled) SXB_CUDA(cudaMemsetAsync(dot0_.ptr, 0, sizeof(float) * R, stream_));
+            if (model_.a1_scaled) SXB_CUDA(cudaMemsetAsync(dot1_.ptr, 0, sizeof(float) * R, stream_));
+            span_begin("density_scales");
+            density_scale_kernel<<<blocks_for(static_cast<long>(R) * 32, 256), 256, 0, stream_>>>(
+                R, first_.ptr, geom_.ptr, grid_, density0.table, density1.table, inv_scale0_.ptr, inv_scale1_.ptr);
+            launches_ += 1;
+            span_end();
+        }
         for (int t0 = 0; t0 < R; t0 += tile_cap) {
             const int T = std::min(tile_cap, R - t0);
             span_begin("l0_forward");
             l0_forward(t0, T);
             span_end();
             span_begin("m0_forward");
-            const dim3 poly_grid(blocks_for(T, kPolyWarps), C / 32);
             float* m0 = M0_.ptr + t0 * rowH;
             if (model_.shape_id == 0)
-                m0_forward_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(T, C, A0_.ptr, element_.ptr + t0, m0_weights_.ptr, m0);
+                SXB_LAUNCH_POLY(m0_forward_kernel_S0, poly_g_forward_, SXB_S0_M0_NUM_TERMS, T, C, stream_, T, C, A0_.ptr, element_.ptr + t0, m0_weights_.ptr, m0);
             else
-                m0_forward_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(T, C, A0_.ptr, element_.ptr + t0, m0_weights_.ptr, m0);
+                SXB_LAUNCH_POLY(m0_forward_kernel_S1, poly_g_forward_, SXB_S1_M0_NUM_TERMS, T, C, stream_, T, C, A0_.ptr, element_.ptr + t0, m0_weights_.ptr, m0);
             launches_ += 1;
             span_end();
             // H1_il = M0_il W_l
@@ -648,14 +682,13 @@ void Evaluator::run_pipeline(int phases)
     if (phases & 2) {
         for (int t0 = 0; t0 < R; t0 += tile_cap) {
             const int T = std::min(tile_cap, R - t0);
-            const dim3 poly_grid(blocks_for(T, kPolyWarps), C / 32);
             span_begin("l1_forward");
             if (model_.shape_id == 0)
                 SXB_LAUNCH_BY_CHANNELS(l1_forward_kernel_S0, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
-                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, coupling_, Phi1_.ptr);
+                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, coupling_, Phi1_.ptr, inv1);
             else
                 SXB_LAUNCH_BY_CHANNELS(l1_forward_kernel_S1, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
-                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, coupling_, Phi1_.ptr);
+                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, coupling_, Phi1_.ptr, inv1);
             launches_ += 1;
             span_end();
             // A1_il = Phi1_il W_l
@@ -673,9 +706,9 @@ void Evaluator::run_pipeline(int phases)
             span_end();
             span_begin("m1_forward");
             if (model_.shape_id == 0)
-                m1_forward_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_.ptr);
+                SXB_LAUNCH_POLY(m1_forward_kernel_S0, poly_g_forward_, SXB_S0_M1_NUM_TERMS, T, C, stream_, T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_.ptr);
             else
-                m1_forward_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_.ptr);
+                SXB_LAUNCH_POLY(m1_forward_kernel_S1, poly_g_forward_, SXB_S1_M1_NUM_TERMS, T, C, stream_, T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_.ptr);
             launches_ += 1;
             span_end();
             // H2 = xs T_element + M1 W
@@ -703,9 +736,9 @@ void Evaluator::run_pipeline(int phases)
             span_end();
             span_begin("m1_reverse");
             if (model_.shape_id == 0)
-                m1_reverse_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_adj_.ptr, A1_adj_.ptr);
+                SXB_LAUNCH_POLY(m1_reverse_kernel_S0, poly_g_reverse_, SXB_S0_M1_NUM_TERMS, T, C, stream_, T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_adj_.ptr, A1_adj_.ptr, model_.a1_scaled ? dot1_.ptr + t0 : nullptr);
             else
-                m1_reverse_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_adj_.ptr, A1_adj_.ptr);
+                SXB_LAUNCH_POLY(m1_reverse_kernel_S1, poly_g_reverse_, SXB_S1_M1_NUM_TERMS, T, C, stream_, T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_adj_.ptr, A1_adj_.ptr, model_.a1_scaled ? dot1_.ptr + t0 : nullptr);
             launches_ += 1;
             span_end();
             span_begin("gemm_a1_reverse");
@@ -723,10 +756,10 @@ void Evaluator::run_pipeline(int phases)
             span_begin("l1_reverse");
             if (model_.shape_id == 0)
                 SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S0, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
-                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
+                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1);
             else
                 SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S1, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
-                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo);
+                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1);
             launches_ += 1;
             span_end();
         }
@@ -735,7 +768,6 @@ void Evaluator::run_pipeline(int phases)
         fo.accumulate_edge = 1;
         for (int t0 = 0; t0 < R; t0 += tile_cap) {
             const int T = std::min(tile_cap, R - t0);
-            const dim3 poly_grid(blocks_for(T, kPolyWarps), C / 32);
             if (tiled) {
                 // the tile workspace no longer holds this tile's A0: regenerate it
                 span_begin("l0_forward_recompute");
@@ -762,22 +794,22 @@ void Evaluator::run_pipeline(int phases)
             span_end();
             span_begin("m0_reverse");
             if (model_.shape_id == 0)
-                m0_reverse_kernel_S0<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(T, C, A0_.ptr, element_.ptr + t0, m0_weights_.ptr, M0_adj_.ptr, A0_adj_.ptr);
+                SXB_LAUNCH_POLY(m0_reverse_kernel_S0, poly_g_reverse_, SXB_S0_M0_NUM_TERMS, T, C, stream_, T, C, A0_.ptr, element_.ptr + t0, m0_weights_.ptr, M0_adj_.ptr, A0_adj_.ptr, model_.a0_scaled ? dot0_.ptr + t0 : nullptr);
             else
-                m0_reverse_kernel_S1<<<poly_grid, 32 * kPolyWarps, 0, stream_>>>(T, C, A0_.ptr, element_.ptr + t0, m0_weights_.ptr, M0_adj_.ptr, A0_adj_.ptr);
+                SXB_LAUNCH_POLY(m0_reverse_kernel_S1, poly_g_reverse_, SXB_S1_M0_NUM_TERMS, T, C, stream_, T, C, A0_.ptr, element_.ptr + t0, m0_weights_.ptr, M0_adj_.ptr, A0_adj_.ptr, model_.a0_scaled ? dot0_.ptr + t0 : nullptr);
             launches_ += 1;
             span_end();
             span_begin("l0_reverse");
             {
                 const int warp_grid = blocks_for(T, kWarpsPerBlock);
                 if (C == 128)
-                    l0_reverse_warp_kernel<4><<<warp_grid, warp_threads, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
+                    l0_reverse_warp_kernel<4><<<warp_grid, warp_threads, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo, density0);
                 else if (C == 64)
-                    l0_reverse_warp_kernel<2><<<warp_grid, warp_threads, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
+                    l0_reverse_warp_kernel<2><<<warp_grid, warp_threads, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo, density0);
                 else if (C == 32)
-                    l0_reverse_warp_kernel<1><<<warp_grid, warp_threads, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
+                    l0_reverse_warp_kernel<1><<<warp_grid, warp_threads, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo, density0);
                 else
-                    l0_reverse_kernel<0><<<T, C, 0, stream_>>>(T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo);
+                    l0_reverse_kernel<0><<<T, C, 0, stream_>>>(T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo, density0);
             }
             launches_ += 1;
             span_end();

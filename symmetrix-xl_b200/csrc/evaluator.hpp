@@ -93,6 +93,7 @@ private:
     std::vector<int> type_begin_;
 
     // model tables on the device
+    DeviceBuffer<float> density0_table_, density1_table_, inv_scale0_, inv_scale1_, dot0_, dot1_;
     DeviceBuffer<float> r0_table_, r1_table_, m0_weights_, m1_weights_, w_h1_, w_a1_[4], h2_skip_, h2_m1_;
     DeviceBuffer<float> readout1_, readout2_w1_, readout2_w2_;
     // the same weights split into TF32-exact high part and residual, stored [N][K] (K contiguous)
@@ -105,6 +106,7 @@ private:
     SplitWeight s_h1_[4], s_a1_[4], s_h2_m1_;
     std::vector<SplitWeight> s_h2_skip_;
     bool use_tensor_cores_ = true;
+    int poly_g_forward_ = 1, poly_g_reverse_ = 1;   // nodes per thread in the symmetric-contraction kernels
     void upload_split(SplitWeight& out, const float* w, int rows, int cols);
     struct TcCall {
         const float* A; RowMap a_rows; const SplitWeight* w; bool reverse; float* C; RowMap c_rows;

@@ -12,105 +12,230 @@
 namespace sxb {
 
 // ---------------------------------------------------------------------------------------------
-// Symmetric contraction.  One thread per (node, channel): the 16 inputs sit in registers and
-// every monomial of the compiled structure is one straight-line statement; weights are laid
-// out [element][term][channel] so a warp reads 128 contiguous bytes per term.
-#define SXB_POLY_F1(out, term, a) o[out] = fmaf(w[(term) * C], x[a], o[out]);
-#define SXB_POLY_F2(out, term, a, b) o[out] = fmaf(w[(term) * C], x[a] * x[b], o[out]);
-#define SXB_POLY_F3(out, term, a, b, c) o[out] = fmaf(w[(term) * C], x[a] * x[b] * x[c], o[out]);
-#define SXB_POLY_R1(out, term, a) g[a] = fmaf(w[(term) * C], adj[out], g[a]);
-#define SXB_POLY_R2(out, term, a, b)                      \
-    {                                                     \
-        const float s_ = w[(term) * C] * adj[out];        \
-        g[a] = fmaf(s_, x[b], g[a]);                      \
-        g[b] = fmaf(s_, x[a], g[b]);                      \
+// Symmetric contraction.  One thread per (group of G consecutive nodes, channel): the 16 inputs of
+// every node of the group sit in registers and every monomial of the compiled structure is one
+// straight-line statement.  Weights are laid out [element][term][channel].  A block covers
+// kPolyNodesPerBlock consecutive nodes and 32 channels; it first copies the [term][32] weight slice
+// of its first node's element to shared memory, and every group whose nodes all have that element
+// (nodes are sorted by element, so nearly all do) reads its weights from there - a mixed group is
+// evaluated node by node from global memory.  At one node per warp and weights from global memory
+// these kernels are bound by re-reading the weight slice from L2 (216 KB per node for the 422-term
+// structure); sharing a slice among the nodes of a block removes that traffic.
+#define SXB_POLY_F1(out, term, a)                                                                     \
+    {                                                                                                 \
+        const float w_ = w[(term) * ws];                                                              \
+        _Pragma("unroll") for (int n_ = 0; n_ < G; ++n_) o[n_][out] = fmaf(w_, x[n_][a], o[n_][out]); \
     }
-#define SXB_POLY_R3(out, term, a, b, c)                   \
-    {                                                     \
-        const float s_ = w[(term) * C] * adj[out];        \
-        g[a] = fmaf(s_, x[b] * x[c], g[a]);               \
-        g[b] = fmaf(s_, x[a] * x[c], g[b]);               \
-        g[c] = fmaf(s_, x[a] * x[b], g[c]);               \
+#define SXB_POLY_F2(out, term, a, b)                                                                  \
+    {                                                                                                 \
+        const float w_ = w[(term) * ws];                                                              \
+        _Pragma("unroll") for (int n_ = 0; n_ < G; ++n_)                                              \
+            o[n_][out] = fmaf(w_, x[n_][a] * x[n_][b], o[n_][out]);                                   \
+    }
+#define SXB_POLY_F3(out, term, a, b, c)                                                               \
+    {                                                                                                 \
+        const float w_ = w[(term) * ws];                                                              \
+        _Pragma("unroll") for (int n_ = 0; n_ < G; ++n_)                                              \
+            o[n_][out] = fmaf(w_, x[n_][a] * x[n_][b] * x[n_][c], o[n_][out]);                        \
+    }
+#define SXB_POLY_R1(out, term, a)                                                                     \
+    {                                                                                                 \
+        const float w_ = w[(term) * ws];                                                              \
+        _Pragma("unroll") for (int n_ = 0; n_ < G; ++n_) g[n_][a] = fmaf(w_, adj[n_][out], g[n_][a]); \
+    }
+#define SXB_POLY_R2(out, term, a, b)                                                                  \
+    {                                                                                                 \
+        const float w_ = w[(term) * ws];                                                              \
+        _Pragma("unroll") for (int n_ = 0; n_ < G; ++n_) {                                            \
+            const float s_ = w_ * adj[n_][out];                                                       \
+            g[n_][a] = fmaf(s_, x[n_][b], g[n_][a]);                                                  \
+            g[n_][b] = fmaf(s_, x[n_][a], g[n_][b]);                                                  \
+        }                                                                                             \
+    }
+#define SXB_POLY_R3(out, term, a, b, c)                                                               \
+    {                                                                                                 \
+        const float w_ = w[(term) * ws];                                                              \
+        _Pragma("unroll") for (int n_ = 0; n_ < G; ++n_) {                                            \
+            const float s_ = w_ * adj[n_][out];                                                       \
+            g[n_][a] = fmaf(s_, x[n_][b] * x[n_][c], g[n_][a]);                                       \
+            g[n_][b] = fmaf(s_, x[n_][a] * x[n_][c], g[n_][b]);                                       \
+            g[n_][c] = fmaf(s_, x[n_][a] * x[n_][b], g[n_][c]);                                       \
+        }                                                                                             \
     }
 
 constexpr int kPolyWarps = 8;
+constexpr int kPolyNodesPerBlock = 32;
+
+// Density-scaled models: dot[node] += sum over (lm, channels of this warp) of A_adj * A, the quantity
+// the reference forms per node before the density force (libsymmetrix/source/mace.cpp:1611-1614,
+// 2430-2433).  Called by a whole warp; one atomic per warp and node.
+__device__ __forceinline__ void poly_accumulate_dot(const float* g, const float* x, float* __restrict__ dot, int node, int num_nodes)
+{
+    float partial = 0.0f;
+#pragma unroll
+    for (int q = 0; q < 16; ++q) partial = fmaf(g[q], x[q], partial);
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, offset);
+    if ((threadIdx.x & 31) == 0 && node < num_nodes) atomicAdd(dot + node, partial);
+}
+
+// Copies the [terms][32] weight slice of one element into shared memory (all threads of the block).
+__device__ __forceinline__ void stage_poly_weights(float* __restrict__ dst, const float* __restrict__ weights, int type,
+                                                   int terms, int C, int k_base)
+{
+    const float* src = weights + static_cast<size_t>(type) * terms * C + k_base;
+    for (int idx = threadIdx.x; idx < terms * 32; idx += blockDim.x) dst[idx] = src[(idx >> 5) * C + (idx & 31)];
+    __syncthreads();
+}
+
+// Walks the node groups of one block: BODY(node0, count_is_full_group_of_block_element, w, ws).
+#define SXB_POLY_WALK(G, NT, CALL_GROUP, CALL_SINGLE)                                                               \
+    extern __shared__ float w_s[];                                                                                  \
+    const int block_node0 = blockIdx.x * kPolyNodesPerBlock;                                                        \
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;                                                     \
+    const int k = blockIdx.y * 32 + lane;                                                                           \
+    const int type0 = element[block_node0];                                                                         \
+    stage_poly_weights(w_s, weights, type0, NT, C, blockIdx.y * 32);                                                \
+    const int block_end = min(block_node0 + kPolyNodesPerBlock, num_nodes);                                         \
+    for (int node0 = block_node0 + warp * G; node0 < block_end; node0 += kPolyWarps * G) {                          \
+        bool same = true;                                                                                           \
+        _Pragma("unroll") for (int n = 0; n < G; ++n) same = same && element[min(node0 + n, num_nodes - 1)] == type0; \
+        if (same) {                                                                                                 \
+            const float* w = w_s + lane;                                                                            \
+            constexpr int ws = 32;                                                                                  \
+            CALL_GROUP;                                                                                             \
+        } else {                                                                                                    \
+            for (int n = node0; n < min(node0 + G, block_end); ++n) {                                               \
+                const float* w = weights + static_cast<size_t>(element[n]) * NT * C + k;                            \
+                const int ws = C;                                                                                   \
+                CALL_SINGLE;                                                                                        \
+            }                                                                                                       \
+        }                                                                                                           \
+    }
 
 #define SXB_DEFINE_POLY_KERNELS(NAME)                                                                               \
-    /* M0[node][LM][k] from A0[node][16][k] */                                                                      \
-    __global__ void __launch_bounds__(32 * kPolyWarps)                                                              \
+    /* M0[node][LM][k] from A0[node][16][k] for the nodes [node0, node0 + G) that exist */                          \
+    template <int G>                                                                                                \
+    __device__ __forceinline__ void m0_forward_group_##NAME(int node0, int num_nodes, int C, int k,                 \
+                                                            const float* __restrict__ A0, const float* w, int ws,   \
+                                                            float* __restrict__ M0)                                 \
+    {                                                                                                               \
+        constexpr int NH = SXB_##NAME##_NUM_HIDDEN;                                                                 \
+        float x[G][16], o[G][NH];                                                                                   \
+        _Pragma("unroll") for (int n = 0; n < G; ++n) {                                                             \
+            const float* in = A0 + static_cast<size_t>(min(node0 + n, num_nodes - 1)) * 16 * C + k;                 \
+            _Pragma("unroll") for (int q = 0; q < 16; ++q) x[n][q] = in[q * C];                                     \
+            _Pragma("unroll") for (int q = 0; q < NH; ++q) o[n][q] = 0.0f;                                          \
+        }                                                                                                           \
+        SXB_##NAME##_M0_TERMS(SXB_POLY_F1, SXB_POLY_F2, SXB_POLY_F3)                                                \
+        _Pragma("unroll") for (int n = 0; n < G; ++n) {                                                             \
+            if (node0 + n < num_nodes) {                                                                            \
+                float* out = M0 + static_cast<size_t>(node0 + n) * NH * C + k;                                      \
+                _Pragma("unroll") for (int q = 0; q < NH; ++q) out[q * C] = o[n][q];                                \
+            }                                                                                                       \
+        }                                                                                                           \
+    }                                                                                                               \
+    template <int G>                                                                                                \
+    __global__ void __launch_bounds__(32 * kPolyWarps, 2)                                                            \
     m0_forward_kernel_##NAME(int num_nodes, int C, const float* __restrict__ A0, const unsigned char* __restrict__ element, \
                              const float* __restrict__ weights, float* __restrict__ M0)                             \
     {                                                                                                               \
-        constexpr int NH = SXB_##NAME##_NUM_HIDDEN, NT = SXB_##NAME##_M0_NUM_TERMS;                                 \
-        const int node = blockIdx.x * kPolyWarps + (threadIdx.x >> 5);                                              \
-        const int k = blockIdx.y * 32 + (threadIdx.x & 31);                                                         \
-        if (node >= num_nodes) return;                                                                              \
-        const float* in = A0 + static_cast<size_t>(node) * 16 * C + k;                                              \
-        float x[16];                                                                                                \
-        _Pragma("unroll") for (int q = 0; q < 16; ++q) x[q] = in[q * C];                                            \
-        const float* w = weights + static_cast<size_t>(element[node]) * NT * C + k;                                 \
-        float o[NH];                                                                                                \
-        _Pragma("unroll") for (int q = 0; q < NH; ++q) o[q] = 0.0f;                                                 \
-        SXB_##NAME##_M0_TERMS(SXB_POLY_F1, SXB_POLY_F2, SXB_POLY_F3)                                                \
-        float* out = M0 + static_cast<size_t>(node) * NH * C + k;                                                   \
-        _Pragma("unroll") for (int q = 0; q < NH; ++q) out[q * C] = o[q];                                           \
+        SXB_POLY_WALK(G, SXB_##NAME##_M0_NUM_TERMS,                                                                 \
+                      m0_forward_group_##NAME<G>(node0, num_nodes, C, k, A0, w, ws, M0),                            \
+                      m0_forward_group_##NAME<1>(n, num_nodes, C, k, A0, w, ws, M0))                                \
     }                                                                                                               \
     /* A0_adj[node][16][k] = sum_LM M0_adj[node][LM][k] dM0[LM]/dA0 */                                              \
-    __global__ void __launch_bounds__(32 * kPolyWarps)                                                              \
+    template <int G>                                                                                                \
+    __device__ __forceinline__ void m0_reverse_group_##NAME(int node0, int num_nodes, int C, int k,                 \
+                                                            const float* __restrict__ A0, const float* w, int ws,   \
+                                                            const float* __restrict__ M0_adj, float* __restrict__ A0_adj, \
+                                                            float* __restrict__ dot)                                \
+    {                                                                                                               \
+        constexpr int NH = SXB_##NAME##_NUM_HIDDEN;                                                                 \
+        float x[G][16], g[G][16], adj[G][NH];                                                                       \
+        _Pragma("unroll") for (int n = 0; n < G; ++n) {                                                             \
+            const size_t node = static_cast<size_t>(min(node0 + n, num_nodes - 1));                                 \
+            const float* in = A0 + node * 16 * C + k;                                                               \
+            _Pragma("unroll") for (int q = 0; q < 16; ++q) { x[n][q] = in[q * C]; g[n][q] = 0.0f; }                 \
+            const float* ain = M0_adj + node * NH * C + k;                                                          \
+            _Pragma("unroll") for (int q = 0; q < NH; ++q) adj[n][q] = ain[q * C];                                  \
+        }                                                                                                           \
+        SXB_##NAME##_M0_TERMS(SXB_POLY_R1, SXB_POLY_R2, SXB_POLY_R3)                                                \
+        _Pragma("unroll") for (int n = 0; n < G; ++n) {                                                             \
+            if (node0 + n < num_nodes) {                                                                            \
+                float* out = A0_adj + static_cast<size_t>(node0 + n) * 16 * C + k;                                  \
+                _Pragma("unroll") for (int q = 0; q < 16; ++q) out[q * C] = g[n][q];                                \
+            }                                                                                                       \
+            if (dot != nullptr) poly_accumulate_dot(g[n], x[n], dot, node0 + n, num_nodes);                         \
+        }                                                                                                           \
+    }                                                                                                               \
+    template <int G>                                                                                                \
+    __global__ void __launch_bounds__(32 * kPolyWarps, 1)                                                            \
     m0_reverse_kernel_##NAME(int num_nodes, int C, const float* __restrict__ A0, const unsigned char* __restrict__ element, \
                              const float* __restrict__ weights, const float* __restrict__ M0_adj,                   \
-                             float* __restrict__ A0_adj)                                                            \
+                             float* __restrict__ A0_adj, float* __restrict__ dot)                                   \
     {                                                                                                               \
-        constexpr int NH = SXB_##NAME##_NUM_HIDDEN, NT = SXB_##NAME##_M0_NUM_TERMS;                                 \
-        const int node = blockIdx.x * kPolyWarps + (threadIdx.x >> 5);                                              \
-        const int k = blockIdx.y * 32 + (threadIdx.x & 31);                                                         \
-        if (node >= num_nodes) return;                                                                              \
-        const float* in = A0 + static_cast<size_t>(node) * 16 * C + k;                                              \
-        float x[16], g[16];                                                                                         \
-        _Pragma("unroll") for (int q = 0; q < 16; ++q) { x[q] = in[q * C]; g[q] = 0.0f; }                           \
-        const float* w = weights + static_cast<size_t>(element[node]) * NT * C + k;                                 \
-        float adj[NH];                                                                                              \
-        const float* ain = M0_adj + static_cast<size_t>(node) * NH * C + k;                                         \
-        _Pragma("unroll") for (int q = 0; q < NH; ++q) adj[q] = ain[q * C];                                         \
-        SXB_##NAME##_M0_TERMS(SXB_POLY_R1, SXB_POLY_R2, SXB_POLY_R3)                                                \
-        float* out = A0_adj + static_cast<size_t>(node) * 16 * C + k;                                               \
-        _Pragma("unroll") for (int q = 0; q < 16; ++q) out[q * C] = g[q];                                           \
+        SXB_POLY_WALK(G, SXB_##NAME##_M0_NUM_TERMS,                                                                 \
+                      m0_reverse_group_##NAME<G>(node0, num_nodes, C, k, A0, w, ws, M0_adj, A0_adj, dot),                \
+                      m0_reverse_group_##NAME<1>(n, num_nodes, C, k, A0, w, ws, M0_adj, A0_adj, dot))                    \
     }                                                                                                               \
     /* M1[node][k] from A1[node][16][k] */                                                                          \
-    __global__ void __launch_bounds__(32 * kPolyWarps)                                                              \
+    template <int G>                                                                                                \
+    __device__ __forceinline__ void m1_forward_group_##NAME(int node0, int num_nodes, int C, int k,                 \
+                                                            const float* __restrict__ A1, const float* w, int ws,   \
+                                                            float* __restrict__ M1)                                 \
+    {                                                                                                               \
+        float x[G][16], o[G][1];                                                                                    \
+        _Pragma("unroll") for (int n = 0; n < G; ++n) {                                                             \
+            const float* in = A1 + static_cast<size_t>(min(node0 + n, num_nodes - 1)) * 16 * C + k;                 \
+            _Pragma("unroll") for (int q = 0; q < 16; ++q) x[n][q] = in[q * C];                                     \
+            o[n][0] = 0.0f;                                                                                         \
+        }                                                                                                           \
+        SXB_##NAME##_M1_TERMS(SXB_POLY_F1, SXB_POLY_F2, SXB_POLY_F3)                                                \
+        _Pragma("unroll") for (int n = 0; n < G; ++n)                                                               \
+            if (node0 + n < num_nodes) M1[static_cast<size_t>(node0 + n) * C + k] = o[n][0];                        \
+    }                                                                                                               \
+    template <int G>                                                                                                \
+    __global__ void __launch_bounds__(32 * kPolyWarps, 2)                                                            \
     m1_forward_kernel_##NAME(int num_nodes, int C, const float* __restrict__ A1, const unsigned char* __restrict__ element, \
                              const float* __restrict__ weights, float* __restrict__ M1)                             \
     {                                                                                                               \
-        constexpr int NT = SXB_##NAME##_M1_NUM_TERMS;                                                               \
-        const int node = blockIdx.x * kPolyWarps + (threadIdx.x >> 5);                                              \
-        const int k = blockIdx.y * 32 + (threadIdx.x & 31);                                                         \
-        if (node >= num_nodes) return;                                                                              \
-        const float* in = A1 + static_cast<size_t>(node) * 16 * C + k;                                              \
-        float x[16];                                                                                                \
-        _Pragma("unroll") for (int q = 0; q < 16; ++q) x[q] = in[q * C];                                            \
-        const float* w = weights + static_cast<size_t>(element[node]) * NT * C + k;                                 \
-        float o[1] = {0.0f};                                                                                        \
-        SXB_##NAME##_M1_TERMS(SXB_POLY_F1, SXB_POLY_F2, SXB_POLY_F3)                                                \
-        M1[static_cast<size_t>(node) * C + k] = o[0];                                                               \
+        SXB_POLY_WALK(G, SXB_##NAME##_M1_NUM_TERMS,                                                                 \
+                      m1_forward_group_##NAME<G>(node0, num_nodes, C, k, A1, w, ws, M1),                            \
+                      m1_forward_group_##NAME<1>(n, num_nodes, C, k, A1, w, ws, M1))                                \
     }                                                                                                               \
     /* A1_adj[node][16][k] = M1_adj[node][k] dM1/dA1 */                                                             \
-    __global__ void __launch_bounds__(32 * kPolyWarps)                                                              \
+    template <int G>                                                                                                \
+    __device__ __forceinline__ void m1_reverse_group_##NAME(int node0, int num_nodes, int C, int k,                 \
+                                                            const float* __restrict__ A1, const float* w, int ws,   \
+                                                            const float* __restrict__ M1_adj, float* __restrict__ A1_adj, \
+                                                            float* __restrict__ dot)                                \
+    {                                                                                                               \
+        float x[G][16], g[G][16], adj[G][1];                                                                        \
+        _Pragma("unroll") for (int n = 0; n < G; ++n) {                                                             \
+            const size_t node = static_cast<size_t>(min(node0 + n, num_nodes - 1));                                 \
+            const float* in = A1 + node * 16 * C + k;                                                               \
+            _Pragma("unroll") for (int q = 0; q < 16; ++q) { x[n][q] = in[q * C]; g[n][q] = 0.0f; }                 \
+            adj[n][0] = M1_adj[node * C + k];                                                                       \
+        }                                                                                                           \
+        SXB_##NAME##_M1_TERMS(SXB_POLY_R1, SXB_POLY_R2, SXB_POLY_R3)                                                \
+        _Pragma("unroll") for (int n = 0; n < G; ++n) {                                                             \
+            if (node0 + n < num_nodes) {                                                                            \
+                float* out = A1_adj + static_cast<size_t>(node0 + n) * 16 * C + k;                                  \
+                _Pragma("unroll") for (int q = 0; q < 16; ++q) out[q * C] = g[n][q];                                \
+            }                                                                                                       \
+            if (dot != nullptr) poly_accumulate_dot(g[n], x[n], dot, node0 + n, num_nodes);                         \
+        }                                                                                                           \
+    }                                                                                                               \
+    template <int G>                                                                                                \
+    __global__ void __launch_bounds__(32 * kPolyWarps, 2)                                                            \
     m1_reverse_kernel_##NAME(int num_nodes, int C, const float* __restrict__ A1, const unsigned char* __restrict__ element, \
                              const float* __restrict__ weights, const float* __restrict__ M1_adj,                   \
-                             float* __restrict__ A1_adj)                                                            \
+                             float* __restrict__ A1_adj, float* __restrict__ dot)                                   \
     {                                                                                                               \
-        constexpr int NT = SXB_##NAME##_M1_NUM_TERMS;                                                               \
-        const int node = blockIdx.x * kPolyWarps + (threadIdx.x >> 5);                                              \
-        const int k = blockIdx.y * 32 + (threadIdx.x & 31);                                                         \
-        if (node >= num_nodes) return;                                                                              \
-        const float* in = A1 + static_cast<size_t>(node) * 16 * C + k;                                              \
-        float x[16], g[16];                                                                                         \
-        _Pragma("unroll") for (int q = 0; q < 16; ++q) { x[q] = in[q * C]; g[q] = 0.0f; }                           \
-        const float* w = weights + static_cast<size_t>(element[node]) * NT * C + k;                                 \
-        float adj[1] = {M1_adj[static_cast<size_t>(node) * C + k]};                                                 \
-        SXB_##NAME##_M1_TERMS(SXB_POLY_R1, SXB_POLY_R2, SXB_POLY_R3)                                                \
-        float* out = A1_adj + static_cast<size_t>(node) * 16 * C + k;                                               \
-        _Pragma("unroll") for (int q = 0; q < 16; ++q) out[q * C] = g[q];                                           \
+        SXB_POLY_WALK(G, SXB_##NAME##_M1_NUM_TERMS,                                                                 \
+                      m1_reverse_group_##NAME<G>(node0, num_nodes, C, k, A1, w, ws, M1_adj, A1_adj, dot),                \
+                      m1_reverse_group_##NAME<1>(n, num_nodes, C, k, A1, w, ws, M1_adj, A1_adj, dot))                    \
     }
 
 SXB_DEFINE_POLY_KERNELS(S0)

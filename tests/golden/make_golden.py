@@ -40,10 +40,11 @@ def evaluator_goldens():
     from oracle import neighbor, ref
 
     pkg = graft.load_package()
-    for arch, cells, cutoff in (("small", 2, 5.0), ("medium", 2, 6.0)):
+    # the third case is a density-scaled model (A0_scaled and A1_scaled, mace.cpp:1562-1636, 2381-2458)
+    for arch, cells, cutoff, scaled in (("small", 2, 5.0, False), ("medium", 2, 6.0, False), ("medium", 2, 6.0, True)):
         with tempfile.TemporaryDirectory() as tmp:
             path = Path(tmp) / "model.json"
-            pkg.modelgen.write_model(path, arch, seed=101)
+            pkg.modelgen.write_model(path, arch, seed=101, a0_scaled=scaled, a1_scaled=scaled)
             pos, cell, types = pkg.modelgen.srtio3(cells, 0.05, 202)
             first, src, shifts = neighbor.build_neighbor_graph(pos, cell, cutoff)
             xyz = neighbor.edge_vectors(pos, cell, first, src, shifts)
@@ -54,7 +55,7 @@ def evaluator_goldens():
             for name in ("A0", "M0", "H1", "Phi1", "A1", "M1", "H2", "H1_adj", "A0_adj"):
                 v = m.get(name)
                 data["sum_" + name] = np.array([v.sum(), np.abs(v).sum(), (v * v).sum()])
-            np.savez_compressed(OUT / f"reference_evaluator_{arch}.npz", **data)
+            np.savez_compressed(OUT / f"reference_evaluator_{arch}{'_scaled' if scaled else ''}.npz", **data)
             print("wrote", arch, len(pos), "atoms", len(src), "edges")
 
 
@@ -109,6 +110,10 @@ def structure_goldens():
 
 if __name__ == "__main__":
     graft.build()
-    evaluator_goldens()
-    harmonics_goldens()
-    structure_goldens()
+    which = sys.argv[1:] or ["evaluator", "harmonics", "structure"]
+    if "evaluator" in which:
+        evaluator_goldens()
+    if "harmonics" in which:
+        harmonics_goldens()
+    if "structure" in which:
+        structure_goldens()
