@@ -98,10 +98,21 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_workload(tmpdir, cells=SUPERCELL):
+RANDOM_SOLID_ELEMENTS = (1, 6, 8, 13, 14, 22, 26, 38, 56, 79)
+
+
+def build_workload(tmpdir, cells=SUPERCELL, workload="srtio3", atoms=20000):
+    """srtio3: medium model (128x0e+128x1o) on a perturbed SrTiO3 supercell.
+    random: higher-order model (128x0e+128x1o+128x2e, 10 elements) on a seeded Poisson-disk
+    disordered solid at 0.085 atoms/A^3 with 1.8 A minimum separation."""
     import __graft_entry__ as graft
 
     pkg = graft.load_package()
+    if workload == "random":
+        model = Path(tmpdir) / "large.json"
+        pkg.modelgen.write_model(model, "large", seed=SEED, atomic_numbers=RANDOM_SOLID_ELEMENTS)
+        pos, cell, types = pkg.modelgen.random_solid(atoms, 0.085, 1.8, len(RANDOM_SOLID_ELEMENTS), SEED)
+        return pkg, model, pos, cell, types
     model = Path(tmpdir) / "medium.json"
     pkg.modelgen.write_model(model, "medium", seed=SEED)
     pos, cell, types = pkg.modelgen.srtio3(cells, SIGMA, SEED)
@@ -226,7 +237,7 @@ def run_ours(args):
         return run_distributed(args)
     torch.cuda.set_device(local_rank)
     with tempfile.TemporaryDirectory() as tmp:
-        pkg, model, pos, cell, types = build_workload(tmp, args.cells)
+        pkg, model, pos, cell, types = build_workload(tmp, args.cells, args.workload, args.atoms)
         ev = pkg.MACEB200(model, device=local_rank)
         if args.tile > 0:
             ev.set_tile_size(args.tile)
@@ -349,7 +360,7 @@ def run_ours(args):
                          "us_per_atom_per_step": md_ms * 1e3 / n, "rebuilds": integ.rebuilds,
                          "max_energy_drift_eV_per_atom": float(np.abs(energies - energies[0]).max() / n)}
         cpu = None
-        if rank == 0 and world == 1 and args.cells == SUPERCELL:
+        if rank == 0 and world == 1 and args.cells == SUPERCELL and args.workload == "srtio3":
             cpu = cpu_baseline(pkg, model, sample_cells=3, calls=2)
 
         if world > 1:
@@ -359,11 +370,12 @@ def run_ours(args):
                 "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": False, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": f"medium-{n}-SrTiO3", "atoms_per_gpu": n, "total_atoms": total_atoms,
+                "config": {"workload": f"medium-{n}-SrTiO3" if args.workload == "srtio3" else f"large-{n}-random-solid",
+                           "atoms_per_gpu": n, "total_atoms": total_atoms,
                            "tile": args.tile if args.tile > 0 else None,
                            "device_memory_gb": round(torch.cuda.mem_get_info()[1] / 1e9 - torch.cuda.mem_get_info()[0] / 1e9, 2),
                            "edges_per_gpu": num_edges, "active_edges_per_gpu": active_edges, "skin": SKIN,
-                           "parallelism": "replicas" if world > 1 else "single", "elements": 3,
+                           "parallelism": "replicas" if world > 1 else "single", "elements": int(types.max()) + 1,
                            "l2": "flushed between timed steps (256 MiB write)"},
                 "atoms_per_s": total_atoms / (step_ms * 1e-3),
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 24 * n,
@@ -455,6 +467,9 @@ def main():
     parser.add_argument("--cells", type=int, default=SUPERCELL, help="SrTiO3 supercell edge (per GPU); default 10 = 5,000 atoms")
     parser.add_argument("--md-steps", type=int, default=0, help="also run this many NVE steps (1 fs, 300 K) and report the drift")
     parser.add_argument("--tile", type=int, default=0, help="receivers per tile for tiled streaming (0 = off)")
+    parser.add_argument("--workload", default="srtio3", choices=["srtio3", "random"],
+                        help="srtio3: medium model on SrTiO3 (default); random: 0e+1o+2e model on a disordered 10-element solid")
+    parser.add_argument("--atoms", type=int, default=20000, help="atoms of the random workload")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -329,7 +329,7 @@ struct ForceOutputs {
     double* atom_forces;     // [N][3], internal node order
     double* virial_slots;    // [kVirialSlots][9]
     double* edge_forces;     // optional [E][3] directed forces dE/d(xyz_ij), may be nullptr
-    int accumulate_edge;     // 0: overwrite edge_forces, 1: add
+    int accumulate_edge;     // 0: overwrite edge_forces, 1: add, 2: add atomically (several kernels share an edge)
 };
 
 __device__ __forceinline__ void warp_reduce3(float& a, float& b, float& c)
@@ -413,7 +413,8 @@ __device__ __forceinline__ void flush_chunk_forces(ForceScratch<kMaxWarps>& fs, 
         v[6] += ez * rx; v[7] += ez * ry; v[8] += ez * rz;
         if (out.edge_forces != nullptr) {
             double* ef = out.edge_forces + 3 * static_cast<size_t>(chunk_begin + t);
-            if (out.accumulate_edge) { ef[0] += ex; ef[1] += ey; ef[2] += ez; }
+            if (out.accumulate_edge == 2) { atomicAdd(ef, ex); atomicAdd(ef + 1, ey); atomicAdd(ef + 2, ez); }
+            else if (out.accumulate_edge) { ef[0] += ex; ef[1] += ey; ef[2] += ez; }
             else { ef[0] = ex; ef[1] = ey; ef[2] = ez; }
         }
     }

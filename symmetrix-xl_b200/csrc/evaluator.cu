@@ -14,6 +14,7 @@
 #include <numeric>
 
 #include "edge_kernels.cuh"
+#include "edge_kernels_split.cuh"
 #include "edge_kernels_warp.cuh"
 #include "graph_kernels.cuh"
 #include "node_kernels.cuh"
@@ -101,8 +102,9 @@ Evaluator::Evaluator(const std::string& json_path, int device_ordinal) : device_
     if (device_ordinal < 0 || device_ordinal >= count) throw std::invalid_argument("CUDA device ordinal is out of range.");
     SXB_CUDA(cudaSetDevice(device_));
     model_ = load_model(json_path);
-    if (model_.shape_id > 1)
-        throw std::invalid_argument("This build carries kernels for hidden irreps 0e and 0e+1o only.");
+    if (model_.shape_id > 2) throw std::invalid_argument("This build carries kernels for hidden irreps up to 0e+1o+2e only.");
+    if (model_.shape_id == 2 && model_.channels != 128)
+        throw std::invalid_argument("Hidden irreps 0e+1o+2e are compiled for 128 channels only.");
     SXB_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
     SXB_CUDA(cudaEventCreate(&event_begin_));
     SXB_CUDA(cudaEventCreate(&event_end_));
@@ -664,8 +666,10 @@ void Evaluator::run_pipeline(int phases)
             float* m0 = M0_.ptr + t0 * rowH;
             if (model_.shape_id == 0)
                 SXB_LAUNCH_POLY(m0_forward_kernel_S0, poly_g_forward_, SXB_S0_M0_NUM_TERMS, T, C, stream_, T, C, A0_.ptr, element_.ptr + t0, m0_weights_.ptr, m0);
-            else
+            else if (model_.shape_id == 1)
                 SXB_LAUNCH_POLY(m0_forward_kernel_S1, poly_g_forward_, SXB_S1_M0_NUM_TERMS, T, C, stream_, T, C, A0_.ptr, element_.ptr + t0, m0_weights_.ptr, m0);
+            else
+                SXB_LAUNCH_POLY(m0_forward_kernel_S2, poly_g_forward_, SXB_S2_M0_NUM_TERMS, T, C, stream_, T, C, A0_.ptr, element_.ptr + t0, m0_weights_.ptr, m0);
             launches_ += 1;
             span_end();
             // H1_il = M0_il W_l
@@ -680,15 +684,28 @@ void Evaluator::run_pipeline(int phases)
         }
     }
     if (phases & 2) {
+        if (model_.shape_id == 2 && fo.edge_forces != nullptr)   // the split gradient kernels accumulate into it
+            SXB_CUDA(cudaMemsetAsync(fo.edge_forces, 0, sizeof(double) * 3 * static_cast<std::size_t>(num_edges_), stream_));
         for (int t0 = 0; t0 < R; t0 += tile_cap) {
             const int T = std::min(tile_cap, R - t0);
             span_begin("l1_forward");
             if (model_.shape_id == 0)
                 SXB_LAUNCH_BY_CHANNELS(l1_forward_kernel_S0, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
                                        reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, coupling_, Phi1_.ptr, inv1);
-            else
+            else if (model_.shape_id == 1)
                 SXB_LAUNCH_BY_CHANNELS(l1_forward_kernel_S1, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
                                        reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, coupling_, Phi1_.ptr, inv1);
+            else {
+                // one launch per path set; the sets write disjoint components of Phi1
+#define SXB_SPLIT_FORWARD(SET)                                                                                            \
+                l1_forward_split_kernel_S2_##SET<128><<<T, 128, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, \
+                    reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, coupling_, Phi1_.ptr, inv1)
+                SXB_SPLIT_FORWARD(G0);
+                SXB_SPLIT_FORWARD(G1);
+                SXB_SPLIT_FORWARD(G2);
+#undef SXB_SPLIT_FORWARD
+                launches_ += 2;
+            }
             launches_ += 1;
             span_end();
             // A1_il = Phi1_il W_l
@@ -707,8 +724,10 @@ void Evaluator::run_pipeline(int phases)
             span_begin("m1_forward");
             if (model_.shape_id == 0)
                 SXB_LAUNCH_POLY(m1_forward_kernel_S0, poly_g_forward_, SXB_S0_M1_NUM_TERMS, T, C, stream_, T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_.ptr);
-            else
+            else if (model_.shape_id == 1)
                 SXB_LAUNCH_POLY(m1_forward_kernel_S1, poly_g_forward_, SXB_S1_M1_NUM_TERMS, T, C, stream_, T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_.ptr);
+            else
+                SXB_LAUNCH_POLY(m1_forward_kernel_S2, poly_g_forward_, SXB_S2_M1_NUM_TERMS, T, C, stream_, T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_.ptr);
             launches_ += 1;
             span_end();
             // H2 = xs T_element + M1 W
@@ -737,8 +756,10 @@ void Evaluator::run_pipeline(int phases)
             span_begin("m1_reverse");
             if (model_.shape_id == 0)
                 SXB_LAUNCH_POLY(m1_reverse_kernel_S0, poly_g_reverse_, SXB_S0_M1_NUM_TERMS, T, C, stream_, T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_adj_.ptr, A1_adj_.ptr, model_.a1_scaled ? dot1_.ptr + t0 : nullptr);
-            else
+            else if (model_.shape_id == 1)
                 SXB_LAUNCH_POLY(m1_reverse_kernel_S1, poly_g_reverse_, SXB_S1_M1_NUM_TERMS, T, C, stream_, T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_adj_.ptr, A1_adj_.ptr, model_.a1_scaled ? dot1_.ptr + t0 : nullptr);
+            else
+                SXB_LAUNCH_POLY(m1_reverse_kernel_S2, poly_g_reverse_, SXB_S2_M1_NUM_TERMS, T, C, stream_, T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_adj_.ptr, A1_adj_.ptr, model_.a1_scaled ? dot1_.ptr + t0 : nullptr);
             launches_ += 1;
             span_end();
             span_begin("gemm_a1_reverse");
@@ -757,9 +778,23 @@ void Evaluator::run_pipeline(int phases)
             if (model_.shape_id == 0)
                 SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S0, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
                                        reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1);
-            else
+            else if (model_.shape_id == 1)
                 SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S1, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
                                        reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1);
+            else {
+                // one launch per path set; the sets add into the same edge forces, so those are cleared
+                // first and accumulated atomically
+                ForceOutputs split = fo;
+                split.accumulate_edge = 2;
+#define SXB_SPLIT_REVERSE(SET)                                                                                            \
+                l1_reverse_split_kernel_S2_##SET<128><<<T, 128, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, \
+                    reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, split, density1)
+                SXB_SPLIT_REVERSE(G0);
+                SXB_SPLIT_REVERSE(G1);
+                SXB_SPLIT_REVERSE(G2);
+#undef SXB_SPLIT_REVERSE
+                launches_ += 2;
+            }
             launches_ += 1;
             span_end();
         }
@@ -795,8 +830,10 @@ void Evaluator::run_pipeline(int phases)
             span_begin("m0_reverse");
             if (model_.shape_id == 0)
                 SXB_LAUNCH_POLY(m0_reverse_kernel_S0, poly_g_reverse_, SXB_S0_M0_NUM_TERMS, T, C, stream_, T, C, A0_.ptr, element_.ptr + t0, m0_weights_.ptr, M0_adj_.ptr, A0_adj_.ptr, model_.a0_scaled ? dot0_.ptr + t0 : nullptr);
-            else
+            else if (model_.shape_id == 1)
                 SXB_LAUNCH_POLY(m0_reverse_kernel_S1, poly_g_reverse_, SXB_S1_M0_NUM_TERMS, T, C, stream_, T, C, A0_.ptr, element_.ptr + t0, m0_weights_.ptr, M0_adj_.ptr, A0_adj_.ptr, model_.a0_scaled ? dot0_.ptr + t0 : nullptr);
+            else
+                SXB_LAUNCH_POLY(m0_reverse_kernel_S2, poly_g_reverse_, SXB_S2_M0_NUM_TERMS, T, C, stream_, T, C, A0_.ptr, element_.ptr + t0, m0_weights_.ptr, M0_adj_.ptr, A0_adj_.ptr, model_.a0_scaled ? dot0_.ptr + t0 : nullptr);
             launches_ += 1;
             span_end();
             span_begin("l0_reverse");

@@ -25,10 +25,11 @@ def _load_pkg():
     return mod
 
 
-SHAPES = [("S0", 3, 0), ("S1", 3, 1), ("S2", 3, 2)]
+# (name, edge l_max, hidden L_max, path sets of the split layer-1 kernels)
+SHAPES = [("S0", 3, 0, 1), ("S1", 3, 1, 1), ("S2", 3, 2, 3)]
 
 
-def emit_shape(name, l_max, L_max, tables):
+def emit_shape(name, l_max, L_max, tables, groups=1):
     out = []
     paths = list(zip(tables["Phi1_l"], tables["Phi1_l1"], tables["Phi1_l2"]))
     num_lm, num_LM = (l_max + 1) ** 2, (L_max + 1) ** 2
@@ -126,8 +127,92 @@ def emit_shape(name, l_max, L_max, tables):
     out.append(" \\\n".join(fwd))
     out.append(f"#define SXB_{name}_L1_REVERSE_BODY \\")
     out.append(" \\\n".join(rev))
+    if groups > 1:
+        out.extend(emit_path_groups(name, paths, row_begin, tables, groups))
     out.append("")
     return "\n".join(out)
+
+
+def emit_path_groups(name, paths, row_begin, tables, groups):
+    """Splits the paths of a shape into `groups` sets with balanced row counts and emits, per set,
+    the same straight-line bodies with rows, paths and outputs renumbered inside the set.  Every
+    output component (lme) is fed by exactly one path, so the sets write disjoint outputs; a kernel
+    instance that handles one set needs only that set's row accumulators in registers."""
+    sizes = [(2 * l1 + 1) * (2 * l2 + 1) for (_, l1, l2) in paths]
+    members = [[] for _ in range(groups)]
+    load = [0] * groups
+    for p in sorted(range(len(paths)), key=lambda q: -sizes[q]):      # largest first, to the lightest set
+        g = min(range(groups), key=lambda q: load[q])
+        members[g].append(p)
+        load[g] += sizes[p]
+    row_path = []
+    for p, n in enumerate(sizes):
+        row_path += [p] * n
+    lme_path = {}
+    for row, lme in zip(tables["Phi1_lelm1lm2"], tables["Phi1_lme"]):
+        assert lme_path.setdefault(lme, row_path[row]) == row_path[row]
+    out = [f"#define SXB_{name}_NUM_GROUPS {groups}"]
+    for g, plist in enumerate(members):
+        plist = sorted(plist)
+        local_row, rows_g = {}, 0
+        for p in plist:
+            for r in range(sizes[p]):
+                local_row[row_begin[p] + r] = rows_g
+                rows_g += 1
+        lmes = sorted(lme for lme, p in lme_path.items() if p in plist)
+        local_lme = {lme: i for i, lme in enumerate(lmes)}
+        hmask = 0
+        for p in plist:
+            l2 = paths[p][2]
+            for b in range(l2 * l2, (l2 + 1) ** 2):
+                hmask |= 1 << b
+        pre = f"SXB_{name}_G{g}"
+        out.append(f"#define {pre}_NUM_PATHS {len(plist)}")
+        out.append(f"#define {pre}_NUM_ROWS {rows_g}")
+        out.append(f"#define {pre}_NUM_LME {len(lmes)}")
+        out.append(f"#define {pre}_PATH_LIST {{{', '.join(map(str, plist))}}}")
+        out.append(f"#define {pre}_LME_LIST {{{', '.join(map(str, lmes))}}}")
+        out.append(f"#define {pre}_SOURCE_MASK {hmask}u   // source components lm2 the set touches")
+        out.append(f"// X(term, row inside the set, output inside the set)")
+        out.append(f"#define {pre}_TERMS(X) \\")
+        out.append(" \\\n".join(f"    X({t}, {local_row[row]}, {local_lme[lme]})" for t, (row, lme) in
+                                enumerate(zip(tables["Phi1_lelm1lm2"], tables["Phi1_lme"])) if row in local_row))
+        fwd, rev = [], []
+        for q, p in enumerate(plist):
+            l, l1, l2 = paths[p]
+            n1, n2 = 2 * l1 + 1, 2 * l2 + 1
+            base = local_row[row_begin[p]]
+            fwd.append(f"    {{ /* path {p}: edge l={l1}, source l={l2} -> l={l} */")
+            for b in range(n2):
+                fwd.append(f"      const float t{b} = R[{q}] * h[{l2 * l2 + b}];")
+            for a in range(n1):
+                for b in range(n2):
+                    row = base + a * n2 + b
+                    fwd.append(f"      acc[{row}] = fmaf(t{b}, y[{l1 * l1 + a}], acc[{row}]);")
+            fwd.append("    }")
+            rev.append(f"    {{ /* path {p}: edge l={l1}, source l={l2} -> l={l} */")
+            rev.append("      float yw = 0.0f;")
+            for a in range(n1):
+                terms_ = [f"h[{l2 * l2 + b}] * adj[{base + a * n2 + b}]" for b in range(n2)]
+                expr = terms_[0]
+                for t_ in terms_[1:]:
+                    hh, aa = t_.split(" * ")
+                    expr = f"fmaf({hh}, {aa}, {expr})"
+                rev.append(f"      {{ const float w = {expr};")
+                rev.append(f"        ang[{l1 * l1 + a}] = fmaf(R[{q}], w, ang[{l1 * l1 + a}]); yw = fmaf(y[{l1 * l1 + a}], w, yw); }}")
+            rev.append(f"      radial = fmaf(dR[{q}], yw, radial);")
+            for b in range(n2):
+                terms_ = [(f"y[{l1 * l1 + a}]", f"adj[{base + a * n2 + b}]") for a in range(n1)]
+                expr = f"{terms_[0][0]} * {terms_[0][1]}"
+                for yy, aa in terms_[1:]:
+                    expr = f"fmaf({yy}, {aa}, {expr})"
+                rev.append(f"      hadj[{l2 * l2 + b}] = fmaf(R[{q}], {expr}, hadj[{l2 * l2 + b}]);")
+            rev.append("    }")
+        out.append(f"#define {pre}_FORWARD_BODY \\")
+        out.append(" \\\n".join(fwd))
+        out.append(f"#define {pre}_REVERSE_BODY \\")
+        out.append(" \\\n".join(rev))
+    return out
 
 
 def main():
@@ -135,9 +220,9 @@ def main():
     text = ["// Generated by symmetrix-xl_b200/csrc/gen_structures.py -- do not edit.",
             "// Coupling structure of the supported model shapes as X-macro lists.",
             "#pragma once", ""]
-    for name, l_max, L_max in SHAPES:
+    for name, l_max, L_max, groups in SHAPES:
         tables = pkg.modelgen.model_tables(l_max, L_max)
-        text.append(emit_shape(name, l_max, L_max, tables))
+        text.append(emit_shape(name, l_max, L_max, tables, groups))
     target = PKG / "csrc" / "generated" / "structures.h"
     target.write_text("\n".join(text))
     print("wrote", target)

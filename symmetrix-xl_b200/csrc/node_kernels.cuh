@@ -240,6 +240,7 @@ __device__ __forceinline__ void stage_poly_weights(float* __restrict__ dst, cons
 
 SXB_DEFINE_POLY_KERNELS(S0)
 SXB_DEFINE_POLY_KERNELS(S1)
+SXB_DEFINE_POLY_KERNELS(S2)
 
 // ---------------------------------------------------------------------------------------------
 // Channel-mixing linear as a tiled FP32 GEMM with structured rows.

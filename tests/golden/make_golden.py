@@ -41,7 +41,9 @@ def evaluator_goldens():
 
     pkg = graft.load_package()
     # the third case is a density-scaled model (A0_scaled and A1_scaled, mace.cpp:1562-1636, 2381-2458)
-    for arch, cells, cutoff, scaled in (("small", 2, 5.0, False), ("medium", 2, 6.0, False), ("medium", 2, 6.0, True)):
+    # and the fourth has hidden irreps up to l = 2 (17 paths, 243 rows)
+    for arch, cells, cutoff, scaled in (("small", 2, 5.0, False), ("medium", 2, 6.0, False), ("medium", 2, 6.0, True),
+                                        ("large", 2, 6.0, False)):
         with tempfile.TemporaryDirectory() as tmp:
             path = Path(tmp) / "model.json"
             pkg.modelgen.write_model(path, arch, seed=101, a0_scaled=scaled, a1_scaled=scaled)

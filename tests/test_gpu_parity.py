@@ -56,7 +56,7 @@ def test_neighbor_graph_triclinic_and_wrapped(pkg, model_path):
 SCALED_STAGES = ["A0", "M0", "H1", "A1", "M1", "H2", "H2_adj", "H1_adj", "M0_adj"]
 
 
-@pytest.mark.parametrize("arch,n,scaled", [("small", 3, False), ("medium", 2, False), ("medium", 2, True), ("small", 3, True)])
+@pytest.mark.parametrize("arch,n,scaled", [("small", 3, False), ("medium", 2, False), ("medium", 2, True), ("small", 3, True), ("large", 2, False), ("large", 2, True)])
 def test_stage_tensors_match_oracle(pkg, model_path, arch, n, scaled):
     path = model_path(arch, a0_scaled=scaled, a1_scaled=scaled)
     pos, cell, types = pkg.modelgen.srtio3(n, 0.05, 11)
@@ -76,7 +76,7 @@ def test_stage_tensors_match_oracle(pkg, model_path, arch, n, scaled):
     assert de <= TOL_E and df <= TOL_F
 
 
-@pytest.mark.parametrize("arch,n,seed,scaled", [("small", 4, 0, False), ("medium", 3, 1, False), ("medium", 3, 2, True)])
+@pytest.mark.parametrize("arch,n,seed,scaled", [("small", 4, 0, False), ("medium", 3, 1, False), ("medium", 3, 2, True), ("large", 2, 3, False)])
 def test_energy_forces_stress_vs_reference_evaluator(pkg, model_path, arch, n, seed, scaled):
     """Against the reference's own serial evaluator (MACECPU<double> and <float>)."""
     if not ref.available():
@@ -203,7 +203,7 @@ def test_graphless_force_and_stress_reduction(pkg, model_path):
 
 @pytest.mark.parametrize("arch,cells,tile,scaled", [("small", (2, 2, 2), 4, False), ("small", (3, 2, 2), 7, False),
                                                     ("medium", (2, 2, 2), 16, False), ("medium", (3, 2, 2), 32, False),
-                                                    ("medium", (2, 2, 2), 16, True)])
+                                                    ("medium", (2, 2, 2), 16, True), ("large", (2, 2, 2), 16, False)])
 def test_tiled_streaming_matches_untiled(pkg, model_path, arch, cells, tile, scaled):
     """Tiled streaming with a reusable workspace against the one-tile evaluation
     (reference: symmetrix/test/test_dual_layer_fixed_workspace.py:104-146, rtol 2e-4 / atol 2e-5)."""

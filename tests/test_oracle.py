@@ -11,7 +11,7 @@ from oracle import mace_numpy, neighbor, ref
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
 
-@pytest.mark.parametrize("arch,scaled", [("small", False), ("medium", False), ("medium", True)])
+@pytest.mark.parametrize("arch,scaled", [("small", False), ("medium", False), ("medium", True), ("large", False)])
 def test_numpy_restatement_matches_reference_evaluator_golden(pkg, model_dir, arch, scaled):
     g = np.load(GOLDEN / f"reference_evaluator_{arch}{'_scaled' if scaled else ''}.npz")
     path = model_dir / f"golden_{arch}_{int(scaled)}.json"
