@@ -98,7 +98,7 @@ namespace sxb {
         const float scale = density.table != nullptr ? density.inv_scale[i] : 1.0f;                                  \
         /* the density force is one term per edge: the first path set carries it */                                 \
         const float density_coef =                                                                                   \
-            (density.table != nullptr && path_of[0] == SXB_##NAME##_FIRST_SET_PATH) ? density.dot[i] * scale : 0.0f; \
+            (density.table != nullptr && SXB_##NAME##_##G##_HAS_PATH0) ? density.dot[i] * scale : 0.0f;              \
         float adj[NRG];                                                                                              \
         {                                                                                                            \
             float dphi[NEG];                                                                                         \
@@ -141,11 +141,14 @@ namespace sxb {
                 {                                                                                                    \
                     float g[16];                                                                                     \
                     load16(s.gx[t], g);                                                                              \
-                    _Pragma("unroll") for (int q = 0; q < 16; ++q) fx = fmaf(ang[q], g[q], fx);                      \
+                    _Pragma("unroll") for (int q = 0; q < 16; ++q)                                                   \
+                        if ((SXB_##NAME##_##G##_EDGE_MASK >> q) & 1u) fx = fmaf(ang[q], g[q], fx);                   \
                     load16(s.gy[t], g);                                                                              \
-                    _Pragma("unroll") for (int q = 0; q < 16; ++q) fy = fmaf(ang[q], g[q], fy);                      \
+                    _Pragma("unroll") for (int q = 0; q < 16; ++q)                                                   \
+                        if ((SXB_##NAME##_##G##_EDGE_MASK >> q) & 1u) fy = fmaf(ang[q], g[q], fy);                   \
                     load16(s.gz[t], g);                                                                              \
-                    _Pragma("unroll") for (int q = 0; q < 16; ++q) fz = fmaf(ang[q], g[q], fz);                      \
+                    _Pragma("unroll") for (int q = 0; q < 16; ++q)                                                   \
+                        if ((SXB_##NAME##_##G##_EDGE_MASK >> q) & 1u) fz = fmaf(ang[q], g[q], fz);                   \
                 }                                                                                                    \
                 const float total = warp_reduce3_transposed(fx, fy, fz, lane);                                       \
                 if ((lane & 7) == 0 && lane < 24) fs.partial[t][warp][lane >> 3] = total;                            \
@@ -156,8 +159,6 @@ namespace sxb {
         finish_receiver_forces<kWarps>(fs, i, out);                                                                  \
     }
 
-// the set that contains path 0 adds the per-edge density force
-#define SXB_S2_FIRST_SET_PATH 0
 SXB_DEFINE_L1_SPLIT_KERNELS(S2, G0)
 SXB_DEFINE_L1_SPLIT_KERNELS(S2, G1)
 SXB_DEFINE_L1_SPLIT_KERNELS(S2, G2)

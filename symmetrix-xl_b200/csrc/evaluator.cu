@@ -19,6 +19,7 @@
 #include "graph_kernels.cuh"
 #include "node_kernels.cuh"
 #include "tc_gemm.cuh"
+#include "tc_gemm_tma.cuh"
 
 namespace sxb {
 
@@ -147,6 +148,9 @@ Evaluator::Evaluator(const std::string& json_path, int device_ordinal) : device_
         upload_split(s_h2_skip_[a], model_.h2_skip.data() + static_cast<std::size_t>(a) * C * C, C, C);
     upload_split(s_h2_m1_, model_.h2_m1.data(), C, C);
     SXB_CUDA(cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes));
+    SXB_CUDA(cudaFuncSetAttribute(tc_gemm_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kT3SmemBytes));
+    SXB_CUDA(cudaDeviceGetAttribute(&num_sms_, cudaDevAttrMultiProcessorCount, device_));
+    if (const char* env = std::getenv("SXB_TMA_ACTIVATIONS")) use_tma_activations_ = env[0] != '0';
     std::memset(&coupling_, 0, sizeof(coupling_));
     if (model_.num_terms > 256) throw std::invalid_argument("Too many coupling terms.");
     for (int t = 0; t < model_.num_terms; ++t) coupling_.cg[t] = model_.cg[t];
@@ -544,10 +548,35 @@ void Evaluator::upload_split(SplitWeight& out, const float* w, int rows, int col
     out.map_fwd_lo = make_weight_map(out.fwd_lo.ptr, cols, rows, std::min(cols, kTcNTile));
     out.map_rev_hi = make_weight_map(out.rev_hi.ptr, rows, cols, std::min(rows, kTcNTile));
     out.map_rev_lo = make_weight_map(out.rev_lo.ptr, rows, cols, std::min(rows, kTcNTile));
+    out.wide_fwd_hi = make_weight_map(out.fwd_hi.ptr, cols, rows, std::min(cols, 128));
+    out.wide_fwd_lo = make_weight_map(out.fwd_lo.ptr, cols, rows, std::min(cols, 128));
+    out.wide_rev_hi = make_weight_map(out.rev_hi.ptr, rows, cols, std::min(rows, 128));
+    out.wide_rev_lo = make_weight_map(out.rev_lo.ptr, rows, cols, std::min(rows, 128));
 }
 
 // Runs a group of independent linears as one tensor-core launch (or as FP32 SIMT launches when the
 // tensor-core path is switched off for comparison).
+namespace {
+// Rank-3 view [node][component][K] of the A rows of a linear (K contiguous floats per row), boxes of
+// whole nodes: box = [nodes_per_tile][components][32 floats], 128-byte swizzle.
+CUtensorMap make_activation_map(const float* A, const RowMap& rows, int first_node, int num_nodes, int K, int nodes_per_tile)
+{
+    CUtensorMap map;
+    const float* base = A + rows.offset + static_cast<long>(first_node) * rows.node_stride;
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows.components), static_cast<cuuint64_t>(num_nodes)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(rows.component_stride) * sizeof(float),
+                                   static_cast<cuuint64_t>(rows.node_stride) * sizeof(float)};
+    const cuuint32_t box[3] = {static_cast<cuuint32_t>(kTcChunk), static_cast<cuuint32_t>(rows.components),
+                               static_cast<cuuint32_t>(nodes_per_tile)};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    const CUresult rc = encode_tiled_entry()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, elem,
+                                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed for an activation tensor.");
+    return map;
+}
+}  // namespace
+
 void Evaluator::launch_tc(const std::vector<TcCall>& calls)
 {
     if (!use_tensor_cores_) {
@@ -555,6 +584,51 @@ void Evaluator::launch_tc(const std::vector<TcCall>& calls)
             const int N = c.reverse ? c.w->rows : c.w->cols, K = c.reverse ? c.w->cols : c.w->rows;
             launch_gemm(c.A, c.a_rows, c.w->full.ptr, c.w->cols, c.reverse, c.C, c.c_rows, c.first_node, c.num_nodes, N, K,
                         c.accumulate, c.bias);
+        }
+        return;
+    }
+    bool streaming = use_tma_activations_;
+    for (const auto& c : calls) {
+        const int N = c.reverse ? c.w->rows : c.w->cols;
+        const int n_tile = std::min(N, 128);
+        if ((n_tile != 32 && n_tile != 64 && n_tile != 128) || N % n_tile != 0) streaming = false;
+    }
+    if (streaming) {
+        std::size_t next = 0;
+        while (next < calls.size()) {
+            Tc3Batch batch;
+            std::memset(static_cast<void*>(&batch), 0, sizeof(batch));
+            int tiles = 0, count = 0;
+            for (; next < calls.size() && count < kT3MaxProblems; ++next) {
+                const auto& c = calls[next];
+                if (c.num_nodes <= 0) continue;
+                Tc3Problem& p = batch.problem[count];
+                p.N = c.reverse ? c.w->rows : c.w->cols;
+                p.K = c.reverse ? c.w->cols : c.w->rows;
+                if (p.K % kTcChunk != 0) throw std::invalid_argument("Linear extents are not supported by the tensor-core kernel.");
+                p.n_tile = std::min(p.N, 128);
+                p.n_tiles = p.N / p.n_tile;
+                p.nodes_per_tile = kTcRows / c.a_rows.components;
+                p.rows_per_tile = p.nodes_per_tile * c.a_rows.components;
+                p.map_a = make_activation_map(c.A, c.a_rows, c.first_node, c.num_nodes, p.K, p.nodes_per_tile);
+                p.map_hi = c.reverse ? c.w->wide_rev_hi : c.w->wide_fwd_hi;
+                p.map_lo = c.reverse ? c.w->wide_rev_lo : c.w->wide_fwd_lo;
+                p.C = c.C;
+                p.bias = c.bias;
+                p.c_rows = c.c_rows;
+                p.first_node = c.first_node;
+                p.M = c.num_nodes * c.a_rows.components;
+                p.accumulate = c.accumulate ? 1 : 0;
+                p.m_tiles = (c.num_nodes + p.nodes_per_tile - 1) / p.nodes_per_tile;
+                p.tile_begin = tiles;
+                tiles += p.m_tiles * p.n_tiles;
+                ++count;
+            }
+            if (count == 0) continue;
+            batch.count = count;
+            batch.total_tiles = tiles;
+            tc_gemm_tma_kernel<<<std::min(tiles, num_sms_), kT3Threads, kT3SmemBytes, stream_>>>(batch, error_flag_.ptr);
+            launches_ += 1;
         }
         return;
     }

@@ -102,10 +102,13 @@ private:
         DeviceBuffer<float> fwd_hi, fwd_lo, rev_hi, rev_lo, full;
         int rows = 0, cols = 0;   // W is [rows = K of fwd][cols = N of fwd]
         CUtensorMap map_fwd_hi, map_fwd_lo, map_rev_hi, map_rev_lo;   // [N][K] tensors, box [n_tile][32]
+        CUtensorMap wide_fwd_hi, wide_fwd_lo, wide_rev_hi, wide_rev_lo;   // the same with box [min(N, 128)][32]
     };
     SplitWeight s_h1_[4], s_a1_[4], s_h2_m1_;
     std::vector<SplitWeight> s_h2_skip_;
     bool use_tensor_cores_ = true;
+    int num_sms_ = 148;
+    bool use_tma_activations_ = true;   // operand-streaming form of the tensor-core linears (N in {32, 64, 128})
     int poly_g_forward_ = 1, poly_g_reverse_ = 1;   // nodes per thread in the symmetric-contraction kernels
     void upload_split(SplitWeight& out, const float* w, int rows, int cols);
     struct TcCall {

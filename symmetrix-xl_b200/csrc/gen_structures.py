@@ -25,11 +25,11 @@ def _load_pkg():
     return mod
 
 
-# (name, edge l_max, hidden L_max, path sets of the split layer-1 kernels)
-SHAPES = [("S0", 3, 0, 1), ("S1", 3, 1, 1), ("S2", 3, 2, 3)]
+# (name, edge l_max, hidden L_max, path sets of the split layer-1 kernels, optional set of each edge l)
+SHAPES = [("S0", 3, 0, 1, None), ("S1", 3, 1, 1, None), ("S2", 3, 2, 3, None)]
 
 
-def emit_shape(name, l_max, L_max, tables, groups=1):
+def emit_shape(name, l_max, L_max, tables, groups=1, by_edge_l=None):
     out = []
     paths = list(zip(tables["Phi1_l"], tables["Phi1_l1"], tables["Phi1_l2"]))
     num_lm, num_LM = (l_max + 1) ** 2, (L_max + 1) ** 2
@@ -128,12 +128,12 @@ def emit_shape(name, l_max, L_max, tables, groups=1):
     out.append(f"#define SXB_{name}_L1_REVERSE_BODY \\")
     out.append(" \\\n".join(rev))
     if groups > 1:
-        out.extend(emit_path_groups(name, paths, row_begin, tables, groups))
+        out.extend(emit_path_groups(name, paths, row_begin, tables, groups, by_edge_l))
     out.append("")
     return "\n".join(out)
 
 
-def emit_path_groups(name, paths, row_begin, tables, groups):
+def emit_path_groups(name, paths, row_begin, tables, groups, by_edge_l=None):
     """Splits the paths of a shape into `groups` sets with balanced row counts and emits, per set,
     the same straight-line bodies with rows, paths and outputs renumbered inside the set.  Every
     output component (lme) is fed by exactly one path, so the sets write disjoint outputs; a kernel
@@ -141,10 +141,16 @@ def emit_path_groups(name, paths, row_begin, tables, groups):
     sizes = [(2 * l1 + 1) * (2 * l2 + 1) for (_, l1, l2) in paths]
     members = [[] for _ in range(groups)]
     load = [0] * groups
-    for p in sorted(range(len(paths)), key=lambda q: -sizes[q]):      # largest first, to the lightest set
-        g = min(range(groups), key=lambda q: load[q])
-        members[g].append(p)
-        load[g] += sizes[p]
+    if by_edge_l is not None:
+        # sets chosen by the edge l of the path: the sets then also split the edge harmonics and the
+        # angular force terms between them, so that work is not repeated
+        for p, (_, l1, _) in enumerate(paths):
+            members[by_edge_l[l1]].append(p)
+    else:
+        for p in sorted(range(len(paths)), key=lambda q: -sizes[q]):      # largest first, to the lightest set
+            g = min(range(groups), key=lambda q: load[q])
+            members[g].append(p)
+            load[g] += sizes[p]
     row_path = []
     for p, n in enumerate(sizes):
         row_path += [p] * n
@@ -161,11 +167,13 @@ def emit_path_groups(name, paths, row_begin, tables, groups):
                 rows_g += 1
         lmes = sorted(lme for lme, p in lme_path.items() if p in plist)
         local_lme = {lme: i for i, lme in enumerate(lmes)}
-        hmask = 0
+        hmask, emask = 0, 0
         for p in plist:
-            l2 = paths[p][2]
+            l1, l2 = paths[p][1], paths[p][2]
             for b in range(l2 * l2, (l2 + 1) ** 2):
                 hmask |= 1 << b
+            for a in range(l1 * l1, (l1 + 1) ** 2):
+                emask |= 1 << a
         pre = f"SXB_{name}_G{g}"
         out.append(f"#define {pre}_NUM_PATHS {len(plist)}")
         out.append(f"#define {pre}_NUM_ROWS {rows_g}")
@@ -173,6 +181,8 @@ def emit_path_groups(name, paths, row_begin, tables, groups):
         out.append(f"#define {pre}_PATH_LIST {{{', '.join(map(str, plist))}}}")
         out.append(f"#define {pre}_LME_LIST {{{', '.join(map(str, lmes))}}}")
         out.append(f"#define {pre}_SOURCE_MASK {hmask}u   // source components lm2 the set touches")
+        out.append(f"#define {pre}_EDGE_MASK {emask}u   // edge harmonics lm1 the set touches")
+        out.append(f"#define {pre}_HAS_PATH0 {1 if 0 in plist else 0}")
         out.append(f"// X(term, row inside the set, output inside the set)")
         out.append(f"#define {pre}_TERMS(X) \\")
         out.append(" \\\n".join(f"    X({t}, {local_row[row]}, {local_lme[lme]})" for t, (row, lme) in
@@ -220,9 +230,9 @@ def main():
     text = ["// Generated by symmetrix-xl_b200/csrc/gen_structures.py -- do not edit.",
             "// Coupling structure of the supported model shapes as X-macro lists.",
             "#pragma once", ""]
-    for name, l_max, L_max, groups in SHAPES:
+    for name, l_max, L_max, groups, by_edge_l in SHAPES:
         tables = pkg.modelgen.model_tables(l_max, L_max)
-        text.append(emit_shape(name, l_max, L_max, tables, groups))
+        text.append(emit_shape(name, l_max, L_max, tables, groups, by_edge_l))
     target = PKG / "csrc" / "generated" / "structures.h"
     target.write_text("\n".join(text))
     print("wrote", target)
