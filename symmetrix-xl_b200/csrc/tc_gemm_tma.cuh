@@ -6,7 +6,7 @@
 //     tiles: operand stages and their mbarrier phases run on across tile boundaries;
 //   * the A rows (node, component, channel-block addressing) are fetched by the TMA engine as boxes
 //     of a rank-3 tensor [node][component][K] straight into the 128-byte-swizzled K-major layout,
-//     five K chunks deep (~64 KB of activations in flight per SM);
+//     four K chunks deep;
 //   * the tensor core reads the raw FP32 tile as the TF32 high part (it uses the upper 19 bits of
 //     every element, the same truncation the split uses); four warps only form the residual
 //     a - trunc(a) from shared memory into a second buffer;
@@ -15,8 +15,11 @@
 //     bytes per 32 columns) while the tensor core already works on tile i + 1.
 // A row tile holds floor(128 / components) whole nodes (128, 126, 125 or 126 rows); the remaining
 // accumulator lanes are never stored.  A column tile is min(N, 128) wide.
-// Thread roles: warps 0-3 residual, warps 4-7 epilogue, warp 8 lane 0 weight TMA + tcgen05.mma
-// issue (warp 8 also owns the tensor-memory allocation), warp 9 lane 0 activation TMA.
+// Thread roles: warps 0-3 residual, warps 4-7 epilogue, warp 8 lane 0 tcgen05.mma issue (warp 8 also
+// owns the tensor-memory allocation), warp 9 lane 0 weight TMA, warp 10 lane 0 activation TMA.  The
+// issuing thread is the narrow point of such a pipeline (every mbarrier or tcgen05 instruction costs
+// it 60-300 cycles of latency), so it does nothing else: per K chunk it waits on one barrier - the
+// weight copy and the 128 residual writers arrive on the same one - issues the 12 MMAs and commits.
 // Every wait is bounded: on expiry the kernel raises bit 1 of the status word, every role leaves
 // its loop, the producers wait (bounded) for their own copies in flight, the tensor memory is
 // freed and the CTA returns.
@@ -26,10 +29,11 @@
 
 namespace sxb {
 
-constexpr int kT3AStages = 4, kT3BStages = 3, kT3LoStages = 3;
+constexpr int kT3AStages = 4;                 // raw activation tiles in flight
+constexpr int kT3Stages = 3;                  // residual tiles and weight tiles (hi + lo)
 constexpr int kT3OperandBytes = 128 * 128;    // 128 rows x 32 floats
-constexpr int kT3SmemBytes = (kT3AStages + kT3LoStages + 2 * kT3BStages) * kT3OperandBytes + 512;
-constexpr int kT3Threads = 320;
+constexpr int kT3SmemBytes = (kT3AStages + 3 * kT3Stages) * kT3OperandBytes + 512;
+constexpr int kT3Threads = 352;
 constexpr int kT3AccColumns = 256;            // two accumulators of up to 128 columns
 
 struct alignas(64) Tc3Problem {
@@ -94,24 +98,21 @@ __global__ void __launch_bounds__(kT3Threads, 1) tc_gemm_tma_kernel(const __grid
     const int tid = threadIdx.x, warp = tid >> 5;
 
     unsigned char* a_raw = smem;                                                    // [kT3AStages]
-    unsigned char* a_lo = a_raw + kT3AStages * kT3OperandBytes;                     // [kT3LoStages]
-    unsigned char* b_buf = a_lo + kT3LoStages * kT3OperandBytes;                    // [kT3BStages][hi, lo]
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(b_buf + 2 * kT3BStages * kT3OperandBytes);
-    unsigned long long* full_a = bars;                       // [5] TMA transaction barriers
-    unsigned long long* free_a = full_a + kT3AStages;        // [5] tcgen05.commit
-    unsigned long long* full_b = free_a + kT3AStages;        // [3]
-    unsigned long long* free_b = full_b + kT3BStages;        // [3]
-    unsigned long long* lo_ready = free_b + kT3BStages;      // [2] 128 arrivals
-    unsigned long long* lo_free = lo_ready + kT3LoStages;    // [2] tcgen05.commit
-    unsigned long long* acc_full = lo_free + kT3LoStages;    // [2] tcgen05.commit
+    unsigned char* a_lo = a_raw + kT3AStages * kT3OperandBytes;                     // [kT3Stages]
+    unsigned char* b_buf = a_lo + kT3Stages * kT3OperandBytes;                      // [kT3Stages][hi, lo]
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(b_buf + 2 * kT3Stages * kT3OperandBytes);
+    unsigned long long* full_a = bars;                       // [4] activation TMA landed (transaction barrier)
+    unsigned long long* free_a = full_a + kT3AStages;        // [4] tcgen05.commit: raw tile read
+    unsigned long long* ready = free_a + kT3AStages;         // [3] weight TMA landed + 128 residual arrivals
+    unsigned long long* free_s = ready + kT3Stages;          // [3] tcgen05.commit: residual and weight tiles read
+    unsigned long long* acc_full = free_s + kT3Stages;       // [2] tcgen05.commit
     unsigned long long* acc_empty = acc_full + 2;            // [2] 128 arrivals
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_empty + 2);
     volatile int* failed = reinterpret_cast<volatile int*>(acc_empty + 3);
 
     if (tid == 256) {
         for (int s = 0; s < kT3AStages; ++s) { mbar_init(&full_a[s], 1); mbar_init(&free_a[s], 1); }
-        for (int s = 0; s < kT3BStages; ++s) { mbar_init(&full_b[s], 1); mbar_init(&free_b[s], 1); }
-        for (int s = 0; s < kT3LoStages; ++s) { mbar_init(&lo_ready[s], 128); mbar_init(&lo_free[s], 1); }
+        for (int s = 0; s < kT3Stages; ++s) { mbar_init(&ready[s], 129); mbar_init(&free_s[s], 1); }
         for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 128); }
         *failed = (smem_u32(smem) & 1023u) ? 1 : 0;   // the swizzled layout needs a 1 KB aligned base
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -133,12 +134,12 @@ __global__ void __launch_bounds__(kT3Threads, 1) tc_gemm_tma_kernel(const __grid
             const Tc3Item it = tc3_locate(batch, item);
             const int chunks = batch.problem[it.problem].K / kTcChunk;
             for (int c = 0; c < chunks; ++c, ++kc) {
-                const int sa = kc % kT3AStages, t = kc % kT3LoStages;
+                const int sa = kc % kT3AStages, s = kc % kT3Stages;
                 if (!mbar_wait(&full_a[sa], static_cast<unsigned>((kc / kT3AStages) & 1), failed)) break;
-                if (kc >= kT3LoStages &&
-                    !mbar_wait(&lo_free[t], static_cast<unsigned>((kc / kT3LoStages - 1) & 1), failed)) break;
+                // residual tile s was last read by chunk kc - 3
+                if (kc >= kT3Stages && !mbar_wait(&free_s[s], static_cast<unsigned>((kc / kT3Stages - 1) & 1), failed)) break;
                 const float4* src = reinterpret_cast<const float4*>(a_raw + sa * kT3OperandBytes);
-                float4* dst = reinterpret_cast<float4*>(a_lo + t * kT3OperandBytes);
+                float4* dst = reinterpret_cast<float4*>(a_lo + s * kT3OperandBytes);
 #pragma unroll
                 for (int p = 0; p < kT3OperandBytes / 16 / 128; ++p) {   // position-wise: the layouts are identical
                     const float4 v = src[p * 128 + tid];
@@ -150,7 +151,7 @@ __global__ void __launch_bounds__(kT3Threads, 1) tc_gemm_tma_kernel(const __grid
                     dst[p * 128 + tid] = lo;
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive(&lo_ready[t]);
+                mbar_arrive(&ready[s]);
             }
         }
     } else if (warp < 8) {
@@ -167,7 +168,9 @@ __global__ void __launch_bounds__(kT3Threads, 1) tc_gemm_tma_kernel(const __grid
             const bool store = row < P.rows_per_tile && g < P.M;
             const int col0 = it.n_index * P.n_tile;
             float* crow = store ? P.C + row_address(P.c_rows, P.first_node, g) + col0 : nullptr;
-            for (int c0 = 0; c0 < P.n_tile; c0 += 32) {
+            const int n_tile = P.n_tile, accumulate = P.accumulate;
+            const float* bias = P.bias;
+            for (int c0 = 0; c0 < n_tile; c0 += 32) {
                 unsigned v[32];
                 const unsigned taddr = tmem_base + (static_cast<unsigned>(quarter * 32) << 16) + static_cast<unsigned>(b * 128 + c0);
                 asm volatile(
@@ -187,11 +190,11 @@ __global__ void __launch_bounds__(kT3Threads, 1) tc_gemm_tma_kernel(const __grid
                         float4 o = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]),
                                                __uint_as_float(v[4 * q + 3]));
                         float4* dst = reinterpret_cast<float4*>(crow + c0 + 4 * q);
-                        if (P.accumulate) {
+                        if (accumulate) {
                             const float4 old = *dst;
                             o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                        } else if (P.bias != nullptr) {
-                            const float4 bv = *reinterpret_cast<const float4*>(P.bias + col0 + c0 + 4 * q);
+                        } else if (bias != nullptr) {
+                            const float4 bv = *reinterpret_cast<const float4*>(bias + col0 + c0 + 4 * q);
                             o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
                         }
                         *dst = o;
@@ -203,51 +206,30 @@ __global__ void __launch_bounds__(kT3Threads, 1) tc_gemm_tma_kernel(const __grid
             mbar_arrive(&acc_empty[b]);
         }
     } else if (tid == 256) {
-        // ------------------------------------------------------------- weight TMA + MMA issue
-        int issued = 0;     // weight chunks requested so far (CTA-wide chunk counter)
-        int kc = 0;         // chunks whose MMAs have been issued
-        int j = 0;
-        // weight chunks are requested kT3BStages - 1 ahead of the MMAs, across work-item boundaries
-        int ahead_item = first_item, ahead_chunk = 0;
-        auto issue_next_b = [&]() -> bool {
-            if (ahead_item >= batch.total_tiles) return true;
-            const Tc3Item it = tc3_locate(batch, ahead_item);
-            const Tc3Problem& P = batch.problem[it.problem];
-            const int s = issued % kT3BStages, use = issued / kT3BStages;
-            if (use > 0 && !mbar_wait(&free_b[s], static_cast<unsigned>((use - 1) & 1), failed)) return false;
-            unsigned char* hi = b_buf + (2 * s) * kT3OperandBytes;
-            mbar_expect_tx(&full_b[s], 2u * static_cast<unsigned>(P.n_tile) * 128u);
-            const int k0 = tc3_rotated_chunk(ahead_item, ahead_chunk, P.K / kTcChunk) * kTcChunk;
-            tma_load_2d(hi, &P.map_hi, &full_b[s], k0, it.n_index * P.n_tile);
-            tma_load_2d(hi + kT3OperandBytes, &P.map_lo, &full_b[s], k0, it.n_index * P.n_tile);
-            ++issued;
-            if (++ahead_chunk == P.K / kTcChunk) { ahead_chunk = 0; ahead_item += item_step; }
-            return true;
-        };
+        // ------------------------------------------------------------- tcgen05.mma issue: one wait and 12 MMAs per chunk
+        const unsigned a_raw_addr = smem_u32(a_raw), a_lo_addr = smem_u32(a_lo), b_addr = smem_u32(b_buf);
+        int kc = 0, j = 0;
         if (!*failed) {
             bool ok = true;
-            for (int q = 0; q < kT3BStages - 1 && ok; ++q) ok = issue_next_b();
             for (int item = first_item; item < batch.total_tiles && ok; item += item_step, ++j) {
                 const Tc3Item it = tc3_locate(batch, item);
-                const Tc3Problem& P = batch.problem[it.problem];
-                const int NT = P.n_tile, chunks = P.K / kTcChunk, b = j & 1;
+                const int NT = batch.problem[it.problem].n_tile, chunks = batch.problem[it.problem].K / kTcChunk, b = j & 1;
                 // instruction descriptor: D = F32, A = B = TF32, both K-major, N = NT, M = 128
                 const unsigned idesc = (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<unsigned>(NT >> 3) << 17) |
                                        (static_cast<unsigned>(kTcRows >> 4) << 24);
                 // the epilogue must have drained this accumulator (work item j - 2)
-                if (j >= 2 && !mbar_wait(&acc_empty[b], static_cast<unsigned>(((j >> 1) - 1) & 1), failed)) { ok = false; break; }
+                if (j >= 2 && !mbar_wait(&acc_empty[b], static_cast<unsigned>(((j >> 1) - 1) & 1), failed)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned tmem_d = tmem_base + static_cast<unsigned>(b * 128);
                 for (int c = 0; c < chunks; ++c, ++kc) {
-                    const int sa = kc % kT3AStages, sb = kc % kT3BStages, t = kc % kT3LoStages;
-                    if (!mbar_wait(&full_b[sb], static_cast<unsigned>((kc / kT3BStages) & 1), failed)) { ok = false; break; }
-                    if (!mbar_wait(&full_a[sa], static_cast<unsigned>((kc / kT3AStages) & 1), failed)) { ok = false; break; }
-                    if (!mbar_wait(&lo_ready[t], static_cast<unsigned>((kc / kT3LoStages) & 1), failed)) { ok = false; break; }
+                    const int sa = kc % kT3AStages, s = kc % kT3Stages;
+                    // weights landed and the residual is written (which implies the raw tile landed)
+                    if (!mbar_wait(&ready[s], static_cast<unsigned>((kc / kT3Stages) & 1), failed)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const unsigned long long da_hi = umma_desc(smem_u32(a_raw + sa * kT3OperandBytes));
-                    const unsigned long long da_lo = umma_desc(smem_u32(a_lo + t * kT3OperandBytes));
-                    const unsigned b_addr = smem_u32(b_buf + (2 * sb) * kT3OperandBytes);
-                    const unsigned long long db_hi = umma_desc(b_addr), db_lo = umma_desc(b_addr + kT3OperandBytes);
+                    const unsigned long long da_hi = umma_desc(a_raw_addr + sa * kT3OperandBytes);
+                    const unsigned long long da_lo = umma_desc(a_lo_addr + s * kT3OperandBytes);
+                    const unsigned long long db_hi = umma_desc(b_addr + (2 * s) * kT3OperandBytes);
+                    const unsigned long long db_lo = umma_desc(b_addr + (2 * s + 1) * kT3OperandBytes);
 #pragma unroll
                     for (int ks = 0; ks < kTcChunk / 8; ++ks) {
                         const unsigned long long step = static_cast<unsigned long long>(ks * 2);   // 32 bytes along K
@@ -256,22 +238,40 @@ __global__ void __launch_bounds__(kT3Threads, 1) tc_gemm_tma_kernel(const __grid
                         umma_tf32(tmem_d, da_lo + step, db_hi + step, idesc, 1u);
                     }
                     umma_commit(&free_a[sa]);
-                    umma_commit(&free_b[sb]);
-                    umma_commit(&lo_free[t]);
+                    umma_commit(&free_s[s]);
                     if (c + 1 == chunks) umma_commit(&acc_full[b]);
-                    // refill: the stage the next request goes to was last read by chunk kc - 1; waiting for that
-                    // chunk here, with the MMAs of chunk kc already queued, leaves no gap on the tensor pipe
-                    if (!issue_next_b()) { ok = false; break; }
                 }
             }
-            // after a failure: let the weight copies still in flight land before the CTA exits
-            if (*failed)
-                for (int q = max(0, issued - kT3BStages); q < issued; ++q) {
-                    int never = 0;
-                    mbar_wait(&full_b[q % kT3BStages], static_cast<unsigned>((q / kT3BStages) & 1), &never);
-                }
         }
     } else if (tid == 288) {
+        // ------------------------------------------------------------- weight TMA
+        int issued = 0;
+        if (!*failed) {
+            bool ok = true;
+            for (int item = first_item; item < batch.total_tiles && ok; item += item_step) {
+                const Tc3Item it = tc3_locate(batch, item);
+                const Tc3Problem& P = batch.problem[it.problem];
+                const unsigned bytes = 2u * static_cast<unsigned>(P.n_tile) * 128u;
+                const int chunks = P.K / kTcChunk, n0 = it.n_index * P.n_tile;
+                for (int c = 0; c < chunks; ++c) {
+                    const int s = issued % kT3Stages, use = issued / kT3Stages;
+                    if (use > 0 && !mbar_wait(&free_s[s], static_cast<unsigned>((use - 1) & 1), failed)) { ok = false; break; }
+                    unsigned char* hi = b_buf + (2 * s) * kT3OperandBytes;
+                    const int k0 = tc3_rotated_chunk(item, c, chunks) * kTcChunk;
+                    mbar_expect_tx(&ready[s], bytes);
+                    tma_load_2d(hi, &P.map_hi, &ready[s], k0, n0);
+                    tma_load_2d(hi + kT3OperandBytes, &P.map_lo, &ready[s], k0, n0);
+                    ++issued;
+                }
+            }
+            // after a failure: let the copies still in flight land before the CTA exits
+            if (*failed)
+                for (int q = max(0, issued - kT3Stages); q < issued; ++q) {
+                    int never = 0;
+                    mbar_wait(&ready[q % kT3Stages], static_cast<unsigned>((q / kT3Stages) & 1), &never);
+                }
+        }
+    } else if (tid == 320) {
         // ------------------------------------------------------------- activation TMA
         int issued = 0;
         if (!*failed) {
