@@ -11,8 +11,8 @@
 //     every element, the same truncation the split uses); four warps only form the residual
 //     a - trunc(a) from shared memory into a second buffer;
 //   * the accumulator is double-buffered in tensor memory (2 x 128 columns): four epilogue warps
-//     write tile i straight from tensor memory (a thread owns one row and stores 128 contiguous
-//     bytes per 32 columns) while the tensor core already works on tile i + 1.
+//     write tile i (tensor memory -> registers -> a small transposing tile in shared memory ->
+//     whole 128-byte row segments) while the tensor core already works on tile i + 1.
 // A row tile holds floor(128 / components) whole nodes (128, 126, 125 or 126 rows); the remaining
 // accumulator lanes are never stored.  A column tile is min(N, 128) wide.
 // Thread roles: warps 0-3 residual, warps 4-7 epilogue, warp 8 lane 0 tcgen05.mma issue (warp 8 also
@@ -32,7 +32,8 @@ namespace sxb {
 constexpr int kT3AStages = 4;                 // raw activation tiles in flight
 constexpr int kT3Stages = 3;                  // residual tiles and weight tiles (hi + lo)
 constexpr int kT3OperandBytes = 128 * 128;    // 128 rows x 32 floats
-constexpr int kT3SmemBytes = (kT3AStages + 3 * kT3Stages) * kT3OperandBytes + 512;
+constexpr int kT3StagingBytes = 4 * 32 * 128;  // epilogue: 32 rows x 128 bytes per warp
+constexpr int kT3SmemBytes = (kT3AStages + 3 * kT3Stages) * kT3OperandBytes + kT3StagingBytes + 512;
 constexpr int kT3Threads = 352;
 constexpr int kT3AccColumns = 256;            // two accumulators of up to 128 columns
 
@@ -100,7 +101,8 @@ __global__ void __launch_bounds__(kT3Threads, 1) tc_gemm_tma_kernel(const __grid
     unsigned char* a_raw = smem;                                                    // [kT3AStages]
     unsigned char* a_lo = a_raw + kT3AStages * kT3OperandBytes;                     // [kT3Stages]
     unsigned char* b_buf = a_lo + kT3Stages * kT3OperandBytes;                      // [kT3Stages][hi, lo]
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(b_buf + 2 * kT3Stages * kT3OperandBytes);
+    unsigned char* staging = b_buf + 2 * kT3Stages * kT3OperandBytes;               // [4 epilogue warps][32 rows][128 B]
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(staging + kT3StagingBytes);
     unsigned long long* full_a = bars;                       // [4] activation TMA landed (transaction barrier)
     unsigned long long* free_a = full_a + kT3AStages;        // [4] tcgen05.commit: raw tile read
     unsigned long long* ready = free_a + kT3AStages;         // [3] weight TMA landed + 128 residual arrivals
@@ -167,9 +169,13 @@ __global__ void __launch_bounds__(kT3Threads, 1) tc_gemm_tma_kernel(const __grid
             const int g = it.m_tile * P.rows_per_tile + row;
             const bool store = row < P.rows_per_tile && g < P.M;
             const int col0 = it.n_index * P.n_tile;
-            float* crow = store ? P.C + row_address(P.c_rows, P.first_node, g) + col0 : nullptr;
+            // row pointer of this lane's accumulator row (0 when the row is not stored)
+            const unsigned long long my_row_ptr =
+                store ? reinterpret_cast<unsigned long long>(P.C + row_address(P.c_rows, P.first_node, g) + col0) : 0ull;
             const int n_tile = P.n_tile, accumulate = P.accumulate;
             const float* bias = P.bias;
+            unsigned char* stage = staging + quarter * (32 * 128);
+            const int lane = tid & 31, sub_row = lane >> 3, sub_chunk = lane & 7;
             for (int c0 = 0; c0 < n_tile; c0 += 32) {
                 unsigned v[32];
                 const unsigned taddr = tmem_base + (static_cast<unsigned>(quarter * 32) << 16) + static_cast<unsigned>(b * 128 + c0);
@@ -184,17 +190,27 @@ __global__ void __launch_bounds__(kT3Threads, 1) tc_gemm_tma_kernel(const __grid
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (store) {
+                // a lane holds 32 columns of one row; through the warp's staging tile (16-byte chunks XORed by
+                // row, conflict-free both ways) the warp stores whole 128-byte row segments, four rows per pass
+                __syncwarp();
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                        float4 o = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]),
-                                               __uint_as_float(v[4 * q + 3]));
-                        float4* dst = reinterpret_cast<float4*>(crow + c0 + 4 * q);
+                for (int q = 0; q < 8; ++q)
+                    *reinterpret_cast<float4*>(stage + lane * 128 + ((q ^ (lane & 7)) << 4)) =
+                        make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]),
+                                    __uint_as_float(v[4 * q + 3]));
+                __syncwarp();
+#pragma unroll
+                for (int pass = 0; pass < 8; ++pass) {
+                    const int r = pass * 4 + sub_row;
+                    const unsigned long long ptr = __shfl_sync(0xffffffffu, my_row_ptr, r);
+                    if (ptr != 0ull) {
+                        float4 o = *reinterpret_cast<const float4*>(stage + r * 128 + ((sub_chunk ^ (r & 7)) << 4));
+                        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(ptr) + c0 + 4 * sub_chunk);
                         if (accumulate) {
                             const float4 old = *dst;
                             o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
                         } else if (bias != nullptr) {
-                            const float4 bv = *reinterpret_cast<const float4*>(bias + col0 + c0 + 4 * q);
+                            const float4 bv = *reinterpret_cast<const float4*>(bias + col0 + c0 + 4 * sub_chunk);
                             o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
                         }
                         *dst = o;
