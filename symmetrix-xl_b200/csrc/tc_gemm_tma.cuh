@@ -86,13 +86,6 @@ __device__ __forceinline__ Tc3Item tc3_locate(const Tc3Batch& batch, int item)
     return {pi, local / batch.problem[pi].n_tiles, local % batch.problem[pi].n_tiles};
 }
 
-// K chunk a work item visits at step c: every item starts at a different chunk, so the CTAs that
-// run in step do not all ask the L2 for the same weight tile at the same moment.
-__device__ __forceinline__ int tc3_rotated_chunk(int item, int c, int chunks)
-{
-    return (c + item * 5) % chunks;
-}
-
 __global__ void __launch_bounds__(kT3Threads, 1) tc_gemm_tma_kernel(const __grid_constant__ Tc3Batch batch, int* __restrict__ error_flag)
 {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -273,7 +266,7 @@ __global__ void __launch_bounds__(kT3Threads, 1) tc_gemm_tma_kernel(const __grid
                     const int s = issued % kT3Stages, use = issued / kT3Stages;
                     if (use > 0 && !mbar_wait(&free_s[s], static_cast<unsigned>((use - 1) & 1), failed)) { ok = false; break; }
                     unsigned char* hi = b_buf + (2 * s) * kT3OperandBytes;
-                    const int k0 = tc3_rotated_chunk(item, c, chunks) * kTcChunk;
+                    const int k0 = c * kTcChunk;
                     mbar_expect_tx(&ready[s], bytes);
                     tma_load_2d(hi, &P.map_hi, &ready[s], k0, n0);
                     tma_load_2d(hi + kT3OperandBytes, &P.map_lo, &ready[s], k0, n0);
@@ -301,7 +294,7 @@ __global__ void __launch_bounds__(kT3Threads, 1) tc_gemm_tma_kernel(const __grid
                     const int s = issued % kT3AStages, use = issued / kT3AStages;
                     if (use > 0 && !mbar_wait(&free_a[s], static_cast<unsigned>((use - 1) & 1), failed)) { ok = false; break; }
                     mbar_expect_tx(&full_a[s], bytes);
-                    tma_load_3d(a_raw + s * kT3OperandBytes, &P.map_a, &full_a[s], tc3_rotated_chunk(item, c, chunks) * kTcChunk, 0, node0);
+                    tma_load_3d(a_raw + s * kT3OperandBytes, &P.map_a, &full_a[s], c * kTcChunk, 0, node0);
                     ++issued;
                 }
             }
