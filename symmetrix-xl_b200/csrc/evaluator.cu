@@ -175,6 +175,7 @@ Evaluator::~Evaluator()
     if (event_end_) cudaEventDestroy(event_end_);
     for (auto e : event_pool_) cudaEventDestroy(e);
     if (stream_ && owns_stream_) cudaStreamDestroy(stream_);
+    if (host_mirror_) cudaFreeHost(host_mirror_);
 }
 
 void Evaluator::prepare_active_types(const std::vector<int>& node_types)
@@ -281,6 +282,7 @@ void Evaluator::install_graph(int num_receivers, int num_nodes, const std::vecto
     SXB_CUDA(cudaStreamSynchronize(stream_));
     generation_ += 1;
     have_results_ = false;
+    mirror_valid_ = false;
     phase_ = 0;
 }
 
@@ -941,6 +943,22 @@ void Evaluator::finish_compute()
     int flag = 0;
     SXB_CUDA(cudaMemcpyAsync(&flag, error_flag_.ptr, sizeof(int), cudaMemcpyDeviceToHost, stream_));
     SXB_CUDA(cudaMemcpyAsync(host_totals_, totals_.ptr, 10 * sizeof(double), cudaMemcpyDeviceToHost, stream_));
+    mirror_valid_ = false;
+    constexpr std::size_t kMirrorLimit = 4u << 20;   // doubles (32 MB): beyond this the getters copy on demand
+    const std::size_t mirror_doubles = static_cast<std::size_t>(num_receivers_) + 3 * static_cast<std::size_t>(num_nodes_);
+    if (mirror_requested_ && mirror_doubles <= kMirrorLimit) {
+        if (host_mirror_capacity_ < mirror_doubles) {
+            if (host_mirror_) SXB_CUDA(cudaFreeHost(host_mirror_));
+            host_mirror_ = nullptr;
+            host_mirror_capacity_ = 0;
+            SXB_CUDA(cudaMallocHost(reinterpret_cast<void**>(&host_mirror_), sizeof(double) * mirror_doubles));
+            host_mirror_capacity_ = mirror_doubles;
+        }
+        SXB_CUDA(cudaMemcpyAsync(host_mirror_, node_energies_out_.ptr, sizeof(double) * num_receivers_, cudaMemcpyDeviceToHost, stream_));
+        SXB_CUDA(cudaMemcpyAsync(host_mirror_ + num_receivers_, forces_out_.ptr, sizeof(double) * 3 * num_nodes_, cudaMemcpyDeviceToHost, stream_));
+        mirror_valid_ = true;
+    }
+    mirror_requested_ = false;
     SXB_CUDA(cudaStreamSynchronize(stream_));
     SXB_CUDA(cudaEventElapsedTime(&last_ms_, event_begin_, event_end_));
     profile_.clear();
@@ -960,8 +978,10 @@ void Evaluator::compute_positions(std::uint64_t generation, const double* positi
     if (!has_shifts_) throw std::invalid_argument("The prepared graph has no periodic shifts; use edge vectors.");
     SXB_CUDA(cudaSetDevice(device_));
     have_results_ = false;
+    mirror_valid_ = false;
     SXB_CUDA(cudaEventRecord(event_begin_, stream_));
     const double* dpos = positions;
+    mirror_requested_ = !on_device;
     if (!on_device) {
         SXB_CUDA(cudaMemcpyAsync(positions_.ptr, positions, sizeof(double) * 3 * num_nodes_, cudaMemcpyHostToDevice, stream_));
         dpos = positions_.ptr;
@@ -979,6 +999,7 @@ void Evaluator::compute_edge_vectors(std::uint64_t generation, const double* xyz
     check_generation(generation);
     SXB_CUDA(cudaSetDevice(device_));
     have_results_ = false;
+    mirror_valid_ = false;
     DeviceBuffer<double> dxyz;
     dxyz.reserve(3 * static_cast<std::size_t>(num_edges_));
     SXB_CUDA(cudaEventRecord(event_begin_, stream_));
@@ -1002,6 +1023,7 @@ void Evaluator::distributed_begin(std::uint64_t generation, const double* device
     }
     SXB_CUDA(cudaSetDevice(device_));
     have_results_ = false;
+    mirror_valid_ = false;
     SXB_CUDA(cudaEventRecord(event_begin_, stream_));
     SXB_CUDA(cudaMemsetAsync(error_flag_.ptr, 0, sizeof(int), stream_));
     geometry_from_positions_kernel<<<blocks_for(static_cast<long>(num_receivers_) * 32, 256), 256, 0, stream_>>>(
@@ -1131,6 +1153,7 @@ void Evaluator::synchronize()
     if (pending_finish_) {
         pending_finish_ = false;
         have_results_ = false;
+        mirror_valid_ = false;
         finish_compute();
         return;
     }
@@ -1145,6 +1168,10 @@ void Evaluator::require_results() const
 void Evaluator::get_node_energies(double* out)
 {
     require_results();
+    if (mirror_valid_) {
+        std::memcpy(out, host_mirror_, sizeof(double) * num_receivers_);
+        return;
+    }
     SXB_CUDA(cudaMemcpyAsync(out, node_energies_out_.ptr, sizeof(double) * num_receivers_, cudaMemcpyDeviceToHost, stream_));
     SXB_CUDA(cudaStreamSynchronize(stream_));
 }
@@ -1152,6 +1179,10 @@ void Evaluator::get_node_energies(double* out)
 void Evaluator::get_atom_forces(double* out)
 {
     require_results();
+    if (mirror_valid_) {
+        std::memcpy(out, host_mirror_ + num_receivers_, sizeof(double) * 3 * num_nodes_);
+        return;
+    }
     SXB_CUDA(cudaMemcpyAsync(out, forces_out_.ptr, sizeof(double) * 3 * num_nodes_, cudaMemcpyDeviceToHost, stream_));
     SXB_CUDA(cudaStreamSynchronize(stream_));
 }
@@ -1200,6 +1231,7 @@ void Evaluator::set_tile_size(int receivers_per_tile)
     tile_size_ = receivers_per_tile;
     generation_ += 1;      // buffers are sized at graph installation: the prepared graph becomes stale
     have_results_ = false;
+    mirror_valid_ = false;
 }
 
 long Evaluator::get_stage(const std::string& name, double* out, long capacity)

@@ -141,6 +141,11 @@ private:
     DeviceBuffer<double> totals_, energy_slots_, virial_slots_;
     DeviceBuffer<int> error_flag_;
     double host_totals_[10] = {0};
+    // pinned host mirror of the per-node results, filled by calls that take host inputs so that the
+    // result getters cost a host copy instead of a device copy and a synchronisation each
+    double* host_mirror_ = nullptr;          // [receivers] energies, then [nodes][3] forces
+    std::size_t host_mirror_capacity_ = 0;   // doubles
+    bool mirror_requested_ = false, mirror_valid_ = false;
     bool keep_edge_forces_ = false;
     bool have_results_ = false;
     long launches_ = 0;
