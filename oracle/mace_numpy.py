@@ -228,8 +228,15 @@ class NumpyMACE:
         m = model
         if m.get("radial_representation") != "compact" or m.get("h1_affine_mode") != "m0_composite":
             raise NotImplementedError("restated for compact, m0_composite models")
-        if m.get("has_zbl") or m.get("first_interaction_residual") or m.get("has_field_coupling"):
-            raise NotImplementedError("ZBL / residual / field coupling are not restated")
+        if m.get("first_interaction_residual") or m.get("has_field_coupling"):
+            raise NotImplementedError("residual / field coupling are not restated")
+        self.has_zbl = bool(m.get("has_zbl", False))
+        if self.has_zbl:                                                 # mace.cpp:2690-2699
+            self.zbl_a_exp, self.zbl_a_prefactor = float(m["zbl_a_exp"]), float(m["zbl_a_prefactor"])
+            self.zbl_c = np.asarray(m["zbl_c"], dtype=np.float64)
+            self.zbl_radii = np.asarray(m["zbl_covalent_radii"], dtype=np.float64)
+            self.zbl_p = int(m["zbl_p"])
+        self.atomic_numbers = np.asarray(m["atomic_numbers"], dtype=np.int64)
         self.dtype = dtype
         dt = dtype
         self.C = C = int(m["num_channels"])
@@ -401,10 +408,38 @@ class NumpyMACE:
         radial0 = (padj * dR0e * Y[:, :, None] * h0).sum(axis=(1, 2))
         ang0 = (padj * R0e * h0).sum(axis=2)
         forces -= radial0[:, None] * direction + np.einsum("em,edm->ed", ang0, Yg)   # mace.cpp:1505-1559
+        if self.has_zbl:                                                 # zbl.cpp:24-139, called at mace.cpp:247-250
+            ez, gz = self.zbl_pair(self.atomic_numbers[typ][recv], self.atomic_numbers[tj], r.astype(dt))
+            np.add.at(energies, recv, ez.astype(np.float64))
+            forces -= direction * gz[:, None].astype(dt)
         self.stage = dict(Y=Y, Y_grad=Yg, A0=A0, M0=M0, H1=H1, Phi1=Phi1, A1=A1, M1=M1, H2=H2,
                           H2_adj=H2_adj, A1_adj=A1_adj, dPhi1=dPhi1, H1_adj=H1_adj, M0_adj=M0_adj,
                           A0_adj=A0_adj, node_energies=energies, node_forces=forces)
         return energies, forces
+
+    def zbl_pair(self, Zu, Zv, r):
+        """Screened-Coulomb pair energy (half per directed edge) and its radial derivative with the
+        polynomial envelope (zbl.cpp:24-99)."""
+        dt = r.dtype
+        c_exps = np.array([-3.2, -0.9423, -0.4028, -0.2016], dtype=dt)      # zbl.hpp:47-50
+        v_pref = dt.type(14.3996)                                            # zbl.hpp:51
+        Zu_f, Zv_f = Zu.astype(dt), Zv.astype(dt)
+        a = dt.type(self.zbl_a_prefactor) * dt.type(0.529) / (Zu_f ** dt.type(self.zbl_a_exp) + Zv_f ** dt.type(self.zbl_a_exp))
+        x = r / a
+        e = self.zbl_c.astype(dt)[None, :] * np.exp(c_exps[None, :] * x[:, None])
+        phi = e.sum(axis=1)
+        dphi = (e * c_exps[None, :]).sum(axis=1) / a
+        v = v_pref * Zu_f * Zv_f / r * phi
+        dv = v_pref * Zu_f * Zv_f * (r * dphi - phi) / (r * r)
+        r_max = (self.zbl_radii[Zu] + self.zbl_radii[Zv]).astype(dt)
+        p = self.zbl_p
+        u = r / r_max
+        inside = r < r_max
+        env = np.where(inside, 1.0 - ((p + 1.0) * (p + 2.0) / 2.0) * u ** p + p * (p + 2.0) * u ** (p + 1)
+                       - (p * (p + 1.0) / 2.0) * u ** (p + 2), 0.0).astype(dt)
+        denv = np.where(inside, (-((p + 1.0) * (p + 2.0) / 2.0) * p * u ** (p - 1) + p * (p + 2.0) * (p + 1.0) * u ** p
+                                 - (p * (p + 1.0) / 2.0) * (p + 2.0) * u ** (p + 1)) / r_max, 0.0).astype(dt)
+        return dt.type(0.5) * v * env, dt.type(0.5) * (v * denv + dv * env)
 
     def energy_forces_stress(self, node_types, positions, cell, first_neigh, sources, shifts,
                              skip_beyond_cutoff=True):

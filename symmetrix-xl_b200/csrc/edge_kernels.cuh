@@ -450,6 +450,89 @@ __device__ __forceinline__ void finish_receiver_forces(ForceScratch<kMaxWarps>& 
 }
 
 // ---------------------------------------------------------------------------------------------
+// Screened-Coulomb (ZBL) pair repulsion with a polynomial envelope, one half of the pair energy per
+// directed edge: E_i += 0.5 env(r) V(r), force on the edge -dE/d(xyz_ij) = -rhat dE/dr
+// (reference: libsymmetrix/source/zbl.cpp:24-139, evaluated in the model precision).  One warp per
+// receiver, one lane per edge; the per-pair constants are tabulated on the host per active pair.
+struct ZblPair {
+    float inv_a;     // 1 / a,  a = a_prefactor * 0.529 / (Z_i^a_exp + Z_j^a_exp)
+    float zz;        // 14.3996 * Z_i * Z_j
+    float r_max;     // sum of the two covalent radii
+    float pad;
+};
+struct ZblParams {
+    const ZblPair* pairs;    // [active_i * num_active + active_j]
+    float c[4];
+    int p;
+};
+
+__global__ void zbl_kernel(int num_receivers, const int* __restrict__ first, const int* __restrict__ sources,
+                           const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype, int num_active,
+                           ZblParams z, double* __restrict__ node_energies, double* __restrict__ energy_slots, ForceOutputs out)
+{
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (i >= num_receivers) return;
+    const int type_i = atype[i];
+    double energy = 0.0, rfx = 0.0, rfy = 0.0, rfz = 0.0;
+    double vir[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+    for (int e = first[i] + lane; e < first[i + 1]; e += 32) {
+        const EdgeGeom g = geom[e];
+        const int j = sources[e];
+        const ZblPair P = z.pairs[type_i * num_active + atype[j]];
+        if (!(g.r < P.r_max)) continue;
+        const float r = g.r, x = r * P.inv_a;
+        const float e0 = z.c[0] * expf(-3.2f * x), e1 = z.c[1] * expf(-0.9423f * x);
+        const float e2 = z.c[2] * expf(-0.4028f * x), e3 = z.c[3] * expf(-0.2016f * x);
+        const float phi = e0 + e1 + e2 + e3;
+        const float dphi = (-3.2f * e0 - 0.9423f * e1 - 0.4028f * e2 - 0.2016f * e3) * P.inv_a;
+        const float v = P.zz / r * phi;
+        const float dv = P.zz * (r * dphi - phi) / (r * r);
+        const float u = r / P.r_max;
+        float up = 1.0f;                                  // u^(p-1)
+        for (int q = 1; q < z.p; ++q) up *= u;
+        const float p = static_cast<float>(z.p);
+        const float upp = up * u, uppp = upp * u, upppp = uppp * u;   // u^p, u^(p+1), u^(p+2)
+        const float env = 1.0f - ((p + 1.0f) * (p + 2.0f) * 0.5f) * upp + p * (p + 2.0f) * uppp - (p * (p + 1.0f) * 0.5f) * upppp;
+        const float denv = (-((p + 1.0f) * (p + 2.0f) * 0.5f) * p * up + p * (p + 2.0f) * (p + 1.0f) * upp -
+                            (p * (p + 1.0f) * 0.5f) * (p + 2.0f) * uppp) / P.r_max;
+        energy += static_cast<double>(0.5f * v * env);
+        const float dEdr = 0.5f * (v * denv + dv * env);
+        const double ex = -static_cast<double>(g.ux * dEdr), ey = -static_cast<double>(g.uy * dEdr), ez = -static_cast<double>(g.uz * dEdr);
+        atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j), ex);
+        atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 1, ey);
+        atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 2, ez);
+        rfx -= ex; rfy -= ey; rfz -= ez;
+        const double rx = static_cast<double>(r) * g.ux, ry = static_cast<double>(r) * g.uy, rz = static_cast<double>(r) * g.uz;
+        vir[0] += ex * rx; vir[1] += ex * ry; vir[2] += ex * rz;
+        vir[3] += ey * rx; vir[4] += ey * ry; vir[5] += ey * rz;
+        vir[6] += ez * rx; vir[7] += ez * ry; vir[8] += ez * rz;
+        if (out.edge_forces != nullptr) {
+            double* ef = out.edge_forces + 3 * static_cast<size_t>(e);
+            ef[0] += ex; ef[1] += ey; ef[2] += ez;
+        }
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        energy += __shfl_xor_sync(0xffffffffu, energy, offset);
+        rfx += __shfl_xor_sync(0xffffffffu, rfx, offset);
+        rfy += __shfl_xor_sync(0xffffffffu, rfy, offset);
+        rfz += __shfl_xor_sync(0xffffffffu, rfz, offset);
+#pragma unroll
+        for (int q = 0; q < 9; ++q) vir[q] += __shfl_xor_sync(0xffffffffu, vir[q], offset);
+    }
+    if (lane == 0) {
+        node_energies[i] += energy;
+        atomicAdd(energy_slots + (i % kVirialSlots), energy);
+        atomicAdd(out.atom_forces + 3 * static_cast<size_t>(i), rfx);
+        atomicAdd(out.atom_forces + 3 * static_cast<size_t>(i) + 1, rfy);
+        atomicAdd(out.atom_forces + 3 * static_cast<size_t>(i) + 2, rfz);
+        const int slot = i % kVirialSlots;
+#pragma unroll
+        for (int q = 0; q < 9; ++q) atomicAdd(out.virial_slots + slot * 9 + q, vir[q]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Layer 0 reverse: f_ij -= sum_{lm,k} A0_adj_i[lm,k] * (rhat S0' Y + S0 grad Y).
 template <int kC>
 __global__ void __launch_bounds__(kC > 0 ? kC : 256)

@@ -193,6 +193,25 @@ void Evaluator::prepare_active_types(const std::vector<int>& node_types)
     if (table.size() > static_cast<std::size_t>(std::numeric_limits<int>::max()))
         throw std::length_error("Layer-0 spline table exceeds 32-bit indexing; too many active element types.");
     upload(r0_table_, table, stream_);
+    if (model_.has_zbl) {
+        // per-pair constants in the model precision, as the reference forms them (zbl.cpp:24-45)
+        const std::size_t n = active_types_.size();
+        std::vector<float> pairs(n * n * 4, 0.0f);
+        for (std::size_t a = 0; a < n; ++a)
+            for (std::size_t b = 0; b < n; ++b) {
+                const int Zu = model_.atomic_numbers[active_types_[a]], Zv = model_.atomic_numbers[active_types_[b]];
+                if (Zu < 0 || Zv < 0 || static_cast<std::size_t>(std::max(Zu, Zv)) >= model_.zbl_covalent_radii.size())
+                    throw std::invalid_argument("ZBL covalent radii do not cover the model's atomic numbers.");
+                const float zu = static_cast<float>(Zu), zv = static_cast<float>(Zv);
+                const float a_exp = static_cast<float>(model_.zbl_a_exp);
+                const float aa = static_cast<float>(model_.zbl_a_prefactor) * 0.529f / (std::pow(zu, a_exp) + std::pow(zv, a_exp));
+                float* p = pairs.data() + (a * n + b) * 4;
+                p[0] = 1.0f / aa;
+                p[1] = 14.3996f * zu * zv;
+                p[2] = static_cast<float>(model_.zbl_covalent_radii[Zu]) + static_cast<float>(model_.zbl_covalent_radii[Zv]);
+            }
+        upload(zbl_pairs_, pairs, stream_);
+    }
     SXB_CUDA(cudaStreamSynchronize(stream_));
 }
 
@@ -924,6 +943,17 @@ void Evaluator::run_pipeline(int phases)
                 else
                     l0_reverse_kernel<0><<<T, C, 0, stream_>>>(T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, r0_table_.ptr, A0_adj_.ptr, fo, density0);
             }
+            launches_ += 1;
+            span_end();
+        }
+        if (model_.has_zbl) {
+            span_begin("zbl");
+            ZblParams zp;
+            zp.pairs = reinterpret_cast<const ZblPair*>(zbl_pairs_.ptr);
+            for (int q = 0; q < 4; ++q) zp.c[q] = static_cast<float>(model_.zbl_c[q]);
+            zp.p = model_.zbl_p;
+            zbl_kernel<<<blocks_for(static_cast<long>(R) * 32, 256), 256, 0, stream_>>>(
+                R, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, zp, node_energies_.ptr, energy_slots_.ptr, fo);
             launches_ += 1;
             span_end();
         }

@@ -108,6 +108,7 @@ private:
     std::vector<SplitWeight> s_h2_skip_;
     bool use_tensor_cores_ = true;
     int num_sms_ = 148;
+    DeviceBuffer<float> zbl_pairs_;    // [active pair][4]: 1/a, 14.3996 Z_i Z_j, r_max, pad (models with ZBL)
     bool use_tma_activations_ = true;   // operand-streaming form of the tensor-core linears (N in {32, 64, 128})
     int poly_g_forward_ = 1, poly_g_reverse_ = 1;   // nodes per thread in the symmetric-contraction kernels
     void upload_split(SplitWeight& out, const float* w, int rows, int cols);

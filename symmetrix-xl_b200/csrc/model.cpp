@@ -183,11 +183,19 @@ HostModel load_model(const std::string& json_path)
         throw std::invalid_argument("Model must use the compact radial representation.");
     if (file.value("num_interactions", 2) != 2 || file.value("single_layer_readout", false))
         throw std::invalid_argument("Only two-interaction models are supported.");
-    if (file.value("has_zbl", false)) throw std::invalid_argument("ZBL pair repulsion is not supported.");
     if (file.value("has_field_coupling", false)) throw std::invalid_argument("MACEField models are not supported.");
     if (file.value("first_interaction_residual", false))
         throw std::invalid_argument("Residual-first models are not supported.");
 
+    m.has_zbl = file.value("has_zbl", false);
+    if (m.has_zbl) {   // libsymmetrix/source/mace.cpp:2690-2699
+        m.zbl_a_exp = file.at("zbl_a_exp").get<double>();
+        m.zbl_a_prefactor = file.at("zbl_a_prefactor").get<double>();
+        m.zbl_c = file.at("zbl_c").get<std::vector<double>>();
+        m.zbl_covalent_radii = file.at("zbl_covalent_radii").get<std::vector<double>>();
+        m.zbl_p = file.at("zbl_p").get<int>();
+        if (m.zbl_c.size() != 4 || m.zbl_p < 1) throw std::invalid_argument("ZBL parameters are malformed.");
+    }
     m.num_elements = file.at("num_elements").get<int>();
     m.channels = file.at("num_channels").get<int>();
     m.r_cut = file.at("r_cut").get<double>();

@@ -44,6 +44,11 @@ struct HostModel {
     // cubic coefficients [interval][4][functions], functions = (l_max+1)*C and paths*C
     std::vector<double> r0_coeff, r1_coeff;
     bool a0_scaled = false, a1_scaled = false;
+    // optional screened-Coulomb pair repulsion (libsymmetrix/source/zbl.cpp)
+    bool has_zbl = false;
+    double zbl_a_exp = 0.0, zbl_a_prefactor = 0.0;
+    std::vector<double> zbl_c, zbl_covalent_radii;   // radii indexed by atomic number
+    int zbl_p = 0;
     std::vector<double> a0_density_coeff, a1_density_coeff;   // [interval][4]
 
     std::vector<double> h0;                  // [A][C]

@@ -53,7 +53,7 @@ def model_tables(l_max: int, L_max: int) -> dict:
 def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), *,
                channels: int | None = None, num_spline_points: int = 256,
                radial_hidden=(64, 64, 64), num_bessel: int = 8, cutoff_p: int = 5,
-               a0_scaled: bool = False, a1_scaled: bool = False) -> dict:
+               a0_scaled: bool = False, a1_scaled: bool = False, zbl: bool = False) -> dict:
     """Random-weight compact model of architecture ``arch`` as a JSON-serialisable dict."""
     cfg = dict(ARCHITECTURES[arch])
     C = int(channels or cfg["channels"])
@@ -137,7 +137,11 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
         "L_max": L_max,
         "atomic_numbers": [int(z) for z in atomic_numbers],
         "atomic_energies": (-1.0 - 0.5 * rng.random(A)).tolist(),
-        "has_zbl": False,
+        "has_zbl": bool(zbl),
+        **({"zbl_a_exp": 0.3, "zbl_a_prefactor": 0.4543, "zbl_c": [0.1818, 0.5099, 0.2802, 0.02817], "zbl_p": 6,
+            # synthetic covalent radii indexed by atomic number (a smooth stand-in, not a literature table)
+            "zbl_covalent_radii": [0.0] + [round(0.6 + 0.45 * np.log1p(z) / np.log(10.0), 4) for z in range(1, 119)]}
+           if zbl else {}),
         "H0_weights": normal(A * C).tolist(),
         "A0_weights": [[normal(C * C, scale=1.0 / np.sqrt(C)).tolist() for _ in range(l_max + 1)]
                        for _ in range(A)],
