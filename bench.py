@@ -338,8 +338,13 @@ def run_ours(args):
         dom_s = stage_ms[dominant] * 1e-3
         achieved = alg_bytes / dom_s / 1e9
         alg_flops = FLOP_PER_EDGE_CHANNEL[dominant] * active_edges * C
+        # DRAM bytes of one launch from the committed ncu capture of the default workload
+        # (dram__bytes_read.sum + dram__bytes_write.sum, profiles/l1_reverse_medium5000.md); other sizes: not captured
+        traffic = None
+        if args.workload == "srtio3" and n == 5000 and args.tile == 0:
+            traffic = {"l1_reverse": 142.9e6, "l1_forward": 76.2e6}.get(dominant)
         roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                    "frac": achieved / hbm_peak, "peak_source": f"{peak_kind} copy bandwidth", "traffic": None,
+                    "frac": achieved / hbm_peak, "peak_source": f"{peak_kind} copy bandwidth", "traffic": traffic,
                     "kernel_ms": stage_ms[dominant], "algorithmic_bytes": alg_bytes,
                     "algorithmic_gflop": alg_flops / 1e9, "achieved_fp32_tflops": alg_flops / dom_s / 1e12,
                     "note": "edge kernels are FP32-issue / L2 bound, not HBM bound; both figures are reported"}

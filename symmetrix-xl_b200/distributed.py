@@ -88,8 +88,11 @@ class _SoloComm:
 
     rank, world = 0, 1
 
-    def all_to_all(self, send, send_counts, recv_counts):
-        return send.clone()
+    def all_to_all(self, send, send_counts, recv_counts, out=None):
+        if out is None:
+            return send.clone()
+        out.copy_(send)
+        return out
 
     def all_reduce_sum(self, tensor):
         return tensor
@@ -102,14 +105,16 @@ class _TorchComm:
         self.dist = dist
         self.rank, self.world = dist.get_rank(), dist.get_world_size()
 
-    def all_to_all(self, send, send_counts, recv_counts):
+    def all_to_all(self, send, send_counts, recv_counts, out=None):
         import torch
 
-        row = send.shape[1:] if send.dim() > 1 else ()
-        recv = torch.empty((int(sum(recv_counts)), *row), dtype=send.dtype, device=send.device)
-        self.dist.all_to_all_single(recv, send.contiguous(), output_split_sizes=[int(c) for c in recv_counts],
-                                    input_split_sizes=[int(c) for c in send_counts])
-        return recv
+        if out is None:
+            row = send.shape[1:] if send.dim() > 1 else ()
+            out = torch.empty((int(sum(recv_counts)), *row), dtype=send.dtype, device=send.device)
+        self.dist.all_to_all_single(out, send if send.is_contiguous() else send.contiguous(),
+                                    output_split_sizes=recv_counts if isinstance(recv_counts, list) else [int(c) for c in recv_counts],
+                                    input_split_sizes=send_counts if isinstance(send_counts, list) else [int(c) for c in send_counts])
+        return out
 
     def all_reduce_sum(self, tensor):
         self.dist.all_reduce(tensor, op=self.dist.ReduceOp.SUM)
@@ -199,6 +204,21 @@ class DistributedCalculator:
         self.ghost_offset = torch.from_numpy((plan.ghost_shift - owner_shift_of_ghost) @ self.cell).to(dev)
         self.owned_positions = torch.from_numpy(owned_pos).to(dev)
         self.row = (self.ev.L_max + 1) ** 2 * self.ev.num_channels
+        # per-step buffers, allocated once per graph: the step then issues no allocation and few host operations
+        n_send = len(self.send_local)
+        self.send_index = self.send_local.long()
+        self.send_counts = [int(c) for c in plan.send_counts]
+        self.recv_counts = [int(c) for c in plan.recv_counts]
+        self._local_pos = torch.empty((n_own + n_ghost, 3), dtype=torch.float64, device=dev)
+        self._send_pos = torch.empty((n_send, 3), dtype=torch.float64, device=dev)
+        self._send_rows = torch.empty((n_send, self.row), dtype=torch.float32, device=dev)
+        self._recv_rows = torch.empty((n_ghost, self.row), dtype=torch.float32, device=dev)
+        self._back_rows = torch.empty((n_ghost, self.row), dtype=torch.float32, device=dev)
+        self._got_rows = torch.empty((n_send, self.row), dtype=torch.float32, device=dev)
+        self._ghost_forces = torch.empty((n_ghost, 3), dtype=torch.float64, device=dev)
+        self._got_forces = torch.empty((n_send, 3), dtype=torch.float64, device=dev)
+        self._totals = torch.empty(10, dtype=torch.float64, device=dev)
+        self._totals_host = torch.empty(10, dtype=torch.float64).pin_memory() if str(dev).startswith("cuda") else torch.empty(10, dtype=torch.float64)
         return plan
 
     def calculate(self, owned_positions=None):
@@ -209,35 +229,39 @@ class DistributedCalculator:
         if owned_positions is None:
             owned_positions = self.owned_positions
         n_own, n_ghost = plan.num_owned, plan.num_ghost
-        sc, rc = plan.send_counts, plan.recv_counts
-        # ghost positions
-        ghost_pos = comm.all_to_all(owned_positions.index_select(0, self.send_local.long()), sc, rc) + self.ghost_offset
-        local_pos = torch.cat([owned_positions, ghost_pos], dim=0).contiguous()
+        sc, rc = self.send_counts, self.recv_counts
+        n_send = len(self.send_local)
+        # ghost positions: straight into the tail of the local position array
+        local_pos = self._local_pos
+        local_pos[:n_own].copy_(owned_positions)
+        torch.index_select(owned_positions, 0, self.send_index, out=self._send_pos)
+        comm.all_to_all(self._send_pos, sc, rc, out=local_pos[n_own:])
+        local_pos[n_own:].add_(self.ghost_offset)
         ev.distributed_begin(self.generation, local_pos.data_ptr())
         # forward halo: H1 rows of my owned atoms to the ranks that hold them as ghosts
-        send = torch.empty((len(self.send_local), self.row), dtype=torch.float32, device=self.device)
-        ev.halo_pack(0, self.send_local.data_ptr(), len(self.send_local), send.data_ptr())
-        recv = comm.all_to_all(send, sc, rc)
-        ev.halo_unpack(0, self.ghost_nodes.data_ptr(), n_ghost, recv.data_ptr(), False)
+        ev.halo_pack(0, self.send_local.data_ptr(), n_send, self._send_rows.data_ptr())
+        comm.all_to_all(self._send_rows, sc, rc, out=self._recv_rows)
+        ev.halo_unpack(0, self.ghost_nodes.data_ptr(), n_ghost, self._recv_rows.data_ptr(), False)
         ev.distributed_continue()
         # reverse halo: H1_adj rows of my ghosts back to their owners, summed there
-        back = torch.empty((n_ghost, self.row), dtype=torch.float32, device=self.device)
-        ev.halo_pack(1, self.ghost_nodes.data_ptr(), n_ghost, back.data_ptr())
-        got = comm.all_to_all(back, rc, sc)
-        ev.halo_unpack(1, self.send_local.data_ptr(), len(self.send_local), got.data_ptr(), True)
+        ev.halo_pack(1, self.ghost_nodes.data_ptr(), n_ghost, self._back_rows.data_ptr())
+        comm.all_to_all(self._back_rows, rc, sc, out=self._got_rows)
+        ev.halo_unpack(1, self.send_local.data_ptr(), n_send, self._got_rows.data_ptr(), True)
         ev.distributed_finish()
         # ghost forces back to the owners
-        _e, f_ptr, _v = ev.device_results()
+        e_ptr, f_ptr, _v = ev.device_results()
         n_local = n_own + n_ghost
         forces = _as_tensor(torch, f_ptr, (n_local, 3), torch.float64, self.device)
-        got_f = comm.all_to_all(forces[n_own:].contiguous(), rc, sc)
-        ev.add_force_rows(self.send_local.data_ptr(), len(self.send_local), got_f.data_ptr())
+        self._ghost_forces.copy_(forces[n_own:])
+        comm.all_to_all(self._ghost_forces, rc, sc, out=self._got_forces)
+        ev.add_force_rows(self.send_local.data_ptr(), n_send, self._got_forces.data_ptr())
         # energy and virial of this rank sit next to each other on the device: [E, 9 virial components]
-        e_ptr, _f, _v = ev.device_results()
-        totals = comm.all_reduce_sum(_as_tensor(torch, e_ptr, (10,), torch.float64, self.device).clone())
-        host = totals.cpu().numpy()
-        ev.synchronize()        # fetches the status word of the evaluation (raises on a device-side error)
-        return {"energy": float(host[0]), "stress": -host[1:].reshape(3, 3) / self.volume,
+        self._totals.copy_(_as_tensor(torch, e_ptr, (10,), torch.float64, self.device))
+        comm.all_reduce_sum(self._totals)
+        self._totals_host.copy_(self._totals, non_blocking=True)
+        ev.synchronize()        # one host synchronisation; fetches the status word (raises on a device-side error)
+        host = self._totals_host.numpy()
+        return {"energy": float(host[0]), "stress": -host[1:].reshape(3, 3).copy() / self.volume,
                 "forces": forces[:n_own], "owned": plan.owned}
 
 
