@@ -37,19 +37,32 @@ class RadialTables:
         self.prefactor = float(basis["prefactor"])
         self.r_max = float(definition["cutoff"]["r_max"])
         self.p = int(definition["cutoff"]["p"])
-        if definition["distance_transform"]["type"] != "none":
-            raise NotImplementedError("only the untransformed distance is restated")
+        transform = definition["distance_transform"]                      # compact_radial.cpp:149-166
+        self.agnesi = transform["type"] == "agnesi"
+        if self.agnesi:
+            self.agnesi_a, self.agnesi_q, self.agnesi_p = float(transform["a"]), float(transform["q"]), float(transform["p"])
+            self.covalent_radii = np.asarray(transform["covalent_radii"], dtype=np.float64)
+        elif transform["type"] != "none":
+            raise NotImplementedError("unknown distance transform")
         self.networks = definition["networks"]
+        self._cache = {}
 
-    def features(self):
+    def features(self, type_i=0, type_j=0):
+        """Bessel features on the spline grid; with the Agnesi transform the Bessel argument is the
+        transformed distance of the species pair (compact_radial.cpp:227-267)."""
         r = self.x0 + np.arange(self.points) * self.h
+        rt = r
+        if self.agnesi:
+            r0 = 0.5 * (self.covalent_radii[type_i] + self.covalent_radii[type_j])
+            sr = r / r0
+            rt = 1.0 / (1.0 + self.agnesi_a * sr ** self.agnesi_q / (1.0 + sr ** (self.agnesi_q - self.agnesi_p)))
         u = r / self.r_max
         p = float(self.p)
         cut = np.where(r < self.r_max,
                        1.0 - ((p + 1.0) * (p + 2.0) / 2.0) * u ** self.p
                        + p * (p + 2.0) * u ** (self.p + 1)
                        - (p * (p + 1.0) / 2.0) * u ** (self.p + 2), 0.0)
-        return self.prefactor * np.sin(self.bessel_w[None, :] * r[:, None]) / r[:, None] * cut[:, None]
+        return self.prefactor * np.sin(self.bessel_w[None, :] * rt[:, None]) / rt[:, None] * cut[:, None]
 
     def mlp(self, name, x, penultimate=False):
         net = self.networks[name]
@@ -96,9 +109,28 @@ class RadialTables:
         d[-1] = 0.0
         return d
 
-    def coefficients(self, name):
+    def pair_coefficients(self, name, types):
+        """[num_types, num_types, intervals, 4, F]: the table of every species pair (symmetric); without a
+        distance transform all pairs share one table."""
+        n = len(types)
+        if not self.agnesi:
+            c = self.coefficients(name)
+            return np.broadcast_to(c, (n, n) + c.shape)
+        out = None
+        for a in range(n):
+            for b in range(a, n):
+                c = self.coefficients(name, types[a], types[b])
+                if out is None:
+                    out = np.zeros((n, n) + c.shape)
+                out[a, b] = out[b, a] = c
+        return out
+
+    def coefficients(self, name, type_i=0, type_j=0):
         """[intervals, 4, F] cubic coefficients of network ``name`` (cubic_spline_set.cpp:8-31)."""
-        v = self.mlp(name, self.features())
+        key = (name, min(type_i, type_j), max(type_i, type_j)) if self.agnesi else (name, 0, 0)
+        if key in self._cache:
+            return self._cache[key]
+        v = self.mlp(name, self.features(type_i, type_j))
         d = self.nodal_derivatives(v)
         h = self.h
         c = np.zeros((self.points - 1, 4, v.shape[1]))
@@ -106,6 +138,7 @@ class RadialTables:
         c[:, 1] = d[:-1]
         c[:, 2] = (-3 * v[:-1] - 2 * h * d[:-1] + 3 * v[1:] - h * d[1:]) / (h * h)
         c[:, 3] = (2 * v[:-1] + h * d[:-1] - 2 * v[1:] + h * d[1:]) / (h * h * h)
+        self._cache[key] = c
         return c
 
 
@@ -246,11 +279,7 @@ class NumpyMACE:
         self.A = A = int(m["num_elements"])
         self.atomic_energies = np.asarray(m["atomic_energies"], dtype=np.float64)
         self.tables = RadialTables(m["compact_radial"], self.r_cut)
-        self.R0 = self.tables.coefficients("R0").astype(dt)
-        self.R1 = self.tables.coefficients("R1").astype(dt)
         self.A0_scaled, self.A1_scaled = bool(m["A0_scaled"]), bool(m.get("A1_scaled", False))
-        self.S0 = self.tables.coefficients("A0").astype(dt) if self.A0_scaled else None
-        self.S1 = self.tables.coefficients("A1").astype(dt) if self.A1_scaled else None
         self.H0 = np.asarray(m["H0_weights"], dtype=dt).reshape(A, C)
         self.WA0 = np.asarray(m["A0_weights"], dtype=dt).reshape(A, self.l_max + 1, C, C)
         self.P0 = [Polynomial(m["M0_monomials"][str(lm)]) for lm in range(self.num_LM)]
@@ -300,8 +329,9 @@ class NumpyMACE:
         E = len(src)
         direction = (xyz / r[:, None]).astype(dt)                      # mace.cpp:2240-2242
         Y, Yg = harmonics(self.l_max, xyz, dt)                          # mace.cpp:1269-1299
-        R0, dR0 = spline_eval(self.R0, self.tables.x0, self.tables.h, r, dt)  # mace.cpp:1119-1144
-        R1, dR1 = spline_eval(self.R1, self.tables.x0, self.tables.h, r, dt)
+        tj = typ[src]
+        R0, dR0 = self._radial("R0", typ[recv], tj, r)                   # mace.cpp:1119-1144
+        R1, dR1 = self._radial("R1", typ[recv], tj, r)
         act = active[:, None].astype(dt)
         R0, dR0, R1, dR1 = R0 * act, dR0 * act, R1 * act, dR1 * act
         l_of_lm = np.array([int(np.floor(np.sqrt(lm + 0.5))) for lm in range(nlm)])
@@ -316,7 +346,7 @@ class NumpyMACE:
         A0 = np.einsum("nmk,nmkj->nmj", Phi0, Wl)
         scale0 = None
         if self.A0_scaled:                                               # mace.cpp:1562-1584
-            s, ds = spline_eval(self.S0, self.tables.x0, self.tables.h, r, dt)
+            s, ds = self._radial("A0", typ[recv], tj, r)
             scale0 = np.ones(N, dtype=dt)
             np.add.at(scale0, recv, s[:, 0])
             A0 = A0 / scale0[:, None, None]
@@ -348,7 +378,7 @@ class NumpyMACE:
             off += nm * ne
         scale1 = None
         if self.A1_scaled:
-            s1, ds1 = spline_eval(self.S1, self.tables.x0, self.tables.h, r, dt)
+            s1, ds1 = self._radial("A1", typ[recv], tj, r)
             scale1 = np.ones(N, dtype=dt)
             np.add.at(scale1, recv, s1[:, 0])
             A1 = A1 / scale1[:, None, None]
@@ -416,6 +446,23 @@ class NumpyMACE:
                           H2_adj=H2_adj, A1_adj=A1_adj, dPhi1=dPhi1, H1_adj=H1_adj, M0_adj=M0_adj,
                           A0_adj=A0_adj, node_energies=energies, node_forces=forces)
         return energies, forces
+
+    def _radial(self, name, type_i, type_j, r):
+        """Spline values and derivatives [E, F] of network ``name`` at the edge lengths, with the table of
+        each edge's species pair (mace.cpp:216-229 pair index, 1119-1144 evaluation)."""
+        dt = self.dtype
+        if not self.tables.agnesi:
+            return spline_eval(self.tables.coefficients(name).astype(dt), self.tables.x0, self.tables.h, r, dt)
+        value = deriv = None
+        lo, hi = np.minimum(type_i, type_j), np.maximum(type_i, type_j)
+        for a, b in sorted(set(zip(lo.tolist(), hi.tolist()))):
+            mask = (lo == a) & (hi == b)
+            v, d = spline_eval(self.tables.coefficients(name, a, b).astype(dt), self.tables.x0, self.tables.h, r[mask], dt)
+            if value is None:
+                value = np.zeros((len(r), v.shape[1]), dtype=v.dtype)
+                deriv = np.zeros_like(value)
+            value[mask], deriv[mask] = v, d
+        return value, deriv
 
     def zbl_pair(self, Zu, Zv, r):
         """Screened-Coulomb pair energy (half per directed edge) and its radial derivative with the

@@ -173,6 +173,7 @@ struct DensityScale {
     const float* table;       // cubic coefficients [interval][4] of s, nullptr when the model has none
     const float* inv_scale;   // [receiver] 1 / (1 + sum_j s(r_ij))
     const float* dot;         // [receiver] sum over (lm, k) of A_adj * A, both taken for the scaled A
+    int types;                // active types the table distinguishes: table [type_i * types + type_j][interval][4]
 };
 
 // Derivative of a scalar spline stored [interval][4].
@@ -190,12 +191,14 @@ __device__ __forceinline__ float scalar_spline_value(const float* __restrict__ t
 // inv_scale[i] = 1 / (1 + sum_j s(r_ij)) for the layer-0 and the layer-1 density spline (either table
 // may be nullptr).  One warp per receiver; edge values in float as every radial function, summed in
 // double.  Reference: libsymmetrix/source/mace.cpp:1562-1584 (layer 0), 2381-2403 (layer 1).
-__global__ void density_scale_kernel(int num_receivers, const int* __restrict__ first, const EdgeGeom* __restrict__ geom,
+__global__ void density_scale_kernel(int num_receivers, const int* __restrict__ first, const int* __restrict__ sources,
+                                     const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype, int num_active,
                                      SplineGrid grid, const float* __restrict__ table0, const float* __restrict__ table1,
                                      float* __restrict__ inv_scale0, float* __restrict__ inv_scale1)
 {
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (i >= num_receivers) return;
+    const int type_i = atype[i];
     double rho0 = 0.0, rho1 = 0.0;
     for (int e = first[i] + lane; e < first[i + 1]; e += 32) {
         const float r = geom[e].r;
@@ -203,8 +206,9 @@ __global__ void density_scale_kernel(int num_receivers, const int* __restrict__ 
         int interval;
         float x;
         spline_point(grid, r, interval, x);
-        if (table0 != nullptr) rho0 += scalar_spline_value(table0, interval, x);
-        if (table1 != nullptr) rho1 += scalar_spline_value(table1, interval, x);
+        const int row = (type_i * num_active + atype[sources[e]]) * grid.intervals + interval;   // table of the ordered pair
+        if (table0 != nullptr) rho0 += scalar_spline_value(table0, row, x);
+        if (table1 != nullptr) rho1 += scalar_spline_value(table1, row, x);
     }
 #pragma unroll
     for (int offset = 16; offset > 0; offset >>= 1) {
@@ -222,7 +226,7 @@ template <bool kGradient, bool kOrderedPairs>
 __device__ __forceinline__ void fill_chunk(ChunkState<kGradient>& s, int begin, int count, const int* __restrict__ sources,
                                            const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype,
                                            int type_i, int num_active, const SplineGrid& grid, int functions,
-                                           const float* __restrict__ density_table = nullptr)
+                                           const float* __restrict__ density_table = nullptr, int density_types = 1)
 {
     for (int t = threadIdx.x; t < count; t += blockDim.x) {
         const int e = begin + t;
@@ -235,8 +239,16 @@ __device__ __forceinline__ void fill_chunk(ChunkState<kGradient>& s, int begin, 
         int interval;
         float x;
         spline_point(grid, g.r, interval, x);
-        int pair = 0;   // layer-1 tables do not depend on the species pair without a distance transform
-        if constexpr (kOrderedPairs) pair = type_i * num_active + atype[j];
+        // layer 0: ordered pair (H0 of the source and W_A0 of the receiver are folded into the table);
+        // layer 1: unordered pair, and a single table when the model has no distance transform (num_active == 1)
+        int pair = 0, type_j = 0;
+        if (kOrderedPairs || num_active > 1) type_j = atype[j];
+        if constexpr (kOrderedPairs) {
+            pair = type_i * num_active + type_j;
+        } else if (num_active > 1) {
+            const int a = min(type_i, type_j), b = max(type_i, type_j);
+            pair = a * (2 * num_active - a - 1) / 2 + b;
+        }
         s.index[t] = make_int2((pair * grid.intervals + interval) * 4 * functions, j);
         s.misc[t] = make_float4(x, g.ux, g.uy, g.uz);
         const float inv_r = 1.0f / g.r;
@@ -244,7 +256,10 @@ __device__ __forceinline__ void fill_chunk(ChunkState<kGradient>& s, int begin, 
             harmonics16<true>(g.ux, g.uy, g.uz, inv_r, reinterpret_cast<float*>(s.y[t]), reinterpret_cast<float*>(s.gx[t]),
                               reinterpret_cast<float*>(s.gy[t]), reinterpret_cast<float*>(s.gz[t]));
             s.len[t] = g.r;
-            s.dens[t] = density_table != nullptr ? scalar_spline_derivative(density_table, interval, x) : 0.0f;
+            // density tables are stored per ordered pair of the density_types active types
+            s.dens[t] = density_table != nullptr
+                            ? scalar_spline_derivative(density_table, (type_i * density_types + (density_types > 1 ? atype[j] : 0)) * grid.intervals + interval, x)
+                            : 0.0f;
         } else {
             harmonics16<false>(g.ux, g.uy, g.uz, inv_r, reinterpret_cast<float*>(s.y[t]), nullptr, nullptr, nullptr);
         }
@@ -562,7 +577,7 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
     for (int chunk = begin; chunk < end; chunk += kEdgeChunk) {
         const int count = min(kEdgeChunk, end - chunk);
         __syncthreads();
-        fill_chunk<true, true>(s, chunk, count, sources, geom, atype, type_i, num_active, grid, F, density.table);
+        fill_chunk<true, true>(s, chunk, count, sources, geom, atype, type_i, num_active, grid, F, density.table, density.types);
         __syncthreads();
         for (int t = 0; t < count; ++t) {
             const int base = s.index[t].x;
@@ -630,7 +645,7 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
                              const unsigned char* __restrict__ atype, SplineGrid grid,                               \
                              const float4* __restrict__ table4, const float* __restrict__ H1,                        \
                              const __grid_constant__ CouplingConstants cgc, float* __restrict__ Phi1,                \
-                             const float* __restrict__ inv_scale)                                                    \
+                             const float* __restrict__ inv_scale, int pair_types)                                    \
     {                                                                                                                \
         constexpr int NP = SXB_##NAME##_NUM_PATHS, NR = SXB_##NAME##_NUM_ROWS, NH = SXB_##NAME##_NUM_HIDDEN;          \
         constexpr int NE = SXB_##NAME##_NUM_LME;                                                                     \
@@ -645,7 +660,7 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
         for (int chunk = begin; chunk < end; chunk += kEdgeChunk) {                                                  \
             const int count = min(kEdgeChunk, end - chunk);                                                          \
             __syncthreads();                                                                                         \
-            fill_chunk<false, false>(s, chunk, count, sources, geom, atype, 0, 1, grid, F);                          \
+            fill_chunk<false, false>(s, chunk, count, sources, geom, atype, atype[i], pair_types, grid, F);          \
             __syncthreads();                                                                                         \
             for (int t = 0; t < count; ++t) {                                                                        \
                 const int2 id = s.index[t];                                                                          \
@@ -681,7 +696,7 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
                              const unsigned char* __restrict__ atype, SplineGrid grid,                               \
                              const float4* __restrict__ table4, const float* __restrict__ H1,                        \
                              const float* __restrict__ dPhi1, const __grid_constant__ CouplingConstants cgc,         \
-                             float* __restrict__ H1_adj, ForceOutputs out, DensityScale density)                     \
+                             float* __restrict__ H1_adj, ForceOutputs out, DensityScale density, int pair_types)     \
     {                                                                                                                \
         constexpr int NP = SXB_##NAME##_NUM_PATHS, NR = SXB_##NAME##_NUM_ROWS, NH = SXB_##NAME##_NUM_HIDDEN;          \
         constexpr int NE = SXB_##NAME##_NUM_LME;                                                                     \
@@ -709,7 +724,8 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
         for (int chunk = begin; chunk < end; chunk += kEdgeChunk) {                                                  \
             const int count = min(kEdgeChunk, end - chunk);                                                          \
             __syncthreads();                                                                                         \
-            fill_chunk<true, false>(s, chunk, count, sources, geom, atype, 0, 1, grid, F, density.table);            \
+            fill_chunk<true, false>(s, chunk, count, sources, geom, atype, atype[i], pair_types, grid, F,            \
+                                    density.table, density.types);                                                   \
             __syncthreads();                                                                                         \
             for (int t = 0; t < count; ++t) {                                                                        \
                 const int2 id = s.index[t];                                                                          \

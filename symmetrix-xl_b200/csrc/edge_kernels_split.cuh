@@ -22,7 +22,7 @@ namespace sxb {
                                          const unsigned char* __restrict__ atype, SplineGrid grid,                   \
                                          const float4* __restrict__ table4, const float* __restrict__ H1,            \
                                          const __grid_constant__ CouplingConstants cgc, float* __restrict__ Phi1,    \
-                                         const float* __restrict__ inv_scale)                                        \
+                                         const float* __restrict__ inv_scale, int pair_types)                        \
     {                                                                                                                \
         constexpr int C = kC;                                                                                        \
         constexpr int NP = SXB_##NAME##_NUM_PATHS, NH = SXB_##NAME##_NUM_HIDDEN, NE = SXB_##NAME##_NUM_LME;          \
@@ -40,7 +40,7 @@ namespace sxb {
         for (int chunk = begin; chunk < end; chunk += kEdgeChunk) {                                                  \
             const int count = min(kEdgeChunk, end - chunk);                                                          \
             __syncthreads();                                                                                         \
-            fill_chunk<false, false>(s, chunk, count, sources, geom, atype, 0, 1, grid, F);                          \
+            fill_chunk<false, false>(s, chunk, count, sources, geom, atype, atype[i], pair_types, grid, F);          \
             __syncthreads();                                                                                         \
             for (int t = 0; t < count; ++t) {                                                                        \
                 const int2 id = s.index[t];                                                                          \
@@ -77,7 +77,7 @@ namespace sxb {
                                          const float4* __restrict__ table4, const float* __restrict__ H1,            \
                                          const float* __restrict__ dPhi1,                                            \
                                          const __grid_constant__ CouplingConstants cgc, float* __restrict__ H1_adj,  \
-                                         ForceOutputs out, DensityScale density)                                     \
+                                         ForceOutputs out, DensityScale density, int pair_types)                     \
     {                                                                                                                \
         constexpr int C = kC;                                                                                        \
         constexpr int NP = SXB_##NAME##_NUM_PATHS, NH = SXB_##NAME##_NUM_HIDDEN, NE = SXB_##NAME##_NUM_LME;          \
@@ -110,7 +110,8 @@ namespace sxb {
         for (int chunk = begin; chunk < end; chunk += kEdgeChunk) {                                                  \
             const int count = min(kEdgeChunk, end - chunk);                                                          \
             __syncthreads();                                                                                         \
-            fill_chunk<true, false>(s, chunk, count, sources, geom, atype, 0, 1, grid, F, density.table);            \
+            fill_chunk<true, false>(s, chunk, count, sources, geom, atype, atype[i], pair_types, grid, F,            \
+                                    density.table, density.types);                                                   \
             __syncthreads();                                                                                         \
             for (int t = 0; t < count; ++t) {                                                                        \
                 const int2 id = s.index[t];                                                                          \

@@ -33,7 +33,7 @@ __device__ __forceinline__ void fill_warp_chunk(WarpChunk<kGradient>& s, int lan
                                                 const int* __restrict__ sources, const EdgeGeom* __restrict__ geom,
                                                 const unsigned char* __restrict__ atype, int type_i, int num_active,
                                                 const SplineGrid& grid, int functions,
-                                                const float* __restrict__ density_table = nullptr)
+                                                const float* __restrict__ density_table = nullptr, int density_types = 1)
 {
     if (lane < count) {
         const int e = begin + lane;
@@ -53,7 +53,9 @@ __device__ __forceinline__ void fill_warp_chunk(WarpChunk<kGradient>& s, int lan
                 harmonics16<true>(g.ux, g.uy, g.uz, inv_r, reinterpret_cast<float*>(s.y[lane]), reinterpret_cast<float*>(s.gx[lane]),
                                   reinterpret_cast<float*>(s.gy[lane]), reinterpret_cast<float*>(s.gz[lane]));
                 s.len[lane] = g.r;
-                s.dens[lane] = density_table != nullptr ? scalar_spline_derivative(density_table, interval, x) : 0.0f;
+                s.dens[lane] = density_table != nullptr
+                                   ? scalar_spline_derivative(density_table, (type_i * density_types + (density_types > 1 ? atype[j] : 0)) * grid.intervals + interval, x)
+                                   : 0.0f;
             } else {
                 harmonics16<false>(g.ux, g.uy, g.uz, inv_r, reinterpret_cast<float*>(s.y[lane]), nullptr, nullptr, nullptr);
             }
@@ -193,7 +195,7 @@ l0_reverse_warp_kernel(int num_nodes, int node0, const int* __restrict__ first, 
     for (int chunk = begin; chunk < end; chunk += kWarpChunk) {
         const int count = min(kWarpChunk, end - chunk);
         __syncwarp();
-        fill_warp_chunk<true>(s, lane, chunk, count, sources, geom, atype, type_i, num_active, grid, F, density.table);
+        fill_warp_chunk<true>(s, lane, chunk, count, sources, geom, atype, type_i, num_active, grid, F, density.table, density.types);
         __syncwarp();
         for (int t = 0; t < count; ++t) {
             const int base = s.index[t].x;

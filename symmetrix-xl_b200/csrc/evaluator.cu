@@ -111,20 +111,8 @@ Evaluator::Evaluator(const std::string& json_path, int device_ordinal) : device_
     SXB_CUDA(cudaEventCreate(&event_end_));
 
     const int C = model_.channels;
-    // layer-1 table in float, repacked from [interval][4][paths*C] to [interval][paths*C][4]
-    {
-        const std::size_t F = static_cast<std::size_t>(model_.num_paths) * C;
-        const std::size_t intervals = static_cast<std::size_t>(model_.spline_points - 1);
-        std::vector<float> r1(model_.r1_coeff.size());
-        for (std::size_t i = 0; i < intervals; ++i)
-            for (std::size_t f = 0; f < F; ++f)
-                for (std::size_t c = 0; c < 4; ++c)
-                    r1[(i * F + f) * 4 + c] = static_cast<float>(model_.r1_coeff[(i * 4 + c) * F + f]);
-        upload(r1_table_, r1, stream_);
-    }
-    // density splines of A0_scaled / A1_scaled models, [interval][4] in float
-    if (model_.a0_scaled) upload(density0_table_, std::vector<float>(model_.a0_density_coeff.begin(), model_.a0_density_coeff.end()), stream_);
-    if (model_.a1_scaled) upload(density1_table_, std::vector<float>(model_.a1_density_coeff.begin(), model_.a1_density_coeff.end()), stream_);
+    // the layer-1 table [pair][interval][paths*C][4] and the density tables depend on the active species
+    // pairs when the model uses a distance transform: they are built in prepare_active_types
     upload(m0_weights_, model_.m0_weights, stream_);
     upload(m1_weights_, model_.m1_weights, stream_);
     upload(w_h1_, model_.w_h1, stream_);
@@ -193,6 +181,14 @@ void Evaluator::prepare_active_types(const std::vector<int>& node_types)
     if (table.size() > static_cast<std::size_t>(std::numeric_limits<int>::max()))
         throw std::length_error("Layer-0 spline table exceeds 32-bit indexing; too many active element types.");
     upload(r0_table_, table, stream_);
+    {
+        int pairs = 1;
+        const auto r1 = build_r1_table(model_, active_types_, &pairs);
+        upload(r1_table_, r1, stream_);
+        r1_pair_types_ = model_.agnesi ? static_cast<int>(active_types_.size()) : 1;
+        if (model_.a0_scaled) upload(density0_table_, build_density_table(model_, "A0", active_types_), stream_);
+        if (model_.a1_scaled) upload(density1_table_, build_density_table(model_, "A1", active_types_), stream_);
+    }
     if (model_.has_zbl) {
         // per-pair constants in the model precision, as the reference forms them (zbl.cpp:24-45)
         const std::size_t n = active_types_.size();
@@ -714,8 +710,8 @@ void Evaluator::run_pipeline(int phases)
     // launch helpers for one tile of T receivers starting at t0 (tile tensors are indexed from 0)
     const float* inv0 = model_.a0_scaled ? inv_scale0_.ptr : nullptr;
     const float* inv1 = model_.a1_scaled ? inv_scale1_.ptr : nullptr;
-    const DensityScale density0{model_.a0_scaled ? density0_table_.ptr : nullptr, inv_scale0_.ptr, dot0_.ptr};
-    const DensityScale density1{model_.a1_scaled ? density1_table_.ptr : nullptr, inv_scale1_.ptr, dot1_.ptr};
+    const DensityScale density0{model_.a0_scaled ? density0_table_.ptr : nullptr, inv_scale0_.ptr, dot0_.ptr, n_active};
+    const DensityScale density1{model_.a1_scaled ? density1_table_.ptr : nullptr, inv_scale1_.ptr, dot1_.ptr, n_active};
     auto l0_forward = [&](int t0, int T) {
         const int warp_grid = blocks_for(T, kWarpsPerBlock);
         if (C == 128)
@@ -748,7 +744,8 @@ void Evaluator::run_pipeline(int phases)
             if (model_.a1_scaled) SXB_CUDA(cudaMemsetAsync(dot1_.ptr, 0, sizeof(float) * R, stream_));
             span_begin("density_scales");
             density_scale_kernel<<<blocks_for(static_cast<long>(R) * 32, 256), 256, 0, stream_>>>(
-                R, first_.ptr, geom_.ptr, grid_, density0.table, density1.table, inv_scale0_.ptr, inv_scale1_.ptr);
+                R, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, n_active, grid_, density0.table, density1.table, inv_scale0_.ptr,
+                inv_scale1_.ptr);
             launches_ += 1;
             span_end();
         }
@@ -786,15 +783,15 @@ void Evaluator::run_pipeline(int phases)
             span_begin("l1_forward");
             if (model_.shape_id == 0)
                 SXB_LAUNCH_BY_CHANNELS(l1_forward_kernel_S0, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
-                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, coupling_, Phi1_.ptr, inv1);
+                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, coupling_, Phi1_.ptr, inv1, r1_pair_types_);
             else if (model_.shape_id == 1)
                 SXB_LAUNCH_BY_CHANNELS(l1_forward_kernel_S1, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
-                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, coupling_, Phi1_.ptr, inv1);
+                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, coupling_, Phi1_.ptr, inv1, r1_pair_types_);
             else {
                 // one launch per path set; the sets write disjoint components of Phi1
 #define SXB_SPLIT_FORWARD(SET)                                                                                            \
                 l1_forward_split_kernel_S2_##SET<128><<<T, 128, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, \
-                    reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, coupling_, Phi1_.ptr, inv1)
+                    reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, coupling_, Phi1_.ptr, inv1, r1_pair_types_)
                 SXB_SPLIT_FORWARD(G0);
                 SXB_SPLIT_FORWARD(G1);
                 SXB_SPLIT_FORWARD(G2);
@@ -872,10 +869,10 @@ void Evaluator::run_pipeline(int phases)
             span_begin("l1_reverse");
             if (model_.shape_id == 0)
                 SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S0, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
-                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1);
+                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1, r1_pair_types_);
             else if (model_.shape_id == 1)
                 SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S1, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
-                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1);
+                                       reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1, r1_pair_types_);
             else {
                 // one launch per path set; the sets add into the same edge forces, so those are cleared
                 // first and accumulated atomically
@@ -883,7 +880,7 @@ void Evaluator::run_pipeline(int phases)
                 split.accumulate_edge = 2;
 #define SXB_SPLIT_REVERSE(SET)                                                                                            \
                 l1_reverse_split_kernel_S2_##SET<128><<<T, 128, 0, stream_>>>(T, t0, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, \
-                    reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, split, density1)
+                    reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, split, density1, r1_pair_types_)
                 SXB_SPLIT_REVERSE(G0);
                 SXB_SPLIT_REVERSE(G1);
                 SXB_SPLIT_REVERSE(G2);

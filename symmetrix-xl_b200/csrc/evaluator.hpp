@@ -108,6 +108,7 @@ private:
     std::vector<SplitWeight> s_h2_skip_;
     bool use_tensor_cores_ = true;
     int num_sms_ = 148;
+    int r1_pair_types_ = 1;   // active types the layer-1 table distinguishes (1 without a distance transform)
     DeviceBuffer<float> zbl_pairs_;    // [active pair][4]: 1/a, 14.3996 Z_i Z_j, r_max, pad (models with ZBL)
     bool use_tma_activations_ = true;   // operand-streaming form of the tensor-core linears (N in {32, 64, 128})
     int poly_g_forward_ = 1, poly_g_reverse_ = 1;   // nodes per thread in the symmetric-contraction kernels

@@ -5,6 +5,7 @@
 #include <fstream>
 #include <map>
 #include <stdexcept>
+#include <tuple>
 
 #include "nlohmann/json.hpp"
 
@@ -150,6 +151,48 @@ std::vector<double> spline_coefficients(const std::vector<double>& values, int p
         }
     }
     return coeff;
+}
+
+// Parsed radial definition of a model: grid, basis, cutoff, optional Agnesi transform, networks,
+// and the tables already built (per unordered species pair; key pair 0,0 without a transform).
+struct RadialDefinition {
+    int points = 0;
+    double x0 = 0.0, h = 0.0;
+    std::vector<double> bessel;
+    double prefactor = 0.0, r_max = 0.0;
+    int p = 0;
+    bool agnesi = false;
+    double agnesi_a = 0.0, agnesi_q = 0.0, agnesi_p = 0.0;
+    std::vector<double> covalent_radii;   // per element type
+    std::map<std::string, Network> networks;
+    mutable std::map<std::tuple<std::string, int, int>, std::vector<double>> cache;
+};
+
+// Bessel x polynomial-cutoff features on the spline grid; with the Agnesi transform the Bessel argument
+// is the transformed distance of the pair (libsymmetrix/source/compact_radial.cpp:227-267).
+std::vector<double> radial_features(const RadialDefinition& d, int type_i, int type_j)
+{
+    const int nb = static_cast<int>(d.bessel.size());
+    double r0 = 1.0;
+    if (d.agnesi) r0 = 0.5 * (d.covalent_radii.at(type_i) + d.covalent_radii.at(type_j));
+    std::vector<double> features(static_cast<std::size_t>(d.points) * nb);
+    for (int node = 0; node < d.points; ++node) {
+        const double r = d.x0 + node * d.h;
+        double rt = r;
+        if (d.agnesi) {
+            const double sr = r / r0;
+            rt = 1.0 / (1.0 + d.agnesi_a * std::pow(sr, d.agnesi_q) / (1.0 + std::pow(sr, d.agnesi_q - d.agnesi_p)));
+        }
+        double cut = 0.0;
+        if (r < d.r_max) {
+            const double u = r / d.r_max;
+            cut = 1.0 - ((d.p + 1.0) * (d.p + 2.0) / 2.0) * std::pow(u, d.p) + d.p * (d.p + 2.0) * std::pow(u, d.p + 1)
+                  - (d.p * (d.p + 1.0) / 2.0) * std::pow(u, d.p + 2);
+        }
+        for (int b = 0; b < nb; ++b)
+            features[static_cast<std::size_t>(node) * nb + b] = d.prefactor * std::sin(d.bessel[b] * rt) / rt * cut;
+    }
+    return features;
 }
 
 template <typename T>
@@ -317,37 +360,49 @@ HostModel load_model(const std::string& json_path)
     const double r_max = cutoff.at("r_max").get<double>();
     const int p = cutoff.at("p").get<int>();
     if (std::abs(r_max - m.r_cut) > 1e-12) throw std::invalid_argument("Compact radial cutoff does not match model r_cut.");
-    if (radial.at("distance_transform").at("type").get<std::string>() != "none")
-        throw std::invalid_argument("Only the untransformed radial distance is supported.");
-    const int nb = static_cast<int>(bessel.size());
-    std::vector<double> features(static_cast<std::size_t>(m.spline_points) * nb);
-    for (int node = 0; node < m.spline_points; ++node) {
-        const double r = m.spline_x0 + node * m.spline_h;
-        double cut = 0.0;
-        if (r < r_max) {
-            const double u = r / r_max;
-            cut = 1.0 - ((p + 1.0) * (p + 2.0) / 2.0) * std::pow(u, p) + p * (p + 2.0) * std::pow(u, p + 1)
-                  - (p * (p + 1.0) / 2.0) * std::pow(u, p + 2);
-        }
-        for (int b = 0; b < nb; ++b)
-            features[static_cast<std::size_t>(node) * nb + b] = prefactor * std::sin(bessel[b] * r) / r * cut;
+    auto def = std::make_shared<RadialDefinition>();
+    def->points = m.spline_points;
+    def->x0 = m.spline_x0;
+    def->h = m.spline_h;
+    def->bessel = bessel;
+    def->prefactor = prefactor;
+    def->r_max = r_max;
+    def->p = p;
+    const auto& transform = radial.at("distance_transform");
+    const std::string transform_type = transform.at("type").get<std::string>();
+    if (transform_type == "agnesi") {   // libsymmetrix/source/compact_radial.cpp:149-166
+        def->agnesi = true;
+        def->agnesi_a = transform.at("a").get<double>();
+        def->agnesi_q = transform.at("q").get<double>();
+        def->agnesi_p = transform.at("p").get<double>();
+        def->covalent_radii = transform.at("covalent_radii").get<std::vector<double>>();
+        if (static_cast<int>(def->covalent_radii.size()) != A)
+            throw std::invalid_argument("Compact radial covalent radii do not match atomic numbers.");
+        for (double rc : def->covalent_radii)
+            if (!(rc > 0.0) || !std::isfinite(rc)) throw std::invalid_argument("Compact radial model has invalid Agnesi data.");
+        if (!std::isfinite(def->agnesi_a) || !std::isfinite(def->agnesi_q) || !std::isfinite(def->agnesi_p))
+            throw std::invalid_argument("Compact radial model has invalid Agnesi data.");
+    } else if (transform_type != "none") {
+        throw std::invalid_argument("Unknown radial distance transform: " + transform_type);
     }
+    m.agnesi = def->agnesi;
+    const int nb = static_cast<int>(bessel.size());
     const auto& networks = radial.at("networks");
-    auto table = [&](const char* name, int expected) {
+    auto add_network = [&](const char* name, int expected) {
         const Network net = parse_network(networks.at(name), name);
         if (net.shape.front() != nb || net.shape.back() != expected)
             throw std::invalid_argument(std::string("Compact radial network ") + name + " has an invalid extent.");
-        const auto values = run_network(net, features, m.spline_points);
-        return spline_coefficients(values, m.spline_points, expected, m.spline_h);
+        def->networks.emplace(name, net);
     };
-    m.r0_coeff = table("R0", (m.l_max + 1) * C);
-    m.r1_coeff = table("R1", m.num_paths * C);
+    add_network("R0", (m.l_max + 1) * C);
+    add_network("R1", m.num_paths * C);
     m.a0_scaled = file.at("A0_scaled").get<bool>();
     m.a1_scaled = file.value("A1_scaled", false);
     if (m.a0_scaled != networks.contains("A0") || m.a1_scaled != networks.contains("A1"))
         throw std::invalid_argument("Compact radial density networks do not match A0_scaled / A1_scaled.");
-    if (m.a0_scaled) m.a0_density_coeff = table("A0", 1);
-    if (m.a1_scaled) m.a1_density_coeff = table("A1", 1);
+    if (m.a0_scaled) add_network("A0", 1);
+    if (m.a1_scaled) add_network("A1", 1);
+    m.radial = def;
 
     // ---- dense weights
     m.h0 = file.at("H0_weights").get<std::vector<double>>();
@@ -398,6 +453,52 @@ HostModel load_model(const std::string& json_path)
     return m;
 }
 
+const std::vector<double>& radial_coefficients(const HostModel& m, const std::string& name, int type_i, int type_j)
+{
+    const auto& d = *static_cast<const RadialDefinition*>(m.radial.get());
+    int a = 0, b = 0;
+    if (d.agnesi) { a = std::min(type_i, type_j); b = std::max(type_i, type_j); }
+    const auto key = std::make_tuple(name, a, b);
+    auto found = d.cache.find(key);
+    if (found != d.cache.end()) return found->second;
+    const Network& net = d.networks.at(name);
+    const auto values = run_network(net, radial_features(d, a, b), d.points);
+    return d.cache.emplace(key, spline_coefficients(values, d.points, net.shape.back(), d.h)).first->second;
+}
+
+std::vector<float> build_r1_table(const HostModel& m, const std::vector<int>& active_types, int* num_pairs)
+{
+    const int n = m.agnesi ? static_cast<int>(active_types.size()) : 1;
+    const int pairs = n * (n + 1) / 2;
+    *num_pairs = pairs;
+    const std::size_t F = static_cast<std::size_t>(m.num_paths) * m.channels;
+    const std::size_t intervals = static_cast<std::size_t>(m.spline_points - 1);
+    std::vector<float> out(static_cast<std::size_t>(pairs) * intervals * F * 4);
+    int pair = 0;
+    for (int a = 0; a < n; ++a)
+        for (int b = a; b < n; ++b, ++pair) {   // pair index a*(2n-a-1)/2 + b
+            const auto& c = radial_coefficients(m, "R1", m.agnesi ? active_types[a] : 0, m.agnesi ? active_types[b] : 0);
+            float* table = out.data() + static_cast<std::size_t>(pair) * intervals * F * 4;
+            for (std::size_t i = 0; i < intervals; ++i)
+                for (std::size_t f = 0; f < F; ++f)
+                    for (std::size_t q = 0; q < 4; ++q) table[(i * F + f) * 4 + q] = static_cast<float>(c[(i * 4 + q) * F + f]);
+        }
+    return out;
+}
+
+std::vector<float> build_density_table(const HostModel& m, const std::string& name, const std::vector<int>& active_types)
+{
+    const int n = static_cast<int>(active_types.size());
+    const std::size_t rows = static_cast<std::size_t>(m.spline_points - 1) * 4;
+    std::vector<float> out(static_cast<std::size_t>(n) * n * rows);
+    for (int a = 0; a < n; ++a)
+        for (int b = 0; b < n; ++b) {
+            const auto& c = radial_coefficients(m, name, active_types[a], active_types[b]);   // [interval][4][1]
+            for (std::size_t q = 0; q < rows; ++q) out[(static_cast<std::size_t>(a) * n + b) * rows + q] = static_cast<float>(c[q]);
+        }
+    return out;
+}
+
 std::vector<float> fold_r0_table(const HostModel& m, const std::vector<int>& active_types)
 {
     const int n = static_cast<int>(active_types.size());
@@ -409,9 +510,10 @@ std::vector<float> fold_r0_table(const HostModel& m, const std::vector<int>& act
         for (int aj = 0; aj < n; ++aj) {
             const double* h0 = m.h0.data() + static_cast<std::size_t>(active_types[aj]) * C;
             float* table = out.data() + static_cast<std::size_t>(ai * n + aj) * rows * F;
+            const std::vector<double>& r0_coeff = radial_coefficients(m, "R0", active_types[ai], active_types[aj]);
             for (int row = 0; row < rows; ++row)
                 for (int l = 0; l < L; ++l) {
-                    const double* c = m.r0_coeff.data() + static_cast<std::size_t>(row) * F + l * C;
+                    const double* c = r0_coeff.data() + static_cast<std::size_t>(row) * F + l * C;
                     const double* w = m.w_a0.data() + (static_cast<std::size_t>(active_types[ai]) * L + l) * C * C;
                     for (int k = 0; k < C; ++k) scaled[k] = c[k] * h0[k];
                     std::fill(acc.begin(), acc.end(), 0.0);

@@ -6,6 +6,7 @@
 #pragma once
 
 #include <cstdint>
+#include <memory>
 #include <string>
 #include <vector>
 
@@ -41,15 +42,17 @@ struct HostModel {
     // radial spline grid
     double spline_x0 = 0.0, spline_h = 0.0;
     int spline_points = 0;
-    // cubic coefficients [interval][4][functions], functions = (l_max+1)*C and paths*C
-    std::vector<double> r0_coeff, r1_coeff;
+    // Radial networks R0, R1 and the density networks A0, A1: kept in parsed form, because with the
+    // Agnesi distance transform the spline tables depend on the species pair and are built per active
+    // pair (radial_coefficients below).  Without a transform every pair shares one table.
+    bool agnesi = false;
+    std::shared_ptr<const void> radial;   // parsed definition, owned by model.cpp
     bool a0_scaled = false, a1_scaled = false;
     // optional screened-Coulomb pair repulsion (libsymmetrix/source/zbl.cpp)
     bool has_zbl = false;
     double zbl_a_exp = 0.0, zbl_a_prefactor = 0.0;
     std::vector<double> zbl_c, zbl_covalent_radii;   // radii indexed by atomic number
     int zbl_p = 0;
-    std::vector<double> a0_density_coeff, a1_density_coeff;   // [interval][4]
 
     std::vector<double> h0;                  // [A][C]
     std::vector<double> w_a0;                // [A][l][C_in][C_out]
@@ -70,6 +73,19 @@ struct HostModel {
 
 // Throws std::runtime_error / std::invalid_argument with a message naming the key.
 HostModel load_model(const std::string& json_path);
+
+// Cubic coefficients [interval][4][functions] (double) of radial network ``name`` ("R0", "R1", "A0",
+// "A1") for the species pair (type_i, type_j) - symmetric in the pair; reference:
+// libsymmetrix/source/compact_radial.cpp:227-289, 326-366 and cubic_spline_set.cpp:8-31.  Tables are
+// cached per unordered pair inside the model.
+const std::vector<double>& radial_coefficients(const HostModel& model, const std::string& name, int type_i, int type_j);
+
+// Layer-1 table for the given active types, repacked to [unordered pair][interval][function][4] in
+// float; one pair when the model has no distance transform.  ``num_pairs`` receives the pair count.
+std::vector<float> build_r1_table(const HostModel& model, const std::vector<int>& active_types, int* num_pairs);
+
+// Density table [ordered pair ai*n+aj][interval][4] in float of network "A0" or "A1".
+std::vector<float> build_density_table(const HostModel& model, const std::string& name, const std::vector<int>& active_types);
 
 // Folds H0[type_j] and W_A0[type_i][l] into the layer-0 spline coefficients for the
 // given active types (the reference does the same per ordered species pair,

@@ -53,7 +53,8 @@ def model_tables(l_max: int, L_max: int) -> dict:
 def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), *,
                channels: int | None = None, num_spline_points: int = 256,
                radial_hidden=(64, 64, 64), num_bessel: int = 8, cutoff_p: int = 5,
-               a0_scaled: bool = False, a1_scaled: bool = False, zbl: bool = False) -> dict:
+               a0_scaled: bool = False, a1_scaled: bool = False, zbl: bool = False,
+               agnesi: bool = False) -> dict:
     """Random-weight compact model of architecture ``arch`` as a JSON-serialisable dict."""
     cfg = dict(ARCHITECTURES[arch])
     C = int(channels or cfg["channels"])
@@ -75,7 +76,7 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
             fan_in, fan_out = shape[layer], shape[layer + 1]
             w = normal(fan_out, fan_in, scale=1.0 / np.sqrt(fan_in))
             if layer == 0:
-                w *= 2.0  # Bessel features are O(0.3)
+                w *= 0.2 if agnesi else 2.0  # Bessel features are O(0.3); O(3) in the transformed distance
             if layer == len(shape) - 2:
                 w *= out_scale
             weights.append(w.reshape(-1).tolist())
@@ -155,7 +156,11 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
                 "prefactor": float(np.sqrt(2.0 / r_cut)),
             },
             "cutoff": {"type": "polynomial", "r_max": r_cut, "p": int(cutoff_p)},
-            "distance_transform": {"type": "none"},
+            # synthetic covalent radii per element slot (a smooth stand-in, not a literature table)
+            "distance_transform": ({"type": "agnesi", "a": 1.0805, "q": 0.9183, "p": 4.5791,
+                                    "covalent_radii": [round(0.6 + 0.45 * float(np.log1p(z)) / float(np.log(10.0)), 4)
+                                                       for z in atomic_numbers]}
+                                   if agnesi else {"type": "none"}),
             "networks": networks,
         },
         "M0_monomials": m0_monomials,

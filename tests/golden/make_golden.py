@@ -42,13 +42,14 @@ def evaluator_goldens():
     pkg = graft.load_package()
     # the third case is a density-scaled model (A0_scaled and A1_scaled, mace.cpp:1562-1636, 2381-2458)
     # and the fourth has hidden irreps up to l = 2 (17 paths, 243 rows)
-    # the fifth adds the screened-Coulomb (ZBL) pair term (zbl.cpp)
-    for arch, cells, cutoff, scaled, zbl in (("small", 2, 5.0, False, False), ("medium", 2, 6.0, False, False),
-                                             ("medium", 2, 6.0, True, False), ("large", 2, 6.0, False, False),
-                                             ("small", 2, 5.0, False, True)):
+    # the fifth adds the screened-Coulomb (ZBL) pair term (zbl.cpp), the sixth the Agnesi distance
+    # transform (species-pair dependent radial tables, compact_radial.cpp:227-267) with density scaling and ZBL
+    for arch, cells, cutoff, scaled, zbl, agnesi in (("small", 2, 5.0, False, False, False), ("medium", 2, 6.0, False, False, False),
+                                                     ("medium", 2, 6.0, True, False, False), ("large", 2, 6.0, False, False, False),
+                                                     ("small", 2, 5.0, False, True, False), ("small", 2, 5.0, True, True, True)):
         with tempfile.TemporaryDirectory() as tmp:
             path = Path(tmp) / "model.json"
-            pkg.modelgen.write_model(path, arch, seed=101, a0_scaled=scaled, a1_scaled=scaled, zbl=zbl)
+            pkg.modelgen.write_model(path, arch, seed=101, a0_scaled=scaled, a1_scaled=scaled, zbl=zbl, agnesi=agnesi)
             pos, cell, types = pkg.modelgen.srtio3(cells, 0.05, 202)
             first, src, shifts = neighbor.build_neighbor_graph(pos, cell, cutoff)
             xyz = neighbor.edge_vectors(pos, cell, first, src, shifts)
@@ -59,7 +60,7 @@ def evaluator_goldens():
             for name in ("A0", "M0", "H1", "Phi1", "A1", "M1", "H2", "H1_adj", "A0_adj"):
                 v = m.get(name)
                 data["sum_" + name] = np.array([v.sum(), np.abs(v).sum(), (v * v).sum()])
-            np.savez_compressed(OUT / f"reference_evaluator_{arch}{'_scaled' if scaled else ''}{'_zbl' if zbl else ''}.npz", **data)
+            np.savez_compressed(OUT / f"reference_evaluator_{arch}{'_scaled' if scaled else ''}{'_zbl' if zbl else ''}{'_agnesi' if agnesi else ''}.npz", **data)
             print("wrote", arch, len(pos), "atoms", len(src), "edges")
 
 

@@ -76,14 +76,16 @@ def test_stage_tensors_match_oracle(pkg, model_path, arch, n, scaled):
     assert de <= TOL_E and df <= TOL_F
 
 
-@pytest.mark.parametrize("arch,n,seed,scaled,zbl", [("small", 4, 0, False, False), ("medium", 3, 1, False, False),
-                                                    ("medium", 3, 2, True, False), ("large", 2, 3, False, False),
-                                                    ("small", 3, 4, False, True), ("medium", 2, 5, True, True)])
-def test_energy_forces_stress_vs_reference_evaluator(pkg, model_path, arch, n, seed, scaled, zbl):
+@pytest.mark.parametrize("arch,n,seed,scaled,zbl,agnesi", [("small", 4, 0, False, False, False), ("medium", 3, 1, False, False, False),
+                                                           ("medium", 3, 2, True, False, False), ("large", 2, 3, False, False, False),
+                                                           ("small", 3, 4, False, True, False), ("medium", 2, 5, True, True, False),
+                                                           ("small", 3, 6, False, False, True), ("medium", 2, 7, True, True, True),
+                                                           ("large", 2, 8, False, False, True)])
+def test_energy_forces_stress_vs_reference_evaluator(pkg, model_path, arch, n, seed, scaled, zbl, agnesi):
     """Against the reference's own serial evaluator (MACECPU<double> and <float>)."""
     if not ref.available():
         pytest.skip("oracle/_ref was not built")
-    path = model_path(arch, a0_scaled=scaled, a1_scaled=scaled, zbl=zbl)
+    path = model_path(arch, a0_scaled=scaled, a1_scaled=scaled, zbl=zbl, agnesi=agnesi)
     pos, cell, types = pkg.modelgen.srtio3(n, 0.05, seed)
     calc = pkg.Calculator(path, skin=0.5)
     out = calc.calculate(pos, cell, types)
@@ -165,10 +167,10 @@ def test_stale_generation_and_bad_inputs_raise(pkg, model_path):
         ev._compute_prepared_factorized_positions(res3["generation"], bad)
 
 
-@pytest.mark.parametrize("scaled,zbl", [(False, False), (True, False), (False, True)])
-def test_forces_are_energy_gradient(pkg, model_path, scaled, zbl):
+@pytest.mark.parametrize("scaled,zbl,agnesi", [(False, False, False), (True, False, False), (False, True, False), (True, False, True)])
+def test_forces_are_energy_gradient(pkg, model_path, scaled, zbl, agnesi):
     """Finite-difference check (reference: symmetrix/test/test_mace.py:74-85)."""
-    path = model_path("small", a0_scaled=scaled, a1_scaled=scaled, zbl=zbl)
+    path = model_path("small", a0_scaled=scaled, a1_scaled=scaled, zbl=zbl, agnesi=agnesi)
     pos, cell, types = pkg.modelgen.srtio3(2, 0.05, 4)
     calc = pkg.Calculator(path, skin=0.5)
     base = calc.calculate(pos, cell, types)

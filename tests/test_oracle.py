@@ -11,12 +11,14 @@ from oracle import mace_numpy, neighbor, ref
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
 
-@pytest.mark.parametrize("arch,scaled,zbl", [("small", False, False), ("medium", False, False), ("medium", True, False),
-                                             ("large", False, False), ("small", False, True)])
-def test_numpy_restatement_matches_reference_evaluator_golden(pkg, model_dir, arch, scaled, zbl):
-    g = np.load(GOLDEN / f"reference_evaluator_{arch}{'_scaled' if scaled else ''}{'_zbl' if zbl else ''}.npz")
-    path = model_dir / f"golden_{arch}_{int(scaled)}_{int(zbl)}.json"
-    pkg.modelgen.write_model(path, arch, seed=101, a0_scaled=scaled, a1_scaled=scaled, zbl=zbl)
+@pytest.mark.parametrize("arch,scaled,zbl,agnesi", [("small", False, False, False), ("medium", False, False, False),
+                                                    ("medium", True, False, False), ("large", False, False, False),
+                                                    ("small", False, True, False), ("small", True, True, True)])
+def test_numpy_restatement_matches_reference_evaluator_golden(pkg, model_dir, arch, scaled, zbl, agnesi):
+    name = f"reference_evaluator_{arch}{'_scaled' if scaled else ''}{'_zbl' if zbl else ''}{'_agnesi' if agnesi else ''}.npz"
+    g = np.load(GOLDEN / name)
+    path = model_dir / f"golden_{arch}_{int(scaled)}_{int(zbl)}_{int(agnesi)}.json"
+    pkg.modelgen.write_model(path, arch, seed=101, a0_scaled=scaled, a1_scaled=scaled, zbl=zbl, agnesi=agnesi)
     pos, cell, types = pkg.modelgen.srtio3(2, 0.05, 202)
     assert np.array_equal(pos, g["positions"]) and np.array_equal(types, g["types"])
     xyz = neighbor.edge_vectors(pos, cell, g["first"], g["sources"], g["shifts"])
