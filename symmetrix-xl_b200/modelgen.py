@@ -86,7 +86,9 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
             net["postprocess"] = postprocess
         return net
 
-    networks = {"R0": network((l_max + 1) * C, 0.4), "R1": network(paths * C, 0.4)}
+    # the transformed distance makes the channels more coherent: a smaller output scale keeps every stage O(1)
+    radial_scale = 0.25 if agnesi else 0.4
+    networks = {"R0": network((l_max + 1) * C, radial_scale), "R1": network(paths * C, radial_scale)}
     if a0_scaled:
         networks["A0"] = network(1, 0.3, "tanh-square")
     if a1_scaled:
