@@ -34,7 +34,7 @@ SUPERCELL = 10
 SIGMA = 0.05
 SKIN = 0.5
 SEED = 17
-# algorithmic work of the reference's formulation per (edge, channel), see DESIGN.md
+# algorithmic work of the reference's formulation per (edge, channel)
 FLOP_PER_EDGE_CHANNEL = {"l0_forward": 56, "l0_reverse": 284, "l1_forward": 408, "l1_reverse": 850}
 
 
@@ -342,7 +342,7 @@ def run_ours(args):
         dominant = max((k for k in stage_ms if k in FLOP_PER_EDGE_CHANNEL), key=lambda k: stage_ms[k])
         hbm_peak, peak_kind = _peaks()
         num_lme, num_hidden = ev.num_lme, (ev.L_max + 1) ** 2
-        # compulsory HBM bytes of one launch of each edge kernel (DESIGN.md): geometry record + source
+        # compulsory HBM bytes of one launch of each edge kernel: geometry record + source
         # index per edge, plus the node rows the kernel must read / write once
         node_rows = {"l0_forward": 16, "l0_reverse": 16, "l1_forward": num_lme + num_hidden,
                      "l1_reverse": num_lme + 3 * num_hidden}
@@ -351,7 +351,7 @@ def run_ours(args):
         achieved = alg_bytes / dom_s / 1e9
         alg_flops = FLOP_PER_EDGE_CHANNEL[dominant] * active_edges * C
         # DRAM bytes of one launch from the committed ncu capture of the default workload
-        # (dram__bytes_read.sum + dram__bytes_write.sum, profiles/l1_reverse_medium5000.md); other sizes: not captured
+        # (dram__bytes_read.sum + dram__bytes_write.sum of that kernel); other sizes: not captured
         traffic = None
         if args.workload == "srtio3" and n == 5000 and args.tile == 0:
             traffic = {"l1_reverse": 142.9e6, "l1_forward": 76.2e6}.get(dominant)

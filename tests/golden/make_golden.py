@@ -1,6 +1,6 @@
 """Generates the golden fixtures of tests/golden/ from the reference's own code.
 
-Run in a container that holds the reference checkout (default /root/reference):
+Run in a container that holds the reference checkout (path in REFERENCE below):
 
     python tests/golden/make_golden.py
 
