@@ -54,6 +54,12 @@ struct DeviceBuffer {
         SXB_CUDA(cudaMalloc(reinterpret_cast<void**>(&ptr), (count > 0 ? count : 1) * sizeof(T)));
         capacity = count;
     }
+    // reserve with ~3 % head room: for arrays whose extent fluctuates from one neighbor-list rebuild to
+    // the next (edges), so that a rebuild does not free and reallocate gigabytes
+    void reserve_with_slack(std::size_t count)
+    {
+        if (count > capacity) reserve(count + count / 32 + 1024);
+    }
     std::size_t bytes() const { return capacity * sizeof(T); }
 };
 

@@ -225,9 +225,15 @@ void Evaluator::install_graph(int num_receivers, int num_nodes, const std::vecto
     prepare_active_types(node_types);
     std::vector<int> type_to_active(model_.num_elements, -1);
     for (std::size_t a = 0; a < active_types_.size(); ++a) type_to_active[active_types_[a]] = static_cast<int>(a);
+    // internal order: receivers stably grouped by element (a counting sort), feature-only nodes after them
     std::vector<int> original(num_nodes);
     std::iota(original.begin(), original.end(), 0);
-    std::stable_sort(original.begin(), original.begin() + num_receivers, [&](int a, int b) { return node_types[a] < node_types[b]; });
+    {
+        std::vector<int> cursor(static_cast<std::size_t>(model_.num_elements) + 1, 0);
+        for (int i = 0; i < num_receivers; ++i) cursor[node_types[i] + 1] += 1;
+        for (int t = 0; t < model_.num_elements; ++t) cursor[t + 1] += cursor[t];
+        for (int i = 0; i < num_receivers; ++i) original[cursor[node_types[i]]++] = i;
+    }
     std::vector<int> internal_of(num_nodes);
     std::vector<unsigned char> atype(num_nodes), element(num_nodes);
     type_begin_.assign(active_types_.size() + 1, 0);
@@ -247,17 +253,17 @@ void Evaluator::install_graph(int num_receivers, int num_nodes, const std::vecto
     // internal CSR
     const int R = num_receivers;
     first_.reserve(R + 1);
-    sources_.reserve(num_edges);
-    if (has_shifts) shifts_.reserve(3 * num_edges);
-    edge_map_.reserve(num_edges);
-    DeviceBuffer<int> counts;
+    sources_.reserve_with_slack(num_edges);
+    if (has_shifts) shifts_.reserve_with_slack(3 * num_edges);
+    edge_map_.reserve_with_slack(num_edges);
+    DeviceBuffer<int>& counts = ig_counts_;
     counts.reserve(R + 1);
     SXB_CUDA(cudaMemsetAsync(counts.ptr, 0, (R + 1) * sizeof(int), stream_));
     gather_counts_kernel<<<blocks_for(R, 256), 256, 0, stream_>>>(R, original_.ptr, first_caller_.ptr, counts.ptr);
     launches_ += 1;
     std::size_t temp_bytes = 0;
     cub::DeviceScan::ExclusiveSum(nullptr, temp_bytes, counts.ptr, first_.ptr, R + 1, stream_);
-    DeviceBuffer<unsigned char> temp;
+    DeviceBuffer<unsigned char>& temp = ig_temp_;
     temp.reserve(temp_bytes);
     cub::DeviceScan::ExclusiveSum(temp.ptr, temp_bytes, counts.ptr, first_.ptr, R + 1, stream_);
     permute_graph_kernel<<<blocks_for(static_cast<long>(R) * 32, 256), 256, 0, stream_>>>(
@@ -271,7 +277,7 @@ void Evaluator::install_graph(int num_receivers, int num_nodes, const std::vecto
     // everything else lives in a workspace sized for one tile of receivers and is reused tile by tile
     const std::size_t N = num_receivers, ALL = num_nodes, C = model_.channels, NH = model_.num_hidden, NE = model_.num_lme;
     const std::size_t T = static_cast<std::size_t>(tile_capacity());
-    geom_.reserve(num_edges);
+    geom_.reserve_with_slack(num_edges);
     A0_.reserve(T * 16 * C);
     A0_adj_.reserve(T * 16 * C);
     M0_.reserve(N * NH * C);
@@ -293,7 +299,7 @@ void Evaluator::install_graph(int num_receivers, int num_nodes, const std::vecto
     forces_.reserve(ALL * 3);
     forces_out_.reserve(ALL * 3);
     positions_.reserve(ALL * 3);
-    if (keep_edge_forces_) edge_forces_.reserve(3 * static_cast<std::size_t>(num_edges));
+    if (keep_edge_forces_) edge_forces_.reserve_with_slack(3 * static_cast<std::size_t>(num_edges));
     SXB_CUDA(cudaStreamSynchronize(stream_));
     generation_ += 1;
     have_results_ = false;
@@ -349,9 +355,11 @@ std::pair<std::uint64_t, long> Evaluator::prepare_periodic_graph(int num_nodes, 
     SXB_CUDA(cudaMemcpyAsync(positions_.ptr, positions, 3 * sizeof(double) * n, cudaMemcpyHostToDevice, stream_));
     SXB_CUDA(cudaMemcpyAsync(cell_.ptr, cell, 9 * sizeof(double), cudaMemcpyHostToDevice, stream_));
     SXB_CUDA(cudaMemcpyAsync(inv_cell_.ptr, inverse_cell, 9 * sizeof(double), cudaMemcpyHostToDevice, stream_));
-    DeviceBuffer<double> wrapped_frac, wrapped_pos;
-    DeviceBuffer<int> wrap_shift, atom_bin, bin_sizes, bin_offsets, cursors, bin_atoms;
-    DeviceBuffer<long long> counts, offsets;
+    // cell-list scratch: members, so that a rebuild of the list allocates nothing once the sizes have settled
+    DeviceBuffer<double>&wrapped_frac = nb_wrapped_frac_, &wrapped_pos = nb_wrapped_pos_;
+    DeviceBuffer<int>&wrap_shift = nb_wrap_shift_, &atom_bin = nb_atom_bin_, &bin_sizes = nb_bin_sizes_, &bin_offsets = nb_bin_offsets_,
+                     &cursors = nb_cursors_, &bin_atoms = nb_bin_atoms_;
+    DeviceBuffer<long long>&counts = nb_counts_, &offsets = nb_offsets_;
     wrapped_frac.reserve(3 * static_cast<std::size_t>(n));
     wrapped_pos.reserve(3 * static_cast<std::size_t>(n));
     wrap_shift.reserve(3 * static_cast<std::size_t>(n));
@@ -371,7 +379,7 @@ std::pair<std::uint64_t, long> Evaluator::prepare_periodic_graph(int num_nodes, 
     std::size_t temp_bytes = 0, temp_bytes2 = 0;
     cub::DeviceScan::ExclusiveSum(nullptr, temp_bytes, bin_sizes.ptr, bin_offsets.ptr, cl.num_bins + 1, stream_);
     cub::DeviceScan::ExclusiveSum(nullptr, temp_bytes2, counts.ptr, offsets.ptr, num_receivers + 1, stream_);
-    DeviceBuffer<unsigned char> temp;
+    DeviceBuffer<unsigned char>& temp = nb_temp_;
     temp.reserve(std::max(temp_bytes, temp_bytes2));
     cub::DeviceScan::ExclusiveSum(temp.ptr, temp_bytes, bin_sizes.ptr, bin_offsets.ptr, cl.num_bins + 1, stream_);
     SXB_CUDA(cudaMemcpyAsync(cursors.ptr, bin_offsets.ptr, (num_bins + 1) * sizeof(int), cudaMemcpyDeviceToDevice, stream_));
@@ -388,8 +396,8 @@ std::pair<std::uint64_t, long> Evaluator::prepare_periodic_graph(int num_nodes, 
     if (total > static_cast<long long>(std::numeric_limits<int>::max()))
         throw std::length_error("Neighbor graph exceeds 32-bit edge indexing.");
     first_caller_.reserve(nr + 1);
-    sources_caller_.reserve(static_cast<std::size_t>(total));
-    shifts_caller_.reserve(3 * static_cast<std::size_t>(total));
+    sources_caller_.reserve_with_slack(static_cast<std::size_t>(total));
+    shifts_caller_.reserve_with_slack(3 * static_cast<std::size_t>(total));
     narrow_offsets_kernel<<<blocks_for(nr + 1, T), T, 0, stream_>>>(nr, offsets.ptr, first_caller_.ptr);
     neighbor_edges_kernel<true><<<blocks_for(nr, T), T, 0, stream_>>>(nr, cl, atom_bin.ptr, bin_offsets.ptr, bin_atoms.ptr,
                                                                       wrapped_pos.ptr, wrap_shift.ptr, cell_.ptr, nullptr,

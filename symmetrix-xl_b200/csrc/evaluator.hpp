@@ -109,6 +109,11 @@ private:
     bool use_tensor_cores_ = true;
     int num_sms_ = 148;
     int r1_pair_types_ = 1;   // active types the layer-1 table distinguishes (1 without a distance transform)
+    // scratch of the cell-list build and of the graph installation (kept between rebuilds)
+    DeviceBuffer<double> nb_wrapped_frac_, nb_wrapped_pos_;
+    DeviceBuffer<int> nb_wrap_shift_, nb_atom_bin_, nb_bin_sizes_, nb_bin_offsets_, nb_cursors_, nb_bin_atoms_, ig_counts_;
+    DeviceBuffer<long long> nb_counts_, nb_offsets_;
+    DeviceBuffer<unsigned char> nb_temp_, ig_temp_;
     DeviceBuffer<float> zbl_pairs_;    // [active pair][4]: 1/a, 14.3996 Z_i Z_j, r_max, pad (models with ZBL)
     bool use_tma_activations_ = true;   // operand-streaming form of the tensor-core linears (N in {32, 64, 128})
     int poly_g_forward_ = 1, poly_g_reverse_ = 1;   // nodes per thread in the symmetric-contraction kernels
