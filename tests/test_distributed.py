@@ -96,11 +96,14 @@ def test_exchange_plan_two_ranks_gloo(tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("arch,cells", [("small", (3, 3, 3)), ("medium", (3, 2, 2))])
-def test_single_rank_decomposition_matches_periodic_evaluation(pkg, model_path, arch, cells):
+@pytest.mark.parametrize("arch,cells,options", [("small", (3, 3, 3), {}), ("medium", (3, 2, 2), {}),
+                                                ("medium", (3, 2, 2), dict(a0_scaled=True, a1_scaled=True, zbl=True, agnesi=True)),
+                                                ("large", (3, 2, 2), {})])
+def test_single_rank_decomposition_matches_periodic_evaluation(pkg, model_path, arch, cells, options):
     """One rank whose ghosts are the periodic images of its own atoms: the three-phase path with
-    halo pack/unpack must reproduce the periodic single-GPU result."""
-    path = model_path(arch)
+    halo pack/unpack must reproduce the periodic single-GPU result (also with density scaling, ZBL
+    and species-pair tables, and for hidden irreps up to l = 2)."""
+    path = model_path(arch, **options)
     pos, cell, types = pkg.modelgen.srtio3(cells, 0.05, 8)
     ref_out = pkg.Calculator(path, skin=0.5).calculate(pos, cell, types)
     calc = pkg.distributed.DistributedCalculator(path, pkg.MACEB200, skin=0.5, device=0)
