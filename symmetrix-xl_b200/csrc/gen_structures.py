@@ -25,8 +25,11 @@ def _load_pkg():
     return mod
 
 
-# (name, edge l_max, hidden L_max, path sets of the split layer-1 kernels, optional set of each edge l)
-SHAPES = [("S0", 3, 0, 1, None), ("S1", 3, 1, 1, None), ("S2", 3, 2, 3, None)]
+# (name, edge l_max, hidden L_max, number of path sets of the split layer-1 kernels, optional explicit sets)
+# S2: set 0 = all paths with source l = 0 or 1 (88 rows, 4 source components), sets 1 and 2 share the
+# source l = 2 paths (80 and 75 rows, 5 source components each)
+SHAPES = [("S0", 3, 0, 1, None), ("S1", 3, 1, 1, None),
+          ("S2", 3, 2, 3, [[0, 3, 8, 13, 1, 4, 5, 9, 10, 14], [7, 2, 6, 11], [16, 12, 15]])]
 
 
 def emit_shape(name, l_max, L_max, tables, groups=1, by_edge_l=None):
@@ -142,10 +145,10 @@ def emit_path_groups(name, paths, row_begin, tables, groups, by_edge_l=None):
     members = [[] for _ in range(groups)]
     load = [0] * groups
     if by_edge_l is not None:
-        # sets chosen by the edge l of the path: the sets then also split the edge harmonics and the
-        # angular force terms between them, so that work is not repeated
-        for p, (_, l1, _) in enumerate(paths):
-            members[by_edge_l[l1]].append(p)
+        # explicit sets (lists of path indices), chosen so that a set touches few source components:
+        # a set loads and atomically updates only the source components of its own paths
+        assert sorted(p for group in by_edge_l for p in group) == list(range(len(paths)))
+        members = [list(group) for group in by_edge_l]
     else:
         for p in sorted(range(len(paths)), key=lambda q: -sizes[q]):      # largest first, to the lightest set
             g = min(range(groups), key=lambda q: load[q])
