@@ -130,7 +130,7 @@ __device__ __forceinline__ void umma_tf32(unsigned tmem_d, unsigned long long de
         : "memory");
 }
 
-// One TMA tile load (no multicast): box [n_tile rows][32 floats] at (k0, n0) of a [N][K] tensor.
+// One TMA tile load into this CTA only: box [n_tile rows][32 floats] at (k0, n0) of a [N][K] tensor.
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, unsigned long long* bar, int k0, int n0)
 {
     asm volatile(
