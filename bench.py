@@ -4,11 +4,13 @@
 
 Workload at every N: the MACE-OMAT-0-medium architecture (random-init weights from a seed) on a
 10x10x10 cubic SrTiO3 supercell (5,000 atoms, a = 3.905 A, sigma = 0.05 A perturbation, 0.5 A
-neighbor skin), FP32 -- per GPU.  For N > 1 each rank evaluates its own replica (weak scaling).
+neighbor skin), FP32 -- per GPU.  For N > 1 the ranks share one periodic system of N x 5,000 atoms,
+decomposed in space (weak scaling: 5,000 owned atoms per GPU; ghost features, adjoints and forces
+cross NVLink), and the line carries the difference to a single-GPU evaluation of the same system.
 `value` is timed with the positions already resident in HBM; `e2e` goes through the host-facing
 call with pinned host buffers (positions H2D, energies / forces / stress D2H inside the timed
 region).  The reference arm (`--impl reference`) times the reference's own serial CPU evaluator
-(oracle/_ref) on a bounded sample of the same workload.
+(oracle/_ref) on the host cores.
 """
 from __future__ import annotations
 
@@ -129,7 +131,13 @@ def run_distributed(args):
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(local_rank)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def all_reduce(tensor, op=None):
+        if world > 1:
+            dist.all_reduce(tensor, op=op if op is not None else dist.ReduceOp.SUM)
+
     import __graft_entry__ as graft
 
     pkg = graft.load_package()
@@ -156,7 +164,8 @@ def run_distributed(args):
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
         def barrier():
-            dist.barrier()
+            if world > 1:
+                dist.barrier()
             torch.cuda.synchronize()
 
         def step_device():
@@ -168,8 +177,8 @@ def run_distributed(args):
 
         def step_e2e():
             t0 = time.perf_counter()
-            dev = pinned.to("cuda", non_blocking=True)
-            out = calc.calculate(dev)
+            calc.owned_positions.copy_(pinned, non_blocking=True)      # H2D straight into the step's input buffer
+            out = calc.calculate()
             forces = out["forces"].cpu()
             return (time.perf_counter() - t0) * 1e3, out, forces
 
@@ -202,11 +211,26 @@ def run_distributed(args):
             e2e_ms.append(ms)
         clocks = sampler.stop()
         t = torch.tensor([float(np.mean(device_ms)), float(np.mean(e2e_ms))], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if world > 1:
+            all_reduce(t, op=dist.ReduceOp.MAX)
         step_ms, e2e_step_ms = float(t[0]), float(t[1])
         counts = torch.tensor([float(n_own), float(plan.num_ghost), float(calc.num_edges), float(launches)], device="cuda",
                               dtype=torch.float64)
-        dist.all_reduce(counts)
+        all_reduce(counts)
+        # outside the timed region: the same global system evaluated by rank 0's GPU alone
+        gathered = torch.zeros((total_atoms, 3), dtype=torch.float64, device="cuda")
+        gathered[torch.from_numpy(last_out["owned"]).cuda()] = last_out["forces"]
+        all_reduce(gathered)
+        parity = None
+        if rank == 0:
+            single_calc = pkg.Calculator(model, skin=SKIN, device=local_rank)
+            if args.tile > 0:
+                single_calc.evaluator.set_tile_size(args.tile)
+            single = single_calc.calculate(pos, cell, types)
+            parity = {"dE_eV_per_atom": abs(last_out["energy"] - single["energy"]) / total_atoms,
+                      "max_dF_eV_per_A": float(np.abs(gathered.cpu().numpy() - single["forces"]).max()),
+                      "max_dstress_eV_per_A3": float(np.abs(last_out["stress"] - single["stress"]).max())}
+            del single_calc
         if rank == 0:
             row_bytes = calc.row * 4
             ghosts = int(counts[1].item())
@@ -220,7 +244,7 @@ def run_distributed(args):
                            "atoms_per_gpu": total_atoms // world,
                            "tile": args.tile if args.tile > 0 else None,
                            "total_atoms": total_atoms, "edges_total": int(counts[2].item()), "ghosts_total": ghosts, "skin": SKIN,
-                           "parallelism": f"domain decomposition {grid[0]}x{grid[1]}x{grid[2]}, NCCL halo exchange",
+                           "parallelism": f"domain decomposition {grid[0]}x{grid[1]}x{grid[2]}, {calc.transport} halo exchange",
                            "halo_bytes_per_step": ghosts * (2 * row_bytes + 24 + 24), "elements": int(types.max()) + 1,
                            "l2": "flushed between timed steps (256 MiB write)"},
                 "atoms_per_s": total_atoms / (step_ms * 1e-3),
@@ -230,11 +254,13 @@ def run_distributed(args):
                 "gpu_launches": int(counts[3].item()),
                 "clocks": clocks,
                 "roofline": None,
+                "parity_vs_single_gpu": parity,
                 "energy_eV_per_atom": last_out["energy"] / total_atoms,
                 "wall_ms_timed_region": wall_ms,
             }))
-        dist.barrier()
-        dist.destroy_process_group()
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
 
 
 def run_ours(args):
@@ -244,7 +270,7 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if world > 1:
+    if world > 1 or args.decomposed:
         return run_distributed(args)
     torch.cuda.set_device(local_rank)
     with tempfile.TemporaryDirectory() as tmp:
@@ -341,25 +367,52 @@ def run_ours(args):
         C = ev.num_channels
         dominant = max((k for k in stage_ms if k in FLOP_PER_EDGE_CHANNEL), key=lambda k: stage_ms[k])
         hbm_peak, peak_kind = _peaks()
+        measured = pkg.measure_device_peaks(local_rank)      # FP32 FMA rate and L2-to-SM bandwidth, probed now
         num_lme, num_hidden = ev.num_lme, (ev.L_max + 1) ** 2
         # compulsory HBM bytes of one launch of each edge kernel: geometry record + source
         # index per edge, plus the node rows the kernel must read / write once
         node_rows = {"l0_forward": 16, "l0_reverse": 16, "l1_forward": num_lme + num_hidden,
                      "l1_reverse": num_lme + 3 * num_hidden}
+        # spline coefficients the formulation pulls from L2 per active edge: 16 B per radial function
+        # (+ the source feature rows in layer 1)
+        l2_bytes_per_edge = {"l0_forward": 16 * 4 * C, "l0_reverse": 16 * 4 * C,
+                             "l1_forward": 16 * ev.num_paths * C + 4 * num_hidden * C,
+                             "l1_reverse": 16 * ev.num_paths * C + 8 * num_hidden * C}
+        kernels = {}
+        for name in FLOP_PER_EDGE_CHANNEL:
+            if name not in stage_ms:
+                continue
+            seconds = stage_ms[name] * 1e-3
+            flops = FLOP_PER_EDGE_CHANNEL[name] * active_edges * C
+            hbm_bytes = num_edges * 20 + n * node_rows[name] * C * 4
+            l2_bytes = l2_bytes_per_edge[name] * active_edges
+            kernels[name] = {"ms": stage_ms[name], "fp32_tflops": flops / seconds / 1e12,
+                             "fp32_frac": flops / seconds / 1e12 / measured["fp32_fma_tflops"],
+                             "hbm_gbs": hbm_bytes / seconds / 1e9, "hbm_frac": hbm_bytes / seconds / 1e9 / hbm_peak,
+                             "l2_gbs": l2_bytes / seconds / 1e9, "l2_frac": l2_bytes / seconds / 1e9 / measured["l2_read_gbs"]}
+        dom = kernels[dominant]
         alg_bytes = num_edges * 20 + n * node_rows[dominant] * C * 4
-        dom_s = stage_ms[dominant] * 1e-3
-        achieved = alg_bytes / dom_s / 1e9
         alg_flops = FLOP_PER_EDGE_CHANNEL[dominant] * active_edges * C
-        # DRAM bytes of one launch from the committed ncu capture of the default workload
-        # (dram__bytes_read.sum + dram__bytes_write.sum of that kernel); other sizes: not captured
+        # DRAM bytes of one launch (dram__bytes_read.sum + dram__bytes_write.sum) from the tracked ncu
+        # summary of this kernel and workload, when one exists
         traffic = None
-        if args.workload == "srtio3" and n == 5000 and args.tile == 0:
-            traffic = {"l1_reverse": 142.9e6, "l1_forward": 76.2e6}.get(dominant)
-        roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                    "frac": achieved / hbm_peak, "peak_source": f"{peak_kind} copy bandwidth", "traffic": traffic,
-                    "kernel_ms": stage_ms[dominant], "algorithmic_bytes": alg_bytes,
-                    "algorithmic_gflop": alg_flops / 1e9, "achieved_fp32_tflops": alg_flops / dom_s / 1e12,
-                    "note": "edge kernels are FP32-issue / L2 bound, not HBM bound; both figures are reported"}
+        captured = ROOT / "profiles" / "dram_traffic.json"
+        if captured.exists() and args.workload == "srtio3" and n == 5000 and args.tile == 0:
+            traffic = json.loads(captured.read_text()).get("medium-5000-SrTiO3", {}).get(dominant)
+        # the edge kernels move their compulsory HBM bytes at a few per cent of the copy bandwidth; what
+        # bounds them is FP32 issue (gradient kernels) or L2-to-SM delivery (forward kernels), so the
+        # fraction reported is the larger of the FP32 and the HBM fraction, each against a measured peak
+        if dom["fp32_frac"] >= dom["hbm_frac"]:
+            roofline = {"bound": "fp32", "kernel": dominant, "achieved": dom["fp32_tflops"], "peak": measured["fp32_fma_tflops"],
+                        "unit": "TFLOP/s", "frac": dom["fp32_frac"], "peak_source": "measured FMA probe (sxb_measure_device_peaks)"}
+        else:
+            roofline = {"bound": "hbm", "kernel": dominant, "achieved": dom["hbm_gbs"], "peak": hbm_peak, "unit": "GB/s",
+                        "frac": dom["hbm_frac"], "peak_source": f"{peak_kind} copy bandwidth"}
+        roofline.update({"traffic": traffic, "kernel_ms": stage_ms[dominant], "algorithmic_bytes": alg_bytes,
+                         "algorithmic_gflop": alg_flops / 1e9, "hbm_gbs": dom["hbm_gbs"], "hbm_peak_gbs": hbm_peak,
+                         "hbm_frac": dom["hbm_frac"], "l2_read_gbs": dom["l2_gbs"], "l2_peak_gbs": measured["l2_read_gbs"],
+                         "l2_frac": dom["l2_frac"], "fp32_peak_tflops": measured["fp32_fma_tflops"],
+                         "edge_kernels": {k: {q: round(v, 4) for q, v in d.items()} for k, d in kernels.items()}})
 
         md_report = None
         if args.md_steps > 0:
@@ -479,7 +532,22 @@ def cpu_baseline(pkg, model, sample_cells=3, calls=2):
                       f"{calls} calls each ({call_ms:.0f} ms per call); one instance alone: {call_ms * 1e3 / atoms:.0f} us/atom"}
 
 
+def _available_memory_gb():
+    try:
+        for line in Path("/proc/meminfo").read_text().splitlines():
+            if line.startswith("MemAvailable:"):
+                return float(line.split()[1]) / 1e6
+    except OSError:
+        pass
+    return 16.0
+
+
 def run_reference(args):
+    """The reference's own CPU implementation of the path (its serial evaluator MACECPU<float>, compiled
+    from the reference's sources into oracle/_ref) on this arm's configuration: the full 5,000-atom
+    SrTiO3 system with the medium model.  Its source has no OpenMP, so the host cores are used the only
+    way it allows: independent evaluator instances, one per thread, each evaluating the whole system
+    (about 3 GB of host memory and 15-30 s per call each; the instance count is capped by the memory)."""
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
@@ -491,20 +559,21 @@ def run_reference(args):
         if not ref.available():
             print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref was not built in this snapshot"}))
             return
-        cells = 3
-        warm = max(1, min(args.warmup, 2))
-        steps = max(1, min(args.steps, 5))
-        threads = _host_threads()
+        cells = SUPERCELL
+        warm = 1                                   # the first call also builds the radial cache
+        steps = max(1, min(args.steps, 2))
+        threads = max(1, min(_host_threads(), int(_available_memory_gb() / 4.0)))
         value, call_ms, atoms, edges = _time_reference(pkg, model, cells, warm, steps, threads)
-        ms = value * atoms / 1e3      # aggregated time per 135-atom step
-        sample = (f"{atoms}-atom SrTiO3 ({cells}x{cells}x{cells}) with the workload's model and perturbation, {edges} edges; "
+        ms = value * atoms / 1e3      # aggregated time per 5,000-atom evaluation
+        sample = (f"the whole workload: {atoms}-atom SrTiO3 ({cells}x{cells}x{cells}), {edges} edges at the model cutoff; "
                   f"{threads} independent instances of the reference's serial evaluator MACECPU<float> (no OpenMP in its "
-                  f"source), one per host thread, {steps} timed calls each, {call_ms:.0f} ms per call")
+                  f"source), one per host thread, {steps} timed calls each after {warm} warm-up, {call_ms / 1e3:.1f} s per call")
         print(json.dumps({
             "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps,
             "warmup": warm, "ms_per_step": ms, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "medium-5000-SrTiO3", "sample_atoms": atoms},
+            "config": {"workload": "medium-5000-SrTiO3", "atoms_per_gpu": atoms, "total_atoms": atoms, "skin": 0.0,
+                       "elements": int(types.max()) + 1},
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "reference", "sample": sample},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }))
@@ -522,6 +591,9 @@ def main():
     parser.add_argument("--workload", default="srtio3", choices=["srtio3", "random"],
                         help="srtio3: medium model on SrTiO3 (default); random: 0e+1o+2e model on a disordered 10-element solid")
     parser.add_argument("--atoms", type=int, default=20000, help="atoms of the random workload")
+    parser.add_argument("--decomposed", action="store_true",
+                        help="with one GPU: run the domain-decomposed path on a single rank (ghosts = periodic images of "
+                             "the rank's own atoms), to separate its bookkeeping from the inter-GPU exchange")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -42,6 +42,19 @@ typedef struct sxb_model_info {
  * symmetrix/source/cpp/mace_kokkos.cpp:262).  Reads a format-v4 compact model JSON, builds the
  * spline tables and uploads the weights to CUDA device `device_ordinal`. */
 int sxb_create(const char* model_json_path, int device_ordinal, sxb_evaluator** out);
+/* The same with a named prediction head of a multi-head model file (the `head` argument of the
+ * reference constructor; select_prediction_head, libsymmetrix/source/prediction_heads.hpp:10-90):
+ * the head's atomic energies, readout weights and ZBL coefficients replace the top-level ones.
+ * head NULL or "" selects the file's default head.  sxb_selected_head copies the name in use
+ * (empty for a file without heads) into out[capacity]. */
+int sxb_create_with_head(const char* model_json_path, int device_ordinal, const char* head, sxb_evaluator** out);
+int sxb_selected_head(const sxb_evaluator* evaluator, char* out, int32_t capacity);
+/* Parses and validates a model file on the host only (no CUDA device is touched): the structure it
+ * would run with, the head that would be selected and that head's atomic energies.  Counterpart of
+ * the reference's metadata inspection (libsymmetrix/source/model_metadata.cpp).  Any output pointer
+ * may be NULL. */
+int sxb_model_file_info(const char* model_json_path, const char* head, sxb_model_info* info, char* selected_head,
+                        int32_t head_capacity, double* atomic_energies, int32_t energies_capacity);
 void sxb_destroy(sxb_evaluator* evaluator);
 const char* sxb_last_error(void);
 
@@ -193,6 +206,30 @@ int sxb_halo_pack(sxb_evaluator* evaluator, int32_t which, const int32_t* device
 int sxb_halo_unpack(sxb_evaluator* evaluator, int32_t which, const int32_t* device_indices, int64_t count,
                     const float* device_in, int32_t accumulate);
 int sxb_add_force_rows(sxb_evaluator* evaluator, const int32_t* device_indices, int64_t count, const double* device_in);
+/* Exchange without staging copies.  Ghost nodes follow the receivers in every node tensor, in the
+ * caller's ghost order, so a rank that orders its ghosts by owner can receive H1 rows straight into,
+ * and send H1_adj rows straight from, the tail of the tensor: sxb_halo_tensor returns the device
+ * address of H1 (which = 0) or H1_adj (which = 1), the floats per row and the row at which the ghosts
+ * start (counterpart of the public views H1 / H1_adj of MACEKokkos, libsymmetrix/source/mace_kokkos.hpp:
+ * 672-708, that the pair style packs from and unpacks into).
+ * sxb_gather_position_rows: out[k] = rows[indices[k]] (+ offsets[k]), three doubles per row -- the
+ * positions of the owned atoms that other ranks hold as ghosts, displaced to their images (the pair
+ * style leaves this to LAMMPS' own forward communication of x).
+ * sxb_pack_ghost_forces / sxb_unpack_ghost_forces: the closing exchange after finish.  The send buffer
+ * holds, per peer p, the force rows of the ghosts p owns (ghost_begin[p] .. ghost_begin[p+1]) followed
+ * by four rows carrying this rank's energy and virial; unpack adds the returned rows into the owners'
+ * force rows (send_begin / indices = the rank's send list) and sums the totals of all ranks in rank
+ * order into totals_out f64[10], so the energy / virial reduction needs no collective of its own
+ * (pair style: reverse communication of f, pair_symmetrix_mace_kokkos.cpp:1853-1876, and LAMMPS' own
+ * reductions of eng_vdwl / virial).  Buffers: f64[(rows + 4*world)*3]; the *_begin arrays are device
+ * int32[world+1]. */
+int sxb_halo_tensor(sxb_evaluator* evaluator, int32_t which, float** device_tensor, int64_t* row_floats, int64_t* first_ghost_row);
+int sxb_gather_position_rows(sxb_evaluator* evaluator, const double* device_rows, const int32_t* device_indices, int64_t count,
+                             const double* device_offsets, double* device_out);
+int sxb_pack_ghost_forces(sxb_evaluator* evaluator, int32_t world, const int32_t* device_ghost_begin, int64_t num_ghosts,
+                          double* device_out);
+int sxb_unpack_ghost_forces(sxb_evaluator* evaluator, int32_t world, const int32_t* device_send_begin,
+                            const int32_t* device_indices, int64_t num_rows, const double* device_in, double* device_totals_out);
 int sxb_set_stream(sxb_evaluator* evaluator, void* stream);
 
 /* Tiled streaming (the reference's fixed-workspace dual-layer plan, allow_fixed_workspace:
@@ -212,6 +249,13 @@ int sxb_set_tile_size(sxb_evaluator* evaluator, int32_t receivers_per_tile);
 int sxb_set_profiling(sxb_evaluator* evaluator, int32_t enabled);
 int sxb_profile_entry(const sxb_evaluator* evaluator, int32_t index, char* name, int32_t name_capacity, float* ms,
                       int32_t* launches, int32_t* count);
+
+/* Measured denominators for the rooflines of the edge kernels on CUDA device `device_ordinal`: the
+ * FP32 FMA rate of the CUDA cores (TFLOP/s, 2 flop per FMA) and the L2-to-SM read bandwidth on an
+ * L2-resident 32 MB table read 512 contiguous bytes per warp at warp-random rows (GB/s), each from a
+ * probe kernel of a few milliseconds timed with CUDA events.  No counterpart in the reference (its
+ * documentation quotes vendor peaks).  Either output pointer may be NULL to skip that probe. */
+int sxb_measure_device_peaks(int32_t device_ordinal, double* fp32_fma_tflops, double* l2_read_gbs);
 
 #ifdef __cplusplus
 }

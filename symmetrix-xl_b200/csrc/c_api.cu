@@ -13,7 +13,7 @@
 
 struct sxb_evaluator {
     sxb::Evaluator impl;
-    sxb_evaluator(const char* path, int device) : impl(path, device) {}
+    sxb_evaluator(const char* path, int device, const char* head) : impl(path, device, head ? head : "") {}
 };
 
 namespace {
@@ -68,7 +68,50 @@ int sxb_create(const char* model_json_path, int device_ordinal, sxb_evaluator** 
     return guarded([&] {
         require(model_json_path, "model_json_path");
         require(out, "out");
-        *out = new sxb_evaluator(model_json_path, device_ordinal);
+        *out = new sxb_evaluator(model_json_path, device_ordinal, nullptr);
+    });
+}
+
+int sxb_create_with_head(const char* model_json_path, int device_ordinal, const char* head, sxb_evaluator** out)
+{
+    return guarded([&] {
+        require(model_json_path, "model_json_path");
+        require(out, "out");
+        *out = new sxb_evaluator(model_json_path, device_ordinal, head);
+    });
+}
+
+int sxb_model_file_info(const char* model_json_path, const char* head, sxb_model_info* info, char* selected_head,
+                        int32_t head_capacity, double* atomic_energies, int32_t energies_capacity)
+{
+    return guarded([&] {
+        require(model_json_path, "model_json_path");
+        const sxb::HostModel m = sxb::load_model(model_json_path, head ? head : "");
+        if (info != nullptr) {
+            info->num_elements = m.num_elements; info->num_channels = m.channels; info->l_max = m.l_max;
+            info->hidden_l_max = m.hidden_l_max; info->num_paths = m.num_paths; info->num_lme = m.num_lme;
+            info->shape_id = m.shape_id; info->reserved = 0; info->r_cut = m.r_cut;
+        }
+        if (selected_head != nullptr) {
+            if (head_capacity <= static_cast<int32_t>(m.selected_head.size()))
+                throw std::invalid_argument("head name buffer is too small.");
+            std::memcpy(selected_head, m.selected_head.c_str(), m.selected_head.size() + 1);
+        }
+        if (atomic_energies != nullptr) {
+            if (energies_capacity < m.num_elements) throw std::invalid_argument("atomic_energies buffer is too small.");
+            for (int a = 0; a < m.num_elements; ++a) atomic_energies[a] = m.atomic_energies[a];
+        }
+    });
+}
+
+int sxb_selected_head(const sxb_evaluator* ev, char* out, int32_t capacity)
+{
+    return guarded([&] {
+        require(ev, "evaluator");
+        require(out, "out");
+        const std::string& name = ev->impl.model().selected_head;
+        if (capacity <= static_cast<int32_t>(name.size())) throw std::invalid_argument("head name buffer is too small.");
+        std::memcpy(out, name.c_str(), name.size() + 1);
     });
 }
 
@@ -313,6 +356,45 @@ int sxb_add_force_rows(sxb_evaluator* ev, const int32_t* device_indices, int64_t
         require(ev, "evaluator");
         if (count > 0) { require(device_indices, "device_indices"); require(device_in, "device_in"); }
         ev->impl.add_force_rows(device_indices, count, device_in);
+    });
+}
+
+int sxb_halo_tensor(sxb_evaluator* ev, int32_t which, float** device_tensor, int64_t* row_floats, int64_t* first_ghost_row)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(device_tensor, "device_tensor");
+        *device_tensor = ev->impl.halo_tensor(which);
+        if (row_floats) *row_floats = ev->impl.halo_row_floats();
+        if (first_ghost_row) *first_ghost_row = ev->impl.num_receivers();
+    });
+}
+
+int sxb_gather_position_rows(sxb_evaluator* ev, const double* device_rows, const int32_t* device_indices, int64_t count,
+                             const double* device_offsets, double* device_out)
+{
+    return guarded([&] {
+        require(ev, "evaluator");
+        if (count > 0) { require(device_rows, "device_rows"); require(device_indices, "device_indices"); require(device_out, "device_out"); }
+        ev->impl.gather_position_rows(device_rows, device_indices, count, device_offsets, device_out);
+    });
+}
+
+int sxb_pack_ghost_forces(sxb_evaluator* ev, int32_t world, const int32_t* device_ghost_begin, int64_t num_ghosts, double* device_out)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(device_ghost_begin, "device_ghost_begin"); require(device_out, "device_out");
+        ev->impl.pack_ghost_forces(world, device_ghost_begin, num_ghosts, device_out);
+    });
+}
+
+int sxb_unpack_ghost_forces(sxb_evaluator* ev, int32_t world, const int32_t* device_send_begin, const int32_t* device_indices,
+                            int64_t num_rows, const double* device_in, double* device_totals_out)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(device_send_begin, "device_send_begin"); require(device_in, "device_in");
+        require(device_totals_out, "device_totals_out");
+        if (num_rows > 0) require(device_indices, "device_indices");
+        ev->impl.unpack_ghost_forces(world, device_send_begin, device_indices, num_rows, device_in, device_totals_out);
     });
 }
 

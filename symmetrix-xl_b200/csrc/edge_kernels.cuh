@@ -117,7 +117,8 @@ __global__ void geometry_from_positions_kernel(int num_nodes, const int* __restr
     const int begin = first[warp], end = first[warp + 1];
     for (int e = begin + lane; e < end; e += 32) {
         const int oj = original[sources[e]];
-        const double sx = shifts[3 * e], sy = shifts[3 * e + 1], sz = shifts[3 * e + 2];
+        const size_t se = 3 * static_cast<size_t>(e);
+        const double sx = shifts[se], sy = shifts[se + 1], sz = shifts[se + 2];
         const double dx = positions[3 * oj] - xi + sx * cell[0] + sy * cell[3] + sz * cell[6];
         const double dy = positions[3 * oj + 1] - yi + sx * cell[1] + sy * cell[4] + sz * cell[7];
         const double dz = positions[3 * oj + 2] - zi + sx * cell[2] + sy * cell[5] + sz * cell[8];

@@ -4,6 +4,7 @@
 // statement libsymmetrix/source/mace.cpp:232-319).
 #include "evaluator.hpp"
 
+#include <cub/device/device_radix_sort.cuh>
 #include <cub/device/device_scan.cuh>
 
 #include <algorithm>
@@ -84,25 +85,28 @@ inline int blocks_for(long n, int threads) { return static_cast<int>((n + thread
     do {                                                                                                     \
         const dim3 grid_(blocks_for((T), kPolyNodesPerBlock), (C) / 32);                                     \
         const std::size_t smem_ = static_cast<std::size_t>(TERMS) * 32 * sizeof(float);                      \
-        if ((G) == 2) {                                                                                      \
-            SXB_CUDA(cudaFuncSetAttribute(KERNEL<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_))); \
-            KERNEL<2><<<grid_, 32 * kPolyWarps, smem_, (STREAM)>>>(__VA_ARGS__);                             \
-        } else {                                                                                             \
-            SXB_CUDA(cudaFuncSetAttribute(KERNEL<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_))); \
-            KERNEL<1><<<grid_, 32 * kPolyWarps, smem_, (STREAM)>>>(__VA_ARGS__);                             \
-        }                                                                                                    \
+        if ((G) == 2) KERNEL<2><<<grid_, 32 * kPolyWarps, smem_, (STREAM)>>>(__VA_ARGS__);                   \
+        else KERNEL<1><<<grid_, 32 * kPolyWarps, smem_, (STREAM)>>>(__VA_ARGS__);                            \
+    } while (0)
+
+// Opts a contraction kernel into the dynamic shared memory its weight slice needs (once, at start-up).
+#define SXB_ALLOW_POLY_SMEM(KERNEL, TERMS)                                                                   \
+    do {                                                                                                     \
+        const int smem_ = static_cast<int>(static_cast<std::size_t>(TERMS) * 32 * sizeof(float));            \
+        SXB_CUDA(cudaFuncSetAttribute(KERNEL<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_));       \
+        SXB_CUDA(cudaFuncSetAttribute(KERNEL<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_));       \
     } while (0)
 
 }  // namespace
 
-Evaluator::Evaluator(const std::string& json_path, int device_ordinal) : device_(device_ordinal)
+Evaluator::Evaluator(const std::string& json_path, int device_ordinal, const std::string& head) : device_(device_ordinal)
 {
     int count = 0;
     if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0)
         throw std::runtime_error("No CUDA device is available; this library has no CPU fallback.");
     if (device_ordinal < 0 || device_ordinal >= count) throw std::invalid_argument("CUDA device ordinal is out of range.");
     SXB_CUDA(cudaSetDevice(device_));
-    model_ = load_model(json_path);
+    model_ = load_model(json_path, head);
     if (model_.shape_id > 2) throw std::invalid_argument("This build carries kernels for hidden irreps up to 0e+1o+2e only.");
     if (model_.shape_id == 2 && model_.channels != 128)
         throw std::invalid_argument("Hidden irreps 0e+1o+2e are compiled for 128 channels only.");
@@ -124,6 +128,7 @@ Evaluator::Evaluator(const std::string& json_path, int device_ordinal) : device_
     upload(readout2_w2_, model_.readout2_w2, stream_);
     upload(atomic_energies_, model_.atomic_energies, stream_);
     if (const char* env = std::getenv("SXB_SIMT_LINEARS")) use_tensor_cores_ = !(env[0] == '1');
+    if (const char* env = std::getenv("SXB_CUDA_GRAPHS")) use_graphs_ = env[0] != '0';
     if (const char* env = std::getenv("SXB_POLY_GROUP")) {   // nodes per thread in the contraction kernels: "<forward><reverse>"
         if (env[0] == '1' || env[0] == '2') poly_g_forward_ = env[0] - '0';
         if (env[0] != 0 && (env[1] == '1' || env[1] == '2')) poly_g_reverse_ = env[1] - '0';
@@ -135,6 +140,12 @@ Evaluator::Evaluator(const std::string& json_path, int device_ordinal) : device_
     for (int a = 0; a < model_.num_elements; ++a)
         upload_split(s_h2_skip_[a], model_.h2_skip.data() + static_cast<std::size_t>(a) * C * C, C, C);
     upload_split(s_h2_m1_, model_.h2_m1.data(), C, C);
+    SXB_ALLOW_POLY_SMEM(m0_forward_kernel_S0, SXB_S0_M0_NUM_TERMS); SXB_ALLOW_POLY_SMEM(m0_reverse_kernel_S0, SXB_S0_M0_NUM_TERMS);
+    SXB_ALLOW_POLY_SMEM(m0_forward_kernel_S1, SXB_S1_M0_NUM_TERMS); SXB_ALLOW_POLY_SMEM(m0_reverse_kernel_S1, SXB_S1_M0_NUM_TERMS);
+    SXB_ALLOW_POLY_SMEM(m0_forward_kernel_S2, SXB_S2_M0_NUM_TERMS); SXB_ALLOW_POLY_SMEM(m0_reverse_kernel_S2, SXB_S2_M0_NUM_TERMS);
+    SXB_ALLOW_POLY_SMEM(m1_forward_kernel_S0, SXB_S0_M1_NUM_TERMS); SXB_ALLOW_POLY_SMEM(m1_reverse_kernel_S0, SXB_S0_M1_NUM_TERMS);
+    SXB_ALLOW_POLY_SMEM(m1_forward_kernel_S1, SXB_S1_M1_NUM_TERMS); SXB_ALLOW_POLY_SMEM(m1_reverse_kernel_S1, SXB_S1_M1_NUM_TERMS);
+    SXB_ALLOW_POLY_SMEM(m1_forward_kernel_S2, SXB_S2_M1_NUM_TERMS); SXB_ALLOW_POLY_SMEM(m1_reverse_kernel_S2, SXB_S2_M1_NUM_TERMS);
     SXB_CUDA(cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes));
     SXB_CUDA(cudaFuncSetAttribute(tc_gemm_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kT3SmemBytes));
     SXB_CUDA(cudaDeviceGetAttribute(&num_sms_, cudaDevAttrMultiProcessorCount, device_));
@@ -159,6 +170,7 @@ Evaluator::Evaluator(const std::string& json_path, int device_ordinal) : device_
 Evaluator::~Evaluator()
 {
     cudaSetDevice(device_);
+    drop_step_graphs();
     if (event_begin_) cudaEventDestroy(event_begin_);
     if (event_end_) cudaEventDestroy(event_end_);
     for (auto e : event_pool_) cudaEventDestroy(e);
@@ -184,6 +196,8 @@ void Evaluator::prepare_active_types(const std::vector<int>& node_types)
     {
         int pairs = 1;
         const auto r1 = build_r1_table(model_, active_types_, &pairs);
+        if (r1.size() > static_cast<std::size_t>(std::numeric_limits<int>::max()))
+            throw std::length_error("Layer-1 spline table exceeds 32-bit indexing; too many active element types.");
         upload(r1_table_, r1, stream_);
         r1_pair_types_ = model_.agnesi ? static_cast<int>(active_types_.size()) : 1;
         if (model_.a0_scaled) upload(density0_table_, build_density_table(model_, "A0", active_types_), stream_);
@@ -307,6 +321,46 @@ void Evaluator::install_graph(int num_receivers, int num_nodes, const std::vecto
     phase_ = 0;
 }
 
+namespace {
+// Bins and stencil reach of the cell list.  Per axis: the spacing of the lattice planes is
+// 1 / |column of the inverse cell|; bins = floor(spacing / cutoff), at least one, so a bin is never
+// thinner than the cutoff; reach = ceil(cutoff * bins / spacing) + 1 bins on either side.  These are
+// the extents of the reference's builder (libsymmetrix/source/neighbor_graph_kokkos.cpp:84-120), which
+// fixes the candidate order.
+CellGrid plan_cell_grid(const double* cell, const double* inverse_cell, double cutoff)
+{
+    if (!std::isfinite(cutoff) || !(cutoff > 0.0)) throw std::invalid_argument("Neighbor cutoff must be finite and positive.");
+    double worst = 0.0;
+    bool finite = true;
+    for (int q = 0; q < 9; ++q) finite = finite && std::isfinite(cell[q]) && std::isfinite(inverse_cell[q]);
+    if (!finite) throw std::invalid_argument("Cell and inverse cell must be finite.");
+    for (int r = 0; r < 3; ++r)
+        for (int c = 0; c < 3; ++c) {
+            const double dot = cell[3 * r] * inverse_cell[c] + cell[3 * r + 1] * inverse_cell[3 + c] + cell[3 * r + 2] * inverse_cell[6 + c];
+            worst = std::max(worst, std::abs(dot - (r == c ? 1.0 : 0.0)));
+        }
+    if (worst > 1e-9) throw std::invalid_argument("inverse_cell is not the inverse of cell.");
+    CellGrid grid;
+    std::size_t total = 1;
+    for (int axis = 0; axis < 3; ++axis) {
+        const double inverse_spacing = std::sqrt(inverse_cell[axis] * inverse_cell[axis] + inverse_cell[3 + axis] * inverse_cell[3 + axis]
+                                                 + inverse_cell[6 + axis] * inverse_cell[6 + axis]);
+        if (!(inverse_spacing > 0.0)) throw std::invalid_argument("Cell is singular.");
+        const double whole_bins = std::floor((1.0 / inverse_spacing) / cutoff);
+        if (whole_bins >= static_cast<double>(std::numeric_limits<int>::max()))
+            throw std::length_error("Cell list needs more bins along one axis than 32-bit indexing allows.");
+        grid.bins[axis] = std::max(1, static_cast<int>(whole_bins));
+        grid.reach[axis] = std::max(1, static_cast<int>(std::ceil(cutoff * inverse_spacing * grid.bins[axis]) + 1.0));
+        total *= static_cast<std::size_t>(grid.bins[axis]);
+        if (total >= static_cast<std::size_t>(std::numeric_limits<int>::max()))
+            throw std::length_error("Cell list needs more bins than 32-bit indexing allows.");
+    }
+    grid.num_bins = static_cast<int>(total);
+    grid.cutoff_squared = cutoff * cutoff;
+    return grid;
+}
+}  // namespace
+
 std::pair<std::uint64_t, long> Evaluator::prepare_periodic_graph(int num_nodes, const int* node_types, const double* positions,
                                                                  const double* cell, const double* inverse_cell, double cutoff,
                                                                  int num_receivers)
@@ -315,94 +369,69 @@ std::pair<std::uint64_t, long> Evaluator::prepare_periodic_graph(int num_nodes, 
     if (num_nodes <= 0) throw std::invalid_argument("Neighbor graph needs at least one node.");
     if (num_receivers < 0) num_receivers = num_nodes;
     if (num_receivers == 0 || num_receivers > num_nodes) throw std::invalid_argument("Receiver count must lie in [1, num_nodes].");
-    if (!std::isfinite(cutoff) || !(cutoff > 0.0)) throw std::invalid_argument("Neighbor graph cutoff must be finite and positive.");
-    for (int i = 0; i < 3 * num_nodes; ++i)
-        if (!std::isfinite(positions[i])) throw std::invalid_argument("Neighbor graph positions must be finite.");
-    for (int i = 0; i < 9; ++i)
-        if (!std::isfinite(cell[i]) || !std::isfinite(inverse_cell[i]))
-            throw std::invalid_argument("Neighbor graph cell must be finite.");
-    for (int row = 0; row < 3; ++row)
-        for (int column = 0; column < 3; ++column) {
-            double product = 0.0;
-            for (int inner = 0; inner < 3; ++inner) product += cell[3 * row + inner] * inverse_cell[3 * inner + column];
-            if (std::abs(product - (row == column ? 1.0 : 0.0)) > 1e-9)
-                throw std::invalid_argument("Neighbor graph cell and inverse cell are inconsistent.");
-        }
-    CellList cl;
-    for (int axis = 0; axis < 3; ++axis) {
-        double inverse_norm_squared = 0.0;
-        for (int component = 0; component < 3; ++component) {
-            const double value = inverse_cell[3 * component + axis];
-            inverse_norm_squared += value * value;
-        }
-        if (!(inverse_norm_squared > 0.0)) throw std::invalid_argument("Neighbor graph cell must be invertible.");
-        const double face_height = 1.0 / std::sqrt(inverse_norm_squared);
-        const double bins = std::floor(face_height / cutoff);
-        if (bins >= static_cast<double>(std::numeric_limits<int>::max()))
-            throw std::length_error("Neighbor graph bin extent exceeds 32-bit indexing.");
-        cl.bins[axis] = std::max(1, static_cast<int>(bins));
-        const double reach = std::ceil(cutoff * std::sqrt(inverse_norm_squared) * cl.bins[axis]) + 1.0;
-        cl.reach[axis] = std::max(1, static_cast<int>(reach));
-    }
-    const std::size_t num_bins = static_cast<std::size_t>(cl.bins[0]) * cl.bins[1] * cl.bins[2];
-    if (num_bins >= static_cast<std::size_t>(std::numeric_limits<int>::max()))
-        throw std::length_error("Neighbor graph bin count exceeds 32-bit indexing.");
-    cl.num_bins = static_cast<int>(num_bins);
-    cl.cutoff_squared = cutoff * cutoff;
+    const CellGrid grid = plan_cell_grid(cell, inverse_cell, cutoff);
+    const int n = num_nodes, nr = num_receivers, threads = 256;
+    const std::size_t num_bins = static_cast<std::size_t>(grid.num_bins);
 
-    const int n = num_nodes;
     positions_.reserve(3 * static_cast<std::size_t>(n));
     SXB_CUDA(cudaMemcpyAsync(positions_.ptr, positions, 3 * sizeof(double) * n, cudaMemcpyHostToDevice, stream_));
     SXB_CUDA(cudaMemcpyAsync(cell_.ptr, cell, 9 * sizeof(double), cudaMemcpyHostToDevice, stream_));
     SXB_CUDA(cudaMemcpyAsync(inv_cell_.ptr, inverse_cell, 9 * sizeof(double), cudaMemcpyHostToDevice, stream_));
-    // cell-list scratch: members, so that a rebuild of the list allocates nothing once the sizes have settled
-    DeviceBuffer<double>&wrapped_frac = nb_wrapped_frac_, &wrapped_pos = nb_wrapped_pos_;
-    DeviceBuffer<int>&wrap_shift = nb_wrap_shift_, &atom_bin = nb_atom_bin_, &bin_sizes = nb_bin_sizes_, &bin_offsets = nb_bin_offsets_,
-                     &cursors = nb_cursors_, &bin_atoms = nb_bin_atoms_;
-    DeviceBuffer<long long>&counts = nb_counts_, &offsets = nb_offsets_;
-    wrapped_frac.reserve(3 * static_cast<std::size_t>(n));
-    wrapped_pos.reserve(3 * static_cast<std::size_t>(n));
-    wrap_shift.reserve(3 * static_cast<std::size_t>(n));
-    atom_bin.reserve(n);
-    bin_sizes.reserve(num_bins + 1);
-    bin_offsets.reserve(num_bins + 1);
-    cursors.reserve(num_bins + 1);
-    bin_atoms.reserve(n);
-    counts.reserve(n + 1);
-    offsets.reserve(n + 1);
-    SXB_CUDA(cudaMemsetAsync(bin_sizes.ptr, 0, (num_bins + 1) * sizeof(int), stream_));
-    SXB_CUDA(cudaMemsetAsync(counts.ptr, 0, (n + 1) * sizeof(long long), stream_));
-    const int T = 128;
-    wrap_positions_kernel<<<blocks_for(n, T), T, 0, stream_>>>(n, positions_.ptr, inv_cell_.ptr, cell_.ptr, wrapped_frac.ptr,
-                                                                wrapped_pos.ptr, wrap_shift.ptr);
-    count_bins_kernel<<<blocks_for(n, T), T, 0, stream_>>>(n, cl, wrapped_frac.ptr, atom_bin.ptr, bin_sizes.ptr);
-    std::size_t temp_bytes = 0, temp_bytes2 = 0;
-    cub::DeviceScan::ExclusiveSum(nullptr, temp_bytes, bin_sizes.ptr, bin_offsets.ptr, cl.num_bins + 1, stream_);
-    cub::DeviceScan::ExclusiveSum(nullptr, temp_bytes2, counts.ptr, offsets.ptr, num_receivers + 1, stream_);
-    DeviceBuffer<unsigned char>& temp = nb_temp_;
-    temp.reserve(std::max(temp_bytes, temp_bytes2));
-    cub::DeviceScan::ExclusiveSum(temp.ptr, temp_bytes, bin_sizes.ptr, bin_offsets.ptr, cl.num_bins + 1, stream_);
-    SXB_CUDA(cudaMemcpyAsync(cursors.ptr, bin_offsets.ptr, (num_bins + 1) * sizeof(int), cudaMemcpyDeviceToDevice, stream_));
-    fill_bins_kernel<<<blocks_for(n, T), T, 0, stream_>>>(n, atom_bin.ptr, cursors.ptr, bin_atoms.ptr);
-    sort_bins_kernel<<<blocks_for(cl.num_bins, T), T, 0, stream_>>>(cl.num_bins, bin_offsets.ptr, bin_atoms.ptr);
-    const int nr = num_receivers;
-    neighbor_edges_kernel<false><<<blocks_for(nr, T), T, 0, stream_>>>(nr, cl, atom_bin.ptr, bin_offsets.ptr, bin_atoms.ptr,
-                                                                       wrapped_pos.ptr, wrap_shift.ptr, cell_.ptr, counts.ptr,
-                                                                       nullptr, nullptr, nullptr);
-    cub::DeviceScan::ExclusiveSum(temp.ptr, temp_bytes2, counts.ptr, offsets.ptr, nr + 1, stream_);
+    // cell-list scratch lives in members: a rebuild allocates nothing once the sizes have settled
+    nb_wrapped_pos_.reserve(3 * static_cast<std::size_t>(n));
+    nb_sorted_pos_.reserve(3 * static_cast<std::size_t>(n));
+    nb_wrap_count_.reserve(3 * static_cast<std::size_t>(n));
+    nb_atom_bin_.reserve(n);
+    nb_atom_index_.reserve(n);
+    nb_sorted_bin_.reserve(n);
+    nb_sorted_atoms_.reserve(n);
+    nb_bin_sizes_.reserve(num_bins + 1);
+    nb_bin_begin_.reserve(num_bins + 1);
+    nb_counts_.reserve(nr + 1);
+    nb_offsets_.reserve(nr + 1);
+    int key_bits = 1;
+    while ((1ll << key_bits) < static_cast<long long>(num_bins)) ++key_bits;
+    std::size_t scan_bins_bytes = 0, scan_edges_bytes = 0, sort_bytes = 0;
+    cub::DeviceScan::ExclusiveSum(nullptr, scan_bins_bytes, nb_bin_sizes_.ptr, nb_bin_begin_.ptr, grid.num_bins + 1, stream_);
+    cub::DeviceScan::ExclusiveSum(nullptr, scan_edges_bytes, nb_counts_.ptr, nb_offsets_.ptr, nr + 1, stream_);
+    cub::DeviceRadixSort::SortPairs(nullptr, sort_bytes, nb_atom_bin_.ptr, nb_sorted_bin_.ptr, nb_atom_index_.ptr, nb_sorted_atoms_.ptr, n,
+                                    0, key_bits, stream_);
+    nb_temp_.reserve(std::max(sort_bytes, std::max(scan_bins_bytes, scan_edges_bytes)));
+
+    SXB_CUDA(cudaMemsetAsync(nb_bin_sizes_.ptr, 0, (num_bins + 1) * sizeof(int), stream_));
+    SXB_CUDA(cudaMemsetAsync(nb_counts_.ptr, 0, (nr + 1) * sizeof(long long), stream_));
+    SXB_CUDA(cudaMemsetAsync(error_flag_.ptr, 0, sizeof(int), stream_));
+    wrap_and_bin_kernel<<<blocks_for(n, threads), threads, 0, stream_>>>(n, grid, positions_.ptr, inv_cell_.ptr, cell_.ptr,
+                                                                          nb_wrapped_pos_.ptr, nb_wrap_count_.ptr, nb_atom_bin_.ptr,
+                                                                          nb_atom_index_.ptr, nb_bin_sizes_.ptr, error_flag_.ptr);
+    cub::DeviceScan::ExclusiveSum(nb_temp_.ptr, scan_bins_bytes, nb_bin_sizes_.ptr, nb_bin_begin_.ptr, grid.num_bins + 1, stream_);
+    // stable sort by bin: inside a bin the atoms stay in ascending index
+    cub::DeviceRadixSort::SortPairs(nb_temp_.ptr, sort_bytes, nb_atom_bin_.ptr, nb_sorted_bin_.ptr, nb_atom_index_.ptr,
+                                    nb_sorted_atoms_.ptr, n, 0, key_bits, stream_);
+    gather_sorted_positions_kernel<<<blocks_for(n, threads), threads, 0, stream_>>>(n, nb_sorted_atoms_.ptr, nb_wrapped_pos_.ptr,
+                                                                                     nb_sorted_pos_.ptr);
+    const int warp_blocks = blocks_for(static_cast<long>(nr) * 32, threads);
+    receiver_edges_kernel<false><<<warp_blocks, threads, 0, stream_>>>(nr, grid, nb_atom_bin_.ptr, nb_bin_begin_.ptr, nb_sorted_atoms_.ptr,
+                                                                        nb_sorted_pos_.ptr, nb_wrapped_pos_.ptr, nb_wrap_count_.ptr,
+                                                                        cell_.ptr, nb_counts_.ptr, nullptr, nullptr, nullptr);
+    cub::DeviceScan::ExclusiveSum(nb_temp_.ptr, scan_edges_bytes, nb_counts_.ptr, nb_offsets_.ptr, nr + 1, stream_);
     long long total = 0;
-    SXB_CUDA(cudaMemcpyAsync(&total, offsets.ptr + nr, sizeof(long long), cudaMemcpyDeviceToHost, stream_));
+    int status = 0;
+    SXB_CUDA(cudaMemcpyAsync(&total, nb_offsets_.ptr + nr, sizeof(long long), cudaMemcpyDeviceToHost, stream_));
+    SXB_CUDA(cudaMemcpyAsync(&status, error_flag_.ptr, sizeof(int), cudaMemcpyDeviceToHost, stream_));
     SXB_CUDA(cudaStreamSynchronize(stream_));
+    if (status & 4) throw std::invalid_argument("Neighbor graph positions must be finite.");
     if (total > static_cast<long long>(std::numeric_limits<int>::max()))
         throw std::length_error("Neighbor graph exceeds 32-bit edge indexing.");
     first_caller_.reserve(nr + 1);
     sources_caller_.reserve_with_slack(static_cast<std::size_t>(total));
     shifts_caller_.reserve_with_slack(3 * static_cast<std::size_t>(total));
-    narrow_offsets_kernel<<<blocks_for(nr + 1, T), T, 0, stream_>>>(nr, offsets.ptr, first_caller_.ptr);
-    neighbor_edges_kernel<true><<<blocks_for(nr, T), T, 0, stream_>>>(nr, cl, atom_bin.ptr, bin_offsets.ptr, bin_atoms.ptr,
-                                                                      wrapped_pos.ptr, wrap_shift.ptr, cell_.ptr, nullptr,
-                                                                      first_caller_.ptr, sources_caller_.ptr, shifts_caller_.ptr);
-    launches_ += 8;
+    narrow_offsets_kernel<<<blocks_for(nr + 1, threads), threads, 0, stream_>>>(nr, nb_offsets_.ptr, first_caller_.ptr);
+    receiver_edges_kernel<true><<<warp_blocks, threads, 0, stream_>>>(nr, grid, nb_atom_bin_.ptr, nb_bin_begin_.ptr, nb_sorted_atoms_.ptr,
+                                                                       nb_sorted_pos_.ptr, nb_wrapped_pos_.ptr, nb_wrap_count_.ptr,
+                                                                       cell_.ptr, nullptr, first_caller_.ptr, sources_caller_.ptr,
+                                                                       shifts_caller_.ptr);
+    launches_ += 5;
     SXB_CUDA(cudaGetLastError());
     std::vector<int> types(node_types, node_types + n);
     install_graph(nr, n, types, static_cast<long>(total), true);
@@ -972,6 +1001,74 @@ void Evaluator::run_pipeline(int phases)
     SXB_CUDA(cudaGetLastError());
 }
 
+// Enqueues the geometry kernel (when `positions` is given) and the pipeline phases on the stream.
+// Outside profiling the sequence is captured once per (phases, graph generation, position buffer)
+// into a CUDA graph and replayed afterwards: every kernel argument is fixed for a prepared graph, so
+// a step costs one graph launch instead of some twenty kernel launches.
+void Evaluator::enqueue_phases(int phases, const double* positions)
+{
+    auto enqueue = [&] {
+        if (positions != nullptr) {
+            SXB_CUDA(cudaMemsetAsync(error_flag_.ptr, 0, sizeof(int), stream_));
+            geometry_from_positions_kernel<<<blocks_for(static_cast<long>(num_receivers_) * 32, 256), 256, 0, stream_>>>(
+                num_receivers_, first_.ptr, sources_.ptr, shifts_.ptr, positions, original_.ptr, cell_.ptr, geom_.ptr, error_flag_.ptr);
+            launches_ += 1;
+        }
+        run_pipeline(phases);
+    };
+    if (!use_graphs_ || profiling_ || stream_ == nullptr) {
+        enqueue();
+        return;
+    }
+    StepGraph& slot = step_graphs_[phases];
+    if (slot.exec == nullptr || slot.generation != generation_ || slot.positions != positions || slot.keep_edge_forces != keep_edge_forces_) {
+        if (slot.exec != nullptr) {
+            cudaGraphExecDestroy(slot.exec);
+            slot.exec = nullptr;
+        }
+        const long before = launches_;
+        if (cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+            cudaGetLastError();        // this stream cannot be captured (e.g. the legacy default stream): launch directly
+            use_graphs_ = false;
+            enqueue();
+            return;
+        }
+        cudaGraph_t graph = nullptr;
+        try {
+            enqueue();
+        } catch (...) {
+            cudaStreamEndCapture(stream_, &graph);
+            if (graph != nullptr) cudaGraphDestroy(graph);
+            launches_ = before;
+            throw;
+        }
+        SXB_CUDA(cudaStreamEndCapture(stream_, &graph));
+        const cudaError_t made = cudaGraphInstantiate(&slot.exec, graph, 0);
+        cudaGraphDestroy(graph);
+        slot.launches = launches_ - before;
+        launches_ = before;
+        if (made != cudaSuccess) {
+            cudaGetLastError();
+            slot.exec = nullptr;
+            use_graphs_ = false;
+            enqueue();
+            return;
+        }
+        slot.generation = generation_;
+        slot.positions = positions;
+        slot.keep_edge_forces = keep_edge_forces_;
+    }
+    SXB_CUDA(cudaGraphLaunch(slot.exec, stream_));
+    launches_ += slot.launches;
+}
+
+void Evaluator::drop_step_graphs()
+{
+    for (auto& entry : step_graphs_)
+        if (entry.second.exec != nullptr) cudaGraphExecDestroy(entry.second.exec);
+    step_graphs_.clear();
+}
+
 void Evaluator::finish_compute()
 {
     SXB_CUDA(cudaEventRecord(event_end_, stream_));
@@ -1021,11 +1118,7 @@ void Evaluator::compute_positions(std::uint64_t generation, const double* positi
         SXB_CUDA(cudaMemcpyAsync(positions_.ptr, positions, sizeof(double) * 3 * num_nodes_, cudaMemcpyHostToDevice, stream_));
         dpos = positions_.ptr;
     }
-    SXB_CUDA(cudaMemsetAsync(error_flag_.ptr, 0, sizeof(int), stream_));
-    geometry_from_positions_kernel<<<blocks_for(static_cast<long>(num_receivers_) * 32, 256), 256, 0, stream_>>>(
-        num_receivers_, first_.ptr, sources_.ptr, shifts_.ptr, dpos, original_.ptr, cell_.ptr, geom_.ptr, error_flag_.ptr);
-    launches_ += 1;
-    run_pipeline(7);
+    enqueue_phases(7, dpos);
     finish_compute();
 }
 
@@ -1035,14 +1128,14 @@ void Evaluator::compute_edge_vectors(std::uint64_t generation, const double* xyz
     SXB_CUDA(cudaSetDevice(device_));
     have_results_ = false;
     mirror_valid_ = false;
-    DeviceBuffer<double> dxyz;
-    dxyz.reserve(3 * static_cast<std::size_t>(num_edges_));
+    DeviceBuffer<double>& dxyz = edge_scratch_;      // kept between calls: the per-step call allocates nothing
+    dxyz.reserve_with_slack(3 * static_cast<std::size_t>(num_edges_));
     SXB_CUDA(cudaEventRecord(event_begin_, stream_));
     SXB_CUDA(cudaMemcpyAsync(dxyz.ptr, xyz, sizeof(double) * 3 * num_edges_, cudaMemcpyHostToDevice, stream_));
     SXB_CUDA(cudaMemsetAsync(error_flag_.ptr, 0, sizeof(int), stream_));
     geometry_from_vectors_kernel<<<blocks_for(num_edges_, 256), 256, 0, stream_>>>(num_edges_, dxyz.ptr, edge_map_.ptr, geom_.ptr, error_flag_.ptr);
     launches_ += 1;
-    run_pipeline(7);
+    enqueue_phases(7, nullptr);
     finish_compute();
 }
 
@@ -1060,11 +1153,7 @@ void Evaluator::distributed_begin(std::uint64_t generation, const double* device
     have_results_ = false;
     mirror_valid_ = false;
     SXB_CUDA(cudaEventRecord(event_begin_, stream_));
-    SXB_CUDA(cudaMemsetAsync(error_flag_.ptr, 0, sizeof(int), stream_));
-    geometry_from_positions_kernel<<<blocks_for(static_cast<long>(num_receivers_) * 32, 256), 256, 0, stream_>>>(
-        num_receivers_, first_.ptr, sources_.ptr, shifts_.ptr, device_positions, original_.ptr, cell_.ptr, geom_.ptr, error_flag_.ptr);
-    launches_ += 1;
-    run_pipeline(1);
+    enqueue_phases(1, device_positions);
     phase_ = 1;
 }
 
@@ -1075,7 +1164,7 @@ void Evaluator::distributed_continue()
         throw std::logic_error("distributed evaluation: continue must follow begin.");
     }
     SXB_CUDA(cudaSetDevice(device_));
-    run_pipeline(2);
+    enqueue_phases(2, nullptr);
     phase_ = 2;
 }
 
@@ -1087,7 +1176,7 @@ void Evaluator::distributed_finish()
     }
     SXB_CUDA(cudaSetDevice(device_));
     phase_ = 0;
-    run_pipeline(4);
+    enqueue_phases(4, nullptr);
     // no host synchronisation here: the caller still has ghost forces to exchange on this stream;
     // synchronize() fetches the totals and checks the device status word
     SXB_CUDA(cudaEventRecord(event_end_, stream_));
@@ -1121,10 +1210,72 @@ __global__ void unpack_rows_kernel(long count, int row_floats, const int* __rest
     float* dst = tensor + node * row_floats + 4 * q;
     if (accumulate) {
         // several images of one owned atom may be ghosts elsewhere: rows can repeat
-        atomicAdd(dst, v.x); atomicAdd(dst + 1, v.y); atomicAdd(dst + 2, v.z); atomicAdd(dst + 3, v.w);
+        atomicAdd(reinterpret_cast<float4*>(dst), v);
     } else {
         *reinterpret_cast<float4*>(dst) = v;
     }
+}
+
+// out[k] = rows[indices[k]] (+ offsets[k]): three doubles per row
+__global__ void gather_rows3_kernel(long count, const int* __restrict__ indices, const double* __restrict__ rows,
+                                    const double* __restrict__ offsets, double* __restrict__ out)
+{
+    const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= count * 3) return;
+    const long k = idx / 3, q = idx % 3;
+    double v = rows[3 * static_cast<long>(indices[k]) + q];
+    if (offsets != nullptr) v += offsets[idx];
+    out[idx] = v;
+}
+
+constexpr int kTotalsRows = 4;   // 10 totals (energy, 9 virial components) padded to four rows of three doubles
+
+// Send buffer of the closing exchange.  Segment of peer p: the force rows of the ghosts that p owns
+// (ghost_begin[p] .. ghost_begin[p+1], contiguous behind the receivers in caller order), then
+// kTotalsRows rows holding this rank's energy and virial.
+__global__ void pack_ghost_forces_kernel(int world, const int* __restrict__ ghost_begin, int num_receivers,
+                                         const double* __restrict__ forces, const double* __restrict__ totals,
+                                         double* __restrict__ out)
+{
+    const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long rows = ghost_begin[world] + static_cast<long>(kTotalsRows) * world;
+    if (idx >= rows * 3) return;
+    const long row = idx / 3;
+    const int q = static_cast<int>(idx % 3);
+    int p = 0;
+    while (p + 1 < world && row >= ghost_begin[p + 1] + static_cast<long>(kTotalsRows) * (p + 1)) ++p;
+    const long local = row - (ghost_begin[p] + static_cast<long>(kTotalsRows) * p);
+    const long ghosts = ghost_begin[p + 1] - ghost_begin[p];
+    if (local < ghosts) {
+        out[idx] = forces[3 * (num_receivers + ghost_begin[p] + local) + q];
+    } else {
+        const long slot = (local - ghosts) * 3 + q;
+        out[idx] = slot < 10 ? totals[slot] : 0.0;
+    }
+}
+
+// Receive buffer of the closing exchange: segment of peer p = force rows for my atoms send_begin[p] ..
+// send_begin[p+1] of the send list, then p's totals.  Forces are added to the owners' rows; the totals
+// of all ranks are summed in rank order (every rank obtains the same bits).
+__global__ void unpack_ghost_forces_kernel(int world, const int* __restrict__ send_begin, const int* __restrict__ indices,
+                                           const double* __restrict__ in, double* __restrict__ forces,
+                                           double* __restrict__ totals_out)
+{
+    const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx < 10) {
+        double sum = 0.0;
+        for (int p = 0; p < world; ++p) sum += in[3 * (send_begin[p + 1] + static_cast<long>(kTotalsRows) * p) + idx];
+        totals_out[idx] = sum;
+    }
+    const long rows = send_begin[world] + static_cast<long>(kTotalsRows) * world;
+    if (idx >= rows * 3) return;
+    const long row = idx / 3;
+    const int q = static_cast<int>(idx % 3);
+    int p = 0;
+    while (p + 1 < world && row >= send_begin[p + 1] + static_cast<long>(kTotalsRows) * (p + 1)) ++p;
+    const long local = row - (send_begin[p] + static_cast<long>(kTotalsRows) * p);
+    if (local < send_begin[p + 1] - send_begin[p])
+        atomicAdd(forces + 3 * static_cast<long>(indices[send_begin[p] + local]) + q, in[idx]);
 }
 
 __global__ void add_force_rows_kernel(long count, const int* __restrict__ indices, const double* __restrict__ in,
@@ -1173,13 +1324,47 @@ void Evaluator::add_force_rows(const int* device_indices, long count, const doub
     SXB_CUDA(cudaGetLastError());
 }
 
+void Evaluator::gather_position_rows(const double* device_rows, const int* device_indices, long count,
+                                     const double* device_offsets, double* device_out)
+{
+    if (count <= 0) return;
+    gather_rows3_kernel<<<blocks_for(count * 3, 256), 256, 0, stream_>>>(count, device_indices, device_rows, device_offsets, device_out);
+    launches_ += 1;
+    SXB_CUDA(cudaGetLastError());
+}
+
+void Evaluator::pack_ghost_forces(int world, const int* device_ghost_begin, long num_ghosts, double* device_out)
+{
+    require_results();
+    if (world <= 0) throw std::invalid_argument("world size must be positive.");
+    const long values = (num_ghosts + static_cast<long>(kTotalsRows) * world) * 3;
+    pack_ghost_forces_kernel<<<blocks_for(values, 256), 256, 0, stream_>>>(world, device_ghost_begin, num_receivers_, forces_out_.ptr,
+                                                                          totals_.ptr, device_out);
+    launches_ += 1;
+    SXB_CUDA(cudaGetLastError());
+}
+
+void Evaluator::unpack_ghost_forces(int world, const int* device_send_begin, const int* device_indices, long num_rows,
+                                    const double* device_in, double* device_totals_out)
+{
+    require_results();
+    if (world <= 0) throw std::invalid_argument("world size must be positive.");
+    const long values = std::max<long>((num_rows + static_cast<long>(kTotalsRows) * world) * 3, 10);
+    unpack_ghost_forces_kernel<<<blocks_for(values, 256), 256, 0, stream_>>>(world, device_send_begin, device_indices, device_in,
+                                                                            forces_out_.ptr, device_totals_out);
+    launches_ += 1;
+    SXB_CUDA(cudaGetLastError());
+}
+
 void Evaluator::set_stream(cudaStream_t stream)
 {
     SXB_CUDA(cudaSetDevice(device_));
     SXB_CUDA(cudaStreamSynchronize(stream_));
+    drop_step_graphs();
     if (owns_stream_ && stream_ != nullptr) SXB_CUDA(cudaStreamDestroy(stream_));
     stream_ = stream;
     owns_stream_ = false;
+    if (const char* env = std::getenv("SXB_CUDA_GRAPHS")) use_graphs_ = env[0] != '0'; else use_graphs_ = true;
 }
 
 void Evaluator::synchronize()
@@ -1226,8 +1411,8 @@ void Evaluator::get_edge_forces(double* out)
 {
     require_results();
     if (!keep_edge_forces_) throw std::invalid_argument("Directed edge forces were not retained; enable them before compute.");
-    DeviceBuffer<double> tmp;
-    tmp.reserve(3 * static_cast<std::size_t>(num_edges_));
+    DeviceBuffer<double>& tmp = edge_scratch_;
+    tmp.reserve_with_slack(3 * static_cast<std::size_t>(num_edges_));
     unpermute_edges_kernel<<<blocks_for(num_edges_, 256), 256, 0, stream_>>>(num_edges_, edge_map_.ptr, edge_forces_.ptr, tmp.ptr);
     launches_ += 1;
     SXB_CUDA(cudaMemcpyAsync(out, tmp.ptr, sizeof(double) * 3 * num_edges_, cudaMemcpyDeviceToHost, stream_));
@@ -1243,7 +1428,8 @@ void Evaluator::set_keep_edge_forces(bool enabled)
 void Evaluator::get_stress(double volume, double* out9)
 {
     require_results();
-    if (!(volume > 0.0)) throw std::invalid_argument("Stress reduction needs a positive volume.");
+    if (pending_finish_) throw std::logic_error("Call synchronize() after distributed_finish before reading host results.");
+    if (!std::isfinite(volume) || !(volume > 0.0)) throw std::invalid_argument("Stress reduction needs a finite positive volume.");
     for (int q = 0; q < 9; ++q) out9[q] = -host_totals_[1 + q] / volume;
 }
 

@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cstdint>
+#include <map>
 #include <stdexcept>
 #include <string>
 #include <utility>
@@ -22,7 +23,7 @@ struct StaleGraph : std::invalid_argument {
 
 class Evaluator {
 public:
-    Evaluator(const std::string& json_path, int device_ordinal);
+    Evaluator(const std::string& json_path, int device_ordinal, const std::string& head = std::string());
     ~Evaluator();
     Evaluator(const Evaluator&) = delete;
     Evaluator& operator=(const Evaluator&) = delete;
@@ -51,6 +52,13 @@ public:
     void pack_rows(int which, const int* device_indices, long count, float* device_out);
     void unpack_rows(int which, const int* device_indices, long count, const float* device_in, bool accumulate);
     void add_force_rows(const int* device_indices, long count, const double* device_in);
+    void gather_position_rows(const double* device_rows, const int* device_indices, long count, const double* device_offsets,
+                              double* device_out);
+    void pack_ghost_forces(int world, const int* device_ghost_begin, long num_ghosts, double* device_out);
+    void unpack_ghost_forces(int world, const int* device_send_begin, const int* device_indices, long num_rows,
+                             const double* device_in, double* device_totals_out);
+    float* halo_tensor(int which);
+    int halo_row_floats() const { return model_.num_hidden * model_.channels; }
     void set_stream(cudaStream_t stream);
     // Tiled streaming: receivers are processed in tiles of this many with one reusable workspace
     // (0 = one tile holding every receiver).  Takes effect at the next graph preparation.
@@ -80,7 +88,18 @@ private:
     void prepare_active_types(const std::vector<int>& node_types);
     void install_graph(int num_receivers, int num_nodes, const std::vector<int>& node_types, long num_edges, bool has_shifts);
     void run_pipeline(int phases);
-    float* halo_tensor(int which);
+    void enqueue_phases(int phases, const double* positions);
+    void drop_step_graphs();
+    // one captured step per phase mask (7: whole evaluation; 1, 2, 4: the distributed phases)
+    struct StepGraph {
+        cudaGraphExec_t exec = nullptr;
+        std::uint64_t generation = 0;
+        const double* positions = nullptr;
+        bool keep_edge_forces = false;
+        long launches = 0;
+    };
+    std::map<int, StepGraph> step_graphs_;
+    bool use_graphs_ = true;
     void finish_compute();
     void launch_gemm(const float* A, const RowMap& a_rows, const float* B, int ldb, bool b_transposed, float* C,
                      const RowMap& c_rows, int first_node, int num_nodes, int N, int K, bool accumulate, const float* bias);
@@ -110,8 +129,8 @@ private:
     int num_sms_ = 148;
     int r1_pair_types_ = 1;   // active types the layer-1 table distinguishes (1 without a distance transform)
     // scratch of the cell-list build and of the graph installation (kept between rebuilds)
-    DeviceBuffer<double> nb_wrapped_frac_, nb_wrapped_pos_;
-    DeviceBuffer<int> nb_wrap_shift_, nb_atom_bin_, nb_bin_sizes_, nb_bin_offsets_, nb_cursors_, nb_bin_atoms_, ig_counts_;
+    DeviceBuffer<double> nb_wrapped_pos_, nb_sorted_pos_;
+    DeviceBuffer<int> nb_wrap_count_, nb_atom_bin_, nb_atom_index_, nb_sorted_bin_, nb_sorted_atoms_, nb_bin_sizes_, nb_bin_begin_, ig_counts_;
     DeviceBuffer<long long> nb_counts_, nb_offsets_;
     DeviceBuffer<unsigned char> nb_temp_, ig_temp_;
     DeviceBuffer<float> zbl_pairs_;    // [active pair][4]: 1/a, 14.3996 Z_i Z_j, r_max, pad (models with ZBL)
@@ -146,6 +165,7 @@ private:
     DeviceBuffer<float> A0_, A0_adj_, M0_, M0_adj_, H1_, H1_adj_, Phi1_, dPhi1_, A1_, A1_adj_, M1_, M1_adj_, H2_, H2_adj_;
     DeviceBuffer<double> node_energies_, node_energies_out_, forces_, forces_out_, edge_forces_;
     DeviceBuffer<double> totals_, energy_slots_, virial_slots_;
+    DeviceBuffer<double> edge_scratch_;      // [E][3]: caller edge vectors on the way in, un-permuted edge forces on the way out
     DeviceBuffer<int> error_flag_;
     double host_totals_[10] = {0};
     // pinned host mirror of the per-node results, filled by calls that take host inputs so that the

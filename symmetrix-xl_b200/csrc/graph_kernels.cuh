@@ -1,147 +1,172 @@
-// Periodic cell-list neighbor graph on the device, receiver-major CSR in the reference's
-// stencil order.  Follows build_periodic_neighbor_graph_kokkos
-// (libsymmetrix/source/neighbor_graph_kokkos.cpp:39-405): wrap -> bin -> sort inside bins by
-// atom index -> count -> scan -> fill.  All double arithmetic on the acceptance path uses
-// round-to-nearest add/mul intrinsics (never contracted into FMAs), so the accepted edge set is
-// the one an IEEE evaluation of the reference's expressions gives.
+// Periodic cell-list neighbor graph on the device: receiver-major CSR whose per-receiver edge order
+// is bin-stencil order (z outermost, x innermost), atoms of a bin in ascending index.  That is the
+// order and the accepted edge set of the reference's builder
+// (libsymmetrix/source/neighbor_graph_kokkos.cpp:39-405); the work split is different:
+//   * atoms are put in bin order by one stable radix sort of (bin, atom) pairs, so bins need no
+//     per-bin sort and the candidates of x-adjacent bins are contiguous in memory;
+//   * one warp owns a receiver; for each (z, y) row of the stencil it walks maximal runs of
+//     x-adjacent bins that share a periodic image, 32 candidates at a time, and compacts the accepted
+//     ones in order with a ballot and a prefix population count.
+// The distance test is evaluated in double with round-to-nearest adds and multiplies that are never
+// contracted into FMAs, in the operand order of the reference's expression, so that a pair at the
+// cutoff is accepted or rejected exactly as an IEEE evaluation of that expression would.
 #pragma once
 
 #include "common.cuh"
 
 namespace sxb {
 
-struct CellList {
+struct CellGrid {
     int bins[3];
     int reach[3];
     int num_bins;
     double cutoff_squared;
 };
 
-__global__ void wrap_positions_kernel(int n, const double* __restrict__ positions, const double* __restrict__ inv_cell,
-                                      const double* __restrict__ cell, double* __restrict__ wrapped_frac,
-                                      double* __restrict__ wrapped_pos, int* __restrict__ wrap_shift)
+// Fractional coordinates wrapped into [0, 1), the wrap count per axis, the wrapped Cartesian position
+// and the atom's bin; a non-finite coordinate raises bit 2 of the status word.
+__global__ void wrap_and_bin_kernel(int n, CellGrid grid, const double* __restrict__ positions,
+                                    const double* __restrict__ inv_cell, const double* __restrict__ cell,
+                                    double* __restrict__ wrapped_pos, int* __restrict__ wrap_count,
+                                    int* __restrict__ atom_bin, int* __restrict__ atom_index, int* __restrict__ bin_sizes,
+                                    int* __restrict__ status)
 {
     const int atom = blockIdx.x * blockDim.x + threadIdx.x;
     if (atom >= n) return;
-    double frac[3];
+    atom_index[atom] = atom;
+    const double p[3] = {positions[3 * atom], positions[3 * atom + 1], positions[3 * atom + 2]};
+    if (!isfinite(p[0]) || !isfinite(p[1]) || !isfinite(p[2])) {
+        atomicOr(status, 4);
+        atom_bin[atom] = 0;
+        atomicAdd(bin_sizes, 1);
+        for (int c = 0; c < 3; ++c) {
+            wrapped_pos[3 * atom + c] = 0.0;
+            wrap_count[3 * atom + c] = 0;
+        }
+        return;
+    }
+    double f[3];
+    int b[3];
+#pragma unroll
     for (int axis = 0; axis < 3; ++axis) {
-        double value = 0.0;
-        for (int component = 0; component < 3; ++component)
-            value = __dadd_rn(value, __dmul_rn(positions[3 * atom + component], inv_cell[3 * component + axis]));
-        const int wrap = static_cast<int>(floor(value));
-        value = __dadd_rn(value, -static_cast<double>(wrap));
-        frac[axis] = value;
-        wrapped_frac[3 * atom + axis] = value;
-        wrap_shift[3 * atom + axis] = wrap;
+        double s = __dmul_rn(p[0], inv_cell[axis]);
+        s = __dadd_rn(s, __dmul_rn(p[1], inv_cell[3 + axis]));
+        s = __dadd_rn(s, __dmul_rn(p[2], inv_cell[6 + axis]));
+        const int w = static_cast<int>(floor(s));
+        f[axis] = __dadd_rn(s, -static_cast<double>(w));
+        wrap_count[3 * atom + axis] = w;
+        b[axis] = min(grid.bins[axis] - 1, static_cast<int>(__dmul_rn(f[axis], static_cast<double>(grid.bins[axis]))));
     }
-    for (int component = 0; component < 3; ++component) {
-        double value = 0.0;
-        for (int axis = 0; axis < 3; ++axis) value = __dadd_rn(value, __dmul_rn(frac[axis], cell[3 * axis + component]));
-        wrapped_pos[3 * atom + component] = value;
+#pragma unroll
+    for (int c = 0; c < 3; ++c) {
+        double s = __dmul_rn(f[0], cell[c]);
+        s = __dadd_rn(s, __dmul_rn(f[1], cell[3 + c]));
+        s = __dadd_rn(s, __dmul_rn(f[2], cell[6 + c]));
+        wrapped_pos[3 * atom + c] = s;
     }
-}
-
-__global__ void count_bins_kernel(int n, CellList cl, const double* __restrict__ wrapped_frac, int* __restrict__ atom_bin,
-                                  int* __restrict__ bin_sizes)
-{
-    const int atom = blockIdx.x * blockDim.x + threadIdx.x;
-    if (atom >= n) return;
-    const int x = min(cl.bins[0] - 1, static_cast<int>(__dmul_rn(wrapped_frac[3 * atom], static_cast<double>(cl.bins[0]))));
-    const int y = min(cl.bins[1] - 1, static_cast<int>(__dmul_rn(wrapped_frac[3 * atom + 1], static_cast<double>(cl.bins[1]))));
-    const int z = min(cl.bins[2] - 1, static_cast<int>(__dmul_rn(wrapped_frac[3 * atom + 2], static_cast<double>(cl.bins[2]))));
-    const int bin = (z * cl.bins[1] + y) * cl.bins[0] + x;
+    const int bin = (b[2] * grid.bins[1] + b[1]) * grid.bins[0] + b[0];
     atom_bin[atom] = bin;
     atomicAdd(bin_sizes + bin, 1);
 }
 
-__global__ void fill_bins_kernel(int n, const int* __restrict__ atom_bin, int* __restrict__ cursors, int* __restrict__ bin_atoms)
+// Wrapped positions gathered into bin order, so that a warp reads its candidates coalesced.
+__global__ void gather_sorted_positions_kernel(int n, const int* __restrict__ sorted_atoms, const double* __restrict__ wrapped_pos,
+                                               double* __restrict__ sorted_pos)
 {
-    const int atom = blockIdx.x * blockDim.x + threadIdx.x;
-    if (atom >= n) return;
-    bin_atoms[atomicAdd(cursors + atom_bin[atom], 1)] = atom;
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= n) return;
+    const int atom = sorted_atoms[k];
+    sorted_pos[3 * k] = wrapped_pos[3 * atom];
+    sorted_pos[3 * k + 1] = wrapped_pos[3 * atom + 1];
+    sorted_pos[3 * k + 2] = wrapped_pos[3 * atom + 2];
 }
 
-__global__ void sort_bins_kernel(int num_bins, const int* __restrict__ offsets, int* __restrict__ bin_atoms)
+// Bin coordinate `raw` of an unbounded bin lattice folded into [0, extent): returns the folded
+// coordinate and stores how many periods were removed (the periodic image of that bin).
+__device__ __forceinline__ int fold_bin(int raw, int extent, int& image)
 {
-    const int bin = blockIdx.x * blockDim.x + threadIdx.x;
-    if (bin >= num_bins) return;
-    const int begin = offsets[bin], end = offsets[bin + 1];
-    for (int index = begin + 1; index < end; ++index) {
-        const int atom = bin_atoms[index];
-        int insertion = index;
-        while (insertion > begin && bin_atoms[insertion - 1] > atom) {
-            bin_atoms[insertion] = bin_atoms[insertion - 1];
-            --insertion;
-        }
-        bin_atoms[insertion] = atom;
-    }
+    image = raw >= 0 ? raw / extent : -((extent - 1 - raw) / extent);
+    return raw - image * extent;
 }
 
-__device__ __forceinline__ int floor_div(int numerator, int denominator)
-{
-    const int quotient = numerator / denominator;
-    const int remainder = numerator % denominator;
-    return quotient - ((remainder != 0 && remainder < 0) ? 1 : 0);
-}
-
-// One thread per receiver; kFill = false counts, true writes sources and shifts at the
-// receiver's offset.  The candidate order is the stencil order (z outermost) then the in-bin order.
+// kFill = false: counts[receiver] = number of accepted candidates.
+// kFill = true:  writes sources / shifts from offsets[receiver] on, in candidate order.
 template <bool kFill>
-__global__ void neighbor_edges_kernel(int n, CellList cl, const int* __restrict__ atom_bin, const int* __restrict__ bin_offsets,
-                                      const int* __restrict__ bin_atoms, const double* __restrict__ wrapped_pos,
-                                      const int* __restrict__ wrap_shift, const double* __restrict__ cell,
-                                      long long* __restrict__ counts, const int* __restrict__ receiver_offsets,
-                                      int* __restrict__ sources, int* __restrict__ shifts)
+__global__ void __launch_bounds__(256)
+receiver_edges_kernel(int num_receivers, CellGrid grid, const int* __restrict__ atom_bin, const int* __restrict__ bin_begin,
+                      const int* __restrict__ sorted_atoms, const double* __restrict__ sorted_pos,
+                      const double* __restrict__ wrapped_pos, const int* __restrict__ wrap_count,
+                      const double* __restrict__ cell, long long* __restrict__ counts, const int* __restrict__ offsets,
+                      int* __restrict__ sources, int* __restrict__ shifts)
 {
-    const int receiver = blockIdx.x * blockDim.x + threadIdx.x;
-    if (receiver >= n) return;
-    const int rb = atom_bin[receiver];
-    const int rx = rb % cl.bins[0];
-    const int ry = (rb / cl.bins[0]) % cl.bins[1];
-    const int rz = rb / (cl.bins[0] * cl.bins[1]);
-    const double px = wrapped_pos[3 * receiver], py = wrapped_pos[3 * receiver + 1], pz = wrapped_pos[3 * receiver + 2];
-    double c[9];
-    for (int q = 0; q < 9; ++q) c[q] = cell[q];
-    long long local = 0;
-    const long long base = kFill ? receiver_offsets[receiver] : 0;
-    for (int dz = -cl.reach[2]; dz <= cl.reach[2]; ++dz) {
-        const int raw_z = rz + dz;
-        const int shift_z = floor_div(raw_z, cl.bins[2]);
-        const int source_z = raw_z - shift_z * cl.bins[2];
-        for (int dy = -cl.reach[1]; dy <= cl.reach[1]; ++dy) {
-            const int raw_y = ry + dy;
-            const int shift_y = floor_div(raw_y, cl.bins[1]);
-            const int source_y = raw_y - shift_y * cl.bins[1];
-            for (int dx = -cl.reach[0]; dx <= cl.reach[0]; ++dx) {
-                const int raw_x = rx + dx;
-                const int shift_x = floor_div(raw_x, cl.bins[0]);
-                const int source_x = raw_x - shift_x * cl.bins[0];
-                const int source_bin = (source_z * cl.bins[1] + source_y) * cl.bins[0] + source_x;
-                const int image[3] = {shift_x, shift_y, shift_z};
-                for (int index = bin_offsets[source_bin]; index < bin_offsets[source_bin + 1]; ++index) {
-                    const int source = bin_atoms[index];
-                    if (source == receiver && shift_x == 0 && shift_y == 0 && shift_z == 0) continue;
-                    double distance_squared = 0.0;
-                    const double rp[3] = {px, py, pz};
-                    for (int component = 0; component < 3; ++component) {
-                        double displacement = __dadd_rn(wrapped_pos[3 * source + component], -rp[component]);
-                        for (int axis = 0; axis < 3; ++axis)
-                            displacement = __dadd_rn(displacement, __dmul_rn(static_cast<double>(image[axis]), c[3 * axis + component]));
-                        distance_squared = __dadd_rn(distance_squared, __dmul_rn(displacement, displacement));
+    const int receiver = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const unsigned lane = threadIdx.x & 31u;
+    if (receiver >= num_receivers) return;
+    const int nx = grid.bins[0], ny = grid.bins[1], nz = grid.bins[2];
+    const int home = atom_bin[receiver];
+    const int hx = home % nx, hy = (home / nx) % ny, hz = home / (nx * ny);
+    const double rx = wrapped_pos[3 * receiver], ry = wrapped_pos[3 * receiver + 1], rz = wrapped_pos[3 * receiver + 2];
+    const int wrx = wrap_count[3 * receiver], wry = wrap_count[3 * receiver + 1], wrz = wrap_count[3 * receiver + 2];
+    long long written = kFill ? offsets[receiver] : 0;
+
+    for (int dz = -grid.reach[2]; dz <= grid.reach[2]; ++dz) {
+        int iz;
+        const int bz = fold_bin(hz + dz, nz, iz);
+        // image translation, one product per (axis, component); the sums below add them one at a time
+        const double zx = __dmul_rn(static_cast<double>(iz), cell[6]), zy = __dmul_rn(static_cast<double>(iz), cell[7]),
+                     zz = __dmul_rn(static_cast<double>(iz), cell[8]);
+        for (int dy = -grid.reach[1]; dy <= grid.reach[1]; ++dy) {
+            int iy;
+            const int by = fold_bin(hy + dy, ny, iy);
+            const double yx = __dmul_rn(static_cast<double>(iy), cell[3]), yy = __dmul_rn(static_cast<double>(iy), cell[4]),
+                         yz = __dmul_rn(static_cast<double>(iy), cell[5]);
+            const int row = (bz * ny + by) * nx;
+            int dx = -grid.reach[0];
+            while (dx <= grid.reach[0]) {
+                int ix;
+                const int bx = fold_bin(hx + dx, nx, ix);
+                // bins bx .. bx+run-1 of this row share the image ix and are contiguous in bin order
+                const int run = min(grid.reach[0] - dx + 1, nx - bx);
+                const double xx = __dmul_rn(static_cast<double>(ix), cell[0]), xy = __dmul_rn(static_cast<double>(ix), cell[1]),
+                             xz = __dmul_rn(static_cast<double>(ix), cell[2]);
+                const bool home_image = ix == 0 && iy == 0 && iz == 0;
+                const int first = bin_begin[row + bx], last = bin_begin[row + bx + run];
+                for (int k0 = first; k0 < last; k0 += 32) {
+                    const int k = k0 + static_cast<int>(lane);
+                    bool accept = false;
+                    int source = -1;
+                    if (k < last) {
+                        source = sorted_atoms[k];
+                        double d = __dadd_rn(sorted_pos[3 * k], -rx);
+                        d = __dadd_rn(__dadd_rn(__dadd_rn(d, xx), yx), zx);
+                        double d2 = __dmul_rn(d, d);
+                        d = __dadd_rn(sorted_pos[3 * k + 1], -ry);
+                        d = __dadd_rn(__dadd_rn(__dadd_rn(d, xy), yy), zy);
+                        d2 = __dadd_rn(d2, __dmul_rn(d, d));
+                        d = __dadd_rn(sorted_pos[3 * k + 2], -rz);
+                        d = __dadd_rn(__dadd_rn(__dadd_rn(d, xz), yz), zz);
+                        d2 = __dadd_rn(d2, __dmul_rn(d, d));
+                        accept = !(d2 > grid.cutoff_squared) && !(home_image && source == receiver);
                     }
-                    if (distance_squared > cl.cutoff_squared) continue;
+                    const unsigned taken = __ballot_sync(0xffffffffu, accept);
                     if constexpr (kFill) {
-                        const long long edge = base + local;
-                        sources[edge] = source;
-                        for (int axis = 0; axis < 3; ++axis)
-                            shifts[3 * edge + axis] = image[axis] - wrap_shift[3 * source + axis] + wrap_shift[3 * receiver + axis];
+                        if (accept) {
+                            const long long edge = written + __popc(taken & ((1u << lane) - 1u));
+                            sources[edge] = source;
+                            shifts[3 * edge] = ix - wrap_count[3 * source] + wrx;
+                            shifts[3 * edge + 1] = iy - wrap_count[3 * source + 1] + wry;
+                            shifts[3 * edge + 2] = iz - wrap_count[3 * source + 2] + wrz;
+                        }
                     }
-                    ++local;
+                    written += __popc(taken);
                 }
+                dx += run;
             }
         }
     }
-    if constexpr (!kFill) counts[receiver] = local;
+    if constexpr (!kFill) {
+        if (lane == 0) counts[receiver] = written;
+    }
 }
 
 // Re-expresses a CSR graph given in caller node order in the internal order (nodes grouped by
@@ -162,9 +187,10 @@ __global__ void permute_graph_kernel(int n, const int* __restrict__ original, co
         new_sources[nb + t] = internal_of[old_sources[ob + t]];
         edge_map[nb + t] = ob + t;
         if (old_shifts != nullptr) {
-            new_shifts[3 * (nb + t)] = old_shifts[3 * (ob + t)];
-            new_shifts[3 * (nb + t) + 1] = old_shifts[3 * (ob + t) + 1];
-            new_shifts[3 * (nb + t) + 2] = old_shifts[3 * (ob + t) + 2];
+            const size_t to = 3 * static_cast<size_t>(nb + t), from = 3 * static_cast<size_t>(ob + t);
+            new_shifts[to] = old_shifts[from];
+            new_shifts[to + 1] = old_shifts[from + 1];
+            new_shifts[to + 2] = old_shifts[from + 2];
         }
     }
 }

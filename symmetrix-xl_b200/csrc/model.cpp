@@ -211,12 +211,73 @@ std::vector<T> to_vec(const std::vector<double>& v)
 const ShapeTables& shape_tables(int shape_id) { return all_shapes().at(shape_id); }
 int num_compiled_shapes() { return static_cast<int>(all_shapes().size()); }
 
-HostModel load_model(const std::string& json_path)
+namespace {
+// Multi-head files keep the per-head parameters (atomic energies, both readouts, the ZBL
+// coefficients) under prediction_heads.parameters[<name>]; the chosen head's values replace the
+// top-level ones before anything else is parsed (reference: select_prediction_head,
+// libsymmetrix/source/prediction_heads.hpp:10-90).  An empty request selects the file's default head.
+void overlay_prediction_head(json& data, const std::string& requested, HostModel& m)
+{
+    const auto found = data.find("prediction_heads");
+    if (found == data.end()) {
+        const std::string only = data.value("head", std::string());
+        if (!requested.empty() && requested != only)
+            throw std::invalid_argument("Requested prediction head '" + requested + "' is unavailable; the file "
+                                        + (only.empty() ? std::string("names no head.") : "holds '" + only + "'."));
+        m.selected_head = only;
+        if (!only.empty()) m.available_heads = {only};
+        return;
+    }
+    const json section = *found;
+    if (!section.is_object() || section.value("schema_version", 0) != 1)
+        throw std::invalid_argument("prediction_heads has an unsupported schema version.");
+    if (!section.contains("names") || !section.at("names").is_array())
+        throw std::invalid_argument("prediction_heads.names must be an array.");
+    const auto names = section.at("names").get<std::vector<std::string>>();
+    std::vector<std::string> sorted_names(names);
+    std::sort(sorted_names.begin(), sorted_names.end());
+    const bool duplicated = std::adjacent_find(sorted_names.begin(), sorted_names.end()) != sorted_names.end();
+    if (names.empty() || duplicated || sorted_names.front().empty())
+        throw std::invalid_argument("prediction_heads.names must contain unique non-empty strings.");
+    if (!section.contains("parameters") || !section.at("parameters").is_object()
+        || section.at("parameters").size() != names.size())
+        throw std::invalid_argument("prediction_heads.parameters must define every named head.");
+    std::vector<std::string> expected = {"atomic_energies", "readout_1_weights_for_M0", "readout_2_weights_1",
+                                         "readout_2_weights_2"};
+    if (data.value("has_zbl", false)) expected.push_back("zbl_c");
+    std::sort(expected.begin(), expected.end());
+    for (const auto& name : names) {
+        const auto& parameters = section.at("parameters");
+        if (!parameters.contains(name) || !parameters.at(name).is_object())
+            throw std::invalid_argument("prediction_heads.parameters must define every named head.");
+        std::vector<std::string> fields;
+        for (const auto& item : parameters.at(name).items()) fields.push_back(item.key());
+        std::sort(fields.begin(), fields.end());
+        if (fields != expected)
+            throw std::invalid_argument("Every prediction-head payload must contain exactly the supported fields.");
+    }
+    const std::string fallback = section.value("default", std::string());
+    if (!std::binary_search(sorted_names.begin(), sorted_names.end(), fallback))
+        throw std::invalid_argument("prediction_heads.default must name a stored head.");
+    const std::string chosen = requested.empty() ? fallback : requested;
+    if (!std::binary_search(sorted_names.begin(), sorted_names.end(), chosen))
+        throw std::invalid_argument("Requested prediction head '" + chosen + "' is unavailable.");
+    for (const auto& item : section.at("parameters").at(chosen).items()) data[item.key()] = item.value();
+    m.selected_head = chosen;
+    m.available_heads = names;
+}
+}  // namespace
+
+HostModel load_model(const std::string& json_path, const std::string& head)
 {
     std::ifstream stream(json_path);
     if (!stream) throw std::runtime_error("Could not open Symmetrix model file: " + json_path);
-    const json file = json::parse(stream);
+    json parsed = json::parse(stream);
     HostModel m;
+    if (parsed.value("model_type", std::string("MACE")) == "MACE" && parsed.value("symmetrix_format_version", 1) == 4
+        && parsed.value("h1_affine_mode", std::string()) == "m0_composite")
+        overlay_prediction_head(parsed, head, m);
+    const json& file = parsed;
 
     if (file.value("model_type", std::string("MACE")) != "MACE")
         throw std::invalid_argument("Only the standard two-layer MACE model family is supported.");

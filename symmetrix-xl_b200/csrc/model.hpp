@@ -36,6 +36,8 @@ struct HostModel {
     double r_cut = 0.0;
     std::vector<int> atomic_numbers;
     std::vector<double> atomic_energies;
+    std::string selected_head;               // prediction head in use ("" when the file names none)
+    std::vector<std::string> available_heads;
     std::vector<int> eta;                    // paths per output l
     std::vector<int> group_begin;            // first lme of each output l
 
@@ -72,7 +74,8 @@ struct HostModel {
 };
 
 // Throws std::runtime_error / std::invalid_argument with a message naming the key.
-HostModel load_model(const std::string& json_path);
+// ``head`` selects a prediction head of a multi-head file; empty = the file's default head.
+HostModel load_model(const std::string& json_path, const std::string& head = std::string());
 
 // Cubic coefficients [interval][4][functions] (double) of radial network ``name`` ("R0", "R1", "A0",
 // "A1") for the species pair (type_i, type_j) - symmetric in the pair; reference:

@@ -7,6 +7,7 @@
 // stages through a scratch array of per-block partial sums.
 #include "../../include/symmetrix_b200.h"
 
+#include <cmath>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -116,7 +117,7 @@ extern "C" int sxb_reduce_edge_forces(int32_t num_nodes, int64_t num_edges, cons
     using namespace sxb;
     try {
         if (num_nodes <= 0 || num_edges < 0) throw std::invalid_argument("Force reduction extents must be positive.");
-        if (!(volume > 0.0)) throw std::invalid_argument("Stress reduction needs a positive volume.");
+        if (!std::isfinite(volume) || !(volume > 0.0)) throw std::invalid_argument("Stress reduction needs a finite positive volume.");
         if (!edge_receivers || !edge_sources || !edge_forces || !xyz || !atom_forces || !stress9)
             throw std::invalid_argument("Force reduction arguments must not be NULL.");
         const size_t E = static_cast<size_t>(num_edges);
@@ -208,7 +209,7 @@ extern "C" int sxb_reduce_edge_forces_static(int32_t num_nodes, int64_t num_edge
         if (num_edges > kStaticMaxEdges)
             throw std::invalid_argument("sxb_reduce_edge_forces_static handles at most 4,194,304 edges per call (" +
                                         std::to_string(num_edges) + " given); split the edge list or use sxb_reduce_edge_forces.");
-        if (!(volume > 0.0)) throw std::invalid_argument("Stress reduction needs a positive volume.");
+        if (!std::isfinite(volume) || !(volume > 0.0)) throw std::invalid_argument("Stress reduction needs a finite positive volume.");
         if (!device_receivers || !device_sources || !device_edge_forces || !device_xyz || !device_atom_forces || !device_stress9)
             throw std::invalid_argument("Force reduction arguments must not be NULL.");
         const StaticScratch& scratch = static_scratch_for_current_device();

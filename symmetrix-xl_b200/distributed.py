@@ -160,7 +160,15 @@ class ExchangePlan:
 
 
 class DistributedCalculator:
-    """Energy, forces and stress of a periodic system decomposed over the ranks of the process group."""
+    """Energy, forces and stress of a periodic system decomposed over the ranks of the process group.
+
+    Per evaluation a rank issues four exchanges and no other collective: ghost positions in, ``H1`` rows
+    forward (received straight into the tail of the feature tensor), ``H1_adj`` rows back (sent
+    straight from the tail of the adjoint tensor, summed at the owner), ghost forces back together with
+    every rank's energy and virial.  All of it is enqueued on one stream with a single host
+    synchronisation at the end."""
+
+    TOTALS_ROWS = 4     # energy + 9 virial components travel as four rows of three doubles
 
     def __init__(self, model_path, evaluator_cls, skin=0.5, device=0):
         import torch
@@ -169,9 +177,13 @@ class DistributedCalculator:
         self.device = torch.device("cuda", device)
         torch.cuda.set_device(self.device)
         self.ev = evaluator_cls(model_path, device=device)
-        self.ev.set_stream(torch.cuda.current_stream().cuda_stream)
+        # the evaluator's kernels and the exchanges share one stream of their own (a stream that can be
+        # captured into CUDA graphs, which the legacy default stream cannot)
+        self.stream = torch.cuda.Stream(self.device)
+        self.ev.set_stream(self.stream.cuda_stream)
         self.skin = float(skin)
         self.comm = make_comm()
+        self.transport = "NCCL" if self.comm.world > 1 else "local-copy"
         self.generation = 0
 
     def prepare(self, positions, cell, types, grid=None):
@@ -186,6 +198,10 @@ class DistributedCalculator:
         self.decomposition = BrickDecomposition(self.cell, grid, halo)
         if self.decomposition.world != self.comm.world:
             raise ValueError("brick grid does not match the number of ranks")
+        # every rank must own atoms: decided together, so that no rank leaves the others waiting in an exchange
+        owner = self.decomposition.owner(positions)
+        if np.bincount(owner, minlength=self.comm.world).min() == 0:
+            raise ValueError("domain decomposition: a brick of the grid owns no atom; use fewer ranks or another grid")
         plan = ExchangePlan(self.decomposition, positions, self.comm, self.device)
         self.plan = plan
         n_own, n_ghost = plan.num_owned, plan.num_ghost
@@ -197,70 +213,87 @@ class DistributedCalculator:
         self.generation = result["generation"]
         self.num_edges = result["num_edges"]
         dev = self.device
+        world = self.comm.world
         self.send_local = torch.from_numpy(plan.send_local).to(dev)
-        self.ghost_nodes = torch.arange(n_own, n_own + n_ghost, dtype=torch.int32, device=dev)
-        # ghost position = owner's current (wrapped-at-prepare) position + image offset relative to it
-        owner_shift_of_ghost = -self.decomposition.wrapped_fractional(positions)[1][plan.ghost_idx]
-        self.ghost_offset = torch.from_numpy((plan.ghost_shift - owner_shift_of_ghost) @ self.cell).to(dev)
-        self.owned_positions = torch.from_numpy(owned_pos).to(dev)
-        self.row = (self.ev.L_max + 1) ** 2 * self.ev.num_channels
-        # per-step buffers, allocated once per graph: the step then issues no allocation and few host operations
         n_send = len(self.send_local)
-        self.send_index = self.send_local.long()
         self.send_counts = [int(c) for c in plan.send_counts]
         self.recv_counts = [int(c) for c in plan.recv_counts]
-        self._local_pos = torch.empty((n_own + n_ghost, 3), dtype=torch.float64, device=dev)
+        # a ghost sits at its owner's current (wrapped-at-prepare) position plus a fixed image offset; the
+        # owners learn the offsets of their rows once, so the per-step gather already yields ghost positions
+        owner_shift_of_ghost = -self.decomposition.wrapped_fractional(positions)[1][plan.ghost_idx]
+        ghost_offset = torch.from_numpy((plan.ghost_shift - owner_shift_of_ghost) @ self.cell).to(dev)
+        self.send_offset = self.comm.all_to_all(ghost_offset, self.recv_counts, self.send_counts,
+                                                out=torch.empty((n_send, 3), dtype=torch.float64, device=dev))
+        self.row = (self.ev.L_max + 1) ** 2 * self.ev.num_channels
+        # per-step buffers, allocated once per graph: the step issues no allocation and few host operations
+        self.local_positions = torch.from_numpy(local_pos).to(dev)           # [owned | ghosts], the step's input buffer
+        self.owned_positions = self.local_positions[:n_own]
         self._send_pos = torch.empty((n_send, 3), dtype=torch.float64, device=dev)
         self._send_rows = torch.empty((n_send, self.row), dtype=torch.float32, device=dev)
-        self._recv_rows = torch.empty((n_ghost, self.row), dtype=torch.float32, device=dev)
-        self._back_rows = torch.empty((n_ghost, self.row), dtype=torch.float32, device=dev)
         self._got_rows = torch.empty((n_send, self.row), dtype=torch.float32, device=dev)
-        self._ghost_forces = torch.empty((n_ghost, 3), dtype=torch.float64, device=dev)
-        self._got_forces = torch.empty((n_send, 3), dtype=torch.float64, device=dev)
-        self._totals = torch.empty(10, dtype=torch.float64, device=dev)
-        self._totals_host = torch.empty(10, dtype=torch.float64).pin_memory() if str(dev).startswith("cuda") else torch.empty(10, dtype=torch.float64)
+        extra = self.TOTALS_ROWS
+        self._force_send = torch.empty((n_ghost + extra * world, 3), dtype=torch.float64, device=dev)
+        self._force_recv = torch.empty((n_send + extra * world, 3), dtype=torch.float64, device=dev)
+        self._force_send_counts = [c + extra for c in self.recv_counts]
+        self._force_recv_counts = [c + extra for c in self.send_counts]
+        self._ghost_begin = torch.tensor(np.concatenate([[0], np.cumsum(self.recv_counts)]), dtype=torch.int32, device=dev)
+        self._send_begin = torch.tensor(np.concatenate([[0], np.cumsum(self.send_counts)]), dtype=torch.int32, device=dev)
+        self._totals = torch.zeros(10, dtype=torch.float64, device=dev)
+        self._totals_host = torch.empty(10, dtype=torch.float64).pin_memory()
+        # ghost rows of H1 / H1_adj: the tail of the evaluator's own tensors
+        n_local = n_own + n_ghost
+        h1_ptr, row, first = self.ev.halo_tensor(0)
+        adj_ptr, _, _ = self.ev.halo_tensor(1)
+        assert row == self.row and first == n_own
+        self._h1_tail = _as_tensor(torch, h1_ptr, (n_local, self.row), torch.float32, dev)[n_own:]
+        self._h1_adj_tail = _as_tensor(torch, adj_ptr, (n_local, self.row), torch.float32, dev)[n_own:]
         return plan
 
     def calculate(self, owned_positions=None):
-        """One evaluation.  ``owned_positions``: device tensor f64 [num_owned, 3] (defaults to the
-        positions given to ``prepare``).  Returns energy and stress of the whole system and the forces
-        on this rank's owned atoms (device tensor)."""
+        """One evaluation.  ``owned_positions``: device tensor f64 [num_owned, 3]; by default the head of
+        ``local_positions`` is used as it stands (a caller may write the new positions there directly).
+        Returns energy and stress of the whole system and the forces on this rank's owned atoms
+        (device tensor)."""
+        torch = self.torch
+        caller_stream = torch.cuda.current_stream(self.device)
+        self.stream.wait_stream(caller_stream)
+        with torch.cuda.stream(self.stream):
+            out = self._calculate_on_stream(owned_positions)
+        caller_stream.wait_stream(self.stream)
+        return out
+
+    def _calculate_on_stream(self, owned_positions):
         torch, ev, plan, comm = self.torch, self.ev, self.plan, self.comm
-        if owned_positions is None:
-            owned_positions = self.owned_positions
         n_own, n_ghost = plan.num_owned, plan.num_ghost
         sc, rc = self.send_counts, self.recv_counts
         n_send = len(self.send_local)
-        # ghost positions: straight into the tail of the local position array
-        local_pos = self._local_pos
-        local_pos[:n_own].copy_(owned_positions)
-        torch.index_select(owned_positions, 0, self.send_index, out=self._send_pos)
+        world = comm.world
+        local_pos = self.local_positions
+        if owned_positions is not None and owned_positions.data_ptr() != local_pos.data_ptr():
+            local_pos[:n_own].copy_(owned_positions)
+        # ghost positions: owners gather their rows, displaced to the images, straight into the peers' tails
+        ev.gather_position_rows(local_pos.data_ptr(), self.send_local.data_ptr(), n_send, self.send_offset.data_ptr(),
+                                self._send_pos.data_ptr())
         comm.all_to_all(self._send_pos, sc, rc, out=local_pos[n_own:])
-        local_pos[n_own:].add_(self.ghost_offset)
         ev.distributed_begin(self.generation, local_pos.data_ptr())
-        # forward halo: H1 rows of my owned atoms to the ranks that hold them as ghosts
+        # forward halo: H1 rows of my owned atoms into the tail of the feature tensor of the ranks that hold them as ghosts
         ev.halo_pack(0, self.send_local.data_ptr(), n_send, self._send_rows.data_ptr())
-        comm.all_to_all(self._send_rows, sc, rc, out=self._recv_rows)
-        ev.halo_unpack(0, self.ghost_nodes.data_ptr(), n_ghost, self._recv_rows.data_ptr(), False)
+        comm.all_to_all(self._send_rows, sc, rc, out=self._h1_tail)
         ev.distributed_continue()
-        # reverse halo: H1_adj rows of my ghosts back to their owners, summed there
-        ev.halo_pack(1, self.ghost_nodes.data_ptr(), n_ghost, self._back_rows.data_ptr())
-        comm.all_to_all(self._back_rows, rc, sc, out=self._got_rows)
+        # reverse halo: H1_adj rows of my ghosts leave from the tail of the adjoint tensor and are summed at their owners
+        comm.all_to_all(self._h1_adj_tail, rc, sc, out=self._got_rows)
         ev.halo_unpack(1, self.send_local.data_ptr(), n_send, self._got_rows.data_ptr(), True)
         ev.distributed_finish()
-        # ghost forces back to the owners
-        e_ptr, f_ptr, _v = ev.device_results()
-        n_local = n_own + n_ghost
-        forces = _as_tensor(torch, f_ptr, (n_local, 3), torch.float64, self.device)
-        self._ghost_forces.copy_(forces[n_own:])
-        comm.all_to_all(self._ghost_forces, rc, sc, out=self._got_forces)
-        ev.add_force_rows(self.send_local.data_ptr(), n_send, self._got_forces.data_ptr())
-        # energy and virial of this rank sit next to each other on the device: [E, 9 virial components]
-        self._totals.copy_(_as_tensor(torch, e_ptr, (10,), torch.float64, self.device))
-        comm.all_reduce_sum(self._totals)
+        # ghost forces back to the owners, with every rank's energy and virial riding along
+        ev.pack_ghost_forces(world, self._ghost_begin.data_ptr(), n_ghost, self._force_send.data_ptr())
+        comm.all_to_all(self._force_send, self._force_send_counts, self._force_recv_counts, out=self._force_recv)
+        ev.unpack_ghost_forces(world, self._send_begin.data_ptr(), self.send_local.data_ptr(), n_send, self._force_recv.data_ptr(),
+                               self._totals.data_ptr())
         self._totals_host.copy_(self._totals, non_blocking=True)
         ev.synchronize()        # one host synchronisation; fetches the status word (raises on a device-side error)
         host = self._totals_host.numpy()
+        _e, f_ptr, _v = ev.device_results()
+        forces = _as_tensor(torch, f_ptr, (n_own + n_ghost, 3), torch.float64, self.device)
         return {"energy": float(host[0]), "stress": -host[1:].reshape(3, 3).copy() / self.volume,
                 "forces": forces[:n_own], "owned": plan.owned}
 

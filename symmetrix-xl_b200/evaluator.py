@@ -36,6 +36,11 @@ class ModelInfo(ctypes.Structure):
 _P = ctypes.c_void_p
 SIGNATURES = {
     "sxb_create": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(_P)]),
+    "sxb_create_with_head": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.c_char_p, ctypes.POINTER(_P)]),
+    "sxb_selected_head": (ctypes.c_int, [_P, ctypes.c_char_p, ctypes.c_int32]),
+    "sxb_model_file_info": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_char_p, ctypes.POINTER(ModelInfo), ctypes.c_char_p,
+                                           ctypes.c_int32, _P, ctypes.c_int32]),
+    "sxb_measure_device_peaks": (ctypes.c_int, [ctypes.c_int32, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]),
     "sxb_destroy": (None, [_P]),
     "sxb_last_error": (ctypes.c_char_p, []),
     "sxb_model_info_get": (ctypes.c_int, [_P, ctypes.POINTER(ModelInfo)]),
@@ -69,6 +74,11 @@ SIGNATURES = {
     "sxb_halo_pack": (ctypes.c_int, [_P, ctypes.c_int32, _P, ctypes.c_int64, _P]),
     "sxb_halo_unpack": (ctypes.c_int, [_P, ctypes.c_int32, _P, ctypes.c_int64, _P, ctypes.c_int32]),
     "sxb_add_force_rows": (ctypes.c_int, [_P, _P, ctypes.c_int64, _P]),
+    "sxb_halo_tensor": (ctypes.c_int, [_P, ctypes.c_int32, ctypes.POINTER(_P), ctypes.POINTER(ctypes.c_int64),
+                                       ctypes.POINTER(ctypes.c_int64)]),
+    "sxb_gather_position_rows": (ctypes.c_int, [_P, _P, _P, ctypes.c_int64, _P, _P]),
+    "sxb_pack_ghost_forces": (ctypes.c_int, [_P, ctypes.c_int32, _P, ctypes.c_int64, _P]),
+    "sxb_unpack_ghost_forces": (ctypes.c_int, [_P, ctypes.c_int32, _P, _P, ctypes.c_int64, _P, _P]),
     "sxb_set_stream": (ctypes.c_int, [_P, _P]),
     "sxb_set_tile_size": (ctypes.c_int, [_P, ctypes.c_int32]),
     "sxb_set_profiling": (ctypes.c_int, [_P, ctypes.c_int32]),
@@ -110,15 +120,39 @@ def _f64(a):
     return np.ascontiguousarray(a, dtype=np.float64)
 
 
+def model_file_info(filename, head: str = ""):
+    """Host-only inspection of a model file: structure, selected prediction head and its atomic energies."""
+    lib = load_library()
+    info = ModelInfo()
+    name = ctypes.create_string_buffer(256)
+    energies = np.zeros(512, dtype=np.float64)
+    _check(lib.sxb_model_file_info(str(filename).encode(), (head or "").encode(), ctypes.byref(info), name, 256,
+                                   energies.ctypes.data, energies.size))
+    return {"num_elements": info.num_elements, "num_channels": info.num_channels, "l_max": info.l_max,
+            "L_max": info.hidden_l_max, "num_paths": info.num_paths, "num_lme": info.num_lme, "shape_id": info.shape_id,
+            "r_cut": info.r_cut, "head": name.value.decode(), "atomic_energies": energies[:info.num_elements].copy()}
+
+
+def measure_device_peaks(device: int = 0):
+    """Measured FP32 FMA rate (TFLOP/s) and L2-to-SM read bandwidth (GB/s) of a device."""
+    lib = load_library()
+    fma, l2 = ctypes.c_double(), ctypes.c_double()
+    _check(lib.sxb_measure_device_peaks(int(device), ctypes.byref(fma), ctypes.byref(l2)))
+    return {"fp32_fma_tflops": fma.value, "l2_read_gbs": l2.value}
+
+
 class MACEB200:
     """FP32 evaluator of a compact two-layer MACE model on one B200."""
 
-    def __init__(self, filename, device: int = 0):
+    def __init__(self, filename, device: int = 0, head: str = ""):
         lib = load_library()
         handle = _P()
-        _check(lib.sxb_create(str(filename).encode(), int(device), ctypes.byref(handle)))
+        _check(lib.sxb_create_with_head(str(filename).encode(), int(device), (head or "").encode(), ctypes.byref(handle)))
         self._h = handle
         self._lib = lib
+        name = ctypes.create_string_buffer(256)
+        _check(lib.sxb_selected_head(self._h, name, 256))
+        self.head = name.value.decode()
         info = ModelInfo()
         _check(lib.sxb_model_info_get(self._h, ctypes.byref(info)))
         self.num_elements = info.num_elements
@@ -126,6 +160,7 @@ class MACEB200:
         self.l_max = info.l_max
         self.L_max = info.hidden_l_max
         self.num_lme = info.num_lme
+        self.num_paths = info.num_paths
         self.r_cut = info.r_cut
         z = np.zeros(info.num_elements, dtype=np.int32)
         _check(lib.sxb_atomic_numbers(self._h, z.ctypes.data, len(z)))
@@ -204,6 +239,24 @@ class MACEB200:
 
     def add_force_rows(self, indices_ptr, count, in_ptr):
         _check(self._lib.sxb_add_force_rows(self._h, ctypes.c_void_p(indices_ptr), int(count), ctypes.c_void_p(in_ptr)))
+
+    def halo_tensor(self, which):
+        """(device address, floats per row, first ghost row) of H1 (0) or H1_adj (1)."""
+        ptr, row, first = _P(), ctypes.c_int64(), ctypes.c_int64()
+        _check(self._lib.sxb_halo_tensor(self._h, int(which), ctypes.byref(ptr), ctypes.byref(row), ctypes.byref(first)))
+        return ptr.value, row.value, first.value
+
+    def gather_position_rows(self, rows_ptr, indices_ptr, count, offsets_ptr, out_ptr):
+        _check(self._lib.sxb_gather_position_rows(self._h, ctypes.c_void_p(rows_ptr), ctypes.c_void_p(indices_ptr), int(count),
+                                                  ctypes.c_void_p(offsets_ptr), ctypes.c_void_p(out_ptr)))
+
+    def pack_ghost_forces(self, world, ghost_begin_ptr, num_ghosts, out_ptr):
+        _check(self._lib.sxb_pack_ghost_forces(self._h, int(world), ctypes.c_void_p(ghost_begin_ptr), int(num_ghosts),
+                                               ctypes.c_void_p(out_ptr)))
+
+    def unpack_ghost_forces(self, world, send_begin_ptr, indices_ptr, num_rows, in_ptr, totals_ptr):
+        _check(self._lib.sxb_unpack_ghost_forces(self._h, int(world), ctypes.c_void_p(send_begin_ptr), ctypes.c_void_p(indices_ptr),
+                                                 int(num_rows), ctypes.c_void_p(in_ptr), ctypes.c_void_p(totals_ptr)))
 
     def set_tile_size(self, receivers_per_tile: int):
         """Tiled streaming with a reusable workspace (0 = off); prepare the graph again afterwards."""
@@ -350,8 +403,8 @@ class Calculator:
     the largest displacement exceeds skin/2, :2894-2899), device graph builder, evaluation from
     positions, and result assembly (:3821-3894)."""
 
-    def __init__(self, model_path, skin: float = 0.5, device: int = 0):
-        self.evaluator = MACEB200(model_path, device)
+    def __init__(self, model_path, skin: float = 0.5, device: int = 0, head: str = ""):
+        self.evaluator = MACEB200(model_path, device, head)
         self.skin = float(skin)
         self._generation = 0
         self._reference_positions = None

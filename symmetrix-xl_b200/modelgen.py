@@ -54,7 +54,7 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
                channels: int | None = None, num_spline_points: int = 256,
                radial_hidden=(64, 64, 64), num_bessel: int = 8, cutoff_p: int = 5,
                a0_scaled: bool = False, a1_scaled: bool = False, zbl: bool = False,
-               agnesi: bool = False) -> dict:
+               agnesi: bool = False, heads=()) -> dict:
     """Random-weight compact model of architecture ``arch`` as a JSON-serialisable dict."""
     cfg = dict(ARCHITECTURES[arch])
     C = int(channels or cfg["channels"])
@@ -189,6 +189,24 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
         "readout_2_hidden_size": 16,
         "readout_2_scale_factor": 1.679177,
     }
+    if heads:
+        # multi-head file (schema of libsymmetrix/source/prediction_heads.hpp:10-90): every head carries its own
+        # atomic energies, readouts and ZBL coefficients; the last head is the default, the top level holds the first
+        fields = ["atomic_energies", "readout_1_weights_for_M0", "readout_2_weights_1", "readout_2_weights_2"]
+        if zbl:
+            fields.append("zbl_c")
+        parameters = {}
+        for index, name in enumerate(heads):
+            payload = {key: model[key] for key in fields}
+            if index > 0:
+                payload = {"atomic_energies": (-1.0 - 0.5 * rng.random(A)).tolist(),
+                           "readout_1_weights_for_M0": normal(C, scale=1.0 / np.sqrt(C)).tolist(),
+                           "readout_2_weights_1": normal(16 * C, scale=1.0 / np.sqrt(C)).tolist(),
+                           "readout_2_weights_2": normal(16, scale=0.25).tolist(),
+                           **({"zbl_c": [0.2, 0.5, 0.25, 0.05]} if zbl else {})}
+            parameters[name] = payload
+        model["prediction_heads"] = {"schema_version": 1, "names": list(heads), "default": heads[-1],
+                                     "parameters": parameters}
     return model
 
 

@@ -40,3 +40,41 @@ def test_product_does_not_import_the_oracle():
         if path.suffix in {".py", ".cu", ".cuh", ".cpp", ".hpp", ".h"}:
             text = path.read_text()
             assert "oracle" not in text.replace("oracles", ""), path
+
+
+def test_model_loader_selects_prediction_heads_on_the_host(pkg, tmp_path):
+    """Multi-head files: the default head's parameters replace the top-level ones, a named head can be
+    asked for, and malformed sections are refused (reference: select_prediction_head,
+    libsymmetrix/source/prediction_heads.hpp:10-90).  Parsed on the host; no device is needed."""
+    import json
+
+    import numpy as np
+
+    model = pkg.modelgen.make_model("small", seed=3, heads=("pbe", "omat"))
+    path = tmp_path / "two_heads.json"
+    path.write_text(json.dumps(model))
+    heads = model["prediction_heads"]["parameters"]
+    info = pkg.model_file_info(path)
+    assert info["head"] == "omat" and info["num_channels"] == 32 and info["shape_id"] == 0
+    assert np.allclose(info["atomic_energies"], heads["omat"]["atomic_energies"])
+    assert not np.allclose(info["atomic_energies"], heads["pbe"]["atomic_energies"])
+    info = pkg.model_file_info(path, head="pbe")
+    assert info["head"] == "pbe" and np.allclose(info["atomic_energies"], heads["pbe"]["atomic_energies"])
+    with pytest.raises(ValueError):
+        pkg.model_file_info(path, head="missing")
+    broken = json.loads(path.read_text())
+    del broken["prediction_heads"]["parameters"]["pbe"]["readout_2_weights_2"]
+    (tmp_path / "broken.json").write_text(json.dumps(broken))
+    with pytest.raises(ValueError):
+        pkg.model_file_info(tmp_path / "broken.json")
+    broken = json.loads(path.read_text())
+    broken["prediction_heads"]["default"] = "nobody"
+    (tmp_path / "broken2.json").write_text(json.dumps(broken))
+    with pytest.raises(ValueError):
+        pkg.model_file_info(tmp_path / "broken2.json")
+    # a single-head file names no head; asking for one is an error
+    single = tmp_path / "single.json"
+    pkg.modelgen.write_model(single, "small", seed=3)
+    assert pkg.model_file_info(single)["head"] == ""
+    with pytest.raises(ValueError):
+        pkg.model_file_info(single, head="pbe")

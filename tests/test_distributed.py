@@ -115,6 +115,17 @@ def test_single_rank_decomposition_matches_periodic_evaluation(pkg, model_path, 
         assert abs(out["energy"] - ref_out["energy"]) / len(pos) <= 1e-6
         assert np.abs(forces - ref_out["forces"][out["owned"]]).max() <= 1e-5
         assert np.abs(out["stress"] - ref_out["stress"]).max() <= 1e-7
+    from conftest import csr_from_positions
+    from oracle import ref
+
+    if ref.available():      # and directly against the reference's serial evaluator
+        first, src, shifts, xyz = csr_from_positions(pos, cell, calc.ev.r_cut)
+        m = ref.ReferenceMACE(str(path), double=False)
+        m.compute(types, np.diff(first), src, xyz)
+        F, S = ref.reduce_forces_stress(len(pos), np.diff(first), src, m.get("node_forces"), xyz, abs(np.linalg.det(cell)))
+        assert abs(out["energy"] - m.get("node_energies").sum()) / len(pos) <= 1e-5
+        assert np.abs(forces - F[out["owned"]]).max() <= 1e-4
+        assert np.abs(out["stress"] - S).max() <= 1e-6
 
 
 @pytest.mark.gpu

@@ -1,6 +1,6 @@
 """GPU parity tests: the CUDA path through the C ABI against the oracles on identical inputs.
 
-Tolerances are BASELINE's: |dE| <= 1e-5 eV/atom, |dF| <= 1e-4 eV/A per component,
+Tolerances of the force path: |dE| <= 1e-5 eV/atom, |dF| <= 1e-4 eV/A per component,
 |dsigma| <= 1e-6 eV/A^3; the neighbor list must be bit-exact.
 """
 import numpy as np
@@ -102,6 +102,89 @@ def test_energy_forces_stress_vs_reference_evaluator(pkg, model_path, arch, n, s
         assert np.abs(out["energies"] - e).max() <= TOL_E
         assert np.abs(out["forces"] - F).max() <= TOL_F
         assert np.abs(out["stress"] - S).max() <= TOL_S
+
+
+def _reference_efs(path, pos, cell, types, r_cut, double=False):
+    """Energy per node, atom forces and stress of the reference's serial evaluator on the exact-cutoff graph."""
+    first, src, shifts, xyz = csr_from_positions(pos, cell, r_cut)
+    m = ref.ReferenceMACE(str(path), double=double)
+    m.compute(types, np.diff(first), src, xyz)
+    F, S = ref.reduce_forces_stress(len(pos), np.diff(first), src, m.get("node_forces"), xyz, abs(np.linalg.det(cell)))
+    return m.get("node_energies"), F, S
+
+
+def _assert_matches_reference(out, e, F, S, natoms):
+    assert abs(out["energy"] - e.sum()) / natoms <= TOL_E
+    assert np.abs(out["energies"] - e).max() <= TOL_E
+    assert np.abs(out["forces"] - F).max() <= TOL_F
+    assert np.abs(out["stress"] - S).max() <= TOL_S
+
+
+def test_headline_configuration_vs_reference_evaluator(pkg, model_path):
+    """The configuration the throughput is quoted on, at full size: OMAT-0-medium architecture,
+    10x10x10 SrTiO3 (5,000 atoms, sigma 0.05 A), 0.5 A skin, against MACECPU<float>."""
+    if not ref.available():
+        pytest.skip("oracle/_ref was not built")
+    path = model_path("medium", seed=17)
+    pos, cell, types = pkg.modelgen.srtio3(10, 0.05, 17)
+    calc = pkg.Calculator(path, skin=0.5)
+    out = calc.calculate(pos, cell, types)
+    e, F, S = _reference_efs(path, pos, cell, types, calc.evaluator.r_cut)
+    _assert_matches_reference(out, e, F, S, len(pos))
+
+
+DISORDERED_ELEMENTS = (1, 6, 8, 13, 14, 22, 26, 38, 56, 79)
+
+
+def test_disordered_ten_element_solid_vs_reference_evaluator(pkg, model_path):
+    """Hidden irreps 0e+1o+2e, ten elements, a 2,000-atom cut of the seeded Poisson-disk solid
+    (0.085 atoms/A^3, 1.8 A minimum separation: irregular neighbor counts) against MACECPU<float>."""
+    if not ref.available():
+        pytest.skip("oracle/_ref was not built")
+    path = model_path("large", seed=17, atomic_numbers=DISORDERED_ELEMENTS)
+    pos, cell, types = pkg.modelgen.random_solid(2000, 0.085, 1.8, len(DISORDERED_ELEMENTS), 17)
+    calc = pkg.Calculator(path, skin=0.5)
+    out = calc.calculate(pos, cell, types)
+    assert len(np.unique(types)) == len(DISORDERED_ELEMENTS)
+    e, F, S = _reference_efs(path, pos, cell, types, calc.evaluator.r_cut)
+    _assert_matches_reference(out, e, F, S, len(pos))
+
+
+@pytest.mark.parametrize("arch,options", [("medium", {}), ("small", dict(a0_scaled=True, a1_scaled=True, zbl=True, agnesi=True))])
+def test_inactive_element_slots(pkg, model_path, arch, options):
+    """A model with ten element slots of which three non-adjacent ones (1, 4, 8) occur in the
+    structure: the active-type tables must skip the unused slots."""
+    if not ref.available():
+        pytest.skip("oracle/_ref was not built")
+    path = model_path(arch, seed=5, atomic_numbers=DISORDERED_ELEMENTS, **options)
+    pos, cell, base_types = pkg.modelgen.srtio3(3, 0.05, 9)
+    types = np.array([1, 4, 8], dtype=np.int32)[base_types]
+    calc = pkg.Calculator(path, skin=0.5)
+    out = calc.calculate(pos, cell, types)
+    for double in (True, False):
+        e, F, S = _reference_efs(path, pos, cell, types, calc.evaluator.r_cut, double=double)
+        _assert_matches_reference(out, e, F, S, len(pos))
+    # a second structure that uses other slots on the same evaluator: the tables are rebuilt
+    types2 = np.array([0, 9, 4], dtype=np.int32)[base_types]
+    out2 = calc.calculate(pos, cell, types2)
+    e, F, S = _reference_efs(path, pos, cell, types2, calc.evaluator.r_cut)
+    _assert_matches_reference(out2, e, F, S, len(pos))
+
+
+def test_multi_head_model_uses_the_selected_head(pkg, model_path, tmp_path):
+    """Two prediction heads: the default head against the reference's evaluator (which applies the
+    same selection), and the other head gives a different energy."""
+    if not ref.available():
+        pytest.skip("oracle/_ref was not built")
+    path = model_path("small", seed=8, heads=("pbe", "omat"), zbl=True)
+    pos, cell, types = pkg.modelgen.srtio3(3, 0.05, 2)
+    calc = pkg.Calculator(path, skin=0.5)
+    assert calc.evaluator.head == "omat"
+    out = calc.calculate(pos, cell, types)
+    e, F, S = _reference_efs(path, pos, cell, types, calc.evaluator.r_cut)
+    _assert_matches_reference(out, e, F, S, len(pos))
+    other = pkg.Calculator(path, skin=0.5, head="pbe").calculate(pos, cell, types)
+    assert abs(other["energy"] - out["energy"]) > 1e-3
 
 
 def test_tiny_systems_and_isolated_atoms(pkg, model_path):
@@ -228,6 +311,9 @@ def test_tiled_streaming_matches_untiled(pkg, model_path, arch, cells, tile, sca
     assert np.abs(got - h1_adj).max() <= 2e-5 * max(1.0, np.abs(h1_adj).max())
     with pytest.raises(ValueError):
         tiled.evaluator.stage("Phi1")
+    if ref.available():      # and directly against the reference's evaluator
+        e, F, S = _reference_efs(path, pos, cell, types, tiled.evaluator.r_cut)
+        _assert_matches_reference(b, e, F, S, len(pos))
 
 
 def test_tile_boundary_sizes(pkg, model_path):

@@ -41,11 +41,16 @@ def test_static_reduction_matches_allocating_entry_point_twice(pkg):
         d_out = torch.full((3 * n,), 7.0, dtype=torch.float64, device="cuda")      # garbage: must be overwritten
         d_stress = torch.full((9,), 7.0, dtype=torch.float64, device="cuda")
         d_status = torch.full((1,), 5, dtype=torch.int32, device="cuda")
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = lib.sxb_reduce_edge_forces_static(n, len(src), d_recv.data_ptr(), d_src.data_ptr(), d_f.data_ptr(), d_x.data_ptr(),
                                                ctypes.c_double(volume), d_out.data_ptr(), d_stress.data_ptr(),
                                                d_status.data_ptr(), ctypes.c_void_p(stream.cuda_stream))
         assert rc == 0, lib.sxb_last_error()
         stream.synchronize()
+        if call > 0:
+            # once the first call has looked up the scratch address, a call takes no device memory
+            assert torch.cuda.mem_get_info()[0] == free_before
         got_f = d_out.cpu().numpy().reshape(n, 3)
         got_s = d_stress.cpu().numpy().reshape(3, 3)
         assert int(d_status.cpu()[0]) == 0
@@ -77,3 +82,20 @@ def test_static_reduction_rejects_oversized_and_flags_bad_edges(pkg):
     assert rc == 0
     torch.cuda.synchronize()
     assert int(d_status.cpu()[0]) == 1
+    # the status word is optional; a volume that is not finite and positive is refused
+    rc = lib.sxb_reduce_edge_forces_static(n, len(src), d_recv.data_ptr(), d_src.data_ptr(), d_f.data_ptr(), d_x.data_ptr(),
+                                           ctypes.c_double(volume), d_out.data_ptr(), d_stress.data_ptr(), None, None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    for bad_volume in (float("inf"), float("nan"), 0.0):
+        rc = lib.sxb_reduce_edge_forces_static(n, len(src), d_recv.data_ptr(), d_src.data_ptr(), d_f.data_ptr(), d_x.data_ptr(),
+                                               ctypes.c_double(bad_volume), d_out.data_ptr(), d_stress.data_ptr(), None, None)
+        assert rc != 0
+    # an empty edge list gives zero forces and zero stress
+    d_out.fill_(3.0)
+    d_stress.fill_(3.0)
+    rc = lib.sxb_reduce_edge_forces_static(n, 0, d_recv.data_ptr(), d_src.data_ptr(), d_f.data_ptr(), d_x.data_ptr(),
+                                           ctypes.c_double(volume), d_out.data_ptr(), d_stress.data_ptr(), None, None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert float(d_out.abs().max()) == 0.0 and float(d_stress.abs().max()) == 0.0
