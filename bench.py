@@ -210,6 +210,16 @@ def run_distributed(args):
             ms, last_out, _forces = step_e2e()
             e2e_ms.append(ms)
         clocks = sampler.stop()
+        # per-stage device times of this rank's kernels (separate passes with event pairs around each stage)
+        calc.ev.set_profiling(True)
+        stage_ms = {}
+        for _ in range(3):
+            flush.fill_(1)
+            barrier()
+            step_device()
+            for name, ms, _l in calc.ev.profile():
+                stage_ms[name] = stage_ms.get(name, 0.0) + ms / 3
+        calc.ev.set_profiling(False)
         t = torch.tensor([float(np.mean(device_ms)), float(np.mean(e2e_ms))], device="cuda", dtype=torch.float64)
         if world > 1:
             all_reduce(t, op=dist.ReduceOp.MAX)
@@ -255,6 +265,7 @@ def run_distributed(args):
                 "clocks": clocks,
                 "roofline": None,
                 "parity_vs_single_gpu": parity,
+                "stage_ms_rank0": {k: round(v, 4) for k, v in stage_ms.items()},
                 "energy_eV_per_atom": last_out["energy"] / total_atoms,
                 "wall_ms_timed_region": wall_ms,
             }))

@@ -57,6 +57,9 @@ int sxb_model_file_info(const char* model_json_path, const char* head, sxb_model
                         int32_t head_capacity, double* atomic_energies, int32_t energies_capacity);
 void sxb_destroy(sxb_evaluator* evaluator);
 const char* sxb_last_error(void);
+/* Number of CUDA devices this process can use (0 when there is none or the driver is missing); a
+ * multi-rank host maps its ranks onto them (the reference leaves this to Kokkos' device selection). */
+int sxb_device_count(void);
 
 /* Attributes atomic_numbers, atomic_energies, r_cut, num_channels ... of the Python class
  * (symmetrix/source/cpp/mace_kokkos.cpp:2040-2087). */
@@ -200,6 +203,32 @@ int sxb_last_compute_ms(const sxb_evaluator* evaluator, float* out);
 int sxb_prepare_local_graph(sxb_evaluator* evaluator, int32_t num_receivers, int32_t num_nodes, const int32_t* node_types,
                             const double* positions, double neighbor_cutoff, uint64_t* generation, int64_t* num_edges);
 int sxb_distributed_begin(sxb_evaluator* evaluator, uint64_t generation, const double* device_positions);
+/* The pair style's own form of the two calls above: it hands over ITS neighbor list and, each step,
+ * ITS edge vectors.  sxb_prepare_local_graph_csr replaces prepare_factorized_graph_device(num_receivers,
+ * num_feature_nodes, node_types, num_neigh, neigh_indices, neigh_types)
+ * (libsymmetrix/source/mace_kokkos.hpp:399-413; pair_symmetrix_mace_kokkos.cpp:1380-1476): owned atoms
+ * first, ghosts after; num_neigh int32[num_receivers], neigh_indices int32[sum num_neigh] index all
+ * num_nodes local nodes; node_types int32[num_nodes].  The three arrays are host pointers, or device
+ * pointers on the evaluator's device when pointers_on_device != 0 (Kokkos views in the reference).
+ * sxb_distributed_begin_edge_vectors replaces begin_factorized_distributed_evaluation(..., xyz, r,
+ * generation) (mace_kokkos.hpp:672-677; pair_symmetrix_mace_kokkos.cpp:1532-1568): device_xyz
+ * f64[3*num_edges] in the caller's edge order.  Edges at or beyond the model cutoff (list skin)
+ * contribute nothing, whether or not the caller has clamped them to the cutoff as the pair style does. */
+int sxb_prepare_local_graph_csr(sxb_evaluator* evaluator, int32_t num_receivers, int32_t num_nodes, const int32_t* node_types,
+                                const int32_t* num_neigh, const int32_t* neigh_indices, int32_t pointers_on_device,
+                                uint64_t* generation);
+int sxb_distributed_begin_edge_vectors(sxb_evaluator* evaluator, uint64_t generation, const double* device_xyz);
+/* Host-buffer forms for a plain (non-Kokkos) LAMMPS pair style, whose halo exchange runs through the
+ * host callbacks pack/unpack_forward_comm and pack/unpack_reverse_comm
+ * (pair_symmetrix/pair_symmetrix_mace.cpp:261-307, 443-646): sxb_distributed_begin_host takes host
+ * positions f64[3*num_nodes] (a graph without periodic shifts uses plain differences x_j - x_i, the
+ * ghosts being explicit atoms); sxb_halo_rows_get / _put copy the caller-order rows
+ * [first_row, first_row + count) of H1 (which = 0) or H1_adj (which = 1) to / from host floats
+ * [count][num_hidden*num_channels]; put with accumulate != 0 adds. */
+int sxb_distributed_begin_host(sxb_evaluator* evaluator, uint64_t generation, const double* host_positions);
+int sxb_halo_rows_get(sxb_evaluator* evaluator, int32_t which, int64_t first_row, int64_t count, float* host_out);
+int sxb_halo_rows_put(sxb_evaluator* evaluator, int32_t which, int64_t first_row, int64_t count, const float* host_in,
+                      int32_t accumulate);
 int sxb_distributed_continue(sxb_evaluator* evaluator);
 int sxb_distributed_finish(sxb_evaluator* evaluator);
 int sxb_halo_pack(sxb_evaluator* evaluator, int32_t which, const int32_t* device_indices, int64_t count, float* device_out);

@@ -63,6 +63,16 @@ extern "C" {
 
 const char* sxb_last_error(void) { return g_last_error.c_str(); }
 
+int sxb_device_count(void)
+{
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return count;
+}
+
 int sxb_create(const char* model_json_path, int device_ordinal, sxb_evaluator** out)
 {
     return guarded([&] {
@@ -210,7 +220,7 @@ int sxb_get_node_energies(sxb_evaluator* ev, double* out, int64_t capacity)
 {
     return guarded([&] {
         require(ev, "evaluator"); require(out, "out");
-        if (capacity < ev->impl.num_nodes()) throw std::invalid_argument("node_energies buffer is too small.");
+        if (capacity < ev->impl.num_receivers()) throw std::invalid_argument("node_energies buffer is too small.");
         ev->impl.get_node_energies(out);
     });
 }
@@ -318,6 +328,50 @@ int sxb_distributed_begin(sxb_evaluator* ev, uint64_t generation, const double* 
     return guarded([&] {
         require(ev, "evaluator"); require(device_positions, "device_positions");
         ev->impl.distributed_begin(generation, device_positions);
+    });
+}
+
+int sxb_prepare_local_graph_csr(sxb_evaluator* ev, int32_t num_receivers, int32_t num_nodes, const int32_t* node_types,
+                                const int32_t* num_neigh, const int32_t* neigh_indices, int32_t pointers_on_device, uint64_t* generation)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(node_types, "node_types"); require(num_neigh, "num_neigh"); require(generation, "generation");
+        *generation = ev->impl.prepare_graph_csr(num_receivers, num_nodes, node_types, num_neigh, neigh_indices, pointers_on_device != 0);
+    });
+}
+
+int sxb_distributed_begin_edge_vectors(sxb_evaluator* ev, uint64_t generation, const double* device_xyz)
+{
+    return guarded([&] {
+        require(ev, "evaluator");
+        if (ev->impl.num_edges() > 0) require(device_xyz, "device_xyz");
+        ev->impl.distributed_begin_edge_vectors(generation, device_xyz);
+    });
+}
+
+int sxb_distributed_begin_host(sxb_evaluator* ev, uint64_t generation, const double* host_positions)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(host_positions, "host_positions");
+        ev->impl.distributed_begin_host(generation, host_positions);
+    });
+}
+
+int sxb_halo_rows_get(sxb_evaluator* ev, int32_t which, int64_t first_row, int64_t count, float* host_out)
+{
+    return guarded([&] {
+        require(ev, "evaluator");
+        if (count > 0) require(host_out, "host_out");
+        ev->impl.get_halo_rows(which, first_row, count, host_out);
+    });
+}
+
+int sxb_halo_rows_put(sxb_evaluator* ev, int32_t which, int64_t first_row, int64_t count, const float* host_in, int32_t accumulate)
+{
+    return guarded([&] {
+        require(ev, "evaluator");
+        if (count > 0) require(host_in, "host_in");
+        ev->impl.put_halo_rows(which, first_row, count, host_in, accumulate != 0);
     });
 }
 

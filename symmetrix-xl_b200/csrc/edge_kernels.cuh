@@ -117,11 +117,14 @@ __global__ void geometry_from_positions_kernel(int num_nodes, const int* __restr
     const int begin = first[warp], end = first[warp + 1];
     for (int e = begin + lane; e < end; e += 32) {
         const int oj = original[sources[e]];
-        const size_t se = 3 * static_cast<size_t>(e);
-        const double sx = shifts[se], sy = shifts[se + 1], sz = shifts[se + 2];
-        const double dx = positions[3 * oj] - xi + sx * cell[0] + sy * cell[3] + sz * cell[6];
-        const double dy = positions[3 * oj + 1] - yi + sx * cell[1] + sy * cell[4] + sz * cell[7];
-        const double dz = positions[3 * oj + 2] - zi + sx * cell[2] + sy * cell[5] + sz * cell[8];
+        double dx = positions[3 * oj] - xi, dy = positions[3 * oj + 1] - yi, dz = positions[3 * oj + 2] - zi;
+        if (shifts != nullptr) {   // graphs without periodic shifts (explicit ghost atoms, open systems): plain differences
+            const size_t se = 3 * static_cast<size_t>(e);
+            const double sx = shifts[se], sy = shifts[se + 1], sz = shifts[se + 2];
+            dx += sx * cell[0] + sy * cell[3] + sz * cell[6];
+            dy += sx * cell[1] + sy * cell[4] + sz * cell[7];
+            dz += sx * cell[2] + sy * cell[5] + sz * cell[8];
+        }
         const double r = sqrt(dx * dx + dy * dy + dz * dz);
         if (!(r > 0.0) || !isfinite(r)) atomicOr(error_flag, 1);
         EdgeGeom g;
@@ -690,8 +693,9 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
         _Pragma("unroll") for (int q = 0; q < NE; ++q) out[q * C] = out_lme[q] * scale;                              \
     }                                                                                                                \
                                                                                                                      \
-    template <int kC>                                                                                                \
-    __global__ void __launch_bounds__(kC > 0 ? kC : 256)                                                             \
+    /* kMinBlocks caps the registers of the 128-channel build: 3 blocks per SM = at most 170 registers */           \
+    template <int kC, int kMinBlocks = 3, int kAblate = 0>                                                           \
+    __global__ void __launch_bounds__(kC > 0 ? kC : 256, kC == 128 ? kMinBlocks : 1)                                 \
     l1_reverse_kernel_##NAME(int num_nodes, int node0, int C_runtime, const int* __restrict__ first,                            \
                              const int* __restrict__ sources, const EdgeGeom* __restrict__ geom,                     \
                              const unsigned char* __restrict__ atype, SplineGrid grid,                               \
@@ -733,7 +737,7 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
                 if (id.x < 0) continue;                                                                              \
                 const float4 m = s.misc[t];                                                                          \
                 const float x = m.x, xx = x * x, xxx = xx * x, x2 = 2.0f * x, xx3 = 3.0f * xx;                       \
-                const float4* c4 = table4 + (id.x >> 2) + k;                                                         \
+                const float4* c4 = table4 + ((kAblate & 2) ? 0 : (id.x >> 2)) + k;                                  \
                 float R[NP], dR[NP];                                                                                 \
                 _Pragma("unroll") for (int p = 0; p < NP; ++p) {                                                     \
                     const float4 c = c4[p * C];                                                                      \
@@ -748,7 +752,9 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
                 _Pragma("unroll") for (int q = 0; q < 16; ++q) ang[q] = 0.0f;                                        \
                 float radial = 0.0f;                                                                                 \
                 SXB_##NAME##_L1_REVERSE_BODY                                                                         \
-                _Pragma("unroll") for (int q = 0; q < NH; ++q) atomicAdd(H1_adj + source_row + q * C, hadj[q]);      \
+                if (!(kAblate & 1)) {                                                                                \
+                    _Pragma("unroll") for (int q = 0; q < NH; ++q) atomicAdd(H1_adj + source_row + q * C, hadj[q]);  \
+                } else if (hadj[0] + hadj[1] == 123.456f) H1_adj[k] = hadj[2] + hadj[NH - 1];                        \
                 float fx = radial * m.y, fy = radial * m.z, fz = radial * m.w;                                       \
                 {                                                                                                    \
                     float g[16];                                                                                     \
@@ -759,8 +765,10 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
                     load16(s.gz[t], g);                                                                              \
                     _Pragma("unroll") for (int q = 0; q < 16; ++q) fz = fmaf(ang[q], g[q], fz);                      \
                 }                                                                                                    \
-                const float total = warp_reduce3_transposed(fx, fy, fz, lane);   /* lanes 0, 8, 16: x, y, z */       \
-                if ((lane & 7) == 0 && lane < 24) fs.partial[t][warp][lane >> 3] = total;                            \
+                if (!(kAblate & 4)) {                                                                                \
+                    const float total = warp_reduce3_transposed(fx, fy, fz, lane);   /* lanes 0, 8, 16: x, y, z */   \
+                    if ((lane & 7) == 0 && lane < 24) fs.partial[t][warp][lane >> 3] = total;                        \
+                } else if (fx + fy + fz == 123.456f) fs.partial[t][warp][0] = fx;                                    \
             }                                                                                                        \
             __syncthreads();                                                                                         \
             flush_chunk_forces<8>(fs, s, chunk, count, num_warps, out, density_coef);                                \

@@ -15,6 +15,7 @@
 #include <numeric>
 
 #include "edge_kernels.cuh"
+#include "edge_kernels_dual.cuh"
 #include "edge_kernels_split.cuh"
 #include "edge_kernels_warp.cuh"
 #include "graph_kernels.cuh"
@@ -32,15 +33,6 @@ void upload(DeviceBuffer<T>& buffer, const std::vector<T>& host, cudaStream_t st
     buffer.reserve(host.size());
     if (!host.empty())
         SXB_CUDA(cudaMemcpyAsync(buffer.ptr, host.data(), host.size() * sizeof(T), cudaMemcpyHostToDevice, stream));
-}
-
-__global__ void unpermute_doubles_kernel(int n, int width, const int* __restrict__ original, const double* __restrict__ in,
-                                         double* __restrict__ out)
-{
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const int o = original[i];
-    for (int q = 0; q < width; ++q) out[static_cast<size_t>(o) * width + q] = in[static_cast<size_t>(i) * width + q];
 }
 
 __global__ void unpermute_stage_kernel(long n, long row, const int* __restrict__ original, const float* __restrict__ in,
@@ -129,6 +121,7 @@ Evaluator::Evaluator(const std::string& json_path, int device_ordinal, const std
     upload(atomic_energies_, model_.atomic_energies, stream_);
     if (const char* env = std::getenv("SXB_SIMT_LINEARS")) use_tensor_cores_ = !(env[0] == '1');
     if (const char* env = std::getenv("SXB_CUDA_GRAPHS")) use_graphs_ = env[0] != '0';
+    if (const char* env = std::getenv("SXB_L1_REVERSE_VARIANT")) l1_reverse_variant_ = env[0] - '0';
     if (const char* env = std::getenv("SXB_POLY_GROUP")) {   // nodes per thread in the contraction kernels: "<forward><reverse>"
         if (env[0] == '1' || env[0] == '2') poly_g_forward_ = env[0] - '0';
         if (env[0] != 0 && (env[1] == '1' || env[1] == '2')) poly_g_reverse_ = env[1] - '0';
@@ -175,7 +168,8 @@ Evaluator::~Evaluator()
     if (event_end_) cudaEventDestroy(event_end_);
     for (auto e : event_pool_) cudaEventDestroy(e);
     if (stream_ && owns_stream_) cudaStreamDestroy(stream_);
-    if (host_mirror_) cudaFreeHost(host_mirror_);
+    if (host_results_) cudaFreeHost(host_results_);
+    if (host_stage_) cudaFreeHost(host_stage_);
 }
 
 void Evaluator::prepare_active_types(const std::vector<int>& node_types)
@@ -315,6 +309,27 @@ void Evaluator::install_graph(int num_receivers, int num_nodes, const std::vecto
     positions_.reserve(ALL * 3);
     if (keep_edge_forces_) edge_forces_.reserve_with_slack(3 * static_cast<std::size_t>(num_edges));
     SXB_CUDA(cudaStreamSynchronize(stream_));
+    // pinned host side of an evaluation: a staging copy of the positions (uploaded by a copy node of the
+    // captured step) and the result block the closing kernel writes through the mapping
+    constexpr std::size_t kHostBlockLimit = 4u << 20;   // doubles (32 MB): beyond this the getters copy on demand
+    const std::size_t result_doubles = 11 + N + 3 * ALL;
+    if (result_doubles <= kHostBlockLimit) {
+        if (host_results_capacity_ < result_doubles) {
+            if (host_results_) SXB_CUDA(cudaFreeHost(host_results_));
+            if (host_stage_) SXB_CUDA(cudaFreeHost(host_stage_));
+            host_results_ = host_stage_ = nullptr;
+            host_results_capacity_ = 0;
+            const std::size_t grown = result_doubles + result_doubles / 16;
+            SXB_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&host_results_), sizeof(double) * grown, cudaHostAllocMapped));
+            SXB_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&host_stage_), sizeof(double) * grown, cudaHostAllocDefault));
+            host_results_capacity_ = grown;
+        }
+    } else if (host_results_) {
+        SXB_CUDA(cudaFreeHost(host_results_));
+        SXB_CUDA(cudaFreeHost(host_stage_));
+        host_results_ = host_stage_ = nullptr;
+        host_results_capacity_ = 0;
+    }
     generation_ += 1;
     have_results_ = false;
     mirror_valid_ = false;
@@ -464,6 +479,72 @@ std::uint64_t Evaluator::prepare_graph(int num_nodes, const int* node_types, con
     }
     std::vector<int> types(node_types, node_types + num_nodes);
     install_graph(num_nodes, num_nodes, types, E, shifts != nullptr);
+    return generation_;
+}
+
+namespace {
+__global__ void widen_counts_kernel(int n, const int* __restrict__ counts, long long* __restrict__ wide, int* __restrict__ status)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i > n) return;
+    const int c = i < n ? counts[i] : 0;
+    if (c < 0) atomicOr(status, 8);
+    wide[i] = c < 0 ? 0 : c;
+}
+
+__global__ void check_indices_kernel(long num_edges, int num_nodes, const int* __restrict__ indices, int* __restrict__ status)
+{
+    const long e = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= num_edges) return;
+    const int j = indices[e];
+    if (j < 0 || j >= num_nodes) atomicOr(status, 16);
+}
+}  // namespace
+
+// A caller-built receiver-major CSR over num_nodes nodes of which the first num_receivers own edge
+// lists (the others are ghosts: feature-only nodes).  Host or device arrays; evaluated from per-step
+// edge vectors.  This is the graph a LAMMPS pair style holds: owned atoms first, ghosts after, the
+// full neighbor list of the owned atoms (reference: MACEKokkos::prepare_factorized_graph_device,
+// libsymmetrix/source/mace_kokkos.hpp:399-413; call site pair_symmetrix_mace_kokkos.cpp:1464-1476).
+std::uint64_t Evaluator::prepare_graph_csr(int num_receivers, int num_nodes, const int* node_types, const int* num_neigh,
+                                           const int* neigh_indices, bool on_device)
+{
+    SXB_CUDA(cudaSetDevice(device_));
+    if (num_nodes <= 0) throw std::invalid_argument("Graph needs at least one node.");
+    if (num_receivers <= 0 || num_receivers > num_nodes) throw std::invalid_argument("Receiver count must lie in [1, num_nodes].");
+    const int R = num_receivers, threads = 256;
+    std::vector<int> types(num_nodes);
+    if (on_device) SXB_CUDA(cudaMemcpyAsync(types.data(), node_types, sizeof(int) * num_nodes, cudaMemcpyDeviceToHost, stream_));
+    else std::copy(node_types, node_types + num_nodes, types.begin());
+    ig_counts_.reserve(R + 1);
+    SXB_CUDA(cudaMemcpyAsync(ig_counts_.ptr, num_neigh, sizeof(int) * R, on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, stream_));
+    nb_counts_.reserve(R + 1);
+    nb_offsets_.reserve(R + 1);
+    SXB_CUDA(cudaMemsetAsync(error_flag_.ptr, 0, sizeof(int), stream_));
+    widen_counts_kernel<<<blocks_for(R + 1, threads), threads, 0, stream_>>>(R, ig_counts_.ptr, nb_counts_.ptr, error_flag_.ptr);
+    std::size_t scan_bytes = 0;
+    cub::DeviceScan::ExclusiveSum(nullptr, scan_bytes, nb_counts_.ptr, nb_offsets_.ptr, R + 1, stream_);
+    nb_temp_.reserve(scan_bytes);
+    cub::DeviceScan::ExclusiveSum(nb_temp_.ptr, scan_bytes, nb_counts_.ptr, nb_offsets_.ptr, R + 1, stream_);
+    long long total = 0;
+    SXB_CUDA(cudaMemcpyAsync(&total, nb_offsets_.ptr + R, sizeof(long long), cudaMemcpyDeviceToHost, stream_));
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+    if (total > static_cast<long long>(std::numeric_limits<int>::max())) throw std::length_error("Graph exceeds 32-bit edge indexing.");
+    const long E = static_cast<long>(total);
+    first_caller_.reserve(R + 1);
+    narrow_offsets_kernel<<<blocks_for(R + 1, threads), threads, 0, stream_>>>(R, nb_offsets_.ptr, first_caller_.ptr);
+    sources_caller_.reserve_with_slack(static_cast<std::size_t>(E));
+    if (E > 0) {
+        SXB_CUDA(cudaMemcpyAsync(sources_caller_.ptr, neigh_indices, sizeof(int) * E, on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, stream_));
+        check_indices_kernel<<<blocks_for(E, threads), threads, 0, stream_>>>(E, num_nodes, sources_caller_.ptr, error_flag_.ptr);
+    }
+    int status = 0;
+    SXB_CUDA(cudaMemcpyAsync(&status, error_flag_.ptr, sizeof(int), cudaMemcpyDeviceToHost, stream_));
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+    launches_ += 3;
+    if (status & 8) throw std::invalid_argument("num_neigh must be non-negative.");
+    if (status & 16) throw std::invalid_argument("neigh_indices entry is out of range.");
+    install_graph(R, num_nodes, types, E, false);
     return generation_;
 }
 
@@ -808,6 +889,12 @@ void Evaluator::run_pipeline(int phases)
                 const RowMap rows{static_cast<long>(NH) * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
                 calls.push_back({m0, rows, &s_h1_[l], false, H1_.ptr + t0 * rowH, rows, 0, T, false, nullptr});
             }
+            // one tile: the element-dependent skip term of H2 (x_i T_element) only needs M0, so it rides in this launch
+            if (!tiled)
+                for_type_ranges(t0, T, [&](int a, int begin, int count) {
+                    calls.push_back({M0_.ptr + begin * rowH, scalar_rows, &s_h2_skip_[active_types_[a]], false,
+                                     H2_.ptr + static_cast<std::size_t>(begin - t0) * C, flat_rows, 0, count, false, nullptr});
+                });
             launch_tc(calls);
             span_end();
         }
@@ -862,25 +949,48 @@ void Evaluator::run_pipeline(int phases)
             // H2 = xs T_element + M1 W
             span_begin("gemm_h2");
             {
-                std::vector<TcCall> calls;
-                for_type_ranges(t0, T, [&](int a, int begin, int count) {
-                    calls.push_back({M0_.ptr + begin * rowH, scalar_rows, &s_h2_skip_[active_types_[a]], false,
-                                     H2_.ptr + static_cast<std::size_t>(begin - t0) * C, flat_rows, 0, count, false, nullptr});
-                });
-                launch_tc(calls);
+                if (tiled) {
+                    std::vector<TcCall> calls;
+                    for_type_ranges(t0, T, [&](int a, int begin, int count) {
+                        calls.push_back({M0_.ptr + begin * rowH, scalar_rows, &s_h2_skip_[active_types_[a]], false,
+                                         H2_.ptr + static_cast<std::size_t>(begin - t0) * C, flat_rows, 0, count, false, nullptr});
+                    });
+                    launch_tc(calls);
+                }
                 launch_tc({{M1_.ptr, flat_rows, &s_h2_m1_, false, H2_.ptr, flat_rows, 0, T, true, nullptr}});
             }
             span_end();
             span_begin("readout");
-            readout_kernel<<<blocks_for(static_cast<long>(T) * 32, 256), 256, 0, stream_>>>(
-                T, C, model_.readout2_hidden, model_.readout2_scale, M0_.ptr + t0 * rowH, NH, H2_.ptr, element_.ptr + t0,
-                atomic_energies_.ptr, readout1_.ptr, readout2_w1_.ptr, readout2_w2_.ptr, node_energies_.ptr + t0,
-                H2_adj_.ptr + static_cast<std::size_t>(t0) * C, energy_slots_.ptr);
+            if (model_.readout2_hidden == 16 && (C == 128 || C == 32)) {
+#define SXB_READOUT16(CHUNKS)                                                                                             \
+                readout16_kernel<CHUNKS><<<blocks_for(static_cast<long>(T) * 32, 256), 256, 0, stream_>>>(                 \
+                    T, model_.readout2_scale, M0_.ptr + t0 * rowH, NH, H2_.ptr, element_.ptr + t0, atomic_energies_.ptr,   \
+                    readout1_.ptr, readout2_w1_.ptr, readout2_w2_.ptr, node_energies_.ptr + t0,                            \
+                    H2_adj_.ptr + static_cast<std::size_t>(t0) * C, energy_slots_.ptr)
+                if (C == 128) SXB_READOUT16(4);
+                else SXB_READOUT16(1);
+#undef SXB_READOUT16
+            } else
+                readout_kernel<<<blocks_for(static_cast<long>(T) * 32, 256), 256, 0, stream_>>>(
+                    T, C, model_.readout2_hidden, model_.readout2_scale, M0_.ptr + t0 * rowH, NH, H2_.ptr, element_.ptr + t0,
+                    atomic_energies_.ptr, readout1_.ptr, readout2_w1_.ptr, readout2_w2_.ptr, node_energies_.ptr + t0,
+                    H2_adj_.ptr + static_cast<std::size_t>(t0) * C, energy_slots_.ptr);
             launches_ += 1;
             span_end();
             // reverse
             span_begin("gemm_h2_reverse");
-            launch_tc({{H2_adj_.ptr + static_cast<std::size_t>(t0) * C, flat_rows, &s_h2_m1_, true, M1_adj_.ptr, flat_rows, 0, T, false, nullptr}});
+            {
+                std::vector<TcCall> calls{{H2_adj_.ptr + static_cast<std::size_t>(t0) * C, flat_rows, &s_h2_m1_, true, M1_adj_.ptr,
+                                           flat_rows, 0, T, false, nullptr}};
+                // one tile: the direct adjoint of the scalar block of M0, q + T_element H2_adj, is known here already;
+                // the reverse of the H1 linear adds to it later
+                if (!tiled)
+                    for_type_ranges(t0, T, [&](int a, int begin, int count) {
+                        calls.push_back({H2_adj_.ptr + static_cast<std::size_t>(begin) * C, flat_rows, &s_h2_skip_[active_types_[a]], true,
+                                         M0_adj_.ptr + (begin - t0) * rowH, scalar_rows, 0, count, false, readout1_.ptr});
+                    });
+                launch_tc(calls);
+            }
             span_end();
             span_begin("m1_reverse");
             if (model_.shape_id == 0)
@@ -907,6 +1017,25 @@ void Evaluator::run_pipeline(int phases)
             if (model_.shape_id == 0)
                 SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S0, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
                                        reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1, r1_pair_types_);
+            else if (model_.shape_id == 1 && C == 128 && l1_reverse_variant_ == 2) {
+                L1ReverseArgs args{first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, reinterpret_cast<const float4*>(r1_table_.ptr),
+                                   H1_.ptr, dPhi1_.ptr, H1_adj_.ptr, fo, density1, r1_pair_types_};
+                l1_reverse_dual_kernel_S1<128><<<T, 256, 0, stream_>>>(T, t0, args, coupling_);
+            } else if (model_.shape_id == 1 && C == 128 && l1_reverse_variant_ >= 3 && l1_reverse_variant_ <= 7) {
+                // timing ablations of the gradient kernel (results are wrong by construction): 3 = no source-adjoint
+                // atomics, 4 = every edge reads the first coefficient slab, 6 = no force reduction, 7 = all three
+#define SXB_ABLATE(BITS)                                                                                                  \
+                l1_reverse_kernel_S1<128, 3, BITS><<<T, 128, 0, stream_>>>(T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, \
+                    reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1, r1_pair_types_)
+                if (l1_reverse_variant_ == 3) SXB_ABLATE(1);
+                else if (l1_reverse_variant_ == 4) SXB_ABLATE(2);
+                else if (l1_reverse_variant_ == 6) SXB_ABLATE(4);
+                else if (l1_reverse_variant_ == 7) SXB_ABLATE(7);
+                else SXB_ABLATE(3);
+#undef SXB_ABLATE
+            } else if (model_.shape_id == 1 && C == 128 && l1_reverse_variant_ == 1)
+                l1_reverse_kernel_S1<128, 4><<<T, 128, 0, stream_>>>(T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
+                    reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1, r1_pair_types_);
             else if (model_.shape_id == 1)
                 SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S1, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
                                        reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1, r1_pair_types_);
@@ -944,16 +1073,21 @@ void Evaluator::run_pipeline(int phases)
                 std::vector<TcCall> calls;
                 for (int l = 0; l <= model_.hidden_l_max; ++l) {
                     const RowMap rows{static_cast<long>(NH) * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
-                    calls.push_back({H1_adj_.ptr + t0 * rowH, rows, &s_h1_[l], true, M0_adj_.ptr, rows, 0, T, false,
-                                     l == 0 ? readout1_.ptr : nullptr});
+                    if (tiled)
+                        calls.push_back({H1_adj_.ptr + t0 * rowH, rows, &s_h1_[l], true, M0_adj_.ptr, rows, 0, T, false,
+                                         l == 0 ? readout1_.ptr : nullptr});
+                    else   // the scalar block already holds the direct adjoint (written with the H2 reverse linear)
+                        calls.push_back({H1_adj_.ptr + t0 * rowH, rows, &s_h1_[l], true, M0_adj_.ptr, rows, 0, T, l == 0, nullptr});
                 }
                 launch_tc(calls);
-                calls.clear();
-                for_type_ranges(t0, T, [&](int a, int begin, int count) {
-                    calls.push_back({H2_adj_.ptr + static_cast<std::size_t>(begin) * C, flat_rows, &s_h2_skip_[active_types_[a]], true,
-                                     M0_adj_.ptr + (begin - t0) * rowH, scalar_rows, 0, count, true, nullptr});
-                });
-                launch_tc(calls);
+                if (tiled) {
+                    calls.clear();
+                    for_type_ranges(t0, T, [&](int a, int begin, int count) {
+                        calls.push_back({H2_adj_.ptr + static_cast<std::size_t>(begin) * C, flat_rows, &s_h2_skip_[active_types_[a]], true,
+                                         M0_adj_.ptr + (begin - t0) * rowH, scalar_rows, 0, count, true, nullptr});
+                    });
+                    launch_tc(calls);
+                }
             }
             span_end();
             span_begin("m0_reverse");
@@ -992,10 +1126,10 @@ void Evaluator::run_pipeline(int phases)
             span_end();
         }
         span_begin("finalize");
-        finalize_kernel<<<1, 32, 0, stream_>>>(energy_slots_.ptr, virial_slots_.ptr, totals_.ptr);
-        unpermute_doubles_kernel<<<blocks_for(ALL, 256), 256, 0, stream_>>>(ALL, 3, original_.ptr, forces_.ptr, forces_out_.ptr);
-        unpermute_doubles_kernel<<<blocks_for(R, 256), 256, 0, stream_>>>(R, 1, original_.ptr, node_energies_.ptr, node_energies_out_.ptr);
-        launches_ += 3;
+        publish_results_kernel<<<blocks_for(11 + static_cast<long>(R) + 3 * static_cast<long>(ALL), 256), 256, 0, stream_>>>(
+            R, ALL, internal_of_.ptr, energy_slots_.ptr, virial_slots_.ptr, node_energies_.ptr, forces_.ptr, error_flag_.ptr, totals_.ptr,
+            node_energies_out_.ptr, forces_out_.ptr, host_results_);
+        launches_ += 1;
         span_end();
     }
     SXB_CUDA(cudaGetLastError());
@@ -1005,13 +1139,16 @@ void Evaluator::run_pipeline(int phases)
 // Outside profiling the sequence is captured once per (phases, graph generation, position buffer)
 // into a CUDA graph and replayed afterwards: every kernel argument is fixed for a prepared graph, so
 // a step costs one graph launch instead of some twenty kernel launches.
-void Evaluator::enqueue_phases(int phases, const double* positions)
+void Evaluator::enqueue_phases(int phases, const double* positions, bool upload_staged)
 {
     auto enqueue = [&] {
+        if (upload_staged)
+            SXB_CUDA(cudaMemcpyAsync(positions_.ptr, host_stage_, sizeof(double) * 3 * num_nodes_, cudaMemcpyHostToDevice, stream_));
         if (positions != nullptr) {
             SXB_CUDA(cudaMemsetAsync(error_flag_.ptr, 0, sizeof(int), stream_));
             geometry_from_positions_kernel<<<blocks_for(static_cast<long>(num_receivers_) * 32, 256), 256, 0, stream_>>>(
-                num_receivers_, first_.ptr, sources_.ptr, shifts_.ptr, positions, original_.ptr, cell_.ptr, geom_.ptr, error_flag_.ptr);
+                num_receivers_, first_.ptr, sources_.ptr, has_shifts_ ? shifts_.ptr : nullptr, positions, original_.ptr, cell_.ptr,
+                geom_.ptr, error_flag_.ptr);
             launches_ += 1;
         }
         run_pipeline(phases);
@@ -1021,7 +1158,8 @@ void Evaluator::enqueue_phases(int phases, const double* positions)
         return;
     }
     StepGraph& slot = step_graphs_[phases];
-    if (slot.exec == nullptr || slot.generation != generation_ || slot.positions != positions || slot.keep_edge_forces != keep_edge_forces_) {
+    if (slot.exec == nullptr || slot.generation != generation_ || slot.positions != positions || slot.upload_staged != upload_staged
+        || slot.keep_edge_forces != keep_edge_forces_) {
         if (slot.exec != nullptr) {
             cudaGraphExecDestroy(slot.exec);
             slot.exec = nullptr;
@@ -1056,6 +1194,7 @@ void Evaluator::enqueue_phases(int phases, const double* positions)
         }
         slot.generation = generation_;
         slot.positions = positions;
+        slot.upload_staged = upload_staged;
         slot.keep_edge_forces = keep_edge_forces_;
     }
     SXB_CUDA(cudaGraphLaunch(slot.exec, stream_));
@@ -1073,25 +1212,18 @@ void Evaluator::finish_compute()
 {
     SXB_CUDA(cudaEventRecord(event_end_, stream_));
     int flag = 0;
-    SXB_CUDA(cudaMemcpyAsync(&flag, error_flag_.ptr, sizeof(int), cudaMemcpyDeviceToHost, stream_));
-    SXB_CUDA(cudaMemcpyAsync(host_totals_, totals_.ptr, 10 * sizeof(double), cudaMemcpyDeviceToHost, stream_));
-    mirror_valid_ = false;
-    constexpr std::size_t kMirrorLimit = 4u << 20;   // doubles (32 MB): beyond this the getters copy on demand
-    const std::size_t mirror_doubles = static_cast<std::size_t>(num_receivers_) + 3 * static_cast<std::size_t>(num_nodes_);
-    if (mirror_requested_ && mirror_doubles <= kMirrorLimit) {
-        if (host_mirror_capacity_ < mirror_doubles) {
-            if (host_mirror_) SXB_CUDA(cudaFreeHost(host_mirror_));
-            host_mirror_ = nullptr;
-            host_mirror_capacity_ = 0;
-            SXB_CUDA(cudaMallocHost(reinterpret_cast<void**>(&host_mirror_), sizeof(double) * mirror_doubles));
-            host_mirror_capacity_ = mirror_doubles;
-        }
-        SXB_CUDA(cudaMemcpyAsync(host_mirror_, node_energies_out_.ptr, sizeof(double) * num_receivers_, cudaMemcpyDeviceToHost, stream_));
-        SXB_CUDA(cudaMemcpyAsync(host_mirror_ + num_receivers_, forces_out_.ptr, sizeof(double) * 3 * num_nodes_, cudaMemcpyDeviceToHost, stream_));
+    if (host_results_ != nullptr) {
+        // the closing kernel has published status, totals, energies and forces into mapped host memory
+        SXB_CUDA(cudaStreamSynchronize(stream_));
+        flag = static_cast<int>(host_results_[0]);
+        std::memcpy(host_totals_, host_results_ + 1, 10 * sizeof(double));
         mirror_valid_ = true;
+    } else {
+        SXB_CUDA(cudaMemcpyAsync(&flag, error_flag_.ptr, sizeof(int), cudaMemcpyDeviceToHost, stream_));
+        SXB_CUDA(cudaMemcpyAsync(host_totals_, totals_.ptr, 10 * sizeof(double), cudaMemcpyDeviceToHost, stream_));
+        SXB_CUDA(cudaStreamSynchronize(stream_));
+        mirror_valid_ = false;
     }
-    mirror_requested_ = false;
-    SXB_CUDA(cudaStreamSynchronize(stream_));
     SXB_CUDA(cudaEventElapsedTime(&last_ms_, event_begin_, event_end_));
     profile_.clear();
     for (const auto& span : spans_) {
@@ -1107,18 +1239,20 @@ void Evaluator::finish_compute()
 void Evaluator::compute_positions(std::uint64_t generation, const double* positions, bool on_device)
 {
     check_generation(generation);
-    if (!has_shifts_) throw std::invalid_argument("The prepared graph has no periodic shifts; use edge vectors.");
     SXB_CUDA(cudaSetDevice(device_));
     have_results_ = false;
     mirror_valid_ = false;
     SXB_CUDA(cudaEventRecord(event_begin_, stream_));
-    const double* dpos = positions;
-    mirror_requested_ = !on_device;
-    if (!on_device) {
+    if (on_device) {
+        enqueue_phases(7, positions, false);
+    } else if (host_stage_ != nullptr) {
+        // through the pinned staging copy: the upload is then a copy node of the captured step
+        std::memcpy(host_stage_, positions, sizeof(double) * 3 * num_nodes_);
+        enqueue_phases(7, positions_.ptr, true);
+    } else {
         SXB_CUDA(cudaMemcpyAsync(positions_.ptr, positions, sizeof(double) * 3 * num_nodes_, cudaMemcpyHostToDevice, stream_));
-        dpos = positions_.ptr;
+        enqueue_phases(7, positions_.ptr, false);
     }
-    enqueue_phases(7, dpos);
     finish_compute();
 }
 
@@ -1135,7 +1269,7 @@ void Evaluator::compute_edge_vectors(std::uint64_t generation, const double* xyz
     SXB_CUDA(cudaMemsetAsync(error_flag_.ptr, 0, sizeof(int), stream_));
     geometry_from_vectors_kernel<<<blocks_for(num_edges_, 256), 256, 0, stream_>>>(num_edges_, dxyz.ptr, edge_map_.ptr, geom_.ptr, error_flag_.ptr);
     launches_ += 1;
-    enqueue_phases(7, nullptr);
+    enqueue_phases(7, nullptr, false);
     finish_compute();
 }
 
@@ -1144,7 +1278,6 @@ void Evaluator::compute_edge_vectors(std::uint64_t generation, const double* xyz
 void Evaluator::distributed_begin(std::uint64_t generation, const double* device_positions)
 {
     check_generation(generation);
-    if (!has_shifts_) throw std::invalid_argument("The prepared graph has no periodic shifts; use edge vectors.");
     if (phase_ != 0) {
         phase_ = 0;
         throw std::logic_error("distributed evaluation: begin called while another evaluation is open.");
@@ -1153,7 +1286,30 @@ void Evaluator::distributed_begin(std::uint64_t generation, const double* device
     have_results_ = false;
     mirror_valid_ = false;
     SXB_CUDA(cudaEventRecord(event_begin_, stream_));
-    enqueue_phases(1, device_positions);
+    enqueue_phases(1, device_positions, false);
+    phase_ = 1;
+}
+
+// The same first phase from caller-held edge vectors (device f64[3*num_edges], caller edge order), as
+// the pair style passes them (begin_factorized_distributed_evaluation(..., xyz, r, generation),
+// libsymmetrix/source/mace_kokkos.hpp:672-677; call site pair_symmetrix_mace_kokkos.cpp:1532-1568).
+void Evaluator::distributed_begin_edge_vectors(std::uint64_t generation, const double* device_xyz)
+{
+    check_generation(generation);
+    if (phase_ != 0) {
+        phase_ = 0;
+        throw std::logic_error("distributed evaluation: begin called while another evaluation is open.");
+    }
+    SXB_CUDA(cudaSetDevice(device_));
+    have_results_ = false;
+    mirror_valid_ = false;
+    SXB_CUDA(cudaEventRecord(event_begin_, stream_));
+    SXB_CUDA(cudaMemsetAsync(error_flag_.ptr, 0, sizeof(int), stream_));
+    if (num_edges_ > 0)
+        geometry_from_vectors_kernel<<<blocks_for(num_edges_, 256), 256, 0, stream_>>>(num_edges_, device_xyz, edge_map_.ptr, geom_.ptr,
+                                                                                      error_flag_.ptr);
+    launches_ += 1;
+    enqueue_phases(1, nullptr, false);
     phase_ = 1;
 }
 
@@ -1164,7 +1320,7 @@ void Evaluator::distributed_continue()
         throw std::logic_error("distributed evaluation: continue must follow begin.");
     }
     SXB_CUDA(cudaSetDevice(device_));
-    enqueue_phases(2, nullptr);
+    enqueue_phases(2, nullptr, false);
     phase_ = 2;
 }
 
@@ -1176,7 +1332,7 @@ void Evaluator::distributed_finish()
     }
     SXB_CUDA(cudaSetDevice(device_));
     phase_ = 0;
-    enqueue_phases(4, nullptr);
+    enqueue_phases(4, nullptr, false);
     // no host synchronisation here: the caller still has ghost forces to exchange on this stream;
     // synchronize() fetches the totals and checks the device status word
     SXB_CUDA(cudaEventRecord(event_end_, stream_));
@@ -1187,25 +1343,27 @@ void Evaluator::distributed_finish()
 namespace {
 // rows of a node tensor (row_floats per node) gathered into / scattered from a dense buffer;
 // indices are caller-order node numbers
-__global__ void pack_rows_kernel(long count, int row_floats, const int* __restrict__ indices, const int* __restrict__ internal_of,
-                                 const float* __restrict__ tensor, float* __restrict__ out)
+// (indices == nullptr: the caller-order rows first_row .. first_row + count - 1)
+__global__ void pack_rows_kernel(long count, int row_floats, const int* __restrict__ indices, long first_row,
+                                 const int* __restrict__ internal_of, const float* __restrict__ tensor, float* __restrict__ out)
 {
     const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
     const int vec = row_floats >> 2;
     if (idx >= count * vec) return;
     const long r = idx / vec, q = idx % vec;
-    const long node = internal_of[indices[r]];
+    const long node = internal_of[indices != nullptr ? indices[r] : first_row + r];
     reinterpret_cast<float4*>(out)[idx] = reinterpret_cast<const float4*>(tensor + node * row_floats)[q];
 }
 
-__global__ void unpack_rows_kernel(long count, int row_floats, const int* __restrict__ indices, const int* __restrict__ internal_of,
-                                   const float* __restrict__ in, float* __restrict__ tensor, int accumulate)
+__global__ void unpack_rows_kernel(long count, int row_floats, const int* __restrict__ indices, long first_row,
+                                   const int* __restrict__ internal_of, const float* __restrict__ in, float* __restrict__ tensor,
+                                   int accumulate)
 {
     const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
     const int vec = row_floats >> 2;
     if (idx >= count * vec) return;
     const long r = idx / vec, q = idx % vec;
-    const long node = internal_of[indices[r]];
+    const long node = internal_of[indices != nullptr ? indices[r] : first_row + r];
     const float4 v = reinterpret_cast<const float4*>(in)[idx];
     float* dst = tensor + node * row_floats + 4 * q;
     if (accumulate) {
@@ -1299,7 +1457,7 @@ void Evaluator::pack_rows(int which, const int* device_indices, long count, floa
 {
     const int row = model_.num_hidden * model_.channels;
     if (count <= 0) return;
-    pack_rows_kernel<<<blocks_for(count * (row / 4), 256), 256, 0, stream_>>>(count, row, device_indices, internal_of_.ptr,
+    pack_rows_kernel<<<blocks_for(count * (row / 4), 256), 256, 0, stream_>>>(count, row, device_indices, 0, internal_of_.ptr,
                                                                               halo_tensor(which), device_out);
     launches_ += 1;
     SXB_CUDA(cudaGetLastError());
@@ -1309,10 +1467,47 @@ void Evaluator::unpack_rows(int which, const int* device_indices, long count, co
 {
     const int row = model_.num_hidden * model_.channels;
     if (count <= 0) return;
-    unpack_rows_kernel<<<blocks_for(count * (row / 4), 256), 256, 0, stream_>>>(count, row, device_indices, internal_of_.ptr, device_in,
-                                                                                halo_tensor(which), accumulate ? 1 : 0);
+    unpack_rows_kernel<<<blocks_for(count * (row / 4), 256), 256, 0, stream_>>>(count, row, device_indices, 0, internal_of_.ptr,
+                                                                                device_in, halo_tensor(which), accumulate ? 1 : 0);
     launches_ += 1;
     SXB_CUDA(cudaGetLastError());
+}
+
+// Host-side access to a range of caller-order rows of H1 / H1_adj, for callers whose halo exchange
+// runs through host buffers (a plain LAMMPS pair style's pack / unpack_forward_comm callbacks).
+void Evaluator::get_halo_rows(int which, long first_row, long count, float* host_out)
+{
+    const int row = model_.num_hidden * model_.channels;
+    if (first_row < 0 || count < 0 || first_row + count > num_nodes_) throw std::invalid_argument("Halo row range is out of bounds.");
+    if (count == 0) return;
+    halo_stage_.reserve_with_slack(static_cast<std::size_t>(count) * row);
+    pack_rows_kernel<<<blocks_for(count * (row / 4), 256), 256, 0, stream_>>>(count, row, nullptr, first_row, internal_of_.ptr,
+                                                                              halo_tensor(which), halo_stage_.ptr);
+    launches_ += 1;
+    SXB_CUDA(cudaMemcpyAsync(host_out, halo_stage_.ptr, sizeof(float) * count * row, cudaMemcpyDeviceToHost, stream_));
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+}
+
+void Evaluator::put_halo_rows(int which, long first_row, long count, const float* host_in, bool accumulate)
+{
+    const int row = model_.num_hidden * model_.channels;
+    if (first_row < 0 || count < 0 || first_row + count > num_nodes_) throw std::invalid_argument("Halo row range is out of bounds.");
+    if (count == 0) return;
+    halo_stage_.reserve_with_slack(static_cast<std::size_t>(count) * row);
+    SXB_CUDA(cudaMemcpyAsync(halo_stage_.ptr, host_in, sizeof(float) * count * row, cudaMemcpyHostToDevice, stream_));
+    unpack_rows_kernel<<<blocks_for(count * (row / 4), 256), 256, 0, stream_>>>(count, row, nullptr, first_row, internal_of_.ptr,
+                                                                                halo_stage_.ptr, halo_tensor(which), accumulate ? 1 : 0);
+    launches_ += 1;
+    SXB_CUDA(cudaStreamSynchronize(stream_));      // host_in may be reused by the caller right away
+}
+
+// First phase from host positions (f64[3*num_nodes], owned atoms first, ghosts after).
+void Evaluator::distributed_begin_host(std::uint64_t generation, const double* host_positions)
+{
+    check_generation(generation);
+    SXB_CUDA(cudaSetDevice(device_));
+    SXB_CUDA(cudaMemcpyAsync(positions_.ptr, host_positions, sizeof(double) * 3 * num_nodes_, cudaMemcpyHostToDevice, stream_));
+    distributed_begin(generation, positions_.ptr);
 }
 
 void Evaluator::add_force_rows(const int* device_indices, long count, const double* device_in)
@@ -1373,8 +1568,8 @@ void Evaluator::synchronize()
     if (pending_finish_) {
         pending_finish_ = false;
         have_results_ = false;
-        mirror_valid_ = false;
         finish_compute();
+        mirror_valid_ = false;      // the published forces predate the ghost forces the caller has added since
         return;
     }
     SXB_CUDA(cudaStreamSynchronize(stream_));
@@ -1389,7 +1584,7 @@ void Evaluator::get_node_energies(double* out)
 {
     require_results();
     if (mirror_valid_) {
-        std::memcpy(out, host_mirror_, sizeof(double) * num_receivers_);
+        std::memcpy(out, host_results_ + 11, sizeof(double) * num_receivers_);
         return;
     }
     SXB_CUDA(cudaMemcpyAsync(out, node_energies_out_.ptr, sizeof(double) * num_receivers_, cudaMemcpyDeviceToHost, stream_));
@@ -1400,7 +1595,7 @@ void Evaluator::get_atom_forces(double* out)
 {
     require_results();
     if (mirror_valid_) {
-        std::memcpy(out, host_mirror_ + num_receivers_, sizeof(double) * 3 * num_nodes_);
+        std::memcpy(out, host_results_ + 11 + num_receivers_, sizeof(double) * 3 * num_nodes_);
         return;
     }
     SXB_CUDA(cudaMemcpyAsync(out, forces_out_.ptr, sizeof(double) * 3 * num_nodes_, cudaMemcpyDeviceToHost, stream_));

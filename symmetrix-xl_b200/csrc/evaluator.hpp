@@ -40,6 +40,8 @@ public:
                                                           int num_receivers = -1);
     std::uint64_t prepare_graph(int num_nodes, const int* node_types, const int* num_neigh, const int* neigh_indices,
                                 const int* shifts, const double* cell);
+    std::uint64_t prepare_graph_csr(int num_receivers, int num_nodes, const int* node_types, const int* num_neigh,
+                                    const int* neigh_indices, bool on_device);
     void get_graph(std::uint64_t generation, int* first, int* sources, int* shifts);
     void check_generation(std::uint64_t generation) const;
 
@@ -47,11 +49,15 @@ public:
     void compute_edge_vectors(std::uint64_t generation, const double* xyz);
     void synchronize();
     void distributed_begin(std::uint64_t generation, const double* device_positions);
+    void distributed_begin_edge_vectors(std::uint64_t generation, const double* device_xyz);
     void distributed_continue();
     void distributed_finish();
     void pack_rows(int which, const int* device_indices, long count, float* device_out);
     void unpack_rows(int which, const int* device_indices, long count, const float* device_in, bool accumulate);
     void add_force_rows(const int* device_indices, long count, const double* device_in);
+    void get_halo_rows(int which, long first_row, long count, float* host_out);
+    void put_halo_rows(int which, long first_row, long count, const float* host_in, bool accumulate);
+    void distributed_begin_host(std::uint64_t generation, const double* host_positions);
     void gather_position_rows(const double* device_rows, const int* device_indices, long count, const double* device_offsets,
                               double* device_out);
     void pack_ghost_forces(int world, const int* device_ghost_begin, long num_ghosts, double* device_out);
@@ -88,18 +94,20 @@ private:
     void prepare_active_types(const std::vector<int>& node_types);
     void install_graph(int num_receivers, int num_nodes, const std::vector<int>& node_types, long num_edges, bool has_shifts);
     void run_pipeline(int phases);
-    void enqueue_phases(int phases, const double* positions);
+    void enqueue_phases(int phases, const double* positions, bool upload_staged);
     void drop_step_graphs();
     // one captured step per phase mask (7: whole evaluation; 1, 2, 4: the distributed phases)
     struct StepGraph {
         cudaGraphExec_t exec = nullptr;
         std::uint64_t generation = 0;
         const double* positions = nullptr;
+        bool upload_staged = false;
         bool keep_edge_forces = false;
         long launches = 0;
     };
     std::map<int, StepGraph> step_graphs_;
     bool use_graphs_ = true;
+    int l1_reverse_variant_ = 0;   // 0: one thread per channel; 1: the same at 128 registers; 2: two threads per channel
     void finish_compute();
     void launch_gemm(const float* A, const RowMap& a_rows, const float* B, int ldb, bool b_transposed, float* C,
                      const RowMap& c_rows, int first_node, int num_nodes, int N, int K, bool accumulate, const float* bias);
@@ -165,14 +173,16 @@ private:
     DeviceBuffer<float> A0_, A0_adj_, M0_, M0_adj_, H1_, H1_adj_, Phi1_, dPhi1_, A1_, A1_adj_, M1_, M1_adj_, H2_, H2_adj_;
     DeviceBuffer<double> node_energies_, node_energies_out_, forces_, forces_out_, edge_forces_;
     DeviceBuffer<double> totals_, energy_slots_, virial_slots_;
+    DeviceBuffer<float> halo_stage_;         // rows of H1 / H1_adj on their way to or from host buffers
     DeviceBuffer<double> edge_scratch_;      // [E][3]: caller edge vectors on the way in, un-permuted edge forces on the way out
     DeviceBuffer<int> error_flag_;
     double host_totals_[10] = {0};
     // pinned host mirror of the per-node results, filled by calls that take host inputs so that the
     // result getters cost a host copy instead of a device copy and a synchronisation each
-    double* host_mirror_ = nullptr;          // [receivers] energies, then [nodes][3] forces
-    std::size_t host_mirror_capacity_ = 0;   // doubles
-    bool mirror_requested_ = false, mirror_valid_ = false;
+    double* host_results_ = nullptr;         // mapped: [status, totals[10], energies[receivers], forces[nodes][3]]
+    double* host_stage_ = nullptr;           // pinned staging copy of the caller's positions
+    std::size_t host_results_capacity_ = 0;  // doubles
+    bool mirror_valid_ = false;
     bool keep_edge_forces_ = false;
     bool have_results_ = false;
     long launches_ = 0;

@@ -28,8 +28,52 @@ def _load_pkg():
 # (name, edge l_max, hidden L_max, number of path sets of the split layer-1 kernels, optional explicit sets)
 # S2: set 0 = all paths with source l = 0 or 1 (88 rows, 4 source components), sets 1 and 2 share the
 # source l = 2 paths (80 and 75 rows, 5 source components each)
-SHAPES = [("S0", 3, 0, 1, None), ("S1", 3, 1, 1, None),
+# S1: two sets by the parity of the edge l (odd: 49 rows, even: 39 rows) for the kernel that gives each
+# channel two threads; a set then needs only its own edge harmonics and harmonic gradients
+SHAPES = [("S0", 3, 0, 1, None), ("S1", 3, 1, 2, [[1, 2, 6, 7, 8], [0, 3, 4, 5, 9]]),
           ("S2", 3, 2, 3, [[0, 3, 8, 13, 1, 4, 5, 9, 10, 14], [7, 2, 6, 11], [16, 12, 15]])]
+
+
+def reverse_path_lines(p, q, l, l1, l2, base):
+    """Straight-line gradient code of one path for one (edge, channel): q = index of the path's radial
+    function in R[] / dR[], base = first row adjoint of the path in adj[].  With w_a = sum_b h_b adj_ab and
+    s_b = sum_a y_a adj_ab the path contributes
+      ang_a += R w_a   (angular part of the force),   hadj_b += R s_b   (source adjoint),
+      radial += dR * sum_a y_a w_a,   and   sum_a y_a w_a = sum_b h_b s_b.
+    The radial sum runs over the shorter index set, and R is folded into that set's vector first, so
+    that the other contraction accumulates straight into its target."""
+    n1, n2 = 2 * l1 + 1, 2 * l2 + 1
+    out = [f"    {{ /* path {p}: edge l={l1}, source l={l2} -> l={l} */"]
+    out.append("      float yw = 0.0f;")
+    if n2 < n1:
+        for b in range(n2):
+            out.append(f"      const float rh{b} = R[{q}] * h[{l2 * l2 + b}];")
+        for a in range(n1):
+            for b in range(n2):
+                out.append(f"      ang[{l1 * l1 + a}] = fmaf(rh{b}, adj[{base + a * n2 + b}], ang[{l1 * l1 + a}]);")
+        for b in range(n2):
+            terms_ = [(f"y[{l1 * l1 + a}]", f"adj[{base + a * n2 + b}]") for a in range(n1)]
+            expr = f"{terms_[0][0]} * {terms_[0][1]}"
+            for yy, aa in terms_[1:]:
+                expr = f"fmaf({yy}, {aa}, {expr})"
+            out.append(f"      {{ const float s_ = {expr};")
+            out.append(f"        hadj[{l2 * l2 + b}] = fmaf(R[{q}], s_, hadj[{l2 * l2 + b}]); yw = fmaf(h[{l2 * l2 + b}], s_, yw); }}")
+    else:
+        for a in range(n1):
+            out.append(f"      const float ry{a} = R[{q}] * y[{l1 * l1 + a}];")
+        for a in range(n1):
+            terms_ = [(f"h[{l2 * l2 + b}]", f"adj[{base + a * n2 + b}]") for b in range(n2)]
+            expr = f"{terms_[0][0]} * {terms_[0][1]}"
+            for hh, aa in terms_[1:]:
+                expr = f"fmaf({hh}, {aa}, {expr})"
+            out.append(f"      {{ const float w = {expr};")
+            out.append(f"        ang[{l1 * l1 + a}] = fmaf(R[{q}], w, ang[{l1 * l1 + a}]); yw = fmaf(y[{l1 * l1 + a}], w, yw); }}")
+        for b in range(n2):
+            for a in range(n1):
+                out.append(f"      hadj[{l2 * l2 + b}] = fmaf(ry{a}, adj[{base + a * n2 + b}], hadj[{l2 * l2 + b}]);")
+    out.append(f"      radial = fmaf(dR[{q}], yw, radial);")
+    out.append("    }")
+    return out
 
 
 def emit_shape(name, l_max, L_max, tables, groups=1, by_edge_l=None):
@@ -108,24 +152,7 @@ def emit_shape(name, l_max, L_max, tables, groups=1, by_edge_l=None):
                 row = row_begin[p] + a * n2 + b
                 fwd.append(f"      acc[{row}] = fmaf(t{b}, y[{l1 * l1 + a}], acc[{row}]);")
         fwd.append("    }")
-        rev.append(f"    {{ /* path {p}: edge l={l1}, source l={l2} -> l={l} */")
-        rev.append("      float yw = 0.0f;")
-        for a in range(n1):
-            terms_ = [f"h[{l2 * l2 + b}] * adj[{row_begin[p] + a * n2 + b}]" for b in range(n2)]
-            expr = terms_[0]
-            for t_ in terms_[1:]:
-                hh, aa = t_.split(" * ")
-                expr = f"fmaf({hh}, {aa}, {expr})"
-            rev.append(f"      {{ const float w = {expr};")
-            rev.append(f"        ang[{l1 * l1 + a}] = fmaf(R[{p}], w, ang[{l1 * l1 + a}]); yw = fmaf(y[{l1 * l1 + a}], w, yw); }}")
-        rev.append(f"      radial = fmaf(dR[{p}], yw, radial);")
-        for b in range(n2):
-            terms_ = [(f"y[{l1 * l1 + a}]", f"adj[{row_begin[p] + a * n2 + b}]") for a in range(n1)]
-            expr = f"{terms_[0][0]} * {terms_[0][1]}"
-            for yy, aa in terms_[1:]:
-                expr = f"fmaf({yy}, {aa}, {expr})"
-            rev.append(f"      hadj[{l2 * l2 + b}] = fmaf(R[{p}], {expr}, hadj[{l2 * l2 + b}]);")
-        rev.append("    }")
+        rev.extend(reverse_path_lines(p, p, l, l1, l2, row_begin[p]))
     out.append(f"#define SXB_{name}_L1_FORWARD_BODY \\")
     out.append(" \\\n".join(fwd))
     out.append(f"#define SXB_{name}_L1_REVERSE_BODY \\")
@@ -203,24 +230,7 @@ def emit_path_groups(name, paths, row_begin, tables, groups, by_edge_l=None):
                     row = base + a * n2 + b
                     fwd.append(f"      acc[{row}] = fmaf(t{b}, y[{l1 * l1 + a}], acc[{row}]);")
             fwd.append("    }")
-            rev.append(f"    {{ /* path {p}: edge l={l1}, source l={l2} -> l={l} */")
-            rev.append("      float yw = 0.0f;")
-            for a in range(n1):
-                terms_ = [f"h[{l2 * l2 + b}] * adj[{base + a * n2 + b}]" for b in range(n2)]
-                expr = terms_[0]
-                for t_ in terms_[1:]:
-                    hh, aa = t_.split(" * ")
-                    expr = f"fmaf({hh}, {aa}, {expr})"
-                rev.append(f"      {{ const float w = {expr};")
-                rev.append(f"        ang[{l1 * l1 + a}] = fmaf(R[{q}], w, ang[{l1 * l1 + a}]); yw = fmaf(y[{l1 * l1 + a}], w, yw); }}")
-            rev.append(f"      radial = fmaf(dR[{q}], yw, radial);")
-            for b in range(n2):
-                terms_ = [(f"y[{l1 * l1 + a}]", f"adj[{base + a * n2 + b}]") for a in range(n1)]
-                expr = f"{terms_[0][0]} * {terms_[0][1]}"
-                for yy, aa in terms_[1:]:
-                    expr = f"fmaf({yy}, {aa}, {expr})"
-                rev.append(f"      hadj[{l2 * l2 + b}] = fmaf(R[{q}], {expr}, hadj[{l2 * l2 + b}]);")
-            rev.append("    }")
+            rev.extend(reverse_path_lines(p, q, l, l1, l2, base))
         out.append(f"#define {pre}_FORWARD_BODY \\")
         out.append(" \\\n".join(fwd))
         out.append(f"#define {pre}_REVERSE_BODY \\")

@@ -382,16 +382,116 @@ readout_kernel(int num_nodes, int C, int hidden, float act_scale, const float* _
     }
 }
 
-__global__ void finalize_kernel(const double* __restrict__ energy_slots, const double* __restrict__ virial_slots,
-                                double* __restrict__ totals /* [0]=energy, [1..9]=virial sum f (x) xyz */)
+// The same readout for the common head shape (16 hidden units, C a multiple of 32, at most 256): the 16
+// pre-activations of a node are formed together, each lane holding its channels' partial sums, and
+// summed over the warp by a butterfly that halves the number of live values at every step (16 shuffles
+// instead of 80); lane L ends up with hidden unit L / 2.  No per-thread array is indexed at run time.
+template <int kChunks>   // C / 32
+__global__ void __launch_bounds__(256)
+readout16_kernel(int num_nodes, float act_scale, const float* __restrict__ M0, int num_hidden_lm,
+                 const float* __restrict__ H2, const unsigned char* __restrict__ element,
+                 const double* __restrict__ atomic_energies, const float* __restrict__ q,
+                 const float* __restrict__ W1 /*[16][C]*/, const float* __restrict__ W2 /*[16]*/,
+                 double* __restrict__ node_energies, float* __restrict__ H2_adj, double* __restrict__ energy_slots)
 {
-    const int t = threadIdx.x;
-    if (t < 10) {
-        double s = 0.0;
-        for (int slot = 0; slot < kVirialSlots; ++slot)
-            s += (t == 0) ? energy_slots[slot] : virial_slots[slot * 9 + (t - 1)];
-        totals[t] = s;
+    constexpr int C = 32 * kChunks, kHidden = 16;
+    const int node = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (node >= num_nodes) return;
+    const float* xs = M0 + static_cast<size_t>(node) * num_hidden_lm * C;   // scalar block of M0
+    const float* h2 = H2 + static_cast<size_t>(node) * C;
+    float hv[kChunks];
+    float e1 = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kChunks; ++j) {
+        hv[j] = h2[lane + 32 * j];
+        e1 = fmaf(q[lane + 32 * j], xs[lane + 32 * j], e1);
     }
+    float v[kHidden];
+#pragma unroll
+    for (int h = 0; h < kHidden; ++h) {
+        float z = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kChunks; ++j) z = fmaf(W1[h * C + lane + 32 * j], hv[j], z);
+        v[h] = z;
+    }
+#pragma unroll
+    for (int offset = 16, live = kHidden; offset >= 2; offset >>= 1, live >>= 1) {
+        const bool upper = (lane & offset) != 0;
+        const int half = live / 2;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (i < half) {
+                const float send = upper ? v[i] : v[i + half];
+                const float recv = __shfl_xor_sync(0xffffffffu, send, offset);
+                v[i] = (upper ? v[i + half] : v[i]) + recv;
+            }
+        }
+    }
+    const float z = v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);      // lanes 2h and 2h+1: hidden unit h
+    const int unit = lane >> 1;
+    const float sig = 1.0f / (1.0f + expf(-z));
+    const float w2 = W2[unit];
+    float e2 = (lane & 1) ? 0.0f : w2 * (act_scale * z * sig);
+    const float coeff = w2 * (act_scale * sig + act_scale * z * sig * (1.0f - sig));
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        e1 += __shfl_xor_sync(0xffffffffu, e1, offset);
+        e2 += __shfl_xor_sync(0xffffffffu, e2, offset);
+    }
+    float g[kChunks];
+#pragma unroll
+    for (int j = 0; j < kChunks; ++j) g[j] = 0.0f;
+#pragma unroll
+    for (int h = 0; h < kHidden; ++h) {
+        const float c = __shfl_sync(0xffffffffu, coeff, 2 * h);
+#pragma unroll
+        for (int j = 0; j < kChunks; ++j) g[j] = fmaf(c, W1[h * C + lane + 32 * j], g[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < kChunks; ++j) H2_adj[static_cast<size_t>(node) * C + lane + 32 * j] = g[j];
+    if (lane == 0) {
+        const double e = atomic_energies[element[node]] + static_cast<double>(e1) + static_cast<double>(e2);
+        node_energies[node] = e;
+        atomicAdd(energy_slots + (node % kVirialSlots), e);
+    }
+}
+
+// Closing kernel of an evaluation, one thread per output value: sums the energy / virial slots into
+// totals[10] and writes node energies and node forces in the caller's node order.  When `host` is
+// given the same values are also published straight into mapped pinned host memory, laid out
+// [status word, totals[10], energies[num_receivers], forces[num_nodes][3]] (consecutive threads write
+// consecutive words, so the writes cross the bus in full segments), and the caller needs no
+// device-to-host copy.
+__global__ void publish_results_kernel(int num_receivers, int num_nodes, const int* __restrict__ internal_of,
+                                       const double* __restrict__ energy_slots, const double* __restrict__ virial_slots,
+                                       const double* __restrict__ node_energies, const double* __restrict__ forces,
+                                       const int* __restrict__ status, double* __restrict__ totals,
+                                       double* __restrict__ energies_out, double* __restrict__ forces_out,
+                                       double* __restrict__ host)
+{
+    const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long total = 11 + static_cast<long>(num_receivers) + 3 * static_cast<long>(num_nodes);
+    if (idx >= total) return;
+    double value;
+    if (idx == 0) {
+        value = static_cast<double>(status[0]);
+    } else if (idx < 11) {
+        const int t = static_cast<int>(idx) - 1;
+        value = 0.0;
+        for (int slot = 0; slot < kVirialSlots; ++slot) value += (t == 0) ? energy_slots[slot] : virial_slots[slot * 9 + (t - 1)];
+        totals[t] = value;
+    } else if (idx < 11 + num_receivers) {
+        const long o = idx - 11;
+        value = node_energies[internal_of[o]];
+        energies_out[o] = value;
+    } else {
+        const long j = idx - 11 - num_receivers;
+        const long o = j / 3, q = j % 3;
+        value = forces[3 * static_cast<long>(internal_of[o]) + q];
+        forces_out[j] = value;
+    }
+    if (host != nullptr) host[idx] = value;
 }
 
 }  // namespace sxb

@@ -43,6 +43,7 @@ SIGNATURES = {
     "sxb_measure_device_peaks": (ctypes.c_int, [ctypes.c_int32, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]),
     "sxb_destroy": (None, [_P]),
     "sxb_last_error": (ctypes.c_char_p, []),
+    "sxb_device_count": (ctypes.c_int, []),
     "sxb_model_info_get": (ctypes.c_int, [_P, ctypes.POINTER(ModelInfo)]),
     "sxb_atomic_numbers": (ctypes.c_int, [_P, _P, ctypes.c_int32]),
     "sxb_prepare_periodic_graph": (ctypes.c_int, [_P, ctypes.c_int32, _P, _P, _P, _P, ctypes.c_double,
@@ -69,6 +70,12 @@ SIGNATURES = {
     "sxb_prepare_local_graph": (ctypes.c_int, [_P, ctypes.c_int32, ctypes.c_int32, _P, _P, ctypes.c_double,
                                                ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_int64)]),
     "sxb_distributed_begin": (ctypes.c_int, [_P, ctypes.c_uint64, _P]),
+    "sxb_prepare_local_graph_csr": (ctypes.c_int, [_P, ctypes.c_int32, ctypes.c_int32, _P, _P, _P, ctypes.c_int32,
+                                                   ctypes.POINTER(ctypes.c_uint64)]),
+    "sxb_distributed_begin_edge_vectors": (ctypes.c_int, [_P, ctypes.c_uint64, _P]),
+    "sxb_distributed_begin_host": (ctypes.c_int, [_P, ctypes.c_uint64, _P]),
+    "sxb_halo_rows_get": (ctypes.c_int, [_P, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, _P]),
+    "sxb_halo_rows_put": (ctypes.c_int, [_P, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, _P, ctypes.c_int32]),
     "sxb_distributed_continue": (ctypes.c_int, [_P]),
     "sxb_distributed_finish": (ctypes.c_int, [_P]),
     "sxb_halo_pack": (ctypes.c_int, [_P, ctypes.c_int32, _P, ctypes.c_int64, _P]),
@@ -220,6 +227,46 @@ class MACEB200:
         self._num_nodes, self._num_edges, self._num_receivers = int(node_types.size), int(edges.value), int(num_receivers)
         return {"generation": int(gen.value), "num_edges": int(edges.value)}
 
+    def prepare_local_graph_csr(self, num_receivers, node_types, num_neigh, neigh_indices):
+        """Caller-built CSR over owned atoms (first ``num_receivers`` nodes) and ghosts, host arrays
+        (reference: prepare_factorized_graph_device, libsymmetrix/source/mace_kokkos.hpp:399-413)."""
+        node_types, num_neigh, neigh_indices = _i32(node_types), _i32(num_neigh), _i32(neigh_indices)
+        if num_neigh.size != int(num_receivers) or neigh_indices.size != int(num_neigh.sum()):
+            raise ValueError("Graph input extents are inconsistent.")
+        gen = ctypes.c_uint64()
+        _check(self._lib.sxb_prepare_local_graph_csr(self._h, int(num_receivers), node_types.size, node_types.ctypes.data,
+                                                     num_neigh.ctypes.data, neigh_indices.ctypes.data, 0, ctypes.byref(gen)))
+        self._num_nodes, self._num_edges, self._num_receivers = int(node_types.size), int(neigh_indices.size), int(num_receivers)
+        return int(gen.value)
+
+    def prepare_local_graph_csr_device(self, num_receivers, num_nodes, num_edges, node_types_ptr, num_neigh_ptr, neigh_indices_ptr):
+        """The same from device arrays (int32) on the evaluator's device."""
+        gen = ctypes.c_uint64()
+        _check(self._lib.sxb_prepare_local_graph_csr(self._h, int(num_receivers), int(num_nodes), ctypes.c_void_p(node_types_ptr),
+                                                     ctypes.c_void_p(num_neigh_ptr), ctypes.c_void_p(neigh_indices_ptr), 1,
+                                                     ctypes.byref(gen)))
+        self._num_nodes, self._num_edges, self._num_receivers = int(num_nodes), int(num_edges), int(num_receivers)
+        return int(gen.value)
+
+    def distributed_begin_host(self, generation, positions):
+        positions = _f64(positions).reshape(-1)
+        if positions.size != 3 * self._num_nodes:
+            raise ValueError("positions extent does not match the prepared graph.")
+        _check(self._lib.sxb_distributed_begin_host(self._h, int(generation), positions.ctypes.data))
+
+    def halo_rows_get(self, which, first_row, count):
+        """Caller-order rows [first_row, first_row + count) of H1 (0) / H1_adj (1) as a float32 host array."""
+        out = np.empty((int(count), (self.L_max + 1) ** 2 * self.num_channels), dtype=np.float32)
+        _check(self._lib.sxb_halo_rows_get(self._h, int(which), int(first_row), int(count), out.ctypes.data))
+        return out
+
+    def halo_rows_put(self, which, first_row, rows, accumulate=False):
+        rows = np.ascontiguousarray(rows, dtype=np.float32)
+        _check(self._lib.sxb_halo_rows_put(self._h, int(which), int(first_row), rows.shape[0], rows.ctypes.data, int(bool(accumulate))))
+
+    def distributed_begin_edge_vectors(self, generation, device_xyz_ptr):
+        _check(self._lib.sxb_distributed_begin_edge_vectors(self._h, int(generation), ctypes.c_void_p(device_xyz_ptr)))
+
     # three-phase evaluation and halo rows (device pointers as integers)
     def distributed_begin(self, generation, device_positions_ptr):
         _check(self._lib.sxb_distributed_begin(self._h, int(generation), ctypes.c_void_p(device_positions_ptr)))
@@ -307,7 +354,7 @@ class MACEB200:
 
     @property
     def node_energies(self):
-        out = np.zeros(getattr(self, "_num_receivers", self._num_nodes), dtype=np.float64)
+        out = np.empty(getattr(self, "_num_receivers", self._num_nodes), dtype=np.float64)
         _check(self._lib.sxb_get_node_energies(self._h, out.ctypes.data, out.size))
         return out
 
@@ -321,7 +368,7 @@ class MACEB200:
     def _reduce_atom_forces(self, num_nodes, edge_receivers=None, edge_sources=None, execution_graph_generation=0):
         if execution_graph_generation == 0:
             raise ValueError("Atom-force reduction needs the generation of the prepared graph.")
-        out = np.zeros((int(num_nodes), 3), dtype=np.float64)
+        out = (np.empty if int(num_nodes) == self._num_nodes else np.zeros)((int(num_nodes), 3), dtype=np.float64)
         _check(self._lib.sxb_reduce_atom_forces(self._h, int(execution_graph_generation), out.ctypes.data, out.size))
         return out
 

@@ -78,3 +78,15 @@ def test_model_loader_selects_prediction_heads_on_the_host(pkg, tmp_path):
     assert pkg.model_file_info(single)["head"] == ""
     with pytest.raises(ValueError):
         pkg.model_file_info(single, head="pbe")
+
+
+def test_lammps_pair_style_compiles_against_the_header_shim():
+    """LAMMPS is not installed here: the pair style is checked for syntax and for agreement with the C ABI
+    against minimal stand-ins of the LAMMPS headers it includes."""
+    import subprocess
+
+    lammps = ROOT / "symmetrix-xl_b200" / "lammps"
+    result = subprocess.run(["g++", "-std=c++17", "-fsyntax-only", "-Wall", "-Werror", "-I", str(lammps / "shim"),
+                             "-I", str(ROOT / "include"), str(lammps / "pair_symmetrix_mace_b200.cpp")],
+                            capture_output=True, text=True)
+    assert result.returncode == 0, result.stderr

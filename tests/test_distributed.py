@@ -161,3 +161,114 @@ def test_two_rank_decomposition_matches_single_gpu(pkg, tmp_path):
 
     r = json.loads(out.read_text())
     assert r["dE_per_atom"] <= 1e-6 and r["dF"] <= 1e-5 and r["dS"] <= 1e-7
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("arch,on_device", [("small", False), ("medium", True)])
+def test_caller_built_list_and_edge_vectors_drive_the_three_phases(pkg, model_path, arch, on_device):
+    """The way the reference's LAMMPS pair style drives the evaluator: its own full neighbor list over
+    owned atoms first and ghosts after (pair_symmetrix/pair_symmetrix_mace_kokkos.cpp:1380-1462), built
+    at cutoff + skin, and per-step edge vectors with list-skin edges clamped to the cutoff (:1532-1560).
+    One rank; the ghosts are the periodic images of its own atoms, so the forward / reverse halo is a
+    row copy / row sum.  Energy and forces against the reference's serial evaluator."""
+    import torch
+    from scipy.spatial import cKDTree
+
+    from conftest import csr_from_positions
+    from oracle import ref
+
+    path = model_path(arch, seed=4)
+    pos, cell, types = pkg.modelgen.srtio3(3, 0.05, 14)
+    ev = pkg.MACEB200(path)
+    skin = 0.5
+    halo = ev.r_cut + skin
+    dec = pkg.distributed.BrickDecomposition(cell, (1, 1, 1), halo)
+    owned, ghost_idx, ghost_shift, owned_shift, _owner = dec.select(pos, 0)
+    n_own, n_ghost = len(owned), len(ghost_idx)
+    local = np.concatenate([pos[owned] + owned_shift @ cell, pos[ghost_idx] + ghost_shift @ cell])
+    local_types = np.concatenate([types[owned], types[ghost_idx]]).astype(np.int32)
+    tree = cKDTree(local)
+    lists = tree.query_ball_point(local[:n_own], halo)
+    num_neigh = np.array([len(row) - 1 for row in lists], dtype=np.int32)
+    neigh = np.concatenate([[j for j in sorted(row) if j != i] for i, row in enumerate(lists)]).astype(np.int32)
+    recv = np.repeat(np.arange(n_own), num_neigh)
+    xyz = local[neigh] - local[recv]
+    r = np.linalg.norm(xyz, axis=1)
+    clamp = r >= ev.r_cut
+    xyz[clamp] *= (ev.r_cut / r[clamp])[:, None]                      # the pair style's clamp of skin edges
+    d_xyz = torch.from_numpy(xyz.reshape(-1).copy()).cuda()
+    if on_device:
+        d_types, d_num, d_neigh = (torch.from_numpy(a).cuda() for a in (local_types, num_neigh, neigh))
+        gen = ev.prepare_local_graph_csr_device(n_own, len(local), len(neigh), d_types.data_ptr(), d_num.data_ptr(), d_neigh.data_ptr())
+    else:
+        gen = ev.prepare_local_graph_csr(n_own, local_types, num_neigh, neigh)
+    row = (ev.L_max + 1) ** 2 * ev.num_channels
+    ghost_nodes = torch.arange(n_own, n_own + n_ghost, dtype=torch.int32, device="cuda")
+    owner_local = torch.from_numpy(np.searchsorted(owned, ghost_idx).astype(np.int32)).cuda()
+    buf = torch.empty((n_ghost, row), dtype=torch.float32, device="cuda")
+    for _ in range(2):
+        ev.distributed_begin_edge_vectors(gen, d_xyz.data_ptr())
+        ev.halo_pack(0, owner_local.data_ptr(), n_ghost, buf.data_ptr())           # forward: ghosts get their owners' H1
+        ev.halo_unpack(0, ghost_nodes.data_ptr(), n_ghost, buf.data_ptr(), False)
+        ev.distributed_continue()
+        ev.halo_pack(1, ghost_nodes.data_ptr(), n_ghost, buf.data_ptr())           # reverse: owners sum their ghosts' H1_adj
+        ev.halo_unpack(1, owner_local.data_ptr(), n_ghost, buf.data_ptr(), True)
+        ev.distributed_finish()
+        ev.synchronize()
+        forces = ev._reduce_atom_forces(n_own + n_ghost, execution_graph_generation=gen)
+        total = forces[:n_own].copy()
+        np.add.at(total, np.searchsorted(owned, ghost_idx), forces[n_own:])       # ghost forces back to the owners
+        energies = ev.node_energies
+        if ref.available():
+            first, src, shifts, exact = csr_from_positions(pos, cell, ev.r_cut)
+            m = ref.ReferenceMACE(str(path), double=False)
+            m.compute(types, np.diff(first), src, exact)
+            F, _S = ref.reduce_forces_stress(len(pos), np.diff(first), src, m.get("node_forces"), exact, abs(np.linalg.det(cell)))
+            assert np.abs(energies - m.get("node_energies")[owned]).max() <= 1e-5
+            assert np.abs(total - F[owned]).max() <= 1e-4
+    with pytest.raises(ValueError):
+        ev.prepare_local_graph_csr(n_own, local_types, num_neigh, neigh + len(local))    # index out of range
+    with pytest.raises(ValueError):
+        ev.prepare_local_graph_csr(n_own, local_types, -num_neigh, neigh)                # negative count
+
+
+@pytest.mark.gpu
+def test_host_buffer_halo_as_a_plain_lammps_pair_style_drives_it(pkg, model_path):
+    """The call sequence of symmetrix-xl_b200/lammps/pair_symmetrix_mace_b200.cpp: list from the host, positions
+    from the host, H1 / H1_adj rows through host buffers (what LAMMPS' forward / reverse communication
+    callbacks pack and unpack), against the periodic evaluation of the same system."""
+    from scipy.spatial import cKDTree
+
+    path = model_path("medium", seed=6)
+    pos, cell, types = pkg.modelgen.srtio3((3, 2, 2), 0.05, 15)
+    want = pkg.Calculator(path, skin=0.5).calculate(pos, cell, types)
+    ev = pkg.MACEB200(path)
+    halo = ev.r_cut + 0.5
+    dec = pkg.distributed.BrickDecomposition(cell, (1, 1, 1), halo)
+    owned, ghost_idx, ghost_shift, owned_shift, _owner = dec.select(pos, 0)
+    n_own, n_ghost = len(owned), len(ghost_idx)
+    local = np.concatenate([pos[owned] + owned_shift @ cell, pos[ghost_idx] + ghost_shift @ cell])
+    local_types = np.concatenate([types[owned], types[ghost_idx]]).astype(np.int32)
+    lists = cKDTree(local).query_ball_point(local[:n_own], halo)
+    num_neigh = np.array([len(row) - 1 for row in lists], dtype=np.int32)
+    neigh = np.concatenate([[j for j in sorted(row) if j != i] for i, row in enumerate(lists)]).astype(np.int32)
+    gen = ev.prepare_local_graph_csr(n_own, local_types, num_neigh, neigh)
+    owner_local = np.searchsorted(owned, ghost_idx)
+    for _ in range(2):
+        ev.distributed_begin_host(gen, local)
+        h1 = ev.halo_rows_get(0, 0, n_own)
+        ev.halo_rows_put(0, n_own, h1[owner_local])                       # forward communication
+        ev.distributed_continue()
+        back = ev.halo_rows_get(1, n_own, n_ghost)
+        summed = np.zeros_like(h1)
+        np.add.at(summed, owner_local, back)                              # reverse communication
+        ev.halo_rows_put(1, 0, summed, accumulate=True)
+        ev.distributed_finish()
+        ev.synchronize()
+        forces = ev._reduce_atom_forces(n_own + n_ghost, execution_graph_generation=gen)
+        total = forces[:n_own].copy()
+        np.add.at(total, owner_local, forces[n_own:])
+        assert abs(ev.node_energies.sum() - want["energy"]) / len(pos) <= 1e-6
+        assert np.abs(total - want["forces"][owned]).max() <= 1e-5
+        stress = ev._reduce_stress(abs(np.linalg.det(cell)), execution_graph_generation=gen)
+        assert np.abs(stress - want["stress"]).max() <= 1e-7
