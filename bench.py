@@ -269,7 +269,10 @@ def run_distributed(args):
                 "energy_eV_per_atom": last_out["energy"] / total_atoms,
                 "wall_ms_timed_region": wall_ms,
             }))
+        calc.close()          # the captured step holds the communicator's kernels: release it before the group goes
+        del calc
         if world > 1:
+            torch.cuda.synchronize()
             dist.barrier()
             dist.destroy_process_group()
 

@@ -259,7 +259,62 @@ int sxb_pack_ghost_forces(sxb_evaluator* evaluator, int32_t world, const int32_t
                           double* device_out);
 int sxb_unpack_ghost_forces(sxb_evaluator* evaluator, int32_t world, const int32_t* device_send_begin,
                             const int32_t* device_indices, int64_t num_rows, const double* device_in, double* device_totals_out);
+/* Folds the packing into the phases (and into their captured CUDA graphs): with a plan set, begin ends
+ * by gathering the H1 rows `device_send_indices` into `device_send_rows`, finish starts by adding
+ * `device_received_rows` into the H1_adj rows of those same atoms and ends by filling
+ * `device_force_send` as sxb_pack_ghost_forces does.  The caller then only moves buffers between the
+ * phases.  Device pointers, valid until the next graph preparation (which clears the plan); calling
+ * with num_send = 0 and NULL indices also clears it.  The reference's pair style keeps the equivalent
+ * send lists inside LAMMPS' Comm (pair_symmetrix_mace_kokkos.cpp:737-1005). */
+int sxb_set_halo_plan(sxb_evaluator* evaluator, const int32_t* device_send_indices, int64_t num_send, float* device_send_rows,
+                      const float* device_received_rows, int32_t world, const int32_t* device_ghost_begin,
+                      double* device_force_send);
+/* For a caller that captured one whole decomposed step (the three phases and its own exchanges) into a
+ * CUDA graph on the evaluator's stream and now replays it: declares that the phases have run, so that
+ * sxb_synchronize and the result getters behave as after sxb_distributed_finish; `launches` = kernels of
+ * this library inside the replayed graph (added to sxb_launch_count).  No counterpart in the reference,
+ * which launches its kernels one by one. */
+int sxb_distributed_replayed(sxb_evaluator* evaluator, uint64_t generation, int64_t launches);
+/* Abandons an evaluation that is open between the phases (the reference resets its phase when a phase
+ * call throws, libsymmetrix/source/mace_kokkos_evaluate.cpp:1737-1746): the next call must be a begin. */
+int sxb_distributed_abort(sxb_evaluator* evaluator);
 int sxb_set_stream(sxb_evaluator* evaluator, void* stream);
+
+/* ---- Halo exchange over NVLink peer memory ---------------------------------------------------------
+ * Replaces the MPI brick swaps of the reference's pair style (pair_symmetrix_mace_kokkos.cpp:737-1005,
+ * 1568-1705) inside one node: every rank maps its peers' receive buffers (CUDA IPC) and an exchange is a
+ * push kernel (16-byte stores into the peers' buffers, then a release store of an arrival flag) followed
+ * by a wait kernel with a time limit; no collective, no staging copy, capturable into a CUDA graph.
+ *   sxb_device_alloc / _free   plain cudaMalloc'd, zeroed buffers (IPC handles exist only for those)
+ *   sxb_ipc_export             64-byte handle of such a buffer (or of sxb_halo_tensor's allocation)
+ *   sxb_peer_create            this rank's exchange object; sxb_peer_flags = its flag table (export it)
+ *   sxb_peer_open              maps a peer's buffer from its handle (closed by sxb_peer_destroy)
+ *   sxb_peer_plan              exchange `phase` (0..3): my outgoing rows `send` ordered by destination
+ *                              (send_begin int64[world+1], rows of row_bytes), the address of my segment in
+ *                              every peer's receive buffer, and every peer's flag table; optionally a gather
+ *                              list over a local tensor, a scatter list into the peers' tensors, and add mode
+ *   sxb_peer_advance           enqueue: next step (once per evaluation, before its first exchange)
+ *   sxb_peer_exchange          enqueue: push my rows of `phase`, then wait for every peer's
+ *   sxb_peer_status            after a synchronisation: 0, or 32 when a wait ran out (about ten seconds);
+ *                              the results of that step are then invalid, the CUDA context stays usable
+ * Every rank must run the same sequence of exchanges. */
+typedef struct PeerExchange sxb_peer_exchange_t;
+int sxb_device_alloc(int32_t device_ordinal, int64_t bytes, void** out);
+int sxb_device_free(void* pointer);
+int sxb_ipc_export(const void* device_pointer, unsigned char* handle64);
+int sxb_peer_create(int32_t device_ordinal, int32_t rank, int32_t world, sxb_peer_exchange_t** out);
+int sxb_peer_flags(sxb_peer_exchange_t* exchange, void** flags);
+int sxb_peer_status(sxb_peer_exchange_t* exchange, int32_t* out);
+int sxb_peer_open(sxb_peer_exchange_t* exchange, const unsigned char* handle64, void** out);
+int sxb_peer_plan(sxb_peer_exchange_t* exchange, int32_t phase, const void* send, const int64_t* send_begin, int32_t row_bytes,
+                  void* const* remote_pointers, void* const* remote_flags, const int32_t* device_row_source,
+                  const int32_t* device_row_dest, int32_t accumulate);
+/* out[k] = row of the evaluator's node tensors (H1, H1_adj) that holds caller-order node indices[k]; device
+ * arrays.  Lets an exchange gather from, or add into, those tensors directly (row_source / row_dest above). */
+int sxb_internal_rows(sxb_evaluator* evaluator, const int32_t* device_indices, int64_t count, int32_t* device_out);
+int sxb_peer_advance(sxb_peer_exchange_t* exchange, void* stream);
+int sxb_peer_exchange(sxb_peer_exchange_t* exchange, int32_t phase, void* stream);
+int sxb_peer_destroy(sxb_peer_exchange_t* exchange);
 
 /* Tiled streaming (the reference's fixed-workspace dual-layer plan, allow_fixed_workspace:
  * libsymmetrix/source/mace_kokkos_evaluate.cpp:755-1148, workspace

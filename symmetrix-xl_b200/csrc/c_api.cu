@@ -452,6 +452,35 @@ int sxb_unpack_ghost_forces(sxb_evaluator* ev, int32_t world, const int32_t* dev
     });
 }
 
+int sxb_set_halo_plan(sxb_evaluator* ev, const int32_t* device_send_indices, int64_t num_send, float* device_send_rows,
+                      const float* device_received_rows, int32_t world, const int32_t* device_ghost_begin, double* device_force_send)
+{
+    return guarded([&] {
+        require(ev, "evaluator");
+        ev->impl.set_halo_plan(device_send_indices, num_send, device_send_rows, device_received_rows, world, device_ghost_begin,
+                               device_force_send);
+    });
+}
+
+int sxb_internal_rows(sxb_evaluator* ev, const int32_t* device_indices, int64_t count, int32_t* device_out)
+{
+    return guarded([&] {
+        require(ev, "evaluator");
+        if (count > 0) { require(device_indices, "device_indices"); require(device_out, "device_out"); }
+        ev->impl.internal_rows(device_indices, count, device_out);
+    });
+}
+
+int sxb_distributed_abort(sxb_evaluator* ev)
+{
+    return guarded([&] { require(ev, "evaluator"); ev->impl.abort_phases(); });
+}
+
+int sxb_distributed_replayed(sxb_evaluator* ev, uint64_t generation, int64_t launches)
+{
+    return guarded([&] { require(ev, "evaluator"); ev->impl.mark_phases_replayed(generation, launches); });
+}
+
 int sxb_set_tile_size(sxb_evaluator* ev, int32_t receivers_per_tile)
 {
     return guarded([&] { require(ev, "evaluator"); ev->impl.set_tile_size(receivers_per_tile); });

@@ -334,6 +334,7 @@ void Evaluator::install_graph(int num_receivers, int num_nodes, const std::vecto
     have_results_ = false;
     mirror_valid_ = false;
     phase_ = 0;
+    halo_plan_ = HaloPlan{};      // buffers of a decomposed run belong to the previous graph
 }
 
 namespace {
@@ -898,6 +899,11 @@ void Evaluator::run_pipeline(int phases)
             launch_tc(calls);
             span_end();
         }
+        if (phases != 7 && halo_plan_.active && halo_plan_.send_rows != nullptr) {   // forward halo: my owned rows that peers hold as ghosts
+            span_begin("halo_pack");
+            pack_rows(0, halo_plan_.send_indices, halo_plan_.num_send, halo_plan_.send_rows);
+            span_end();
+        }
     }
     if (phases & 2) {
         if (model_.shape_id == 2 && fo.edge_forces != nullptr)   // the split gradient kernels accumulate into it
@@ -1059,6 +1065,11 @@ void Evaluator::run_pipeline(int phases)
     }
     if (phases & 4) {
         fo.accumulate_edge = 1;
+        if (phases != 7 && halo_plan_.active && halo_plan_.received_rows != nullptr) {   // reverse halo: adjoints my atoms collected as ghosts of the peers
+            span_begin("halo_unpack");
+            unpack_rows(1, halo_plan_.send_indices, halo_plan_.num_send, halo_plan_.received_rows, true);
+            span_end();
+        }
         for (int t0 = 0; t0 < R; t0 += tile_cap) {
             const int T = std::min(tile_cap, R - t0);
             if (tiled) {
@@ -1130,6 +1141,10 @@ void Evaluator::run_pipeline(int phases)
             R, ALL, internal_of_.ptr, energy_slots_.ptr, virial_slots_.ptr, node_energies_.ptr, forces_.ptr, error_flag_.ptr, totals_.ptr,
             node_energies_out_.ptr, forces_out_.ptr, host_results_);
         launches_ += 1;
+        if (phases != 7 && halo_plan_.active) {
+            have_results_ = true;
+            pack_ghost_forces(halo_plan_.world, halo_plan_.ghost_begin, num_nodes_ - num_receivers_, halo_plan_.force_send);
+        }
         span_end();
     }
     SXB_CUDA(cudaGetLastError());
@@ -1153,8 +1168,10 @@ void Evaluator::enqueue_phases(int phases, const double* positions, bool upload_
         }
         run_pipeline(phases);
     };
-    if (!use_graphs_ || profiling_ || stream_ == nullptr) {
-        enqueue();
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (stream_ != nullptr && cudaStreamIsCapturing(stream_, &capturing) != cudaSuccess) cudaGetLastError();
+    if (!use_graphs_ || profiling_ || stream_ == nullptr || capturing != cudaStreamCaptureStatusNone) {
+        enqueue();      // also when the caller is capturing this stream itself: the kernels then join its graph
         return;
     }
     StepGraph& slot = step_graphs_[phases];
@@ -1224,7 +1241,10 @@ void Evaluator::finish_compute()
         SXB_CUDA(cudaStreamSynchronize(stream_));
         mirror_valid_ = false;
     }
-    SXB_CUDA(cudaEventElapsedTime(&last_ms_, event_begin_, event_end_));
+    if (cudaEventElapsedTime(&last_ms_, event_begin_, event_end_) != cudaSuccess) {
+        cudaGetLastError();       // the bracket was not recorded on this path (a caller-captured step): no device time
+        last_ms_ = 0.0f;
+    }
     profile_.clear();
     for (const auto& span : spans_) {
         float ms = 0.0f;
@@ -1519,6 +1539,26 @@ void Evaluator::add_force_rows(const int* device_indices, long count, const doub
     SXB_CUDA(cudaGetLastError());
 }
 
+namespace {
+__global__ void internal_rows_kernel(long count, const int* __restrict__ indices, const int* __restrict__ internal_of, int num_nodes,
+                                     int* __restrict__ out)
+{
+    const long k = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (k >= count) return;
+    const int node = indices[k];
+    out[k] = (node >= 0 && node < num_nodes) ? internal_of[node] : -1;
+}
+}  // namespace
+
+void Evaluator::internal_rows(const int* device_indices, long count, int* device_out)
+{
+    if (count <= 0) return;
+    internal_rows_kernel<<<blocks_for(count, 256), 256, 0, stream_>>>(count, device_indices, internal_of_.ptr, num_nodes_, device_out);
+    launches_ += 1;
+    SXB_CUDA(cudaGetLastError());
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+}
+
 void Evaluator::gather_position_rows(const double* device_rows, const int* device_indices, long count,
                                      const double* device_offsets, double* device_out)
 {
@@ -1549,6 +1589,52 @@ void Evaluator::unpack_ghost_forces(int world, const int* device_send_begin, con
                                                                             forces_out_.ptr, device_totals_out);
     launches_ += 1;
     SXB_CUDA(cudaGetLastError());
+}
+
+// Registers the buffers of a domain-decomposed run, so that the halo packing and unpacking become
+// part of the (captured) phases instead of separate calls: the first phase ends by gathering the H1
+// rows `send_indices` into `send_rows`; the third phase starts by adding `received_rows` (the adjoints
+// peers collected for those same rows) into H1_adj and ends by packing the ghost forces and this
+// rank's totals into `force_send` (layout of pack_ghost_forces).  All pointers are device memory that
+// stays valid until the next graph preparation; NULL send_indices switches the plan off.
+void Evaluator::set_halo_plan(const int* send_indices, long num_send, float* send_rows, const float* received_rows, int world,
+                              const int* ghost_begin, double* force_send)
+{
+    drop_step_graphs();
+    halo_plan_ = HaloPlan{};
+    if (send_indices == nullptr && num_send > 0) return;
+    // send_rows / received_rows may be NULL: the exchange then gathers from H1 and adds into H1_adj by itself
+    if (world <= 0 || ghost_begin == nullptr || force_send == nullptr)
+        throw std::invalid_argument("Halo plan needs the ghost offsets and the force buffer.");
+    halo_plan_.active = true;
+    halo_plan_.send_indices = send_indices;
+    halo_plan_.num_send = num_send;
+    halo_plan_.send_rows = send_rows;
+    halo_plan_.received_rows = received_rows;
+    halo_plan_.world = world;
+    halo_plan_.ghost_begin = ghost_begin;
+    halo_plan_.force_send = force_send;
+}
+
+// A caller that has captured begin / continue / finish (with its exchanges in between) into a CUDA
+// graph of its own and replays that graph tells the evaluator so: the host-side state then is the one
+// after distributed_finish, and synchronize() fetches status and totals as usual.
+void Evaluator::mark_phases_replayed(std::uint64_t generation, long launches)
+{
+    check_generation(generation);
+    phase_ = 0;
+    pending_finish_ = true;
+    have_results_ = true;
+    mirror_valid_ = false;
+    launches_ += launches;
+}
+
+void Evaluator::abort_phases()
+{
+    phase_ = 0;
+    pending_finish_ = false;
+    have_results_ = false;
+    mirror_valid_ = false;
 }
 
 void Evaluator::set_stream(cudaStream_t stream)

@@ -55,6 +55,11 @@ public:
     void pack_rows(int which, const int* device_indices, long count, float* device_out);
     void unpack_rows(int which, const int* device_indices, long count, const float* device_in, bool accumulate);
     void add_force_rows(const int* device_indices, long count, const double* device_in);
+    void internal_rows(const int* device_indices, long count, int* device_out);
+    void mark_phases_replayed(std::uint64_t generation, long launches);
+    void abort_phases();
+    void set_halo_plan(const int* send_indices, long num_send, float* send_rows, const float* received_rows, int world,
+                       const int* ghost_begin, double* force_send);
     void get_halo_rows(int which, long first_row, long count, float* host_out);
     void put_halo_rows(int which, long first_row, long count, const float* host_in, bool accumulate);
     void distributed_begin_host(std::uint64_t generation, const double* host_positions);
@@ -106,6 +111,17 @@ private:
         long launches = 0;
     };
     std::map<int, StepGraph> step_graphs_;
+    struct HaloPlan {
+        bool active = false;
+        const int* send_indices = nullptr;
+        long num_send = 0;
+        float* send_rows = nullptr;
+        const float* received_rows = nullptr;
+        int world = 0;
+        const int* ghost_begin = nullptr;
+        double* force_send = nullptr;
+    };
+    HaloPlan halo_plan_;
     bool use_graphs_ = true;
     int l1_reverse_variant_ = 0;   // 0: one thread per channel; 1: the same at 128 registers; 2: two threads per channel
     void finish_compute();

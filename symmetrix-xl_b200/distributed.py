@@ -14,6 +14,8 @@ kernel of this package reads another GPU's memory.
 """
 from __future__ import annotations
 
+import os
+
 import numpy as np
 
 GRIDS = {1: (1, 1, 1), 2: (2, 1, 1), 4: (2, 2, 1), 8: (2, 2, 2)}
@@ -159,6 +161,74 @@ class ExchangePlan:
         self.num_owned, self.num_ghost = len(owned), len(ghost_idx)
 
 
+class PeerTransport:
+    """The four exchanges of a step over NVLink peer memory (csrc/peer_exchange.cu): every rank maps the
+    receive buffers of its peers through CUDA IPC; an exchange is a push kernel plus a bounded wait kernel
+    on the calculator's stream.  Receive buffers: the ghost tail of the position array, the ghost tail of
+    the evaluator's H1 tensor, the returned-adjoint rows and the returned-force rows."""
+
+    PHASE_POSITIONS, PHASE_H1, PHASE_H1_ADJ, PHASE_FORCES = 0, 1, 2, 3
+
+    def __init__(self, lib, device_index, rank, world):
+        import ctypes
+
+        self.lib, self.ctypes = lib, ctypes
+        self.device_index, self.rank, self.world = device_index, rank, world
+        self.handle = ctypes.c_void_p()
+        self._check(lib.sxb_peer_create(device_index, rank, world, ctypes.byref(self.handle)))
+        flags = ctypes.c_void_p()
+        self._check(lib.sxb_peer_flags(self.handle, ctypes.byref(flags)))
+        self.flags = flags.value
+        self.owned_buffers = []
+
+    def _check(self, status):
+        if status != 0:
+            raise RuntimeError(self.lib.sxb_last_error().decode())
+
+    def alloc(self, nbytes):
+        ptr = self.ctypes.c_void_p()
+        self._check(self.lib.sxb_device_alloc(self.device_index, max(int(nbytes), 256), self.ctypes.byref(ptr)))
+        self.owned_buffers.append(ptr.value)
+        return ptr.value
+
+    def export(self, ptr):
+        buf = self.ctypes.create_string_buffer(64)
+        self._check(self.lib.sxb_ipc_export(self.ctypes.c_void_p(ptr), buf))
+        return bytes(buf.raw)
+
+    def open(self, handle):
+        out = self.ctypes.c_void_p()
+        self._check(self.lib.sxb_peer_open(self.handle, handle, self.ctypes.byref(out)))
+        return out.value
+
+    def plan(self, phase, send_ptr, send_begin, row_bytes, remote_ptrs, remote_flags, row_source=None, row_dest=None, accumulate=False):
+        c = self.ctypes
+        begin = (c.c_int64 * (self.world + 1))(*[int(v) for v in send_begin])
+        remotes = (c.c_void_p * self.world)(*[c.c_void_p(int(v)) for v in remote_ptrs])
+        flags = (c.c_void_p * self.world)(*[c.c_void_p(int(v)) for v in remote_flags])
+        self._check(self.lib.sxb_peer_plan(self.handle, int(phase), c.c_void_p(send_ptr), begin, int(row_bytes), remotes, flags,
+                                           c.c_void_p(row_source), c.c_void_p(row_dest), int(bool(accumulate))))
+
+    def advance(self, stream_ptr):
+        self._check(self.lib.sxb_peer_advance(self.handle, self.ctypes.c_void_p(stream_ptr)))
+
+    def exchange(self, phase, stream_ptr):
+        self._check(self.lib.sxb_peer_exchange(self.handle, int(phase), self.ctypes.c_void_p(stream_ptr)))
+
+    def status(self):
+        out = self.ctypes.c_int32()
+        self._check(self.lib.sxb_peer_status(self.handle, self.ctypes.byref(out)))
+        return out.value
+
+    def close(self):
+        if self.handle:
+            self.lib.sxb_peer_destroy(self.handle)
+            self.handle = None
+            for ptr in self.owned_buffers:
+                self.lib.sxb_device_free(self.ctypes.c_void_p(ptr))
+            self.owned_buffers = []
+
+
 class DistributedCalculator:
     """Energy, forces and stress of a periodic system decomposed over the ranks of the process group.
 
@@ -184,6 +254,7 @@ class DistributedCalculator:
         self.skin = float(skin)
         self.comm = make_comm()
         self.transport = "NCCL" if self.comm.world > 1 else "local-copy"
+        self.peer = None
         self.generation = 0
 
     def prepare(self, positions, cell, types, grid=None):
@@ -202,6 +273,9 @@ class DistributedCalculator:
         owner = self.decomposition.owner(positions)
         if np.bincount(owner, minlength=self.comm.world).min() == 0:
             raise ValueError("domain decomposition: a brick of the grid owns no atom; use fewer ranks or another grid")
+        # mappings of the peers' buffers are closed on every rank before any rank may re-allocate what it exported
+        self._release_peer()
+        self.comm.all_reduce_sum(torch.zeros(1, dtype=torch.float64, device=self.device))
         plan = ExchangePlan(self.decomposition, positions, self.comm, self.device)
         self.plan = plan
         n_own, n_ghost = plan.num_owned, plan.num_ghost
@@ -226,14 +300,24 @@ class DistributedCalculator:
                                                 out=torch.empty((n_send, 3), dtype=torch.float64, device=dev))
         self.row = (self.ev.L_max + 1) ** 2 * self.ev.num_channels
         # per-step buffers, allocated once per graph: the step issues no allocation and few host operations
-        self.local_positions = torch.from_numpy(local_pos).to(dev)           # [owned | ghosts], the step's input buffer
+        extra = self.TOTALS_ROWS
+        n_local = n_own + n_ghost
+        self.peer = self._make_peer_transport()
+        if self.peer is not None:
+            # receive buffers that peers write into must be plain device allocations (they are shared by IPC handle)
+            self.local_positions = _as_tensor(torch, self.peer.alloc(24 * n_local), (n_local, 3), torch.float64, dev)
+            self.local_positions.copy_(torch.from_numpy(local_pos))
+            self._got_rows = None          # the peers add their H1_adj rows straight into this rank's tensor
+            self._force_recv = _as_tensor(torch, self.peer.alloc(24 * (n_send + extra * world)), (n_send + extra * world, 3),
+                                          torch.float64, dev)
+        else:
+            self.local_positions = torch.from_numpy(local_pos).to(dev)       # [owned | ghosts], the step's input buffer
+            self._got_rows = torch.empty((n_send, self.row), dtype=torch.float32, device=dev)
+            self._force_recv = torch.empty((n_send + extra * world, 3), dtype=torch.float64, device=dev)
         self.owned_positions = self.local_positions[:n_own]
         self._send_pos = torch.empty((n_send, 3), dtype=torch.float64, device=dev)
         self._send_rows = torch.empty((n_send, self.row), dtype=torch.float32, device=dev)
-        self._got_rows = torch.empty((n_send, self.row), dtype=torch.float32, device=dev)
-        extra = self.TOTALS_ROWS
         self._force_send = torch.empty((n_ghost + extra * world, 3), dtype=torch.float64, device=dev)
-        self._force_recv = torch.empty((n_send + extra * world, 3), dtype=torch.float64, device=dev)
         self._force_send_counts = [c + extra for c in self.recv_counts]
         self._force_recv_counts = [c + extra for c in self.send_counts]
         self._ghost_begin = torch.tensor(np.concatenate([[0], np.cumsum(self.recv_counts)]), dtype=torch.int32, device=dev)
@@ -241,61 +325,205 @@ class DistributedCalculator:
         self._totals = torch.zeros(10, dtype=torch.float64, device=dev)
         self._totals_host = torch.empty(10, dtype=torch.float64).pin_memory()
         # ghost rows of H1 / H1_adj: the tail of the evaluator's own tensors
-        n_local = n_own + n_ghost
         h1_ptr, row, first = self.ev.halo_tensor(0)
         adj_ptr, _, _ = self.ev.halo_tensor(1)
         assert row == self.row and first == n_own
         self._h1_tail = _as_tensor(torch, h1_ptr, (n_local, self.row), torch.float32, dev)[n_own:]
         self._h1_adj_tail = _as_tensor(torch, adj_ptr, (n_local, self.row), torch.float32, dev)[n_own:]
+        # packing and unpacking run inside the evaluator's phases (and their captured graphs)
+        if self.peer is None:
+            self.ev.set_halo_plan(self.send_local.data_ptr(), n_send, self._send_rows.data_ptr(), self._got_rows.data_ptr(), world,
+                                  self._ghost_begin.data_ptr(), self._force_send.data_ptr())
+        self._step_graph, self._step_graph_launches, self._eager_steps = None, 0, 0
+        self._capture_allowed = os.environ.get("SXB_STEP_GRAPH", "1") != "0"
+        if self.peer is not None:
+            self._plan_peer_exchanges(h1_ptr, adj_ptr)
+            self.transport = "NVLink peer-memory"
+            # collectives captured in a graph tie the communicator to it; the peer kernels have no such tie
+        elif world > 1:
+            self.transport = "NCCL"
+            self._capture_allowed = self._capture_allowed and os.environ.get("SXB_STEP_GRAPH_NCCL", "0") == "1"
         return plan
+
+    def _make_peer_transport(self):
+        """A PeerTransport when every rank can create one (and SXB_HALO_TRANSPORT does not say ``nccl``), else None."""
+        if self.comm.world == 1 or os.environ.get("SXB_HALO_TRANSPORT", "peer") == "nccl":
+            return None
+        from .evaluator import load_library
+
+        torch = self.torch
+        peer = None
+        try:
+            peer = PeerTransport(load_library(), self.device.index, self.comm.rank, self.comm.world)
+            peer.export(peer.flags)        # fails where CUDA IPC is not available
+            ok = 1.0
+        except Exception:
+            ok = 0.0
+        agreed = self.comm.all_reduce_sum(torch.tensor([ok], dtype=torch.float64, device=self.device))
+        if float(agreed[0]) < self.comm.world:
+            if peer is not None:
+                peer.close()
+            return None
+        return peer
+
+    def _release_peer(self):
+        if getattr(self, "peer", None) is not None:
+            self.torch.cuda.synchronize(self.device)
+            self._step_graph = None
+            self.peer.close()
+            self.peer = None
+
+    def _plan_peer_exchanges(self, h1_ptr, adj_ptr):
+        """Exchanges handles and row offsets with every rank and registers the four push plans."""
+        import torch.distributed as dist
+
+        peer, plan, world, me = self.peer, self.plan, self.comm.world, self.comm.rank
+        n_own, extra, row_bytes = plan.num_owned, self.TOTALS_ROWS, 4 * self.row
+        ghost_begin = np.concatenate([[0], np.cumsum(self.recv_counts)]).astype(np.int64)
+        send_begin = np.concatenate([[0], np.cumsum(self.send_counts)]).astype(np.int64)
+        torch, dev = self.torch, self.device
+        n_send = len(self.send_local)
+        # rows of the evaluator's tensors that hold my send list: H1 rows are gathered straight out of the tensor
+        # while they are pushed, and the peers add their H1_adj rows straight into mine
+        self._send_rows_internal = torch.zeros(max(n_send, 1), dtype=torch.int32, device=dev)
+        self.ev.internal_rows(self.send_local.data_ptr(), n_send, self._send_rows_internal.data_ptr())
+        mine = {"n_own": n_own, "ghost_begin": ghost_begin.tolist(), "send_begin": send_begin.tolist(),
+                "send_rows_internal": self._send_rows_internal[:n_send].cpu().numpy(),
+                "positions": peer.export(self.local_positions.data_ptr()), "h1": peer.export(h1_ptr), "h1_adj": peer.export(adj_ptr),
+                "force_recv": peer.export(self._force_recv.data_ptr()), "flags": peer.export(peer.flags)}
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine)
+        local = {"positions": self.local_positions.data_ptr(), "h1": h1_ptr, "h1_adj": adj_ptr,
+                 "force_recv": self._force_recv.data_ptr(), "flags": peer.flags}
+        base = [{k: (local[k] if p == me else peer.open(everyone[p][k])) for k in local} for p in range(world)]
+        flags = [base[p]["flags"] for p in range(world)]
+        # where my segment starts in peer p's receive buffers
+        ghost_slot = [everyone[p]["n_own"] + everyone[p]["ghost_begin"][me] for p in range(world)]     # rows behind p's owned atoms
+        sent_slot = [everyone[p]["send_begin"][me] for p in range(world)]                              # position in p's send list
+        peer.plan(peer.PHASE_POSITIONS, self._send_pos.data_ptr(), send_begin, 24,
+                  [base[p]["positions"] + 24 * ghost_slot[p] for p in range(world)], flags)
+        peer.plan(peer.PHASE_H1, h1_ptr, send_begin, row_bytes,
+                  [base[p]["h1"] + row_bytes * ghost_slot[p] for p in range(world)], flags,
+                  row_source=self._send_rows_internal.data_ptr())
+        # my ghost g, owned by p, is entry (sent_slot[p] + k) of p's send list: its adjoint goes to that row of p's H1_adj
+        owner_rows = [np.asarray(everyone[p]["send_rows_internal"][sent_slot[p]:sent_slot[p] + self.recv_counts[p]], dtype=np.int32)
+                      for p in range(world)]
+        self._ghost_owner_rows = torch.from_numpy(np.concatenate(owner_rows + [np.zeros(1, dtype=np.int32)])).to(dev)
+        peer.plan(peer.PHASE_H1_ADJ, adj_ptr + row_bytes * n_own, ghost_begin, row_bytes,
+                  [base[p]["h1_adj"] for p in range(world)], flags, row_dest=self._ghost_owner_rows.data_ptr(), accumulate=True)
+        force_begin = ghost_begin + extra * np.arange(world + 1)
+        peer.plan(peer.PHASE_FORCES, self._force_send.data_ptr(), force_begin, 24,
+                  [base[p]["force_recv"] + 24 * (sent_slot[p] + extra * me) for p in range(world)], flags)
+        # the evaluator then neither packs H1 rows nor unpacks H1_adj rows itself
+        self.ev.set_halo_plan(self.send_local.data_ptr(), n_send, 0, 0, world, self._ghost_begin.data_ptr(), self._force_send.data_ptr())
+        dist.barrier()        # nobody pushes before every rank has mapped and planned
 
     def calculate(self, owned_positions=None):
         """One evaluation.  ``owned_positions``: device tensor f64 [num_owned, 3]; by default the head of
         ``local_positions`` is used as it stands (a caller may write the new positions there directly).
         Returns energy and stress of the whole system and the forces on this rank's owned atoms
-        (device tensor)."""
+        (device tensor).
+
+        After two eager evaluations of a prepared graph the whole step -- the gather, the three phases
+        and the four exchanges -- is captured into one CUDA graph and replayed from then on (every
+        buffer of the step is fixed per graph); ``SXB_STEP_GRAPH=0`` keeps it eager."""
         torch = self.torch
+        n_own = self.plan.num_owned
         caller_stream = torch.cuda.current_stream(self.device)
         self.stream.wait_stream(caller_stream)
         with torch.cuda.stream(self.stream):
-            out = self._calculate_on_stream(owned_positions)
+            if owned_positions is not None and owned_positions.data_ptr() != self.local_positions.data_ptr():
+                self.local_positions[:n_own].copy_(owned_positions)
+            if self._step_graph is not None:
+                self._step_graph.replay()
+                self.ev.distributed_replayed(self.generation, self._step_graph_launches)
+            elif self._capture_allowed and self._eager_steps >= 2:
+                self._capture_step()
+            else:
+                self._enqueue_step()
+                self._eager_steps += 1
+            self.ev.synchronize()        # one host synchronisation; fetches the status word (raises on a device-side error)
+            if self.peer is not None and self.peer.status() != 0:
+                raise RuntimeError("halo exchange: a peer did not deliver its rows within the time limit; this step is invalid")
         caller_stream.wait_stream(self.stream)
-        return out
+        host = self._totals_host.numpy()
+        _e, f_ptr, _v = self.ev.device_results()
+        forces = _as_tensor(torch, f_ptr, (n_own + self.plan.num_ghost, 3), torch.float64, self.device)
+        return {"energy": float(host[0]), "stress": -host[1:].reshape(3, 3).copy() / self.volume,
+                "forces": forces[:n_own], "owned": self.plan.owned}
 
-    def _calculate_on_stream(self, owned_positions):
-        torch, ev, plan, comm = self.torch, self.ev, self.plan, self.comm
+    def close(self):
+        """Releases the captured step.  Call it before the process group is destroyed: a communicator whose
+        collectives sit in a live CUDA graph cannot be torn down."""
+        if getattr(self, "_step_graph", None) is not None:
+            self.torch.cuda.synchronize(self.device)
+            self._step_graph = None
+            self._capture_allowed = False
+        self._release_peer()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _capture_step(self):
+        """Captures one step into a CUDA graph on the calculator's stream (it also runs once, by replay)."""
+        torch = self.torch
+        before = self.ev.launch_count
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=self.stream, capture_error_mode="thread_local"):
+                self._enqueue_step()
+            self._step_graph_launches = self.ev.launch_count - before
+            self._step_graph = graph
+            graph.replay()
+            self.ev.distributed_replayed(self.generation, 0)
+        except Exception:       # capture is an optimisation: any refusal falls back to eager launches for good
+            self._capture_allowed = False
+            self._step_graph = None
+            torch.cuda.synchronize(self.device)
+            self.ev.distributed_abort()
+            self._enqueue_step()
+
+    def _enqueue_step(self):
+        ev, plan, comm = self.ev, self.plan, self.comm
         n_own, n_ghost = plan.num_owned, plan.num_ghost
         sc, rc = self.send_counts, self.recv_counts
         n_send = len(self.send_local)
         world = comm.world
         local_pos = self.local_positions
-        if owned_positions is not None and owned_positions.data_ptr() != local_pos.data_ptr():
-            local_pos[:n_own].copy_(owned_positions)
         # ghost positions: owners gather their rows, displaced to the images, straight into the peers' tails
+        peer, stream = self.peer, self.stream.cuda_stream
+        if peer is not None:
+            peer.advance(stream)
         ev.gather_position_rows(local_pos.data_ptr(), self.send_local.data_ptr(), n_send, self.send_offset.data_ptr(),
                                 self._send_pos.data_ptr())
-        comm.all_to_all(self._send_pos, sc, rc, out=local_pos[n_own:])
-        ev.distributed_begin(self.generation, local_pos.data_ptr())
-        # forward halo: H1 rows of my owned atoms into the tail of the feature tensor of the ranks that hold them as ghosts
-        ev.halo_pack(0, self.send_local.data_ptr(), n_send, self._send_rows.data_ptr())
-        comm.all_to_all(self._send_rows, sc, rc, out=self._h1_tail)
+        if peer is not None:
+            peer.exchange(peer.PHASE_POSITIONS, stream)
+        else:
+            comm.all_to_all(self._send_pos, sc, rc, out=local_pos[n_own:])
+        ev.distributed_begin(self.generation, local_pos.data_ptr())       # ends by packing my H1 rows into _send_rows
+        # forward halo: into the tail of the feature tensor of the ranks that hold my atoms as ghosts
+        if peer is not None:
+            peer.exchange(peer.PHASE_H1, stream)
+        else:
+            comm.all_to_all(self._send_rows, sc, rc, out=self._h1_tail)
         ev.distributed_continue()
         # reverse halo: H1_adj rows of my ghosts leave from the tail of the adjoint tensor and are summed at their owners
-        comm.all_to_all(self._h1_adj_tail, rc, sc, out=self._got_rows)
-        ev.halo_unpack(1, self.send_local.data_ptr(), n_send, self._got_rows.data_ptr(), True)
-        ev.distributed_finish()
+        if peer is not None:
+            peer.exchange(peer.PHASE_H1_ADJ, stream)
+        else:
+            comm.all_to_all(self._h1_adj_tail, rc, sc, out=self._got_rows)
+        ev.distributed_finish()       # starts by adding _got_rows, ends by packing ghost forces + totals into _force_send
         # ghost forces back to the owners, with every rank's energy and virial riding along
-        ev.pack_ghost_forces(world, self._ghost_begin.data_ptr(), n_ghost, self._force_send.data_ptr())
-        comm.all_to_all(self._force_send, self._force_send_counts, self._force_recv_counts, out=self._force_recv)
+        if peer is not None:
+            peer.exchange(peer.PHASE_FORCES, stream)
+        else:
+            comm.all_to_all(self._force_send, self._force_send_counts, self._force_recv_counts, out=self._force_recv)
         ev.unpack_ghost_forces(world, self._send_begin.data_ptr(), self.send_local.data_ptr(), n_send, self._force_recv.data_ptr(),
                                self._totals.data_ptr())
         self._totals_host.copy_(self._totals, non_blocking=True)
-        ev.synchronize()        # one host synchronisation; fetches the status word (raises on a device-side error)
-        host = self._totals_host.numpy()
-        _e, f_ptr, _v = ev.device_results()
-        forces = _as_tensor(torch, f_ptr, (n_own + n_ghost, 3), torch.float64, self.device)
-        return {"energy": float(host[0]), "stress": -host[1:].reshape(3, 3).copy() / self.volume,
-                "forces": forces[:n_own], "owned": plan.owned}
 
 
 def _as_tensor(torch, ptr, shape, dtype, device):

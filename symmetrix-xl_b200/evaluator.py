@@ -86,7 +86,22 @@ SIGNATURES = {
     "sxb_gather_position_rows": (ctypes.c_int, [_P, _P, _P, ctypes.c_int64, _P, _P]),
     "sxb_pack_ghost_forces": (ctypes.c_int, [_P, ctypes.c_int32, _P, ctypes.c_int64, _P]),
     "sxb_unpack_ghost_forces": (ctypes.c_int, [_P, ctypes.c_int32, _P, _P, ctypes.c_int64, _P, _P]),
+    "sxb_set_halo_plan": (ctypes.c_int, [_P, _P, ctypes.c_int64, _P, _P, ctypes.c_int32, _P, _P]),
+    "sxb_distributed_replayed": (ctypes.c_int, [_P, ctypes.c_uint64, ctypes.c_int64]),
+    "sxb_distributed_abort": (ctypes.c_int, [_P]),
     "sxb_set_stream": (ctypes.c_int, [_P, _P]),
+    "sxb_device_alloc": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int64, ctypes.POINTER(_P)]),
+    "sxb_device_free": (ctypes.c_int, [_P]),
+    "sxb_ipc_export": (ctypes.c_int, [_P, ctypes.c_char_p]),
+    "sxb_peer_create": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(_P)]),
+    "sxb_peer_flags": (ctypes.c_int, [_P, ctypes.POINTER(_P)]),
+    "sxb_peer_status": (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_int32)]),
+    "sxb_peer_open": (ctypes.c_int, [_P, ctypes.c_char_p, ctypes.POINTER(_P)]),
+    "sxb_peer_plan": (ctypes.c_int, [_P, ctypes.c_int32, _P, _P, ctypes.c_int32, _P, _P, _P, _P, ctypes.c_int32]),
+    "sxb_internal_rows": (ctypes.c_int, [_P, _P, ctypes.c_int64, _P]),
+    "sxb_peer_advance": (ctypes.c_int, [_P, _P]),
+    "sxb_peer_exchange": (ctypes.c_int, [_P, ctypes.c_int32, _P]),
+    "sxb_peer_destroy": (ctypes.c_int, [_P]),
     "sxb_set_tile_size": (ctypes.c_int, [_P, ctypes.c_int32]),
     "sxb_set_profiling": (ctypes.c_int, [_P, ctypes.c_int32]),
     "sxb_profile_entry": (ctypes.c_int, [_P, ctypes.c_int32, ctypes.c_char_p, ctypes.c_int32, ctypes.POINTER(ctypes.c_float),
@@ -304,6 +319,20 @@ class MACEB200:
     def unpack_ghost_forces(self, world, send_begin_ptr, indices_ptr, num_rows, in_ptr, totals_ptr):
         _check(self._lib.sxb_unpack_ghost_forces(self._h, int(world), ctypes.c_void_p(send_begin_ptr), ctypes.c_void_p(indices_ptr),
                                                  int(num_rows), ctypes.c_void_p(in_ptr), ctypes.c_void_p(totals_ptr)))
+
+    def set_halo_plan(self, send_indices_ptr, num_send, send_rows_ptr, received_rows_ptr, world, ghost_begin_ptr, force_send_ptr):
+        _check(self._lib.sxb_set_halo_plan(self._h, ctypes.c_void_p(send_indices_ptr), int(num_send), ctypes.c_void_p(send_rows_ptr),
+                                           ctypes.c_void_p(received_rows_ptr), int(world), ctypes.c_void_p(ghost_begin_ptr),
+                                           ctypes.c_void_p(force_send_ptr)))
+
+    def distributed_abort(self):
+        _check(self._lib.sxb_distributed_abort(self._h))
+
+    def distributed_replayed(self, generation, launches):
+        _check(self._lib.sxb_distributed_replayed(self._h, int(generation), int(launches)))
+
+    def internal_rows(self, indices_ptr, count, out_ptr):
+        _check(self._lib.sxb_internal_rows(self._h, ctypes.c_void_p(indices_ptr), int(count), ctypes.c_void_p(out_ptr)))
 
     def set_tile_size(self, receivers_per_tile: int):
         """Tiled streaming with a reusable workspace (0 = off); prepare the graph again afterwards."""

@@ -27,8 +27,9 @@ def main():
         pos, cell, types = pkg.modelgen.srtio3(tuple(4 * g for g in grid), 0.05, 9)
         calc = pkg.distributed.DistributedCalculator(path, pkg.MACEB200, skin=0.5, device=local)
         calc.prepare(pos, cell, types)
-        out = calc.calculate()
-        out = calc.calculate()
+        for _ in range(4):       # two eager evaluations, then the captured step and one replay
+            out = calc.calculate()
+        assert calc._step_graph is not None or os.environ.get("SXB_STEP_GRAPH") == "0", "the step was not captured"
         forces = torch.zeros((len(pos), 3), dtype=torch.float64, device="cuda")
         forces[torch.from_numpy(out["owned"]).cuda()] = out["forces"]
         dist.all_reduce(forces)
@@ -39,6 +40,8 @@ def main():
                       "dS": float(np.abs(out["stress"] - single["stress"]).max()), "world": world, "atoms": len(pos)}
             Path(sys.argv[1]).write_text(json.dumps(result))
             print(result)
+        calc.close()
+    torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()
 
