@@ -65,6 +65,12 @@ int sxb_device_count(void);
  * (symmetrix/source/cpp/mace_kokkos.cpp:2040-2087). */
 int sxb_model_info_get(const sxb_evaluator* evaluator, sxb_model_info* out);
 int sxb_atomic_numbers(const sxb_evaluator* evaluator, int32_t* out, int32_t capacity);
+int sxb_atomic_energies(const sxb_evaluator* evaluator, double* out, int32_t capacity);
+/* Bytes of device memory the evaluator's graph and work buffers hold, and the device's free / total
+ * memory: the numbers behind the reference's execution-plan report (libsymmetrix/source/execution_plan.hpp:
+ * 32-50: estimated_bytes, available_bytes).  Any output may be NULL. */
+int sxb_memory_report(const sxb_evaluator* evaluator, int64_t* workspace_bytes, int64_t* device_free_bytes,
+                      int64_t* device_total_bytes);
 
 /* Replaces _prepare_periodic_factorized_graph(node_types, positions, cell, inverse_cell,
  * neighbor_cutoff) -> {generation, num_edges} (symmetrix/source/cpp/mace_kokkos.cpp:1580-1603;
@@ -83,6 +89,21 @@ int sxb_prepare_periodic_graph(sxb_evaluator* evaluator, int32_t num_nodes, cons
 int sxb_prepare_graph(sxb_evaluator* evaluator, int32_t num_nodes, const int32_t* node_types,
                       const int32_t* num_neigh, const int32_t* neigh_indices, const int32_t* shifts,
                       const double* cell, uint64_t* generation);
+
+/* Replace _prepare_factorized_geometry / _prepare_factorized_fractional_geometry (fractional != 0) and
+ * _update_factorized_cell (symmetrix/source/cpp/mace_kokkos.cpp:1608-1685; device side
+ * update_prepared_factorized_positions_geometry, mace_kokkos_factorized_lifecycle.cpp:2915-3076) for a
+ * graph prepared with sxb_prepare_graph without shifts (the calculator's host-graph branch, used for
+ * non-periodic and mixed-periodic systems, calculator.py:3274-3359): the reference positions
+ * f64[3*num_nodes] (Cartesian, or fractional), the edge vectors of that state f64[3*num_edges] in the
+ * caller's edge order (Cartesian, or fractional), the cell pair and the periodic axes int32[3].
+ * sxb_compute_positions then moves the edges with the atoms: xyz_ij = ref_xyz_ij + d_j - d_i with the
+ * displacements reduced to the nearest image along periodic axes.  sxb_update_cell swaps the cell of a
+ * fractional reference (an affine deformation keeps the graph) or of a graph with integer shifts. */
+int sxb_prepare_reference_geometry(sxb_evaluator* evaluator, uint64_t generation, int32_t fractional,
+                                   const double* reference_positions, const double* reference_xyz, const double* cell,
+                                   const double* inverse_cell, const int32_t* pbc);
+int sxb_update_cell(sxb_evaluator* evaluator, uint64_t generation, const double* cell, const double* inverse_cell);
 
 /* Copies the prepared graph out in the caller's node order and the reference's edge order
  * (the arrays KokkosNeighborGraph holds: receiver_offsets, sources, shifts;

@@ -156,6 +156,29 @@ int sxb_atomic_numbers(const sxb_evaluator* ev, int32_t* out, int32_t capacity)
     });
 }
 
+int sxb_atomic_energies(const sxb_evaluator* ev, double* out, int32_t capacity)
+{
+    return guarded([&] {
+        require(ev, "evaluator");
+        require(out, "out");
+        const auto& e = ev->impl.model().atomic_energies;
+        if (capacity < static_cast<int32_t>(e.size())) throw std::invalid_argument("atomic_energies buffer is too small.");
+        for (std::size_t i = 0; i < e.size(); ++i) out[i] = e[i];
+    });
+}
+
+int sxb_memory_report(const sxb_evaluator* ev, int64_t* workspace_bytes, int64_t* device_free_bytes, int64_t* device_total_bytes)
+{
+    return guarded([&] {
+        require(ev, "evaluator");
+        std::size_t free_bytes = 0, total_bytes = 0;
+        SXB_CUDA(cudaMemGetInfo(&free_bytes, &total_bytes));
+        if (workspace_bytes) *workspace_bytes = static_cast<int64_t>(ev->impl.workspace_bytes());
+        if (device_free_bytes) *device_free_bytes = static_cast<int64_t>(free_bytes);
+        if (device_total_bytes) *device_total_bytes = static_cast<int64_t>(total_bytes);
+    });
+}
+
 int sxb_prepare_periodic_graph(sxb_evaluator* ev, int32_t num_nodes, const int32_t* node_types, const double* positions,
                                const double* cell, const double* inverse_cell, double neighbor_cutoff, uint64_t* generation,
                                int64_t* num_edges)
@@ -176,6 +199,25 @@ int sxb_prepare_graph(sxb_evaluator* ev, int32_t num_nodes, const int32_t* node_
         require(ev, "evaluator"); require(node_types, "node_types"); require(num_neigh, "num_neigh");
         require(neigh_indices, "neigh_indices"); require(generation, "generation");
         *generation = ev->impl.prepare_graph(num_nodes, node_types, num_neigh, neigh_indices, shifts, cell);
+    });
+}
+
+int sxb_prepare_reference_geometry(sxb_evaluator* ev, uint64_t generation, int32_t fractional, const double* reference_positions,
+                                   const double* reference_xyz, const double* cell, const double* inverse_cell, const int32_t* pbc)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(reference_positions, "reference_positions"); require(cell, "cell");
+        require(inverse_cell, "inverse_cell"); require(pbc, "pbc");
+        if (ev->impl.num_edges() > 0) require(reference_xyz, "reference_xyz");
+        ev->impl.prepare_reference_geometry(generation, fractional != 0, reference_positions, reference_xyz, cell, inverse_cell, pbc);
+    });
+}
+
+int sxb_update_cell(sxb_evaluator* ev, uint64_t generation, const double* cell, const double* inverse_cell)
+{
+    return guarded([&] {
+        require(ev, "evaluator"); require(cell, "cell"); require(inverse_cell, "inverse_cell");
+        ev->impl.update_cell(generation, cell, inverse_cell);
     });
 }
 

@@ -136,6 +136,66 @@ __global__ void geometry_from_positions_kernel(int num_nodes, const int* __restr
     }
 }
 
+// Per-step geometry from a reference state (graphs built by the caller without integer shifts):
+//   Cartesian  (kFractional = false): xyz_ij = ref_xyz_ij + d_j - d_i,  d = position - reference position
+//   fractional (kFractional = true):  xyz_ij = (ref_fxyz_ij + f_j - f_i) . cell,  f = position . cell^-1 - reference
+// where d / f are reduced to the nearest image along the periodic axes, so an atom that crossed the cell
+// boundary since the reference keeps its edges (reference: update_prepared_factorized_positions_geometry,
+// libsymmetrix/source/mace_kokkos_factorized_lifecycle.cpp:2915-3076).  One warp per receiver.
+template <bool kFractional>
+__global__ void geometry_from_reference_kernel(int num_nodes, const int* __restrict__ first, const int* __restrict__ sources,
+                                               const double* __restrict__ positions, const int* __restrict__ original,
+                                               const double* __restrict__ reference, const double* __restrict__ reference_xyz,
+                                               const int* __restrict__ edge_map, const double* __restrict__ cell,
+                                               const double* __restrict__ inv_cell, int pbc_mask, EdgeGeom* __restrict__ geom,
+                                               int* __restrict__ error_flag)
+{
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= num_nodes) return;
+    // displacement of a node from its reference, in fractional coordinates reduced to the nearest image
+    auto displacement = [&](int caller_node, double* f) {
+        const double px = positions[3 * caller_node], py = positions[3 * caller_node + 1], pz = positions[3 * caller_node + 2];
+        double q[3];
+        if (kFractional) {
+            for (int a = 0; a < 3; ++a) q[a] = px * inv_cell[a] + py * inv_cell[3 + a] + pz * inv_cell[6 + a] - reference[3 * caller_node + a];
+        } else {
+            const double dx = px - reference[3 * caller_node], dy = py - reference[3 * caller_node + 1], dz = pz - reference[3 * caller_node + 2];
+            for (int a = 0; a < 3; ++a) q[a] = dx * inv_cell[a] + dy * inv_cell[3 + a] + dz * inv_cell[6 + a];
+        }
+        for (int a = 0; a < 3; ++a) f[a] = ((pbc_mask >> a) & 1) ? q[a] - rint(q[a]) : q[a];
+    };
+    double fi[3];
+    displacement(original[warp], fi);
+    const int begin = first[warp], end = first[warp + 1];
+    for (int e = begin + lane; e < end; e += 32) {
+        double fj[3];
+        displacement(original[sources[e]], fj);
+        const size_t o = 3 * static_cast<size_t>(edge_map[e]);
+        double dx, dy, dz;
+        if (kFractional) {
+            const double gx = reference_xyz[o] + fj[0] - fi[0], gy = reference_xyz[o + 1] + fj[1] - fi[1],
+                         gz = reference_xyz[o + 2] + fj[2] - fi[2];
+            dx = gx * cell[0] + gy * cell[3] + gz * cell[6];
+            dy = gx * cell[1] + gy * cell[4] + gz * cell[7];
+            dz = gx * cell[2] + gy * cell[5] + gz * cell[8];
+        } else {
+            const double gx = fj[0] - fi[0], gy = fj[1] - fi[1], gz = fj[2] - fi[2];
+            dx = reference_xyz[o] + gx * cell[0] + gy * cell[3] + gz * cell[6];
+            dy = reference_xyz[o + 1] + gx * cell[1] + gy * cell[4] + gz * cell[7];
+            dz = reference_xyz[o + 2] + gx * cell[2] + gy * cell[5] + gz * cell[8];
+        }
+        const double r = sqrt(dx * dx + dy * dy + dz * dz);
+        if (!(r > 0.0) || !isfinite(r)) atomicOr(error_flag, 1);
+        EdgeGeom g;
+        g.ux = static_cast<float>(dx / r);
+        g.uy = static_cast<float>(dy / r);
+        g.uz = static_cast<float>(dz / r);
+        g.r = static_cast<float>(r);
+        geom[e] = g;
+    }
+}
+
 // Geometry from caller-supplied edge vectors (original edge order == internal edge order of
 // each receiver; ``edge_map`` gives the caller's edge index of every internal edge).
 __global__ void geometry_from_vectors_kernel(long num_edges, const double* __restrict__ xyz,

@@ -335,6 +335,7 @@ void Evaluator::install_graph(int num_receivers, int num_nodes, const std::vecto
     mirror_valid_ = false;
     phase_ = 0;
     halo_plan_ = HaloPlan{};      // buffers of a decomposed run belong to the previous graph
+    geometry_mode_ = 0;           // a reference geometry belongs to the graph it was given for
 }
 
 namespace {
@@ -343,9 +344,18 @@ namespace {
 // thinner than the cutoff; reach = ceil(cutoff * bins / spacing) + 1 bins on either side.  These are
 // the extents of the reference's builder (libsymmetrix/source/neighbor_graph_kokkos.cpp:84-120), which
 // fixes the candidate order.
+void validate_cell_pair(const double* cell, const double* inverse_cell);
+CellGrid finish_cell_grid(const double* inverse_cell, double cutoff);
+
 CellGrid plan_cell_grid(const double* cell, const double* inverse_cell, double cutoff)
 {
     if (!std::isfinite(cutoff) || !(cutoff > 0.0)) throw std::invalid_argument("Neighbor cutoff must be finite and positive.");
+    validate_cell_pair(cell, inverse_cell);
+    return finish_cell_grid(inverse_cell, cutoff);
+}
+
+void validate_cell_pair(const double* cell, const double* inverse_cell)
+{
     double worst = 0.0;
     bool finite = true;
     for (int q = 0; q < 9; ++q) finite = finite && std::isfinite(cell[q]) && std::isfinite(inverse_cell[q]);
@@ -356,6 +366,10 @@ CellGrid plan_cell_grid(const double* cell, const double* inverse_cell, double c
             worst = std::max(worst, std::abs(dot - (r == c ? 1.0 : 0.0)));
         }
     if (worst > 1e-9) throw std::invalid_argument("inverse_cell is not the inverse of cell.");
+}
+
+CellGrid finish_cell_grid(const double* inverse_cell, double cutoff)
+{
     CellGrid grid;
     std::size_t total = 1;
     for (int axis = 0; axis < 3; ++axis) {
@@ -547,6 +561,45 @@ std::uint64_t Evaluator::prepare_graph_csr(int num_receivers, int num_nodes, con
     if (status & 16) throw std::invalid_argument("neigh_indices entry is out of range.");
     install_graph(R, num_nodes, types, E, false);
     return generation_;
+}
+
+// Reference state for graphs the caller built without integer shifts: reference positions (Cartesian
+// or fractional), the edge vectors of that state in the caller's edge order, the cell and the periodic
+// axes.  Evaluations from positions then follow the atoms from that reference
+// (reference: prepare_factorized_geometry / prepare_factorized_fractional_geometry / update_factorized_cell,
+// symmetrix/source/cpp/mace_kokkos.cpp:1608-1685).
+void Evaluator::prepare_reference_geometry(std::uint64_t generation, bool fractional, const double* reference_positions,
+                                           const double* reference_xyz, const double* cell, const double* inverse_cell, const int* pbc)
+{
+    check_generation(generation);
+    if (has_shifts_) throw std::invalid_argument("The prepared graph carries periodic shifts; it needs no reference geometry.");
+    SXB_CUDA(cudaSetDevice(device_));
+    validate_cell_pair(cell, inverse_cell);
+    reference_positions_.reserve(3 * static_cast<std::size_t>(num_nodes_));
+    reference_xyz_.reserve_with_slack(3 * static_cast<std::size_t>(std::max<long>(num_edges_, 1)));
+    SXB_CUDA(cudaMemcpyAsync(reference_positions_.ptr, reference_positions, sizeof(double) * 3 * num_nodes_, cudaMemcpyHostToDevice, stream_));
+    if (num_edges_ > 0)
+        SXB_CUDA(cudaMemcpyAsync(reference_xyz_.ptr, reference_xyz, sizeof(double) * 3 * num_edges_, cudaMemcpyHostToDevice, stream_));
+    SXB_CUDA(cudaMemcpyAsync(cell_.ptr, cell, 9 * sizeof(double), cudaMemcpyHostToDevice, stream_));
+    SXB_CUDA(cudaMemcpyAsync(inv_cell_.ptr, inverse_cell, 9 * sizeof(double), cudaMemcpyHostToDevice, stream_));
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+    pbc_mask_ = (pbc[0] ? 1 : 0) | (pbc[1] ? 2 : 0) | (pbc[2] ? 4 : 0);
+    geometry_mode_ = fractional ? 2 : 1;
+    drop_step_graphs();
+    have_results_ = false;
+}
+
+void Evaluator::update_cell(std::uint64_t generation, const double* cell, const double* inverse_cell)
+{
+    check_generation(generation);
+    if (geometry_mode_ != 2 && !has_shifts_)
+        throw std::invalid_argument("A cell update needs fractional reference geometry or a graph with periodic shifts.");
+    SXB_CUDA(cudaSetDevice(device_));
+    validate_cell_pair(cell, inverse_cell);
+    SXB_CUDA(cudaMemcpyAsync(cell_.ptr, cell, 9 * sizeof(double), cudaMemcpyHostToDevice, stream_));
+    SXB_CUDA(cudaMemcpyAsync(inv_cell_.ptr, inverse_cell, 9 * sizeof(double), cudaMemcpyHostToDevice, stream_));
+    SXB_CUDA(cudaStreamSynchronize(stream_));
+    have_results_ = false;
 }
 
 void Evaluator::check_generation(std::uint64_t generation) const
@@ -1161,9 +1214,19 @@ void Evaluator::enqueue_phases(int phases, const double* positions, bool upload_
             SXB_CUDA(cudaMemcpyAsync(positions_.ptr, host_stage_, sizeof(double) * 3 * num_nodes_, cudaMemcpyHostToDevice, stream_));
         if (positions != nullptr) {
             SXB_CUDA(cudaMemsetAsync(error_flag_.ptr, 0, sizeof(int), stream_));
-            geometry_from_positions_kernel<<<blocks_for(static_cast<long>(num_receivers_) * 32, 256), 256, 0, stream_>>>(
-                num_receivers_, first_.ptr, sources_.ptr, has_shifts_ ? shifts_.ptr : nullptr, positions, original_.ptr, cell_.ptr,
-                geom_.ptr, error_flag_.ptr);
+            const int grid = blocks_for(static_cast<long>(num_receivers_) * 32, 256);
+            if (geometry_mode_ == 1)
+                geometry_from_reference_kernel<false><<<grid, 256, 0, stream_>>>(
+                    num_receivers_, first_.ptr, sources_.ptr, positions, original_.ptr, reference_positions_.ptr, reference_xyz_.ptr,
+                    edge_map_.ptr, cell_.ptr, inv_cell_.ptr, pbc_mask_, geom_.ptr, error_flag_.ptr);
+            else if (geometry_mode_ == 2)
+                geometry_from_reference_kernel<true><<<grid, 256, 0, stream_>>>(
+                    num_receivers_, first_.ptr, sources_.ptr, positions, original_.ptr, reference_positions_.ptr, reference_xyz_.ptr,
+                    edge_map_.ptr, cell_.ptr, inv_cell_.ptr, pbc_mask_, geom_.ptr, error_flag_.ptr);
+            else
+                geometry_from_positions_kernel<<<grid, 256, 0, stream_>>>(
+                    num_receivers_, first_.ptr, sources_.ptr, has_shifts_ ? shifts_.ptr : nullptr, positions, original_.ptr, cell_.ptr,
+                    geom_.ptr, error_flag_.ptr);
             launches_ += 1;
         }
         run_pipeline(phases);

@@ -42,6 +42,9 @@ public:
                                 const int* shifts, const double* cell);
     std::uint64_t prepare_graph_csr(int num_receivers, int num_nodes, const int* node_types, const int* num_neigh,
                                     const int* neigh_indices, bool on_device);
+    void prepare_reference_geometry(std::uint64_t generation, bool fractional, const double* reference_positions,
+                                    const double* reference_xyz, const double* cell, const double* inverse_cell, const int* pbc);
+    void update_cell(std::uint64_t generation, const double* cell, const double* inverse_cell);
     void get_graph(std::uint64_t generation, int* first, int* sources, int* shifts);
     void check_generation(std::uint64_t generation) const;
 
@@ -87,6 +90,14 @@ public:
     const double* device_forces() const { return forces_out_.ptr; }
     const double* device_virial() const { return totals_.ptr + 1; }
     long launches() const { return launches_; }
+    std::size_t workspace_bytes() const
+    {
+        return geom_.bytes() + A0_.bytes() + A0_adj_.bytes() + M0_.bytes() + M0_adj_.bytes() + H1_.bytes() + H1_adj_.bytes() + Phi1_.bytes()
+               + dPhi1_.bytes() + A1_.bytes() + A1_adj_.bytes() + M1_.bytes() + M1_adj_.bytes() + H2_.bytes() + H2_adj_.bytes()
+               + first_.bytes() + sources_.bytes() + shifts_.bytes() + edge_map_.bytes() + first_caller_.bytes() + sources_caller_.bytes()
+               + shifts_caller_.bytes() + forces_.bytes() + forces_out_.bytes() + positions_.bytes() + edge_forces_.bytes()
+               + r0_table_.bytes() + r1_table_.bytes();
+    }
     // Per-kernel device times of the last compute (CUDA events on the evaluator's stream), only
     // collected while profiling is switched on.
     void set_profiling(bool enabled) { profiling_ = enabled; }
@@ -183,6 +194,9 @@ private:
     DeviceBuffer<int> first_, sources_, shifts_, edge_map_, original_, internal_of_;
     DeviceBuffer<unsigned char> atype_, element_;
     DeviceBuffer<double> cell_, inv_cell_, positions_;
+    // reference state of a caller-built graph: 0 none, 1 Cartesian, 2 fractional
+    DeviceBuffer<double> reference_positions_, reference_xyz_;
+    int geometry_mode_ = 0, pbc_mask_ = 0;
 
     // work buffers
     DeviceBuffer<EdgeGeom> geom_;

@@ -46,6 +46,10 @@ SIGNATURES = {
     "sxb_device_count": (ctypes.c_int, []),
     "sxb_model_info_get": (ctypes.c_int, [_P, ctypes.POINTER(ModelInfo)]),
     "sxb_atomic_numbers": (ctypes.c_int, [_P, _P, ctypes.c_int32]),
+    "sxb_atomic_energies": (ctypes.c_int, [_P, _P, ctypes.c_int32]),
+    "sxb_memory_report": (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64)]),
+    "sxb_prepare_reference_geometry": (ctypes.c_int, [_P, ctypes.c_uint64, ctypes.c_int32, _P, _P, _P, _P, _P]),
+    "sxb_update_cell": (ctypes.c_int, [_P, ctypes.c_uint64, _P, _P]),
     "sxb_prepare_periodic_graph": (ctypes.c_int, [_P, ctypes.c_int32, _P, _P, _P, _P, ctypes.c_double,
                                                   ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_int64)]),
     "sxb_prepare_graph": (ctypes.c_int, [_P, ctypes.c_int32, _P, _P, _P, _P, _P, ctypes.POINTER(ctypes.c_uint64)]),
@@ -187,8 +191,14 @@ class MACEB200:
         z = np.zeros(info.num_elements, dtype=np.int32)
         _check(lib.sxb_atomic_numbers(self._h, z.ctypes.data, len(z)))
         self.atomic_numbers = z.tolist()
+        e0 = np.zeros(info.num_elements, dtype=np.float64)
+        _check(lib.sxb_atomic_energies(self._h, e0.ctypes.data, len(e0)))
+        self.atomic_energies = e0.tolist()
+        self.single_layer_readout = False
+        self.h1_affine_mode = "m0_composite"
         self._num_nodes = 0
         self._num_edges = 0
+        self._tile_size = 0
 
     def __del__(self):
         if getattr(self, "_h", None):
@@ -227,6 +237,64 @@ class MACEB200:
                                            neigh_indices.ctypes.data, sp, cp, ctypes.byref(gen)))
         self._num_nodes, self._num_edges, self._num_receivers = int(num_nodes), int(neigh_indices.size), int(num_nodes)
         return int(gen.value)
+
+    # -- what else the reference's calculator reads from its evaluator (calculator.py:1956-2640, 3162-3403) ------
+    def supports_streamed_edges(self):
+        return True
+
+    @property
+    def streamed_edges_mode(self):
+        """Edge state is always regenerated inside the kernels and never stored graph-wide: the reference's
+        ``direct`` streamed mode."""
+        return "direct"
+
+    def set_streamed_edges(self, mode):
+        if str(mode) not in ("direct", "generic", "auto", "True", "true"):
+            raise ValueError("this evaluator only runs streamed edges (mode 'direct'); got %r" % (mode,))
+
+    def _validate_graph_cardinality(self, num_receivers, num_feature_nodes, num_edges):
+        limit = 2 ** 31 - 1
+        if num_receivers < 0 or num_feature_nodes < num_receivers:
+            raise ValueError("Graph receivers must not outnumber the feature nodes.")
+        if num_feature_nodes > limit or num_edges > limit:
+            raise ValueError("Graph exceeds 32-bit node or edge indexing.")
+
+    def _load_jit_cuda_plugin(self, path, persistent_blocks_per_compute_unit=4):
+        raise RuntimeError("the layer-1 kernels of this library are compiled in; it loads no kernel plugin")
+
+    @property
+    def execution_plan_report(self):
+        """Shape of the reference's plan report (libsymmetrix/source/execution_plan.hpp:32-50) for the one plan this
+        library has per setting: whole-graph work buffers, or tiled streaming with a reusable tile workspace."""
+        work, free, total = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()
+        _check(self._lib.sxb_memory_report(self._h, ctypes.byref(work), ctypes.byref(free), ctypes.byref(total)))
+        plan = "tiled-streaming(%d)" % self._tile_size if self._tile_size else "streamed-edges"
+        return {"requested_algorithm": "direct", "requested_profile": "capacity" if self._tile_size else "speed",
+                "selection_source": "request", "state": "resolved" if self._num_nodes else "pending", "selected_id": plan,
+                "selection_reason": "the only plan of this evaluator for the current tile setting",
+                "available_bytes": int(free.value), "reserve_bytes": 0, "boundary_attempt": False,
+                "candidates": [{"id": plan, "qualified": True, "estimated_bytes": int(work.value), "reason": "in use"}]}
+
+    def _prepare_factorized_geometry(self, execution_graph_generation, reference_positions, reference_xyz, cell, inverse_cell, pbc):
+        self._reference_geometry(execution_graph_generation, False, reference_positions, reference_xyz, cell, inverse_cell, pbc)
+
+    def _prepare_factorized_fractional_geometry(self, execution_graph_generation, fractional_positions, fractional_xyz, cell,
+                                                inverse_cell, pbc):
+        self._reference_geometry(execution_graph_generation, True, fractional_positions, fractional_xyz, cell, inverse_cell, pbc)
+
+    def _reference_geometry(self, generation, fractional, positions, xyz, cell, inverse_cell, pbc):
+        positions, xyz = _f64(positions).reshape(-1), _f64(xyz).reshape(-1)
+        cell, inverse_cell, pbc = _f64(cell).reshape(-1), _f64(inverse_cell).reshape(-1), _i32(pbc).reshape(-1)
+        if positions.size != 3 * self._num_nodes or xyz.size != 3 * self._num_edges or cell.size != 9 or inverse_cell.size != 9 or pbc.size != 3:
+            raise ValueError("Reference geometry extents do not match the prepared graph.")
+        _check(self._lib.sxb_prepare_reference_geometry(self._h, int(generation), int(fractional), positions.ctypes.data, xyz.ctypes.data,
+                                                        cell.ctypes.data, inverse_cell.ctypes.data, pbc.ctypes.data))
+
+    def _update_factorized_cell(self, execution_graph_generation, cell, inverse_cell):
+        cell, inverse_cell = _f64(cell).reshape(-1), _f64(inverse_cell).reshape(-1)
+        if cell.size != 9 or inverse_cell.size != 9:
+            raise ValueError("Cell extents are inconsistent.")
+        _check(self._lib.sxb_update_cell(self._h, int(execution_graph_generation), cell.ctypes.data, inverse_cell.ctypes.data))
 
     def prepare_local_graph(self, num_receivers, node_types, positions, neighbor_cutoff):
         """Graph of an open node set whose first ``num_receivers`` nodes are receivers (owned atoms) and
@@ -337,6 +405,7 @@ class MACEB200:
     def set_tile_size(self, receivers_per_tile: int):
         """Tiled streaming with a reusable workspace (0 = off); prepare the graph again afterwards."""
         _check(self._lib.sxb_set_tile_size(self._h, int(receivers_per_tile)))
+        self._tile_size = int(receivers_per_tile)
 
     def set_stream(self, stream_ptr):
         _check(self._lib.sxb_set_stream(self._h, ctypes.c_void_p(stream_ptr)))
@@ -473,10 +542,57 @@ def reduce_edge_forces(num_nodes, edge_receivers, edge_sources, edge_forces, xyz
     return forces, stress
 
 
+def host_neighbor_list(positions, cell, pbc, cutoff):
+    """Receiver-major neighbor list of a system with any mix of periodic axes, built on the host the way
+    the reference's calculator does for non-periodic and mixed-periodic systems (its host-graph branch,
+    symmetrix/source/symmetrix/calculator.py:2973-2996): images of the atoms along the periodic axes out
+    to the cutoff, then a k-d tree.  Returns (num_neigh int32[N], neigh_indices int32[E], xyz f64[E,3])."""
+    from scipy.spatial import cKDTree
+
+    positions = _f64(positions).reshape(-1, 3)
+    cell = _f64(cell).reshape(3, 3)
+    pbc = [bool(p) for p in pbc]
+    n = len(positions)
+    if any(pbc):
+        inv = np.linalg.inv(cell)
+        spacing = 1.0 / np.sqrt((inv ** 2).sum(axis=0))
+        reach = [int(np.ceil(cutoff / spacing[a])) if pbc[a] else 0 for a in range(3)]
+        frac = positions @ inv
+        for a in range(3):
+            if pbc[a]:
+                frac[:, a] -= np.floor(frac[:, a])
+        home = frac @ cell
+    else:
+        reach, home = [0, 0, 0], positions
+    images, owners = [], []
+    for sx in range(-reach[0], reach[0] + 1):
+        for sy in range(-reach[1], reach[1] + 1):
+            for sz in range(-reach[2], reach[2] + 1):
+                images.append(home + np.array([sx, sy, sz], dtype=np.float64) @ cell)
+                owners.append(np.arange(n))
+    images, owners = np.concatenate(images), np.concatenate(owners)
+    zero_image = (len(images) // n) // 2          # the (0, 0, 0) image sits in the middle of the loop order
+    tree = cKDTree(images)
+    lists = tree.query_ball_point(home, cutoff)
+    num_neigh = np.zeros(n, dtype=np.int32)
+    neigh, xyz = [], []
+    for i, row in enumerate(lists):
+        row = np.array(sorted(row), dtype=np.int64)
+        row = row[row != zero_image * n + i]
+        num_neigh[i] = len(row)
+        neigh.append(owners[row])
+        xyz.append(images[row] - home[i])
+    neigh = np.concatenate(neigh).astype(np.int32) if n else np.zeros(0, dtype=np.int32)
+    xyz = np.concatenate(xyz) if n else np.zeros((0, 3))
+    return num_neigh, neigh, xyz
+
+
 class Calculator:
     """Minimal stand-in for the reference's ASE calculator hot path (``Symmetrix.calculate``,
     symmetrix/source/symmetrix/calculator.py:3934-4021): Verlet-skin neighbor cache (rebuild when
-    the largest displacement exceeds skin/2, :2894-2899), device graph builder, evaluation from
+    the largest displacement exceeds skin/2, :2894-2899), reuse of the list under an affine change of a
+    fully periodic cell (:2857-2888), device graph builder for fully periodic systems, host graph with a
+    reference geometry for non-periodic and mixed-periodic ones (:2973-2996, 3274-3359), evaluation from
     positions, and result assembly (:3821-3894)."""
 
     def __init__(self, model_path, skin: float = 0.5, device: int = 0, head: str = ""):
@@ -485,32 +601,81 @@ class Calculator:
         self._generation = 0
         self._reference_positions = None
         self._reference_cell = None
+        self._reference_fractional = None
         self._types = None
+        self._pbc = None
         self.rebuilds = 0
+        self.cell_updates = 0
 
-    def calculate(self, positions, cell, node_types):
+    def _can_reuse(self, positions, cell, node_types, pbc):
+        if self._generation == 0 or self._reference_positions.shape != positions.shape:
+            return False, False
+        if not np.array_equal(self._types, node_types) or self._pbc != pbc:
+            return False, False
+        if np.array_equal(self._reference_cell, cell):
+            delta = positions - self._reference_positions
+            if any(pbc) and not all(pbc):
+                # the reference geometry of the host graph follows an atom across a periodic boundary: measure the
+                # displacement to the nearest image (the device graph of a fully periodic cell does not, it stores shifts)
+                frac = delta @ self._work_inverse
+                for a in range(3):
+                    if pbc[a]:
+                        frac[:, a] -= np.round(frac[:, a])
+                delta = frac @ self._work_cell
+            moved = np.sqrt((delta ** 2).sum(axis=1).max())
+            return moved <= 0.5 * self.skin, False
+        if not all(pbc):
+            return False, False
+        # affine change of a periodic cell: the list stays valid while no pair distance can have changed by more
+        # than the skin -- largest fractional displacement and the strain of the cell, both measured against the cutoff
+        frac = positions @ np.linalg.inv(cell)
+        dfrac = frac - self._reference_fractional
+        dfrac -= np.round(dfrac)
+        moved = np.sqrt((((dfrac @ cell)) ** 2).sum(axis=1).max())
+        strain = np.linalg.norm(np.linalg.inv(self._reference_cell) @ cell - np.eye(3), ord=2)
+        reach = self.evaluator.r_cut + self.skin
+        return moved + strain * reach <= 0.5 * self.skin, True
+
+    def calculate(self, positions, cell, node_types, pbc=(True, True, True)):
         positions = _f64(positions).reshape(-1, 3)
         cell = _f64(cell).reshape(3, 3)
         node_types = _i32(node_types)
-        reuse = (self._generation != 0 and self._reference_positions.shape == positions.shape
-                 and np.array_equal(self._reference_cell, cell) and np.array_equal(self._types, node_types)
-                 and np.sqrt(((positions - self._reference_positions) ** 2).sum(axis=1).max()) <= 0.5 * self.skin)
-        if not reuse:
-            result = self.evaluator._prepare_periodic_factorized_graph(
-                node_types, positions, cell, np.linalg.inv(cell), self.evaluator.r_cut + self.skin)
-            self._generation = result["generation"]
+        pbc = tuple(bool(p) for p in pbc)
+        ev = self.evaluator
+        reuse, new_cell = self._can_reuse(positions, cell, node_types, pbc)
+        if reuse and new_cell:
+            ev._update_factorized_cell(self._generation, cell, np.linalg.inv(cell))
+            self.cell_updates += 1
+        elif not reuse:
+            cutoff = ev.r_cut + self.skin
+            if all(pbc):
+                result = ev._prepare_periodic_factorized_graph(node_types, positions, cell, np.linalg.inv(cell), cutoff)
+                self._generation = result["generation"]
+            else:
+                # axes that are not periodic get a stand-in cell vector long enough that nothing wraps
+                work_cell = cell.copy()
+                span = np.ptp(positions, axis=0).max() + 4.0 * cutoff + 1.0
+                for a in range(3):
+                    if not pbc[a]:
+                        work_cell[a] = 0.0
+                        work_cell[a, a] = span
+                self._work_cell, self._work_inverse = work_cell, np.linalg.inv(work_cell)
+                num_neigh, neigh, xyz = host_neighbor_list(positions, work_cell, pbc, cutoff)
+                ev._validate_graph_cardinality(len(positions), len(positions), len(neigh))
+                self._generation = ev._prepare_factorized_graph(len(positions), node_types, num_neigh, neigh, node_types[neigh])
+                ev._prepare_factorized_geometry(self._generation, positions, xyz, work_cell, np.linalg.inv(work_cell),
+                                                np.array(pbc, dtype=np.int32))
             self._reference_positions = positions.copy()
             self._reference_cell = cell.copy()
+            self._reference_fractional = positions @ np.linalg.inv(cell) if all(pbc) else None
             self._types = node_types.copy()
+            self._pbc = pbc
             self.rebuilds += 1
-        ev = self.evaluator
         ev._compute_prepared_factorized_positions(self._generation, positions)
         n = len(node_types)
-        volume = abs(np.linalg.det(cell))
         energies = ev.node_energies
-        return {
-            "energy": float(energies.sum()),
-            "energies": energies,
-            "forces": ev._reduce_atom_forces(n, execution_graph_generation=self._generation),
-            "stress": ev._reduce_stress(volume, execution_graph_generation=self._generation),
-        }
+        out = {"energy": float(energies.sum()), "energies": energies,
+               "forces": ev._reduce_atom_forces(n, execution_graph_generation=self._generation)}
+        if all(pbc):
+            out["stress"] = ev._reduce_stress(abs(np.linalg.det(cell)), execution_graph_generation=self._generation)
+        return out
