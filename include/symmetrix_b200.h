@@ -346,6 +346,17 @@ int sxb_peer_destroy(sxb_peer_exchange_t* exchange);
  * invalidates the prepared graph; prepare again afterwards. */
 int sxb_set_tile_size(sxb_evaluator* evaluator, int32_t receivers_per_tile);
 
+/* Reproducible mode (off by default).  The default kernels add the source adjoint H1_adj and the forces
+ * on source atoms with atomics, whose order -- and so the last bits of the results -- varies between
+ * runs.  With this mode on, the kernels leave one record per edge and fixed-order passes sum them over a
+ * source-sorted schedule, the device counterpart of the reference's source schedule and source-owner
+ * accumulation (source_offsets / source_edges, libsymmetrix/source/mace_kokkos_factorized_lifecycle.cpp:
+ * 2133-2195; symmetrix/source/symmetrix/jit_codegen.py:1018-1109): two evaluations of one input give
+ * identical bits.  Costs 4*num_hidden*num_channels bytes per edge (refused above 16 GB), so it is meant
+ * for small and medium systems; not available for hidden irreps 0e+1o+2e or density-scaled models.
+ * The setting invalidates the prepared graph; prepare again afterwards. */
+int sxb_set_deterministic(sxb_evaluator* evaluator, int32_t enabled);
+
 /* Per-stage device times of the last compute (CUDA events on the evaluator's stream around each
  * kernel group), collected only while profiling is enabled; counterpart of the reference's per-stage
  * counters (factorized_last_evaluation_ms ..., libsymmetrix/source/mace_kokkos.hpp:1431-1454).

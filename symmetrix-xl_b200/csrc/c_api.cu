@@ -523,6 +523,11 @@ int sxb_distributed_replayed(sxb_evaluator* ev, uint64_t generation, int64_t lau
     return guarded([&] { require(ev, "evaluator"); ev->impl.mark_phases_replayed(generation, launches); });
 }
 
+int sxb_set_deterministic(sxb_evaluator* ev, int32_t enabled)
+{
+    return guarded([&] { require(ev, "evaluator"); ev->impl.set_deterministic(enabled != 0); });
+}
+
 int sxb_set_tile_size(sxb_evaluator* ev, int32_t receivers_per_tile)
 {
     return guarded([&] { require(ev, "evaluator"); ev->impl.set_tile_size(receivers_per_tile); });

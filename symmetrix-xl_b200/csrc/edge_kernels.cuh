@@ -405,10 +405,14 @@ l0_forward_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
 // channel-partial edge force in ``partial``; after the chunk one thread per edge sums the warps,
 // pushes +f to the source atom, adds -f to the receiver total and f (x) xyz to the virial.
 struct ForceOutputs {
-    double* atom_forces;     // [N][3], internal node order
+    double* atom_forces;     // [N][3], internal node order; nullptr in the reproducible mode (see below)
     double* virial_slots;    // [kVirialSlots][9]
     double* edge_forces;     // optional [E][3] directed forces dE/d(xyz_ij), may be nullptr
     int accumulate_edge;     // 0: overwrite edge_forces, 1: add, 2: add atomically (several kernels share an edge)
+    // Reproducible mode: nothing is accumulated atomically.  The kernels leave the directed force of
+    // every edge in edge_forces and the source adjoint of every edge in edge_source_adjoint
+    // [E][num_hidden][C]; fixed-order passes over the source schedule (deterministic_kernels.cuh) sum them.
+    float* edge_source_adjoint;
 };
 
 __device__ __forceinline__ void warp_reduce3(float& a, float& b, float& c)
@@ -480,9 +484,11 @@ __device__ __forceinline__ void flush_chunk_forces(ForceScratch<kMaxWarps>& fs, 
         // directed force dE/d(xyz_ij) with the reference's sign: force -= adjoint * (...)
         const double ex = -static_cast<double>(px), ey = -static_cast<double>(py), ez = -static_cast<double>(pz);
         const int j = s.index[t].y;
-        atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j), ex);
-        atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 1, ey);
-        atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 2, ez);
+        if (out.atom_forces != nullptr) {
+            atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j), ex);
+            atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 1, ey);
+            atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 2, ez);
+        }
         fx -= ex; fy -= ey; fz -= ez;
         const double len = s.len[t];
         const float4 m = s.misc[t];
@@ -521,6 +527,7 @@ template <int kMaxWarps>
 __device__ __forceinline__ void finish_receiver_forces(ForceScratch<kMaxWarps>& fs, int receiver, const ForceOutputs& out)
 {
     __syncthreads();
+    if (out.atom_forces == nullptr) return;      // reproducible mode: forces and virial come from the per-edge records
     if (threadIdx.x < 3) atomicAdd(out.atom_forces + 3 * static_cast<size_t>(receiver) + threadIdx.x, fs.receiver[threadIdx.x]);
     if (threadIdx.x < 9) {
         const int slot = receiver % kVirialSlots;
@@ -577,9 +584,11 @@ __global__ void zbl_kernel(int num_receivers, const int* __restrict__ first, con
         energy += static_cast<double>(0.5f * v * env);
         const float dEdr = 0.5f * (v * denv + dv * env);
         const double ex = -static_cast<double>(g.ux * dEdr), ey = -static_cast<double>(g.uy * dEdr), ez = -static_cast<double>(g.uz * dEdr);
-        atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j), ex);
-        atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 1, ey);
-        atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 2, ez);
+        if (out.atom_forces != nullptr) {
+            atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j), ex);
+            atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 1, ey);
+            atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 2, ez);
+        }
         rfx -= ex; rfy -= ey; rfz -= ez;
         const double rx = static_cast<double>(r) * g.ux, ry = static_cast<double>(r) * g.uy, rz = static_cast<double>(r) * g.uz;
         vir[0] += ex * rx; vir[1] += ex * ry; vir[2] += ex * rz;
@@ -601,13 +610,15 @@ __global__ void zbl_kernel(int num_receivers, const int* __restrict__ first, con
     }
     if (lane == 0) {
         node_energies[i] += energy;
-        atomicAdd(energy_slots + (i % kVirialSlots), energy);
-        atomicAdd(out.atom_forces + 3 * static_cast<size_t>(i), rfx);
-        atomicAdd(out.atom_forces + 3 * static_cast<size_t>(i) + 1, rfy);
-        atomicAdd(out.atom_forces + 3 * static_cast<size_t>(i) + 2, rfz);
-        const int slot = i % kVirialSlots;
+        if (out.atom_forces != nullptr) {
+            atomicAdd(energy_slots + (i % kVirialSlots), energy);
+            atomicAdd(out.atom_forces + 3 * static_cast<size_t>(i), rfx);
+            atomicAdd(out.atom_forces + 3 * static_cast<size_t>(i) + 1, rfy);
+            atomicAdd(out.atom_forces + 3 * static_cast<size_t>(i) + 2, rfz);
+            const int slot = i % kVirialSlots;
 #pragma unroll
-        for (int q = 0; q < 9; ++q) atomicAdd(out.virial_slots + slot * 9 + q, vir[q]);
+            for (int q = 0; q < 9; ++q) atomicAdd(out.virial_slots + slot * 9 + q, vir[q]);
+        }
     }
 }
 
@@ -812,7 +823,10 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
                 _Pragma("unroll") for (int q = 0; q < 16; ++q) ang[q] = 0.0f;                                        \
                 float radial = 0.0f;                                                                                 \
                 SXB_##NAME##_L1_REVERSE_BODY                                                                         \
-                if (!(kAblate & 1)) {                                                                                \
+                if (out.edge_source_adjoint != nullptr) {   /* reproducible mode: one record per edge, summed later */ \
+                    float* record = out.edge_source_adjoint + static_cast<size_t>(chunk + t) * NH * C + k;           \
+                    _Pragma("unroll") for (int q = 0; q < NH; ++q) record[q * C] = hadj[q];                          \
+                } else if (!(kAblate & 1)) {                                                                         \
                     _Pragma("unroll") for (int q = 0; q < NH; ++q) atomicAdd(H1_adj + source_row + q * C, hadj[q]);  \
                 } else if (hadj[0] + hadj[1] == 123.456f) H1_adj[k] = hadj[2] + hadj[NH - 1];                        \
                 float fx = radial * m.y, fy = radial * m.z, fz = radial * m.w;                                       \

@@ -253,9 +253,11 @@ l0_reverse_warp_kernel(int num_nodes, int node0, const int* __restrict__ first, 
             const double ey = -static_cast<double>(s.force[lane][1] - dens * u.z);
             const double ez = -static_cast<double>(s.force[lane][2] - dens * u.w);
             const int j = s.index[lane].y;
-            atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j), ex);
-            atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 1, ey);
-            atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 2, ez);
+            if (out.atom_forces != nullptr) {
+                atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j), ex);
+                atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 1, ey);
+                atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 2, ez);
+            }
             rfx -= ex; rfy -= ey; rfz -= ez;
             const double len = s.len[lane];
             const float4 m = s.misc[lane];
@@ -282,7 +284,7 @@ l0_reverse_warp_kernel(int num_nodes, int node0, const int* __restrict__ first, 
 #pragma unroll
         for (int q = 0; q < 9; ++q) vir[q] += __shfl_xor_sync(0xffffffffu, vir[q], offset);
     }
-    if (lane == 0) {
+    if (lane == 0 && out.atom_forces != nullptr) {
         atomicAdd(out.atom_forces + 3 * static_cast<size_t>(i), rfx);
         atomicAdd(out.atom_forces + 3 * static_cast<size_t>(i) + 1, rfy);
         atomicAdd(out.atom_forces + 3 * static_cast<size_t>(i) + 2, rfz);

@@ -14,6 +14,7 @@
 #include <limits>
 #include <numeric>
 
+#include "deterministic_kernels.cuh"
 #include "edge_kernels.cuh"
 #include "edge_kernels_dual.cuh"
 #include "edge_kernels_split.cuh"
@@ -307,6 +308,43 @@ void Evaluator::install_graph(int num_receivers, int num_nodes, const std::vecto
     forces_.reserve(ALL * 3);
     forces_out_.reserve(ALL * 3);
     positions_.reserve(ALL * 3);
+    if (deterministic_) {
+        // source schedule: edge ids sorted by source (stable, so ascending edge index inside a source) and the
+        // offsets of each source's run; plus one record per edge for the source adjoint and the directed force
+        if (model_.shape_id == 2) throw std::invalid_argument("The reproducible mode is not available for hidden irreps 0e+1o+2e.");
+        if (model_.a0_scaled || model_.a1_scaled)
+            throw std::invalid_argument("The reproducible mode is not available for density-scaled models.");
+        const std::size_t record_floats = static_cast<std::size_t>(num_edges) * NH * C;
+        if (record_floats * sizeof(float) > (16ull << 30))
+            throw std::length_error("The reproducible mode keeps one source-adjoint record per edge; this graph would need more than 16 GB.");
+        keep_edge_forces_ = true;
+        edge_source_adjoint_.reserve_with_slack(std::max<std::size_t>(record_floats, 1));
+        source_offsets_.reserve(ALL + 1);
+        source_edges_.reserve_with_slack(std::max<long>(num_edges, 1));
+        det_sorted_sources_.reserve_with_slack(std::max<long>(num_edges, 1));
+        det_edge_ids_.reserve_with_slack(std::max<long>(num_edges, 1));
+        det_counts_.reserve(ALL + 1);
+        const long blocks_e = blocks_for(std::max<long>(num_edges, 1), 256);
+        det_partials_.reserve(static_cast<std::size_t>(std::max<long>(blocks_e, blocks_for(R, 256))) * 10);
+        SXB_CUDA(cudaMemsetAsync(det_counts_.ptr, 0, (ALL + 1) * sizeof(int), stream_));
+        if (num_edges > 0) {
+            count_sources_kernel<<<blocks_e, 256, 0, stream_>>>(num_edges, sources_.ptr, det_counts_.ptr);
+            iota_kernel<<<blocks_e, 256, 0, stream_>>>(num_edges, det_edge_ids_.ptr);
+        }
+        std::size_t scan_bytes = 0, sort_bytes = 0;
+        int key_bits = 1;
+        while ((1ll << key_bits) < static_cast<long long>(ALL)) ++key_bits;
+        cub::DeviceScan::ExclusiveSum(nullptr, scan_bytes, det_counts_.ptr, source_offsets_.ptr, static_cast<int>(ALL + 1), stream_);
+        cub::DeviceRadixSort::SortPairs(nullptr, sort_bytes, sources_.ptr, det_sorted_sources_.ptr, det_edge_ids_.ptr, source_edges_.ptr,
+                                        static_cast<int>(num_edges), 0, key_bits, stream_);
+        ig_temp_.reserve(std::max(scan_bytes, sort_bytes));
+        cub::DeviceScan::ExclusiveSum(ig_temp_.ptr, scan_bytes, det_counts_.ptr, source_offsets_.ptr, static_cast<int>(ALL + 1), stream_);
+        if (num_edges > 0)
+            cub::DeviceRadixSort::SortPairs(ig_temp_.ptr, sort_bytes, sources_.ptr, det_sorted_sources_.ptr, det_edge_ids_.ptr,
+                                            source_edges_.ptr, static_cast<int>(num_edges), 0, key_bits, stream_);
+        launches_ += 2;
+        SXB_CUDA(cudaGetLastError());
+    }
     if (keep_edge_forces_) edge_forces_.reserve_with_slack(3 * static_cast<std::size_t>(num_edges));
     SXB_CUDA(cudaStreamSynchronize(stream_));
     // pinned host side of an evaluation: a staging copy of the positions (uploaded by a copy node of the
@@ -877,6 +915,12 @@ void Evaluator::run_pipeline(int phases)
     fo.virial_slots = virial_slots_.ptr;
     fo.edge_forces = keep_edge_forces_ ? edge_forces_.ptr : nullptr;
     fo.accumulate_edge = 0;
+    fo.edge_source_adjoint = nullptr;
+    if (deterministic_) {       // no atomics: per-edge records, summed over the source schedule
+        fo.atom_forces = nullptr;
+        fo.edge_source_adjoint = edge_source_adjoint_.ptr;
+    }
+    double* const energy_slots = deterministic_ ? nullptr : energy_slots_.ptr;
     const int warp_threads = 32 * kWarpsPerBlock;
 
     // launch helpers for one tile of T receivers starting at t0 (tile tensors are indexed from 0)
@@ -1025,7 +1069,7 @@ void Evaluator::run_pipeline(int phases)
                 readout16_kernel<CHUNKS><<<blocks_for(static_cast<long>(T) * 32, 256), 256, 0, stream_>>>(                 \
                     T, model_.readout2_scale, M0_.ptr + t0 * rowH, NH, H2_.ptr, element_.ptr + t0, atomic_energies_.ptr,   \
                     readout1_.ptr, readout2_w1_.ptr, readout2_w2_.ptr, node_energies_.ptr + t0,                            \
-                    H2_adj_.ptr + static_cast<std::size_t>(t0) * C, energy_slots_.ptr)
+                    H2_adj_.ptr + static_cast<std::size_t>(t0) * C, energy_slots)
                 if (C == 128) SXB_READOUT16(4);
                 else SXB_READOUT16(1);
 #undef SXB_READOUT16
@@ -1033,7 +1077,7 @@ void Evaluator::run_pipeline(int phases)
                 readout_kernel<<<blocks_for(static_cast<long>(T) * 32, 256), 256, 0, stream_>>>(
                     T, C, model_.readout2_hidden, model_.readout2_scale, M0_.ptr + t0 * rowH, NH, H2_.ptr, element_.ptr + t0,
                     atomic_energies_.ptr, readout1_.ptr, readout2_w1_.ptr, readout2_w2_.ptr, node_energies_.ptr + t0,
-                    H2_adj_.ptr + static_cast<std::size_t>(t0) * C, energy_slots_.ptr);
+                    H2_adj_.ptr + static_cast<std::size_t>(t0) * C, energy_slots);
             launches_ += 1;
             span_end();
             // reverse
@@ -1115,6 +1159,13 @@ void Evaluator::run_pipeline(int phases)
             launches_ += 1;
             span_end();
         }
+        if (deterministic_) {
+            span_begin("source_adjoint_schedule");
+            reduce_source_adjoint_kernel<<<ALL, 128, 0, stream_>>>(NH * C, source_offsets_.ptr, source_edges_.ptr, geom_.ptr, grid_.r_cut,
+                                                                  edge_source_adjoint_.ptr, H1_adj_.ptr);
+            launches_ += 1;
+            span_end();
+        }
     }
     if (phases & 4) {
         fo.accumulate_edge = 1;
@@ -1190,6 +1241,15 @@ void Evaluator::run_pipeline(int phases)
             span_end();
         }
         span_begin("finalize");
+        if (deterministic_) {
+            const long blocks = std::max<long>(blocks_for(std::max<long>(num_edges_, 1), kTotalsThreads), blocks_for(R, kTotalsThreads));
+            reduce_node_forces_kernel<<<blocks_for(ALL, 128), 128, 0, stream_>>>(ALL, R, first_.ptr, source_offsets_.ptr, source_edges_.ptr,
+                                                                                  edge_forces_.ptr, forces_.ptr);
+            partial_totals_kernel<<<blocks, kTotalsThreads, 0, stream_>>>(num_edges_, R, geom_.ptr, edge_forces_.ptr, node_energies_.ptr,
+                                                                          det_partials_.ptr);
+            final_totals_kernel<<<1, 32, 0, stream_>>>(static_cast<int>(blocks), det_partials_.ptr, energy_slots_.ptr, virial_slots_.ptr);
+            launches_ += 3;
+        }
         publish_results_kernel<<<blocks_for(11 + static_cast<long>(R) + 3 * static_cast<long>(ALL), 256), 256, 0, stream_>>>(
             R, ALL, internal_of_.ptr, energy_slots_.ptr, virial_slots_.ptr, node_energies_.ptr, forces_.ptr, error_flag_.ptr, totals_.ptr,
             node_energies_out_.ptr, forces_out_.ptr, host_results_);
@@ -1788,6 +1848,15 @@ int Evaluator::tile_capacity() const
 {
     if (tile_size_ > 0 && tile_size_ < num_receivers_) return tile_size_;
     return std::max(num_receivers_, 1);
+}
+
+void Evaluator::set_deterministic(bool enabled)
+{
+    deterministic_ = enabled;
+    drop_step_graphs();
+    generation_ += 1;      // buffers and the source schedule are made at graph installation: prepare again
+    have_results_ = false;
+    mirror_valid_ = false;
 }
 
 void Evaluator::set_tile_size(int receivers_per_tile)

@@ -77,6 +77,8 @@ public:
     // Tiled streaming: receivers are processed in tiles of this many with one reusable workspace
     // (0 = one tile holding every receiver).  Takes effect at the next graph preparation.
     void set_tile_size(int receivers_per_tile);
+    // Reproducible mode: every accumulation in a fixed order (no atomics); takes effect at the next graph preparation.
+    void set_deterministic(bool enabled);
     int tile_capacity() const;
 
     void get_node_energies(double* out);
@@ -203,6 +205,11 @@ private:
     DeviceBuffer<float> A0_, A0_adj_, M0_, M0_adj_, H1_, H1_adj_, Phi1_, dPhi1_, A1_, A1_adj_, M1_, M1_adj_, H2_, H2_adj_;
     DeviceBuffer<double> node_energies_, node_energies_out_, forces_, forces_out_, edge_forces_;
     DeviceBuffer<double> totals_, energy_slots_, virial_slots_;
+    bool deterministic_ = false;
+    DeviceBuffer<float> edge_source_adjoint_;                 // [E][num_hidden][C] records of the reproducible mode
+    DeviceBuffer<int> source_offsets_, source_edges_;         // source schedule: edges sorted by source
+    DeviceBuffer<int> det_sorted_sources_, det_edge_ids_, det_counts_;
+    DeviceBuffer<double> det_partials_;
     DeviceBuffer<float> halo_stage_;         // rows of H1 / H1_adj on their way to or from host buffers
     DeviceBuffer<double> edge_scratch_;      // [E][3]: caller edge vectors on the way in, un-permuted edge forces on the way out
     DeviceBuffer<int> error_flag_;

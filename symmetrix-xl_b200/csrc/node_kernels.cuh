@@ -378,7 +378,7 @@ readout_kernel(int num_nodes, int C, int hidden, float act_scale, const float* _
     if (lane == 0) {
         const double e = atomic_energies[element[node]] + static_cast<double>(e1) + static_cast<double>(e2);
         node_energies[node] = e;
-        atomicAdd(energy_slots + (node % kVirialSlots), e);
+        if (energy_slots != nullptr) atomicAdd(energy_slots + (node % kVirialSlots), e);
     }
 }
 
@@ -453,7 +453,7 @@ readout16_kernel(int num_nodes, float act_scale, const float* __restrict__ M0, i
     if (lane == 0) {
         const double e = atomic_energies[element[node]] + static_cast<double>(e1) + static_cast<double>(e2);
         node_energies[node] = e;
-        atomicAdd(energy_slots + (node % kVirialSlots), e);
+        if (energy_slots != nullptr) atomicAdd(energy_slots + (node % kVirialSlots), e);
     }
 }
 

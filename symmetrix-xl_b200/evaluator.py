@@ -107,6 +107,7 @@ SIGNATURES = {
     "sxb_peer_exchange": (ctypes.c_int, [_P, ctypes.c_int32, _P]),
     "sxb_peer_destroy": (ctypes.c_int, [_P]),
     "sxb_set_tile_size": (ctypes.c_int, [_P, ctypes.c_int32]),
+    "sxb_set_deterministic": (ctypes.c_int, [_P, ctypes.c_int32]),
     "sxb_set_profiling": (ctypes.c_int, [_P, ctypes.c_int32]),
     "sxb_profile_entry": (ctypes.c_int, [_P, ctypes.c_int32, ctypes.c_char_p, ctypes.c_int32, ctypes.POINTER(ctypes.c_float),
                                          ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]),
@@ -401,6 +402,11 @@ class MACEB200:
 
     def internal_rows(self, indices_ptr, count, out_ptr):
         _check(self._lib.sxb_internal_rows(self._h, ctypes.c_void_p(indices_ptr), int(count), ctypes.c_void_p(out_ptr)))
+
+    def set_deterministic(self, enabled: bool):
+        """Reproducible mode: fixed-order accumulation, bit-identical results from run to run (prepare the
+        graph again afterwards)."""
+        _check(self._lib.sxb_set_deterministic(self._h, int(bool(enabled))))
 
     def set_tile_size(self, receivers_per_tile: int):
         """Tiled streaming with a reusable workspace (0 = off); prepare the graph again afterwards."""

@@ -335,6 +335,40 @@ def test_tile_boundary_sizes(pkg, model_path):
         assert np.abs(a["forces"] - b["forces"]).max() <= 1e-5
 
 
+@pytest.mark.parametrize("arch,zbl", [("medium", False), ("small", True)])
+def test_reproducible_mode_gives_identical_bits(pkg, model_path, arch, zbl):
+    """Fixed-order accumulation over the source schedule (the reference's source-sorted schedule,
+    libsymmetrix/source/mace_kokkos_factorized_lifecycle.cpp:2133-2195): repeated evaluations, and a second
+    evaluator, give bit-identical energies, forces, stress and source adjoints; the values agree with the
+    default (atomic) mode and with the reference's evaluator within the tolerances."""
+    path = model_path(arch, seed=12, zbl=zbl)
+    pos, cell, types = pkg.modelgen.srtio3(3, 0.05, 31)
+    runs = []
+    for instance in range(2):
+        calc = pkg.Calculator(path, skin=0.5)
+        calc.evaluator.set_deterministic(True)
+        for repeat in range(2):
+            out = calc.calculate(pos, cell, types)
+            runs.append((out["energy"], out["energies"].copy(), out["forces"].copy(), out["stress"].copy(),
+                         calc.evaluator.stage("H1_adj")))
+    for other in runs[1:]:
+        assert other[0] == runs[0][0]
+        for a, b in zip(other[1:], runs[0][1:]):
+            assert np.array_equal(a, b)
+    plain = pkg.Calculator(path, skin=0.5).calculate(pos, cell, types)
+    assert abs(plain["energy"] - runs[0][0]) / len(pos) <= 1e-7
+    assert np.abs(plain["forces"] - runs[0][2]).max() <= 1e-5
+    assert np.abs(plain["stress"] - runs[0][3]).max() <= 1e-8
+    if ref.available():
+        e, F, S = _reference_efs(path, pos, cell, types, calc.evaluator.r_cut)
+        _assert_matches_reference({"energy": runs[0][0], "energies": runs[0][1], "forces": runs[0][2], "stress": runs[0][3]}, e, F, S,
+                                  len(pos))
+    scaled = pkg.Calculator(model_path("small", a0_scaled=True, a1_scaled=True), skin=0.5)
+    scaled.evaluator.set_deterministic(True)
+    with pytest.raises(ValueError):
+        scaled.calculate(pos, cell, types)
+
+
 def test_nve_energy_conservation(pkg, model_path):
     """20 velocity-Verlet steps of 1 fs at 300 K: total energy is conserved to integrator accuracy."""
     path = model_path("small")
