@@ -103,7 +103,7 @@ __device__ __forceinline__ void spline_point(const SplineGrid& g, float r, int& 
 // ---------------------------------------------------------------------------------------------
 // Per-step geometry: xyz_ij = r_j - r_i + shift * cell in double, then the float record.
 // One warp per receiver, lanes over its edges.
-__global__ void geometry_from_positions_kernel(int num_nodes, const int* __restrict__ first,
+static __global__ void geometry_from_positions_kernel(int num_nodes, const int* __restrict__ first,
                                                const int* __restrict__ sources, const int* __restrict__ shifts,
                                                const double* __restrict__ positions, const int* __restrict__ original,
                                                const double* __restrict__ cell, EdgeGeom* __restrict__ geom,
@@ -198,7 +198,7 @@ __global__ void geometry_from_reference_kernel(int num_nodes, const int* __restr
 
 // Geometry from caller-supplied edge vectors (original edge order == internal edge order of
 // each receiver; ``edge_map`` gives the caller's edge index of every internal edge).
-__global__ void geometry_from_vectors_kernel(long num_edges, const double* __restrict__ xyz,
+static __global__ void geometry_from_vectors_kernel(long num_edges, const double* __restrict__ xyz,
                                              const int* __restrict__ edge_map, EdgeGeom* __restrict__ geom,
                                              int* __restrict__ error_flag)
 {
@@ -255,7 +255,7 @@ __device__ __forceinline__ float scalar_spline_value(const float* __restrict__ t
 // inv_scale[i] = 1 / (1 + sum_j s(r_ij)) for the layer-0 and the layer-1 density spline (either table
 // may be nullptr).  One warp per receiver; edge values in float as every radial function, summed in
 // double.  Reference: libsymmetrix/source/mace.cpp:1562-1584 (layer 0), 2381-2403 (layer 1).
-__global__ void density_scale_kernel(int num_receivers, const int* __restrict__ first, const int* __restrict__ sources,
+static __global__ void density_scale_kernel(int num_receivers, const int* __restrict__ first, const int* __restrict__ sources,
                                      const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype, int num_active,
                                      SplineGrid grid, const float* __restrict__ table0, const float* __restrict__ table1,
                                      float* __restrict__ inv_scale0, float* __restrict__ inv_scale1)
@@ -290,7 +290,8 @@ template <bool kGradient, bool kOrderedPairs>
 __device__ __forceinline__ void fill_chunk(ChunkState<kGradient>& s, int begin, int count, const int* __restrict__ sources,
                                            const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype,
                                            int type_i, int num_active, const SplineGrid& grid, int functions,
-                                           const float* __restrict__ density_table = nullptr, int density_types = 1)
+                                           const float* __restrict__ density_table = nullptr, int density_types = 1,
+                                           const float* __restrict__ given_harmonics = nullptr)
 {
     for (int t = threadIdx.x; t < count; t += blockDim.x) {
         const int e = begin + t;
@@ -324,6 +325,10 @@ __device__ __forceinline__ void fill_chunk(ChunkState<kGradient>& s, int begin, 
             s.dens[t] = density_table != nullptr
                             ? scalar_spline_derivative(density_table, (type_i * density_types + (density_types > 1 ? atype[j] : 0)) * grid.intervals + interval, x)
                             : 0.0f;
+        } else if (given_harmonics != nullptr) {
+            // the caller supplies Y_lm per edge [E][16] (the kernel-plugin interface passes them instead of directions)
+            const float4* row = reinterpret_cast<const float4*>(given_harmonics + 16 * static_cast<size_t>(e));
+            s.y[t][0] = row[0]; s.y[t][1] = row[1]; s.y[t][2] = row[2]; s.y[t][3] = row[3];
         } else {
             harmonics16<false>(g.ux, g.uy, g.uz, inv_r, reinterpret_cast<float*>(s.y[t]), nullptr, nullptr, nullptr);
         }
@@ -552,7 +557,7 @@ struct ZblParams {
     int p;
 };
 
-__global__ void zbl_kernel(int num_receivers, const int* __restrict__ first, const int* __restrict__ sources,
+static __global__ void zbl_kernel(int num_receivers, const int* __restrict__ first, const int* __restrict__ sources,
                            const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype, int num_active,
                            ZblParams z, double* __restrict__ node_energies, double* __restrict__ energy_slots, ForceOutputs out)
 {
@@ -720,7 +725,8 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
                              const unsigned char* __restrict__ atype, SplineGrid grid,                               \
                              const float4* __restrict__ table4, const float* __restrict__ H1,                        \
                              const __grid_constant__ CouplingConstants cgc, float* __restrict__ Phi1,                \
-                             const float* __restrict__ inv_scale, int pair_types)                                    \
+                             const float* __restrict__ inv_scale, int pair_types,                                    \
+                             const float* __restrict__ given_harmonics = nullptr)                                    \
     {                                                                                                                \
         constexpr int NP = SXB_##NAME##_NUM_PATHS, NR = SXB_##NAME##_NUM_ROWS, NH = SXB_##NAME##_NUM_HIDDEN;          \
         constexpr int NE = SXB_##NAME##_NUM_LME;                                                                     \
@@ -735,7 +741,8 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
         for (int chunk = begin; chunk < end; chunk += kEdgeChunk) {                                                  \
             const int count = min(kEdgeChunk, end - chunk);                                                          \
             __syncthreads();                                                                                         \
-            fill_chunk<false, false>(s, chunk, count, sources, geom, atype, atype[i], pair_types, grid, F);          \
+            fill_chunk<false, false>(s, chunk, count, sources, geom, atype, atype[i], pair_types, grid, F, nullptr, 1,   \
+                                     given_harmonics);                                                               \
             __syncthreads();                                                                                         \
             for (int t = 0; t < count; ++t) {                                                                        \
                 const int2 id = s.index[t];                                                                          \

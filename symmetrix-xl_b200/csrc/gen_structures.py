@@ -106,6 +106,8 @@ def emit_shape(name, l_max, L_max, tables, groups=1, by_edge_l=None):
     out.append(f"#define SXB_{name}_TERMS(X) \\")
     out.append(" \\\n".join(f"    X({t}, {row}, {lme})" for t, (row, lme) in
                             enumerate(zip(tables["Phi1_lelm1lm2"], tables["Phi1_lme"]))))
+    out.append(f"// this library's own derivation of the coupling coefficients, by term (a model file carries its own)")
+    out.append(f"#define SXB_{name}_DEFAULT_CG {{" + ", ".join(f"{float(v)!r}f" for v in tables["Phi1_clebsch_gordan"]) + "}")
     # symmetric contraction: weights laid out [type][term][channel], term = offset(LM) + index
     offset = 0
     lines1, lines2, lines3 = [], [], []

@@ -41,6 +41,7 @@ SIGNATURES = {
     "sxb_model_file_info": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_char_p, ctypes.POINTER(ModelInfo), ctypes.c_char_p,
                                            ctypes.c_int32, _P, ctypes.c_int32]),
     "sxb_measure_device_peaks": (ctypes.c_int, [ctypes.c_int32, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]),
+    "sxb_jit_plugin_coupling": (ctypes.c_int, [_P, ctypes.c_int32, _P, _P]),
     "sxb_destroy": (None, [_P]),
     "sxb_last_error": (ctypes.c_char_p, []),
     "sxb_device_count": (ctypes.c_int, []),

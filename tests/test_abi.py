@@ -10,9 +10,11 @@ ROOT = Path(__file__).resolve().parents[1]
 
 
 def declared_symbols():
-    text = (ROOT / "include" / "symmetrix_b200.h").read_text()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(sxb_[a-z0-9_]+)\s*\(", text)))
+    names = set()
+    for header in sorted((ROOT / "include").glob("*.h")):
+        text = re.sub(r"/\*.*?\*/", "", header.read_text(), flags=re.S)
+        names.update(re.findall(r"\b(sxb_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def test_library_exports_every_declared_symbol(pkg):
@@ -22,6 +24,7 @@ def test_library_exports_every_declared_symbol(pkg):
     for name in names:
         assert hasattr(lib, name), name
     assert set(names) == set(pkg.SIGNATURES), "Python signature table and header disagree"
+    assert hasattr(lib, "symmetrix_jit_cuda_plugin_query_v2")       # the reference's kernel-plugin query symbol
 
 
 def test_errors_are_reported_without_a_device_or_model(pkg, tmp_path):
