@@ -8,7 +8,7 @@ it is copied into the repository) on the contract fixture of the OMAT-0 / MPA-0 
 source for sm_100a and leaves, under oracle/_ref/ (git-ignored; it travels with a repository snapshot):
     libsymmetrix_ref_r1_cuda.so          the reference's plugin (symmetrix_jit_cuda_plugin_query_v2)
     r1_medium_coupling.json              the contract's sparse coupling terms (row, output, coefficient)
-Usage:  python oracle/build_reference_r1_plugin.py [reference checkout]
+Usage:  python oracle/build_reference_r1_plugin.py <reference checkout>   (oracle/Makefile passes its REFERENCE_ROOT)
 """
 from __future__ import annotations
 
@@ -23,7 +23,10 @@ HERE = Path(__file__).resolve().parent
 
 
 def main():
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_ROOT", "/root/reference"))
+    given = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_ROOT")
+    if not given:
+        raise SystemExit("usage: build_reference_r1_plugin.py <reference checkout>   (or set REFERENCE_ROOT)")
+    root = Path(given)
     out = HERE / "_ref"
     if not root.exists():
         print("reference checkout not present: keeping prebuilt oracle/_ref (if any)")

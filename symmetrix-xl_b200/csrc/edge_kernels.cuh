@@ -772,7 +772,7 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
     }                                                                                                                \
                                                                                                                      \
     /* kMinBlocks caps the registers of the 128-channel build: 3 blocks per SM = at most 170 registers */           \
-    template <int kC, int kMinBlocks = 3, int kAblate = 0>                                                           \
+    template <int kC, int kMinBlocks = 3>                                                                            \
     __global__ void __launch_bounds__(kC > 0 ? kC : 256, kC == 128 ? kMinBlocks : 1)                                 \
     l1_reverse_kernel_##NAME(int num_nodes, int node0, int C_runtime, const int* __restrict__ first,                            \
                              const int* __restrict__ sources, const EdgeGeom* __restrict__ geom,                     \
@@ -815,7 +815,7 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
                 if (id.x < 0) continue;                                                                              \
                 const float4 m = s.misc[t];                                                                          \
                 const float x = m.x, xx = x * x, xxx = xx * x, x2 = 2.0f * x, xx3 = 3.0f * xx;                       \
-                const float4* c4 = table4 + ((kAblate & 2) ? 0 : (id.x >> 2)) + k;                                  \
+                const float4* c4 = table4 + (id.x >> 2) + k;                                                         \
                 float R[NP], dR[NP];                                                                                 \
                 _Pragma("unroll") for (int p = 0; p < NP; ++p) {                                                     \
                     const float4 c = c4[p * C];                                                                      \
@@ -833,9 +833,9 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
                 if (out.edge_source_adjoint != nullptr) {   /* reproducible mode: one record per edge, summed later */ \
                     float* record = out.edge_source_adjoint + static_cast<size_t>(chunk + t) * NH * C + k;           \
                     _Pragma("unroll") for (int q = 0; q < NH; ++q) record[q * C] = hadj[q];                          \
-                } else if (!(kAblate & 1)) {                                                                         \
+                } else {                                                                                             \
                     _Pragma("unroll") for (int q = 0; q < NH; ++q) atomicAdd(H1_adj + source_row + q * C, hadj[q]);  \
-                } else if (hadj[0] + hadj[1] == 123.456f) H1_adj[k] = hadj[2] + hadj[NH - 1];                        \
+                }                                                                                                    \
                 float fx = radial * m.y, fy = radial * m.z, fz = radial * m.w;                                       \
                 {                                                                                                    \
                     float g[16];                                                                                     \
@@ -846,10 +846,8 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
                     load16(s.gz[t], g);                                                                              \
                     _Pragma("unroll") for (int q = 0; q < 16; ++q) fz = fmaf(ang[q], g[q], fz);                      \
                 }                                                                                                    \
-                if (!(kAblate & 4)) {                                                                                \
-                    const float total = warp_reduce3_transposed(fx, fy, fz, lane);   /* lanes 0, 8, 16: x, y, z */   \
-                    if ((lane & 7) == 0 && lane < 24) fs.partial[t][warp][lane >> 3] = total;                        \
-                } else if (fx + fy + fz == 123.456f) fs.partial[t][warp][0] = fx;                                    \
+                const float total = warp_reduce3_transposed(fx, fy, fz, lane);   /* lanes 0, 8, 16: x, y, z */       \
+                if ((lane & 7) == 0 && lane < 24) fs.partial[t][warp][lane >> 3] = total;                            \
             }                                                                                                        \
             __syncthreads();                                                                                         \
             flush_chunk_forces<8>(fs, s, chunk, count, num_warps, out, density_coef);                                \

@@ -16,7 +16,6 @@
 
 #include "deterministic_kernels.cuh"
 #include "edge_kernels.cuh"
-#include "edge_kernels_dual.cuh"
 #include "edge_kernels_split.cuh"
 #include "edge_kernels_warp.cuh"
 #include "graph_kernels.cuh"
@@ -122,7 +121,6 @@ Evaluator::Evaluator(const std::string& json_path, int device_ordinal, const std
     upload(atomic_energies_, model_.atomic_energies, stream_);
     if (const char* env = std::getenv("SXB_SIMT_LINEARS")) use_tensor_cores_ = !(env[0] == '1');
     if (const char* env = std::getenv("SXB_CUDA_GRAPHS")) use_graphs_ = env[0] != '0';
-    if (const char* env = std::getenv("SXB_L1_REVERSE_VARIANT")) l1_reverse_variant_ = env[0] - '0';
     if (const char* env = std::getenv("SXB_POLY_GROUP")) {   // nodes per thread in the contraction kernels: "<forward><reverse>"
         if (env[0] == '1' || env[0] == '2') poly_g_forward_ = env[0] - '0';
         if (env[0] != 0 && (env[1] == '1' || env[1] == '2')) poly_g_reverse_ = env[1] - '0';
@@ -1120,25 +1118,6 @@ void Evaluator::run_pipeline(int phases)
             if (model_.shape_id == 0)
                 SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S0, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
                                        reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1, r1_pair_types_);
-            else if (model_.shape_id == 1 && C == 128 && l1_reverse_variant_ == 2) {
-                L1ReverseArgs args{first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, reinterpret_cast<const float4*>(r1_table_.ptr),
-                                   H1_.ptr, dPhi1_.ptr, H1_adj_.ptr, fo, density1, r1_pair_types_};
-                l1_reverse_dual_kernel_S1<128><<<T, 256, 0, stream_>>>(T, t0, args, coupling_);
-            } else if (model_.shape_id == 1 && C == 128 && l1_reverse_variant_ >= 3 && l1_reverse_variant_ <= 7) {
-                // timing ablations of the gradient kernel (results are wrong by construction): 3 = no source-adjoint
-                // atomics, 4 = every edge reads the first coefficient slab, 6 = no force reduction, 7 = all three
-#define SXB_ABLATE(BITS)                                                                                                  \
-                l1_reverse_kernel_S1<128, 3, BITS><<<T, 128, 0, stream_>>>(T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_, \
-                    reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1, r1_pair_types_)
-                if (l1_reverse_variant_ == 3) SXB_ABLATE(1);
-                else if (l1_reverse_variant_ == 4) SXB_ABLATE(2);
-                else if (l1_reverse_variant_ == 6) SXB_ABLATE(4);
-                else if (l1_reverse_variant_ == 7) SXB_ABLATE(7);
-                else SXB_ABLATE(3);
-#undef SXB_ABLATE
-            } else if (model_.shape_id == 1 && C == 128 && l1_reverse_variant_ == 1)
-                l1_reverse_kernel_S1<128, 4><<<T, 128, 0, stream_>>>(T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
-                    reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1, r1_pair_types_);
             else if (model_.shape_id == 1)
                 SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S1, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
                                        reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1, r1_pair_types_);

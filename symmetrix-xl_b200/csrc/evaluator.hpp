@@ -136,7 +136,6 @@ private:
     };
     HaloPlan halo_plan_;
     bool use_graphs_ = true;
-    int l1_reverse_variant_ = 0;   // 0: one thread per channel; 1: the same at 128 registers; 2: two threads per channel
     void finish_compute();
     void launch_gemm(const float* A, const RowMap& a_rows, const float* B, int ldb, bool b_transposed, float* C,
                      const RowMap& c_rows, int first_node, int num_nodes, int N, int K, bool accumulate, const float* bias);

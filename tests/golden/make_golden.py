@@ -1,8 +1,9 @@
 """Generates the golden fixtures of tests/golden/ from the reference's own code.
 
-Run in a container that holds the reference checkout (path in REFERENCE below):
+Run where the reference checkout is present, naming it as the first argument or in REFERENCE_ROOT
+(the same variable oracle/Makefile reads):
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py <reference checkout>
 
 1. reference_evaluator_<arch>.npz -- energies, directed edge forces and stage-tensor checksums of
    the reference's serial evaluator MACECPU<double> (built into oracle/_ref from the checkout's
@@ -21,6 +22,7 @@ from __future__ import annotations
 import ctypes
 import importlib
 import json
+import os
 import subprocess
 import sys
 import tempfile
@@ -30,7 +32,10 @@ import numpy as np
 
 ROOT = Path(__file__).resolve().parents[2]
 sys.path.insert(0, str(ROOT))
-REFERENCE = Path("/root/reference")
+_reference_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_ROOT")
+if not _reference_root:
+    raise SystemExit("usage: make_golden.py <reference checkout>   (or set REFERENCE_ROOT)")
+REFERENCE = Path(_reference_root)
 OUT = Path(__file__).resolve().parent
 
 import __graft_entry__ as graft  # noqa: E402
