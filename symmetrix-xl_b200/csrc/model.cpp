@@ -162,6 +162,7 @@ struct RadialDefinition {
     double prefactor = 0.0, r_max = 0.0;
     int p = 0;
     bool agnesi = false;
+    bool stored_pairs = false;   // tables were read from the file (pair-splines), nothing to build
     double agnesi_a = 0.0, agnesi_q = 0.0, agnesi_p = 0.0;
     std::vector<double> covalent_radii;   // per element type
     std::map<std::string, Network> networks;
@@ -266,6 +267,95 @@ void overlay_prediction_head(json& data, const std::string& requested, HostModel
     m.selected_head = chosen;
     m.available_heads = names;
 }
+// Stored pair splines (radial_representation "pair-splines": the exporter's nodal values and
+// derivatives per unordered element pair, libsymmetrix/source/mace.cpp:2714-2737, 2746-2761; Hermite
+// form cubic_spline_set.cpp:8-31).  Every pair's table goes straight into the definition's cache in
+// the layout radial_coefficients() returns; the kernels then treat the model like one with a
+// species-pair dependent distance transform.
+void hermite_table(const std::vector<std::vector<double>>& values, const std::vector<std::vector<double>>& derivs, int points,
+                   double h, const char* what, std::vector<double>& out)
+{
+    const std::size_t F = values.size();
+    if (derivs.size() != F) throw std::invalid_argument(std::string(what) + ": values and derivatives differ in extent.");
+    out.assign(static_cast<std::size_t>(points - 1) * 4 * F, 0.0);
+    for (std::size_t f = 0; f < F; ++f) {
+        const auto& v = values[f];
+        const auto& d = derivs[f];
+        if (static_cast<int>(v.size()) != points || static_cast<int>(d.size()) != points)
+            throw std::invalid_argument(std::string(what) + ": every spline must hold one value and one derivative per node.");
+        for (int i = 0; i < points; ++i)
+            if (!std::isfinite(v[i]) || !std::isfinite(d[i])) throw std::invalid_argument(std::string(what) + " contains a non-finite value.");
+        // the edge kernels skip edges at or beyond the cutoff, which is exact only for functions that end at zero
+        const double scale = 1.0 + std::abs(v[points / 2]);
+        if (std::abs(v[points - 1]) > 1e-6 * scale || std::abs(d[points - 1]) * h > 1e-6 * scale)
+            throw std::invalid_argument(std::string(what) + " must vanish with zero slope at the cutoff.");
+        for (int i = 0; i < points - 1; ++i) {
+            double* c = out.data() + static_cast<std::size_t>(i) * 4 * F + f;
+            c[0] = v[i];
+            c[F] = d[i];
+            c[2 * F] = (-3 * v[i] - 2 * h * d[i] + 3 * v[i + 1] - h * d[i + 1]) / (h * h);
+            c[3 * F] = (2 * v[i] + h * d[i] - 2 * v[i + 1] + h * d[i + 1]) / (h * h * h);
+        }
+    }
+}
+
+void load_pair_splines(const json& file, HostModel& m)
+{
+    const int A = m.num_elements, C = m.channels, pairs = A * (A + 1) / 2;
+    auto def = std::make_shared<RadialDefinition>();
+    def->stored_pairs = true;
+    def->h = file.at("radial_spline_h").get<double>();
+    def->x0 = file.value("radial_spline_min", 0.0);
+    using Table = std::vector<std::vector<std::vector<double>>>;   // [pair][function][node]
+    const Table values0 = file.at("radial_spline_values_0").get<Table>(), derivs0 = file.at("radial_spline_derivs_0").get<Table>();
+    const Table values1 = file.at("radial_spline_values_1").get<Table>(), derivs1 = file.at("radial_spline_derivs_1").get<Table>();
+    if (static_cast<int>(values0.size()) != pairs || static_cast<int>(derivs0.size()) != pairs
+        || static_cast<int>(values1.size()) != pairs || static_cast<int>(derivs1.size()) != pairs)
+        throw std::invalid_argument("Pair-spline tables must hold one entry per unordered element pair.");
+    if (values0[0].empty() || values0[0][0].size() < 2) throw std::invalid_argument("Pair-spline tables are empty.");
+    def->points = static_cast<int>(values0[0][0].size());
+    if (!(def->h > 0.0) || !std::isfinite(def->h) || !(def->x0 >= 0.0) || !std::isfinite(def->x0))
+        throw std::invalid_argument("Pair-spline grid is invalid.");
+    if (std::abs(def->x0 + def->h * (def->points - 1) - m.r_cut) > 1e-9 * m.r_cut)
+        throw std::invalid_argument("Pair-spline grid must end at the model cutoff.");
+    m.spline_x0 = def->x0;
+    m.spline_h = def->h;
+    m.spline_points = def->points;
+    m.a0_scaled = file.at("A0_scaled").get<bool>();
+    m.a1_scaled = file.value("A1_scaled", false);
+    // density splines: one per pair on a grid of their own, which must be the radial grid (mace.cpp:2746-2761)
+    auto density = [&](const char* name, const char* prefix) {
+        const std::string p(prefix);
+        const double h = file.at(p + "_spline_h").get<double>(), x0 = file.value(p + "_spline_min", 0.0);
+        if (std::abs(h - def->h) > 1e-12 * def->h || std::abs(x0 - def->x0) > 1e-12)
+            throw std::invalid_argument(p + " density splines must use the grid of the radial splines.");
+        const auto values = file.at(p + "_spline_values").get<std::vector<std::vector<double>>>();
+        const auto derivs = file.at(p + "_spline_derivs").get<std::vector<std::vector<double>>>();
+        if (static_cast<int>(values.size()) != pairs || static_cast<int>(derivs.size()) != pairs)
+            throw std::invalid_argument(p + " density splines must hold one entry per unordered element pair.");
+        int pair = 0;
+        for (int a = 0; a < A; ++a)
+            for (int b = a; b < A; ++b, ++pair)
+                hermite_table({values[pair]}, {derivs[pair]}, def->points, def->h, (p + "_spline_values").c_str(),
+                              def->cache[std::make_tuple(std::string(name), a, b)]);
+    };
+    int pair = 0;
+    for (int a = 0; a < A; ++a)
+        for (int b = a; b < A; ++b, ++pair) {   // the exporter's pair order: a <= b, row by row
+            if (static_cast<int>(values0[pair].size()) != (m.l_max + 1) * C)
+                throw std::invalid_argument("radial_spline_values_0 must hold (l_max+1)*num_channels splines per pair.");
+            if (static_cast<int>(values1[pair].size()) != m.num_paths * C)
+                throw std::invalid_argument("radial_spline_values_1 must hold paths*num_channels splines per pair.");
+            hermite_table(values0[pair], derivs0[pair], def->points, def->h, "radial_spline_values_0",
+                          def->cache[std::make_tuple(std::string("R0"), a, b)]);
+            hermite_table(values1[pair], derivs1[pair], def->points, def->h, "radial_spline_values_1",
+                          def->cache[std::make_tuple(std::string("R1"), a, b)]);
+        }
+    if (m.a0_scaled) density("A0", "A0");
+    if (m.a1_scaled) density("A1", "A1");
+    m.agnesi = true;   // tables depend on the species pair
+    m.radial = def;
+}
 }  // namespace
 
 HostModel load_model(const std::string& json_path, const std::string& head)
@@ -283,8 +373,9 @@ HostModel load_model(const std::string& json_path, const std::string& head)
         throw std::invalid_argument("Only the standard two-layer MACE model family is supported.");
     if (file.value("symmetrix_format_version", 1) != 4 || file.value("h1_affine_mode", std::string()) != "m0_composite")
         throw std::invalid_argument("Model must be format version 4 with h1_affine_mode m0_composite.");
-    if (file.value("radial_representation", std::string()) != "compact")
-        throw std::invalid_argument("Model must use the compact radial representation.");
+    const std::string radial_representation = file.value("radial_representation", std::string());
+    if (radial_representation != "compact" && radial_representation != "pair-splines")
+        throw std::invalid_argument("Model must use the compact or the pair-splines radial representation.");
     if (file.value("num_interactions", 2) != 2 || file.value("single_layer_readout", false))
         throw std::invalid_argument("Only two-interaction models are supported.");
     if (file.value("has_field_coupling", false)) throw std::invalid_argument("MACEField models are not supported.");
@@ -404,6 +495,9 @@ HostModel load_model(const std::string& json_path, const std::string& head)
     }
 
     // ---- radial tables
+    if (radial_representation == "pair-splines") {
+        load_pair_splines(file, m);
+    } else {
     const auto& radial = file.at("compact_radial");
     m.spline_x0 = radial.at("spline_grid_min").get<double>();
     m.spline_points = radial.at("num_spline_points").get<int>();
@@ -464,6 +558,7 @@ HostModel load_model(const std::string& json_path, const std::string& head)
     if (m.a0_scaled) add_network("A0", 1);
     if (m.a1_scaled) add_network("A1", 1);
     m.radial = def;
+    }
 
     // ---- dense weights
     m.h0 = file.at("H0_weights").get<std::vector<double>>();
@@ -518,10 +613,11 @@ const std::vector<double>& radial_coefficients(const HostModel& m, const std::st
 {
     const auto& d = *static_cast<const RadialDefinition*>(m.radial.get());
     int a = 0, b = 0;
-    if (d.agnesi) { a = std::min(type_i, type_j); b = std::max(type_i, type_j); }
+    if (d.agnesi || d.stored_pairs) { a = std::min(type_i, type_j); b = std::max(type_i, type_j); }
     const auto key = std::make_tuple(name, a, b);
     auto found = d.cache.find(key);
     if (found != d.cache.end()) return found->second;
+    if (d.stored_pairs) throw std::invalid_argument("Pair-spline model holds no table " + name + " for the requested element pair.");
     const Network& net = d.networks.at(name);
     const auto values = run_network(net, radial_features(d, a, b), d.points);
     return d.cache.emplace(key, spline_coefficients(values, d.points, net.shape.back(), d.h)).first->second;

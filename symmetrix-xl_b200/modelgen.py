@@ -54,8 +54,14 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
                channels: int | None = None, num_spline_points: int = 256,
                radial_hidden=(64, 64, 64), num_bessel: int = 8, cutoff_p: int = 5,
                a0_scaled: bool = False, a1_scaled: bool = False, zbl: bool = False,
-               agnesi: bool = False, heads=()) -> dict:
-    """Random-weight compact model of architecture ``arch`` as a JSON-serialisable dict."""
+               agnesi: bool = False, heads=(), radial: str = "compact") -> dict:
+    """Random-weight model of architecture ``arch`` as a JSON-serialisable dict.  ``radial`` selects the
+    radial representation: "compact" (radial networks) or "pair-splines" (stored nodal values and
+    derivatives per unordered element pair, the exporter's older form)."""
+    if radial not in ("compact", "pair-splines"):
+        raise ValueError("radial must be 'compact' or 'pair-splines'")
+    if radial == "pair-splines" and agnesi:
+        raise ValueError("the distance transform belongs to the compact representation")
     cfg = dict(ARCHITECTURES[arch])
     C = int(channels or cfg["channels"])
     l_max, L_max, r_cut = cfg["l_max"], cfg["L_max"], float(cfg["r_cut"])
@@ -189,6 +195,54 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
         "readout_2_hidden_size": 16,
         "readout_2_scale_factor": 1.679177,
     }
+    if radial == "pair-splines":
+        # Stored pair splines on the exporter's grid linspace(1e-12, r_cut, points): smooth random
+        # functions sum_b c_b sin(b pi r / r_cut) under the polynomial cutoff envelope, with their exact
+        # derivatives; every unordered element pair (a <= b, row by row) gets coefficients of its own.
+        del model["compact_radial"]
+        model["radial_representation"] = "pair-splines"
+        r, h = np.linspace(1e-12, r_cut, int(num_spline_points), retstep=True)
+        u = r / r_cut
+        p = float(cutoff_p)
+        envelope = 1.0 - (p + 1) * (p + 2) / 2 * u ** p + p * (p + 2) * u ** (p + 1) - p * (p + 1) / 2 * u ** (p + 2)
+        d_envelope = (-(p + 1) * (p + 2) / 2 * p * u ** (p - 1) + p * (p + 2) * (p + 1) * u ** p
+                      - p * (p + 1) / 2 * (p + 2) * u ** (p + 1)) / r_cut
+        envelope[-1] = d_envelope[-1] = 0.0
+        k = np.arange(1, num_bessel + 1) * np.pi / r_cut
+        waves = np.sin(np.outer(k, r))                      # [b][node]
+        d_waves = k[:, None] * np.cos(np.outer(k, r))
+
+        def functions(count, scale):
+            c = rng.normal(size=(count, num_bessel)) * scale / np.sqrt(num_bessel)
+            g, dg = c @ waves, c @ d_waves
+            return g * envelope, dg * envelope + g * d_envelope
+
+        tables = {key: [] for key in ("radial_spline_values_0", "radial_spline_derivs_0", "radial_spline_values_1",
+                                      "radial_spline_derivs_1", "A0_spline_values", "A0_spline_derivs",
+                                      "A1_spline_values", "A1_spline_derivs")}
+        for a in range(A):
+            for b in range(a, A):
+                v, d = functions((l_max + 1) * C, 0.5)
+                tables["radial_spline_values_0"].append(v.tolist())
+                tables["radial_spline_derivs_0"].append(d.tolist())
+                v, d = functions(paths * C, 0.5)
+                tables["radial_spline_values_1"].append(v.tolist())
+                tables["radial_spline_derivs_1"].append(d.tolist())
+                for name, on in (("A0", a0_scaled), ("A1", a1_scaled)):
+                    if on:   # tanh(g^2), as the exporter stores the density functions
+                        g, dg = functions(1, 0.8)
+                        tables[name + "_spline_values"].append(np.tanh(g[0] ** 2).tolist())
+                        tables[name + "_spline_derivs"].append((2.0 * g[0] * dg[0] / np.cosh(g[0] ** 2) ** 2).tolist())
+        model["radial_spline_h"] = float(h)
+        model["radial_spline_min"] = float(r[0])
+        for key in ("radial_spline_values_0", "radial_spline_derivs_0", "radial_spline_values_1", "radial_spline_derivs_1"):
+            model[key] = tables[key]
+        for name, on in (("A0", a0_scaled), ("A1", a1_scaled)):
+            if on:
+                model[name + "_spline_h"] = float(h)
+                model[name + "_spline_min"] = float(r[0])
+                model[name + "_spline_values"] = tables[name + "_spline_values"]
+                model[name + "_spline_derivs"] = tables[name + "_spline_derivs"]
     if heads:
         # multi-head file (schema of libsymmetrix/source/prediction_heads.hpp:10-90): every head carries its own
         # atomic energies, readouts and ZBL coefficients; the last head is the default, the top level holds the first

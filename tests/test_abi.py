@@ -83,6 +83,33 @@ def test_model_loader_selects_prediction_heads_on_the_host(pkg, tmp_path):
         pkg.model_file_info(single, head="pbe")
 
 
+def test_model_loader_reads_and_validates_pair_splines_on_the_host(pkg, tmp_path):
+    """Stored pair splines (libsymmetrix/source/mace.cpp:2714-2737): accepted when every table is complete and ends
+    at zero with zero slope at the cutoff (edges at or beyond the cutoff are skipped on the device), refused otherwise."""
+    import json
+
+    model = pkg.modelgen.make_model("small", seed=3, radial="pair-splines", num_spline_points=32, a0_scaled=True)
+    path = tmp_path / "pairs.json"
+    path.write_text(json.dumps(model))
+    info = pkg.model_file_info(path)
+    assert info["num_channels"] == 32 and info["shape_id"] == 0 and info["r_cut"] == 5.0
+
+    def refused(change, error=ValueError):
+        broken = json.loads(path.read_text())
+        change(broken)
+        (tmp_path / "broken.json").write_text(json.dumps(broken))
+        with pytest.raises(error):
+            pkg.model_file_info(tmp_path / "broken.json")
+
+    refused(lambda m: m["radial_spline_values_0"][2][5].__setitem__(-1, 0.3))      # does not vanish at the cutoff
+    refused(lambda m: m["radial_spline_derivs_1"][0][0].__setitem__(-1, 0.5))      # slope at the cutoff
+    refused(lambda m: m["radial_spline_values_1"].pop())                           # a pair is missing
+    refused(lambda m: m["radial_spline_values_0"][1].pop())                        # a function is missing
+    refused(lambda m: m.__setitem__("radial_spline_h", m["radial_spline_h"] * 0.5))  # grid does not reach the cutoff
+    refused(lambda m: m.__setitem__("A0_spline_h", m["A0_spline_h"] * 2.0))        # density grid differs
+    refused(lambda m: m.__delitem__("A0_spline_values"), RuntimeError)              # a missing key is the parser's error
+
+
 def test_lammps_pair_style_compiles_against_the_header_shim():
     """LAMMPS is not installed here: the pair style is checked for syntax and for agreement with the C ABI
     against minimal stand-ins of the LAMMPS headers it includes."""

@@ -120,6 +120,21 @@ def _assert_matches_reference(out, e, F, S, natoms):
     assert np.abs(out["stress"] - S).max() <= TOL_S
 
 
+@pytest.mark.parametrize("arch,n,scaled,zbl", [("small", 3, False, False), ("small", 2, True, True), ("medium", 2, False, False)])
+def test_pair_spline_models_vs_reference_evaluator(pkg, model_path, arch, n, scaled, zbl):
+    """The stored pair-spline radial representation (nodal values and derivatives per unordered element
+    pair instead of radial networks), with and without density splines and the pair repulsion."""
+    if not ref.available():
+        pytest.skip("oracle/_ref was not built")
+    path = model_path(arch, seed=23, radial="pair-splines", num_spline_points=96, a0_scaled=scaled, a1_scaled=scaled, zbl=zbl)
+    pos, cell, types = pkg.modelgen.srtio3(n, 0.05, 29)
+    calc = pkg.Calculator(path, skin=0.5)
+    out = calc.calculate(pos, cell, types)
+    for double in (True, False):
+        e, F, S = _reference_efs(path, pos, cell, types, calc.evaluator.r_cut, double=double)
+        _assert_matches_reference(out, e, F, S, len(pos))
+
+
 def test_headline_configuration_vs_reference_evaluator(pkg, model_path):
     """The configuration the throughput is quoted on, at full size: OMAT-0-medium architecture,
     10x10x10 SrTiO3 (5,000 atoms, sigma 0.05 A), 0.5 A skin, against MACECPU<float>."""
