@@ -35,6 +35,7 @@ UNIT = "us/atom"
 SUPERCELL = 10
 SIGMA = 0.05
 SKIN = 0.5
+PARITY_ATOM_LIMIT = 1_500_000   # largest system the N > 1 runs re-evaluate on one GPU for the parity entry
 SEED = 17
 # algorithmic work of the reference's formulation per (edge, channel)
 FLOP_PER_EDGE_CHANNEL = {"l0_forward": 56, "l0_reverse": 284, "l1_forward": 408, "l1_reverse": 850}
@@ -236,7 +237,8 @@ def run_distributed(args):
         gathered[torch.from_numpy(last_out["owned"]).cuda()] = last_out["forces"]
         all_reduce(gathered)
         parity = None
-        if rank == 0:
+        # the whole system on one GPU beside the decomposed state: only while it fits comfortably
+        if rank == 0 and total_atoms <= PARITY_ATOM_LIMIT:
             single_calc = pkg.Calculator(model, skin=SKIN, device=local_rank)
             if args.tile > 0:
                 single_calc.evaluator.set_tile_size(args.tile)

@@ -686,3 +686,50 @@ class Calculator:
         if all(pbc):
             out["stress"] = ev._reduce_stress(abs(np.linalg.det(cell)), execution_graph_generation=self._generation)
         return out
+
+
+class EnsembleCalculator:
+    """Same-process committee of calculators, after the reference's ``SymmetrixEnsemble``
+    (symmetrix/source/symmetrix/ensemble.py:65-212): members are evaluated one after the other on the same
+    input; every property ``x`` is returned as the member mean under ``x``, the stacked member values under
+    ``x_comm`` and the population variance under ``x_var``.  Members must agree on cutoff, element list and
+    skin (the reference's compatibility check, :133-144).  Exactly one of ``model_files`` / ``calculators``."""
+
+    def __init__(self, model_files=None, *, calculators=None, **calculator_kwargs):
+        if (model_files is None) == (calculators is None):
+            raise ValueError("Provide exactly one of model_files or calculators.")
+        if model_files is not None:
+            if isinstance(model_files, (str, bytes)) or hasattr(model_files, "__fspath__"):
+                model_files = (model_files,)
+            members = tuple(Calculator(path, **calculator_kwargs) for path in model_files)
+        else:
+            if calculator_kwargs:
+                raise ValueError("Calculator construction options cannot be used with calculators: "
+                                 + ", ".join(sorted(calculator_kwargs)) + ".")
+            members = (calculators,) if isinstance(calculators, Calculator) else tuple(calculators)
+        if not members:
+            raise ValueError("An ensemble must contain at least one member.")
+        for index, member in enumerate(members):
+            if not isinstance(member, Calculator):
+                raise TypeError(f"Ensemble members must be calculators; member {index} is {type(member).__name__}.")
+        first = members[0]
+        for index, member in enumerate(members[1:], start=1):
+            for name, expected, actual in (("cutoff", first.evaluator.r_cut, member.evaluator.r_cut),
+                                           ("atomic-number mapping", tuple(first.evaluator.atomic_numbers),
+                                            tuple(member.evaluator.atomic_numbers)),
+                                           ("neighbor skin", first.skin, member.skin)):
+                if expected != actual:
+                    raise ValueError(f"Ensemble member {index} has incompatible {name}: expected {expected!r}, got {actual!r}.")
+        self.calculators = members
+        self.num_models = len(members)
+
+    def calculate(self, positions, cell, node_types, pbc=(True, True, True)):
+        outputs = [member.calculate(positions, cell, node_types, pbc) for member in self.calculators]
+        results = {}
+        for name in outputs[0]:
+            committee = np.stack([np.asarray(out[name], dtype=np.float64) for out in outputs], axis=0)
+            mean, variance = committee.mean(axis=0), committee.var(axis=0)
+            results[name] = float(mean) if mean.ndim == 0 else mean
+            results[name + "_var"] = float(variance) if variance.ndim == 0 else variance
+            results[name + "_comm"] = committee
+        return results

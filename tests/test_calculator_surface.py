@@ -119,3 +119,29 @@ def test_affine_cell_change_reuses_the_neighbor_list(pkg, model_path):
     big = np.eye(3) * 1.08
     calc.calculate(pos @ big, cell @ big, types)
     assert calc.rebuilds == 2                      # a large strain rebuilds
+
+
+def test_ensemble_returns_mean_committee_and_variance(pkg, model_path):
+    """Committee of models evaluated in one process (symmetrix/source/symmetrix/ensemble.py:166-212)."""
+    paths = [model_path("small", seed=s) for s in (31, 32, 33)]
+    pos, cell, types = pkg.modelgen.srtio3(2, 0.05, 8)
+    ensemble = pkg.EnsembleCalculator(paths, skin=0.5)
+    out = ensemble.calculate(pos, cell, types)
+    singles = [pkg.Calculator(p, skin=0.5).calculate(pos, cell, types) for p in paths]
+    assert ensemble.num_models == 3 and out["forces_comm"].shape == (3, len(pos), 3) and out["stress_comm"].shape == (3, 3, 3)
+    for name in ("energy", "energies", "forces", "stress"):
+        stack = np.stack([np.asarray(s[name]) for s in singles])
+        assert np.abs(out[name + "_comm"] - stack).max() <= 1e-4
+        assert np.allclose(out[name], out[name + "_comm"].mean(axis=0))
+        assert np.allclose(out[name + "_var"], out[name + "_comm"].var(axis=0))
+    assert isinstance(out["energy"], float) and out["energy_var"] > 0.0
+    with pytest.raises(ValueError):
+        pkg.EnsembleCalculator(paths, calculators=ensemble.calculators)
+    with pytest.raises(ValueError):
+        pkg.EnsembleCalculator(calculators=ensemble.calculators, skin=0.5)
+    with pytest.raises(ValueError):
+        pkg.EnsembleCalculator(calculators=[ensemble.calculators[0], pkg.Calculator(paths[1], skin=0.3)])
+    with pytest.raises(ValueError):
+        pkg.EnsembleCalculator(calculators=[ensemble.calculators[0], pkg.Calculator(model_path("medium", seed=31), skin=0.5)])
+    with pytest.raises(TypeError):
+        pkg.EnsembleCalculator(calculators=[ensemble.calculators[0], object()])
