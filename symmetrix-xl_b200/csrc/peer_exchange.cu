@@ -3,10 +3,12 @@
 // The reference moves ghost rows with LAMMPS' MPI brick swaps
 // (pair_symmetrix/pair_symmetrix_mace_kokkos.cpp:737-1005, 1568-1705).  Here every rank maps the receive
 // buffers of its peers (CUDA IPC handles of plain cudaMalloc allocations) and an exchange is two small
-// kernels on the evaluator's stream:
+// steps on the evaluator's stream:
 //   push: copies this rank's outgoing rows, segment by segment, straight into the peers' receive
 //         buffers with 16-byte stores over NVLink, then raises this rank's arrival flag at each peer;
-//   wait: spins, with a time limit, until every peer's flag shows the current step.
+//   wait: spins, with a time limit, until every peer's flag shows the current step.  By default the
+//         thread that raised the flag for a peer also waits for that peer's flag, inside the push
+//         kernel (one launch per exchange); SXB_PEER_SPLIT_WAIT=1 runs the wait as a kernel of its own.
 // There is no collective and no staging copy, and the kernels can be captured into a CUDA graph: the
 // step number lives in device memory and is advanced by a kernel.  Every wait is bounded; when it
 // expires the kernel records bit 32 in the status word and returns, so the context stays usable and the
@@ -16,6 +18,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <stdexcept>
 #include <string>
@@ -48,7 +51,25 @@ struct PushPlan {
 
 // grid.y = destination rank; blocks of a rank stride over its segment.  The last block to finish a
 // segment publishes the flag after a system-wide fence.
-__global__ void __launch_bounds__(256) push_segments_kernel(PushPlan plan, unsigned int* __restrict__ done_counters)
+// Bounded spin until `flag` shows step `want`; records bit 32 in the status word when the limit runs out.
+__device__ __forceinline__ void wait_for_flag(const unsigned long long* flag, unsigned long long want, int* status)
+{
+    const long long start = clock64();
+    for (;;) {
+        unsigned long long seen;
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(flag) : "memory");
+        if (seen >= want) break;
+        if (clock64() - start > kWaitCycles) {
+            *reinterpret_cast<volatile int*>(status) = 32;
+            break;
+        }
+        __nanosleep(200);
+    }
+}
+
+__global__ void __launch_bounds__(256) push_segments_kernel(PushPlan plan, unsigned int* __restrict__ done_counters,
+                                                            const unsigned long long* __restrict__ incoming /*[world] or nullptr*/,
+                                                            int* __restrict__ status)
 {
     const int peer = blockIdx.y;
     const long long first = plan.send_begin[peer], rows = plan.send_begin[peer + 1] - first;
@@ -86,6 +107,8 @@ __global__ void __launch_bounds__(256) push_segments_kernel(PushPlan plan, unsig
             __threadfence_system();
             const unsigned long long step = *plan.step;
             asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(plan.remote_flag[peer]), "l"(step) : "memory");
+            // this peer's rows for me: nothing of mine is pending any more, so the wait cannot block a push
+            if (incoming != nullptr) wait_for_flag(incoming + peer, step, status);
         }
     }
 }
@@ -96,18 +119,7 @@ __global__ void wait_flags_kernel(int world, const unsigned long long* __restric
 {
     const int peer = threadIdx.x;
     if (peer >= world) return;
-    const unsigned long long want = *step;
-    const long long start = clock64();
-    for (;;) {
-        unsigned long long seen;
-        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(flags + peer) : "memory");
-        if (seen >= want) break;
-        if (clock64() - start > kWaitCycles) {
-            *reinterpret_cast<volatile int*>(status) = 32;
-            break;
-        }
-        __nanosleep(200);
-    }
+    wait_for_flag(flags + peer, *step, status);
 }
 
 __global__ void advance_step_kernel(unsigned long long* step) { *step += 1ull; }
@@ -123,6 +135,7 @@ struct PeerExchange {
     int* status = nullptr;                      // mapped pinned host word; bit 32: a wait expired
     std::vector<void*> opened;                  // mappings of peer memory to close
     PushPlan plans[kPhases];
+    bool split_wait = false;                    // SXB_PEER_SPLIT_WAIT=1: the wait as a kernel of its own
     bool planned[kPhases] = {false, false, false, false};
 };
 
@@ -175,6 +188,7 @@ int sxb_peer_create(int32_t device_ordinal, int32_t rank, int32_t world, PeerExc
         SXB_CUDA(cudaSetDevice(device_ordinal));
         auto* px = new PeerExchange();
         px->device = device_ordinal; px->rank = rank; px->world = world;
+        if (const char* env = std::getenv("SXB_PEER_SPLIT_WAIT")) px->split_wait = env[0] == '1';
         SXB_CUDA(cudaMalloc(reinterpret_cast<void**>(&px->flags), sizeof(unsigned long long) * sxb::kPhases * sxb::kMaxPeers));
         SXB_CUDA(cudaMemset(px->flags, 0, sizeof(unsigned long long) * sxb::kPhases * sxb::kMaxPeers));
         SXB_CUDA(cudaMalloc(reinterpret_cast<void**>(&px->step), sizeof(unsigned long long)));
@@ -281,8 +295,10 @@ int sxb_peer_exchange(PeerExchange* px, int32_t phase, void* stream)
         // enough 16-byte stores in flight to fill the links: up to 128 blocks per destination
         int blocks = static_cast<int>(std::min<long long>(128, std::max<long long>(1, largest / (256 * 32))));
         dim3 grid(blocks, px->world);
-        sxb::push_segments_kernel<<<grid, 256, 0, s>>>(plan, px->counters + phase * sxb::kMaxPeers);
-        sxb::wait_flags_kernel<<<1, 32, 0, s>>>(px->world, px->flags + phase * sxb::kMaxPeers, px->step, px->status);
+        const unsigned long long* incoming = px->flags + phase * sxb::kMaxPeers;
+        sxb::push_segments_kernel<<<grid, 256, 0, s>>>(plan, px->counters + phase * sxb::kMaxPeers, px->split_wait ? nullptr : incoming,
+                                                       px->status);
+        if (px->split_wait) sxb::wait_flags_kernel<<<1, 32, 0, s>>>(px->world, incoming, px->step, px->status);
         SXB_CUDA(cudaGetLastError());
         return SXB_OK;
     } catch (const std::invalid_argument& e) { sxb::set_last_error(e.what()); return SXB_ERR_INVALID_ARGUMENT;
