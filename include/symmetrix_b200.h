@@ -33,7 +33,7 @@ typedef struct sxb_model_info {
     int32_t num_paths;      /* layer-1 tensor-product paths */
     int32_t num_lme;        /* layer-1 output components */
     int32_t shape_id;       /* compiled coupling structure in use */
-    int32_t reserved;
+    int32_t single_layer;   /* 1: single_layer_readout model (no second message step) */
     double r_cut;
 } sxb_model_info;
 

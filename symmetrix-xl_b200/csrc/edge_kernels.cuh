@@ -286,7 +286,7 @@ static __global__ void density_scale_kernel(int num_receivers, const int* __rest
 }
 
 // Fills the chunk state for edges [begin, begin+count) of one receiver.
-template <bool kGradient, bool kOrderedPairs>
+template <bool kGradient, bool kOrderedPairs, bool kGivenHarmonics = false>
 __device__ __forceinline__ void fill_chunk(ChunkState<kGradient>& s, int begin, int count, const int* __restrict__ sources,
                                            const EdgeGeom* __restrict__ geom, const unsigned char* __restrict__ atype,
                                            int type_i, int num_active, const SplineGrid& grid, int functions,
@@ -325,7 +325,7 @@ __device__ __forceinline__ void fill_chunk(ChunkState<kGradient>& s, int begin, 
             s.dens[t] = density_table != nullptr
                             ? scalar_spline_derivative(density_table, (type_i * density_types + (density_types > 1 ? atype[j] : 0)) * grid.intervals + interval, x)
                             : 0.0f;
-        } else if (given_harmonics != nullptr) {
+        } else if (kGivenHarmonics) {
             // the caller supplies Y_lm per edge [E][16] (the kernel-plugin interface passes them instead of directions)
             const float4* row = reinterpret_cast<const float4*>(given_harmonics + 16 * static_cast<size_t>(e));
             s.y[t][0] = row[0]; s.y[t][1] = row[1]; s.y[t][2] = row[2]; s.y[t][3] = row[3];
@@ -459,7 +459,9 @@ struct ForceScratch {
     double virial[9];
 };
 
-template <int kMaxWarps>
+// kRecords = true: the caller knows at compile time that atom_forces is null (layer-1 gradient in the
+// reproducible / plugin mode); false keeps the run-time test, which the other callers rely on.
+template <int kMaxWarps, bool kRecords = false>
 __device__ __forceinline__ void flush_chunk_forces(ForceScratch<kMaxWarps>& fs, const ChunkState<true>& s, int chunk_begin,
                                                    int count, int num_warps, const ForceOutputs& out,
                                                    float density_coef = 0.0f)
@@ -489,7 +491,7 @@ __device__ __forceinline__ void flush_chunk_forces(ForceScratch<kMaxWarps>& fs, 
         // directed force dE/d(xyz_ij) with the reference's sign: force -= adjoint * (...)
         const double ex = -static_cast<double>(px), ey = -static_cast<double>(py), ez = -static_cast<double>(pz);
         const int j = s.index[t].y;
-        if (out.atom_forces != nullptr) {
+        if (!kRecords && out.atom_forces != nullptr) {
             atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j), ex);
             atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 1, ey);
             atomicAdd(out.atom_forces + 3 * static_cast<size_t>(j) + 2, ez);
@@ -528,11 +530,11 @@ __device__ __forceinline__ void flush_chunk_forces(ForceScratch<kMaxWarps>& fs, 
     }
 }
 
-template <int kMaxWarps>
+template <int kMaxWarps, bool kRecords = false>
 __device__ __forceinline__ void finish_receiver_forces(ForceScratch<kMaxWarps>& fs, int receiver, const ForceOutputs& out)
 {
     __syncthreads();
-    if (out.atom_forces == nullptr) return;      // reproducible mode: forces and virial come from the per-edge records
+    if (kRecords || out.atom_forces == nullptr) return;      // reproducible mode: forces and virial come from the per-edge records
     if (threadIdx.x < 3) atomicAdd(out.atom_forces + 3 * static_cast<size_t>(receiver) + threadIdx.x, fs.receiver[threadIdx.x]);
     if (threadIdx.x < 9) {
         const int slot = receiver % kVirialSlots;
@@ -718,7 +720,8 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
 #define SXB_TERM_TRANSPOSE(term, row, lme) adj[row] = fmaf(cgc.cg[term], dphi[lme], adj[row]);
 
 #define SXB_DEFINE_L1_KERNELS(NAME)                                                                                  \
-    template <int kC>                                                                                                \
+    /* kGivenHarmonics: the caller passes Y_lm per edge [E][16] (the kernel-plugin interface) */                     \
+    template <int kC, bool kGivenHarmonics = false>                                                                  \
     __global__ void __launch_bounds__(kC > 0 ? kC : 256)                                                             \
     l1_forward_kernel_##NAME(int num_nodes, int node0, int C_runtime, const int* __restrict__ first,                            \
                              const int* __restrict__ sources, const EdgeGeom* __restrict__ geom,                     \
@@ -741,8 +744,8 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
         for (int chunk = begin; chunk < end; chunk += kEdgeChunk) {                                                  \
             const int count = min(kEdgeChunk, end - chunk);                                                          \
             __syncthreads();                                                                                         \
-            fill_chunk<false, false>(s, chunk, count, sources, geom, atype, atype[i], pair_types, grid, F, nullptr, 1,   \
-                                     given_harmonics);                                                               \
+            fill_chunk<false, false, kGivenHarmonics>(s, chunk, count, sources, geom, atype, atype[i], pair_types, grid, \
+                                                      F, nullptr, 1, given_harmonics);                               \
             __syncthreads();                                                                                         \
             for (int t = 0; t < count; ++t) {                                                                        \
                 const int2 id = s.index[t];                                                                          \
@@ -772,7 +775,8 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
     }                                                                                                                \
                                                                                                                      \
     /* kMinBlocks caps the registers of the 128-channel build: 3 blocks per SM = at most 170 registers */           \
-    template <int kC, int kMinBlocks = 3>                                                                            \
+    /* kRecords: nothing is accumulated atomically; per-edge records are left for fixed-order passes */             \
+    template <int kC, int kMinBlocks = 3, bool kRecords = false>                                                     \
     __global__ void __launch_bounds__(kC > 0 ? kC : 256, kC == 128 ? kMinBlocks : 1)                                 \
     l1_reverse_kernel_##NAME(int num_nodes, int node0, int C_runtime, const int* __restrict__ first,                            \
                              const int* __restrict__ sources, const EdgeGeom* __restrict__ geom,                     \
@@ -830,7 +834,7 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
                 _Pragma("unroll") for (int q = 0; q < 16; ++q) ang[q] = 0.0f;                                        \
                 float radial = 0.0f;                                                                                 \
                 SXB_##NAME##_L1_REVERSE_BODY                                                                         \
-                if (out.edge_source_adjoint != nullptr) {   /* reproducible mode: one record per edge, summed later */ \
+                if (kRecords) {   /* reproducible mode: one record per edge, summed later */                         \
                     float* record = out.edge_source_adjoint + static_cast<size_t>(chunk + t) * NH * C + k;           \
                     _Pragma("unroll") for (int q = 0; q < NH; ++q) record[q * C] = hadj[q];                          \
                 } else {                                                                                             \
@@ -850,9 +854,9 @@ l0_reverse_kernel(int num_nodes, int node0, int C_runtime, const int* __restrict
                 if ((lane & 7) == 0 && lane < 24) fs.partial[t][warp][lane >> 3] = total;                            \
             }                                                                                                        \
             __syncthreads();                                                                                         \
-            flush_chunk_forces<8>(fs, s, chunk, count, num_warps, out, density_coef);                                \
+            flush_chunk_forces<8, kRecords>(fs, s, chunk, count, num_warps, out, density_coef);                      \
         }                                                                                                            \
-        finish_receiver_forces<8>(fs, i, out);                                                                       \
+        finish_receiver_forces<8, kRecords>(fs, i, out);                                                             \
     }
 
 SXB_DEFINE_L1_KERNELS(S0)

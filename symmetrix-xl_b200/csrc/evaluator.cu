@@ -112,7 +112,13 @@ Evaluator::Evaluator(const std::string& json_path, int device_ordinal, const std
     upload(m0_weights_, model_.m0_weights, stream_);
     upload(m1_weights_, model_.m1_weights, stream_);
     upload(w_h1_, model_.w_h1, stream_);
-    for (int l = 0; l <= model_.l_max; ++l) upload(w_a1_[l], model_.w_a1[l], stream_);
+    if (!model_.single_layer)
+        for (int l = 0; l <= model_.l_max; ++l) upload(w_a1_[l], model_.w_a1[l], stream_);
+    else {
+        if (model_.num_hidden > kMaxHidden) throw std::invalid_argument("Single-layer models are supported for hidden irreps up to l = 2.");
+        upload(hidden_poly_terms_, model_.hidden_poly_terms, stream_);
+        upload(hidden_poly_weights_, model_.hidden_poly_weights, stream_);
+    }
     upload(h2_skip_, model_.h2_skip, stream_);
     upload(h2_m1_, model_.h2_m1, stream_);
     upload(readout1_, model_.readout1, stream_);
@@ -127,7 +133,8 @@ Evaluator::Evaluator(const std::string& json_path, int device_ordinal, const std
     }
     for (int l = 0; l <= model_.hidden_l_max; ++l)
         upload_split(s_h1_[l], model_.w_h1.data() + static_cast<std::size_t>(l) * C * C, C, C);
-    for (int l = 0; l <= model_.l_max; ++l) upload_split(s_a1_[l], model_.w_a1[l].data(), model_.eta[l] * C, C);
+    if (!model_.single_layer)
+        for (int l = 0; l <= model_.l_max; ++l) upload_split(s_a1_[l], model_.w_a1[l].data(), model_.eta[l] * C, C);
     s_h2_skip_.resize(model_.num_elements);
     for (int a = 0; a < model_.num_elements; ++a)
         upload_split(s_h2_skip_[a], model_.h2_skip.data() + static_cast<std::size_t>(a) * C * C, C, C);
@@ -187,11 +194,13 @@ void Evaluator::prepare_active_types(const std::vector<int>& node_types)
         throw std::length_error("Layer-0 spline table exceeds 32-bit indexing; too many active element types.");
     upload(r0_table_, table, stream_);
     {
-        int pairs = 1;
-        const auto r1 = build_r1_table(model_, active_types_, &pairs);
-        if (r1.size() > static_cast<std::size_t>(std::numeric_limits<int>::max()))
-            throw std::length_error("Layer-1 spline table exceeds 32-bit indexing; too many active element types.");
-        upload(r1_table_, r1, stream_);
+        if (!model_.single_layer) {
+            int pairs = 1;
+            const auto r1 = build_r1_table(model_, active_types_, &pairs);
+            if (r1.size() > static_cast<std::size_t>(std::numeric_limits<int>::max()))
+                throw std::length_error("Layer-1 spline table exceeds 32-bit indexing; too many active element types.");
+            upload(r1_table_, r1, stream_);
+        }
         r1_pair_types_ = model_.agnesi ? static_cast<int>(active_types_.size()) : 1;
         if (model_.a0_scaled) upload(density0_table_, build_density_table(model_, "A0", active_types_), stream_);
         if (model_.a1_scaled) upload(density1_table_, build_density_table(model_, "A1", active_types_), stream_);
@@ -310,6 +319,7 @@ void Evaluator::install_graph(int num_receivers, int num_nodes, const std::vecto
         // source schedule: edge ids sorted by source (stable, so ascending edge index inside a source) and the
         // offsets of each source's run; plus one record per edge for the source adjoint and the directed force
         if (model_.shape_id == 2) throw std::invalid_argument("The reproducible mode is not available for hidden irreps 0e+1o+2e.");
+        if (model_.single_layer) throw std::invalid_argument("The reproducible mode is not available for single-layer models.");
         if (model_.a0_scaled || model_.a1_scaled)
             throw std::invalid_argument("The reproducible mode is not available for density-scaled models.");
         const std::size_t record_floats = static_cast<std::size_t>(num_edges) * NH * C;
@@ -1005,6 +1015,15 @@ void Evaluator::run_pipeline(int phases)
             SXB_CUDA(cudaMemsetAsync(fo.edge_forces, 0, sizeof(double) * 3 * static_cast<std::size_t>(num_edges_), stream_));
         for (int t0 = 0; t0 < R; t0 += tile_cap) {
             const int T = std::min(tile_cap, R - t0);
+            if (model_.single_layer) {
+                // no second message step: the readout polynomial acts on H1 of the receivers
+                span_begin("m1_forward");
+                hidden_poly_kernel<false><<<blocks_for(static_cast<long>(T) * C, 128), 128, 0, stream_>>>(
+                    T, C, NH, static_cast<int>(model_.hidden_poly_terms.size() / 4), reinterpret_cast<const int4*>(hidden_poly_terms_.ptr),
+                    H1_.ptr + t0 * rowH, element_.ptr + t0, hidden_poly_weights_.ptr, M1_.ptr, nullptr, nullptr);
+                launches_ += 1;
+                span_end();
+            } else {
             span_begin("l1_forward");
             if (model_.shape_id == 0)
                 SXB_LAUNCH_BY_CHANNELS(l1_forward_kernel_S0, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
@@ -1047,6 +1066,7 @@ void Evaluator::run_pipeline(int phases)
                 SXB_LAUNCH_POLY(m1_forward_kernel_S2, poly_g_forward_, SXB_S2_M1_NUM_TERMS, T, C, stream_, T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_.ptr);
             launches_ += 1;
             span_end();
+            }
             // H2 = xs T_element + M1 W
             span_begin("gemm_h2");
             {
@@ -1093,6 +1113,15 @@ void Evaluator::run_pipeline(int phases)
                 launch_tc(calls);
             }
             span_end();
+            if (model_.single_layer) {
+                span_begin("m1_reverse");
+                hidden_poly_kernel<true><<<blocks_for(static_cast<long>(T) * C, 128), 128, 0, stream_>>>(
+                    T, C, NH, static_cast<int>(model_.hidden_poly_terms.size() / 4), reinterpret_cast<const int4*>(hidden_poly_terms_.ptr),
+                    H1_.ptr + t0 * rowH, element_.ptr + t0, hidden_poly_weights_.ptr, nullptr, M1_adj_.ptr, H1_adj_.ptr + t0 * rowH);
+                launches_ += 1;
+                span_end();
+                continue;
+            }
             span_begin("m1_reverse");
             if (model_.shape_id == 0)
                 SXB_LAUNCH_POLY(m1_reverse_kernel_S0, poly_g_reverse_, SXB_S0_M1_NUM_TERMS, T, C, stream_, T, C, A1_.ptr, element_.ptr + t0, m1_weights_.ptr, M1_adj_.ptr, A1_adj_.ptr, model_.a1_scaled ? dot1_.ptr + t0 : nullptr);
@@ -1115,7 +1144,13 @@ void Evaluator::run_pipeline(int phases)
             }
             span_end();
             span_begin("l1_reverse");
-            if (model_.shape_id == 0)
+            if (deterministic_ && model_.shape_id == 0)      // records instead of atomics: the build with the channel count at run time
+                l1_reverse_kernel_S0<0, 3, true><<<T, C, 0, stream_>>>(T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
+                    reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1, r1_pair_types_);
+            else if (deterministic_ && model_.shape_id == 1)
+                l1_reverse_kernel_S1<0, 3, true><<<T, C, 0, stream_>>>(T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
+                    reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1, r1_pair_types_);
+            else if (model_.shape_id == 0)
                 SXB_LAUNCH_BY_CHANNELS(l1_reverse_kernel_S0, C, T, stream_, T, t0, C, first_.ptr, sources_.ptr, geom_.ptr, atype_.ptr, grid_,
                                        reinterpret_cast<const float4*>(r1_table_.ptr), H1_.ptr, dPhi1_.ptr, coupling_, H1_adj_.ptr, fo, density1, r1_pair_types_);
             else if (model_.shape_id == 1)
@@ -1138,7 +1173,7 @@ void Evaluator::run_pipeline(int phases)
             launches_ += 1;
             span_end();
         }
-        if (deterministic_) {
+        if (deterministic_ && !model_.single_layer) {
             span_begin("source_adjoint_schedule");
             reduce_source_adjoint_kernel<<<ALL, 128, 0, stream_>>>(NH * C, source_offsets_.ptr, source_edges_.ptr, geom_.ptr, grid_.r_cut,
                                                                   edge_source_adjoint_.ptr, H1_adj_.ptr);
@@ -1147,7 +1182,7 @@ void Evaluator::run_pipeline(int phases)
         }
     }
     if (phases & 4) {
-        fo.accumulate_edge = 1;
+        fo.accumulate_edge = model_.single_layer ? 0 : 1;   // the layer-1 gradient wrote the edge forces first
         if (phases != 7 && halo_plan_.active && halo_plan_.received_rows != nullptr) {   // reverse halo: adjoints my atoms collected as ghosts of the peers
             span_begin("halo_unpack");
             unpack_rows(1, halo_plan_.send_indices, halo_plan_.num_send, halo_plan_.received_rows, true);

@@ -150,6 +150,8 @@ private:
     // model tables on the device
     DeviceBuffer<float> density0_table_, density1_table_, inv_scale0_, inv_scale1_, dot0_, dot1_;
     DeviceBuffer<float> r0_table_, r1_table_, m0_weights_, m1_weights_, w_h1_, w_a1_[4], h2_skip_, h2_m1_;
+    DeviceBuffer<int> hidden_poly_terms_;          // single-layer models: monomials of the readout polynomial over H1
+    DeviceBuffer<float> hidden_poly_weights_;
     DeviceBuffer<float> readout1_, readout2_w1_, readout2_w2_;
     // the same weights split into TF32-exact high part and residual, stored [N][K] (K contiguous)
     // for the product with W ("fwd", C = A W) and with W^T ("rev", C = A W^T)

@@ -173,7 +173,7 @@ int32_t forward_launch(const SymmetrixJitCudaR1ForwardArgsV2* a, void* stream_po
         Scratch& s = prepare(a->radial, a->num_nodes, a->num_edges, a->node_types, a->type_to_active, a->radius, nullptr, 0, 0, stream);
         plugin_offsets_kernel<<<blocks(a->num_nodes), 256, 0, stream>>>(a->num_nodes, a->first_neigh, a->num_neigh, s.first.ptr);
         const int pair_types = a->radial.edge_types > 1 ? static_cast<int>(a->active_type_count) : 1;
-        l1_forward_kernel_S1<kChannels><<<static_cast<int>(a->num_nodes), kChannels, 0, stream>>>(
+        l1_forward_kernel_S1<kChannels, true><<<static_cast<int>(a->num_nodes), kChannels, 0, stream>>>(
             static_cast<int>(a->num_nodes), 0, kChannels, s.first.ptr, a->neigh_indices, s.geom.ptr, s.atype.ptr, grid_of(a->radial, a->cutoff),
             reinterpret_cast<const float4*>(s.table.ptr), static_cast<const float*>(a->neighbor_features), coupling(),
             static_cast<float*>(a->output), nullptr, pair_types, static_cast<const float*>(a->harmonics_values));

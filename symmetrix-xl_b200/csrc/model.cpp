@@ -308,9 +308,13 @@ void load_pair_splines(const json& file, HostModel& m)
     def->x0 = file.value("radial_spline_min", 0.0);
     using Table = std::vector<std::vector<std::vector<double>>>;   // [pair][function][node]
     const Table values0 = file.at("radial_spline_values_0").get<Table>(), derivs0 = file.at("radial_spline_derivs_0").get<Table>();
-    const Table values1 = file.at("radial_spline_values_1").get<Table>(), derivs1 = file.at("radial_spline_derivs_1").get<Table>();
+    Table values1, derivs1;
+    if (!m.single_layer) {
+        values1 = file.at("radial_spline_values_1").get<Table>();
+        derivs1 = file.at("radial_spline_derivs_1").get<Table>();
+    }
     if (static_cast<int>(values0.size()) != pairs || static_cast<int>(derivs0.size()) != pairs
-        || static_cast<int>(values1.size()) != pairs || static_cast<int>(derivs1.size()) != pairs)
+        || (!m.single_layer && (static_cast<int>(values1.size()) != pairs || static_cast<int>(derivs1.size()) != pairs)))
         throw std::invalid_argument("Pair-spline tables must hold one entry per unordered element pair.");
     if (values0[0].empty() || values0[0][0].size() < 2) throw std::invalid_argument("Pair-spline tables are empty.");
     def->points = static_cast<int>(values0[0][0].size());
@@ -344,10 +348,11 @@ void load_pair_splines(const json& file, HostModel& m)
         for (int b = a; b < A; ++b, ++pair) {   // the exporter's pair order: a <= b, row by row
             if (static_cast<int>(values0[pair].size()) != (m.l_max + 1) * C)
                 throw std::invalid_argument("radial_spline_values_0 must hold (l_max+1)*num_channels splines per pair.");
-            if (static_cast<int>(values1[pair].size()) != m.num_paths * C)
-                throw std::invalid_argument("radial_spline_values_1 must hold paths*num_channels splines per pair.");
             hermite_table(values0[pair], derivs0[pair], def->points, def->h, "radial_spline_values_0",
                           def->cache[std::make_tuple(std::string("R0"), a, b)]);
+            if (m.single_layer) continue;
+            if (static_cast<int>(values1[pair].size()) != m.num_paths * C)
+                throw std::invalid_argument("radial_spline_values_1 must hold paths*num_channels splines per pair.");
             hermite_table(values1[pair], derivs1[pair], def->points, def->h, "radial_spline_values_1",
                           def->cache[std::make_tuple(std::string("R1"), a, b)]);
         }
@@ -376,8 +381,9 @@ HostModel load_model(const std::string& json_path, const std::string& head)
     const std::string radial_representation = file.value("radial_representation", std::string());
     if (radial_representation != "compact" && radial_representation != "pair-splines")
         throw std::invalid_argument("Model must use the compact or the pair-splines radial representation.");
-    if (file.value("num_interactions", 2) != 2 || file.value("single_layer_readout", false))
-        throw std::invalid_argument("Only two-interaction models are supported.");
+    m.single_layer = file.value("single_layer_readout", false);
+    if (file.value("num_interactions", 2) != (m.single_layer ? 1 : 2))
+        throw std::invalid_argument("MACE interaction count and single-layer readout metadata disagree.");
     if (file.value("has_field_coupling", false)) throw std::invalid_argument("MACEField models are not supported.");
     if (file.value("first_interaction_residual", false))
         throw std::invalid_argument("Residual-first models are not supported.");
@@ -406,18 +412,21 @@ HostModel load_model(const std::string& json_path, const std::string& head)
     if (C % 32 != 0 || C > 256) throw std::invalid_argument("num_channels must be a multiple of 32, at most 256.");
 
     // ---- structure: match against a compiled shape
-    const auto phi_l = file.at("Phi1_l").get<std::vector<int>>();
-    const auto phi_l1 = file.at("Phi1_l1").get<std::vector<int>>();
-    const auto phi_l2 = file.at("Phi1_l2").get<std::vector<int>>();
-    const auto phi_lme = file.at("Phi1_lme").get<std::vector<int>>();
-    const auto phi_row = file.at("Phi1_lelm1lm2").get<std::vector<int>>();
-    const auto phi_cg = file.at("Phi1_clebsch_gordan").get<std::vector<double>>();
+    // a single-layer model has no second message step: its file carries no Phi1 tables (mace.cpp:2860-2873)
+    const std::vector<int> none;
+    const auto phi_l = file.value("Phi1_l", none);
+    const auto phi_l1 = file.value("Phi1_l1", none);
+    const auto phi_l2 = file.value("Phi1_l2", none);
+    const auto phi_lme = file.value("Phi1_lme", none);
+    const auto phi_row = file.value("Phi1_lelm1lm2", none);
+    const auto phi_cg = file.value("Phi1_clebsch_gordan", std::vector<double>());
+    if (m.single_layer && !phi_l.empty()) throw std::invalid_argument("A single-layer model must not carry Phi1 tables.");
     const auto m0_monomials = file.at("M0_monomials").get<std::map<std::string, std::vector<std::vector<int>>>>();
     const auto m1_monomials = file.at("M1_monomials").get<std::vector<std::vector<int>>>();
     const ShapeTables* shape = nullptr;
     for (const auto& s : all_shapes())
-        if (s.l_max == m.l_max && s.hidden_l_max == m.hidden_l_max && s.path_l == phi_l && s.path_l1 == phi_l1
-            && s.path_l2 == phi_l2)
+        if (s.l_max == m.l_max && s.hidden_l_max == m.hidden_l_max
+            && (m.single_layer || (s.path_l == phi_l && s.path_l1 == phi_l1 && s.path_l2 == phi_l2)))
             shape = &s;
     if (shape == nullptr)
         throw std::invalid_argument("Model coupling structure (l_max, L_max, paths) matches no compiled shape.");
@@ -442,7 +451,7 @@ HostModel load_model(const std::string& json_path, const std::string& head)
         }
     }
     m.eta.assign(m.l_max + 1, 0);
-    for (int l : phi_l) m.eta[l] += 1;
+    for (int l : (m.single_layer ? shape->path_l : phi_l)) m.eta[l] += 1;
     m.group_begin.assign(m.l_max + 2, 0);
     for (int l = 0; l <= m.l_max; ++l) m.group_begin[l + 1] = m.group_begin[l] + (2 * l + 1) * m.eta[l];
 
@@ -482,8 +491,30 @@ HostModel load_model(const std::string& json_path, const std::string& head)
                             static_cast<float>(w[t]);
                 }
         }
-        const auto position = map_terms(shape->m1_terms, nullptr, 0, m1_monomials, "M1_monomials");
         const auto& w1 = file.at("M1_weights");
+        if (m.single_layer) {
+            // the readout polynomial acts on H1 (mace.cpp:2465-2466): its monomials index the hidden components and
+            // are kept as data for the generic polynomial kernel, in the file's order
+            const int terms = static_cast<int>(m1_monomials.size());
+            m.hidden_poly_terms.assign(static_cast<std::size_t>(terms) * 4, -1);
+            for (int t = 0; t < terms; ++t) {
+                const auto& mono = m1_monomials[t];
+                if (mono.empty() || mono.size() > 3) throw std::invalid_argument("M1_monomials must have degree 1 to 3.");
+                for (std::size_t q = 0; q < mono.size(); ++q) {
+                    if (mono[q] < 0 || mono[q] >= m.num_hidden) throw std::invalid_argument("M1_monomials index a component outside H1.");
+                    m.hidden_poly_terms[static_cast<std::size_t>(t) * 4 + q] = mono[q];
+                }
+            }
+            m.hidden_poly_weights.assign(static_cast<std::size_t>(A) * terms * C, 0.0f);
+            for (int a = 0; a < A; ++a)
+                for (int k = 0; k < C; ++k) {
+                    const auto w = w1.at(std::to_string(a)).at(std::to_string(k)).get<std::vector<double>>();
+                    if (static_cast<int>(w.size()) != terms) throw std::invalid_argument("M1_weights extent mismatch.");
+                    for (int t = 0; t < terms; ++t)
+                        m.hidden_poly_weights[(static_cast<std::size_t>(a) * terms + t) * C + k] = static_cast<float>(w[t]);
+                }
+        } else {
+        const auto position = map_terms(shape->m1_terms, nullptr, 0, m1_monomials, "M1_monomials");
         for (int a = 0; a < A; ++a)
             for (int k = 0; k < C; ++k) {
                 const auto w = w1.at(std::to_string(a)).at(std::to_string(k)).get<std::vector<double>>();
@@ -492,6 +523,7 @@ HostModel load_model(const std::string& json_path, const std::string& head)
                     m.m1_weights[(static_cast<std::size_t>(a) * m.m1_num_terms + position[t]) * C + k] +=
                         static_cast<float>(w[t]);
             }
+        }
     }
 
     // ---- radial tables
@@ -550,7 +582,9 @@ HostModel load_model(const std::string& json_path, const std::string& head)
         def->networks.emplace(name, net);
     };
     add_network("R0", (m.l_max + 1) * C);
-    add_network("R1", m.num_paths * C);
+    if (networks.contains("R1") == m.single_layer)   // compact_radial: has_R1() == single_layer is an error (mace.cpp:2768-2771)
+        throw std::invalid_argument("Compact radial R1 network does not match single_layer_readout.");
+    if (!m.single_layer) add_network("R1", m.num_paths * C);
     m.a0_scaled = file.at("A0_scaled").get<bool>();
     m.a1_scaled = file.value("A1_scaled", false);
     if (m.a0_scaled != networks.contains("A0") || m.a1_scaled != networks.contains("A1"))
@@ -578,7 +612,7 @@ HostModel load_model(const std::string& json_path, const std::string& head)
     m.w_h1 = to_vec<float>(file.at("H1_weights").get<std::vector<double>>());
     if (m.w_h1.size() != static_cast<std::size_t>(m.hidden_l_max + 1) * C * C)
         throw std::invalid_argument("H1_weights extent mismatch.");
-    {
+    if (!m.single_layer) {
         const auto w = file.at("A1_weights").get<std::vector<std::vector<double>>>();
         if (static_cast<int>(w.size()) != m.l_max + 1) throw std::invalid_argument("A1_weights extent mismatch.");
         for (int l = 0; l <= m.l_max; ++l) {
@@ -601,6 +635,7 @@ HostModel load_model(const std::string& json_path, const std::string& head)
     m.readout2_w2 = to_vec<float>(file.at("readout_2_weights_2").get<std::vector<double>>());
     m.readout2_hidden = file.value("readout_2_hidden_size", 16);
     m.readout2_scale = static_cast<float>(file.at("readout_2_scale_factor").get<double>());
+    if (m.single_layer && m.a1_scaled) throw std::invalid_argument("A single-layer model cannot scale a second message step (A1_scaled).");
     if (m.h2_m1.size() != static_cast<std::size_t>(C) * C || m.readout1.size() != static_cast<std::size_t>(C)
         || m.readout2_hidden <= 0 || m.readout2_hidden > 64
         || m.readout2_w1.size() != static_cast<std::size_t>(C) * m.readout2_hidden

@@ -71,6 +71,10 @@ struct HostModel {
     int readout2_hidden = 16;
     float readout2_scale = 1.0f;
     std::vector<float> cg;                   // [compiled term]
+    // single-layer models (single_layer_readout): no second message step, the readout polynomial acts on H1
+    bool single_layer = false;
+    std::vector<int> hidden_poly_terms;      // [term][4]: up to three hidden-component indices, -1 padded
+    std::vector<float> hidden_poly_weights;  // [A][term][C]
 };
 
 // Throws std::runtime_error / std::invalid_argument with a message naming the key.

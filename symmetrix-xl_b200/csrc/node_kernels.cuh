@@ -243,6 +243,52 @@ SXB_DEFINE_POLY_KERNELS(S1)
 SXB_DEFINE_POLY_KERNELS(S2)
 
 // ---------------------------------------------------------------------------------------------
+// Readout polynomial of a single-layer model: M1[node][k] = sum_t w[element][t][k] prod_q H1[node][idx_t,q][k]
+// over monomials of degree 1 to 3 in the hidden components, read as data (reference:
+// libsymmetrix/source/mace.cpp:2460-2482 with the polynomial input switched to H1, and its gradient
+// 2485-2512, which adds to H1_adj).  One thread per (node, channel); the monomial list is short (the
+// invariants of at most nine components), so it is walked from global memory.
+constexpr int kMaxHidden = 9;
+
+template <bool kReverse>
+__global__ void __launch_bounds__(128) hidden_poly_kernel(int num_nodes, int C, int num_hidden, int num_terms,
+                                                          const int4* __restrict__ terms, const float* __restrict__ H1,
+                                                          const unsigned char* __restrict__ element,
+                                                          const float* __restrict__ weights, float* __restrict__ M1,
+                                                          const float* __restrict__ M1_adj, float* __restrict__ H1_adj)
+{
+    const long index = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (index >= static_cast<long>(num_nodes) * C) return;
+    const int node = static_cast<int>(index / C), k = static_cast<int>(index - static_cast<long>(node) * C);
+    float x[kMaxHidden], g[kMaxHidden];
+#pragma unroll
+    for (int q = 0; q < kMaxHidden; ++q) {
+        x[q] = q < num_hidden ? H1[(static_cast<size_t>(node) * num_hidden + q) * C + k] : 0.0f;
+        g[q] = 0.0f;
+    }
+    const float* w = weights + static_cast<size_t>(element[node]) * num_terms * C + k;
+    float value = 0.0f;
+    for (int t = 0; t < num_terms; ++t) {
+        const int4 m = terms[t];
+        const float wt = w[static_cast<size_t>(t) * C];
+        const float a = x[m.x], b = m.y >= 0 ? x[m.y] : 1.0f, c = m.z >= 0 ? x[m.z] : 1.0f;
+        if (!kReverse) {
+            value = fmaf(wt, a * b * c, value);
+        } else {
+            g[m.x] = fmaf(wt, b * c, g[m.x]);
+            if (m.y >= 0) g[m.y] = fmaf(wt, a * c, g[m.y]);
+            if (m.z >= 0) g[m.z] = fmaf(wt, a * b, g[m.z]);
+        }
+    }
+    if (!kReverse) {
+        M1[static_cast<size_t>(node) * C + k] = value;
+    } else {
+        const float adj = M1_adj[static_cast<size_t>(node) * C + k];
+        for (int q = 0; q < num_hidden; ++q) H1_adj[(static_cast<size_t>(node) * num_hidden + q) * C + k] += adj * g[q];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Channel-mixing linear as a tiled FP32 GEMM with structured rows.
 //   C[row(g)][n] (+)= sum_k A[row(g)][k] * B[k][n]      (B stored [K][N], or [N][K] when transposed)
 // Logical row g of a node tensor (node, component, channel): node = first_node + g / components,

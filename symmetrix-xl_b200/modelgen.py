@@ -54,7 +54,7 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
                channels: int | None = None, num_spline_points: int = 256,
                radial_hidden=(64, 64, 64), num_bessel: int = 8, cutoff_p: int = 5,
                a0_scaled: bool = False, a1_scaled: bool = False, zbl: bool = False,
-               agnesi: bool = False, heads=(), radial: str = "compact") -> dict:
+               agnesi: bool = False, heads=(), radial: str = "compact", single_layer: bool = False) -> dict:
     """Random-weight model of architecture ``arch`` as a JSON-serialisable dict.  ``radial`` selects the
     radial representation: "compact" (radial networks) or "pair-splines" (stored nodal values and
     derivatives per unordered element pair, the exporter's older form)."""
@@ -62,6 +62,8 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
         raise ValueError("radial must be 'compact' or 'pair-splines'")
     if radial == "pair-splines" and agnesi:
         raise ValueError("the distance transform belongs to the compact representation")
+    if single_layer and a1_scaled:
+        raise ValueError("a single-layer model has no second message step to scale")
     cfg = dict(ARCHITECTURES[arch])
     C = int(channels or cfg["channels"])
     l_max, L_max, r_cut = cfg["l_max"], cfg["L_max"], float(cfg["r_cut"])
@@ -129,7 +131,15 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
             vals = per_m[M].reshape(A, C, -1)
             for a in range(A):
                 M0_weights[str(a)][str(L * L + M)] = {str(k): vals[a, k].tolist() for k in range(C)}
-    m1_vals = poly_weights(0, A * C)[0].reshape(A, C, -1)
+    if single_layer:
+        # one interaction: the readout polynomial acts on H1, its monomials index the (L_max+1)^2 hidden components
+        derived, chains = _structure.contraction_basis(L_max, 0)
+        m1_monomials = [list(t) for t in derived[0]]
+        degree = np.array([d for d, _ in chains])
+        w = rng.normal(size=(A * C, len(chains))) * np.where(degree == 1, 0.7, np.where(degree == 2, 0.35, 0.25))
+        m1_vals = (w @ np.stack([coeff[0] for _, coeff in chains])).reshape(A, C, -1)
+    else:
+        m1_vals = poly_weights(0, A * C)[0].reshape(A, C, -1)
     M1_weights = {str(a): {str(k): m1_vals[a, k].tolist() for k in range(C)} for a in range(A)}
 
     model = {
@@ -195,6 +205,14 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
         "readout_2_hidden_size": 16,
         "readout_2_scale_factor": 1.679177,
     }
+    if single_layer:
+        # H1 feeds a cubic polynomial directly: keep it O(1) so that the readout stays well conditioned in FP32
+        model["H1_weights"] = (0.3 * np.asarray(model["H1_weights"])).tolist()
+        model["num_interactions"] = 1
+        model["single_layer_readout"] = True
+        for key in ("Phi1_l", "Phi1_l1", "Phi1_l2", "Phi1_lme", "Phi1_lelm1lm2", "Phi1_clebsch_gordan", "A1_weights"):
+            del model[key]
+        del model["compact_radial"]["networks"]["R1"]
     if radial == "pair-splines":
         # Stored pair splines on the exporter's grid linspace(1e-12, r_cut, points): smooth random
         # functions sum_b c_b sin(b pi r / r_cut) under the polynomial cutoff envelope, with their exact
@@ -212,6 +230,7 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
         waves = np.sin(np.outer(k, r))                      # [b][node]
         d_waves = k[:, None] * np.cos(np.outer(k, r))
 
+        # amplitudes chosen so that the sums over ~50 neighbours keep every stage O(1), as the compact models do
         def functions(count, scale):
             c = rng.normal(size=(count, num_bessel)) * scale / np.sqrt(num_bessel)
             g, dg = c @ waves, c @ d_waves
@@ -222,12 +241,13 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
                                       "A1_spline_values", "A1_spline_derivs")}
         for a in range(A):
             for b in range(a, A):
-                v, d = functions((l_max + 1) * C, 0.5)
+                v, d = functions((l_max + 1) * C, 0.08)
                 tables["radial_spline_values_0"].append(v.tolist())
                 tables["radial_spline_derivs_0"].append(d.tolist())
-                v, d = functions(paths * C, 0.5)
-                tables["radial_spline_values_1"].append(v.tolist())
-                tables["radial_spline_derivs_1"].append(d.tolist())
+                if not single_layer:
+                    v, d = functions(paths * C, 0.08)
+                    tables["radial_spline_values_1"].append(v.tolist())
+                    tables["radial_spline_derivs_1"].append(d.tolist())
                 for name, on in (("A0", a0_scaled), ("A1", a1_scaled)):
                     if on:   # tanh(g^2), as the exporter stores the density functions
                         g, dg = functions(1, 0.8)
@@ -236,7 +256,8 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
         model["radial_spline_h"] = float(h)
         model["radial_spline_min"] = float(r[0])
         for key in ("radial_spline_values_0", "radial_spline_derivs_0", "radial_spline_values_1", "radial_spline_derivs_1"):
-            model[key] = tables[key]
+            if tables[key]:
+                model[key] = tables[key]
         for name, on in (("A0", a0_scaled), ("A1", a1_scaled)):
             if on:
                 model[name + "_spline_h"] = float(h)

@@ -110,6 +110,33 @@ def test_model_loader_reads_and_validates_pair_splines_on_the_host(pkg, tmp_path
     refused(lambda m: m.__delitem__("A0_spline_values"), RuntimeError)              # a missing key is the parser's error
 
 
+def test_model_loader_reads_single_layer_models_on_the_host(pkg, tmp_path):
+    """single_layer_readout files carry one interaction, no Phi1 tables, no R1 network and a readout polynomial over the
+    hidden components (libsymmetrix/source/mace.cpp:2676-2679, 2768-2771, 2902-2914)."""
+    import json
+
+    for arch, hidden in (("small", 0), ("medium", 1), ("large", 2)):
+        model = pkg.modelgen.make_model(arch, seed=5, single_layer=True)
+        path = tmp_path / f"single_{arch}.json"
+        path.write_text(json.dumps(model))
+        info = pkg.model_file_info(path)
+        assert info["single_layer"] and info["L_max"] == hidden and info["shape_id"] == hidden
+        assert max(max(t) for t in model["M1_monomials"]) < (hidden + 1) ** 2
+    assert not pkg.model_file_info(pkg.modelgen.write_model(tmp_path / "two.json", "small", seed=5))["single_layer"]
+
+    def refused(change):
+        broken = json.loads((tmp_path / "single_small.json").read_text())
+        change(broken)
+        (tmp_path / "broken.json").write_text(json.dumps(broken))
+        with pytest.raises(ValueError):
+            pkg.model_file_info(tmp_path / "broken.json")
+
+    refused(lambda m: m.__setitem__("num_interactions", 2))                     # metadata disagree
+    refused(lambda m: m.__setitem__("Phi1_l", [0]))                             # a second message step in a single-layer file
+    refused(lambda m: m["M1_monomials"].__setitem__(0, [7]))                    # component outside H1
+    refused(lambda m: m.__setitem__("A1_scaled", True))
+
+
 def test_lammps_pair_style_compiles_against_the_header_shim():
     """LAMMPS is not installed here: the pair style is checked for syntax and for agreement with the C ABI
     against minimal stand-ins of the LAMMPS headers it includes."""

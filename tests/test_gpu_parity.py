@@ -135,6 +135,31 @@ def test_pair_spline_models_vs_reference_evaluator(pkg, model_path, arch, n, sca
         _assert_matches_reference(out, e, F, S, len(pos))
 
 
+@pytest.mark.parametrize("arch,n,kwargs", [("small", 3, {}), ("medium", 2, {"a0_scaled": True}), ("large", 2, {"zbl": True}),
+                                           ("small", 2, {"radial": "pair-splines", "num_spline_points": 96})])
+def test_single_layer_models_vs_reference_evaluator(pkg, model_path, arch, n, kwargs):
+    """Models with one interaction (single_layer_readout): the readout polynomial acts on H1 and there is no second
+    message step (libsymmetrix/source/mace.cpp:265-283), for hidden irreps up to l = 0, 1 and 2; untiled and tiled."""
+    if not ref.available():
+        pytest.skip("oracle/_ref was not built")
+    path = model_path(arch, seed=41, single_layer=True, **kwargs)
+    pos, cell, types = pkg.modelgen.srtio3(n, 0.05, 43)
+    calc = pkg.Calculator(path, skin=0.5)
+    assert calc.evaluator.single_layer_readout
+    out = calc.calculate(pos, cell, types)
+    for double in (True, False):
+        e, F, S = _reference_efs(path, pos, cell, types, calc.evaluator.r_cut, double=double)
+        _assert_matches_reference(out, e, F, S, len(pos))
+    tiled = pkg.Calculator(path, skin=0.5)
+    tiled.evaluator.set_tile_size(16)
+    out_tiled = tiled.calculate(pos, cell, types)
+    _assert_matches_reference(out_tiled, e, F, S, len(pos))
+    with pytest.raises(ValueError):
+        rep = pkg.MACEB200(path)
+        rep.set_deterministic(True)
+        rep._prepare_periodic_factorized_graph(types, pos, cell, np.linalg.inv(cell), rep.r_cut + 0.5)
+
+
 def test_headline_configuration_vs_reference_evaluator(pkg, model_path):
     """The configuration the throughput is quoted on, at full size: OMAT-0-medium architecture,
     10x10x10 SrTiO3 (5,000 atoms, sigma 0.05 A), 0.5 A skin, against MACECPU<float>."""
