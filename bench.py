@@ -124,7 +124,11 @@ def build_workload(tmpdir, cells=SUPERCELL, workload="srtio3", atoms=20000):
 
 def run_distributed(args):
     """N > 1: one periodic SrTiO3 system of 5,000 atoms per GPU (10x10x10 cells per brick), decomposed
-    in space over the ranks; ghost features, adjoints and forces cross NVLink through NCCL."""
+    in space over the ranks; ghost positions, features, adjoints and forces cross NVLink as pushes into peer memory
+    (NCCL all-to-alls where peer mapping is unavailable)."""
+    # NCCL only carries the set-up collectives and the barriers here: in-switch reduction buys nothing, and a rank that
+    # dies while bound to an NVLink multicast object can disturb its peers' GPUs
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     import torch
     import torch.distributed as dist
 
