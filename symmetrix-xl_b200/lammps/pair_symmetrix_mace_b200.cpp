@@ -14,6 +14,7 @@
 #include "pair_symmetrix_mace_b200.h"
 
 #include <algorithm>
+#include <chrono>
 #include <cstring>
 
 #include "atom.h"
@@ -182,6 +183,11 @@ void PairSymmetrixMACEB200::compute(int eflag, int vflag)
 {
   ev_init(eflag, vflag);
   if (vflag_atom) error->all(FLERR, "Atomic virials are not supported by pair_style symmetrix/mace/b200");
+  using clock = std::chrono::steady_clock;
+  auto seconds_since = [](clock::time_point start) { return std::chrono::duration<double>(clock::now() - start).count(); };
+  const bool time_pair = execution_timing_enabled != 0.0;
+  const clock::time_point pair_start = clock::now();
+  execution_pair_evaluation_count += 1.0;
   const int nlocal = atom->nlocal, nall = atom->nlocal + atom->nghost;
   if (nlocal == 0) error->one(FLERR, "symmetrix/mace/b200: a rank owns no atom");
   if (generation == 0 || neighbor->ago == 0 || nlocal != graph_nlocal || nall != graph_nall) rebuild_graph();
@@ -192,17 +198,31 @@ void PairSymmetrixMACEB200::compute(int eflag, int vflag)
   rows.assign(static_cast<std::size_t>(nall) * row_floats, 0.0f);
 
   check(sxb_distributed_begin_host(evaluator, generation, positions.data()), "the first phase");
+  clock::time_point exchange_start = clock::now();            // reading H1 waits for the first phase: staging counts as exchange
   check(sxb_halo_rows_get(evaluator, 0, 0, nlocal, rows.data()), "reading H1");
   comm->forward_comm(this);                                   // ghosts receive their owners' H1 rows
   check(sxb_halo_rows_put(evaluator, 0, nlocal, nall - nlocal, rows.data() + static_cast<std::size_t>(nlocal) * row_floats, 0),
         "writing the ghost H1 rows");
+  {
+    const double seconds = seconds_since(exchange_start);
+    execution_mpi_hidden_state_forward_seconds += seconds;
+    execution_mpi_hidden_state_seconds += seconds;
+    execution_mpi_hidden_state_forward_calls += 1.0;
+  }
 
   check(sxb_distributed_continue(evaluator), "the second phase");
   std::fill(rows.begin(), rows.begin() + static_cast<std::size_t>(nlocal) * row_floats, 0.0f);
+  exchange_start = clock::now();
   check(sxb_halo_rows_get(evaluator, 1, nlocal, nall - nlocal, rows.data() + static_cast<std::size_t>(nlocal) * row_floats),
         "reading the ghost H1_adj rows");
   comm->reverse_comm(this);                                   // owners sum the adjoints of their ghost images
   check(sxb_halo_rows_put(evaluator, 1, 0, nlocal, rows.data(), 1), "adding the returned H1_adj rows");
+  {
+    const double seconds = seconds_since(exchange_start);
+    execution_mpi_hidden_state_reverse_seconds += seconds;
+    execution_mpi_hidden_state_seconds += seconds;
+    execution_mpi_hidden_state_reverse_calls += 1.0;
+  }
 
   check(sxb_distributed_finish(evaluator), "the third phase");
   check(sxb_synchronize(evaluator), "synchronising");
@@ -228,6 +248,27 @@ void PairSymmetrixMACEB200::compute(int eflag, int vflag)
     virial[4] -= 0.5 * (s[2] + s[6]);
     virial[5] -= 0.5 * (s[5] + s[7]);
   }
+  // the call synchronised the device above, so the wall clock bounds completed device work
+  if (time_pair) execution_pair_seconds += seconds_since(pair_start);
+}
+
+/* The counters `compute symmetrix/timing` resolves by name (it matches any pair style whose name begins with
+   symmetrix/mace; pair_symmetrix/compute_symmetrix_timing.cpp:88-113). */
+void *PairSymmetrixMACEB200::extract(const char *name, int &dim)
+{
+  dim = 0;
+  const struct { const char *key; double *value; } table[] = {
+      {"symmetrix_pair_seconds", &execution_pair_seconds},
+      {"symmetrix_pair_evaluation_count", &execution_pair_evaluation_count},
+      {"symmetrix_timing_enabled", &execution_timing_enabled},
+      {"symmetrix_mpi_hidden_state_forward_seconds", &execution_mpi_hidden_state_forward_seconds},
+      {"symmetrix_mpi_hidden_state_reverse_seconds", &execution_mpi_hidden_state_reverse_seconds},
+      {"symmetrix_mpi_hidden_state_seconds", &execution_mpi_hidden_state_seconds},
+      {"symmetrix_mpi_hidden_state_forward_calls", &execution_mpi_hidden_state_forward_calls},
+      {"symmetrix_mpi_hidden_state_reverse_calls", &execution_mpi_hidden_state_reverse_calls}};
+  for (const auto &entry : table)
+    if (std::strcmp(name, entry.key) == 0) return static_cast<void *>(entry.value);
+  return nullptr;
 }
 
 /* forward: owners pack their H1 rows, ghosts unpack them */

@@ -43,6 +43,7 @@ class PairSymmetrixMACEB200 : public Pair {
   void unpack_forward_comm(int, int, double *) override;
   int pack_reverse_comm(int, int, double *) override;
   void unpack_reverse_comm(int, int *, double *) override;
+  void *extract(const char *, int &) override;
 
  protected:
   void allocate();
@@ -64,6 +65,15 @@ class PairSymmetrixMACEB200 : public Pair {
   std::vector<double> positions;  // [nall][3]
   std::vector<float> rows;        // [nall][row_floats]: H1 going forward, H1_adj coming back
   std::vector<double> energies, forces;
+
+  // Run-to-date counters read by `compute symmetrix/timing` through extract(), under the names the
+  // reference's pair styles publish (pair_symmetrix/pair_symmetrix_mace.cpp:84-105): the whole pair call,
+  // and the hidden-state exchange (staging out of and into the device included) forward and reverse.
+  // The pair call is timed only while a compute has raised symmetrix_timing_enabled.
+  double execution_pair_seconds = 0.0, execution_pair_evaluation_count = 0.0, execution_timing_enabled = 0.0;
+  double execution_mpi_hidden_state_forward_seconds = 0.0, execution_mpi_hidden_state_reverse_seconds = 0.0;
+  double execution_mpi_hidden_state_seconds = 0.0;
+  double execution_mpi_hidden_state_forward_calls = 0.0, execution_mpi_hidden_state_reverse_calls = 0.0;
 };
 
 }    // namespace LAMMPS_NS

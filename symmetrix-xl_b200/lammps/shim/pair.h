@@ -14,6 +14,7 @@ class Pair : protected Pointers {
   virtual void unpack_forward_comm(int, int, double *) {}
   virtual int pack_reverse_comm(int, int, double *) { return 0; }
   virtual void unpack_reverse_comm(int, int *, double *) {}
+  virtual void *extract(const char *, int &) { return nullptr; }
   double eng_vdwl = 0.0, virial[6] = {0, 0, 0, 0, 0, 0};
   double *eatom = nullptr;
   int comm_forward = 0, comm_reverse = 0;
