@@ -320,6 +320,7 @@ void Evaluator::install_graph(int num_receivers, int num_nodes, const std::vecto
         // offsets of each source's run; plus one record per edge for the source adjoint and the directed force
         if (model_.shape_id == 2) throw std::invalid_argument("The reproducible mode is not available for hidden irreps 0e+1o+2e.");
         if (model_.single_layer) throw std::invalid_argument("The reproducible mode is not available for single-layer models.");
+        if (model_.legacy_h1_basis) throw std::invalid_argument("The reproducible mode is not available for format-version 1 / 2 models.");
         if (model_.a0_scaled || model_.a1_scaled)
             throw std::invalid_argument("The reproducible mode is not available for density-scaled models.");
         const std::size_t record_floats = static_cast<std::size_t>(num_edges) * NH * C;
@@ -961,6 +962,11 @@ void Evaluator::run_pipeline(int phases)
         events_used_ = 0;
         SXB_CUDA(cudaMemsetAsync(forces_.ptr, 0, sizeof(double) * 3 * ALL, stream_));
         SXB_CUDA(cudaMemsetAsync(H1_adj_.ptr, 0, sizeof(float) * static_cast<std::size_t>(ALL) * rowH, stream_));
+        if (model_.legacy_h1_basis) {   // old basis: dE/dH1 starts from the first readout's weights on the scalar block
+            fill_scalar_block_kernel<<<blocks_for(static_cast<long>(R) * C, 256), 256, 0, stream_>>>(R, C, static_cast<long>(rowH),
+                                                                                                    readout1_.ptr, H1_adj_.ptr);
+            launches_ += 1;
+        }
         SXB_CUDA(cudaMemsetAsync(energy_slots_.ptr, 0, sizeof(double) * kVirialSlots, stream_));
         SXB_CUDA(cudaMemsetAsync(virial_slots_.ptr, 0, sizeof(double) * kVirialSlots * 9, stream_));
         if (model_.a0_scaled || model_.a1_scaled) {
@@ -996,7 +1002,7 @@ void Evaluator::run_pipeline(int phases)
                 calls.push_back({m0, rows, &s_h1_[l], false, H1_.ptr + t0 * rowH, rows, 0, T, false, nullptr});
             }
             // one tile: the element-dependent skip term of H2 (x_i T_element) only needs M0, so it rides in this launch
-            if (!tiled)
+            if (!tiled && !model_.legacy_h1_basis)
                 for_type_ranges(t0, T, [&](int a, int begin, int count) {
                     calls.push_back({M0_.ptr + begin * rowH, scalar_rows, &s_h2_skip_[active_types_[a]], false,
                                      H2_.ptr + static_cast<std::size_t>(begin - t0) * C, flat_rows, 0, count, false, nullptr});
@@ -1070,10 +1076,11 @@ void Evaluator::run_pipeline(int phases)
             // H2 = xs T_element + M1 W
             span_begin("gemm_h2");
             {
-                if (tiled) {
+                if (tiled || model_.legacy_h1_basis) {
+                    const float* skip_input = model_.legacy_h1_basis ? H1_.ptr : M0_.ptr;   // old basis: the skip reads H1
                     std::vector<TcCall> calls;
                     for_type_ranges(t0, T, [&](int a, int begin, int count) {
-                        calls.push_back({M0_.ptr + begin * rowH, scalar_rows, &s_h2_skip_[active_types_[a]], false,
+                        calls.push_back({skip_input + begin * rowH, scalar_rows, &s_h2_skip_[active_types_[a]], false,
                                          H2_.ptr + static_cast<std::size_t>(begin - t0) * C, flat_rows, 0, count, false, nullptr});
                     });
                     launch_tc(calls);
@@ -1082,10 +1089,11 @@ void Evaluator::run_pipeline(int phases)
             }
             span_end();
             span_begin("readout");
+            const float* readout_input = model_.legacy_h1_basis ? H1_.ptr : M0_.ptr;   // scalar block the first readout acts on
             if (model_.readout2_hidden == 16 && (C == 128 || C == 32)) {
 #define SXB_READOUT16(CHUNKS)                                                                                             \
                 readout16_kernel<CHUNKS><<<blocks_for(static_cast<long>(T) * 32, 256), 256, 0, stream_>>>(                 \
-                    T, model_.readout2_scale, M0_.ptr + t0 * rowH, NH, H2_.ptr, element_.ptr + t0, atomic_energies_.ptr,   \
+                    T, model_.readout2_scale, readout_input + t0 * rowH, NH, H2_.ptr, element_.ptr + t0, atomic_energies_.ptr, \
                     readout1_.ptr, readout2_w1_.ptr, readout2_w2_.ptr, node_energies_.ptr + t0,                            \
                     H2_adj_.ptr + static_cast<std::size_t>(t0) * C, energy_slots)
                 if (C == 128) SXB_READOUT16(4);
@@ -1093,7 +1101,7 @@ void Evaluator::run_pipeline(int phases)
 #undef SXB_READOUT16
             } else
                 readout_kernel<<<blocks_for(static_cast<long>(T) * 32, 256), 256, 0, stream_>>>(
-                    T, C, model_.readout2_hidden, model_.readout2_scale, M0_.ptr + t0 * rowH, NH, H2_.ptr, element_.ptr + t0,
+                    T, C, model_.readout2_hidden, model_.readout2_scale, readout_input + t0 * rowH, NH, H2_.ptr, element_.ptr + t0,
                     atomic_energies_.ptr, readout1_.ptr, readout2_w1_.ptr, readout2_w2_.ptr, node_energies_.ptr + t0,
                     H2_adj_.ptr + static_cast<std::size_t>(t0) * C, energy_slots);
             launches_ += 1;
@@ -1105,7 +1113,7 @@ void Evaluator::run_pipeline(int phases)
                                            flat_rows, 0, T, false, nullptr}};
                 // one tile: the direct adjoint of the scalar block of M0, q + T_element H2_adj, is known here already;
                 // the reverse of the H1 linear adds to it later
-                if (!tiled)
+                if (!tiled && !model_.legacy_h1_basis)
                     for_type_ranges(t0, T, [&](int a, int begin, int count) {
                         calls.push_back({H2_adj_.ptr + static_cast<std::size_t>(begin) * C, flat_rows, &s_h2_skip_[active_types_[a]], true,
                                          M0_adj_.ptr + (begin - t0) * rowH, scalar_rows, 0, count, false, readout1_.ptr});
@@ -1198,7 +1206,21 @@ void Evaluator::run_pipeline(int phases)
             }
             span_begin("gemm_h1_reverse");
             // M0_adj_il = H1_adj_il W_l^T, then the direct adjoint q + T_element H2_adj on the scalar block
-            {
+            if (model_.legacy_h1_basis) {
+                // old basis: the skip's adjoint S_element H2_adj joins H1_adj (which started from q) before the linear
+                std::vector<TcCall> calls;
+                for_type_ranges(t0, T, [&](int a, int begin, int count) {
+                    calls.push_back({H2_adj_.ptr + static_cast<std::size_t>(begin) * C, flat_rows, &s_h2_skip_[active_types_[a]], true,
+                                     H1_adj_.ptr + begin * rowH, scalar_rows, 0, count, true, nullptr});
+                });
+                launch_tc(calls);
+                calls.clear();
+                for (int l = 0; l <= model_.hidden_l_max; ++l) {
+                    const RowMap rows{static_cast<long>(NH) * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
+                    calls.push_back({H1_adj_.ptr + t0 * rowH, rows, &s_h1_[l], true, M0_adj_.ptr, rows, 0, T, false, nullptr});
+                }
+                launch_tc(calls);
+            } else {
                 std::vector<TcCall> calls;
                 for (int l = 0; l <= model_.hidden_l_max; ++l) {
                     const RowMap rows{static_cast<long>(NH) * C, C, static_cast<long>(l) * l * C, 2 * l + 1};

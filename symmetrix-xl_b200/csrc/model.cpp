@@ -376,9 +376,29 @@ HostModel load_model(const std::string& json_path, const std::string& head)
 
     if (file.value("model_type", std::string("MACE")) != "MACE")
         throw std::invalid_argument("Only the standard two-layer MACE model family is supported.");
-    if (file.value("symmetrix_format_version", 1) != 4 || file.value("h1_affine_mode", std::string()) != "m0_composite")
-        throw std::invalid_argument("Model must be format version 4 with h1_affine_mode m0_composite.");
-    const std::string radial_representation = file.value("radial_representation", std::string());
+    // H1 affine basis (libsymmetrix/source/h1_affine_schema.hpp:179-240): format 4 with the first readout and the
+    // H1->H2 skip on the scalar block of M0, or format 1 / 2 with both on the scalar block of H1 (after linear_up)
+    const int format_version = file.value("symmetrix_format_version", 1);
+    if (format_version == 1 || format_version == 2) {
+        for (const char* key : {"h1_affine_mode", "h1_affine_version", "readout_1_weights_for_M0", "H2_weights_for_M0",
+                                "readout_1_weights_for_H1_pre_linear_up", "H2_weights_for_H1_pre_linear_up"})
+            if (file.contains(key))
+                throw std::invalid_argument("Symmetrix MACE format version " + std::to_string(format_version)
+                                            + " must not declare h1_affine fields; they require format version 4.");
+        if (file.contains("prediction_heads"))
+            throw std::invalid_argument("Multi-head files are supported in format version 4 only.");
+        m.legacy_h1_basis = true;
+    } else if (format_version != 4) {
+        throw std::invalid_argument("Unsupported Symmetrix model format version.");
+    } else if (file.value("h1_affine_mode", std::string()) != "m0_composite") {
+        throw std::invalid_argument("Format version 4 models must use h1_affine_mode m0_composite (pre_linear_up is not supported).");
+    } else if (file.value("h1_affine_version", 0) != 1) {
+        throw std::invalid_argument("Unsupported h1_affine_version (supported: 1).");
+    } else if (file.contains("readout_1_weights") || file.contains("H2_weights_for_H1")) {
+        throw std::invalid_argument("A format-version-4 MACE JSON must not contain the old-basis readout_1_weights or H2_weights_for_H1 fields.");
+    }
+    const std::string radial_representation =
+        file.value("radial_representation", std::string(format_version == 1 ? "pair-splines" : ""));
     if (radial_representation != "compact" && radial_representation != "pair-splines")
         throw std::invalid_argument("Model must use the compact or the pair-splines radial representation.");
     m.single_layer = file.value("single_layer_readout", false);
@@ -621,7 +641,8 @@ HostModel load_model(const std::string& json_path, const std::string& head)
         }
     }
     {
-        const auto w = file.at("H2_weights_for_M0").get<std::vector<std::vector<double>>>();
+        const char* skip_key = m.legacy_h1_basis ? "H2_weights_for_H1" : "H2_weights_for_M0";
+        const auto w = file.at(skip_key).get<std::vector<std::vector<double>>>();
         if (static_cast<int>(w.size()) != A) throw std::invalid_argument("H2_weights_for_M0 extent mismatch.");
         for (const auto& block : w) {
             if (block.size() != static_cast<std::size_t>(C) * C) throw std::invalid_argument("H2_weights_for_M0 extent mismatch.");
@@ -630,7 +651,7 @@ HostModel load_model(const std::string& json_path, const std::string& head)
         }
     }
     m.h2_m1 = to_vec<float>(file.at("H2_weights_for_M1").get<std::vector<double>>());
-    m.readout1 = to_vec<float>(file.at("readout_1_weights_for_M0").get<std::vector<double>>());
+    m.readout1 = to_vec<float>(file.at(m.legacy_h1_basis ? "readout_1_weights" : "readout_1_weights_for_M0").get<std::vector<double>>());
     m.readout2_w1 = to_vec<float>(file.at("readout_2_weights_1").get<std::vector<double>>());
     m.readout2_w2 = to_vec<float>(file.at("readout_2_weights_2").get<std::vector<double>>());
     m.readout2_hidden = file.value("readout_2_hidden_size", 16);

@@ -71,6 +71,9 @@ struct HostModel {
     int readout2_hidden = 16;
     float readout2_scale = 1.0f;
     std::vector<float> cg;                   // [compiled term]
+    // format versions 1 / 2: the first readout and the H1->H2 skip act on the scalar block of H1 (after the linear),
+    // not of M0; h2_skip and readout1 then hold H2_weights_for_H1 and readout_1_weights
+    bool legacy_h1_basis = false;
     // single-layer models (single_layer_readout): no second message step, the readout polynomial acts on H1
     bool single_layer = false;
     std::vector<int> hidden_poly_terms;      // [term][4]: up to three hidden-component indices, -1 padded

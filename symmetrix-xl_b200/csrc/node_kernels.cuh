@@ -503,6 +503,16 @@ readout16_kernel(int num_nodes, float act_scale, const float* __restrict__ M0, i
     }
 }
 
+// tensor[node][0][k] = values[k] for the first num_nodes nodes of a (node, component, channel) tensor.
+__global__ void fill_scalar_block_kernel(int num_nodes, int C, long node_stride, const float* __restrict__ values,
+                                         float* __restrict__ tensor)
+{
+    const long index = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (index >= static_cast<long>(num_nodes) * C) return;
+    const long node = index / C, k = index - node * C;
+    tensor[node * node_stride + k] = values[k];
+}
+
 // Closing kernel of an evaluation, one thread per output value: sums the energy / virial slots into
 // totals[10] and writes node energies and node forces in the caller's node order.  When `host` is
 // given the same values are also published straight into mapped pinned host memory, laid out

@@ -54,7 +54,8 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
                channels: int | None = None, num_spline_points: int = 256,
                radial_hidden=(64, 64, 64), num_bessel: int = 8, cutoff_p: int = 5,
                a0_scaled: bool = False, a1_scaled: bool = False, zbl: bool = False,
-               agnesi: bool = False, heads=(), radial: str = "compact", single_layer: bool = False) -> dict:
+               agnesi: bool = False, heads=(), radial: str = "compact", single_layer: bool = False,
+               format_version: int = 4) -> dict:
     """Random-weight model of architecture ``arch`` as a JSON-serialisable dict.  ``radial`` selects the
     radial representation: "compact" (radial networks) or "pair-splines" (stored nodal values and
     derivatives per unordered element pair, the exporter's older form)."""
@@ -62,6 +63,10 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
         raise ValueError("radial must be 'compact' or 'pair-splines'")
     if radial == "pair-splines" and agnesi:
         raise ValueError("the distance transform belongs to the compact representation")
+    if format_version not in (2, 4):
+        raise ValueError("format_version must be 4 or 2 (the old basis: first readout and skip stored on H1)")
+    if format_version == 2 and heads:
+        raise ValueError("prediction heads need format version 4")
     if single_layer and a1_scaled:
         raise ValueError("a single-layer model has no second message step to scale")
     cfg = dict(ARCHITECTURES[arch])
@@ -205,6 +210,12 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
         "readout_2_hidden_size": 16,
         "readout_2_scale_factor": 1.679177,
     }
+    if format_version == 2:
+        # old basis (format versions 1 / 2): the first readout and the H1 -> H2 skip act on the scalar block of H1
+        model["symmetrix_format_version"] = 2
+        del model["h1_affine_mode"], model["h1_affine_version"]
+        model["readout_1_weights"] = model.pop("readout_1_weights_for_M0")
+        model["H2_weights_for_H1"] = model.pop("H2_weights_for_M0")
     if single_layer:
         # H1 feeds a cubic polynomial directly: keep it O(1) so that the readout stays well conditioned in FP32
         model["H1_weights"] = (0.3 * np.asarray(model["H1_weights"])).tolist()

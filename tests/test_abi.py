@@ -137,6 +137,36 @@ def test_model_loader_reads_single_layer_models_on_the_host(pkg, tmp_path):
     refused(lambda m: m.__setitem__("A1_scaled", True))
 
 
+def test_model_loader_tells_the_h1_affine_basis_on_the_host(pkg, tmp_path):
+    """Format 4 (`m0_composite`) and the old basis of formats 1 / 2 are told apart by the version; mixed or partial
+    declarations are refused (libsymmetrix/source/h1_affine_schema.hpp:179-240)."""
+    import json
+
+    new = pkg.modelgen.make_model("small", seed=7)
+    old = pkg.modelgen.make_model("small", seed=7, format_version=2)
+    assert "readout_1_weights" in old and "readout_1_weights_for_M0" not in old and "h1_affine_mode" not in old
+
+    def info(model):
+        (tmp_path / "m.json").write_text(json.dumps(model))
+        return pkg.model_file_info(tmp_path / "m.json")
+
+    assert info(new)["h1_affine_mode"] == "m0_composite" and info(old)["h1_affine_mode"] == "legacy"
+    for change in (lambda m: m.__setitem__("h1_affine_mode", "m0_composite"),          # a format-4 field in a format-2 file
+                   lambda m: m.__setitem__("symmetrix_format_version", 3),
+                   lambda m: m.__setitem__("prediction_heads", {})):
+        broken = json.loads(json.dumps(old))
+        change(broken)
+        with pytest.raises(ValueError):
+            info(broken)
+    for change in (lambda m: m.__setitem__("h1_affine_mode", "pre_linear_up"),
+                   lambda m: m.__setitem__("h1_affine_version", 2),
+                   lambda m: m.__setitem__("readout_1_weights", m["readout_1_weights_for_M0"])):   # old-basis field in format 4
+        broken = json.loads(json.dumps(new))
+        change(broken)
+        with pytest.raises(ValueError):
+            info(broken)
+
+
 def test_lammps_pair_style_compiles_against_the_header_shim():
     """LAMMPS is not installed here: the pair style is checked for syntax and for agreement with the C ABI
     against minimal stand-ins of the LAMMPS headers it includes."""

@@ -113,9 +113,9 @@ def _reference_efs(path, pos, cell, types, r_cut, double=False):
     return m.get("node_energies"), F, S
 
 
-def _assert_matches_reference(out, e, F, S, natoms):
+def _assert_matches_reference(out, e, F, S, natoms, node_tol=TOL_E):
     assert abs(out["energy"] - e.sum()) / natoms <= TOL_E
-    assert np.abs(out["energies"] - e).max() <= TOL_E
+    assert np.abs(out["energies"] - e).max() <= node_tol
     assert np.abs(out["forces"] - F).max() <= TOL_F
     assert np.abs(out["stress"] - S).max() <= TOL_S
 
@@ -158,6 +158,27 @@ def test_single_layer_models_vs_reference_evaluator(pkg, model_path, arch, n, kw
         rep = pkg.MACEB200(path)
         rep.set_deterministic(True)
         rep._prepare_periodic_factorized_graph(types, pos, cell, np.linalg.inv(cell), rep.r_cut + 0.5)
+
+
+@pytest.mark.parametrize("arch,n,kwargs", [("small", 3, {}), ("medium", 2, {"a0_scaled": True, "a1_scaled": True}),
+                                           ("medium", 2, {"radial": "pair-splines", "num_spline_points": 64}),
+                                           ("small", 2, {"single_layer": True})])
+def test_old_basis_models_vs_reference_evaluator(pkg, model_path, arch, n, kwargs):
+    """Format version 2 (and 1): the first readout and the H1 -> H2 skip act on the scalar block of H1, after the linear
+    (libsymmetrix/source/h1_affine_schema.hpp:5-30, mace.cpp:2516-2557); untiled and tiled.  The reference's own float and
+    double evaluators differ by up to 8e-6 eV in single node energies on these models, hence the wider per-node bound."""
+    if not ref.available():
+        pytest.skip("oracle/_ref was not built")
+    path = model_path(arch, seed=51, format_version=2, **kwargs)
+    pos, cell, types = pkg.modelgen.srtio3(n, 0.05, 53)
+    calc = pkg.Calculator(path, skin=0.5)
+    assert calc.evaluator.h1_affine_mode == "legacy"
+    out = calc.calculate(pos, cell, types)
+    e, F, S = _reference_efs(path, pos, cell, types, calc.evaluator.r_cut, double=True)
+    _assert_matches_reference(out, e, F, S, len(pos), node_tol=3e-5)
+    tiled = pkg.Calculator(path, skin=0.5)
+    tiled.evaluator.set_tile_size(16)
+    _assert_matches_reference(tiled.calculate(pos, cell, types), e, F, S, len(pos), node_tol=3e-5)
 
 
 def test_headline_configuration_vs_reference_evaluator(pkg, model_path):
