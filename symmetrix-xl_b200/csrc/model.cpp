@@ -373,6 +373,8 @@ HostModel load_model(const std::string& json_path, const std::string& head)
         && parsed.value("h1_affine_mode", std::string()) == "m0_composite")
         overlay_prediction_head(parsed, head, m);
     const json& file = parsed;
+    if (parsed.contains("prediction_heads") && parsed.value("h1_affine_mode", std::string()) == "pre_linear_up")
+        throw std::invalid_argument("Multi-head files are supported in the m0_composite basis only.");
 
     if (file.value("model_type", std::string("MACE")) != "MACE")
         throw std::invalid_argument("Only the standard two-layer MACE model family is supported.");
@@ -390,12 +392,26 @@ HostModel load_model(const std::string& json_path, const std::string& head)
         m.legacy_h1_basis = true;
     } else if (format_version != 4) {
         throw std::invalid_argument("Unsupported Symmetrix model format version.");
-    } else if (file.value("h1_affine_mode", std::string()) != "m0_composite") {
-        throw std::invalid_argument("Format version 4 models must use h1_affine_mode m0_composite (pre_linear_up is not supported).");
-    } else if (file.value("h1_affine_version", 0) != 1) {
-        throw std::invalid_argument("Unsupported h1_affine_version (supported: 1).");
-    } else if (file.contains("readout_1_weights") || file.contains("H2_weights_for_H1")) {
-        throw std::invalid_argument("A format-version-4 MACE JSON must not contain the old-basis readout_1_weights or H2_weights_for_H1 fields.");
+    } else {
+        const std::string mode = file.value("h1_affine_mode", std::string());
+        if (mode != "m0_composite" && mode != "pre_linear_up")
+            throw std::invalid_argument("Symmetrix MACE format version 4 requires h1_affine_mode 'm0_composite' or 'pre_linear_up'.");
+        m.pre_linear_up = mode == "pre_linear_up";
+        if (file.value("h1_affine_version", 0) != 1) throw std::invalid_argument("Unsupported h1_affine_version (supported: 1).");
+        if (file.contains("readout_1_weights") || file.contains("H2_weights_for_H1"))
+            throw std::invalid_argument("A format-version-4 MACE JSON must not contain the old-basis readout_1_weights or H2_weights_for_H1 fields.");
+        const char* other_readout = m.pre_linear_up ? "readout_1_weights_for_M0" : "readout_1_weights_for_H1_pre_linear_up";
+        const char* other_skip = m.pre_linear_up ? "H2_weights_for_M0" : "H2_weights_for_H1_pre_linear_up";
+        if (file.contains(other_readout) || file.contains(other_skip))
+            throw std::invalid_argument("A '" + mode + "' MACE JSON must not contain " + other_readout + " or " + other_skip + ".");
+        const bool residual = file.value("first_interaction_residual", false);
+        if (!m.pre_linear_up && !file.value("single_layer_readout", false) && residual)
+            throw std::invalid_argument("The m0_composite basis cannot represent first-interaction residual features; such models use "
+                                        "h1_affine_mode 'pre_linear_up'.");
+        if (m.pre_linear_up && (file.value("single_layer_readout", false) || file.value("num_interactions", 2) != 2))
+            throw std::invalid_argument("The pre_linear_up basis applies to two-interaction models only.");
+        if (m.pre_linear_up && !file.contains("H1_product_weights"))
+            throw std::invalid_argument("The pre_linear_up basis requires H1_product_weights.");
     }
     const std::string radial_representation =
         file.value("radial_representation", std::string(format_version == 1 ? "pair-splines" : ""));
@@ -405,8 +421,9 @@ HostModel load_model(const std::string& json_path, const std::string& head)
     if (file.value("num_interactions", 2) != (m.single_layer ? 1 : 2))
         throw std::invalid_argument("MACE interaction count and single-layer readout metadata disagree.");
     if (file.value("has_field_coupling", false)) throw std::invalid_argument("MACEField models are not supported.");
-    if (file.value("first_interaction_residual", false))
-        throw std::invalid_argument("Residual-first models are not supported.");
+    m.first_residual = file.value("first_interaction_residual", false);
+    if (m.first_residual && !m.pre_linear_up)
+        throw std::invalid_argument("Residual-first models are supported in the pre_linear_up basis of format version 4 only.");
 
     m.has_zbl = file.value("has_zbl", false);
     if (m.has_zbl) {   // libsymmetrix/source/mace.cpp:2690-2699
@@ -632,6 +649,38 @@ HostModel load_model(const std::string& json_path, const std::string& head)
     m.w_h1 = to_vec<float>(file.at("H1_weights").get<std::vector<double>>());
     if (m.w_h1.size() != static_cast<std::size_t>(m.hidden_l_max + 1) * C * C)
         throw std::invalid_argument("H1_weights extent mismatch.");
+    if (m.pre_linear_up) {
+        // the first readout and the skip act on x = M0[l=0] P0 (+ the residual's scalar block): keep P0 = H1_product_weights[l=0]
+        const auto product = file.at("H1_product_weights").get<std::vector<double>>();
+        if (product.size() != m.w_h1.size())
+            throw std::invalid_argument("The pre_linear_up basis requires H1_product_weights of the H1_weights extent.");
+        m.w_product0.assign(product.begin(), product.begin() + static_cast<std::ptrdiff_t>(C) * C);
+    } else if (file.contains("H1_first_residual_weights") && !file.at("H1_first_residual_weights").empty()) {
+        throw std::invalid_argument("Non-residual MACE JSON must not contain H1 residual weights.");
+    }
+    if (m.first_residual) {
+        // H1 += R U per element (the residual passes through linear_up, mace.cpp:2801-2829); x += R[l=0]
+        const auto residual = file.at("H1_first_residual_weights").get<std::vector<double>>();
+        const auto linear_up = file.at("H1_linear_up_weights").get<std::vector<double>>();
+        const std::size_t NHs = static_cast<std::size_t>(m.num_hidden);
+        if (residual.size() != static_cast<std::size_t>(A) * NHs * C) throw std::invalid_argument("Residual-first MACE JSON has an invalid H1 residual extent.");
+        if (linear_up.size() != m.w_h1.size()) throw std::invalid_argument("Residual-first MACE JSON requires split H1 weights.");
+        m.residual_fused.assign(residual.size(), 0.0f);
+        m.residual_scalar.assign(static_cast<std::size_t>(A) * C, 0.0f);
+        for (int a = 0; a < A; ++a) {
+            for (int l = 0; l <= m.hidden_l_max; ++l)
+                for (int mm = 0; mm < 2 * l + 1; ++mm) {
+                    const std::size_t lm = static_cast<std::size_t>(l) * l + mm;
+                    for (int out = 0; out < C; ++out) {
+                        double sum = 0.0;
+                        for (int in = 0; in < C; ++in)
+                            sum += residual[(a * NHs + lm) * C + in] * linear_up[(static_cast<std::size_t>(l) * C + in) * C + out];
+                        m.residual_fused[(a * NHs + lm) * C + out] = static_cast<float>(sum);
+                    }
+                }
+            for (int k = 0; k < C; ++k) m.residual_scalar[static_cast<std::size_t>(a) * C + k] = static_cast<float>(residual[a * NHs * C + k]);
+        }
+    }
     if (!m.single_layer) {
         const auto w = file.at("A1_weights").get<std::vector<std::vector<double>>>();
         if (static_cast<int>(w.size()) != m.l_max + 1) throw std::invalid_argument("A1_weights extent mismatch.");
@@ -641,7 +690,7 @@ HostModel load_model(const std::string& json_path, const std::string& head)
         }
     }
     {
-        const char* skip_key = m.legacy_h1_basis ? "H2_weights_for_H1" : "H2_weights_for_M0";
+        const char* skip_key = m.legacy_h1_basis ? "H2_weights_for_H1" : m.pre_linear_up ? "H2_weights_for_H1_pre_linear_up" : "H2_weights_for_M0";
         const auto w = file.at(skip_key).get<std::vector<std::vector<double>>>();
         if (static_cast<int>(w.size()) != A) throw std::invalid_argument("H2_weights_for_M0 extent mismatch.");
         for (const auto& block : w) {
@@ -651,7 +700,9 @@ HostModel load_model(const std::string& json_path, const std::string& head)
         }
     }
     m.h2_m1 = to_vec<float>(file.at("H2_weights_for_M1").get<std::vector<double>>());
-    m.readout1 = to_vec<float>(file.at(m.legacy_h1_basis ? "readout_1_weights" : "readout_1_weights_for_M0").get<std::vector<double>>());
+    m.readout1 = to_vec<float>(file.at(m.legacy_h1_basis ? "readout_1_weights"
+                                       : m.pre_linear_up ? "readout_1_weights_for_H1_pre_linear_up"
+                                                         : "readout_1_weights_for_M0").get<std::vector<double>>());
     m.readout2_w1 = to_vec<float>(file.at("readout_2_weights_1").get<std::vector<double>>());
     m.readout2_w2 = to_vec<float>(file.at("readout_2_weights_2").get<std::vector<double>>());
     m.readout2_hidden = file.value("readout_2_hidden_size", 16);

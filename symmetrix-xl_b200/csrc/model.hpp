@@ -74,6 +74,12 @@ struct HostModel {
     // format versions 1 / 2: the first readout and the H1->H2 skip act on the scalar block of H1 (after the linear),
     // not of M0; h2_skip and readout1 then hold H2_weights_for_H1 and readout_1_weights
     bool legacy_h1_basis = false;
+    // format version 4, h1_affine_mode pre_linear_up: both act on x = M0[l=0] P0 + residual[l=0] (P0 = H1_product_weights of
+    // l = 0); with first_interaction_residual an element-dependent constant R U joins H1 (libsymmetrix/source/mace.cpp:1759-1888)
+    bool pre_linear_up = false, first_residual = false;
+    std::vector<float> w_product0;           // [C_in][C_out]
+    std::vector<float> residual_fused;       // [A][num_hidden][C]: R U, added to H1
+    std::vector<float> residual_scalar;      // [A][C]: R of the scalar block, added to x
     // single-layer models (single_layer_readout): no second message step, the readout polynomial acts on H1
     bool single_layer = false;
     std::vector<int> hidden_poly_terms;      // [term][4]: up to three hidden-component indices, -1 padded
