@@ -34,7 +34,7 @@ typedef struct sxb_model_info {
     int32_t num_lme;        /* layer-1 output components */
     int32_t shape_id;       /* compiled coupling structure in use */
     int32_t single_layer;   /* 1: single_layer_readout model (no second message step) */
-    int32_t legacy_h1_basis; /* 1: format version 1 / 2 (first readout and skip act on H1, not on M0) */
+    int32_t h1_basis;       /* input of the first readout and the skip: 0 M0 (m0_composite), 1 H1 (format 1 / 2), 2 M0 P0 + residual (pre_linear_up) */
     int32_t reserved;
     double r_cut;
 } sxb_model_info;

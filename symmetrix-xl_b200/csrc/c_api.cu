@@ -100,7 +100,7 @@ int sxb_model_file_info(const char* model_json_path, const char* head, sxb_model
         if (info != nullptr) {
             info->num_elements = m.num_elements; info->num_channels = m.channels; info->l_max = m.l_max;
             info->hidden_l_max = m.hidden_l_max; info->num_paths = m.num_paths; info->num_lme = m.num_lme;
-            info->shape_id = m.shape_id; info->single_layer = m.single_layer ? 1 : 0; info->legacy_h1_basis = m.legacy_h1_basis ? 1 : 0; info->reserved = 0; info->r_cut = m.r_cut;
+            info->shape_id = m.shape_id; info->single_layer = m.single_layer ? 1 : 0; info->h1_basis = m.legacy_h1_basis ? 1 : m.pre_linear_up ? 2 : 0; info->reserved = 0; info->r_cut = m.r_cut;
         }
         if (selected_head != nullptr) {
             if (head_capacity <= static_cast<int32_t>(m.selected_head.size()))
@@ -141,7 +141,7 @@ int sxb_model_info_get(const sxb_evaluator* ev, sxb_model_info* out)
         out->num_lme = m.num_lme;
         out->shape_id = m.shape_id;
         out->single_layer = m.single_layer ? 1 : 0;
-        out->legacy_h1_basis = m.legacy_h1_basis ? 1 : 0;
+        out->h1_basis = m.legacy_h1_basis ? 1 : m.pre_linear_up ? 2 : 0;
         out->reserved = 0;
         out->r_cut = m.r_cut;
     });

@@ -139,6 +139,11 @@ Evaluator::Evaluator(const std::string& json_path, int device_ordinal, const std
     for (int a = 0; a < model_.num_elements; ++a)
         upload_split(s_h2_skip_[a], model_.h2_skip.data() + static_cast<std::size_t>(a) * C * C, C, C);
     upload_split(s_h2_m1_, model_.h2_m1.data(), C, C);
+    if (model_.pre_linear_up) upload_split(s_product0_, model_.w_product0.data(), C, C);
+    if (model_.first_residual) {
+        upload(residual_fused_, model_.residual_fused, stream_);
+        upload(residual_scalar_, model_.residual_scalar, stream_);
+    }
     SXB_ALLOW_POLY_SMEM(m0_forward_kernel_S0, SXB_S0_M0_NUM_TERMS); SXB_ALLOW_POLY_SMEM(m0_reverse_kernel_S0, SXB_S0_M0_NUM_TERMS);
     SXB_ALLOW_POLY_SMEM(m0_forward_kernel_S1, SXB_S1_M0_NUM_TERMS); SXB_ALLOW_POLY_SMEM(m0_reverse_kernel_S1, SXB_S1_M0_NUM_TERMS);
     SXB_ALLOW_POLY_SMEM(m0_forward_kernel_S2, SXB_S2_M0_NUM_TERMS); SXB_ALLOW_POLY_SMEM(m0_reverse_kernel_S2, SXB_S2_M0_NUM_TERMS);
@@ -308,6 +313,10 @@ void Evaluator::install_graph(int num_receivers, int num_nodes, const std::vecto
     M1_adj_.reserve(T * C);
     H2_.reserve(T * C);
     H2_adj_.reserve(N * C);
+    if (model_.pre_linear_up) {   // scalar input of the first readout and the skip, and its adjoint, for every receiver
+        scalar_input_.reserve(N * C);
+        scalar_adjoint_.reserve(N * C);
+    }
     node_energies_.reserve(N);
     if (model_.a0_scaled) { inv_scale0_.reserve(N); dot0_.reserve(N); }
     if (model_.a1_scaled) { inv_scale1_.reserve(N); dot1_.reserve(N); }
@@ -321,6 +330,7 @@ void Evaluator::install_graph(int num_receivers, int num_nodes, const std::vecto
         if (model_.shape_id == 2) throw std::invalid_argument("The reproducible mode is not available for hidden irreps 0e+1o+2e.");
         if (model_.single_layer) throw std::invalid_argument("The reproducible mode is not available for single-layer models.");
         if (model_.legacy_h1_basis) throw std::invalid_argument("The reproducible mode is not available for format-version 1 / 2 models.");
+        if (model_.pre_linear_up) throw std::invalid_argument("The reproducible mode is not available for pre_linear_up models.");
         if (model_.a0_scaled || model_.a1_scaled)
             throw std::invalid_argument("The reproducible mode is not available for density-scaled models.");
         const std::size_t record_floats = static_cast<std::size_t>(num_edges) * NH * C;
@@ -1002,12 +1012,22 @@ void Evaluator::run_pipeline(int phases)
                 calls.push_back({m0, rows, &s_h1_[l], false, H1_.ptr + t0 * rowH, rows, 0, T, false, nullptr});
             }
             // one tile: the element-dependent skip term of H2 (x_i T_element) only needs M0, so it rides in this launch
-            if (!tiled && !model_.legacy_h1_basis)
+            if (!tiled && !model_.legacy_h1_basis && !model_.pre_linear_up)
                 for_type_ranges(t0, T, [&](int a, int begin, int count) {
                     calls.push_back({M0_.ptr + begin * rowH, scalar_rows, &s_h2_skip_[active_types_[a]], false,
                                      H2_.ptr + static_cast<std::size_t>(begin - t0) * C, flat_rows, 0, count, false, nullptr});
                 });
+            if (model_.pre_linear_up)   // x = M0[l=0] P0, the scalar input of the first readout and the skip
+                calls.push_back({m0, scalar_rows, &s_product0_, false, scalar_input_.ptr + static_cast<std::size_t>(t0) * C, flat_rows, 0, T,
+                                 false, nullptr});
             launch_tc(calls);
+            if (model_.first_residual) {   // element-dependent constants: R U joins H1, R of the scalar block joins x
+                add_element_rows_kernel<<<blocks_for(static_cast<long>(T) * rowH, 256), 256, 0, stream_>>>(
+                    T, static_cast<int>(rowH), element_.ptr + t0, residual_fused_.ptr, H1_.ptr + t0 * rowH);
+                add_element_rows_kernel<<<blocks_for(static_cast<long>(T) * C, 256), 256, 0, stream_>>>(
+                    T, C, element_.ptr + t0, residual_scalar_.ptr, scalar_input_.ptr + static_cast<std::size_t>(t0) * C);
+                launches_ += 2;
+            }
             span_end();
         }
         if (phases != 7 && halo_plan_.active && halo_plan_.send_rows != nullptr) {   // forward halo: my owned rows that peers hold as ghosts
@@ -1076,12 +1096,16 @@ void Evaluator::run_pipeline(int phases)
             // H2 = xs T_element + M1 W
             span_begin("gemm_h2");
             {
-                if (tiled || model_.legacy_h1_basis) {
+                if (tiled || model_.legacy_h1_basis || model_.pre_linear_up) {
                     const float* skip_input = model_.legacy_h1_basis ? H1_.ptr : M0_.ptr;   // old basis: the skip reads H1
                     std::vector<TcCall> calls;
                     for_type_ranges(t0, T, [&](int a, int begin, int count) {
-                        calls.push_back({skip_input + begin * rowH, scalar_rows, &s_h2_skip_[active_types_[a]], false,
-                                         H2_.ptr + static_cast<std::size_t>(begin - t0) * C, flat_rows, 0, count, false, nullptr});
+                        if (model_.pre_linear_up)
+                            calls.push_back({scalar_input_.ptr + static_cast<std::size_t>(begin) * C, flat_rows, &s_h2_skip_[active_types_[a]],
+                                             false, H2_.ptr + static_cast<std::size_t>(begin - t0) * C, flat_rows, 0, count, false, nullptr});
+                        else
+                            calls.push_back({skip_input + begin * rowH, scalar_rows, &s_h2_skip_[active_types_[a]], false,
+                                             H2_.ptr + static_cast<std::size_t>(begin - t0) * C, flat_rows, 0, count, false, nullptr});
                     });
                     launch_tc(calls);
                 }
@@ -1089,11 +1113,15 @@ void Evaluator::run_pipeline(int phases)
             }
             span_end();
             span_begin("readout");
-            const float* readout_input = model_.legacy_h1_basis ? H1_.ptr : M0_.ptr;   // scalar block the first readout acts on
+            // scalar block the first readout acts on, and the stride between nodes in components
+            const float* readout_input = model_.pre_linear_up ? scalar_input_.ptr : model_.legacy_h1_basis ? H1_.ptr : M0_.ptr;
+            const int readout_stride = model_.pre_linear_up ? 1 : NH;
+            const std::size_t readout_row = static_cast<std::size_t>(readout_stride) * C;
             if (model_.readout2_hidden == 16 && (C == 128 || C == 32)) {
 #define SXB_READOUT16(CHUNKS)                                                                                             \
                 readout16_kernel<CHUNKS><<<blocks_for(static_cast<long>(T) * 32, 256), 256, 0, stream_>>>(                 \
-                    T, model_.readout2_scale, readout_input + t0 * rowH, NH, H2_.ptr, element_.ptr + t0, atomic_energies_.ptr, \
+                    T, model_.readout2_scale, readout_input + t0 * readout_row, readout_stride, H2_.ptr, element_.ptr + t0,         \
+                    atomic_energies_.ptr,                                                                                 \
                     readout1_.ptr, readout2_w1_.ptr, readout2_w2_.ptr, node_energies_.ptr + t0,                            \
                     H2_adj_.ptr + static_cast<std::size_t>(t0) * C, energy_slots)
                 if (C == 128) SXB_READOUT16(4);
@@ -1101,7 +1129,7 @@ void Evaluator::run_pipeline(int phases)
 #undef SXB_READOUT16
             } else
                 readout_kernel<<<blocks_for(static_cast<long>(T) * 32, 256), 256, 0, stream_>>>(
-                    T, C, model_.readout2_hidden, model_.readout2_scale, readout_input + t0 * rowH, NH, H2_.ptr, element_.ptr + t0,
+                    T, C, model_.readout2_hidden, model_.readout2_scale, readout_input + t0 * readout_row, readout_stride, H2_.ptr, element_.ptr + t0,
                     atomic_energies_.ptr, readout1_.ptr, readout2_w1_.ptr, readout2_w2_.ptr, node_energies_.ptr + t0,
                     H2_adj_.ptr + static_cast<std::size_t>(t0) * C, energy_slots);
             launches_ += 1;
@@ -1113,7 +1141,12 @@ void Evaluator::run_pipeline(int phases)
                                            flat_rows, 0, T, false, nullptr}};
                 // one tile: the direct adjoint of the scalar block of M0, q + T_element H2_adj, is known here already;
                 // the reverse of the H1 linear adds to it later
-                if (!tiled && !model_.legacy_h1_basis)
+                if (model_.pre_linear_up)   // adjoint of x: q + S_element H2_adj, multiplied by P0^T in the last phase
+                    for_type_ranges(t0, T, [&](int a, int begin, int count) {
+                        calls.push_back({H2_adj_.ptr + static_cast<std::size_t>(begin) * C, flat_rows, &s_h2_skip_[active_types_[a]], true,
+                                         scalar_adjoint_.ptr + static_cast<std::size_t>(begin) * C, flat_rows, 0, count, false, readout1_.ptr});
+                    });
+                else if (!tiled && !model_.legacy_h1_basis)
                     for_type_ranges(t0, T, [&](int a, int begin, int count) {
                         calls.push_back({H2_adj_.ptr + static_cast<std::size_t>(begin) * C, flat_rows, &s_h2_skip_[active_types_[a]], true,
                                          M0_adj_.ptr + (begin - t0) * rowH, scalar_rows, 0, count, false, readout1_.ptr});
@@ -1206,7 +1239,17 @@ void Evaluator::run_pipeline(int phases)
             }
             span_begin("gemm_h1_reverse");
             // M0_adj_il = H1_adj_il W_l^T, then the direct adjoint q + T_element H2_adj on the scalar block
-            if (model_.legacy_h1_basis) {
+            if (model_.pre_linear_up) {
+                // M0_adj = H1_adj W^T, then the scalar block gains (q + S_element H2_adj) P0^T
+                std::vector<TcCall> calls;
+                for (int l = 0; l <= model_.hidden_l_max; ++l) {
+                    const RowMap rows{static_cast<long>(NH) * C, C, static_cast<long>(l) * l * C, 2 * l + 1};
+                    calls.push_back({H1_adj_.ptr + t0 * rowH, rows, &s_h1_[l], true, M0_adj_.ptr, rows, 0, T, false, nullptr});
+                }
+                launch_tc(calls);
+                launch_tc({{scalar_adjoint_.ptr + static_cast<std::size_t>(t0) * C, flat_rows, &s_product0_, true, M0_adj_.ptr, scalar_rows, 0, T,
+                            true, nullptr}});
+            } else if (model_.legacy_h1_basis) {
                 // old basis: the skip's adjoint S_element H2_adj joins H1_adj (which started from q) before the linear
                 std::vector<TcCall> calls;
                 for_type_ranges(t0, T, [&](int a, int begin, int count) {

@@ -150,6 +150,8 @@ private:
     // model tables on the device
     DeviceBuffer<float> density0_table_, density1_table_, inv_scale0_, inv_scale1_, dot0_, dot1_;
     DeviceBuffer<float> r0_table_, r1_table_, m0_weights_, m1_weights_, w_h1_, w_a1_[4], h2_skip_, h2_m1_;
+    // pre_linear_up basis: x = M0[l=0] P0 (+ residual) and its adjoint per receiver; residual-first constants per element
+    DeviceBuffer<float> scalar_input_, scalar_adjoint_, residual_fused_, residual_scalar_;
     DeviceBuffer<int> hidden_poly_terms_;          // single-layer models: monomials of the readout polynomial over H1
     DeviceBuffer<float> hidden_poly_weights_;
     DeviceBuffer<float> readout1_, readout2_w1_, readout2_w2_;
@@ -163,6 +165,7 @@ private:
     };
     SplitWeight s_h1_[4], s_a1_[4], s_h2_m1_;
     std::vector<SplitWeight> s_h2_skip_;
+    SplitWeight s_product0_;          // P0 of the pre_linear_up basis
     bool use_tensor_cores_ = true;
     int num_sms_ = 148;
     int r1_pair_types_ = 1;   // active types the layer-1 table distinguishes (1 without a distance transform)

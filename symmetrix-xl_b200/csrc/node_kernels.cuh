@@ -513,6 +513,16 @@ __global__ void fill_scalar_block_kernel(int num_nodes, int C, long node_stride,
     tensor[node * node_stride + k] = values[k];
 }
 
+// tensor[node][:] += table[element[node]][:] over rows of row_floats values (element-dependent constants).
+__global__ void add_element_rows_kernel(int num_nodes, int row_floats, const unsigned char* __restrict__ element,
+                                        const float* __restrict__ table, float* __restrict__ tensor)
+{
+    const long index = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (index >= static_cast<long>(num_nodes) * row_floats) return;
+    const long node = index / row_floats, k = index - node * row_floats;
+    tensor[index] += table[static_cast<long>(element[node]) * row_floats + k];
+}
+
 // Closing kernel of an evaluation, one thread per output value: sums the energy / virial slots into
 // totals[10] and writes node energies and node forces in the caller's node order.  When `host` is
 // given the same values are also published straight into mapped pinned host memory, laid out

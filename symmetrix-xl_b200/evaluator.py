@@ -29,8 +29,11 @@ _lib = None
 class ModelInfo(ctypes.Structure):
     _fields_ = [("num_elements", ctypes.c_int32), ("num_channels", ctypes.c_int32), ("l_max", ctypes.c_int32),
                 ("hidden_l_max", ctypes.c_int32), ("num_paths", ctypes.c_int32), ("num_lme", ctypes.c_int32),
-                ("shape_id", ctypes.c_int32), ("single_layer", ctypes.c_int32), ("legacy_h1_basis", ctypes.c_int32),
+                ("shape_id", ctypes.c_int32), ("single_layer", ctypes.c_int32), ("h1_basis", ctypes.c_int32),
                 ("reserved", ctypes.c_int32), ("r_cut", ctypes.c_double)]
+
+
+H1_BASIS_NAMES = ("m0_composite", "legacy", "pre_linear_up")     # sxb_model_info.h1_basis
 
 
 # name -> (restype, argtypes); every symbol include/symmetrix_b200.h declares
@@ -160,7 +163,7 @@ def model_file_info(filename, head: str = ""):
     return {"num_elements": info.num_elements, "num_channels": info.num_channels, "l_max": info.l_max,
             "L_max": info.hidden_l_max, "num_paths": info.num_paths, "num_lme": info.num_lme, "shape_id": info.shape_id,
             "r_cut": info.r_cut, "single_layer": bool(info.single_layer),
-            "h1_affine_mode": "legacy" if info.legacy_h1_basis else "m0_composite", "head": name.value.decode(), "atomic_energies": energies[:info.num_elements].copy()}
+            "h1_affine_mode": H1_BASIS_NAMES[info.h1_basis], "head": name.value.decode(), "atomic_energies": energies[:info.num_elements].copy()}
 
 
 def measure_device_peaks(device: int = 0):
@@ -199,7 +202,7 @@ class MACEB200:
         _check(lib.sxb_atomic_energies(self._h, e0.ctypes.data, len(e0)))
         self.atomic_energies = e0.tolist()
         self.single_layer_readout = bool(info.single_layer)
-        self.h1_affine_mode = "legacy" if info.legacy_h1_basis else "m0_composite"
+        self.h1_affine_mode = H1_BASIS_NAMES[info.h1_basis]
         self._num_nodes = 0
         self._num_edges = 0
         self._tile_size = 0

@@ -55,7 +55,7 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
                radial_hidden=(64, 64, 64), num_bessel: int = 8, cutoff_p: int = 5,
                a0_scaled: bool = False, a1_scaled: bool = False, zbl: bool = False,
                agnesi: bool = False, heads=(), radial: str = "compact", single_layer: bool = False,
-               format_version: int = 4) -> dict:
+               format_version: int = 4, pre_linear_up: bool = False, first_residual: bool = False) -> dict:
     """Random-weight model of architecture ``arch`` as a JSON-serialisable dict.  ``radial`` selects the
     radial representation: "compact" (radial networks) or "pair-splines" (stored nodal values and
     derivatives per unordered element pair, the exporter's older form)."""
@@ -67,6 +67,10 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
         raise ValueError("format_version must be 4 or 2 (the old basis: first readout and skip stored on H1)")
     if format_version == 2 and heads:
         raise ValueError("prediction heads need format version 4")
+    if first_residual and not pre_linear_up:
+        raise ValueError("a first-interaction residual needs the pre_linear_up basis")
+    if pre_linear_up and (format_version != 4 or single_layer or heads):
+        raise ValueError("the pre_linear_up basis is a format-4, two-interaction, single-head form")
     if single_layer and a1_scaled:
         raise ValueError("a single-layer model has no second message step to scale")
     cfg = dict(ARCHITECTURES[arch])
@@ -210,6 +214,22 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
         "readout_2_hidden_size": 16,
         "readout_2_scale_factor": 1.679177,
     }
+    if pre_linear_up:
+        # the file keeps the product map P and linear_up U apart (H1_weights = P U still feeds the second interaction);
+        # the first readout and the skip act on x = M0[l=0] P0 (+ the residual's scalar block)
+        P = normal(L_max + 1, C, C, scale=1.0 / np.sqrt(C))
+        U = normal(L_max + 1, C, C, scale=1.0 / np.sqrt(C)) + np.eye(C)[None] * 0.5
+        model["h1_affine_mode"] = "pre_linear_up"
+        model["H1_product_weights"] = P.reshape(-1).tolist()
+        model["H1_linear_up_weights"] = U.reshape(-1).tolist()
+        model["H1_weights"] = np.einsum("lij,ljk->lik", P, U).reshape(-1).tolist()
+        model["readout_1_weights_for_H1_pre_linear_up"] = model.pop("readout_1_weights_for_M0")
+        model["H2_weights_for_H1_pre_linear_up"] = model.pop("H2_weights_for_M0")
+        if first_residual:
+            model["first_interaction_residual"] = True
+            residual = np.zeros((A, num_LM, C))
+            residual[:, 0, :] = normal(A, C, scale=0.3)      # an element-dependent constant on the scalar block
+            model["H1_first_residual_weights"] = residual.reshape(-1).tolist()
     if format_version == 2:
         # old basis (format versions 1 / 2): the first readout and the H1 -> H2 skip act on the scalar block of H1
         model["symmetrix_format_version"] = 2

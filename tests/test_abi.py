@@ -151,6 +151,20 @@ def test_model_loader_tells_the_h1_affine_basis_on_the_host(pkg, tmp_path):
         return pkg.model_file_info(tmp_path / "m.json")
 
     assert info(new)["h1_affine_mode"] == "m0_composite" and info(old)["h1_affine_mode"] == "legacy"
+    split = pkg.modelgen.make_model("small", seed=7, pre_linear_up=True, first_residual=True)
+    assert info(split)["h1_affine_mode"] == "pre_linear_up"
+    for change in (lambda m: m.__delitem__("H1_product_weights"),                       # the split basis needs P
+                   lambda m: m.__setitem__("readout_1_weights_for_M0", [0.0] * 32),     # a field of the other basis
+                   lambda m: m.__setitem__("H1_first_residual_weights", [0.0] * 5),     # wrong residual extent
+                   lambda m: m.__setitem__("single_layer_readout", True)):
+        broken = json.loads(json.dumps(split))
+        change(broken)
+        with pytest.raises(ValueError):
+            info(broken)
+    residual_in_m0 = json.loads(json.dumps(new))
+    residual_in_m0["first_interaction_residual"] = True                                  # needs the pre_linear_up basis
+    with pytest.raises(ValueError):
+        info(residual_in_m0)
     for change in (lambda m: m.__setitem__("h1_affine_mode", "m0_composite"),          # a format-4 field in a format-2 file
                    lambda m: m.__setitem__("symmetrix_format_version", 3),
                    lambda m: m.__setitem__("prediction_heads", {})):
@@ -158,7 +172,7 @@ def test_model_loader_tells_the_h1_affine_basis_on_the_host(pkg, tmp_path):
         change(broken)
         with pytest.raises(ValueError):
             info(broken)
-    for change in (lambda m: m.__setitem__("h1_affine_mode", "pre_linear_up"),
+    for change in (lambda m: m.__setitem__("h1_affine_mode", "pre_linear_up"),          # without the fields of that basis
                    lambda m: m.__setitem__("h1_affine_version", 2),
                    lambda m: m.__setitem__("readout_1_weights", m["readout_1_weights_for_M0"])):   # old-basis field in format 4
         broken = json.loads(json.dumps(new))

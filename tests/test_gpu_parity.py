@@ -181,6 +181,26 @@ def test_old_basis_models_vs_reference_evaluator(pkg, model_path, arch, n, kwarg
     _assert_matches_reference(tiled.calculate(pos, cell, types), e, F, S, len(pos), node_tol=3e-5)
 
 
+@pytest.mark.parametrize("arch,n,kwargs", [("small", 3, {}), ("medium", 2, {"first_residual": True}),
+                                           ("large", 2, {"first_residual": True, "a0_scaled": True, "a1_scaled": True})])
+def test_pre_linear_up_models_vs_reference_evaluator(pkg, model_path, arch, n, kwargs):
+    """Format 4 in the pre_linear_up basis: the first readout and the skip act on x = M0[l=0] P0 (+ the scalar block of the
+    first-interaction residual), and an element-dependent constant R U joins H1 (libsymmetrix/source/mace.cpp:1759-1888);
+    untiled and tiled."""
+    if not ref.available():
+        pytest.skip("oracle/_ref was not built")
+    path = model_path(arch, seed=61, pre_linear_up=True, **kwargs)
+    pos, cell, types = pkg.modelgen.srtio3(n, 0.05, 63)
+    calc = pkg.Calculator(path, skin=0.5)
+    assert calc.evaluator.h1_affine_mode == "pre_linear_up"
+    out = calc.calculate(pos, cell, types)
+    e, F, S = _reference_efs(path, pos, cell, types, calc.evaluator.r_cut, double=True)
+    _assert_matches_reference(out, e, F, S, len(pos), node_tol=3e-5)
+    tiled = pkg.Calculator(path, skin=0.5)
+    tiled.evaluator.set_tile_size(16)
+    _assert_matches_reference(tiled.calculate(pos, cell, types), e, F, S, len(pos), node_tol=3e-5)
+
+
 def test_headline_configuration_vs_reference_evaluator(pkg, model_path):
     """The configuration the throughput is quoted on, at full size: OMAT-0-medium architecture,
     10x10x10 SrTiO3 (5,000 atoms, sigma 0.05 A), 0.5 A skin, against MACECPU<float>."""
