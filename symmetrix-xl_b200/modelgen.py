@@ -236,6 +236,10 @@ def make_model(arch: str = "medium", seed: int = 0, atomic_numbers=(8, 22, 38), 
         del model["h1_affine_mode"], model["h1_affine_version"]
         model["readout_1_weights"] = model.pop("readout_1_weights_for_M0")
         model["H2_weights_for_H1"] = model.pop("H2_weights_for_M0")
+        if single_layer:
+            # exported single-layer models carry a zero first readout; the reference's serial evaluator relies on it (it
+            # clears the readout's adjoint on its single-layer path, libsymmetrix/source/mace.cpp:265-271)
+            model["readout_1_weights"] = [0.0] * C
     if single_layer:
         # H1 feeds a cubic polynomial directly: keep it O(1) so that the readout stays well conditioned in FP32
         model["H1_weights"] = (0.3 * np.asarray(model["H1_weights"])).tolist()
