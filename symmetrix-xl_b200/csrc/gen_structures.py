@@ -28,9 +28,7 @@ def _load_pkg():
 # (name, edge l_max, hidden L_max, number of path sets of the split layer-1 kernels, optional explicit sets)
 # S2: set 0 = all paths with source l = 0 or 1 (88 rows, 4 source components), sets 1 and 2 share the
 # source l = 2 paths (80 and 75 rows, 5 source components each)
-# S1: two sets by the parity of the edge l (odd: 49 rows, even: 39 rows) for the kernel that gives each
-# channel two threads; a set then needs only its own edge harmonics and harmonic gradients
-SHAPES = [("S0", 3, 0, 1, None), ("S1", 3, 1, 2, [[1, 2, 6, 7, 8], [0, 3, 4, 5, 9]]),
+SHAPES = [("S0", 3, 0, 1, None), ("S1", 3, 1, 1, None),
           ("S2", 3, 2, 3, [[0, 3, 8, 13, 1, 4, 5, 9, 10, 14], [7, 2, 6, 11], [16, 12, 15]])]
 
 
