@@ -1331,7 +1331,9 @@ void Evaluator::run_pipeline(int phases)
         }
         publish_results_kernel<<<blocks_for(11 + static_cast<long>(R) + 3 * static_cast<long>(ALL), 256), 256, 0, stream_>>>(
             R, ALL, internal_of_.ptr, energy_slots_.ptr, virial_slots_.ptr, node_energies_.ptr, forces_.ptr, error_flag_.ptr, totals_.ptr,
-            node_energies_out_.ptr, forces_out_.ptr, host_results_);
+            node_energies_out_.ptr, forces_out_.ptr, host_results_,
+            // a decomposed run with a halo plan keeps energies and forces on the device: status and totals only
+            (phases != 7 && halo_plan_.active) ? 11L : 11 + static_cast<long>(R) + 3 * static_cast<long>(ALL));
         launches_ += 1;
         if (phases != 7 && halo_plan_.active) {
             have_results_ = true;
@@ -1436,7 +1438,7 @@ void Evaluator::finish_compute()
         SXB_CUDA(cudaStreamSynchronize(stream_));
         flag = static_cast<int>(host_results_[0]);
         std::memcpy(host_totals_, host_results_ + 1, 10 * sizeof(double));
-        mirror_valid_ = true;
+        mirror_valid_ = !halo_plan_.active;     // with a halo plan only status and totals were published
     } else {
         SXB_CUDA(cudaMemcpyAsync(&flag, error_flag_.ptr, sizeof(int), cudaMemcpyDeviceToHost, stream_));
         SXB_CUDA(cudaMemcpyAsync(host_totals_, totals_.ptr, 10 * sizeof(double), cudaMemcpyDeviceToHost, stream_));

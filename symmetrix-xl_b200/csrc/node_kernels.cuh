@@ -528,13 +528,14 @@ __global__ void add_element_rows_kernel(int num_nodes, int row_floats, const uns
 // given the same values are also published straight into mapped pinned host memory, laid out
 // [status word, totals[10], energies[num_receivers], forces[num_nodes][3]] (consecutive threads write
 // consecutive words, so the writes cross the bus in full segments), and the caller needs no
-// device-to-host copy.
+// device-to-host copy.  Only the first `host_values` values go to the host (a caller that keeps the forces
+// on the device asks for status and totals alone and saves the bus traffic).
 __global__ void publish_results_kernel(int num_receivers, int num_nodes, const int* __restrict__ internal_of,
                                        const double* __restrict__ energy_slots, const double* __restrict__ virial_slots,
                                        const double* __restrict__ node_energies, const double* __restrict__ forces,
                                        const int* __restrict__ status, double* __restrict__ totals,
                                        double* __restrict__ energies_out, double* __restrict__ forces_out,
-                                       double* __restrict__ host)
+                                       double* __restrict__ host, long host_values)
 {
     const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
     const long total = 11 + static_cast<long>(num_receivers) + 3 * static_cast<long>(num_nodes);
@@ -557,7 +558,7 @@ __global__ void publish_results_kernel(int num_receivers, int num_nodes, const i
         value = forces[3 * static_cast<long>(internal_of[o]) + q];
         forces_out[j] = value;
     }
-    if (host != nullptr) host[idx] = value;
+    if (host != nullptr && idx < host_values) host[idx] = value;
 }
 
 }  // namespace sxb
