@@ -220,7 +220,7 @@ def run_distributed(args):
         barrier()
         clocks = sampler.stop()
         # per-stage device times of this rank's kernels (separate passes with event pairs around each stage)
-        calc.ev.set_profiling(True)
+        calc.set_profiling(True)
         stage_ms = {}
         for _ in range(3):
             flush.fill_(1)
@@ -228,7 +228,11 @@ def run_distributed(args):
             step_device()
             for name, ms, _l in calc.ev.profile():
                 stage_ms[name] = stage_ms.get(name, 0.0) + ms / 3
-        calc.ev.set_profiling(False)
+        calc.set_profiling(False)
+        # where a step spends its time: the four exchanges and the three phases, from eager launches (outside the timed region)
+        barrier()
+        timeline = calc.timeline(5)
+        barrier()
         t = torch.tensor([float(np.mean(device_ms)), float(np.mean(e2e_ms))], device="cuda", dtype=torch.float64)
         if world > 1:
             all_reduce(t, op=dist.ReduceOp.MAX)
@@ -276,6 +280,7 @@ def run_distributed(args):
                 "roofline": None,
                 "parity_vs_single_gpu": parity,
                 "stage_ms_rank0": {k: round(v, 4) for k, v in stage_ms.items()},
+                "step_timeline_ms_rank0": {k: round(v, 4) for k, v in timeline.items()},
                 "step_ms_rank0": {"min": float(np.min(device_ms)), "median": float(np.median(device_ms)), "max": float(np.max(device_ms))},
                 "energy_eV_per_atom": last_out["energy"] / total_atoms,
                 "wall_ms_timed_region": wall_ms,

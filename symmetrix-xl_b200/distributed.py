@@ -7,9 +7,11 @@ the atoms inside its brick and keeps ghost copies of every atom image within the
 forward exchange of ghost features and one reverse exchange of ghost adjoints per evaluation, plus
 ghost positions in and ghost forces out -- the protocol of the reference's LAMMPS pair style
 (pair_symmetrix/pair_symmetrix_mace_kokkos.cpp:1285-1938; phases
-libsymmetrix/source/mace_kokkos_evaluate.cpp:1658-2101), carried here by ``torch.distributed``
-all-to-all exchanges (NCCL over NVLink between GPUs, gloo in the CPU tests of the exchange plan)
-instead of LAMMPS' MPI brick swaps.  Remote rows always land in a local receive buffer first; no
+libsymmetrix/source/mace_kokkos_evaluate.cpp:1658-2101), carried here, instead of LAMMPS' MPI brick
+swaps, by pushes into the peers' memory over NVLink (``PeerTransport``: every rank writes its rows into
+the receiving rank's buffers and raises a flag there) or, where peer mapping is unavailable, by
+``torch.distributed`` all-to-all exchanges (NCCL between GPUs, gloo in the CPU tests of the exchange
+plan).  Remote rows always land in the receiving rank's own memory before any kernel reads them; no
 kernel of this package reads another GPU's memory.
 """
 from __future__ import annotations
@@ -434,10 +436,10 @@ class DistributedCalculator:
         with torch.cuda.stream(self.stream):
             if owned_positions is not None and owned_positions.data_ptr() != self.local_positions.data_ptr():
                 self.local_positions[:n_own].copy_(owned_positions)
-            if self._step_graph is not None:
+            if self._step_graph is not None and not getattr(self, "_profiling", False):
                 self._step_graph.replay()
                 self.ev.distributed_replayed(self.generation, self._step_graph_launches)
-            elif self._capture_allowed and self._eager_steps >= 2:
+            elif self._capture_allowed and self._eager_steps >= 2 and self._step_graph is None:
                 self._capture_step()
             else:
                 self._enqueue_step()
@@ -486,6 +488,36 @@ class DistributedCalculator:
             self.ev.distributed_abort()
             self._enqueue_step()
 
+    def set_profiling(self, enabled: bool):
+        """Per-stage event timing of the evaluator's kernels (``ev.profile()``); steps then run as eager launches,
+        because the replayed graph of a normal step has no stage boundaries."""
+        self._profiling = bool(enabled)
+        self.ev.set_profiling(enabled)
+
+    def timeline(self, repeats=5):
+        """Device time of the seven segments of a step -- the four exchanges and the three phases -- from CUDA events
+        between eager launches on the calculator's stream (ms, mean over ``repeats`` steps).  A diagnostic: the
+        replayed graph of a normal step has no such boundaries.  Collective: every rank must call it."""
+        torch = self.torch
+        names = ["positions", "phase_1", "h1", "phase_2", "h1_adj", "phase_3", "forces"]
+        total = dict.fromkeys(names, 0.0)
+        with torch.cuda.stream(self.stream):
+            for _ in range(repeats):
+                marks = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
+                self._marks = iter(marks)
+                next(self._marks).record(self.stream)
+                self._enqueue_step()
+                self._marks = None
+                self.ev.synchronize()
+                for name, a, b in zip(names, marks[:-1], marks[1:]):
+                    total[name] += a.elapsed_time(b) / repeats
+        return total
+
+    def _mark(self):
+        marks = getattr(self, "_marks", None)
+        if marks is not None:
+            next(marks).record(self.stream)
+
     def _enqueue_step(self):
         ev, plan, comm = self.ev, self.plan, self.comm
         n_own, n_ghost = plan.num_owned, plan.num_ghost
@@ -503,19 +535,25 @@ class DistributedCalculator:
             peer.exchange(peer.PHASE_POSITIONS, stream)
         else:
             comm.all_to_all(self._send_pos, sc, rc, out=local_pos[n_own:])
+        self._mark()
         ev.distributed_begin(self.generation, local_pos.data_ptr())       # ends by packing my H1 rows into _send_rows
+        self._mark()
         # forward halo: into the tail of the feature tensor of the ranks that hold my atoms as ghosts
         if peer is not None:
             peer.exchange(peer.PHASE_H1, stream)
         else:
             comm.all_to_all(self._send_rows, sc, rc, out=self._h1_tail)
+        self._mark()
         ev.distributed_continue()
+        self._mark()
         # reverse halo: H1_adj rows of my ghosts leave from the tail of the adjoint tensor and are summed at their owners
         if peer is not None:
             peer.exchange(peer.PHASE_H1_ADJ, stream)
         else:
             comm.all_to_all(self._h1_adj_tail, rc, sc, out=self._got_rows)
+        self._mark()
         ev.distributed_finish()       # starts by adding _got_rows, ends by packing ghost forces + totals into _force_send
+        self._mark()
         # ghost forces back to the owners, with every rank's energy and virial riding along
         if peer is not None:
             peer.exchange(peer.PHASE_FORCES, stream)
@@ -524,6 +562,7 @@ class DistributedCalculator:
         ev.unpack_ghost_forces(world, self._send_begin.data_ptr(), self.send_local.data_ptr(), n_send, self._force_recv.data_ptr(),
                                self._totals.data_ptr())
         self._totals_host.copy_(self._totals, non_blocking=True)
+        self._mark()
 
 
 def _as_tensor(torch, ptr, shape, dtype, device):
