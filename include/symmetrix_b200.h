@@ -62,6 +62,10 @@ const char* sxb_last_error(void);
 /* Number of CUDA devices this process can use (0 when there is none or the driver is missing); a
  * multi-rank host maps its ranks onto them (the reference leaves this to Kokkos' device selection). */
 int sxb_device_count(void);
+/* What the evaluator's `device_cuda_environment` attribute reports about its device
+ * (symmetrix/source/cpp/mace_kokkos.cpp:807-828): name, and values[6] = compute capability code (100 for
+ * sm_100), multiprocessor count, warp width, CUDA runtime version, driver version, device memory in MiB. */
+int sxb_device_properties(int32_t device_ordinal, char* name, int32_t name_capacity, int64_t* values6);
 
 /* Attributes atomic_numbers, atomic_energies, r_cut, num_channels ... of the Python class
  * (symmetrix/source/cpp/mace_kokkos.cpp:2040-2087). */

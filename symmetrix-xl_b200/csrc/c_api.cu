@@ -73,6 +73,31 @@ int sxb_device_count(void)
     return count;
 }
 
+int sxb_device_properties(int32_t device_ordinal, char* name, int32_t name_capacity, int64_t* values6)
+{
+    return guarded([&] {
+        if (name == nullptr || name_capacity <= 0 || values6 == nullptr) throw std::invalid_argument("NULL output argument.");
+        int count = 0;
+        if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) {
+            cudaGetLastError();
+            throw std::runtime_error("No CUDA device is available.");
+        }
+        if (device_ordinal < 0 || device_ordinal >= count) throw std::invalid_argument("CUDA device ordinal is out of range.");
+        cudaDeviceProp prop;
+        if (cudaGetDeviceProperties(&prop, device_ordinal) != cudaSuccess) throw std::runtime_error("cudaGetDeviceProperties failed.");
+        std::snprintf(name, static_cast<std::size_t>(name_capacity), "%s", prop.name);
+        int runtime = 0, driver = 0;
+        cudaRuntimeGetVersion(&runtime);
+        cudaDriverGetVersion(&driver);
+        values6[0] = prop.major * 10 + prop.minor;
+        values6[1] = prop.multiProcessorCount;
+        values6[2] = prop.warpSize;
+        values6[3] = runtime;
+        values6[4] = driver;
+        values6[5] = static_cast<int64_t>(prop.totalGlobalMem >> 20);
+    });
+}
+
 int sxb_create(const char* model_json_path, int device_ordinal, sxb_evaluator** out)
 {
     return guarded([&] {

@@ -49,6 +49,7 @@ SIGNATURES = {
     "sxb_destroy": (None, [_P]),
     "sxb_last_error": (ctypes.c_char_p, []),
     "sxb_device_count": (ctypes.c_int, []),
+    "sxb_device_properties": (ctypes.c_int, [ctypes.c_int32, ctypes.c_char_p, ctypes.c_int32, _P]),
     "sxb_model_info_get": (ctypes.c_int, [_P, ctypes.POINTER(ModelInfo)]),
     "sxb_atomic_numbers": (ctypes.c_int, [_P, _P, ctypes.c_int32]),
     "sxb_atomic_energies": (ctypes.c_int, [_P, _P, ctypes.c_int32]),
@@ -183,6 +184,9 @@ class MACEB200:
         _check(lib.sxb_create_with_head(str(filename).encode(), int(device), (head or "").encode(), ctypes.byref(handle)))
         self._h = handle
         self._lib = lib
+        self.device = int(device)
+        self.jit_cuda_plugin_ready = False
+        self.jit_cuda_plugin_path = ""
         name = ctypes.create_string_buffer(256)
         _check(lib.sxb_selected_head(self._h, name, 256))
         self.head = name.value.decode()
@@ -267,7 +271,50 @@ class MACEB200:
             raise ValueError("Graph exceeds 32-bit node or edge indexing.")
 
     def _load_jit_cuda_plugin(self, path, persistent_blocks_per_compute_unit=4):
-        raise RuntimeError("the layer-1 kernels of this library are compiled in; it loads no kernel plugin")
+        """The reference calculator builds a model-specific kernel plugin for its ``direct`` mode and hands it to the
+        evaluator (calculator.py:2549-2563).  This library's layer-1 kernels are specialised at compile time, so the
+        plugin is checked -- it must be a loadable library that exports ``symmetrix_jit_cuda_plugin_query_v2`` -- and
+        recorded, and the compiled-in kernels keep serving the stage.  A file that is no such plugin raises, as the
+        reference's loader does."""
+        if int(persistent_blocks_per_compute_unit) <= 0:
+            raise ValueError("persistent_blocks_per_compute_unit must be positive")
+        try:
+            plugin = ctypes.CDLL(str(path))
+            getattr(plugin, "symmetrix_jit_cuda_plugin_query_v2")
+        except (OSError, AttributeError) as error:
+            raise RuntimeError(f"{path} is not a loadable Symmetrix CUDA kernel plugin: {error}") from error
+        self.jit_cuda_plugin_path = str(path)
+        self.jit_cuda_plugin_ready = True
+
+    @property
+    def jit_cuda_plugin_artifact_id(self):
+        """Identity of the layer-1 kernels in use: the compiled-in ones."""
+        return f"symmetrix-xl-b200-r1-{self.num_channels}-l{self.l_max}-L{self.L_max}"
+
+    @property
+    def device_cuda_environment(self):
+        """The dictionary the calculator reads to choose a compile target (symmetrix/source/cpp/mace_kokkos.cpp:807-828)."""
+        name = ctypes.create_string_buffer(256)
+        values = (ctypes.c_int64 * 6)()
+        _check(load_library().sxb_device_properties(self.device, name, 256, values))
+        code = int(values[0])
+        return {"available": True, "backend": "cuda", "device_name": name.value.decode(), "device_ordinal": self.device,
+                "compute_capability": f"{code // 10}.{code % 10}", "compute_capability_code": code,
+                "multiprocessor_count": int(values[1]), "warp_width": int(values[2]), "runtime_version": int(values[3]),
+                "driver_version": int(values[4])}
+
+    @property
+    def execution_device_execution_environment(self):
+        """Wider form of the same report (symmetrix/source/cpp/device_environment.hpp:7-37)."""
+        base = self.device_cuda_environment
+        memory_mib = (ctypes.c_int64 * 6)()
+        name = ctypes.create_string_buffer(256)
+        _check(load_library().sxb_device_properties(self.device, name, 256, memory_mib))
+        base.update({"execution_space": "Cuda", "memory_space": "CudaSpace", "device_memory": int(memory_mib[5]) << 20,
+                     "architecture": f"sm_{base['compute_capability_code']}", "native_subgroup_width": base["warp_width"],
+                     "compute_unit_count": base["multiprocessor_count"], "aot_available": True, "jit_available": False,
+                     "batched_blas_available": False})
+        return base
 
     @property
     def execution_plan_report(self):

@@ -37,8 +37,18 @@ def test_attribute_surface(pkg, model_path):
         ev._validate_graph_cardinality(10, 5, 100)
     with pytest.raises(ValueError):
         ev._validate_graph_cardinality(10, 12, 2 ** 31)
+    # the calculator hands over the kernel plugin it built for its direct mode: a real plugin is accepted and recorded
+    # (the compiled-in kernels keep serving the stage), anything else is refused
     with pytest.raises(RuntimeError):
         ev._load_jit_cuda_plugin("plugin.so")
+    assert not ev.jit_cuda_plugin_ready
+    ev._load_jit_cuda_plugin(pkg.LIBRARY_PATH, 4)       # this library exports the plugin query itself
+    assert ev.jit_cuda_plugin_ready and ev.jit_cuda_plugin_artifact_id == "symmetrix-xl-b200-r1-32-l3-L0"
+    environment = ev.device_cuda_environment
+    assert environment["available"] and environment["backend"] == "cuda" and environment["compute_capability_code"] == 100
+    assert environment["multiprocessor_count"] > 0 and environment["warp_width"] == 32
+    wide = ev.execution_device_execution_environment
+    assert wide["execution_space"] == "Cuda" and wide["device_memory"] > 0 and wide["architecture"] == "sm_100"
     pos, cell, types = pkg.modelgen.srtio3(2, 0.05, 1)
     ev._prepare_periodic_factorized_graph(types, pos, cell, np.linalg.inv(cell), 5.5)
     report = ev.execution_plan_report
