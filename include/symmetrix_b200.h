@@ -51,6 +51,9 @@ int sxb_create(const char* model_json_path, int device_ordinal, sxb_evaluator** 
  * (empty for a file without heads) into out[capacity]. */
 int sxb_create_with_head(const char* model_json_path, int device_ordinal, const char* head, sxb_evaluator** out);
 int sxb_selected_head(const sxb_evaluator* evaluator, char* out, int32_t capacity);
+/* The names of all heads the file carries (attribute available_heads, symmetrix/source/cpp/mace_kokkos.cpp:2088-2100),
+ * joined by newlines into out[capacity]; empty for a file without heads. */
+int sxb_available_heads(const sxb_evaluator* evaluator, char* out, int32_t capacity);
 /* Parses and validates a model file on the host only (no CUDA device is touched): the structure it
  * would run with, the head that would be selected and that head's atomic energies.  Counterpart of
  * the reference's metadata inspection (libsymmetrix/source/model_metadata.cpp).  Any output pointer

@@ -150,6 +150,21 @@ int sxb_selected_head(const sxb_evaluator* ev, char* out, int32_t capacity)
     });
 }
 
+int sxb_available_heads(const sxb_evaluator* ev, char* out, int32_t capacity)
+{
+    return guarded([&] {
+        require(ev, "evaluator");
+        require(out, "out");
+        std::string joined;
+        for (const std::string& name : ev->impl.model().available_heads) {
+            if (!joined.empty()) joined += '\n';
+            joined += name;
+        }
+        if (capacity <= static_cast<int32_t>(joined.size())) throw std::invalid_argument("head name buffer is too small.");
+        std::memcpy(out, joined.c_str(), joined.size() + 1);
+    });
+}
+
 void sxb_destroy(sxb_evaluator* evaluator) { delete evaluator; }
 
 int sxb_model_info_get(const sxb_evaluator* ev, sxb_model_info* out)

@@ -42,6 +42,7 @@ SIGNATURES = {
     "sxb_create": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(_P)]),
     "sxb_create_with_head": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.c_char_p, ctypes.POINTER(_P)]),
     "sxb_selected_head": (ctypes.c_int, [_P, ctypes.c_char_p, ctypes.c_int32]),
+    "sxb_available_heads": (ctypes.c_int, [_P, ctypes.c_char_p, ctypes.c_int32]),
     "sxb_model_file_info": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_char_p, ctypes.POINTER(ModelInfo), ctypes.c_char_p,
                                            ctypes.c_int32, _P, ctypes.c_int32]),
     "sxb_measure_device_peaks": (ctypes.c_int, [ctypes.c_int32, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]),
@@ -190,6 +191,11 @@ class MACEB200:
         name = ctypes.create_string_buffer(256)
         _check(lib.sxb_selected_head(self._h, name, 256))
         self.head = name.value.decode()
+        self.selected_head = self.head
+        names = ctypes.create_string_buffer(4096)
+        _check(lib.sxb_available_heads(self._h, names, 4096))
+        self.available_heads = [n for n in names.value.decode().split("\n") if n]
+        self.supports_factorized = True      # the calculator's "auto" then selects its direct mode
         info = ModelInfo()
         _check(lib.sxb_model_info_get(self._h, ctypes.byref(info)))
         self.num_elements = info.num_elements

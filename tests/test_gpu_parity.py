@@ -260,7 +260,8 @@ def test_multi_head_model_uses_the_selected_head(pkg, model_path, tmp_path):
     path = model_path("small", seed=8, heads=("pbe", "omat"), zbl=True)
     pos, cell, types = pkg.modelgen.srtio3(3, 0.05, 2)
     calc = pkg.Calculator(path, skin=0.5)
-    assert calc.evaluator.head == "omat"
+    assert calc.evaluator.head == "omat" and calc.evaluator.selected_head == "omat"
+    assert calc.evaluator.available_heads == ["pbe", "omat"] and calc.evaluator.supports_factorized
     out = calc.calculate(pos, cell, types)
     e, F, S = _reference_efs(path, pos, cell, types, calc.evaluator.r_cut)
     _assert_matches_reference(out, e, F, S, len(pos))
