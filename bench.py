@@ -122,6 +122,60 @@ def build_workload(tmpdir, cells=SUPERCELL, workload="srtio3", atoms=20000):
     return pkg, model, pos, cell, types
 
 
+def edge_kernel_roofline(ev, stage_ms, num_edges, active_edges, n, measured, hbm_peak, peak_kind, traffic_key=None):
+    """The `roofline` object of the bench line from the per-stage times of one rank: for every edge kernel the FP32,
+    L2 and HBM fractions against measured denominators; the dominant kernel's larger fraction is `frac`.
+    n = receivers of the rank, num_edges / active_edges = its edges in the list / inside the model cutoff."""
+    C = ev.num_channels
+    dominant = max((k for k in stage_ms if k in FLOP_PER_EDGE_CHANNEL), key=lambda k: stage_ms[k])
+    num_lme, num_hidden = ev.num_lme, (ev.L_max + 1) ** 2
+    # compulsory HBM bytes of one launch of each edge kernel: geometry record + source
+    # index per edge, plus the node rows the kernel must read / write once
+    node_rows = {"l0_forward": 16, "l0_reverse": 16, "l1_forward": num_lme + num_hidden,
+                 "l1_reverse": num_lme + 3 * num_hidden}
+    # spline coefficients the formulation pulls from L2 per active edge: 16 B per radial function
+    # (+ the source feature rows in layer 1)
+    l2_bytes_per_edge = {"l0_forward": 16 * 4 * C, "l0_reverse": 16 * 4 * C,
+                         "l1_forward": 16 * ev.num_paths * C + 4 * num_hidden * C,
+                         "l1_reverse": 16 * ev.num_paths * C + 8 * num_hidden * C}
+    kernels = {}
+    for name in FLOP_PER_EDGE_CHANNEL:
+        if name not in stage_ms:
+            continue
+        seconds = stage_ms[name] * 1e-3
+        flops = FLOP_PER_EDGE_CHANNEL[name] * active_edges * C
+        hbm_bytes = num_edges * 20 + n * node_rows[name] * C * 4
+        l2_bytes = l2_bytes_per_edge[name] * active_edges
+        kernels[name] = {"ms": stage_ms[name], "fp32_tflops": flops / seconds / 1e12,
+                         "fp32_frac": flops / seconds / 1e12 / measured["fp32_fma_tflops"],
+                         "hbm_gbs": hbm_bytes / seconds / 1e9, "hbm_frac": hbm_bytes / seconds / 1e9 / hbm_peak,
+                         "l2_gbs": l2_bytes / seconds / 1e9, "l2_frac": l2_bytes / seconds / 1e9 / measured["l2_read_gbs"]}
+    dom = kernels[dominant]
+    alg_bytes = num_edges * 20 + n * node_rows[dominant] * C * 4
+    alg_flops = FLOP_PER_EDGE_CHANNEL[dominant] * active_edges * C
+    # DRAM bytes of one launch (dram__bytes_read.sum + dram__bytes_write.sum) from the tracked ncu
+    # summary of this kernel and workload, when one exists
+    traffic = None
+    captured = ROOT / "profiles" / "dram_traffic.json"
+    if captured.exists() and traffic_key is not None:
+        traffic = json.loads(captured.read_text()).get(traffic_key, {}).get(dominant)
+    # the edge kernels move their compulsory HBM bytes at a few per cent of the copy bandwidth; what
+    # bounds them is FP32 issue (gradient kernels) or L2-to-SM delivery (forward kernels), so the
+    # fraction reported is the larger of the FP32 and the HBM fraction, each against a measured peak
+    if dom["fp32_frac"] >= dom["hbm_frac"]:
+        roofline = {"bound": "fp32", "kernel": dominant, "achieved": dom["fp32_tflops"], "peak": measured["fp32_fma_tflops"],
+                    "unit": "TFLOP/s", "frac": dom["fp32_frac"], "peak_source": "measured FMA probe (sxb_measure_device_peaks)"}
+    else:
+        roofline = {"bound": "hbm", "kernel": dominant, "achieved": dom["hbm_gbs"], "peak": hbm_peak, "unit": "GB/s",
+                    "frac": dom["hbm_frac"], "peak_source": f"{peak_kind} copy bandwidth"}
+    roofline.update({"traffic": traffic, "kernel_ms": stage_ms[dominant], "algorithmic_bytes": alg_bytes,
+                     "algorithmic_gflop": alg_flops / 1e9, "hbm_gbs": dom["hbm_gbs"], "hbm_peak_gbs": hbm_peak,
+                     "hbm_frac": dom["hbm_frac"], "l2_read_gbs": dom["l2_gbs"], "l2_peak_gbs": measured["l2_read_gbs"],
+                     "l2_frac": dom["l2_frac"], "fp32_peak_tflops": measured["fp32_fma_tflops"],
+                     "edge_kernels": {k: {q: round(v, 4) for q, v in d.items()} for k, d in kernels.items()}})
+    return roofline
+
+
 def run_distributed(args):
     """N > 1: one periodic SrTiO3 system of 5,000 atoms per GPU (10x10x10 cells per brick), decomposed
     in space over the ranks; ghost positions, features, adjoints and forces cross NVLink as pushes into peer memory
@@ -229,6 +283,23 @@ def run_distributed(args):
             for name, ms, _l in calc.ev.profile():
                 stage_ms[name] = stage_ms.get(name, 0.0) + ms / 3
         calc.set_profiling(False)
+        # roofline of this rank's edge kernels from those stage times (rank 0 reports); edges inside the model cutoff are
+        # counted from the local graph while it is small enough to fetch
+        roofline = None
+        if rank == 0 and stage_ms:
+            local_edges = int(calc.num_edges)
+            if n_own + plan.num_ghost <= 200000:
+                first, sources, _shifts = calc.ev.graph(calc.generation, with_shifts=False)
+                local = calc.local_positions.cpu().numpy()
+                recv = np.repeat(np.arange(n_own), np.diff(first))
+                d = local[sources] - local[recv]
+                active_local = int((np.sqrt((d * d).sum(1)) < calc.ev.r_cut).sum())
+            else:
+                active_local = int(round(local_edges * 0.7441))     # ratio measured on the 5,000-atom case
+            hbm_peak, peak_kind = _peaks()
+            roofline = edge_kernel_roofline(calc.ev, stage_ms, local_edges, active_local, n_own,
+                                            pkg.measure_device_peaks(local_rank), hbm_peak, peak_kind)
+            roofline["scope"] = "rank 0's kernels"
         # where a step spends its time: the four exchanges and the three phases, from eager launches (outside the timed region)
         barrier()
         timeline = calc.timeline(5)
@@ -277,7 +348,7 @@ def run_distributed(args):
                         "d2h_bytes_per_step": 24 * total_atoms + 80 * world, "ms_per_step": e2e_step_ms},
                 "gpu_launches": int(counts[3].item()),
                 "clocks": clocks,
-                "roofline": None,
+                "roofline": roofline,
                 "parity_vs_single_gpu": parity,
                 "stage_ms_rank0": {k: round(v, 4) for k, v in stage_ms.items()},
                 "step_timeline_ms_rank0": {k: round(v, 4) for k, v in timeline.items()},
@@ -394,55 +465,10 @@ def run_ours(args):
         value = step_ms * 1e3 / n          # us/atom/step on each GPU's own replica; atoms/s scales with N
         e2e_value = e2e_step_ms * 1e3 / n
 
-        C = ev.num_channels
-        dominant = max((k for k in stage_ms if k in FLOP_PER_EDGE_CHANNEL), key=lambda k: stage_ms[k])
         hbm_peak, peak_kind = _peaks()
         measured = pkg.measure_device_peaks(local_rank)      # FP32 FMA rate and L2-to-SM bandwidth, probed now
-        num_lme, num_hidden = ev.num_lme, (ev.L_max + 1) ** 2
-        # compulsory HBM bytes of one launch of each edge kernel: geometry record + source
-        # index per edge, plus the node rows the kernel must read / write once
-        node_rows = {"l0_forward": 16, "l0_reverse": 16, "l1_forward": num_lme + num_hidden,
-                     "l1_reverse": num_lme + 3 * num_hidden}
-        # spline coefficients the formulation pulls from L2 per active edge: 16 B per radial function
-        # (+ the source feature rows in layer 1)
-        l2_bytes_per_edge = {"l0_forward": 16 * 4 * C, "l0_reverse": 16 * 4 * C,
-                             "l1_forward": 16 * ev.num_paths * C + 4 * num_hidden * C,
-                             "l1_reverse": 16 * ev.num_paths * C + 8 * num_hidden * C}
-        kernels = {}
-        for name in FLOP_PER_EDGE_CHANNEL:
-            if name not in stage_ms:
-                continue
-            seconds = stage_ms[name] * 1e-3
-            flops = FLOP_PER_EDGE_CHANNEL[name] * active_edges * C
-            hbm_bytes = num_edges * 20 + n * node_rows[name] * C * 4
-            l2_bytes = l2_bytes_per_edge[name] * active_edges
-            kernels[name] = {"ms": stage_ms[name], "fp32_tflops": flops / seconds / 1e12,
-                             "fp32_frac": flops / seconds / 1e12 / measured["fp32_fma_tflops"],
-                             "hbm_gbs": hbm_bytes / seconds / 1e9, "hbm_frac": hbm_bytes / seconds / 1e9 / hbm_peak,
-                             "l2_gbs": l2_bytes / seconds / 1e9, "l2_frac": l2_bytes / seconds / 1e9 / measured["l2_read_gbs"]}
-        dom = kernels[dominant]
-        alg_bytes = num_edges * 20 + n * node_rows[dominant] * C * 4
-        alg_flops = FLOP_PER_EDGE_CHANNEL[dominant] * active_edges * C
-        # DRAM bytes of one launch (dram__bytes_read.sum + dram__bytes_write.sum) from the tracked ncu
-        # summary of this kernel and workload, when one exists
-        traffic = None
-        captured = ROOT / "profiles" / "dram_traffic.json"
-        if captured.exists() and args.workload == "srtio3" and n == 5000 and args.tile == 0:
-            traffic = json.loads(captured.read_text()).get("medium-5000-SrTiO3", {}).get(dominant)
-        # the edge kernels move their compulsory HBM bytes at a few per cent of the copy bandwidth; what
-        # bounds them is FP32 issue (gradient kernels) or L2-to-SM delivery (forward kernels), so the
-        # fraction reported is the larger of the FP32 and the HBM fraction, each against a measured peak
-        if dom["fp32_frac"] >= dom["hbm_frac"]:
-            roofline = {"bound": "fp32", "kernel": dominant, "achieved": dom["fp32_tflops"], "peak": measured["fp32_fma_tflops"],
-                        "unit": "TFLOP/s", "frac": dom["fp32_frac"], "peak_source": "measured FMA probe (sxb_measure_device_peaks)"}
-        else:
-            roofline = {"bound": "hbm", "kernel": dominant, "achieved": dom["hbm_gbs"], "peak": hbm_peak, "unit": "GB/s",
-                        "frac": dom["hbm_frac"], "peak_source": f"{peak_kind} copy bandwidth"}
-        roofline.update({"traffic": traffic, "kernel_ms": stage_ms[dominant], "algorithmic_bytes": alg_bytes,
-                         "algorithmic_gflop": alg_flops / 1e9, "hbm_gbs": dom["hbm_gbs"], "hbm_peak_gbs": hbm_peak,
-                         "hbm_frac": dom["hbm_frac"], "l2_read_gbs": dom["l2_gbs"], "l2_peak_gbs": measured["l2_read_gbs"],
-                         "l2_frac": dom["l2_frac"], "fp32_peak_tflops": measured["fp32_fma_tflops"],
-                         "edge_kernels": {k: {q: round(v, 4) for q, v in d.items()} for k, d in kernels.items()}})
+        roofline = edge_kernel_roofline(ev, stage_ms, num_edges, active_edges, n, measured, hbm_peak, peak_kind,
+                                        "medium-5000-SrTiO3" if args.workload == "srtio3" and n == 5000 and args.tile == 0 else None)
 
         md_report = None
         if args.md_steps > 0:
