@@ -325,8 +325,9 @@ int sxb_set_stream(sxb_evaluator* evaluator, void* stream);
  *                              list over a local tensor, a scatter list into the peers' tensors, and add mode
  *   sxb_peer_advance           enqueue: next step (once per evaluation, before its first exchange)
  *   sxb_peer_exchange          enqueue: push my rows of `phase`, then wait for every peer's
- *   sxb_peer_status            after a synchronisation: 0, or 32 when a wait ran out (about ten seconds);
- *                              the results of that step are then invalid, the CUDA context stays usable
+ *   sxb_peer_status            after a synchronisation: 0, or 32 when a wait ran out (ten seconds unless
+ *                              sxb_peer_set_wait_limit changed it); the results of that step are then invalid,
+ *                              the CUDA context stays usable
  * Every rank must run the same sequence of exchanges. */
 typedef struct PeerExchange sxb_peer_exchange_t;
 int sxb_device_alloc(int32_t device_ordinal, int64_t bytes, void** out);
@@ -344,6 +345,7 @@ int sxb_peer_plan(sxb_peer_exchange_t* exchange, int32_t phase, const void* send
 int sxb_internal_rows(sxb_evaluator* evaluator, const int32_t* device_indices, int64_t count, int32_t* device_out);
 int sxb_peer_advance(sxb_peer_exchange_t* exchange, void* stream);
 int sxb_peer_exchange(sxb_peer_exchange_t* exchange, int32_t phase, void* stream);
+int sxb_peer_set_wait_limit(sxb_peer_exchange_t* exchange, double seconds);
 int sxb_peer_destroy(sxb_peer_exchange_t* exchange);
 
 /* Tiled streaming (the reference's fixed-workspace dual-layer plan, allow_fixed_workspace:

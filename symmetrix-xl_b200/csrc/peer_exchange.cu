@@ -34,7 +34,7 @@ namespace {
 
 constexpr int kMaxPeers = 16;
 constexpr int kPhases = 4;                       // positions, H1, H1_adj, forces
-constexpr long long kWaitCycles = 20000000000ll;  // about ten seconds at the boost clock
+constexpr double kDefaultWaitSeconds = 10.0;      // limit of every wait unless sxb_peer_set_wait_limit says otherwise
 
 struct PushPlan {
     int world;
@@ -52,14 +52,15 @@ struct PushPlan {
 // grid.y = destination rank; blocks of a rank stride over its segment.  The last block to finish a
 // segment publishes the flag after a system-wide fence.
 // Bounded spin until `flag` shows step `want`; records bit 32 in the status word when the limit runs out.
-__device__ __forceinline__ void wait_for_flag(const unsigned long long* flag, unsigned long long want, int* status)
+__device__ __forceinline__ void wait_for_flag(const unsigned long long* flag, unsigned long long want, int* status,
+                                              long long limit_cycles)
 {
     const long long start = clock64();
     for (;;) {
         unsigned long long seen;
         asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(flag) : "memory");
         if (seen >= want) break;
-        if (clock64() - start > kWaitCycles) {
+        if (clock64() - start > limit_cycles) {
             *reinterpret_cast<volatile int*>(status) = 32;
             break;
         }
@@ -69,7 +70,7 @@ __device__ __forceinline__ void wait_for_flag(const unsigned long long* flag, un
 
 __global__ void __launch_bounds__(256) push_segments_kernel(PushPlan plan, unsigned int* __restrict__ done_counters,
                                                             const unsigned long long* __restrict__ incoming /*[world] or nullptr*/,
-                                                            int* __restrict__ status)
+                                                            int* __restrict__ status, long long limit_cycles)
 {
     const int peer = blockIdx.y;
     const long long first = plan.send_begin[peer], rows = plan.send_begin[peer + 1] - first;
@@ -108,18 +109,18 @@ __global__ void __launch_bounds__(256) push_segments_kernel(PushPlan plan, unsig
             const unsigned long long step = *plan.step;
             asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(plan.remote_flag[peer]), "l"(step) : "memory");
             // this peer's rows for me: nothing of mine is pending any more, so the wait cannot block a push
-            if (incoming != nullptr) wait_for_flag(incoming + peer, step, status);
+            if (incoming != nullptr) wait_for_flag(incoming + peer, step, status, limit_cycles);
         }
     }
 }
 
 // One thread per peer waits until that peer's flag reaches the current step.
 __global__ void wait_flags_kernel(int world, const unsigned long long* __restrict__ flags /*[world]*/,
-                                  const unsigned long long* __restrict__ step, int* __restrict__ status)
+                                  const unsigned long long* __restrict__ step, int* __restrict__ status, long long limit_cycles)
 {
     const int peer = threadIdx.x;
     if (peer >= world) return;
-    wait_for_flag(flags + peer, *step, status);
+    wait_for_flag(flags + peer, *step, status, limit_cycles);
 }
 
 __global__ void advance_step_kernel(unsigned long long* step) { *step += 1ull; }
@@ -136,6 +137,8 @@ struct PeerExchange {
     std::vector<void*> opened;                  // mappings of peer memory to close
     PushPlan plans[kPhases];
     bool split_wait = false;                    // SXB_PEER_SPLIT_WAIT=1: the wait as a kernel of its own
+    long long wait_cycles = 0;                  // limit of a wait in SM clock cycles
+    double cycles_per_second = 0.0;
     bool planned[kPhases] = {false, false, false, false};
 };
 
@@ -189,6 +192,10 @@ int sxb_peer_create(int32_t device_ordinal, int32_t rank, int32_t world, PeerExc
         auto* px = new PeerExchange();
         px->device = device_ordinal; px->rank = rank; px->world = world;
         if (const char* env = std::getenv("SXB_PEER_SPLIT_WAIT")) px->split_wait = env[0] == '1';
+        int clock_khz = 0;
+        SXB_CUDA(cudaDeviceGetAttribute(&clock_khz, cudaDevAttrClockRate, device_ordinal));
+        px->cycles_per_second = 1e3 * std::max(clock_khz, 1);
+        px->wait_cycles = static_cast<long long>(sxb::kDefaultWaitSeconds * px->cycles_per_second);
         SXB_CUDA(cudaMalloc(reinterpret_cast<void**>(&px->flags), sizeof(unsigned long long) * sxb::kPhases * sxb::kMaxPeers));
         SXB_CUDA(cudaMemset(px->flags, 0, sizeof(unsigned long long) * sxb::kPhases * sxb::kMaxPeers));
         SXB_CUDA(cudaMalloc(reinterpret_cast<void**>(&px->step), sizeof(unsigned long long)));
@@ -297,12 +304,24 @@ int sxb_peer_exchange(PeerExchange* px, int32_t phase, void* stream)
         dim3 grid(blocks, px->world);
         const unsigned long long* incoming = px->flags + phase * sxb::kMaxPeers;
         sxb::push_segments_kernel<<<grid, 256, 0, s>>>(plan, px->counters + phase * sxb::kMaxPeers, px->split_wait ? nullptr : incoming,
-                                                       px->status);
-        if (px->split_wait) sxb::wait_flags_kernel<<<1, 32, 0, s>>>(px->world, incoming, px->step, px->status);
+                                                       px->status, px->wait_cycles);
+        if (px->split_wait) sxb::wait_flags_kernel<<<1, 32, 0, s>>>(px->world, incoming, px->step, px->status, px->wait_cycles);
         SXB_CUDA(cudaGetLastError());
         return SXB_OK;
     } catch (const std::invalid_argument& e) { sxb::set_last_error(e.what()); return SXB_ERR_INVALID_ARGUMENT;
     } catch (const std::exception& e) { sxb::set_last_error(e.what()); return SXB_ERR_RUNTIME; }
+}
+
+// Limit of every wait from now on (seconds of SM clock at the nominal rate; 10 by default).  Exchanges that are
+// already captured in a CUDA graph keep the limit they were captured with.
+int sxb_peer_set_wait_limit(PeerExchange* px, double seconds)
+{
+    if (px == nullptr || !(seconds > 0.0) || !(seconds <= 60.0)) {
+        sxb::set_last_error("The wait limit must lie in (0, 60] seconds.");
+        return SXB_ERR_INVALID_ARGUMENT;
+    }
+    px->wait_cycles = std::max(1ll, static_cast<long long>(seconds * px->cycles_per_second));
+    return SXB_OK;
 }
 
 int sxb_peer_destroy(PeerExchange* px)

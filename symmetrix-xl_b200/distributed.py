@@ -165,8 +165,8 @@ class ExchangePlan:
 
 class PeerTransport:
     """The four exchanges of a step over NVLink peer memory (csrc/peer_exchange.cu): every rank maps the
-    receive buffers of its peers through CUDA IPC; an exchange is a push kernel plus a bounded wait kernel
-    on the calculator's stream.  Receive buffers: the ghost tail of the position array, the ghost tail of
+    receive buffers of its peers through CUDA IPC; an exchange is one kernel on the calculator's stream that pushes
+    the rows, raises this rank's flag at every peer and waits, with a time limit, for the peers' flags.  Receive buffers: the ghost tail of the position array, the ghost tail of
     the evaluator's H1 tensor, the returned-adjoint rows and the returned-force rows."""
 
     PHASE_POSITIONS, PHASE_H1, PHASE_H1_ADJ, PHASE_FORCES = 0, 1, 2, 3
@@ -216,6 +216,10 @@ class PeerTransport:
 
     def exchange(self, phase, stream_ptr):
         self._check(self.lib.sxb_peer_exchange(self.handle, int(phase), self.ctypes.c_void_p(stream_ptr)))
+
+    def set_wait_limit(self, seconds):
+        """Limit of every arrival wait from now on (ten seconds by default)."""
+        self._check(self.lib.sxb_peer_set_wait_limit(self.handle, float(seconds)))
 
     def status(self):
         out = self.ctypes.c_int32()

@@ -113,6 +113,7 @@ SIGNATURES = {
     "sxb_peer_advance": (ctypes.c_int, [_P, _P]),
     "sxb_peer_exchange": (ctypes.c_int, [_P, ctypes.c_int32, _P]),
     "sxb_peer_destroy": (ctypes.c_int, [_P]),
+    "sxb_peer_set_wait_limit": (ctypes.c_int, [_P, ctypes.c_double]),
     "sxb_set_tile_size": (ctypes.c_int, [_P, ctypes.c_int32]),
     "sxb_set_deterministic": (ctypes.c_int, [_P, ctypes.c_int32]),
     "sxb_set_profiling": (ctypes.c_int, [_P, ctypes.c_int32]),

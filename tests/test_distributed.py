@@ -272,3 +272,50 @@ def test_host_buffer_halo_as_a_plain_lammps_pair_style_drives_it(pkg, model_path
         assert np.abs(total - want["forces"][owned]).max() <= 1e-5
         stress = ev._reduce_stress(abs(np.linalg.det(cell)), execution_graph_generation=gen)
         assert np.abs(stress - want["stress"]).max() <= 1e-7
+
+
+@pytest.mark.gpu
+def test_arrival_wait_runs_out_and_reports_instead_of_hanging(pkg):
+    """A peer that never raises its flag: the exchange kernel gives up after the wait limit, the status word shows
+    it, and the CUDA context stays usable.  One process stands for rank 0 of two; the absent rank 1's flag table and
+    receive buffer are plain local buffers that nothing ever writes."""
+    import torch
+
+    lib = pkg.load_library()
+    peer = pkg.distributed.PeerTransport(lib, 0, 0, 2)
+    try:
+        peer.set_wait_limit(0.05)
+        with pytest.raises(RuntimeError):
+            peer.set_wait_limit(0.0)
+        rows = 64
+        send = torch.arange(rows * 4, dtype=torch.float32, device="cuda").reshape(rows, 4)       # 16-byte rows
+        mine = peer.alloc(rows * 16)                 # where "my own" segment lands (rank 0 -> rank 0)
+        absent = peer.alloc(rows * 16)               # stands for rank 1's receive buffer
+        absent_flags = peer.alloc(8 * 16 * 4)        # stands for rank 1's flag table: rank 0 may raise its flag there
+        peer.plan(peer.PHASE_H1, send.data_ptr(), [0, rows // 2, rows], 16, [mine, absent], [peer.flags, absent_flags])
+        stream = torch.cuda.current_stream().cuda_stream
+        peer.advance(stream)
+        start = torch.cuda.Event(enable_timing=True)
+        stop = torch.cuda.Event(enable_timing=True)
+        start.record()
+        peer.exchange(peer.PHASE_H1, stream)
+        stop.record()
+        torch.cuda.synchronize()
+        assert peer.status() == 32                   # rank 1 never delivered
+        assert 20.0 <= start.elapsed_time(stop) <= 2000.0      # it waited about the limit, not the default ten seconds
+        assert peer.status() == 0                    # reading clears the word
+        # my own half arrived, and the context still runs kernels
+        landed = torch.empty(rows // 2 * 4, dtype=torch.float32, device="cuda")
+        view = torch.as_tensor(_DeviceArray(mine, rows // 2 * 4), device="cuda")
+        landed.copy_(view)
+        assert torch.equal(landed.reshape(rows // 2, 4), send[: rows // 2])
+        assert float((send + 1).sum()) > 0.0
+    finally:
+        peer.close()
+
+
+class _DeviceArray:
+    """Zero-copy view of device memory for torch (float32)."""
+
+    def __init__(self, pointer, count):
+        self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (int(pointer), False), "version": 2}
