@@ -183,6 +183,17 @@ __global__ void __launch_bounds__(kT3Threads, 1) tc_gemm_tma_kernel(const __grid
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                // accumulating launches: fetch the old values of all eight passes first, so that their latency (the output
+                // has usually left L2 by now) is paid once per column group and not once per pass
+                float4 old[8];
+                if (accumulate) {
+#pragma unroll
+                    for (int pass = 0; pass < 8; ++pass) {
+                        const unsigned long long ptr = __shfl_sync(0xffffffffu, my_row_ptr, pass * 4 + sub_row);
+                        old[pass] = ptr != 0ull ? *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(ptr) + c0 + 4 * sub_chunk)
+                                                : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
                 // a lane holds 32 columns of one row; through the warp's staging tile (16-byte chunks XORed by
                 // row, conflict-free both ways) the warp stores whole 128-byte row segments, four rows per pass
                 __syncwarp();
@@ -200,8 +211,7 @@ __global__ void __launch_bounds__(kT3Threads, 1) tc_gemm_tma_kernel(const __grid
                         float4 o = *reinterpret_cast<const float4*>(stage + r * 128 + ((sub_chunk ^ (r & 7)) << 4));
                         float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(ptr) + c0 + 4 * sub_chunk);
                         if (accumulate) {
-                            const float4 old = *dst;
-                            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                            o.x += old[pass].x; o.y += old[pass].y; o.z += old[pass].z; o.w += old[pass].w;
                         } else if (bias != nullptr) {
                             const float4 bv = *reinterpret_cast<const float4*>(bias + col0 + c0 + 4 * sub_chunk);
                             o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
