@@ -142,6 +142,49 @@ class RadialTables:
         return c
 
 
+class StoredPairTables:
+    """Radial tables of the ``pair-splines`` representation: nodal values and derivatives per unordered element
+    pair, read from the file (mace.cpp:2714-2737; density splines 2746-2761, 2884-2897), Hermite form
+    cubic_spline_set.cpp:8-31.  Presents the interface of RadialTables with species-pair dependent tables."""
+
+    agnesi = True      # tables depend on the species pair
+
+    def __init__(self, model: dict, num_elements: int, single_layer: bool):
+        self.h = float(model["radial_spline_h"])
+        self.x0 = float(model.get("radial_spline_min", 0.0))
+        self.num_elements = num_elements
+        self._tables = {"R0": (model["radial_spline_values_0"], model["radial_spline_derivs_0"])}
+        if not single_layer:
+            self._tables["R1"] = (model["radial_spline_values_1"], model["radial_spline_derivs_1"])
+        for name in ("A0", "A1"):
+            if model.get(name + "_scaled", False):
+                if float(model[name + "_spline_h"]) != self.h or float(model.get(name + "_spline_min", 0.0)) != self.x0:
+                    raise NotImplementedError("density splines on a grid of their own are not restated")
+                self._tables[name] = ([[v] for v in model[name + "_spline_values"]], [[d] for d in model[name + "_spline_derivs"]])
+        self.points = len(model["radial_spline_values_0"][0][0])
+        self._cache = {}
+
+    def _pair(self, type_i, type_j):                                      # mace.cpp:216-229
+        a, b = min(type_i, type_j), max(type_i, type_j)
+        n = self.num_elements
+        return a * (2 * n - a - 1) // 2 + b
+
+    def coefficients(self, name, type_i=0, type_j=0):
+        key = (name, self._pair(type_i, type_j))
+        if key not in self._cache:
+            values, derivs = self._tables[name]
+            v = np.asarray(values[key[1]], dtype=np.float64).T                # [node, F]
+            d = np.asarray(derivs[key[1]], dtype=np.float64).T
+            h = self.h
+            c = np.zeros((self.points - 1, 4, v.shape[1]))
+            c[:, 0] = v[:-1]
+            c[:, 1] = d[:-1]
+            c[:, 2] = (-3 * v[:-1] - 2 * h * d[:-1] + 3 * v[1:] - h * d[1:]) / (h * h)
+            c[:, 3] = (2 * v[:-1] + h * d[:-1] - 2 * v[1:] + h * d[1:]) / (h * h * h)
+            self._cache[key] = c
+        return self._cache[key]
+
+
 def spline_eval(coeff, x0, h, r, dtype=np.float64):
     """Value and derivative of every function at every r (cubic_spline_set.cpp:33-80).
 
@@ -252,17 +295,27 @@ class Polynomial:
 
 # ----------------------------------------------------------------------------- model
 class NumpyMACE:
-    """Two-layer compact MACE (format v4, m0_composite) evaluated stage by stage."""
+    """Compact MACE evaluated stage by stage: two interactions or one (single_layer_readout), radial networks or stored
+    pair splines, and the three bases of the first readout and the H1 -> H2 skip (h1_affine_schema.hpp:5-30):
+    ``m0_composite`` (format 4, scalar block of M0), ``pre_linear_up`` (format 4, M0 P0 + residual) and the old basis of
+    formats 1 / 2 (scalar block of H1)."""
 
     def __init__(self, model, dtype=np.float64):
         if not isinstance(model, dict):
             with open(model) as fh:
                 model = json.load(fh)
         m = model
-        if m.get("radial_representation") != "compact" or m.get("h1_affine_mode") != "m0_composite":
-            raise NotImplementedError("restated for compact, m0_composite models")
-        if m.get("first_interaction_residual") or m.get("has_field_coupling"):
-            raise NotImplementedError("residual / field coupling are not restated")
+        version = int(m.get("symmetrix_format_version", 1))
+        self.basis = "legacy" if version in (1, 2) else m.get("h1_affine_mode")
+        if self.basis not in ("legacy", "m0_composite", "pre_linear_up"):
+            raise NotImplementedError("unknown h1 affine basis")
+        radial = m.get("radial_representation", "pair-splines" if version == 1 else "")
+        if radial not in ("compact", "pair-splines"):
+            raise NotImplementedError("unknown radial representation")
+        if m.get("has_field_coupling"):
+            raise NotImplementedError("field coupling is not restated")
+        self.single_layer = bool(m.get("single_layer_readout", False))
+        self.residual = bool(m.get("first_interaction_residual", False))
         self.has_zbl = bool(m.get("has_zbl", False))
         if self.has_zbl:                                                 # mace.cpp:2690-2699
             self.zbl_a_exp, self.zbl_a_prefactor = float(m["zbl_a_exp"]), float(m["zbl_a_prefactor"])
@@ -278,7 +331,8 @@ class NumpyMACE:
         self.r_cut = float(m["r_cut"])
         self.A = A = int(m["num_elements"])
         self.atomic_energies = np.asarray(m["atomic_energies"], dtype=np.float64)
-        self.tables = RadialTables(m["compact_radial"], self.r_cut)
+        self.tables = (RadialTables(m["compact_radial"], self.r_cut) if radial == "compact"
+                       else StoredPairTables(m, A, self.single_layer))
         self.A0_scaled, self.A1_scaled = bool(m["A0_scaled"]), bool(m.get("A1_scaled", False))
         self.H0 = np.asarray(m["H0_weights"], dtype=dt).reshape(A, C)
         self.WA0 = np.asarray(m["A0_weights"], dtype=dt).reshape(A, self.l_max + 1, C, C)
@@ -289,15 +343,29 @@ class NumpyMACE:
         self.W1 = np.asarray([[m["M1_weights"][str(a)][str(k)] for k in range(C)] for a in range(A)],
                              dtype=dt).transpose(0, 2, 1)
         self.WH1 = np.asarray(m["H1_weights"], dtype=dt).reshape(self.L_max + 1, C, C)
-        self.Phi1_l = list(m["Phi1_l"]); self.Phi1_l1 = list(m["Phi1_l1"]); self.Phi1_l2 = list(m["Phi1_l2"])
-        self.t_lme = np.asarray(m["Phi1_lme"]); self.t_row = np.asarray(m["Phi1_lelm1lm2"])
-        self.t_cg = np.asarray(m["Phi1_clebsch_gordan"], dtype=dt)
+        self.Phi1_l = list(m.get("Phi1_l", [])); self.Phi1_l1 = list(m.get("Phi1_l1", [])); self.Phi1_l2 = list(m.get("Phi1_l2", []))
+        self.t_lme = np.asarray(m.get("Phi1_lme", [])); self.t_row = np.asarray(m.get("Phi1_lelm1lm2", []))
+        self.t_cg = np.asarray(m.get("Phi1_clebsch_gordan", []), dtype=dt)
         self.num_lme = sum(2 * l + 1 for l in self.Phi1_l)
         self.eta = [sum(1 for l in self.Phi1_l if l == ll) for ll in range(self.l_max + 1)]
-        self.WA1 = [np.asarray(m["A1_weights"][l], dtype=dt).reshape(self.eta[l] * C, C) for l in range(self.l_max + 1)]
-        self.T = np.asarray(m["H2_weights_for_M0"], dtype=dt).reshape(A, C, C)
+        if not self.single_layer:
+            self.WA1 = [np.asarray(m["A1_weights"][l], dtype=dt).reshape(self.eta[l] * C, C) for l in range(self.l_max + 1)]
+        # first readout q and skip T act on the basis' scalar input (keys: h1_affine_schema.hpp:62-74)
+        skip_key = {"legacy": "H2_weights_for_H1", "m0_composite": "H2_weights_for_M0",
+                    "pre_linear_up": "H2_weights_for_H1_pre_linear_up"}[self.basis]
+        readout_key = {"legacy": "readout_1_weights", "m0_composite": "readout_1_weights_for_M0",
+                       "pre_linear_up": "readout_1_weights_for_H1_pre_linear_up"}[self.basis]
+        self.T = np.asarray(m[skip_key], dtype=dt).reshape(A, C, C)
         self.WM1 = np.asarray(m["H2_weights_for_M1"], dtype=dt).reshape(C, C)
-        self.q = np.asarray(m["readout_1_weights_for_M0"], dtype=dt)
+        self.q = np.asarray(m[readout_key], dtype=dt)
+        if self.basis == "pre_linear_up":                                # mace.cpp:1773-1778
+            self.P0w = np.asarray(m["H1_product_weights"], dtype=dt).reshape(self.L_max + 1, C, C)[0]
+        if self.residual:                                                # mace.cpp:2801-2829, 1845-1882
+            R = np.asarray(m["H1_first_residual_weights"], dtype=dt).reshape(A, self.num_LM, C)
+            U = np.asarray(m["H1_linear_up_weights"], dtype=dt).reshape(self.L_max + 1, C, C)
+            L_of = np.array([int(np.floor(np.sqrt(lm + 0.5))) for lm in range(self.num_LM)])
+            self.R_scalar = R[:, 0, :]
+            self.R_fused = np.einsum("amk,mkj->amj", R, U[L_of])
         hid = int(m.get("readout_2_hidden_size", 16))
         self.V1 = np.asarray(m["readout_2_weights_1"], dtype=dt).reshape(hid, C)
         self.V2 = np.asarray(m["readout_2_weights_2"], dtype=dt).reshape(1, hid)
@@ -331,9 +399,11 @@ class NumpyMACE:
         Y, Yg = harmonics(self.l_max, xyz, dt)                          # mace.cpp:1269-1299
         tj = typ[src]
         R0, dR0 = self._radial("R0", typ[recv], tj, r)                   # mace.cpp:1119-1144
-        R1, dR1 = self._radial("R1", typ[recv], tj, r)
         act = active[:, None].astype(dt)
-        R0, dR0, R1, dR1 = R0 * act, dR0 * act, R1 * act, dR1 * act
+        R0, dR0 = R0 * act, dR0 * act
+        if not self.single_layer:
+            R1, dR1 = self._radial("R1", typ[recv], tj, r)
+            R1, dR1 = R1 * act, dR1 * act
         l_of_lm = np.array([int(np.floor(np.sqrt(lm + 0.5))) for lm in range(nlm)])
         tj = typ[src]
 
@@ -355,9 +425,22 @@ class NumpyMACE:
         M0g = np.zeros((N, nLM, nlm, C), dtype=dt)
         for lm in range(nLM):
             M0[:, lm], M0g[:, lm] = self.P0[lm].evaluate(A0, self.W0[lm][typ])
-        xs = M0[:, 0, :].copy()                                          # mace.cpp:1759-1782
         L_of_LM = np.array([int(np.floor(np.sqrt(lm + 0.5))) for lm in range(nLM)])
         H1 = np.einsum("nmk,mkj->nmj", M0, self.WH1[L_of_LM])           # mace.cpp:1691-1724
+        if self.residual:                                                # mace.cpp:1845-1861: H1 += R U of the node's element
+            H1 = H1 + self.R_fused[typ]
+        # scalar input of the first readout and the skip (mace.cpp:1759-1782, 1863-1873; old basis 2524-2525)
+        if self.basis == "m0_composite":
+            xs = M0[:, 0, :].copy()
+        elif self.basis == "pre_linear_up":
+            xs = M0[:, 0, :] @ self.P0w
+            if self.residual:
+                xs = xs + self.R_scalar[typ]
+        else:
+            xs = H1[:, 0, :].copy()
+        if self.single_layer:
+            return self._finish_single_layer(typ, recv, tj, r, direction, Y, Yg, R0, dR0, A0, scale0,
+                                             ds if self.A0_scaled else None, M0, M0g, H1, xs, Wl, l_of_lm, L_of_LM)
         # Phi1 (mace.cpp:2023-2083)
         p_of_row, lm1_of_row, lm2_of_row = self.rows[:, 0], self.rows[:, 1], self.rows[:, 2]
         R1e = R1.reshape(E, len(self.Phi1_l), C)
@@ -383,17 +466,8 @@ class NumpyMACE:
             np.add.at(scale1, recv, s1[:, 0])
             A1 = A1 / scale1[:, None, None]
         M1, M1g = self.P1.evaluate(A1, self.W1[typ])                     # mace.cpp:2461-2484
-        H2 = np.einsum("nk,nkj->nj", xs, self.T[typ]) + M1 @ self.WM1    # mace.cpp:2516-2557
-        # readouts (mace.cpp:2622-2657; MLP multilayer_perceptron.cpp:34-80)
-        z = H2 @ self.V1.T
-        sig = 1.0 / (1.0 + np.exp(-z))
-        hidden = self.act * z * sig
-        e2 = (hidden @ self.V2.T)[:, 0]
-        energies = self.atomic_energies[typ] + (xs @ self.q).astype(np.float64) + e2.astype(np.float64)
-        dact = self.act * sig + self.act * z * sig * (1 - sig)
-        H2_adj = (self.V2[0][None, :] * dact) @ self.V1
+        H2, H2_adj, energies, direct = self._readouts(typ, xs, M1)
         # reverse (mace.cpp:298-318)
-        direct = self.q[None, :] + np.einsum("nkj,nj->nk", self.T[typ], H2_adj)   # mace.cpp:2568-2580
         M1_adj = H2_adj @ self.WM1.T
         A1_adj = M1g * M1_adj[:, None, :]                                 # mace.cpp:2487-2513
         forces = np.zeros((E, 3), dtype=dt)
@@ -423,8 +497,40 @@ class NumpyMACE:
         for row in range(len(self.rows)):
             msg[:, lm2_of_row[row]] += contrib[:, row]
         np.add.at(H1_adj, src, msg)
+        if self.basis == "legacy":                                       # old basis: q and the skip's adjoint join H1_adj (mace.cpp:2588-2601, 2645-2646)
+            H1_adj[:, 0, :] += direct
+        M0_adj, A0_adj = self._reverse_layer0(typ, recv, tj, r, direction, Y, Yg, R0, dR0, A0, scale0,
+                                              ds if self.A0_scaled else None, M0g, H1_adj, direct, Wl, l_of_lm, L_of_LM,
+                                              energies, forces)
+        self.stage = dict(Y=Y, Y_grad=Yg, A0=A0, M0=M0, H1=H1, Phi1=Phi1, A1=A1, M1=M1, H2=H2,
+                          H2_adj=H2_adj, A1_adj=A1_adj, dPhi1=dPhi1, H1_adj=H1_adj, M0_adj=M0_adj,
+                          A0_adj=A0_adj, node_energies=energies, node_forces=forces)
+        return energies, forces
+
+    def _readouts(self, typ, xs, M1):
+        """H2, node energies and the adjoints leaving the readouts (mace.cpp:2516-2557, 2622-2657)."""
+        H2 = np.einsum("nk,nkj->nj", xs, self.T[typ]) + M1 @ self.WM1
+        z = H2 @ self.V1.T
+        sig = 1.0 / (1.0 + np.exp(-z))
+        hidden = self.act * z * sig
+        e2 = (hidden @ self.V2.T)[:, 0]
+        energies = self.atomic_energies[typ] + (xs @ self.q).astype(np.float64) + e2.astype(np.float64)
+        dact = self.act * sig + self.act * z * sig * (1 - sig)
+        H2_adj = (self.V2[0][None, :] * dact) @ self.V1
+        direct = self.q[None, :] + np.einsum("nkj,nj->nk", self.T[typ], H2_adj)   # mace.cpp:2568-2580
+        return H2, H2_adj, energies, direct
+
+    def _reverse_layer0(self, typ, recv, tj, r, direction, Y, Yg, R0, dR0, A0, scale0, ds, M0g, H1_adj, direct, Wl, l_of_lm,
+                        L_of_LM, energies, forces):
+        """From H1_adj down to the edge forces of layer 0, plus the pair repulsion (mace.cpp:304-318); ``forces`` and
+        ``energies`` are updated in place."""
+        dt = self.dtype
+        E, C = len(r), self.C
         M0_adj = np.einsum("nmj,mkj->nmk", H1_adj, self.WH1[L_of_LM])   # mace.cpp:1727-1757
-        M0_adj[:, 0, :] += direct                                        # mace.cpp:1785-1813
+        if self.basis == "m0_composite":
+            M0_adj[:, 0, :] += direct                                    # mace.cpp:1785-1813
+        elif self.basis == "pre_linear_up":
+            M0_adj[:, 0, :] += direct @ self.P0w.T                       # mace.cpp:1799-1806
         A0_adj = np.einsum("nLmk,nLk->nmk", M0g, M0_adj)                 # mace.cpp:1665-1688
         if self.A0_scaled:                                               # mace.cpp:1587-1636
             dot = (A0_adj * A0).sum(axis=(1, 2))
@@ -433,6 +539,7 @@ class NumpyMACE:
             A0_adj = A0_adj / scale0[:, None, None]
         Phi0_adj = np.einsum("nmj,nmkj->nmk", A0_adj, Wl)                # mace.cpp:1486-1503
         padj = Phi0_adj[recv]
+        R0e = R0.reshape(E, self.l_max + 1, C)[:, l_of_lm, :]
         dR0e = dR0.reshape(E, self.l_max + 1, C)[:, l_of_lm, :]
         h0 = self.H0[tj][:, None, :]
         radial0 = (padj * dR0e * Y[:, :, None] * h0).sum(axis=(1, 2))
@@ -442,8 +549,25 @@ class NumpyMACE:
             ez, gz = self.zbl_pair(self.atomic_numbers[typ][recv], self.atomic_numbers[tj], r.astype(dt))
             np.add.at(energies, recv, ez.astype(np.float64))
             forces -= direction * gz[:, None].astype(dt)
-        self.stage = dict(Y=Y, Y_grad=Yg, A0=A0, M0=M0, H1=H1, Phi1=Phi1, A1=A1, M1=M1, H2=H2,
-                          H2_adj=H2_adj, A1_adj=A1_adj, dPhi1=dPhi1, H1_adj=H1_adj, M0_adj=M0_adj,
+        return M0_adj, A0_adj
+
+    def _finish_single_layer(self, typ, recv, tj, r, direction, Y, Yg, R0, dR0, A0, scale0, ds, M0, M0g, H1, xs, Wl, l_of_lm,
+                             L_of_LM):
+        """One interaction: the readout polynomial acts on H1 and there is no second message step
+        (mace.cpp:265-283; polynomial input 2465-2466, its adjoint adds to H1_adj 2499-2510)."""
+        dt = self.dtype
+        M1, M1g = self.P1.evaluate(H1, self.W1[typ])
+        H2, H2_adj, energies, direct = self._readouts(typ, xs, M1)
+        M1_adj = H2_adj @ self.WM1.T
+        H1_adj = M1g * M1_adj[:, None, :]
+        if self.basis == "legacy":
+            # the serial evaluator clears H1_adj after the readouts on this path (mace.cpp:269), so the first readout's
+            # own adjoint q does not reach the forces; exported single-layer files carry q = 0
+            H1_adj[:, 0, :] += direct - self.q[None, :]
+        forces = np.zeros((len(r), 3), dtype=dt)
+        M0_adj, A0_adj = self._reverse_layer0(typ, recv, tj, r, direction, Y, Yg, R0, dR0, A0, scale0, ds, M0g, H1_adj, direct,
+                                              Wl, l_of_lm, L_of_LM, energies, forces)
+        self.stage = dict(Y=Y, Y_grad=Yg, A0=A0, M0=M0, H1=H1, M1=M1, H2=H2, H2_adj=H2_adj, H1_adj=H1_adj, M0_adj=M0_adj,
                           A0_adj=A0_adj, node_energies=energies, node_forces=forces)
         return energies, forces
 

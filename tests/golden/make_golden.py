@@ -3,11 +3,12 @@
 Run where the reference checkout is present, naming it as the first argument or in REFERENCE_ROOT
 (the same variable oracle/Makefile reads):
 
-    python tests/golden/make_golden.py <reference checkout>
+    python tests/golden/make_golden.py <reference checkout> [evaluator] [variants] [harmonics] [structure]
 
 1. reference_evaluator_<arch>.npz -- energies, directed edge forces and stage-tensor checksums of
    the reference's serial evaluator MACECPU<double> (built into oracle/_ref from the checkout's
    sources) on a small seeded SrTiO3 cell with a seeded synthetic model of each architecture.
+   reference_evaluator_variant_<name>.npz -- the same for the model-file variants of variants.json.
 2. harmonics_reference.npz -- Y_lm and their Cartesian gradients from the reference's first-party
    closed forms for l <= 3: the C text its generator emits for the device force kernels
    (symmetrix/source/symmetrix/jit_codegen.py, _render_direct_harmonic_gradient_helper, and the
@@ -69,6 +70,36 @@ def evaluator_goldens():
             print("wrote", arch, len(pos), "atoms", len(src), "edges")
 
 
+def variant_goldens():
+    """reference_evaluator_variant_<name>.npz: the model-file variants of tests/golden/variants.json (stored pair splines,
+    one interaction, the old basis of formats 1 / 2, the pre_linear_up basis with a first-interaction residual), each
+    evaluated by MACECPU<double> on the 40-atom cell."""
+    from oracle import neighbor, ref
+
+    pkg = graft.load_package()
+    variants = json.loads((OUT / "variants.json").read_text())
+    pos, cell, types = pkg.modelgen.srtio3(2, 0.05, 202)
+    for name, entry in variants.items():
+        if name.startswith("_"):
+            continue
+        arch, kwargs = entry
+        cutoff = pkg.modelgen.ARCHITECTURES[arch]["r_cut"]
+        first, src, shifts = neighbor.build_neighbor_graph(pos, cell, cutoff)
+        xyz = neighbor.edge_vectors(pos, cell, first, src, shifts)
+        with tempfile.TemporaryDirectory() as tmp:
+            path = Path(tmp) / "model.json"
+            pkg.modelgen.write_model(path, arch, seed=101, **kwargs)
+            m = ref.ReferenceMACE(str(path), double=True)
+            m.compute(types, np.diff(first), src, xyz)
+            data = {"positions": pos, "cell": cell, "types": types, "first": first, "sources": src, "shifts": shifts,
+                    "node_energies": m.get("node_energies"), "edge_forces": m.get("node_forces")}
+            for stage in ("A0", "M0", "H1", "M1", "H2"):
+                v = m.get(stage)
+                data["sum_" + stage] = np.array([v.sum(), np.abs(v).sum(), (v * v).sum()])
+            np.savez_compressed(OUT / f"reference_evaluator_variant_{name}.npz", **data)
+            print("wrote variant", name)
+
+
 def harmonics_goldens():
     sys.path.insert(0, str(REFERENCE / "symmetrix" / "source"))
     codegen = importlib.import_module("symmetrix.jit_codegen")
@@ -120,9 +151,11 @@ def structure_goldens():
 
 if __name__ == "__main__":
     graft.build()
-    which = sys.argv[1:] or ["evaluator", "harmonics", "structure"]
+    which = sys.argv[2:] or ["evaluator", "variants", "harmonics", "structure"]
     if "evaluator" in which:
         evaluator_goldens()
+    if "variants" in which:
+        variant_goldens()
     if "harmonics" in which:
         harmonics_goldens()
     if "structure" in which:

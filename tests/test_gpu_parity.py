@@ -3,6 +3,9 @@
 Tolerances of the force path: |dE| <= 1e-5 eV/atom, |dF| <= 1e-4 eV/A per component,
 |dsigma| <= 1e-6 eV/A^3; the neighbor list must be bit-exact.
 """
+import json
+from pathlib import Path
+
 import numpy as np
 import pytest
 
@@ -199,6 +202,29 @@ def test_pre_linear_up_models_vs_reference_evaluator(pkg, model_path, arch, n, k
     tiled = pkg.Calculator(path, skin=0.5)
     tiled.evaluator.set_tile_size(16)
     _assert_matches_reference(tiled.calculate(pos, cell, types), e, F, S, len(pos), node_tol=3e-5)
+
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+GOLDEN_CASES = {"small": ("small", {}), "medium": ("medium", {}), "medium_scaled": ("medium", {"a0_scaled": True, "a1_scaled": True}),
+                "large": ("large", {}), "small_zbl": ("small", {"zbl": True}),
+                "small_scaled_zbl_agnesi": ("small", {"a0_scaled": True, "a1_scaled": True, "zbl": True, "agnesi": True})}
+GOLDEN_CASES.update({"variant_" + k: tuple(v) for k, v in json.loads((GOLDEN / "variants.json").read_text()).items()
+                     if not k.startswith("_")})
+
+
+@pytest.mark.parametrize("name", sorted(GOLDEN_CASES))
+def test_committed_golden_vectors_of_the_reference_evaluator(pkg, model_path, name):
+    """Energies, forces and stress against the committed vectors of the reference's MACECPU<double> (tests/golden/,
+    written by make_golden.py): the standard models and every model-file variant; needs no reference build."""
+    arch, kwargs = GOLDEN_CASES[name]
+    g = np.load(GOLDEN / f"reference_evaluator_{name}.npz")
+    path = model_path(arch, seed=101, **kwargs)
+    pos, cell, types = pkg.modelgen.srtio3(2, 0.05, 202)
+    assert np.array_equal(pos, g["positions"])
+    out = pkg.Calculator(path, skin=0.5).calculate(pos, cell, types)
+    xyz = neighbor.edge_vectors(pos, cell, g["first"], g["sources"], g["shifts"])
+    F, S = ref.reduce_forces_stress(len(pos), np.diff(g["first"]), g["sources"], g["edge_forces"], xyz, abs(np.linalg.det(cell)))
+    _assert_matches_reference(out, g["node_energies"], F, S, len(pos), node_tol=3e-5)
 
 
 def test_headline_configuration_vs_reference_evaluator(pkg, model_path):

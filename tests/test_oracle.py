@@ -1,6 +1,7 @@
 """CPU tests of the oracles: the NumPy restatement against golden vectors produced by the
 reference's own code (tests/golden/make_golden.py), and the neighbor-graph restatement against
 a brute-force search and the reference's published edge counts."""
+import json
 from pathlib import Path
 
 import numpy as np
@@ -30,6 +31,47 @@ def test_numpy_restatement_matches_reference_evaluator_golden(pkg, model_dir, ar
         v = o.stage[name]
         got = np.array([v.sum(), np.abs(v).sum(), (v * v).sum()])
         assert np.allclose(got, g["sum_" + name], rtol=1e-10, atol=1e-10), name
+
+
+VARIANTS = {k: v for k, v in json.loads((GOLDEN / "variants.json").read_text()).items() if not k.startswith("_")}
+
+
+@pytest.mark.parametrize("name", sorted(VARIANTS))
+def test_numpy_restatement_matches_reference_golden_of_model_variants(pkg, model_dir, name):
+    """Stored pair splines, one interaction, the old basis of formats 1 / 2 and the pre_linear_up basis with a
+    first-interaction residual: the restatement against vectors of the reference's MACECPU<double>."""
+    arch, kwargs = VARIANTS[name]
+    g = np.load(GOLDEN / f"reference_evaluator_variant_{name}.npz")
+    path = model_dir / f"golden_variant_{name}.json"
+    pkg.modelgen.write_model(path, arch, seed=101, **kwargs)
+    pos, cell, types = pkg.modelgen.srtio3(2, 0.05, 202)
+    assert np.array_equal(pos, g["positions"]) and np.array_equal(types, g["types"])
+    xyz = neighbor.edge_vectors(pos, cell, g["first"], g["sources"], g["shifts"])
+    o = mace_numpy.NumpyMACE(str(path))
+    e, f = o.compute(types, g["first"], g["sources"], xyz)
+    assert np.abs(e - g["node_energies"]).max() < 1e-11
+    assert np.abs(f.reshape(-1) - g["edge_forces"]).max() < 1e-11
+    for stage in ("A0", "M0", "H1", "M1", "H2"):
+        v = o.stage[stage]
+        got = np.array([v.sum(), np.abs(v).sum(), (v * v).sum()])
+        assert np.allclose(got, g["sum_" + stage], rtol=1e-10, atol=1e-10), stage
+
+
+@pytest.mark.parametrize("name", sorted(VARIANTS))
+def test_numpy_restatement_matches_live_reference_on_model_variants(pkg, model_path, name):
+    """The same variants against oracle/_ref itself on another model seed and cell, when it is built."""
+    if not ref.available():
+        pytest.skip("oracle/_ref was not built")
+    arch, kwargs = VARIANTS[name]
+    path = model_path(arch, seed=71, **kwargs)
+    pos, cell, types = pkg.modelgen.srtio3(2, 0.05, 43)
+    first, src, shifts = neighbor.build_neighbor_graph(pos, cell, pkg.modelgen.ARCHITECTURES[arch]["r_cut"])
+    xyz = neighbor.edge_vectors(pos, cell, first, src, shifts)
+    m = ref.ReferenceMACE(str(path), double=True)
+    m.compute(types, np.diff(first), src, xyz)
+    e, f = mace_numpy.NumpyMACE(str(path)).compute(types, first, src, xyz)
+    assert np.abs(e - m.get("node_energies")).max() < 1e-11
+    assert np.abs(f.reshape(-1) - m.get("node_forces")).max() < 1e-11
 
 
 def test_numpy_restatement_matches_live_reference_evaluator(pkg, model_path):
