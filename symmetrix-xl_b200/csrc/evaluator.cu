@@ -770,8 +770,12 @@ void Evaluator::upload_split(SplitWeight& out, const float* w, int rows, int col
     for (int r = 0; r < rows; ++r)
         for (int c = 0; c < cols; ++c) {
             const float v = w[static_cast<std::size_t>(r) * cols + c];
+            // high part rounded to nearest TF32 (not truncated): the residual then has either sign, so the one product
+            // the three-pass scheme drops, a_lo * w_lo, carries no systematic sign (the activations' high part is the
+            // hardware's truncation, whose residual always has the sign of the value)
             std::uint32_t bits;
             std::memcpy(&bits, &v, 4);
+            if ((bits & 0x7f800000u) != 0x7f800000u) bits += 0x00001000u;
             bits &= 0xffffe000u;
             float h;
             std::memcpy(&h, &bits, 4);

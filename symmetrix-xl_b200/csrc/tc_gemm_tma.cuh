@@ -86,6 +86,14 @@ __device__ __forceinline__ Tc3Item tc3_locate(const Tc3Batch& batch, int item)
     return {pi, local / batch.problem[pi].n_tiles, local % batch.problem[pi].n_tiles};
 }
 
+// Nearest TF32 value of x (ties away from zero), returned as a float whose low 13 mantissa bits are zero.
+__device__ __forceinline__ float tf32_round(float x)
+{
+    unsigned r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
 __global__ void __launch_bounds__(kT3Threads, 1) tc_gemm_tma_kernel(const __grid_constant__ Tc3Batch batch, int* __restrict__ error_flag)
 {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -139,10 +147,12 @@ __global__ void __launch_bounds__(kT3Threads, 1) tc_gemm_tma_kernel(const __grid
                 for (int p = 0; p < kT3OperandBytes / 16 / 128; ++p) {   // position-wise: the layouts are identical
                     const float4 v = src[p * 128 + tid];
                     float4 lo;
-                    lo.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
-                    lo.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
-                    lo.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
-                    lo.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
+                    // the residual is itself read as TF32 by the tensor core, i.e. truncated; rounding it to nearest here
+                    // keeps that last truncation from always pulling the product towards zero
+                    lo.x = tf32_round(v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u));
+                    lo.y = tf32_round(v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u));
+                    lo.z = tf32_round(v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u));
+                    lo.w = tf32_round(v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u));
                     dst[p * 128 + tid] = lo;
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -42,6 +42,19 @@ OUT = Path(__file__).resolve().parent
 import __graft_entry__ as graft  # noqa: E402
 
 
+def float_deviation(ref, path, types, first, src, xyz, cell, reference_double):
+    """[max |dE_node|, max |dF_atom|, max |dsigma|] between the reference's own float and double evaluators on this
+    input: the FP32 resolution of the model itself, which a parity bound cannot undercut."""
+    n = len(types)
+    volume = abs(np.linalg.det(cell))
+    m = ref.ReferenceMACE(str(path), double=False)
+    m.compute(types, np.diff(first), src, xyz)
+    Ff, Sf = ref.reduce_forces_stress(n, np.diff(first), src, m.get("node_forces"), xyz, volume)
+    Fd, Sd = ref.reduce_forces_stress(n, np.diff(first), src, reference_double.get("node_forces"), xyz, volume)
+    return np.array([np.abs(m.get("node_energies") - reference_double.get("node_energies")).max(), np.abs(Ff - Fd).max(),
+                     np.abs(Sf - Sd).max()])
+
+
 def evaluator_goldens():
     from oracle import neighbor, ref
 
@@ -62,7 +75,8 @@ def evaluator_goldens():
             m = ref.ReferenceMACE(str(path), double=True)
             m.compute(types, np.diff(first), src, xyz)
             data = {"positions": pos, "cell": cell, "types": types, "first": first, "sources": src, "shifts": shifts,
-                    "node_energies": m.get("node_energies"), "edge_forces": m.get("node_forces")}
+                    "node_energies": m.get("node_energies"), "edge_forces": m.get("node_forces"),
+                    "float_deviation": float_deviation(ref, path, types, first, src, xyz, cell, m)}
             for name in ("A0", "M0", "H1", "Phi1", "A1", "M1", "H2", "H1_adj", "A0_adj"):
                 v = m.get(name)
                 data["sum_" + name] = np.array([v.sum(), np.abs(v).sum(), (v * v).sum()])
@@ -92,7 +106,8 @@ def variant_goldens():
             m = ref.ReferenceMACE(str(path), double=True)
             m.compute(types, np.diff(first), src, xyz)
             data = {"positions": pos, "cell": cell, "types": types, "first": first, "sources": src, "shifts": shifts,
-                    "node_energies": m.get("node_energies"), "edge_forces": m.get("node_forces")}
+                    "node_energies": m.get("node_energies"), "edge_forces": m.get("node_forces"),
+                    "float_deviation": float_deviation(ref, path, types, first, src, xyz, cell, m)}
             for stage in ("A0", "M0", "H1", "M1", "H2"):
                 v = m.get(stage)
                 data["sum_" + stage] = np.array([v.sum(), np.abs(v).sum(), (v * v).sum()])

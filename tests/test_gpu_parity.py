@@ -224,7 +224,14 @@ def test_committed_golden_vectors_of_the_reference_evaluator(pkg, model_path, na
     out = pkg.Calculator(path, skin=0.5).calculate(pos, cell, types)
     xyz = neighbor.edge_vectors(pos, cell, g["first"], g["sources"], g["shifts"])
     F, S = ref.reduce_forces_stress(len(pos), np.diff(g["first"]), g["sources"], g["edge_forces"], xyz, abs(np.linalg.det(cell)))
-    _assert_matches_reference(out, g["node_energies"], F, S, len(pos), node_tol=3e-5)
+    # bounds: the tolerances of the force path, or eight times the deviation of the reference's own float evaluator
+    # from these double vectors on the same input (stored beside them), whichever is larger: on a 40-atom cell the
+    # FP32 resolution of the model itself can come close to the stress tolerance
+    floor = 8.0 * g["float_deviation"]
+    assert abs(out["energy"] - g["node_energies"].sum()) / len(pos) <= TOL_E
+    assert np.abs(out["energies"] - g["node_energies"]).max() <= max(TOL_E, floor[0])
+    assert np.abs(out["forces"] - F).max() <= max(TOL_F, floor[1])
+    assert np.abs(out["stress"] - S).max() <= max(TOL_S, floor[2])
 
 
 def test_headline_configuration_vs_reference_evaluator(pkg, model_path):
