@@ -9,7 +9,7 @@ from its own kernels.  This script fills the interface's argument blocks once, f
 fused coordinate reverse of either plugin on the same device buffers, times every launch with CUDA
 events (L2 flushed in between), and compares the outputs.
 
-    python oracle/kernel_ab.py [--cells 10] [--repeats 10] [--out gpurun_out/kernel_ab.json]
+    python oracle/kernel_ab.py [--cells 10] [--repeats 10] [--out report.json]
 """
 from __future__ import annotations
 
@@ -81,7 +81,7 @@ def main(argv=None):
     parser = argparse.ArgumentParser()
     parser.add_argument("--cells", type=int, default=10)
     parser.add_argument("--repeats", type=int, default=10)
-    parser.add_argument("--out", default=str(ROOT / "gpurun_out" / "kernel_ab.json"))
+    parser.add_argument("--out", default=None, help="also write the report to this file")
     args = parser.parse_args(argv)
 
     import torch
@@ -200,8 +200,9 @@ def main(argv=None):
               "max_abs_value": {k: float(np.abs(a[k]).max()) for k in ("phi", "h1_adj", "forces")}}
     for k in ("phi", "h1_adj", "forces"):
         assert report["max_abs_difference"][k] <= 2e-4 * max(1.0, report["max_abs_value"][k]), (k, report["max_abs_difference"][k])
-    Path(args.out).parent.mkdir(parents=True, exist_ok=True)
-    Path(args.out).write_text(json.dumps(report, indent=1))
+    if args.out:
+        Path(args.out).parent.mkdir(parents=True, exist_ok=True)
+        Path(args.out).write_text(json.dumps(report, indent=1))
     print(json.dumps(report))
     return report
 
