@@ -41,8 +41,9 @@ typedef struct sxb_model_info {
 
 /* Replaces the evaluator constructor MACEKokkos<float>(filename)
  * (libsymmetrix/source/mace_kokkos_model.cpp:146; loader twin mace.cpp:2660-2959; Python binding
- * symmetrix/source/cpp/mace_kokkos.cpp:262).  Reads a format-v4 compact model JSON, builds the
- * spline tables and uploads the weights to CUDA device `device_ordinal`. */
+ * symmetrix/source/cpp/mace_kokkos.cpp:262).  Reads a model JSON (format version 4 in the m0_composite or
+ * pre_linear_up basis, or format versions 1 / 2; radial networks or stored pair splines; one or two
+ * interactions), builds the spline tables and uploads the weights to CUDA device `device_ordinal`. */
 int sxb_create(const char* model_json_path, int device_ordinal, sxb_evaluator** out);
 /* The same with a named prediction head of a multi-head model file (the `head` argument of the
  * reference constructor; select_prediction_head, libsymmetrix/source/prediction_heads.hpp:10-90):
