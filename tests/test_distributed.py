@@ -1,4 +1,5 @@
-"""Domain decomposition: exchange plan on CPU (gloo, 2 ranks), decomposed evaluation on the GPU."""
+"""Domain decomposition: brick selection and the exchange plan on CPU (gloo, 2 / 4 / 8 ranks), decomposed evaluation and
+the peer exchange on the GPU."""
 import os
 import subprocess
 import sys
@@ -85,14 +86,18 @@ def _plan_worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-def test_exchange_plan_two_ranks_gloo(tmp_path):
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_exchange_plan_over_gloo_ranks(tmp_path, world):
+    """The exchange plan on 2, 4 and 8 CPU ranks (brick grids 2x1x1, 2x2x1, 2x2x2): the forward exchange reproduces every
+    ghost position and the reverse exchange returns every ghost's contribution to its owner."""
     import torch.multiprocessing as mp
 
-    port = 29500 + os.getpid() % 2000
-    mp.spawn(_plan_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
-    r0, r1 = np.load(tmp_path / "r0.npy"), np.load(tmp_path / "r1.npy")
-    assert r0[0] and r0[1] and r1[0] and r1[1]
-    assert r0[2] + r1[2] == 4 * 2 * 2 * 5
+    port = 29500 + (os.getpid() + 17 * world) % 2000
+    mp.spawn(_plan_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    results = [np.load(tmp_path / f"r{rank}.npy") for rank in range(world)]
+    assert all(r[0] and r[1] for r in results)
+    assert sum(int(r[2]) for r in results) == 4 * 2 * 2 * 5
+    assert all(r[2] > 0 and r[3] > 0 for r in results)
 
 
 @pytest.mark.gpu
